@@ -1,0 +1,79 @@
+// Per-row argmax over the vocabulary and greedy prefix acceptance, on device.
+// Reference: k_topk with k = 1 (engine/kernels/ops.hip:702-716: maximum value, ties -> lowest index) and the
+// host acceptance loop of the MTP driver (engine/bench/spec27b.cpp:92-97). The reference copies the ids to the
+// host and compares there; here the comparison runs on the device so that no logits or ids round-trip is needed.
+#include "hp_common.cuh"
+#include "kernels.h"
+
+namespace hp {
+namespace {
+
+constexpr int AM_CHUNK = 8192;   // elements per stage-1 block
+
+__device__ __forceinline__ void am_better(float& bv, int& bi, float v, int i) {
+    if (v > bv || (v == bv && i < bi && i >= 0)) { bv = v; bi = i; }
+}
+__device__ __forceinline__ void am_block_reduce(float& bv, int& bi, float* sv, int* si) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, off); const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+        am_better(bv, bi, ov, oi);
+    }
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    if (l == 0) { sv[w] = bv; si[w] = bi; }
+    __syncthreads();
+    if (w == 0) {
+        bv = l < (int)(blockDim.x >> 5) ? sv[l] : -INFINITY; bi = l < (int)(blockDim.x >> 5) ? si[l] : -1;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, off); const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+            am_better(bv, bi, ov, oi);
+        }
+    }
+}
+__global__ void __launch_bounds__(256) k_argmax_part(const float* __restrict__ x, int n, int ld, float* __restrict__ pv, int* __restrict__ pi) {
+    __shared__ float sv[8]; __shared__ int si[8];
+    const int r = blockIdx.y, c0 = blockIdx.x * AM_CHUNK, c1 = min(n, c0 + AM_CHUNK);
+    const float* xr = x + (size_t)r * ld;
+    float bv = -INFINITY; int bi = -1;
+    for (int i = c0 + threadIdx.x; i < c1; i += 256) { const float v = xr[i]; if (v > bv) { bv = v; bi = i; } }
+    am_block_reduce(bv, bi, sv, si);
+    if (threadIdx.x == 0) { pv[(size_t)r * gridDim.x + blockIdx.x] = bv; pi[(size_t)r * gridDim.x + blockIdx.x] = bi; }
+}
+__global__ void __launch_bounds__(256) k_argmax_final(const float* __restrict__ pv, const int* __restrict__ pi, int np, int* __restrict__ ids, float* __restrict__ vals) {
+    __shared__ float sv[8]; __shared__ int si[8];
+    const int r = blockIdx.x;
+    float bv = -INFINITY; int bi = -1;
+    for (int i = threadIdx.x; i < np; i += 256) am_better(bv, bi, pv[(size_t)r * np + i], pi[(size_t)r * np + i]);
+    am_block_reduce(bv, bi, sv, si);
+    if (threadIdx.x == 0) { ids[r] = bi; if (vals) vals[r] = bv; }
+}
+// out[0] = mm (accepted drafts), out[1] = bonus token ids[mm]
+__global__ void k_accept(const int* __restrict__ ids, const int* __restrict__ drafts, int n_draft, int* __restrict__ out) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        int mm = 0; while (mm < n_draft && ids[mm] == drafts[mm]) ++mm;
+        out[0] = mm; out[1] = ids[mm];
+    }
+}
+
+}  // namespace
+
+size_t argmax_scratch_bytes(int R, int n) { return (size_t)R * ((n + AM_CHUNK - 1) / AM_CHUNK) * 8; }
+
+int argmax_rows(const float* logits, int R, int n, int ld, int* ids, float* vals, void* scratch, cudaStream_t s) {
+    HP_REQUIRE(R >= 1 && n >= 1 && ld >= n && scratch, "argmax_rows: bad arguments R=%d n=%d ld=%d", R, n, ld);
+    const int np = (n + AM_CHUNK - 1) / AM_CHUNK;
+    float* pv = (float*)scratch; int* pi = (int*)(pv + (size_t)R * np);
+    k_argmax_part<<<dim3(np, R), 256, 0, s>>>(logits, n, ld, pv, pi);
+    k_argmax_final<<<R, 256, 0, s>>>(pv, pi, np, ids, vals);
+    HP_CUDA(cudaGetLastError());
+    return HP_OK;
+}
+int accept_greedy(const int* ids, const int* drafts, int n_draft, int* out, cudaStream_t s) {
+    HP_REQUIRE(n_draft >= 0 && n_draft <= 31, "accept_greedy: n_draft=%d out of range", n_draft);
+    k_accept<<<1, 32, 0, s>>>(ids, drafts, n_draft, out);
+    HP_CUDA(cudaGetLastError());
+    return HP_OK;
+}
+
+}  // namespace hp

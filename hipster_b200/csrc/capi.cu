@@ -1,0 +1,98 @@
+// extern "C" boundary: argument checks, status codes, last-error string. No exceptions cross it.
+#include "hp_common.cuh"
+#include "kernels.h"
+#include "../../include/hipster_b200.h"
+#include <cstdarg>
+#include <cstdio>
+#include <string>
+#include <exception>
+
+namespace hp {
+static thread_local std::string g_last_error;
+void set_error(const char* fmt, ...) {
+    char buf[512]; va_list ap; va_start(ap, fmt); vsnprintf(buf, sizeof buf, fmt, ap); va_end(ap);
+    g_last_error = buf;
+}
+int cuda_fail(cudaError_t e, const char* what, const char* file, int line) {
+    set_error("CUDA error %d (%s) in %s @%s:%d", (int)e, cudaGetErrorString(e), what, file, line);
+    return HP_ECUDA;
+}
+// one status word per process, set by kernels whose bounded waits gave up
+static int* g_dev_err = nullptr;
+int* device_err_flag() {
+    if (!g_dev_err) { if (cudaMalloc(&g_dev_err, sizeof(int)) != cudaSuccess) return nullptr; cudaMemset(g_dev_err, 0, sizeof(int)); }
+    return g_dev_err;
+}
+}  // namespace hp
+
+#define HP_GUARD_BEGIN try {
+#define HP_GUARD_END } catch (const std::exception& e) { hp::set_error("exception: %s", e.what()); return HP_ESTATE; } catch (...) { hp::set_error("unknown exception"); return HP_ESTATE; }
+
+extern "C" {
+
+const char* hp_last_error(void) { return hp::g_last_error.c_str(); }
+int hp_version(void) { return 100; }
+
+int hp_device_status(void* stream) {
+    HP_GUARD_BEGIN
+    int* f = hp::device_err_flag();
+    if (!f) { hp::set_error("cannot allocate the device status word"); return HP_ENOMEM; }
+    int h = 0;
+    HP_CUDA(cudaMemcpyAsync(&h, f, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    HP_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    if (h != 0) { HP_CUDA(cudaMemsetAsync(f, 0, sizeof(int), (cudaStream_t)stream)); hp::set_error("a kernel gave up a bounded wait (device status %d)", h); return h; }
+    return HP_OK;
+    HP_GUARD_END
+}
+
+size_t hp_xq8_q_bytes(int R, int K) { return hp::xq_q_bytes(R, K); }
+size_t hp_xq8_sc_bytes(int R, int K) { return hp::xq_sc_floats(R, K) * sizeof(float); }
+
+int hp_quantize_x_q8(const float* x_dev, int ldx, int R, int K, void* xq_q_dev, void* xq_sc_dev, void* stream) {
+    HP_GUARD_BEGIN
+    HP_REQUIRE(x_dev && xq_q_dev && xq_sc_dev, "hp_quantize_x_q8: null pointer");
+    return hp::quantize_x_q8(x_dev, ldx, hp::XQ8F{xq_q_dev, xq_sc_dev}, R, K, (cudaStream_t)stream);
+    HP_GUARD_END
+}
+int hp_xq8_unpack(const void* xq_q_dev, const void* xq_sc_dev, int R, int K, int8_t* q_dev, float* d_dev, float* s_dev, void* stream) {
+    HP_GUARD_BEGIN
+    HP_REQUIRE(xq_q_dev && xq_sc_dev && q_dev && d_dev && s_dev, "hp_xq8_unpack: null pointer");
+    HP_REQUIRE(R >= 1 && K > 0 && K % 64 == 0, "hp_xq8_unpack: bad shape R=%d K=%d", R, K);
+    return hp::xq8_unpack(hp::XQ8F{(void*)xq_q_dev, (void*)xq_sc_dev}, R, K, q_dev, d_dev, s_dev, (cudaStream_t)stream);
+    HP_GUARD_END
+}
+int hp_dequant_q4k(const void* w_dev, size_t nblk, float* out_dev, void* stream) {
+    HP_GUARD_BEGIN
+    HP_REQUIRE(w_dev && out_dev, "hp_dequant_q4k: null pointer");
+    return hp::dequant_q4k(w_dev, nblk, out_dev, (cudaStream_t)stream);
+    HP_GUARD_END
+}
+int hp_gemv_q4k_q8(const void* w_dev, const void* xq_q_dev, const void* xq_sc_dev, float* y_dev, int N, int K, int R, int ldy, void* stream) {
+    HP_GUARD_BEGIN
+    HP_REQUIRE(w_dev && xq_q_dev && xq_sc_dev && y_dev, "hp_gemv_q4k_q8: null pointer");
+    HP_REQUIRE(((uintptr_t)w_dev & 15) == 0, "hp_gemv_q4k_q8: weights must be 16-byte aligned");
+    return hp::gemv_q4k_q8(w_dev, hp::XQ8F{(void*)xq_q_dev, (void*)xq_sc_dev}, y_dev, N, K, R, ldy, hp::device_err_flag(), (cudaStream_t)stream, false);
+    HP_GUARD_END
+}
+int hp_gemv_q4k_f32(const void* w_dev, const float* x_dev, float* y_dev, int N, int K, int R, void* stream) {
+    HP_GUARD_BEGIN
+    HP_REQUIRE(w_dev && x_dev && y_dev, "hp_gemv_q4k_f32: null pointer");
+    HP_REQUIRE(((uintptr_t)w_dev & 15) == 0, "hp_gemv_q4k_f32: weights must be 16-byte aligned");
+    return hp::gemv_q4k_f32(w_dev, x_dev, y_dev, N, K, R, (cudaStream_t)stream);
+    HP_GUARD_END
+}
+size_t hp_argmax_scratch_bytes(int R, int n) { return (R < 1 || n < 1) ? 0 : hp::argmax_scratch_bytes(R, n); }
+int hp_argmax(const float* logits_dev, int R, int n, int ld, int* ids_dev, float* vals_dev, void* scratch_dev, void* stream) {
+    HP_GUARD_BEGIN
+    HP_REQUIRE(logits_dev && ids_dev, "hp_argmax: null pointer");
+    return hp::argmax_rows(logits_dev, R, n, ld, ids_dev, vals_dev, scratch_dev, (cudaStream_t)stream);
+    HP_GUARD_END
+}
+int hp_accept_greedy(const int* ids_dev, const int* drafts_dev, int n_draft, int* out_dev, void* stream) {
+    HP_GUARD_BEGIN
+    HP_REQUIRE(ids_dev && out_dev && (drafts_dev || n_draft == 0), "hp_accept_greedy: null pointer");
+    return hp::accept_greedy(ids_dev, drafts_dev, n_draft, out_dev, (cudaStream_t)stream);
+    HP_GUARD_END
+}
+
+}  // extern "C"

@@ -1,0 +1,60 @@
+/* hipster_b200 -- C ABI of the B200-native MTP speculative-decode path.
+ *
+ * The reference (dzannotti/hipster) has no C ABI: its engine is a C++ class API (engine/src/qwen35.h:50-98,
+ * engine/src/qwen4exp.h:54-90) over free kernel launchers taking device pointers and a stream
+ * (engine/kernels/gemv.h, ops.h, fn.h), consumed by the token-level `struct Backend` of the server
+ * (front/serve.cpp:28-41) and by the MTP drivers (engine/bench/spec27b.cpp, specfn.cpp, batchfn.cpp).
+ * Every entry point below names the reference interface it replaces.
+ *
+ * Conventions: all functions return 0 on success or an HP_E* code; hp_last_error() gives the message of the
+ * last failure on the calling thread's library instance (the reference throws std::runtime_error instead,
+ * engine/src/qwen35.cpp:10,290-298). Nothing throws across this boundary. `stream` is a cudaStream_t passed as
+ * void* (NULL = default stream). Pointers named *_dev are device memory, *_host host memory.
+ * Not thread-safe per handle: one caller thread per engine, like the reference (front/serve.cpp:249).
+ */
+#ifndef HIPSTER_B200_H
+#define HIPSTER_B200_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { HP_OK = 0, HP_EINVAL = 1, HP_ECUDA = 2, HP_ENOMEM = 3, HP_ETIMEOUT = 4, HP_ESTATE = 5, HP_ECOMM = 6 };
+
+const char* hp_last_error(void);
+int hp_version(void);
+/* Reads (and clears) the device-side status word that kernels set when a bounded wait gave up. */
+int hp_device_status(void* stream);
+
+/* ------------------------------------------------------------------ kernel level (engine/kernels/gemv.h, ops.h) */
+
+/* Size of the quantised-activation buffers for R rows of K elements (reference: struct XQ8, gemv.h:8).
+ * The layout is private to the library; buffers must be zero-initialised once by the caller. */
+size_t hp_xq8_q_bytes(int R, int K);
+size_t hp_xq8_sc_bytes(int R, int K);
+/* x f32 [R][ldx] -> int8 per 32 elements. Replaces quantize_x_q8 (gemv.h:9, gemv.hip:36-51). */
+int hp_quantize_x_q8(const float* x_dev, int ldx, int R, int K, void* xq_q_dev, void* xq_sc_dev, void* stream);
+/* Converts the private layout to the reference's XQ8 rows: q [R][K] i8, d [R][K/32], s [R][K/32] (gemv.h:7-8). */
+int hp_xq8_unpack(const void* xq_q_dev, const void* xq_sc_dev, int R, int K, int8_t* q_dev, float* d_dev, float* s_dev, void* stream);
+/* Dequantise nblk Q4_K blocks to f32. Replaces the device twins of dequant_q4_K (quant.h:43-53; ops.hip:154-171). */
+int hp_dequant_q4k(const void* w_dev, size_t nblk, float* out_dev, void* stream);
+/* y[r][n] = sum_k W[n][k] x[r][k], W = Q4_K [N][K/256] blocks, x quantised by hp_quantize_x_q8, y f32 [R][ldy].
+ * 1 <= R <= 32; the result of a row does not depend on R. Replaces gemv_q8 / gemv_multi / gemv_wmma
+ * (gemv.h:23-33, gemv.hip:291-367,602-672,1306-1331). */
+int hp_gemv_q4k_q8(const void* w_dev, const void* xq_q_dev, const void* xq_sc_dev, float* y_dev, int N, int K, int R, int ldy, void* stream);
+/* f32-activation baseline, R <= 8, y [R][N]. Replaces gemv_q4_K_f32 (gemv.h:57, gemv.hip:1177-1216). */
+int hp_gemv_q4k_f32(const void* w_dev, const float* x_dev, float* y_dev, int N, int K, int R, void* stream);
+/* Row-wise argmax (maximum value, lowest index on ties) of logits [R][ld] over n entries.
+ * Replaces argmax_topk with k = 1 (ops.h:118, ops.hip:702-716). scratch_dev: hp_argmax_scratch_bytes(R, n) bytes. */
+size_t hp_argmax_scratch_bytes(int R, int n);
+int hp_argmax(const float* logits_dev, int R, int n, int ld, int* ids_dev, float* vals_dev, void* scratch_dev, void* stream);
+/* Greedy prefix acceptance on device: out_dev[0] = number of accepted drafts mm, out_dev[1] = ids[mm] (bonus token).
+ * ids_dev holds n_draft+1 target argmaxes. Replaces the host loop of engine/bench/spec27b.cpp:92-97. */
+int hp_accept_greedy(const int* ids_dev, const int* drafts_dev, int n_draft, int* out_dev, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,99 @@
+"""ctypes loader of the CPU oracle (TEST INFRASTRUCTURE: imported only by tests/, the smoke check and the
+CPU-baseline leg of bench.py; the product package never imports this module)."""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libhp_oracle.so")
+REF_PATH = os.path.join(HERE, "_ref", "libhipster_ref.so")
+
+_lib = None
+_ref = None
+
+
+def build():
+    subprocess.run(["make", "-C", HERE, "-s"], check=True)
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            build()
+        _lib = ctypes.CDLL(LIB_PATH)
+        for name in ("orc_f16_to_f32", "orc_expf", "orc_log1pf_pos", "orc_sigmoid", "orc_silu", "orc_softplus"):
+            getattr(_lib, name).restype = ctypes.c_float
+        for name in ("orc_expf", "orc_log1pf_pos", "orc_sigmoid", "orc_silu", "orc_softplus"):
+            getattr(_lib, name).argtypes = [ctypes.c_float]
+        _lib.orc_f32_to_f16.restype = ctypes.c_uint16
+        _lib.orc_f32_to_f16.argtypes = [ctypes.c_float]
+    return _lib
+
+
+def ref():
+    """The reference's own host code (None when oracle/_ref was not built)."""
+    global _ref
+    if _ref is None and os.path.exists(REF_PATH):
+        _ref = ctypes.CDLL(REF_PATH)
+        _ref.ref_f16_to_f32.restype = ctypes.c_float
+        _ref.ref_f32_to_f16.restype = ctypes.c_uint16
+        _ref.ref_f32_to_f16.argtypes = [ctypes.c_float]
+    return _ref
+
+
+def P(a):
+    return a.ctypes.data_as(ctypes.c_void_p)
+
+
+def dequant_q4k(blocks):
+    blocks = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1)
+    nblk = blocks.size // 144
+    out = np.empty(nblk * 256, dtype=np.float32)
+    lib().orc_dequant_q4k(P(blocks), ctypes.c_size_t(nblk), P(out))
+    return out
+
+
+def quantize_x_q8(x):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    R, K = x.shape
+    q = np.empty((R, K), dtype=np.int8); d = np.empty((R, K // 32), dtype=np.float32); s = np.empty_like(d)
+    lib().orc_quantize_x_q8(P(x), R, K, P(q), P(d), P(s))
+    return q, d, s
+
+
+def gemv_q4k_f32(W, x, N, K, tpr=4):
+    x = np.ascontiguousarray(x, dtype=np.float32); R = x.shape[0]
+    y = np.empty((R, N), dtype=np.float32)
+    lib().orc_gemv_q4k_f32(P(W), P(x), P(y), N, K, R, tpr)
+    return y
+
+
+def gemv_q4k_q8(W, q, d, s, N, K):
+    R = q.shape[0]
+    y = np.empty((R, N), dtype=np.float32)
+    lib().orc_gemv_q4k_q8(P(W), P(np.ascontiguousarray(q)), P(np.ascontiguousarray(d)), P(np.ascontiguousarray(s)), P(y), N, K, R, N)
+    return y
+
+
+def gemv_q4k_double(W, x, N, K):
+    x = np.ascontiguousarray(x, dtype=np.float32); R = x.shape[0]
+    y = np.empty((R, N), dtype=np.float64); mag = np.empty((R, N), dtype=np.float64)
+    lib().orc_gemv_q4k_double(P(W), P(x), P(y), P(mag), N, K, R)
+    return y, mag
+
+
+def argmax(logits):
+    logits = np.ascontiguousarray(logits, dtype=np.float32); R, n = logits.shape
+    ids = np.empty(R, dtype=np.int32); vals = np.empty(R, dtype=np.float32)
+    lib().orc_argmax(P(logits), R, n, n, P(ids), P(vals))
+    return ids, vals
+
+
+def accept(ids, drafts):
+    ids = np.ascontiguousarray(ids, dtype=np.int32); drafts = np.ascontiguousarray(drafts, dtype=np.int32)
+    bonus = ctypes.c_int(0)
+    mm = lib().orc_accept(P(ids), P(drafts), int(drafts.size), ctypes.byref(bonus))
+    return mm, bonus.value
