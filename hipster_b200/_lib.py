@@ -4,7 +4,7 @@ import os
 import re
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libhipster_b200.so")
+LIB_PATH = os.environ.get("HIPSTER_B200_LIB") or os.path.join(HERE, "libhipster_b200.so")
 HEADER = os.path.join(HERE, "..", "include", "hipster_b200.h")
 
 _lib = None

@@ -23,6 +23,18 @@ int* device_err_flag() {
     if (!g_dev_err) { if (cudaMalloc(&g_dev_err, sizeof(int)) != cudaSuccess) return nullptr; cudaMemset(g_dev_err, 0, sizeof(int)); }
     return g_dev_err;
 }
+// workspace of the kernel-level GEMV entry point (allocated on first use; the engine owns its own)
+static GemvWorkspace g_ws = {nullptr, 0, nullptr};
+int default_gemv_workspace(GemvWorkspace* out, size_t need) {
+    if (need > g_ws.part_bytes) {
+        if (g_ws.part) HP_CUDA(cudaFree(g_ws.part));
+        g_ws.part = nullptr; g_ws.part_bytes = 0;
+        HP_CUDA(cudaMalloc(&g_ws.part, need));
+        g_ws.part_bytes = need;
+    }
+    g_ws.err = device_err_flag();
+    *out = g_ws; return HP_OK;
+}
 }  // namespace hp
 
 #define HP_GUARD_BEGIN try {
@@ -71,9 +83,12 @@ int hp_gemv_q4k_q8(const void* w_dev, const void* xq_q_dev, const void* xq_sc_de
     HP_GUARD_BEGIN
     HP_REQUIRE(w_dev && xq_q_dev && xq_sc_dev && y_dev, "hp_gemv_q4k_q8: null pointer");
     HP_REQUIRE(((uintptr_t)w_dev & 15) == 0, "hp_gemv_q4k_q8: weights must be 16-byte aligned");
-    return hp::gemv_q4k_q8(w_dev, hp::XQ8F{(void*)xq_q_dev, (void*)xq_sc_dev}, y_dev, N, K, R, ldy, hp::device_err_flag(), (cudaStream_t)stream, false);
+    HP_REQUIRE(N > 0 && K > 0 && K % 256 == 0 && R >= 1 && R <= 32, "hp_gemv_q4k_q8: bad shape N=%d K=%d R=%d", N, K, R);
+    hp::GemvWorkspace ws; { const int rc = hp::default_gemv_workspace(&ws, (size_t)4 * R * N * sizeof(float)); if (rc) return rc; }
+    return hp::gemv_q4k_q8(w_dev, hp::XQ8F{(void*)xq_q_dev, (void*)xq_sc_dev}, y_dev, N, K, R, ldy, ws, (cudaStream_t)stream, false);
     HP_GUARD_END
 }
+int hp_gemv_parts(int N, int K) { return (N > 0 && K > 0 && K % 256 == 0) ? hp::gemv_parts(N, K) : 0; }
 int hp_gemv_q4k_f32(const void* w_dev, const float* x_dev, float* y_dev, int N, int K, int R, void* stream) {
     HP_GUARD_BEGIN
     HP_REQUIRE(w_dev && x_dev && y_dev, "hp_gemv_q4k_f32: null pointer");

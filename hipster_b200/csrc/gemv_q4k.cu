@@ -4,146 +4,263 @@
 // the T-invariant production kernel k_gemv_wmma<Q4_K> (gemv.hip:602-672) and the f32-activation baseline
 // k_gemv_q4_K_f32 (gemv.hip:1177-1216).
 //
-// Design (sm_100a): weights stay in the 144-byte ggml Q4_K block format, [N][K/256] blocks, rows contiguous.
-// A CTA owns 16 consecutive weight rows. A producer warp streams them with 1-D bulk async copies
-// (cp.async.bulk + mbarrier) through a ring of shared-memory stages, 4 blocks (576 B) of every row per stage;
-// four consumer warps take one block of the stage each (block b belongs to warp b % 4), unpack the nibbles in
-// registers and feed them to the int8 tensor-core tile mma.m16n8k32 (weights on M, verify rows on N = 8), which
-// yields the exact int32 dot of every 32-element sub-block. One fp32 update per sub-block follows, in block order:
+// Design (sm_100a). Weights stay in the 144-byte ggml Q4_K block format, [N][K/256] blocks, rows contiguous, and
+// every weight byte is read from HBM once per launch. The launch is one persistent CTA per SM (148 CTAs x 12 warps).
+// K is cut into P equal parts (P = 1, 2 or 4, a function of the tensor shape only, chosen so that the 16-row tiles
+// divide evenly over the SMs); the 148/P CTAs of part p share the tiles evenly, and inside a CTA the stream of units
+// (16 rows x 2 blocks, tile-major then along K) is divided evenly and contiguously over the 12 warps. Each warp runs
+// its own ring of 1-D bulk async copies (cp.async.bulk + mbarrier, 16 row pieces of 288 B per stage), unpacks the
+// nibbles in registers and feeds the int8 tensor-core tile mma.m16n8k32 (weights on M, verify rows on N = 8), which
+// yields the exact int32 dot of every 32-element sub-block. The quantised activations of the CTA's K part are staged
+// once per CTA in shared memory by bulk copies. One fp32 update per sub-block follows, in block order:
 //     acc = fmaf((d*sc) * xd, (float)idot, acc);  acc = fmaf(-(dmin*mn), xs, acc);
-// and the four per-warp partial sums are added in warp order. The order depends on the tensor shape only, never on
-// the number of verify rows, so a row of an n+1-row verify pass is bit-identical to the same row of a 1-row pass
-// (the reference's "T-invariance", gemv.hip:600-601). Each weight byte is read from HBM once per pass.
+// A tile whose blocks are spread over several warps of the CTA is finished through shared memory: the partial sums
+// are added in warp order. Each K part writes its own output plane; the planes are added in part order by the
+// consumer (or by the small reduction kernel of the public entry point). No atomics, no cross-CTA traffic.
+// The partition is a function of (N, K) only, never of the number of verify rows, so a row of an n+1-row verify pass
+// is bit-identical to the same row of a 1-row pass (the reference's "T-invariance", gemv.hip:600-601), and a CPU can
+// reproduce the result bit for bit.
 #include "hp_common.cuh"
 #include "kernels.h"
 
 namespace hp {
 namespace {
 
-constexpr int GEMV_ROWS = 16;            // weight rows per CTA (one mma M tile)
-constexpr int GEMV_KS = 4;               // consumer warps = K slices
-constexpr int GEMV_STAGES = 6;
-constexpr int GEMV_ROW_BYTES = 4 * 144;  // bytes of one row in one stage
-constexpr int GEMV_ROW_STRIDE = GEMV_ROW_BYTES + 96;   // 672 = 5*128 + 32: rows land on distinct 32-byte bank groups
-constexpr int GEMV_STAGE_BYTES = GEMV_ROWS * GEMV_ROW_STRIDE;
-constexpr int GEMV_THREADS = (GEMV_KS + 1) * 32;
-
-struct GemvSmem {
-    alignas(128) uint8_t ring[GEMV_STAGES][GEMV_STAGE_BYTES];
-    alignas(16) float4 scr[GEMV_KS][4][GEMV_ROWS];   // per warp: {s0(2j), -m(2j), s0(2j+1), -m(2j+1)} [j][row]
-    alignas(8) unsigned long long full[GEMV_STAGES];
-    alignas(8) unsigned long long empty[GEMV_STAGES];
+constexpr int SK_STAGES = GEMV_STAGES;
+constexpr int SK_THREADS = GEMV_WARPS * 32;
+constexpr int SK_SCR_BYTES = 8 * 16 * 16;          // per warp: [8 sub-blocks][16 rows] float4 {s0, s0, -m, -m}
+template <int CB> struct SkGeom {
+    static constexpr int ROW_STRIDE = CB == 2 ? 288 : 160;   // 288 = 2*128+32, 160 = 128+32: rows land on distinct 32-byte bank groups
+    static constexpr int STAGE_BYTES = 16 * ROW_STRIDE;
+    static constexpr int FIXED = GEMV_WARPS * SK_STAGES * STAGE_BYTES + GEMV_WARPS * SK_SCR_BYTES + 1024;
 };
 
-template <int NT>
-__global__ void __launch_bounds__(GEMV_THREADS) k_gemv_q4k_q8(const uint8_t* __restrict__ W, const uint4* __restrict__ xq, const float4* __restrict__ xsc,
-                                                               float* __restrict__ y, int N, int nb, int R, int ldy, int* __restrict__ err) {
-    extern __shared__ __align__(128) uint8_t smem_raw[];
-    GemvSmem& sm = *reinterpret_cast<GemvSmem*>(smem_raw);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row0 = blockIdx.x * GEMV_ROWS;
-    const int nrows = min(GEMV_ROWS, N - row0);
-    const int nst = (nb + 3) >> 2;
-    const size_t row_bytes = (size_t)nb * 144;
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+    float2 r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(reinterpret_cast<unsigned long long&>(r))
+        : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)));
+    return r;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    float2 r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(reinterpret_cast<unsigned long long&>(r))
+        : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)));
+    return r;
+}
+// D = A * B + 0x4B400000 per element
+__device__ __forceinline__ void mma_u8s8_magic(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0x4B400000));
+}
+__device__ __forceinline__ void fma2(float2& acc, float2 a, float2 b) {   // acc = a * b + acc, per lane, one rounding each
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(reinterpret_cast<unsigned long long&>(acc))
+        : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)));
+}
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < GEMV_STAGES; ++s) { mbar_init(smem_u32(&sm.full[s]), 1); mbar_init(smem_u32(&sm.empty[s]), GEMV_KS); }
+template <int NT, int CB>
+__global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __restrict__ W, const uint4* __restrict__ xq, const float4* __restrict__ xsc,
+                                                                float* __restrict__ y, int N, int nb, int P, int R, int ldy, size_t part_stride,
+                                                                int* __restrict__ err) {
+    using Geo = SkGeom<CB>;
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t* ring_all = smem;
+    float4* scr_all = reinterpret_cast<float4*>(smem + GEMV_WARPS * SK_STAGES * Geo::STAGE_BYTES);
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + GEMV_WARPS * SK_STAGES * Geo::STAGE_BYTES + GEMV_WARPS * SK_SCR_BYTES);
+    const int nbp = nb / P;                                // blocks of this CTA's K part
+    const uint4* xq_s = reinterpret_cast<const uint4*>(smem + Geo::FIXED);
+    const float4* xsc_s = reinterpret_cast<const float4*>(smem + Geo::FIXED + NT * nbp * 2048);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const GemvCta ct = gemv_cta(N, nb, P, blockIdx.x);
+    const int C = nbp / CB, kb0 = ct.part * nbp;
+    const int cu = (ct.t1 - ct.t0) * C;                    // units of this CTA
+    const int weff = cu < GEMV_WARPS ? cu : GEMV_WARPS;
+    const int u0 = warp < weff ? gemv_warp_start(cu, weff, warp) : 0, u1 = warp < weff ? gemv_warp_start(cu, weff, warp + 1) : 0;
+    const int nunits = u1 - u0;
+    uint8_t* ring = ring_all + warp * SK_STAGES * Geo::STAGE_BYTES;
+    float4* scr = scr_all + warp * (SK_SCR_BYTES / 16);
+    const uint32_t bar0 = smem_u32(&bars[warp * SK_STAGES]);
+    const uint32_t xbar = smem_u32(&bars[GEMV_WARPS * SK_STAGES]);
+    const uint32_t row_bytes = (uint32_t)nb * 144u;
+    constexpr uint32_t unit_bytes = CB * 144u;
+    y += (size_t)ct.part * part_stride;
+
+    if (lane == 0) {
+        for (int s = 0; s < SK_STAGES; ++s) mbar_init(bar0 + 8 * s, 1);
+        if (warp == 0) mbar_init(xbar, 1);
         fence_barrier_init();
     }
     __syncthreads();
 
-    if (warp == GEMV_KS) {
-        // ---------------- producer: weights do not depend on the previous kernel, so streaming starts at once
-        const uint8_t* src = W + (size_t)(row0 + lane) * row_bytes;
-        for (int i = 0; i < nst; ++i) {
-            const int s = i % GEMV_STAGES;
-            if (i >= GEMV_STAGES) { if (!mbar_wait(smem_u32(&sm.empty[s]), ((i / GEMV_STAGES) - 1) & 1, err)) break; }
-            const uint32_t bytes = (uint32_t)min(4, nb - 4 * i) * 144u;
-            if (lane == 0) mbar_expect_tx(smem_u32(&sm.full[s]), bytes * (uint32_t)nrows);
-            __syncwarp();
-            if (lane < nrows) bulk_g2s(smem_u32(&sm.ring[s][lane * GEMV_ROW_STRIDE]), src + (size_t)i * GEMV_ROW_BYTES, bytes, smem_u32(&sm.full[s]));
+    // issue cursor (tile, chunk) of the next unit to fetch; advanced incrementally, no divisions in the loop
+    const int first_tile = ct.t0 + (nunits ? u0 / C : 0);
+    int it_tile = first_tile, it_chunk = nunits ? u0 % C : 0, it_i = 0;
+    const uint8_t* it_src = W + ((size_t)it_tile * 16 + (lane & 15)) * row_bytes + (size_t)(kb0 + it_chunk * CB) * 144;
+    const uint32_t ring_lane = smem_u32(ring) + (lane & 15) * Geo::ROW_STRIDE;
+    auto issue = [&]() {
+        const int s = it_i % SK_STAGES;
+        const int nrows = min(16, N - it_tile * 16);
+        const uint32_t bar = bar0 + 8 * s;
+        if (lane == 0) mbar_expect_tx(bar, unit_bytes * (uint32_t)nrows);
+        __syncwarp();
+        if (lane < nrows) bulk_g2s(ring_lane + s * Geo::STAGE_BYTES, it_src, unit_bytes, bar);
+        ++it_i; ++it_chunk; it_src += unit_bytes;
+        if (it_chunk == C) { it_chunk = 0; ++it_tile; it_src += (size_t)16 * row_bytes - (size_t)C * unit_bytes; }
+    };
+    // the weight stream does not depend on the previous kernel: prime the ring before waiting for it
+    for (int i = 0; i < SK_STAGES && i < nunits; ++i) issue();
+
+    pdl_wait();
+    if (threadIdx.x == 0) {   // quantised activations of blocks [kb0, kb0 + nbp), all NT column tiles, by bulk copies
+        mbar_expect_tx(xbar, (uint32_t)NT * nbp * 2560u);
+        for (int n = 0; n < NT; ++n) {
+            bulk_g2s(smem_u32(smem + Geo::FIXED + n * nbp * 2048), xq + ((size_t)n * nb + kb0) * 128, nbp * 2048u, xbar);
+            bulk_g2s(smem_u32(smem + Geo::FIXED + NT * nbp * 2048 + n * nbp * 512), xsc + ((size_t)n * nb + kb0) * 32, nbp * 512u, xbar);
         }
-    } else {
-        // ---------------- consumers
-        const int g = lane >> 2, t = lane & 3;
-        float acc[NT][4];
+    }
+    pdl_launch_dependents();
+
+    float2 acc[NT][2];   // [n][0] = row g, cols 2t,2t+1 ; [n][1] = row g+8
+    auto zero_acc = [&]() {
 #pragma unroll
-        for (int n = 0; n < NT; ++n) { acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f; }
-        const int njj = nb * 4, nsb = nb * 8;
-        pdl_wait();   // activations come from the previous kernel
-        bool ok = true;
-        for (int i = 0; i < nst && ok; ++i) {
-            const int s = i % GEMV_STAGES;
-            ok = mbar_wait(smem_u32(&sm.full[s]), (i / GEMV_STAGES) & 1, err);
-            const int b = 4 * i + warp;
-            if (ok && b < nb) {
-                const uint8_t* st = sm.ring[s] + warp * 144;
-                {   // scale pre-pass: lane -> (row = lane/2, half = lane&1) decodes 4 sub-blocks
-                    const int r = lane >> 1, hf = lane & 1;
-                    const uint4 hdr = *reinterpret_cast<const uint4*>(st + r * GEMV_ROW_STRIDE);
-                    const float d = h2f((uint16_t)(hdr.x & 0xFFFF)), dmin = h2f((uint16_t)(hdr.x >> 16));
-                    float v[8];
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        uint32_t sc, mn; q4k_scale_min(hdr, 4 * hf + k, sc, mn);
-                        v[2 * k] = d * (float)sc; v[2 * k + 1] = -(dmin * (float)mn);
-                    }
-                    sm.scr[warp][2 * hf][r] = make_float4(v[0], v[1], v[2], v[3]);
-                    sm.scr[warp][2 * hf + 1][r] = make_float4(v[4], v[5], v[6], v[7]);
-                }
-                __syncwarp();
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint2 w0 = *reinterpret_cast<const uint2*>(st + g * GEMV_ROW_STRIDE + 16 + 32 * j + 8 * t);
-                    const uint2 w1 = *reinterpret_cast<const uint2*>(st + (g + 8) * GEMV_ROW_STRIDE + 16 + 32 * j + 8 * t);
-                    const uint32_t alo[4] = {w0.x & 0x0F0F0F0Fu, w1.x & 0x0F0F0F0Fu, w0.y & 0x0F0F0F0Fu, w1.y & 0x0F0F0F0Fu};
-                    const uint32_t ahi[4] = {(w0.x >> 4) & 0x0F0F0F0Fu, (w1.x >> 4) & 0x0F0F0F0Fu, (w0.y >> 4) & 0x0F0F0F0Fu, (w1.y >> 4) & 0x0F0F0F0Fu};
-                    const float4 sa = sm.scr[warp][j][g], sb8 = sm.scr[warp][j][g + 8];
-                    const int jj = b * 4 + j, sb = b * 8 + 2 * j;
-#pragma unroll
-                    for (int n = 0; n < NT; ++n) {
-                        const uint4 xf = __ldg(xq + ((size_t)n * njj + jj) * 32 + lane);
-                        const float4 x0 = __ldg(xsc + ((size_t)n * nsb + sb) * 4 + t);
-                        const float4 x1 = __ldg(xsc + ((size_t)n * nsb + sb + 1) * 4 + t);
-                        int c0[4], c1[4];
-                        mma_u8s8(c0, alo, xf.x, xf.y);
-                        mma_u8s8(c1, ahi, xf.z, xf.w);
-                        // low-nibble sub-block 2j
-                        acc[n][0] = fmaf(sa.x * x0.x, (float)c0[0], acc[n][0]);  acc[n][0] = fmaf(sa.y, x0.z, acc[n][0]);
-                        acc[n][1] = fmaf(sa.x * x0.y, (float)c0[1], acc[n][1]);  acc[n][1] = fmaf(sa.y, x0.w, acc[n][1]);
-                        acc[n][2] = fmaf(sb8.x * x0.x, (float)c0[2], acc[n][2]); acc[n][2] = fmaf(sb8.y, x0.z, acc[n][2]);
-                        acc[n][3] = fmaf(sb8.x * x0.y, (float)c0[3], acc[n][3]); acc[n][3] = fmaf(sb8.y, x0.w, acc[n][3]);
-                        // high-nibble sub-block 2j+1
-                        acc[n][0] = fmaf(sa.z * x1.x, (float)c1[0], acc[n][0]);  acc[n][0] = fmaf(sa.w, x1.z, acc[n][0]);
-                        acc[n][1] = fmaf(sa.z * x1.y, (float)c1[1], acc[n][1]);  acc[n][1] = fmaf(sa.w, x1.w, acc[n][1]);
-                        acc[n][2] = fmaf(sb8.z * x1.x, (float)c1[2], acc[n][2]); acc[n][2] = fmaf(sb8.w, x1.z, acc[n][2]);
-                        acc[n][3] = fmaf(sb8.z * x1.y, (float)c1[3], acc[n][3]); acc[n][3] = fmaf(sb8.w, x1.w, acc[n][3]);
-                    }
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&sm.empty[s]));
-        }
-        // ---------------- split-K reduction in warp order (the ring is free: every stage has been consumed)
-        asm volatile("bar.sync 1, %0;" ::"n"(GEMV_KS * 32));
-        float* red = reinterpret_cast<float*>(sm.ring);   // [KS][NT*4][32]
+        for (int n = 0; n < NT; ++n) { acc[n][0] = make_float2(0.f, 0.f); acc[n][1] = make_float2(0.f, 0.f); }
+    };
+    zero_acc();
+    auto store_tile = [&](int tile, const float (&v)[NT][4]) {
 #pragma unroll
         for (int n = 0; n < NT; ++n)
 #pragma unroll
-            for (int k = 0; k < 4; ++k) red[(warp * NT * 4 + n * 4 + k) * 32 + lane] = acc[n][k];
-        asm volatile("bar.sync 1, %0;" ::"n"(GEMV_KS * 32));
-        if (warp == 0) {
+            for (int k = 0; k < 4; ++k) {
+                const int row = tile * 16 + g + ((k & 2) ? 8 : 0), col = n * 8 + 2 * t + (k & 1);
+                if (row < N && col < R) y[(size_t)col * ldy + row] = v[n][k];
+            }
+    };
+    // a tile covered by this warp alone is stored at once; otherwise the partial sum goes to shared memory
+    // (slot 0 = the warp's first tile, slot 1 = its last tile) and is combined after the CTA barrier
+    float* red = reinterpret_cast<float*>(ring_all);   // reused after every warp has drained its ring
+    float part_v[2][NT][4]; bool part_on[2] = {false, false}; int part_tile[2] = {0, 0};
+    auto flush = [&](int tile, bool whole) {
+        float v[NT][4];
+#pragma unroll
+        for (int n = 0; n < NT; ++n) { v[n][0] = acc[n][0].x; v[n][1] = acc[n][0].y; v[n][2] = acc[n][1].x; v[n][3] = acc[n][1].y; }
+        if (whole) { store_tile(tile, v); return; }
+        const int slot = tile == first_tile ? 0 : 1;
+        part_on[slot] = true; part_tile[slot] = tile;
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) part_v[slot][n][k] = v[n][k];
+    };
+
+    // per-lane constant offsets
+    const uint32_t w_lane = g * Geo::ROW_STRIDE + 16 + 8 * t;            // weights: row g (+8 rows: + 8*ROW_STRIDE)
+    const uint32_t hdr_lane = (lane >> 1) * Geo::ROW_STRIDE;             // pre-pass: row lane/2
+    const int hf = lane & 1;
+    float4* scr_w = scr + (4 * hf) * 16 + (lane >> 1);                   // pre-pass writes sub-blocks 4hf..4hf+3 of its row
+    const float4* scr_r = scr + g;
+
+    int cur_tile = first_tile, chunk = nunits ? u0 % C : 0;
+    bool cur_from_start = chunk == 0;
+    bool ok = mbar_wait(xbar, 0, err);
+    for (int i = 0; i < nunits && ok; ++i) {
+        const int s = i % SK_STAGES;
+        ok = mbar_wait(bar0 + 8 * s, (i / SK_STAGES) & 1, err);
+        if (!ok) break;
+        const uint8_t* st = ring + s * Geo::STAGE_BYTES;
+        const uint4* xqp = xq_s + (chunk * CB) * 128 + lane;
+        const float4* xsp = xsc_s + (chunk * CB) * 32 + t;
+#pragma unroll
+        for (int blk = 0; blk < CB; ++blk) {
+            {   // scale pre-pass: lane -> (row = lane/2, half = lane&1) decodes sub-blocks 4hf..4hf+3 of its row
+                const uint4 hdr = *reinterpret_cast<const uint4*>(st + hdr_lane + blk * 144);
+                const float d = h2f((uint16_t)(hdr.x & 0xFFFF)), nd = -h2f((uint16_t)(hdr.x >> 16));
+                const uint32_t scv = hf ? ((hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u)) : (hdr.y & 0x3F3F3F3Fu);
+                const uint32_t mnv = hf ? (((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u)) : (hdr.z & 0x3F3F3F3Fu);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    float s0 = d * (float)((scv >> (8 * k)) & 0xFFu);
+                    // odd sub-blocks take the high nibbles unshifted (16 * q): their scale carries the exact 1/16
+                    if (k & 1) s0 = s0 * 0.0625f;
+                    const float nm = nd * (float)((mnv >> (8 * k)) & 0xFFu);   // -(dmin * mn), exact sign flip
+                    scr_w[k * 16] = make_float4(s0, s0, nm, nm);
+                }
+            }
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint2 w0 = *reinterpret_cast<const uint2*>(st + w_lane + blk * 144 + 32 * j);
+                const uint2 w1 = *reinterpret_cast<const uint2*>(st + w_lane + 8 * Geo::ROW_STRIDE + blk * 144 + 32 * j);
+                const uint32_t alo[4] = {w0.x & 0x0F0F0F0Fu, w1.x & 0x0F0F0F0Fu, w0.y & 0x0F0F0F0Fu, w1.y & 0x0F0F0F0Fu};
+                const uint32_t ahi[4] = {w0.x & 0xF0F0F0F0u, w1.x & 0xF0F0F0F0u, w0.y & 0xF0F0F0F0u, w1.y & 0xF0F0F0F0u};
+                const float4 sa0 = scr_r[(2 * j) * 16], sb0 = scr_r[(2 * j) * 16 + 8];          // low-nibble sub-block: rows g, g+8
+                const float4 sa1 = scr_r[(2 * j + 1) * 16], sb1 = scr_r[(2 * j + 1) * 16 + 8];  // high-nibble sub-block
+#pragma unroll
+                for (int n = 0; n < NT; ++n) {
+                    const uint4 xf = xqp[n * nbp * 128 + (blk * 4 + j) * 32];
+                    const float4 x0 = xsp[n * nbp * 32 + (blk * 8 + 2 * j) * 4];
+                    const float4 x1 = xsp[n * nbp * 32 + (blk * 8 + 2 * j + 1) * 4];
+                    // The accumulator input carries 0x4B400000: the int32 result, read as fp32, is 12582912 + idot
+                    // exactly (|idot| < 2^22), so the int -> float conversion is one exact packed subtraction.
+                    int c0[4], c1[4];
+                    mma_u8s8_magic(c0, alo, xf.x, xf.y);
+                    mma_u8s8_magic(c1, ahi, xf.z, xf.w);
+                    const float2 xd0 = make_float2(x0.x, x0.y), xs0 = make_float2(x0.z, x0.w);
+                    const float2 xd1 = make_float2(x1.x, x1.y), xs1 = make_float2(x1.z, x1.w);
+                    const float2 mg = make_float2(-12582912.f, -12582912.f);
+                    // low-nibble sub-block 2j, then high-nibble sub-block 2j+1 (block order)
+                    fma2(acc[n][0], mul2(make_float2(sa0.x, sa0.y), xd0), add2(make_float2(__int_as_float(c0[0]), __int_as_float(c0[1])), mg));
+                    fma2(acc[n][0], make_float2(sa0.z, sa0.w), xs0);
+                    fma2(acc[n][1], mul2(make_float2(sb0.x, sb0.y), xd0), add2(make_float2(__int_as_float(c0[2]), __int_as_float(c0[3])), mg));
+                    fma2(acc[n][1], make_float2(sb0.z, sb0.w), xs0);
+                    fma2(acc[n][0], mul2(make_float2(sa1.x, sa1.y), xd1), add2(make_float2(__int_as_float(c1[0]), __int_as_float(c1[1])), mg));
+                    fma2(acc[n][0], make_float2(sa1.z, sa1.w), xs1);
+                    fma2(acc[n][1], mul2(make_float2(sb1.x, sb1.y), xd1), add2(make_float2(__int_as_float(c1[2]), __int_as_float(c1[3])), mg));
+                    fma2(acc[n][1], make_float2(sb1.z, sb1.w), xs1);
+                }
+            }
+            __syncwarp();
+        }
+        if (it_i < nunits) issue();
+        if (++chunk == C) {
+            flush(cur_tile, cur_from_start);
+            zero_acc();
+            chunk = 0; ++cur_tile; cur_from_start = true;
+        } else if (i + 1 == nunits) {
+            flush(cur_tile, false);
+        }
+    }
+    // ---------------- tiles shared by several warps of this CTA: combine through shared memory in warp order
+    __syncthreads();   // every ring is drained: its memory becomes the exchange buffer [warp][slot][NT*4][32]
+#pragma unroll
+    for (int sl = 0; sl < 2; ++sl)
+        if (part_on[sl])
 #pragma unroll
             for (int n = 0; n < NT; ++n)
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    float v = red[(n * 4 + k) * 32 + lane];
+                for (int k = 0; k < 4; ++k) red[((warp * 2 + sl) * NT * 4 + n * 4 + k) * 32 + lane] = part_v[sl][n][k];
+    __syncthreads();
+    if (!ok) return;
 #pragma unroll
-                    for (int w = 1; w < GEMV_KS; ++w) v = v + red[(w * NT * 4 + n * 4 + k) * 32 + lane];
-                    const int row = row0 + g + ((k & 2) ? 8 : 0), col = n * 8 + 2 * t + (k & 1);
-                    if (row < N && col < R) y[(size_t)col * ldy + row] = v;
+    for (int sl = 0; sl < 2; ++sl) {
+        if (!part_on[sl]) continue;
+        const int tile = part_tile[sl], tl = tile - ct.t0;
+        if ((tl + 1) * C > u1) continue;                     // the tile ends in a later warp: that warp finishes it
+        const int w_first = gemv_warp_owner(cu, weff, tl * C);
+        float v[NT][4];
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                float a = 0.f;
+                for (int ww = w_first; ww <= warp; ++ww) {
+                    const int wsl = (gemv_warp_start(cu, weff, ww) / C == tl) ? 0 : 1;
+                    const float pv = red[((ww * 2 + wsl) * NT * 4 + n * 4 + k) * 32 + lane];
+                    a = ww == w_first ? pv : a + pv;
                 }
-        }
+                v[n][k] = a;
+            }
+        store_tile(tile, v);
     }
 }
 
@@ -193,30 +310,80 @@ __global__ void __launch_bounds__(256) k_gemv_q4k_f32(const uint8_t* __restrict_
         for (int c = 0; c < NCOL; ++c) y[(size_t)c * N + row] = acc[c];
 }
 
-template <int NT>
-int launch_q8(const uint8_t* W, const void* xq, const void* xsc, float* y, int N, int nb, int R, int ldy, int* err, cudaStream_t s, bool pdl) {
-    static bool attr_set = false;
-    if (!attr_set) { HP_CUDA(cudaFuncSetAttribute(k_gemv_q4k_q8<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(GemvSmem))); attr_set = true; }
+template <int NT, int CB>
+int launch_sk2(const uint8_t* W, const void* xq, const void* xsc, float* y, int N, int nb, int P, int R, int ldy, size_t part_stride,
+               int* err, cudaStream_t s, bool pdl) {
+    const size_t smem = SkGeom<CB>::FIXED + (size_t)NT * (nb / P) * 2560;
+    static size_t attr_smem = 0;
+    if (smem > attr_smem) { HP_CUDA(cudaFuncSetAttribute(k_gemv_q4k_sk<NT, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr_smem = smem; }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((N + GEMV_ROWS - 1) / GEMV_ROWS); cfg.blockDim = dim3(GEMV_THREADS); cfg.dynamicSmemBytes = sizeof(GemvSmem); cfg.stream = s;
+    cfg.gridDim = dim3(GEMV_NCTA); cfg.blockDim = dim3(SK_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = s;
     cudaLaunchAttribute at[1]; at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at; cfg.numAttrs = pdl ? 1 : 0;
-    HP_CUDA(cudaLaunchKernelEx(&cfg, k_gemv_q4k_q8<NT>, W, (const uint4*)xq, (const float4*)xsc, y, N, nb, R, ldy, err));
+    HP_CUDA(cudaLaunchKernelEx(&cfg, k_gemv_q4k_sk<NT, CB>, W, (const uint4*)xq, (const float4*)xsc, y, N, nb, P, R, ldy, part_stride, err));
     return HP_OK;
+}
+template <int NT>
+int launch_sk(const uint8_t* W, const void* xq, const void* xsc, float* y, int N, int nb, int P, int R, int ldy, size_t part_stride,
+              int* err, cudaStream_t s, bool pdl) {
+#ifdef HP_FORCE_CB1
+    return launch_sk2<NT, 1>(W, xq, xsc, y, N, nb, P, R, ldy, part_stride, err, s, pdl);
+#endif
+    return ((nb / P) % 2 == 0) ? launch_sk2<NT, 2>(W, xq, xsc, y, N, nb, P, R, ldy, part_stride, err, s, pdl)
+                               : launch_sk2<NT, 1>(W, xq, xsc, y, N, nb, P, R, ldy, part_stride, err, s, pdl);
+}
+
+// sum the K-part planes in part order: y[r][n] = ((p0 + p1) + p2) + p3
+__global__ void k_reduce_parts(const float* __restrict__ parts, size_t part_stride, int P, float* __restrict__ y, int N, int R, int ldp, int ldy) {
+    const int n = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y;
+    if (n >= N || r >= R) return;
+    float v = parts[(size_t)r * ldp + n];
+    for (int p = 1; p < P; ++p) v = v + parts[(size_t)p * part_stride + (size_t)r * ldp + n];
+    y[(size_t)r * ldy + n] = v;
 }
 
 }  // namespace
 
-int gemv_q4k_q8(const void* W, const XQ8F& x, float* y, int N, int K, int R, int ldy, int* err, cudaStream_t s, bool pdl) {
+int gemv_parts(int N, int K) { return gemv_num_parts(N, K / 256); }
+
+int gemv_q4k_q8_parts(const void* W, const XQ8F& x, float* yparts, int N, int K, int R, int ldy, size_t part_stride, int* err, cudaStream_t s, bool pdl) {
     HP_REQUIRE(K > 0 && K % 256 == 0, "gemv_q4k_q8: K=%d must be a positive multiple of 256", K);
     HP_REQUIRE(N > 0 && R >= 1 && R <= 32 && ldy >= N, "gemv_q4k_q8: bad shape N=%d R=%d ldy=%d", N, R, ldy);
-    const int nb = K / 256;
-    switch ((R + 7) / 8) {
-        case 1: return launch_q8<1>((const uint8_t*)W, x.q, x.sc, y, N, nb, R, ldy, err, s, pdl);
-        case 2: return launch_q8<2>((const uint8_t*)W, x.q, x.sc, y, N, nb, R, ldy, err, s, pdl);
-        case 3: return launch_q8<3>((const uint8_t*)W, x.q, x.sc, y, N, nb, R, ldy, err, s, pdl);
-        default: return launch_q8<4>((const uint8_t*)W, x.q, x.sc, y, N, nb, R, ldy, err, s, pdl);
+    const int nb = K / 256, P = gemv_num_parts(N, nb);
+    HP_REQUIRE(P > 0, "gemv_q4k_q8: K=%d is too large for the activation staging buffer", K);
+    const int ntile = (R + 7) / 8, nbp = nb / P;
+    // all column tiles in one launch when their activations fit in shared memory beside the rings; otherwise one
+    // launch per tile of 8 columns (same per-column arithmetic either way)
+    const bool fused = ntile == 1 || (size_t)SkGeom<2>::FIXED + (size_t)ntile * nbp * 2560 <= (size_t)GEMV_SMEM_LIMIT;
+    for (int c0 = 0; c0 < ntile; c0 += fused ? ntile : 1) {
+        const int nt = fused ? ntile : 1;
+        const int Rl = min(R - c0 * 8, nt * 8);
+        const uint8_t* xqp = (const uint8_t*)x.q + (size_t)c0 * K * 8;
+        const uint8_t* xsp = (const uint8_t*)x.sc + (size_t)c0 * (K / 32) * 64;
+        float* yp = yparts + (size_t)c0 * 8 * ldy;
+        int rc;
+        switch (nt) {
+            case 1: rc = launch_sk<1>((const uint8_t*)W, xqp, xsp, yp, N, nb, P, Rl, ldy, part_stride, err, s, pdl); break;
+            case 2: rc = launch_sk<2>((const uint8_t*)W, xqp, xsp, yp, N, nb, P, Rl, ldy, part_stride, err, s, pdl); break;
+            case 3: rc = launch_sk<3>((const uint8_t*)W, xqp, xsp, yp, N, nb, P, Rl, ldy, part_stride, err, s, pdl); break;
+            default: rc = launch_sk<4>((const uint8_t*)W, xqp, xsp, yp, N, nb, P, Rl, ldy, part_stride, err, s, pdl); break;
+        }
+        if (rc != HP_OK) return rc;
     }
+    return HP_OK;
+}
+
+int gemv_q4k_q8(const void* W, const XQ8F& x, float* y, int N, int K, int R, int ldy, const GemvWorkspace& ws, cudaStream_t s, bool pdl) {
+    HP_REQUIRE(K > 0 && K % 256 == 0 && N > 0, "gemv_q4k_q8: bad shape N=%d K=%d", N, K);
+    const int P = gemv_num_parts(N, K / 256);
+    if (P == 1) return gemv_q4k_q8_parts(W, x, y, N, K, R, ldy, 0, ws.err, s, pdl);
+    HP_REQUIRE(ws.part && (size_t)P * R * N * sizeof(float) <= ws.part_bytes, "gemv_q4k_q8: workspace too small for %d K-part planes of %d x %d", P, R, N);
+    const size_t stride = (size_t)R * N;
+    const int rc = gemv_q4k_q8_parts(W, x, ws.part, N, K, R, N, stride, ws.err, s, pdl);
+    if (rc != HP_OK) return rc;
+    k_reduce_parts<<<dim3((N + 255) / 256, R), 256, 0, s>>>(ws.part, stride, P, y, N, R, N, ldy);
+    HP_CUDA(cudaGetLastError());
+    return HP_OK;
 }
 
 int gemv_q4k_f32(const void* W, const float* x, float* y, int N, int K, int R, cudaStream_t s) {

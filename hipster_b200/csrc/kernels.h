@@ -14,7 +14,45 @@ struct XQ8F { void* q; void* sc; };
 int* device_err_flag();
 
 // ---- gemv_q4k.cu ----
-int gemv_q4k_q8(const void* W, const XQ8F& x, float* y, int N, int K, int R, int ldy, int* err, cudaStream_t s, bool pdl);
+// Work partition of the tensor-core GEMV. It is part of the numerics contract (it fixes the fp32 summation order)
+// and depends on the tensor shape only.
+#ifndef HP_GEMV_WARPS
+#define HP_GEMV_WARPS 12
+#endif
+#ifndef HP_GEMV_STAGES
+#define HP_GEMV_STAGES 2
+#endif
+constexpr int GEMV_NCTA = 148, GEMV_WARPS = HP_GEMV_WARPS, GEMV_STAGES = HP_GEMV_STAGES;
+constexpr int GEMV_SMEM_LIMIT = 227 * 1024, GEMV_MAX_PART_BLOCKS = 36;
+// number of K parts: P in {1, 2, 4} dividing K/256 with at most 36 blocks per part, maximising
+//   1000 * tiles / (ctas_per_part * ceil(tiles / ctas_per_part)) - 20 * log2(P) - (50 if K/256/P is odd)
+// (ties -> smaller P); 0 when no P qualifies.
+__host__ __device__ inline int gemv_num_parts(int N, int nb) {
+    const int tiles = (N + 15) / 16; int best = 0, best_score = -1000000;
+    for (int lg = 0; lg < 3; ++lg) {
+        const int P = 1 << lg; if (nb % P) continue;
+        const int nbp = nb / P; if (nbp > GEMV_MAX_PART_BLOCKS) continue;
+        const int gc = GEMV_NCTA / P, per = (tiles + gc - 1) / gc;
+        const int score = (int)((long long)tiles * 1000 / ((long long)gc * per)) - 20 * lg - ((nbp & 1) ? 50 : 0);
+        if (score > best_score) { best_score = score; best = P; }
+    }
+    return best;
+}
+// CTA c works on K part c / (148/P) and on tiles [t0, t1): the tiles are split evenly over the CTAs of the part
+struct GemvCta { int part, t0, t1; };
+__host__ __device__ inline GemvCta gemv_cta(int N, int nb, int P, int c) {
+    const int tiles = (N + 15) / 16, gc = GEMV_NCTA / P, cg = c % gc;
+    GemvCta r; r.part = c / gc; r.t0 = (int)((long long)cg * tiles / gc); r.t1 = (int)((long long)(cg + 1) * tiles / gc); return r;
+}
+// inside a CTA the cu units are split evenly and contiguously over weff = min(12, cu) warps
+__host__ __device__ inline int gemv_warp_start(int cu, int weff, int w) { return (int)((long long)w * cu / weff); }
+__host__ __device__ inline int gemv_warp_owner(int cu, int weff, int u) { return (int)((((long long)u + 1) * weff - 1) / cu); }
+// scratch for the K-part planes of the public (single-output) entry point
+struct GemvWorkspace { float* part; size_t part_bytes; int* err; };
+int gemv_parts(int N, int K);
+// raw form: part p of the K split writes plane yparts + p * part_stride ([R][ldy] each); the caller adds the planes in order
+int gemv_q4k_q8_parts(const void* W, const XQ8F& x, float* yparts, int N, int K, int R, int ldy, size_t part_stride, int* err, cudaStream_t s, bool pdl);
+int gemv_q4k_q8(const void* W, const XQ8F& x, float* y, int N, int K, int R, int ldy, const GemvWorkspace& ws, cudaStream_t s, bool pdl);
 int gemv_q4k_f32(const void* W, const float* x, float* y, int N, int K, int R, cudaStream_t s);
 
 // ---- quant_ops.cu ----

@@ -44,6 +44,10 @@ int hp_dequant_q4k(const void* w_dev, size_t nblk, float* out_dev, void* stream)
  * 1 <= R <= 32; the result of a row does not depend on R. Replaces gemv_q8 / gemv_multi / gemv_wmma
  * (gemv.h:23-33, gemv.hip:291-367,602-672,1306-1331). */
 int hp_gemv_q4k_q8(const void* w_dev, const void* xq_q_dev, const void* xq_sc_dev, float* y_dev, int N, int K, int R, int ldy, void* stream);
+/* Number of K parts (1, 2 or 4) the GEMV splits a [N][K] tensor into; a function of the shape only. It fixes the
+ * fp32 summation order, so it is part of the result's definition (reference analogue: the KS split of gemv_wmma,
+ * gemv.hip:1315). */
+int hp_gemv_parts(int N, int K);
 /* f32-activation baseline, R <= 8, y [R][N]. Replaces gemv_q4_K_f32 (gemv.h:57, gemv.hip:1177-1216). */
 int hp_gemv_q4k_f32(const void* w_dev, const float* x_dev, float* y_dev, int N, int K, int R, void* stream);
 /* Row-wise argmax (maximum value, lowest index on ties) of logits [R][ld] over n entries.

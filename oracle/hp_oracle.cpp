@@ -188,36 +188,79 @@ extern "C" void orc_gemv_q4k_f32(const uint8_t* W, const float* x, float* y, int
 
 // ---------------------------------------------------------------- Q4_K GEMV, int8 activations (production numerics)
 // gemv.hip:602-672 contract: exact int32 dot over each 32-element sub-block, one fp32 update per sub-block in block
-// order, split-K partials summed in a fixed order that depends on the tensor shape only. Here: 4 slices, block b
-// belongs to slice b % 4; update = fmaf(-(dmin*mn), xs, fmaf((d*sc)*xd, (float)idot, acc)); y = ((p0+p1)+p2)+p3.
+// order, split-K partials summed in a fixed order that depends on the tensor shape only:
+//     acc = fmaf((d*sc)*xd, (float)idot, acc);  acc = fmaf(-(dmin*mn), xs, acc);
+// The shape-only partition of this build (restated from the kernel's description, not shared with it):
+//  - K/256 blocks are cut into P equal parts, P in {1, 2, 4} dividing K/256 with at most 36 blocks per part, chosen to
+//    maximise 1000*tiles/(g*ceil(tiles/g)) - 20*log2(P) - (50 if blocks per part is odd), g = 148/P, ties -> smaller P;
+//  - the g work groups of a part split the 16-row tiles evenly: group c owns tiles [c*tiles/g, (c+1)*tiles/g);
+//  - inside a group the stream of units (tile major, then chunks of cb = 2 (or 1) blocks along the part) is divided
+//    evenly over min(12, units) workers: worker w owns units [w*U/We, (w+1)*U/We);
+//  - a tile's value for a part is the sum, in worker order, of each worker's partial sum over its own blocks;
+//  - y is the sum of the part values in part order.
+static int orc_num_parts(int N, int nb) {
+    const int tiles = (N + 15) / 16; int best = 0, best_score = -1000000;
+    for (int lg = 0; lg < 3; ++lg) {
+        const int P = 1 << lg; if (nb % P) continue;
+        const int nbp = nb / P; if (nbp > 36) continue;
+        const int gc = 148 / P, per = (tiles + gc - 1) / gc;
+        const int score = (int)((long long)tiles * 1000 / ((long long)gc * per)) - 20 * lg - ((nbp & 1) ? 50 : 0);
+        if (score > best_score) { best_score = score; best = P; }
+    }
+    return best;
+}
+extern "C" int orc_gemv_parts(int N, int K) { return orc_num_parts(N, K / 256); }
 extern "C" void orc_gemv_q4k_q8(const uint8_t* W, const int8_t* q, const float* xd, const float* xs, float* y, int N, int K, int R, int ldy) {
-    const int nb = K / 256, nsb = K / 32;
-#pragma omp parallel for schedule(static)
-    for (int row = 0; row < N; ++row) {
-        const uint8_t* wrow = W + (size_t)row * nb * 144;
-        for (int c = 0; c < R; ++c) {
-            const int8_t* xq = q + (size_t)c * K; const float* cd = xd + (size_t)c * nsb; const float* cs = xs + (size_t)c * nsb;
-            float part[4] = {0.f, 0.f, 0.f, 0.f};
-            for (int b = 0; b < nb; ++b) {
-                const uint8_t* blk = wrow + (size_t)b * 144;
-                uint16_t dh, mh; memcpy(&dh, blk, 2); memcpy(&mh, blk + 2, 2);
-                const float d = orc_f16_to_f32(dh), dmin = orc_f16_to_f32(mh);
-                uint8_t sc[8], mn[8]; orc_q4k_scale_min(blk + 4, sc, mn);
-                float acc = part[b & 3];
-                for (int sb = 0; sb < 8; ++sb) {
-                    const int g = sb >> 1, hi = sb & 1;
-                    const uint8_t* qs = blk + 16 + 32 * g; const int8_t* xe = xq + (size_t)b * 256 + 32 * sb;
-                    int idot = 0;
-                    for (int e = 0; e < 32; ++e) idot += (int)(hi ? (qs[e] >> 4) : (qs[e] & 0xF)) * (int)xe[e];
-                    const float s0 = d * (float)sc[sb], m = dmin * (float)mn[sb];
-                    const float t = s0 * cd[b * 8 + sb];
-                    acc = fmaf(t, (float)idot, acc);
-                    acc = fmaf(-m, cs[b * 8 + sb], acc);
+    const int nb = K / 256, nsb = K / 32, tiles = (N + 15) / 16;
+    const int P = orc_num_parts(N, nb);
+    if (P == 0) return;
+    const int nbp = nb / P, cb = (nbp % 2 == 0) ? 2 : 1, C = nbp / cb, gc = 148 / P;
+    for (int p = 0; p < P; ++p) {
+        const int kb0 = p * nbp;
+#pragma omp parallel for schedule(dynamic, 1)
+        for (int cg = 0; cg < gc; ++cg) {
+            const int t0 = (int)((long long)cg * tiles / gc), t1 = (int)((long long)(cg + 1) * tiles / gc);
+            const long long cu = (long long)(t1 - t0) * C; if (cu == 0) continue;
+            const long long we = cu < 12 ? cu : 12;
+            auto start = [&](long long w) { return w * cu / we; };
+            auto owner = [&](long long u) { return ((u + 1) * we - 1) / cu; };
+            for (int tile = t0; tile < t1; ++tile) {
+                const long long a0 = (long long)(tile - t0) * C, a1 = a0 + C;
+                const long long w_first = owner(a0), w_last = owner(a1 - 1);
+                for (int rr = 0; rr < 16; ++rr) {
+                    const int row = tile * 16 + rr; if (row >= N) break;
+                    const uint8_t* wrow = W + (size_t)row * nb * 144;
+                    for (int c = 0; c < R; ++c) {
+                        const int8_t* xq = q + (size_t)c * K; const float* cd = xd + (size_t)c * nsb; const float* cs = xs + (size_t)c * nsb;
+                        float v = 0.f;
+                        for (long long ww = w_first; ww <= w_last; ++ww) {
+                            const long long ulo = start(ww) > a0 ? start(ww) : a0, uhi = start(ww + 1) < a1 ? start(ww + 1) : a1;
+                            float acc = 0.f;
+                            for (long long u = ulo; u < uhi; ++u)
+                                for (int blk = 0; blk < cb; ++blk) {
+                                    const int b = kb0 + (int)(u - a0) * cb + blk;
+                                    const uint8_t* bp = wrow + (size_t)b * 144;
+                                    uint16_t dh, mh; memcpy(&dh, bp, 2); memcpy(&mh, bp + 2, 2);
+                                    const float d = orc_f16_to_f32(dh), dmin = orc_f16_to_f32(mh);
+                                    uint8_t sc[8], mn[8]; orc_q4k_scale_min(bp + 4, sc, mn);
+                                    for (int sb = 0; sb < 8; ++sb) {
+                                        const int grp = sb >> 1, hi = sb & 1;
+                                        const uint8_t* qs = bp + 16 + 32 * grp; const int8_t* xe = xq + (size_t)b * 256 + 32 * sb;
+                                        int idot = 0;
+                                        for (int e = 0; e < 32; ++e) idot += (int)(hi ? (qs[e] >> 4) : (qs[e] & 0xF)) * (int)xe[e];
+                                        const float s0 = d * (float)sc[sb], m = dmin * (float)mn[sb];
+                                        const float tt = s0 * cd[b * 8 + sb];
+                                        acc = fmaf(tt, (float)idot, acc);
+                                        acc = fmaf(-m, cs[b * 8 + sb], acc);
+                                    }
+                                }
+                            v = ww == w_first ? acc : v + acc;
+                        }
+                        float* yp = y + (size_t)c * ldy + row;
+                        *yp = p > 0 ? *yp + v : v;
+                    }
                 }
-                part[b & 3] = acc;
             }
-            float v = part[0]; v = v + part[1]; v = v + part[2]; v = v + part[3];
-            y[(size_t)c * ldy + row] = v;
         }
     }
 }

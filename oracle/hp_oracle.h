@@ -48,7 +48,7 @@ void orc_quantize_x_q8(const float* x, int R, int K, int8_t* q, float* d, float*
  * y [R][N]. */
 void orc_gemv_q4k_f32(const uint8_t* W, const float* x, float* y, int N, int K, int R, int tpr);
 /* W4A8: exact int32 dot per 32-element sub-block, one fp32 update per sub-block in block order
- * (gemv.hip:602-672 numerics contract), K split over 4 slices (block b -> slice b%4) summed in slice order.
+ * (gemv.hip:602-672 numerics contract); split-K partial sums are added in a fixed, shape-only order (see the .cpp).
  * y [R][ldy] (row stride ldy >= N). */
 void orc_gemv_q4k_q8(const uint8_t* W, const int8_t* q, const float* d, const float* s, float* y, int N, int K, int R, int ldy);
 /* reference check of bench_gemv.cpp:97-104: dequantised row . x in double; also returns sum|w*x| */
