@@ -56,6 +56,14 @@ __global__ void k_accept(const int* __restrict__ ids, const int* __restrict__ dr
     }
 }
 
+// Scratch of the allocation-free entry point: partial (value, index) pairs for at most AM_STATIC_ROWS rows of at most
+// AM_STATIC_PARTS * AM_CHUNK logits. It lives in the library image, so every GPU that loads the library holds these
+// 16 KiB until the process exits. In host code the name below is only a handle for cudaGetSymbolAddress.
+constexpr int AM_STATIC_ROWS = 32, AM_STATIC_PARTS = 64;
+static __device__ __align__(256) unsigned char g_argmax_scratch[AM_STATIC_ROWS * AM_STATIC_PARTS * 8];
+constexpr int AM_MAX_DEVICES = 64;
+static void* g_argmax_scratch_addr[AM_MAX_DEVICES] = {};
+
 }  // namespace
 
 size_t argmax_scratch_bytes(int R, int n) { return (size_t)R * ((n + AM_CHUNK - 1) / AM_CHUNK) * 8; }
@@ -69,6 +77,31 @@ int argmax_rows(const float* logits, int R, int n, int ld, int* ids, float* vals
     HP_CUDA(cudaGetLastError());
     return HP_OK;
 }
+int argmax_static_max_rows() { return AM_STATIC_ROWS; }
+int argmax_static_max_n() { return AM_STATIC_PARTS * AM_CHUNK; }
+
+// Same two kernels as argmax_rows, with the partials in the file-scope device array above instead of caller memory.
+// The first call on a device looks the array's device address up (once per device, with that device current).
+int argmax_rows_static(const float* logits, int R, int n, int ld, int* ids, float* vals, cudaStream_t s) {
+    HP_REQUIRE(R >= 1 && n >= 1 && ld >= n, "argmax_rows_static: bad arguments R=%d n=%d ld=%d", R, n, ld);
+    HP_REQUIRE(R <= AM_STATIC_ROWS && n <= AM_STATIC_PARTS * AM_CHUNK,
+               "argmax_rows_static: R=%d n=%d exceed the built-in scratch (at most %d rows of %d entries)", R, n, AM_STATIC_ROWS, AM_STATIC_PARTS * AM_CHUNK);
+    int dev = -1;
+    HP_CUDA(cudaGetDevice(&dev));
+    HP_REQUIRE(dev >= 0 && dev < AM_MAX_DEVICES, "argmax_rows_static: device ordinal %d not supported", dev);
+    if (!g_argmax_scratch_addr[dev]) {
+        void* p = nullptr;
+        HP_CUDA(cudaGetSymbolAddress(&p, g_argmax_scratch));
+        g_argmax_scratch_addr[dev] = p;
+    }
+    const int np = (n + AM_CHUNK - 1) / AM_CHUNK;
+    float* pv = (float*)g_argmax_scratch_addr[dev]; int* pi = (int*)(pv + (size_t)R * np);
+    k_argmax_part<<<dim3(np, R), 256, 0, s>>>(logits, n, ld, pv, pi);
+    k_argmax_final<<<R, 256, 0, s>>>(pv, pi, np, ids, vals);
+    HP_CUDA(cudaGetLastError());
+    return HP_OK;
+}
+
 int accept_greedy(const int* ids, const int* drafts, int n_draft, int* out, cudaStream_t s) {
     HP_REQUIRE(n_draft >= 0 && n_draft <= 31, "accept_greedy: n_draft=%d out of range", n_draft);
     k_accept<<<1, 32, 0, s>>>(ids, drafts, n_draft, out);

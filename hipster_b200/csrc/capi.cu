@@ -103,6 +103,14 @@ int hp_argmax(const float* logits_dev, int R, int n, int ld, int* ids_dev, float
     return hp::argmax_rows(logits_dev, R, n, ld, ids_dev, vals_dev, scratch_dev, (cudaStream_t)stream);
     HP_GUARD_END
 }
+int hp_argmax_noalloc(const float* logits_dev, int R, int n, int ld, int* ids_dev, float* vals_dev, void* stream) {
+    HP_GUARD_BEGIN
+    HP_REQUIRE(logits_dev && ids_dev, "hp_argmax_noalloc: null pointer");
+    return hp::argmax_rows_static(logits_dev, R, n, ld, ids_dev, vals_dev, (cudaStream_t)stream);
+    HP_GUARD_END
+}
+int hp_argmax_noalloc_max_rows(void) { return hp::argmax_static_max_rows(); }
+int hp_argmax_noalloc_max_n(void) { return hp::argmax_static_max_n(); }
 int hp_accept_greedy(const int* ids_dev, const int* drafts_dev, int n_draft, int* out_dev, void* stream) {
     HP_GUARD_BEGIN
     HP_REQUIRE(ids_dev && out_dev && (drafts_dev || n_draft == 0), "hp_accept_greedy: null pointer");

@@ -64,6 +64,10 @@ int dequant_q4k(const void* W, size_t nblk, float* out, cudaStream_t s);
 // per-row argmax (max value, lowest index) of logits [R][ld] -> ids/vals on device
 int argmax_rows(const float* logits, int R, int n, int ld, int* ids, float* vals, void* scratch, cudaStream_t s);
 size_t argmax_scratch_bytes(int R, int n);
+// allocation-free variant: partials in a static device array of fixed size (see argmax.cu)
+int argmax_rows_static(const float* logits, int R, int n, int ld, int* ids, float* vals, cudaStream_t s);
+int argmax_static_max_rows();
+int argmax_static_max_n();
 // greedy prefix acceptance on device: out[0] = accepted drafts mm, out[1] = bonus id ids[mm]
 int accept_greedy(const int* ids, const int* drafts, int n_draft, int* out, cudaStream_t s);
 

@@ -72,6 +72,17 @@ def argmax(logits, n=None):
     return ids, vals
 
 
+def argmax_noalloc(logits, n=None):
+    """argmax() for callers that cannot allocate device memory: the library's built-in scratch holds the partial
+    results, so the call takes only the input and the two output tensors (created by the caller beforehand)."""
+    R, ld = logits.shape[0], logits.stride(0)
+    n = n or logits.shape[1]
+    ids = torch.empty(R, dtype=torch.int32, device=logits.device)
+    vals = torch.empty(R, dtype=torch.float32, device=logits.device)
+    check(lib().hp_argmax_noalloc(ptr(logits), R, n, ld, ptr(ids), ptr(vals), _stream()))
+    return ids, vals
+
+
 def accept_greedy(ids, drafts):
     """-> int32 tensor [mm, bonus] on device (reference host loop, engine/bench/spec27b.cpp:92-97)."""
     out = torch.empty(2, dtype=torch.int32, device=ids.device)

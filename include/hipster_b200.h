@@ -54,6 +54,18 @@ int hp_gemv_q4k_f32(const void* w_dev, const float* x_dev, float* y_dev, int N, 
  * Replaces argmax_topk with k = 1 (ops.h:118, ops.hip:702-716). scratch_dev: hp_argmax_scratch_bytes(R, n) bytes. */
 size_t hp_argmax_scratch_bytes(int R, int n);
 int hp_argmax(const float* logits_dev, int R, int n, int ld, int* ids_dev, float* vals_dev, void* scratch_dev, void* stream);
+/* hp_argmax for callers that must not allocate. It has no counterpart in the reference. A serving loop that has sized
+ * its weights, KV caches and state to fill the GPU, or that runs its decode steps on a latency-critical thread, cannot
+ * afford a cudaMalloc per call: the allocation may fail, and it serialises against everything running on the device.
+ * This variant needs no scratch from the caller: its partial results live in a fixed 16 KiB array inside the library
+ * image (held by every GPU that loads the library until the process exits). It accepts at most
+ * hp_argmax_noalloc_max_rows() rows of hp_argmax_noalloc_max_n() entries and rejects larger shapes with HP_EINVAL.
+ * It calls no allocating routine. The first call on each device resolves the array's address; make that call before
+ * any stream capture begins. All calls share the one array: nothing in it has to be cleared between calls (every
+ * element read is written first by the same call), but two calls that overlap on the GPU race on it. */
+int hp_argmax_noalloc(const float* logits_dev, int R, int n, int ld, int* ids_dev, float* vals_dev, void* stream);
+int hp_argmax_noalloc_max_rows(void);
+int hp_argmax_noalloc_max_n(void);
 /* Greedy prefix acceptance on device: out_dev[0] = number of accepted drafts mm, out_dev[1] = ids[mm] (bonus token).
  * ids_dev holds n_draft+1 target argmaxes. Replaces the host loop of engine/bench/spec27b.cpp:92-97. */
 int hp_accept_greedy(const int* ids_dev, const int* drafts_dev, int n_draft, int* out_dev, void* stream);
