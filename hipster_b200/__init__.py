@@ -5,3 +5,4 @@ engine classes) over the C ABI of libhipster_b200.so; torch is used for device m
 """
 from ._lib import HipsterError, lib, check, ptr, declared_symbols, LIB_PATH  # noqa: F401
 from . import kernels  # noqa: F401
+from .engine import Engine, ModelCfg, SlotReq  # noqa: F401

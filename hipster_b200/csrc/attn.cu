@@ -1,0 +1,213 @@
+// GQA decode attention over the f16 KV cache for the rows of a verify pass.
+//
+// Reference: k_qk_norm_rope_kv (engine/kernels/ops.hip:363-411), the scalar decode attention k_attn (:413-465, the
+// semantic reference) and the production split-KV structure k_attn_mq + k_attn_mq_merge (:831-948): fixed absolute
+// key splits merged in split order, so that a row's result does not depend on the number of rows in the pass.
+//
+// Here: head_dim 256, NeoX RoPE on the first n_rot = 64 dims from a host-built cos/sin table (double precision,
+// rounded to fp32), K and V stored row-major f16 [slot][kv head][position][256]. One CTA per (split of 128 keys,
+// kv head, row group <= 8 rows): the K and V tiles are read once for all rows x q-heads of the group. All arithmetic
+// is fp32 FMA in a fixed order (scores: fmaf chain over d = 0..255; P.V: fmaf chain over keys in position order;
+// merge: splits in order), so the CPU oracle reproduces it bit for bit. KV traffic is ~2 % of a pass's bytes, so SIMT
+// fp32 is affordable, and it avoids the tensor-core rounding hazard the reference documents (docs/decode-27b.md:117-126).
+#include "hp_common.cuh"
+#include "kernels.h"
+
+namespace hp {
+namespace {
+
+constexpr int HD = 256, SPL = ATTN_SPLIT, MAXP = ATTN_MAX_PAIRS;   // pairs = rows of the group x q-heads per kv head
+constexpr int KSTRIDE = HD + 4;                                     // f16 elements per K/V tile row (520 B: conflict-free)
+
+template <int NW>
+__device__ __forceinline__ float block_sum_det(float v, float* sh) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = v + __shfl_xor_sync(0xffffffffu, v, off);
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    __syncthreads();
+    if (l == 0) sh[w] = v;
+    __syncthreads();
+    float tot = sh[0];
+#pragma unroll
+    for (int i = 1; i < NW; ++i) tot = tot + sh[i];
+    return tot;
+}
+
+// grid: rows * (n_head + n_kv) blocks of 256 threads; row layout: [q_full: n_head x (256 q | 256 gate) | k: n_kv x 256 | v: n_kv x 256]
+__global__ void __launch_bounds__(256) k_qk_norm_rope_kv(float* __restrict__ qkv, int ld, int n_head, int n_kv, const uint16_t* __restrict__ qw, const uint16_t* __restrict__ kw,
+                                                          const float2* __restrict__ rope, int n_rot, const int* __restrict__ row_pos, const int* __restrict__ row_slot,
+                                                          uint16_t* __restrict__ kc, uint16_t* __restrict__ vc, size_t kv_stride, int max_ctx, float eps) {
+    __shared__ float sh[8]; __shared__ float buf[HD];
+    const int t = threadIdx.x, hb = blockIdx.x % (n_head + n_kv), r = blockIdx.x / (n_head + n_kv);
+    const int pos = row_pos[r], slot = row_slot[r];
+    const bool isq = hb < n_head;
+    float* x = isq ? qkv + (size_t)r * ld + hb * 512 : qkv + (size_t)r * ld + n_head * 512 + (hb - n_head) * HD;
+    const float xv = x[t];
+    const float ss = block_sum_det<8>(xv * xv, sh);
+    float n = (xv * (1.0f / sqrtf(ss / (float)HD + eps))) * bf2f((isq ? qw : kw)[t]);
+    buf[t] = n;
+    __syncthreads();
+    const int half = n_rot / 2;
+    if (t < n_rot) {
+        const int i = t % half; const float2 cs = rope[(size_t)pos * half + i];   // (cos, sin) of pos * base^(-2i/n_rot)
+        const float x0 = buf[i], x1 = buf[i + half];
+        n = t < half ? fmaf(-x1, cs.y, x0 * cs.x) : fmaf(x1, cs.x, x0 * cs.y);
+    }
+    x[t] = n;
+    if (!isq) {
+        const int kh = hb - n_head;
+        const float vv = qkv[(size_t)r * ld + n_head * 512 + n_kv * HD + kh * HD + t];
+        const size_t o = (size_t)slot * kv_stride + ((size_t)kh * max_ctx + pos) * HD + t;
+        kc[o] = f2h(n); vc[o] = f2h(vv);
+    }
+}
+
+struct AttnArgs {
+    const float* qkv; int ld, n_head, n_kv;
+    const uint16_t* kc; const uint16_t* vc; size_t kv_stride; int max_ctx;
+    const int* groups;        // device: per group {r0, T, slot, pos0}
+    float* pO; float* pm; float* pl; int nsplit_max;   // partials [group][kv head][split][MAXP] (x 256 for pO)
+};
+// grid (nsplit_max, n_kv, ngroups), 256 threads, dynamic smem
+__global__ void __launch_bounds__(256) k_attn_split(AttnArgs a) {
+    extern __shared__ __align__(16) uint8_t sm_raw[];
+    float* sQ = reinterpret_cast<float*>(sm_raw);                                   // [MAXP][256]
+    float* sE = sQ + MAXP * HD;                                                     // [SPL][MAXP] scores, then weights
+    uint16_t* sK = reinterpret_cast<uint16_t*>(sE + SPL * MAXP);                    // [SPL][KSTRIDE]
+    uint16_t* sV = sK + SPL * KSTRIDE;                                              // [SPL][KSTRIDE]
+    const int split = blockIdx.x, kh = blockIdx.y, gi = blockIdx.z, tid = threadIdx.x;
+    const int r0 = a.groups[gi * 4], T = a.groups[gi * 4 + 1], slot = a.groups[gi * 4 + 2], pos0 = a.groups[gi * 4 + 3];
+    const int G = a.n_head / a.n_kv, npairs = T * G;
+    const int k_lo = split * SPL;
+    const int nkeys = min(SPL, pos0 + T - k_lo);          // keys of this split visible to the last row of the group
+    if (nkeys <= 0 || T <= 0) return;
+    const size_t pbase = (((size_t)gi * a.n_kv + kh) * a.nsplit_max + split) * MAXP;
+    // stage Q (pair = t*G + hh -> row r0+t, head kh*G + hh), K and V tiles
+    for (int i = tid; i < npairs * (HD / 4); i += 256) {
+        const int p = i / (HD / 4), d4 = i % (HD / 4), tr = p / G, hh = p % G;
+        reinterpret_cast<float4*>(sQ)[p * (HD / 4) + d4] = reinterpret_cast<const float4*>(a.qkv + (size_t)(r0 + tr) * a.ld + (kh * G + hh) * 512)[d4];
+    }
+    const uint16_t* Kg = a.kc + (size_t)slot * a.kv_stride + ((size_t)kh * a.max_ctx + k_lo) * HD;
+    const uint16_t* Vg = a.vc + (size_t)slot * a.kv_stride + ((size_t)kh * a.max_ctx + k_lo) * HD;
+    for (int i = tid; i < nkeys * (HD / 8); i += 256) {
+        const int k = i / (HD / 8), c = i % (HD / 8);
+        const uint4 kv = reinterpret_cast<const uint4*>(Kg + (size_t)k * HD)[c], vv = reinterpret_cast<const uint4*>(Vg + (size_t)k * HD)[c];
+        uint2* dk = reinterpret_cast<uint2*>(sK + k * KSTRIDE + c * 8); dk[0] = make_uint2(kv.x, kv.y); dk[1] = make_uint2(kv.z, kv.w);
+        uint2* dv = reinterpret_cast<uint2*>(sV + k * KSTRIDE + c * 8); dv[0] = make_uint2(vv.x, vv.y); dv[1] = make_uint2(vv.z, vv.w);
+    }
+    __syncthreads();
+    // scores: thread (kq = tid % 32, pq = tid / 32) -> keys kq + 32*i (i < 4), pairs pq*6 + jx (jx < 6); fmaf chain over d
+    {
+        const int kq = tid & 31, pq = tid >> 5;
+        float s[4][6];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int jx = 0; jx < 6; ++jx) s[i][jx] = 0.f;
+        for (int d = 0; d < HD; d += 4) {
+            float kf[4][4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint2 kk = *reinterpret_cast<const uint2*>(sK + (kq + 32 * i) * KSTRIDE + d);
+                kf[i][0] = h2f((uint16_t)(kk.x & 0xFFFF)); kf[i][1] = h2f((uint16_t)(kk.x >> 16));
+                kf[i][2] = h2f((uint16_t)(kk.y & 0xFFFF)); kf[i][3] = h2f((uint16_t)(kk.y >> 16));
+            }
+#pragma unroll
+            for (int jx = 0; jx < 6; ++jx) {
+                const int p = pq * 6 + jx;
+                const float4 qv = p < npairs ? *reinterpret_cast<const float4*>(sQ + p * HD + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    s[i][jx] = fmaf(qv.x, kf[i][0], s[i][jx]); s[i][jx] = fmaf(qv.y, kf[i][1], s[i][jx]);
+                    s[i][jx] = fmaf(qv.z, kf[i][2], s[i][jx]); s[i][jx] = fmaf(qv.w, kf[i][3], s[i][jx]);
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int jx = 0; jx < 6; ++jx) { const int p = pq * 6 + jx; if (p < MAXP) sE[(kq + 32 * i) * MAXP + p] = s[i][jx] * 0.0625f; }
+    }
+    __syncthreads();
+    // softmax pieces per pair (one thread each): row t of the group sees keys <= pos0 + t
+    if (tid < npairs) {
+        const int tr = tid / G;
+        const int nk = min(nkeys, pos0 + tr + 1 - k_lo);
+        float mx = -INFINITY;
+        for (int k = 0; k < nk; ++k) mx = fmaxf(mx, sE[k * MAXP + tid]);
+        float l = 0.f;
+        for (int k = 0; k < nkeys; ++k) {
+            const float e = k < nk ? expf_det(sE[k * MAXP + tid] - mx) : 0.f;
+            sE[k * MAXP + tid] = e; l = l + e;
+        }
+        a.pm[pbase + tid] = mx; a.pl[pbase + tid] = l;   // nk <= 0: mx = -inf, l = 0 (the merge skips it)
+    }
+    __syncthreads();
+    // o[pair][d] = sum_k e[k][pair] * v[k][d], keys in position order; thread = dim d
+    {
+        float o[MAXP];
+#pragma unroll
+        for (int p = 0; p < MAXP; ++p) o[p] = 0.f;
+        for (int k = 0; k < nkeys; ++k) {
+            const float v = h2f(sV[k * KSTRIDE + tid]);
+#pragma unroll
+            for (int p4 = 0; p4 < MAXP / 4; ++p4) {
+                const float4 e = *reinterpret_cast<const float4*>(sE + k * MAXP + p4 * 4);
+                o[p4 * 4 + 0] = fmaf(e.x, v, o[p4 * 4 + 0]); o[p4 * 4 + 1] = fmaf(e.y, v, o[p4 * 4 + 1]);
+                o[p4 * 4 + 2] = fmaf(e.z, v, o[p4 * 4 + 2]); o[p4 * 4 + 3] = fmaf(e.w, v, o[p4 * 4 + 3]);
+            }
+        }
+#pragma unroll
+        for (int p = 0; p < MAXP; ++p) if (p < npairs) a.pO[(pbase + p) * HD + tid] = o[p];
+    }
+}
+
+// merge the splits of one (row, q-head) in split order, gate, write f32 + q8. grid rows * n_head, 256 threads
+__global__ void __launch_bounds__(256) k_attn_merge(const float* __restrict__ qkv, int ld, int n_head, int n_kv, const int* __restrict__ groups, const int* __restrict__ row_group,
+                                                     const float* __restrict__ pO, const float* __restrict__ pm, const float* __restrict__ pl, int nsplit_max,
+                                                     float* __restrict__ out, int8_t* __restrict__ oq, float* __restrict__ osc) {
+    const int r = blockIdx.x / n_head, head = blockIdx.x % n_head, d = threadIdx.x;
+    const int gi = row_group[r];
+    const int r0 = groups[gi * 4], pos0 = groups[gi * 4 + 3];
+    const int G = n_head / n_kv, kh = head / G, hh = head % G, tr = r - r0, pair = tr * G + hh;
+    const int nsplit = (pos0 + tr + 1 + SPL - 1) / SPL;
+    const size_t pb = (((size_t)gi * n_kv + kh) * nsplit_max) * MAXP + pair;
+    float mx = -INFINITY;
+    for (int s = 0; s < nsplit; ++s) mx = fmaxf(mx, pm[pb + (size_t)s * MAXP]);
+    float o = 0.f, l = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+        const float ms = pm[pb + (size_t)s * MAXP];
+        const float w = expf_det(ms - mx);
+        o = fmaf(w, pO[(pb + (size_t)s * MAXP) * HD + d], o);
+        l = fmaf(w, pl[pb + (size_t)s * MAXP], l);
+    }
+    const float gate = qkv[(size_t)r * ld + head * 512 + HD + d];
+    const float v = (o / l) * sigmoid_det(gate);
+    const size_t oi = (size_t)r * n_head * HD + head * HD + d;
+    if (out) out[oi] = v;
+    if (oq) warp_quant32_store(v, r, (head * HD + d) >> 5, n_head * HD, oq, osc, d & 31);
+}
+
+}  // namespace
+
+size_t attn_smem_bytes() { return (size_t)MAXP * HD * 4 + (size_t)SPL * MAXP * 4 + 2 * (size_t)SPL * KSTRIDE * 2; }
+size_t attn_partial_floats(int ngroups, int n_kv, int nsplit_max) { return (size_t)ngroups * n_kv * nsplit_max * MAXP; }
+
+int attn_rope_kv(const AttnParams& p, int rows, cudaStream_t s) {
+    HP_REQUIRE(rows >= 1 && p.n_head % p.n_kv == 0 && p.n_rot % 2 == 0 && p.n_rot <= HD, "attn_rope_kv: bad shape");
+    k_qk_norm_rope_kv<<<rows * (p.n_head + p.n_kv), 256, 0, s>>>(p.qkv, p.ld, p.n_head, p.n_kv, (const uint16_t*)p.q_norm, (const uint16_t*)p.k_norm, (const float2*)p.rope, p.n_rot,
+                                                                 p.row_pos, p.row_slot, (uint16_t*)p.kc, (uint16_t*)p.vc, p.kv_stride, p.max_ctx, p.eps);
+    HP_CUDA(cudaGetLastError()); return HP_OK;
+}
+int attn_decode(const AttnParams& p, int rows, int ngroups, cudaStream_t s) {
+    HP_REQUIRE(rows >= 1 && ngroups >= 1 && p.n_head % p.n_kv == 0 && (p.n_head / p.n_kv) * 8 <= MAXP, "attn_decode: at most %d (row, head) pairs per kv head and group", MAXP);
+    static bool attr = false;
+    if (!attr) { HP_CUDA(cudaFuncSetAttribute(k_attn_split, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem_bytes())); attr = true; }
+    AttnArgs a; a.qkv = p.qkv; a.ld = p.ld; a.n_head = p.n_head; a.n_kv = p.n_kv; a.kc = (const uint16_t*)p.kc; a.vc = (const uint16_t*)p.vc;
+    a.kv_stride = p.kv_stride; a.max_ctx = p.max_ctx; a.groups = p.groups; a.pO = p.pO; a.pm = p.pm; a.pl = p.pl; a.nsplit_max = p.nsplit_max;
+    k_attn_split<<<dim3(p.nsplit_max, p.n_kv, ngroups), 256, attn_smem_bytes(), s>>>(a);
+    k_attn_merge<<<rows * p.n_head, 256, 0, s>>>(p.qkv, p.ld, p.n_head, p.n_kv, p.groups, p.row_group, p.pO, p.pm, p.pl, p.nsplit_max, p.out, (int8_t*)p.xq.q, (float*)p.xq.sc);
+    HP_CUDA(cudaGetLastError()); return HP_OK;
+}
+
+}  // namespace hp

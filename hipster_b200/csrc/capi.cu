@@ -1,6 +1,8 @@
 // extern "C" boundary: argument checks, status codes, last-error string. No exceptions cross it.
 #include "hp_common.cuh"
 #include "kernels.h"
+#include "engine.h"
+#include <cstring>
 #include "../../include/hipster_b200.h"
 #include <cstdarg>
 #include <cstdio>
@@ -116,6 +118,67 @@ int hp_accept_greedy(const int* ids_dev, const int* drafts_dev, int n_draft, int
     HP_REQUIRE(ids_dev && out_dev && (drafts_dev || n_draft == 0), "hp_accept_greedy: null pointer");
     return hp::accept_greedy(ids_dev, drafts_dev, n_draft, out_dev, (cudaStream_t)stream);
     HP_GUARD_END
+}
+
+// ------------------------------------------------------------------ engine
+struct hp_engine { hp::Engine impl; explicit hp_engine(const hp_model_cfg& c) : impl(c) {} };
+
+int hp_model_preset(const char* preset, hp_model_cfg* o) {
+    HP_GUARD_BEGIN
+    HP_REQUIRE(preset && o, "hp_model_preset: null pointer");
+    memset(o, 0, sizeof *o);
+    o->rms_eps = 1e-6f; o->rope_base = 1e7f; o->n_rot = 64; o->attn_every = 4; o->has_mtp = 1; o->n_slots = 1;
+    if (!strcmp(preset, "qwen35-27b")) {          // struct Qwen35Dims, engine/src/qwen35.h:15-26
+        o->n_embd = 5120; o->n_layer = 64; o->n_ff = 17408; o->n_vocab = 248320; o->n_head = 24; o->n_head_kv = 4;
+        o->gdn_qk_heads = 16; o->gdn_v_heads = 48; o->max_ctx = 8192; o->seed = 27;
+    } else if (!strcmp(preset, "flash-next")) {   // BASELINE config 4 shape (head geometry from struct FnDims, qwen4exp.h:18-28)
+        o->n_embd = 2048; o->n_layer = 48; o->n_ff = 0; o->n_vocab = 248320; o->n_head = 24; o->n_head_kv = 2;
+        o->gdn_qk_heads = 16; o->gdn_v_heads = 48; o->max_ctx = 4096; o->n_slots = 8; o->seed = 48;
+        o->n_expert = 512; o->n_expert_used = 10; o->expert_ff = 512; o->gdn_sigmoid_gate = 1;
+    } else if (!strcmp(preset, "tiny")) {
+        o->n_embd = 512; o->n_layer = 4; o->n_ff = 1024; o->n_vocab = 2048; o->n_head = 4; o->n_head_kv = 2;
+        o->gdn_qk_heads = 2; o->gdn_v_heads = 4; o->max_ctx = 512; o->n_slots = 2; o->seed = 7;
+    } else if (!strcmp(preset, "tiny-moe")) {
+        o->n_embd = 512; o->n_layer = 4; o->n_ff = 0; o->n_vocab = 2048; o->n_head = 4; o->n_head_kv = 2;
+        o->gdn_qk_heads = 2; o->gdn_v_heads = 4; o->max_ctx = 512; o->n_slots = 4; o->seed = 9;
+        o->n_expert = 16; o->n_expert_used = 4; o->expert_ff = 256; o->gdn_sigmoid_gate = 1;
+    } else { hp::set_error("unknown preset '%s'", preset); return HP_EINVAL; }
+    return HP_OK;
+    HP_GUARD_END
+}
+int hp_load(const hp_model_cfg* cfg, hp_engine** out) {
+    HP_GUARD_BEGIN
+    HP_REQUIRE(cfg && out, "hp_load: null pointer");
+    hp_engine* e = new hp_engine(*cfg);
+    const int rc = e->impl.init();
+    if (rc != HP_OK) { delete e; *out = nullptr; return rc; }
+    *out = e; return HP_OK;
+    HP_GUARD_END
+}
+int hp_free(hp_engine* e) { delete e; return HP_OK; }
+int hp_n_slots(const hp_engine* e) { return e ? e->impl.cfg().n_slots : 0; }
+size_t hp_weight_bytes(const hp_engine* e) { return e ? e->impl.weight_bytes() : 0; }
+float hp_last_ms(const hp_engine* e) { return e ? e->impl.last_ms() : 0.f; }
+#define HP_ENGINE_CALL(expr) HP_GUARD_BEGIN HP_REQUIRE(e, "null engine handle"); return (expr); HP_GUARD_END
+int hp_reset(hp_engine* e) { HP_ENGINE_CALL(e->impl.reset()) }
+int hp_reset_slot(hp_engine* e, int slot) { HP_ENGINE_CALL(e->impl.reset_slot(slot)) }
+int hp_forward(hp_engine* e, const hp_slot_req* reqs, int S, float* ms_out) { HP_ENGINE_CALL(e->impl.forward(reqs, S, ms_out)) }
+int hp_accept(hp_engine* e, int slot, int m) { HP_ENGINE_CALL(e->impl.accept(slot, m)) }
+int hp_mtp_forward(hp_engine* e, int slot, const int* tokens_host, const float* h_dev, int T, int pos0) { HP_ENGINE_CALL(e->impl.mtp_forward(tokens_host, h_dev, T, pos0, slot, true)) }
+int hp_topk(hp_engine* e, int which, int T, int* ids_host, float* vals_host) { HP_ENGINE_CALL(e->impl.topk(which, T, ids_host, vals_host)) }
+const float* hp_logits_dev(const hp_engine* e) { return e ? e->impl.logits() : nullptr; }
+const float* hp_h_nextn_dev(const hp_engine* e) { return e ? e->impl.h_nextn() : nullptr; }
+const float* hp_mtp_logits_dev(const hp_engine* e) { return e ? e->impl.mtp_logits() : nullptr; }
+const float* hp_mtp_h_dev(const hp_engine* e) { return e ? e->impl.mtp_h() : nullptr; }
+int hp_tensor_dev(const hp_engine* e, int layer, int kind, void** ptr_out, size_t* bytes_out) {
+    HP_GUARD_BEGIN HP_REQUIRE(e && ptr_out && bytes_out, "hp_tensor_dev: null pointer"); return e->impl.tensor(layer, kind, ptr_out, bytes_out); HP_GUARD_END
+}
+int hp_gdn_state_dev(hp_engine* e, int slot, int gdn_layer, float** ptr_out, size_t* bytes_out) {
+    HP_GUARD_BEGIN HP_REQUIRE(e && ptr_out && bytes_out, "hp_gdn_state_dev: null pointer"); return e->impl.gdn_state(slot, gdn_layer, ptr_out, bytes_out); HP_GUARD_END
+}
+int hp_spec_begin(hp_engine* e, int slot, int id_last, int pos, const float* h_pending_dev) { HP_ENGINE_CALL(e->impl.spec_begin(slot, id_last, pos, h_pending_dev)) }
+int hp_spec_round(hp_engine* e, int slot, int n_draft, const int* subst_host, int* out_tokens_host, int* out_count) {
+    HP_ENGINE_CALL(e->impl.spec_round(slot, n_draft, subst_host, out_tokens_host, out_count))
 }
 
 }  // extern "C"

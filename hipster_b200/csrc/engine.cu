@@ -1,0 +1,546 @@
+// Host engine: see engine.h. Reference: engine/src/qwen35.cpp (constructor :80-153, forward :289-381, accept :383-403,
+// mtp_forward :405-424, topk :426-430), MTP driver engine/bench/spec27b.cpp:59-103.
+#include "hp_common.cuh"
+#include "engine.h"
+#include <cmath>
+#include <cstring>
+#include <algorithm>
+
+namespace hp {
+
+// ------------------------------------------------------------------ seeded weight generation (device)
+// Counter-based: value = f(seed, tensor id, index); integer arithmetic plus exactly-rounded float operations only,
+// so a CPU regenerates identical tensors. Normal deviates are approximated by the sum of four uniform 16-bit
+// integers (Irwin-Hall, sigma = 65536 * sqrt(4/12)), which is bounded by +-3.46 sigma.
+__host__ __device__ inline uint64_t splitmix64(uint64_t x) {
+    x += 0x9E3779B97F4A7C15ull; x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull; x = (x ^ (x >> 27)) * 0x94D049BB133111EBull; return x ^ (x >> 31);
+}
+__host__ __device__ inline uint64_t rnd64(uint64_t seed, uint64_t tid, uint64_t idx) { return splitmix64(splitmix64(seed ^ (tid * 0x9E3779B97F4A7C15ull)) + idx); }
+__host__ __device__ inline float irwin(uint64_t u) {
+    const int sum = (int)(u & 0xFFFF) + (int)((u >> 16) & 0xFFFF) + (int)((u >> 32) & 0xFFFF) + (int)(u >> 48) - 131070;
+    return (float)sum * 2.6429e-5f;
+}
+__host__ __device__ inline uint16_t f32_to_f16_bits(float f) {   // same rounding as the reference's f32_to_f16 (engine/src/quant.h:150-155)
+    const uint32_t x = f_bits(f); const uint32_t sign = (x >> 16) & 0x8000; const int e = (int)((x >> 23) & 0xff) - 127 + 15; uint32_t m = x & 0x7fffff;
+    if (e <= 0) { if (e < -10) return (uint16_t)sign; m |= 0x800000; const uint32_t t = 14 - e; uint32_t r = m >> t; if ((m >> (t - 1)) & 1) r++; return (uint16_t)(sign | r); }
+    if (e >= 31) return (uint16_t)(sign | 0x7c00);
+    uint32_t r = sign | ((uint32_t)e << 10) | (m >> 13); if (m & 0x1000) r++;
+    return (uint16_t)r;
+}
+__host__ __device__ inline uint16_t f32_to_bf16_bits(float f) { uint32_t u = f_bits(f); u += 0x7FFFu + ((u >> 16) & 1u); return (uint16_t)(u >> 16); }
+
+// Q4_K blocks: quants uniform 0..15, the 6-bit scales/mins uniform 0..63 (any 12 bytes), d and dmin = f16(|N(0, 0.01)|)
+__global__ void k_gen_q4k(uint64_t* __restrict__ w, size_t nwords, uint64_t seed, uint64_t tid) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; if (i >= nwords) return;
+    uint64_t v = rnd64(seed, tid, i);
+    if (i % 18 == 0) {
+        const size_t b = i / 18;
+        const uint16_t d = f32_to_f16_bits(fabsf(irwin(rnd64(seed, tid ^ 0xD00Dull, b))) * 0.01f);
+        const uint16_t dm = f32_to_f16_bits(fabsf(irwin(rnd64(seed, tid ^ 0xE00Eull, b))) * 0.01f);
+        v = (v & 0xFFFFFFFF00000000ull) | (uint64_t)d | ((uint64_t)dm << 16);
+    }
+    w[i] = v;
+}
+__global__ void k_gen_bf16(uint16_t* __restrict__ p, size_t n, uint64_t seed, uint64_t tid, float mean, float std) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; if (i >= n) return;
+    p[i] = f32_to_bf16_bits(mean + std * irwin(rnd64(seed, tid, i)));
+}
+__global__ void k_gen_f32(float* __restrict__ p, size_t n, uint64_t seed, uint64_t tid, float mean, float std, int neg_abs) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; if (i >= n) return;
+    float v = mean + std * irwin(rnd64(seed, tid, i)); if (neg_abs) v = -fabsf(v);
+    p[i] = v;
+}
+__global__ void k_set_ints(int* p, int n, int v) { const int i = blockIdx.x * blockDim.x + threadIdx.x; if (i < n) p[i] = v; }
+__global__ void k_reduce_planes(const float* __restrict__ parts, size_t part_stride, int P, float* __restrict__ y, int N, int ldy) {
+    const int n = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y; if (n >= N) return;
+    float v = parts[(size_t)r * N + n];
+    for (int p = 1; p < P; ++p) v = v + parts[(size_t)p * part_stride + (size_t)r * N + n];
+    y[(size_t)r * ldy + n] = v;
+}
+
+// ---- fused speculative round: tiny device-side bookkeeping kernels (the host loop of engine/bench/spec27b.cpp:77-103) ----
+enum { SP_ID_LAST = 0, SP_POS = 1, SP_MM = 2, SP_COUNT = 3, SP_POS_OLD = 4, SP_DRAFTS = 8, SP_IDS = 16, SP_OUT = 32, SP_SUBST = 48, SP_INTS = 64 };
+enum { D_TOK = 0, D_POS = 32, D_SLOT = 64, D_RGROUP = 96, D_GROUPS = 128, D_SEQS = 160, D_INTS = 256 };
+// draft step i: one row (token = last emitted token or the previous draft) at position pos + i (spec27b.cpp:81-85)
+__global__ void k_spec_draft_setup(const int* __restrict__ sp, int* __restrict__ d, int i, int slot) {
+    if (threadIdx.x) return;
+    d[D_TOK] = i == 0 ? sp[SP_ID_LAST] : sp[SP_DRAFTS + i - 1]; d[D_POS] = sp[SP_POS] + i; d[D_SLOT] = slot; d[D_RGROUP] = 0;
+    d[D_GROUPS] = 0; d[D_GROUPS + 1] = 1; d[D_GROUPS + 2] = slot; d[D_GROUPS + 3] = sp[SP_POS] + i;
+}
+// the draft is the MTP argmax unless the caller substitutes it (seeded acceptance control)
+__global__ void k_spec_take(int* __restrict__ sp, const int* __restrict__ mids, int i) {
+    if (threadIdx.x) return;
+    const int sub = sp[SP_SUBST + i]; sp[SP_DRAFTS + i] = sub >= 0 ? sub : mids[0];
+}
+// verify rows [id_last, d1..dn] at positions pos.. (spec27b.cpp:88-90)
+__global__ void k_spec_verify_setup(const int* __restrict__ sp, int* __restrict__ d, int n, int slot) {
+    const int t = threadIdx.x;
+    if (t <= n) { d[D_TOK + t] = t == 0 ? sp[SP_ID_LAST] : sp[SP_DRAFTS + t - 1]; d[D_POS + t] = sp[SP_POS] + t; d[D_SLOT + t] = slot; d[D_RGROUP + t] = 0; }
+    if (t == 0) { d[D_GROUPS] = 0; d[D_GROUPS + 1] = n + 1; d[D_GROUPS + 2] = slot; d[D_GROUPS + 3] = sp[SP_POS];
+                  d[D_SEQS] = 0; d[D_SEQS + 1] = n + 1; d[D_SEQS + 2] = slot; d[D_SEQS + 3] = 0; }
+}
+// greedy prefix acceptance (spec27b.cpp:92-102): mm accepted drafts, bonus = ids[mm], commit mm+1 rows, h_pending = h row mm
+__global__ void __launch_bounds__(256) k_spec_accept(int* __restrict__ sp, const int* __restrict__ ids, int* __restrict__ replay_n, int n, int slot,
+                                                      const float* __restrict__ h, float* __restrict__ hpend, int E) {
+    __shared__ int smm;
+    if (threadIdx.x == 0) {
+        int mm = 0; while (mm < n && ids[mm] == sp[SP_DRAFTS + mm]) ++mm;
+        for (int i = 0; i <= n; ++i) sp[SP_IDS + i] = ids[i];
+        for (int i = 0; i < mm; ++i) sp[SP_OUT + i] = sp[SP_DRAFTS + i];
+        sp[SP_OUT + mm] = ids[mm];
+        sp[SP_MM] = mm; sp[SP_COUNT] = mm + 1; sp[SP_POS_OLD] = sp[SP_POS]; sp[SP_POS] = sp[SP_POS] + mm + 1; sp[SP_ID_LAST] = ids[mm];
+        replay_n[slot] = mm + 1;
+        smm = mm;
+    }
+    __syncthreads();
+    const float* src = h + (size_t)smm * E;
+    for (int i = threadIdx.x; i < E; i += 256) hpend[i] = src[i];
+}
+// MTP catch-up rows: drafts at positions pos_old + 1 .. with the target's h rows (spec27b.cpp:99). All n rows run; rows
+// beyond the accepted prefix only write KV entries that the next round rewrites before reading them.
+__global__ void k_spec_catchup_setup(const int* __restrict__ sp, int* __restrict__ d, int n, int slot) {
+    const int t = threadIdx.x;
+    if (t < n) { d[D_TOK + t] = sp[SP_DRAFTS + t]; d[D_POS + t] = sp[SP_POS_OLD] + 1 + t; d[D_SLOT + t] = slot; d[D_RGROUP + t] = 0; }
+    if (t == 0) { d[D_GROUPS] = 0; d[D_GROUPS + 1] = n; d[D_GROUPS + 2] = slot; d[D_GROUPS + 3] = sp[SP_POS_OLD] + 1; }
+}
+
+// descriptor layout (ints)
+Engine::Engine(const hp_model_cfg& cfg) : c_(cfg) {}
+Engine::~Engine() {
+    for (cudaGraphExec_t g : graphs_) if (g) cudaGraphExecDestroy(g);
+    for (void* p : allocs_) cudaFree(p);
+    if (h_desc_) cudaFreeHost(h_desc_);
+    if (h_spec_) cudaFreeHost(h_spec_);
+    if (ev0_) cudaEventDestroy(ev0_); if (ev1_) cudaEventDestroy(ev1_);
+    if (s_) cudaStreamDestroy(s_);
+}
+int Engine::nattn() const { return c_.n_layer / c_.attn_every; }
+int Engine::ngdn() const { return c_.n_layer - nattn(); }
+
+int Engine::alloc(void** p, size_t bytes) {
+    cudaError_t e = cudaMalloc(p, bytes ? bytes : 16);
+    if (e != cudaSuccess) { set_error("out of device memory allocating %zu bytes (%s)", bytes, cudaGetErrorString(e)); return HP_ENOMEM; }
+    allocs_.push_back(*p); return HP_OK;
+}
+int Engine::gen_lin(Lin& l, int N, int K, uint64_t tid) {
+    l.N = N; l.K = K; l.bytes = (size_t)N * (K / 256) * 144; l.P = gemv_parts(N, K);
+    HP_REQUIRE(K % 256 == 0 && l.P > 0, "tensor %d x %d is not a valid Q4_K GEMV shape", N, K);
+    if (int rc = alloc((void**)&l.w, l.bytes)) return rc;
+    const size_t nwords = l.bytes / 8;
+    k_gen_q4k<<<(unsigned)((nwords + 255) / 256), 256, 0, s_>>>((uint64_t*)l.w, nwords, c_.seed, tid);
+    HP_CUDA(cudaGetLastError());
+    weight_bytes_ += l.bytes; return HP_OK;
+}
+int Engine::gen_bf16(uint16_t** p, size_t n, uint64_t tid, float mean, float std) {
+    if (int rc = alloc((void**)p, n * 2)) return rc;
+    k_gen_bf16<<<(unsigned)((n + 255) / 256), 256, 0, s_>>>(*p, n, c_.seed, tid, mean, std);
+    HP_CUDA(cudaGetLastError()); weight_bytes_ += n * 2; return HP_OK;
+}
+int Engine::gen_f32(float** p, size_t n, uint64_t tid, float mean, float std, bool neg_abs) {
+    if (int rc = alloc((void**)p, n * 4)) return rc;
+    k_gen_f32<<<(unsigned)((n + 255) / 256), 256, 0, s_>>>(*p, n, c_.seed, tid, mean, std, neg_abs ? 1 : 0);
+    HP_CUDA(cudaGetLastError()); weight_bytes_ += n * 4; return HP_OK;
+}
+
+#define HP_TRY(x) do { const int rc_ = (x); if (rc_ != HP_OK) return rc_; } while (0)
+static inline uint64_t tensor_id(int layer, int kind) { return (uint64_t)(layer + 1) * 64 + (uint64_t)kind; }
+
+int Engine::init() {
+    const hp_model_cfg& c = c_;
+    HP_REQUIRE(c.n_embd > 0 && c.n_embd % 256 == 0 && c.n_layer >= 1 && c.n_vocab > 0, "bad model shape");
+    HP_REQUIRE(c.n_head >= 1 && c.n_head_kv >= 1 && c.n_head % c.n_head_kv == 0 && (c.n_head / c.n_head_kv) * 8 <= ATTN_MAX_PAIRS, "bad attention head counts");
+    HP_REQUIRE(c.gdn_qk_heads >= 1 && c.gdn_v_heads % c.gdn_qk_heads == 0 && (c.gdn_v_heads * 128) % 256 == 0, "bad GDN head counts");
+    HP_REQUIRE(c.attn_every >= 1 && c.n_slots >= 1 && c.n_slots <= MAXS && c.max_ctx >= 16 && c.n_rot % 2 == 0 && c.n_rot <= 256, "bad configuration");
+    HP_REQUIRE(c.n_expert == 0 ? (c.n_ff > 0 && c.n_ff % 256 == 0) : (c.expert_ff % 256 == 0 && c.n_expert_used >= 1 && c.n_expert_used <= 15), "bad FFN shape");
+    HP_CUDA(cudaStreamCreateWithFlags(&s_, cudaStreamNonBlocking));
+    HP_CUDA(cudaEventCreate(&ev0_)); HP_CUDA(cudaEventCreate(&ev1_));
+    const int E = c.n_embd, nv = c.gdn_v_heads, nq = c.gdn_qk_heads;
+    const int gdn_in = (2 * nq + nv) * 128 + nv * 128 + 2 * nv, attn_in = c.n_head * 512 + 2 * c.n_head_kv * 256;
+    ld_in_ = gdn_in;
+    auto gen_layer = [&](LayerW& L, int il, bool is_attn) -> int {
+        L.is_attn = is_attn;
+        HP_TRY(gen_bf16(&L.attn_norm, E, tensor_id(il, TK_ATTN_NORM), 1.f, 0.1f));
+        HP_TRY(gen_bf16(&L.post_norm, E, tensor_id(il, TK_POST_NORM), 1.f, 0.1f));
+        if (is_attn) {
+            HP_TRY(gen_lin(L.in_proj, attn_in, E, tensor_id(il, TK_IN_PROJ)));
+            HP_TRY(gen_lin(L.out_proj, E, c.n_head * 256, tensor_id(il, TK_OUT_PROJ)));
+            HP_TRY(gen_bf16(&L.q_norm, 256, tensor_id(il, TK_Q_NORM), 1.f, 0.2f));
+            HP_TRY(gen_bf16(&L.k_norm, 256, tensor_id(il, TK_K_NORM), 1.f, 0.2f));
+        } else {
+            HP_TRY(gen_lin(L.in_proj, gdn_in, E, tensor_id(il, TK_IN_PROJ)));
+            HP_TRY(gen_lin(L.out_proj, E, nv * 128, tensor_id(il, TK_OUT_PROJ)));
+            HP_TRY(gen_f32(&L.conv_w, (size_t)(2 * nq + nv) * 128 * 4, tensor_id(il, TK_CONV_W), 0.f, 0.5f, false));
+            HP_TRY(gen_bf16(&L.dt_bias, nv, tensor_id(il, TK_DT_BIAS), 0.f, 0.5f));
+            HP_TRY(gen_bf16(&L.a_neg, nv, tensor_id(il, TK_A_NEG), -0.8f, 0.4f));
+            HP_TRY(gen_bf16(&L.ssm_norm, 128, tensor_id(il, TK_SSM_NORM), 1.f, 0.3f));
+        }
+        if (c.n_expert == 0) {
+            HP_TRY(gen_lin(L.gate_up, 2 * c.n_ff, E, tensor_id(il, TK_GATE_UP)));
+            HP_TRY(gen_lin(L.down, E, c.n_ff, tensor_id(il, TK_DOWN)));
+        }
+        return HP_OK;
+    };
+    layers_.resize(c.n_layer);
+    for (int il = 0; il < c.n_layer; ++il) HP_TRY(gen_layer(layers_[il], il, (il + 1) % c.attn_every == 0));
+    HP_TRY(gen_bf16(&embed_, (size_t)c.n_vocab * E, tensor_id(-1, TK_EMBED), 0.f, 1.f));
+    HP_TRY(gen_bf16(&output_norm_, E, tensor_id(-1, TK_OUTPUT_NORM), 1.f, 0.1f));
+    HP_TRY(gen_lin(lm_head_, c.n_vocab, E, tensor_id(-1, TK_LM_HEAD)));
+    if (c.has_mtp) {
+        HP_TRY(gen_layer(mtp_, c.n_layer, true));
+        HP_TRY(gen_bf16(&mtp_enorm_, E, tensor_id(-1, TK_MTP_ENORM), 1.f, 0.1f));
+        HP_TRY(gen_bf16(&mtp_hnorm_, E, tensor_id(-1, TK_MTP_HNORM), 1.f, 0.1f));
+        HP_TRY(gen_bf16(&mtp_head_norm_, E, tensor_id(-1, TK_MTP_HEAD_NORM), 1.f, 0.1f));
+        HP_TRY(gen_lin(eh_proj_, E, 2 * E, tensor_id(-1, TK_MTP_EH_PROJ)));
+    }
+    // RoPE table (cos, sin) of pos * base^(-2i/n_rot), computed in double precision on the host
+    {
+        const int half = c.n_rot / 2; std::vector<float> tab((size_t)c.max_ctx * half * 2);
+        for (int p = 0; p < c.max_ctx; ++p)
+            for (int i = 0; i < half; ++i) {
+                const double th = (double)p * std::pow((double)c.rope_base, -2.0 * i / (double)c.n_rot);
+                tab[((size_t)p * half + i) * 2] = (float)std::cos(th); tab[((size_t)p * half + i) * 2 + 1] = (float)std::sin(th);
+            }
+        HP_TRY(alloc((void**)&rope_, tab.size() * 4));
+        HP_CUDA(cudaMemcpyAsync(rope_, tab.data(), tab.size() * 4, cudaMemcpyHostToDevice, s_));
+        HP_CUDA(cudaStreamSynchronize(s_));
+    }
+    // state
+    st_layer_ = (size_t)nv * 128 * 128; st_stride_ = st_layer_ * ngdn();
+    cs_layer_ = (size_t)nv * 3 * 384; cs_stride_ = cs_layer_ * ngdn();
+    HP_TRY(alloc((void**)&gdn_state_, st_stride_ * c.n_slots * 4)); HP_TRY(alloc((void**)&conv_state_, cs_stride_ * c.n_slots * 4));
+    kv_layer_ = (size_t)c.n_head_kv * c.max_ctx * 256; kv_slot_ = kv_layer_ * nattn();
+    HP_TRY(alloc((void**)&kc_, kv_slot_ * c.n_slots * 2)); HP_TRY(alloc((void**)&vc_, kv_slot_ * c.n_slots * 2));
+    HP_CUDA(cudaMemsetAsync(kc_, 0, kv_slot_ * c.n_slots * 2, s_)); HP_CUDA(cudaMemsetAsync(vc_, 0, kv_slot_ * c.n_slots * 2, s_));
+    if (c.has_mtp) {
+        HP_TRY(alloc((void**)&mkc_, kv_layer_ * c.n_slots * 2)); HP_TRY(alloc((void**)&mvc_, kv_layer_ * c.n_slots * 2));
+        HP_CUDA(cudaMemsetAsync(mkc_, 0, kv_layer_ * c.n_slots * 2, s_)); HP_CUDA(cudaMemsetAsync(mvc_, 0, kv_layer_ * c.n_slots * 2, s_));
+    }
+    sv_layer_ = (size_t)nv * 8 * 388; sv_stride_ = sv_layer_ * ngdn();   // raw GDN inputs of the last pass, per slot / layer / head (replay buffers, qwen35.h:124)
+    HP_TRY(alloc((void**)&saved_, sv_stride_ * c.n_slots * 4)); HP_CUDA(cudaMemsetAsync(saved_, 0, sv_stride_ * c.n_slots * 4, s_));
+    HP_TRY(alloc((void**)&replay_n_, MAXS * 4)); HP_CUDA(cudaMemsetAsync(replay_n_, 0, MAXS * 4, s_));
+    pend_.assign(c.n_slots, 0); last_r0_.assign(c.n_slots, 0); last_T_.assign(c.n_slots, 0);
+    // work buffers
+    const int F = c.n_expert ? c.expert_ff : c.n_ff;
+    const size_t bigw = std::max<size_t>({(size_t)gdn_in, (size_t)attn_in, (size_t)2 * F, (size_t)2 * E});
+    const size_t kmax = std::max<size_t>({(size_t)2 * E, (size_t)F, (size_t)c.n_head * 256, (size_t)nv * 128});
+    HP_TRY(alloc((void**)&x_, (size_t)MAXR * E * 4)); HP_TRY(alloc((void**)&emb_, (size_t)MAXR * E * 4));
+    HP_TRY(alloc((void**)&big_, (size_t)MAXR * bigw * 4)); HP_TRY(alloc((void**)&cat_, (size_t)MAXR * 2 * E * 4));
+    HP_TRY(alloc((void**)&yparts_, (size_t)4 * MAXR * std::max<size_t>(bigw, E) * 4));
+    HP_TRY(alloc((void**)&logits_, (size_t)MAXR * c.n_vocab * 4)); HP_TRY(alloc((void**)&mlogits_, (size_t)MAXR * c.n_vocab * 4));
+    HP_TRY(alloc((void**)&h_, (size_t)MAXR * E * 4)); HP_TRY(alloc((void**)&mh_, (size_t)MAXR * E * 4));
+    HP_CUDA(cudaMemsetAsync(h_, 0, (size_t)MAXR * E * 4, s_)); HP_CUDA(cudaMemsetAsync(mh_, 0, (size_t)MAXR * E * 4, s_));
+    HP_TRY(alloc(&xq_.q, xq_q_bytes(MAXR, (int)kmax))); HP_TRY(alloc(&xq_.sc, xq_sc_floats(MAXR, (int)kmax) * 4));
+    HP_CUDA(cudaMemsetAsync(xq_.q, 0, xq_q_bytes(MAXR, (int)kmax), s_)); HP_CUDA(cudaMemsetAsync(xq_.sc, 0, xq_sc_floats(MAXR, (int)kmax) * 4, s_));
+    nsplit_max_ = (c.max_ctx + ATTN_SPLIT - 1) / ATTN_SPLIT;
+    const size_t np = attn_partial_floats(MAXR / 8 + MAXS, c.n_head_kv, nsplit_max_);
+    HP_TRY(alloc((void**)&pO_, np * 256 * 4)); HP_TRY(alloc((void**)&pm_, np * 4)); HP_TRY(alloc((void**)&pl_, np * 4));
+    HP_TRY(alloc((void**)&d_desc_, D_INTS * 4)); HP_CUDA(cudaMallocHost((void**)&h_desc_, D_INTS * 4)); memset(h_desc_, 0, D_INTS * 4);
+    HP_TRY(alloc((void**)&d_ids_, MAXR * 4)); HP_TRY(alloc((void**)&d_mids_, MAXR * 4)); HP_TRY(alloc((void**)&d_vals_, MAXR * 4)); HP_TRY(alloc((void**)&d_mvals_, MAXR * 4));
+    HP_TRY(alloc(&am_scratch_, argmax_scratch_bytes(MAXR, c.n_vocab)));
+    HP_TRY(alloc((void**)&d_spec_, SP_INTS * 4)); HP_CUDA(cudaMallocHost((void**)&h_spec_, 2 * SP_INTS * 4));
+    HP_CUDA(cudaMemsetAsync(d_spec_, 0, SP_INTS * 4, s_));
+    HP_TRY(alloc((void**)&hpend_, (size_t)E * 4)); HP_CUDA(cudaMemsetAsync(hpend_, 0, (size_t)E * 4, s_));
+    HP_TRY(alloc((void**)&err_, 4)); HP_CUDA(cudaMemsetAsync(err_, 0, 4, s_));
+    HP_TRY(reset());
+    HP_CUDA(cudaStreamSynchronize(s_));
+    return HP_OK;
+}
+
+int Engine::reset() {
+    HP_CUDA(cudaMemsetAsync(gdn_state_, 0, st_stride_ * c_.n_slots * 4, s_)); HP_CUDA(cudaMemsetAsync(conv_state_, 0, cs_stride_ * c_.n_slots * 4, s_));
+    HP_CUDA(cudaMemsetAsync(replay_n_, 0, MAXS * 4, s_));
+    for (int s = 0; s < c_.n_slots; ++s) { pend_[s] = 0; last_T_[s] = 0; last_r0_[s] = 0; }
+    return HP_OK;
+}
+int Engine::reset_slot(int slot) {
+    HP_REQUIRE(slot >= 0 && slot < c_.n_slots, "reset_slot: bad slot %d", slot);
+    HP_CUDA(cudaMemsetAsync(gdn_state_ + (size_t)slot * st_stride_, 0, st_stride_ * 4, s_)); HP_CUDA(cudaMemsetAsync(conv_state_ + (size_t)slot * cs_stride_, 0, cs_stride_ * 4, s_));
+    HP_CUDA(cudaMemsetAsync(replay_n_ + slot, 0, 4, s_));
+    pend_[slot] = 0; last_T_[slot] = 0; return HP_OK;
+}
+
+int Engine::upload_desc() { HP_CUDA(cudaMemcpyAsync(d_desc_, h_desc_, D_INTS * 4, cudaMemcpyHostToDevice, s_)); return HP_OK; }
+
+int Engine::lin_parts(const Lin& l, int R) {
+    return gemv_q4k_q8_parts(l.w, xq_, yparts_, l.N, l.K, R, l.N, (size_t)R * l.N, err_, s_, false);
+}
+int Engine::lin(const Lin& l, float* out, int ld, int R) {
+    if (l.P == 1) return gemv_q4k_q8_parts(l.w, xq_, out, l.N, l.K, R, ld, 0, err_, s_, false);
+    HP_TRY(lin_parts(l, R));
+    k_reduce_planes<<<dim3((l.N + 255) / 256, R), 256, 0, s_>>>(yparts_, (size_t)R * l.N, l.P, out, l.N, ld);
+    HP_CUDA(cudaGetLastError()); return HP_OK;
+}
+// residual add of the previous projection's planes + RMSNorm + quantise (qwen35.cpp:311-315)
+int Engine::norm_in(const Lin* prev, bool have_y, const uint16_t* w, float* xn, int R) {
+    return add_rmsnorm_quant(x_, have_y ? yparts_ : nullptr, have_y ? prev->P : 0, have_y ? (size_t)R * prev->N : 0, have_y ? prev->N : 0, w, xn, xq_, R, c_.n_embd, c_.rms_eps, s_);
+}
+// qwen35.cpp:247-276
+int Engine::attn_block(const LayerW& L, uint16_t* kc, uint16_t* vc, size_t kv_stride, int R, int ngroups) {
+    const int ld = L.in_proj.N;
+    HP_TRY(lin(L.in_proj, big_, ld, R));
+    AttnParams p; p.qkv = big_; p.ld = ld; p.n_head = c_.n_head; p.n_kv = c_.n_head_kv; p.n_rot = c_.n_rot;
+    p.q_norm = L.q_norm; p.k_norm = L.k_norm; p.rope = rope_; p.row_pos = d_desc_ + D_POS; p.row_slot = d_desc_ + D_SLOT; p.row_group = d_desc_ + D_RGROUP; p.groups = d_desc_ + D_GROUPS;
+    p.kc = kc; p.vc = vc; p.kv_stride = kv_stride; p.max_ctx = c_.max_ctx; p.pO = pO_; p.pm = pm_; p.pl = pl_; p.nsplit_max = nsplit_max_;
+    p.out = nullptr; p.xq = xq_; p.eps = c_.rms_eps;
+    HP_TRY(attn_rope_kv(p, R, s_));
+    HP_TRY(attn_decode(p, R, ngroups, s_));
+    return lin_parts(L.out_proj, R);
+}
+// qwen35.cpp:278-287
+int Engine::ffn_block(const LayerW& L, int R) {
+    const int F = c_.n_ff;
+    HP_TRY(lin(L.gate_up, big_, 2 * F, R));
+    HP_TRY(silu_mul_quant(big_, 2 * F, F, xq_, R, s_));
+    return lin_parts(L.down, R);
+}
+
+// qwen35.cpp:309-376
+int Engine::run_pass(int R, int nseq, int ngroups) {
+    const hp_model_cfg& c = c_;
+    HP_TRY(embed_bf16(d_desc_ + D_TOK, embed_, x_, R, c.n_embd, c.n_vocab, s_));
+    const Lin* prev = nullptr; int gi = 0, ai = 0;
+    for (int il = 0; il < c.n_layer; ++il) {
+        const LayerW& L = layers_[il];
+        HP_TRY(norm_in(prev, prev != nullptr, L.attn_norm, nullptr, R));
+        if (!L.is_attn) {
+            HP_TRY(lin(L.in_proj, big_, ld_in_, R));
+            GdnParams g; g.rows = big_; g.saved = saved_ + (size_t)gi * sv_layer_; g.saved_stride = sv_stride_; g.ld = ld_in_;
+            g.n_qk = c.gdn_qk_heads; g.n_v = c.gdn_v_heads;
+            g.off_z = (2 * g.n_qk + g.n_v) * 128; g.off_b = g.off_z + g.n_v * 128; g.off_a = g.off_b + g.n_v;
+            g.conv_w = L.conv_w; g.dt_bias = L.dt_bias; g.a_neg = L.a_neg; g.norm_w = L.ssm_norm;
+            g.state = gdn_state_ + (size_t)gi * st_layer_; g.conv_state = conv_state_ + (size_t)gi * cs_layer_; g.state_stride = st_stride_; g.conv_stride = cs_stride_;
+            g.seq = d_desc_ + D_SEQS; g.replay_n = replay_n_; g.out = nullptr; g.xq = xq_; g.snap = nullptr; g.snap_row_stride = 0; g.eps = c.rms_eps; g.sigmoid_gate = c.gdn_sigmoid_gate;
+            HP_TRY(gdn_forward(g, nseq, s_));
+            HP_TRY(lin_parts(L.out_proj, R));
+            ++gi;
+        } else {
+            HP_TRY(attn_block(L, kc_ + (size_t)ai * kv_layer_, vc_ + (size_t)ai * kv_layer_, kv_slot_, R, ngroups));
+            ++ai;
+        }
+        HP_TRY(norm_in(&L.out_proj, true, L.post_norm, nullptr, R));
+        HP_TRY(ffn_block(L, R));
+        prev = &L.down;
+    }
+    HP_TRY(norm_in(prev, true, output_norm_, h_, R));      // h for all rows (+ q8 of all rows), qwen35.cpp:370
+    HP_TRY(lin(lm_head_, logits_, c.n_vocab, R));
+    return argmax_rows(logits_, R, c.n_vocab, c.n_vocab, d_ids_, d_vals_, am_scratch_, s_);
+}
+
+int Engine::flush_commits() {
+    // apply pending accepts: a pass with no new rows (the GDN kernel only replays and writes the state back)
+    int n = 0; int* seqs = h_desc_ + D_SEQS;
+    // every slot: the replay count lives on the device (the fused round sets it there), 0 means nothing to do
+    for (int s = 0; s < c_.n_slots; ++s) { seqs[n * 4] = 0; seqs[n * 4 + 1] = 0; seqs[n * 4 + 2] = s; seqs[n * 4 + 3] = 0; ++n; }
+    HP_TRY(upload_desc());
+    HP_CUDA(cudaStreamSynchronize(s_));   // the pinned descriptor is rewritten by the caller right after
+    int gi = 0;
+    for (int il = 0; il < c_.n_layer; ++il) {
+        const LayerW& L = layers_[il]; if (L.is_attn) continue;
+        GdnParams g; g.rows = big_; g.saved = saved_ + (size_t)gi * sv_layer_; g.saved_stride = sv_stride_; g.ld = ld_in_;
+        g.n_qk = c_.gdn_qk_heads; g.n_v = c_.gdn_v_heads; g.off_z = (2 * g.n_qk + g.n_v) * 128; g.off_b = g.off_z + g.n_v * 128; g.off_a = g.off_b + g.n_v;
+        g.conv_w = L.conv_w; g.dt_bias = L.dt_bias; g.a_neg = L.a_neg; g.norm_w = L.ssm_norm;
+        g.state = gdn_state_ + (size_t)gi * st_layer_; g.conv_state = conv_state_ + (size_t)gi * cs_layer_; g.state_stride = st_stride_; g.conv_stride = cs_stride_;
+        g.seq = d_desc_ + D_SEQS; g.replay_n = replay_n_; g.out = nullptr; g.xq = XQ8F{nullptr, nullptr}; g.snap = nullptr; g.snap_row_stride = 0; g.eps = c_.rms_eps; g.sigmoid_gate = c_.gdn_sigmoid_gate;
+        HP_TRY(gdn_forward(g, n, s_));
+        ++gi;
+    }
+    HP_CUDA(cudaMemsetAsync(replay_n_, 0, MAXS * 4, s_));
+    for (int s = 0; s < c_.n_slots; ++s) pend_[s] = 0;
+    return HP_OK;
+}
+
+int Engine::forward(const hp_slot_req* reqs, int S, float* ms) {
+    HP_REQUIRE(reqs && S >= 1 && S <= c_.n_slots, "bad S");                                  // qwen35.cpp:290
+    int T = 0; for (int i = 0; i < S; ++i) T += reqs[i].T;
+    HP_REQUIRE(T >= 1 && T <= MAXR, "bad T");                                                // qwen35.cpp:293
+    std::vector<char> in_pass(c_.n_slots, 0);
+    for (int i = 0; i < S; ++i) {
+        const hp_slot_req& r = reqs[i];
+        HP_REQUIRE(r.slot >= 0 && r.slot < c_.n_slots && r.T >= 1 && r.T <= 8 && r.pos >= 0 && r.pos + r.T <= c_.max_ctx && r.tokens && !in_pass[r.slot], "bad request");   // qwen35.cpp:298
+        in_pass[r.slot] = 1;
+    }
+    int* d = h_desc_; int r0 = 0, ng = 0;
+    for (int i = 0; i < S; ++i) {
+        const hp_slot_req& r = reqs[i];
+        d[D_SEQS + i * 4] = r0; d[D_SEQS + i * 4 + 1] = r.T; d[D_SEQS + i * 4 + 2] = r.slot; d[D_SEQS + i * 4 + 3] = 0;
+        d[D_GROUPS + ng * 4] = r0; d[D_GROUPS + ng * 4 + 1] = r.T; d[D_GROUPS + ng * 4 + 2] = r.slot; d[D_GROUPS + ng * 4 + 3] = r.pos;
+        for (int t = 0; t < r.T; ++t) { d[D_TOK + r0 + t] = r.tokens[t]; d[D_POS + r0 + t] = r.pos + t; d[D_SLOT + r0 + t] = r.slot; d[D_RGROUP + r0 + t] = ng; }
+        ++ng; r0 += r.T;
+    }
+    HP_CUDA(cudaEventRecord(ev0_, s_));
+    HP_TRY(upload_desc());
+    HP_TRY(run_pass(T, S, ng));
+    // the accepted prefixes of the previous pass are now part of the stored state
+    r0 = 0;
+    for (int i = 0; i < S; ++i) {
+        const hp_slot_req& r = reqs[i];
+        HP_CUDA(cudaMemsetAsync(replay_n_ + r.slot, 0, 4, s_)); pend_[r.slot] = 0;
+        last_r0_[r.slot] = r0; last_T_[r.slot] = r.T; r0 += r.T;
+    }
+    last_rows_ = T;
+    HP_CUDA(cudaEventRecord(ev1_, s_)); HP_CUDA(cudaEventSynchronize(ev1_));
+    HP_CUDA(cudaEventElapsedTime(&last_ms_, ev0_, ev1_));
+    int herr = 0; HP_CUDA(cudaMemcpy(&herr, err_, 4, cudaMemcpyDeviceToHost));
+    if (herr) { cudaMemset(err_, 0, 4); set_error("a kernel gave up a bounded wait (device status %d)", herr); return herr; }
+    if (ms) *ms = last_ms_;
+    return HP_OK;
+}
+
+int Engine::accept(int slot, int m) {
+    HP_REQUIRE(slot >= 0 && slot < c_.n_slots && last_T_[slot] > 0, "accept: slot had no rows in the last pass");   // qwen35.cpp:384
+    HP_REQUIRE(m >= 1 && m <= last_T_[slot], "bad accept");                                                          // qwen35.cpp:386
+    pend_[slot] = m; last_T_[slot] = 0;
+    k_set_ints<<<1, 32, 0, s_>>>(replay_n_ + slot, 1, m);
+    HP_CUDA(cudaGetLastError()); return HP_OK;
+}
+
+// qwen35.cpp:405-424
+int Engine::run_mtp(int R, int ngroups, const float* h_dev, int ldh, bool want_logits) {
+    const hp_model_cfg& c = c_;
+    HP_TRY(embed_bf16(d_desc_ + D_TOK, embed_, emb_, R, c.n_embd, c.n_vocab, s_));
+    HP_TRY(norm2_concat_quant(emb_, mtp_enorm_, h_dev, ldh, mtp_hnorm_, nullptr, xq_, R, c.n_embd, c.rms_eps, s_));
+    HP_TRY(lin(eh_proj_, x_, c.n_embd, R));
+    HP_TRY(norm_in(nullptr, false, mtp_.attn_norm, nullptr, R));
+    HP_TRY(attn_block(mtp_, mkc_, mvc_, kv_layer_, R, ngroups));
+    HP_TRY(norm_in(&mtp_.out_proj, true, mtp_.post_norm, nullptr, R));
+    HP_TRY(ffn_block(mtp_, R));
+    HP_TRY(norm_in(&mtp_.down, true, mtp_head_norm_, mh_, R));
+    if (want_logits) {
+        HP_TRY(lin(lm_head_, mlogits_, c.n_vocab, R));
+        HP_TRY(argmax_rows(mlogits_, R, c.n_vocab, c.n_vocab, d_mids_, d_mvals_, am_scratch_, s_));
+    }
+    return HP_OK;
+}
+int Engine::mtp_forward(const int* tokens, const float* h_dev, int T, int pos0, int slot, bool want_logits) {
+    HP_REQUIRE(c_.has_mtp, "model has no MTP block");
+    HP_REQUIRE(tokens && h_dev && T >= 1 && T <= 8 && slot >= 0 && slot < c_.n_slots && pos0 >= 0 && pos0 + T <= c_.max_ctx, "bad T");   // qwen35.cpp:406
+    int* d = h_desc_;
+    for (int t = 0; t < T; ++t) { d[D_TOK + t] = tokens[t]; d[D_POS + t] = pos0 + t; d[D_SLOT + t] = slot; d[D_RGROUP + t] = 0; }
+    d[D_GROUPS] = 0; d[D_GROUPS + 1] = T; d[D_GROUPS + 2] = slot; d[D_GROUPS + 3] = pos0;
+    HP_TRY(upload_desc());
+    HP_TRY(run_mtp(T, 1, h_dev, c_.n_embd, want_logits));
+    HP_CUDA(cudaStreamSynchronize(s_));
+    return HP_OK;
+}
+
+int Engine::topk(int which, int T, int* ids, float* vals) {
+    HP_REQUIRE(T >= 1 && T <= MAXR && ids, "topk: bad arguments");
+    HP_CUDA(cudaStreamSynchronize(s_));
+    HP_CUDA(cudaMemcpy(ids, which ? d_mids_ : d_ids_, T * 4, cudaMemcpyDeviceToHost));
+    if (vals) HP_CUDA(cudaMemcpy(vals, which ? d_mvals_ : d_vals_, T * 4, cudaMemcpyDeviceToHost));
+    return HP_OK;
+}
+
+int Engine::tensor(int layer, int kind, void** ptr, size_t* bytes) const {
+    const hp_model_cfg& c = c_; const int E = c.n_embd;
+    auto set = [&](const void* p, size_t b) { *ptr = (void*)p; *bytes = b; return HP_OK; };
+    if (layer < 0) {
+        switch (kind) {
+            case TK_EMBED: return set(embed_, (size_t)c.n_vocab * E * 2);
+            case TK_OUTPUT_NORM: return set(output_norm_, (size_t)E * 2);
+            case TK_LM_HEAD: return set(lm_head_.w, lm_head_.bytes);
+            case TK_MTP_ENORM: return set(mtp_enorm_, (size_t)E * 2);
+            case TK_MTP_HNORM: return set(mtp_hnorm_, (size_t)E * 2);
+            case TK_MTP_HEAD_NORM: return set(mtp_head_norm_, (size_t)E * 2);
+            case TK_MTP_EH_PROJ: return set(eh_proj_.w, eh_proj_.bytes);
+        }
+        set_error("unknown model-level tensor %d", kind); return HP_EINVAL;
+    }
+    HP_REQUIRE(layer <= c.n_layer && (layer < c.n_layer || c.has_mtp), "bad layer %d", layer);
+    const LayerW& L = layer == c.n_layer ? mtp_ : layers_[layer];
+    const int nv = c.gdn_v_heads, nq = c.gdn_qk_heads;
+    switch (kind) {
+        case TK_ATTN_NORM: return set(L.attn_norm, (size_t)E * 2);
+        case TK_POST_NORM: return set(L.post_norm, (size_t)E * 2);
+        case TK_IN_PROJ: return set(L.in_proj.w, L.in_proj.bytes);
+        case TK_OUT_PROJ: return set(L.out_proj.w, L.out_proj.bytes);
+        case TK_GATE_UP: return set(L.gate_up.w, L.gate_up.bytes);
+        case TK_DOWN: return set(L.down.w, L.down.bytes);
+        case TK_CONV_W: return set(L.conv_w, (size_t)(2 * nq + nv) * 128 * 4 * 4);
+        case TK_DT_BIAS: return set(L.dt_bias, (size_t)nv * 2);
+        case TK_A_NEG: return set(L.a_neg, (size_t)nv * 2);
+        case TK_SSM_NORM: return set(L.ssm_norm, 256);
+        case TK_Q_NORM: return set(L.q_norm, 512);
+        case TK_K_NORM: return set(L.k_norm, 512);
+    }
+    set_error("unknown layer tensor %d", kind); return HP_EINVAL;
+}
+int Engine::gdn_state(int slot, int gdn_layer, float** ptr, size_t* bytes) {
+    HP_REQUIRE(slot >= 0 && slot < c_.n_slots && gdn_layer >= 0 && gdn_layer < ngdn(), "gdn_state: bad index");
+    HP_TRY(flush_commits());
+    HP_CUDA(cudaStreamSynchronize(s_));
+    *ptr = gdn_state_ + (size_t)slot * st_stride_ + (size_t)gdn_layer * st_layer_; *bytes = st_layer_ * 4;
+    return HP_OK;
+}
+
+size_t Engine::pass_weight_bytes(bool mtp, bool with_head) const {
+    size_t b = 0;
+    if (!mtp) for (const LayerW& L : layers_) b += L.in_proj.bytes + L.out_proj.bytes + L.gate_up.bytes + L.down.bytes;
+    else b += eh_proj_.bytes + mtp_.in_proj.bytes + mtp_.out_proj.bytes + mtp_.gate_up.bytes + mtp_.down.bytes;
+    if (with_head) b += lm_head_.bytes;
+    return b;
+}
+
+// ------------------------------------------------------------------ fused device-side round
+int Engine::spec_begin(int slot, int id_last, int pos, const float* h_pending_dev) {
+    HP_REQUIRE(c_.has_mtp, "model has no MTP block");
+    HP_REQUIRE(slot >= 0 && slot < c_.n_slots && pos >= 0 && pos < c_.max_ctx && h_pending_dev, "spec_begin: bad arguments");
+    h_spec_[0] = id_last; h_spec_[1] = pos;
+    HP_CUDA(cudaMemcpyAsync(d_spec_, h_spec_, 8, cudaMemcpyHostToDevice, s_));
+    HP_CUDA(cudaMemcpyAsync(hpend_, h_pending_dev, (size_t)c_.n_embd * 4, cudaMemcpyDeviceToDevice, s_));
+    HP_CUDA(cudaStreamSynchronize(s_));
+    spec_pos_ = pos; spec_slot_ = slot; last_T_[slot] = 0;
+    return HP_OK;
+}
+int Engine::enqueue_round(int slot, int n) {
+    HP_CUDA(cudaMemcpyAsync(d_spec_ + SP_SUBST, h_spec_, 8 * 4, cudaMemcpyHostToDevice, s_));
+    for (int i = 0; i < n; ++i) {   // draft, chained on the MTP's own h (spec27b.cpp:81-85)
+        k_spec_draft_setup<<<1, 32, 0, s_>>>(d_spec_, d_desc_, i, slot);
+        HP_TRY(run_mtp(1, 1, i == 0 ? hpend_ : mh_, c_.n_embd, true));
+        k_spec_take<<<1, 32, 0, s_>>>(d_spec_, d_mids_, i);
+    }
+    k_spec_verify_setup<<<1, 32, 0, s_>>>(d_spec_, d_desc_, n, slot);
+    HP_TRY(run_pass(n + 1, 1, 1));
+    k_spec_accept<<<1, 256, 0, s_>>>(d_spec_, d_ids_, replay_n_, n, slot, h_, hpend_, c_.n_embd);
+    k_spec_catchup_setup<<<1, 32, 0, s_>>>(d_spec_, d_desc_, n, slot);
+    HP_TRY(run_mtp(n, 1, h_, c_.n_embd, false));
+    HP_CUDA(cudaMemcpyAsync(h_spec_ + SP_INTS, d_spec_, SP_INTS * 4, cudaMemcpyDeviceToHost, s_));
+    HP_CUDA(cudaGetLastError());
+    return HP_OK;
+}
+int Engine::spec_round(int slot, int n, const int* subst, int* out_tokens, int* out_count) {
+    HP_REQUIRE(c_.has_mtp, "model has no MTP block");
+    HP_REQUIRE(slot == spec_slot_ && n >= 1 && n <= 7 && out_tokens && out_count, "spec_round: bad arguments (call hp_spec_begin first; 1 <= n_draft <= 7)");
+    HP_REQUIRE(spec_pos_ + 2 * n + 2 <= c_.max_ctx, "spec_round: context exhausted");
+    for (int i = 0; i < 8; ++i) h_spec_[i] = (subst && i < n) ? subst[i] : -1;
+    static const bool no_graph = getenv("HIPSTER_B200_NO_GRAPH") != nullptr;
+    const int key = slot * 8 + n;
+    if (no_graph) HP_TRY(enqueue_round(slot, n));
+    else {
+        if (!graphs_[key]) {
+            if (!warmed_[key]) { HP_TRY(enqueue_round(slot, n)); HP_CUDA(cudaStreamSynchronize(s_)); warmed_[key] = true; goto done; }   // first call: eager (sets kernel attributes)
+            cudaGraph_t g = nullptr;
+            HP_CUDA(cudaStreamBeginCapture(s_, cudaStreamCaptureModeThreadLocal));
+            const int rc = enqueue_round(slot, n);
+            const cudaError_t ce = cudaStreamEndCapture(s_, &g);
+            if (rc != HP_OK) { if (g) cudaGraphDestroy(g); return rc; }
+            HP_CUDA(ce);
+            HP_CUDA(cudaGraphInstantiate(&graphs_[key], g, 0));
+            HP_CUDA(cudaGraphDestroy(g));
+        }
+        HP_CUDA(cudaGraphLaunch(graphs_[key], s_));
+    }
+done:
+    HP_CUDA(cudaStreamSynchronize(s_));
+    {
+        int herr = 0; HP_CUDA(cudaMemcpy(&herr, err_, 4, cudaMemcpyDeviceToHost));
+        if (herr) { cudaMemset(err_, 0, 4); set_error("a kernel gave up a bounded wait (device status %d)", herr); return herr; }
+    }
+    const int* r = h_spec_ + SP_INTS;
+    *out_count = r[SP_COUNT];
+    for (int i = 0; i < r[SP_COUNT]; ++i) out_tokens[i] = r[SP_OUT + i];
+    spec_pos_ = r[SP_POS];
+    return HP_OK;
+}
+
+}  // namespace hp

@@ -1,0 +1,95 @@
+// Host engine of the MTP speculative-decode path: weight arena (random-init, generated on device from a seed),
+// per-slot recurrent state and KV caches, the verify / decode pass, the MTP draft block, accept with deferred commit,
+// and the fused device-side speculative round. C++ inside the library; exported through the C ABI in capi.cu.
+//
+// Reference: class Qwen35 (engine/src/qwen35.h:50-149, qwen35.cpp) and class Qwen4Exp (engine/src/qwen4exp.h:54-90).
+#pragma once
+#include "kernels.h"
+#include "../../include/hipster_b200.h"
+#include <vector>
+#include <string>
+
+namespace hp {
+
+struct Lin { uint8_t* w = nullptr; int N = 0, K = 0, P = 1; size_t bytes = 0; };   // merged Q4_K matrix [N][K/256 blocks]
+
+struct LayerW {
+    bool is_attn = false;
+    uint16_t *attn_norm = nullptr, *post_norm = nullptr;          // bf16 [E]
+    Lin in_proj;      // GDN: qkv | z | beta | alpha rows; attention: q_full | k | v rows
+    Lin out_proj;     // GDN: ssm_out; attention: wo
+    Lin gate_up, down;                                            // dense FFN (gate rows then up rows)
+    float* conv_w = nullptr; uint16_t *dt_bias = nullptr, *a_neg = nullptr, *ssm_norm = nullptr;   // GDN
+    uint16_t *q_norm = nullptr, *k_norm = nullptr;                // attention
+    // MoE (n_expert > 0): router f32 [n_expert + 1][E]; expert matrices contiguous per tensor
+    float* router = nullptr; Lin exp_gate_up, exp_down, sh_gate_up, sh_down;
+};
+
+enum TensorKind { TK_ATTN_NORM = 0, TK_POST_NORM, TK_IN_PROJ, TK_OUT_PROJ, TK_GATE_UP, TK_DOWN, TK_CONV_W, TK_DT_BIAS, TK_A_NEG, TK_SSM_NORM,
+                  TK_Q_NORM, TK_K_NORM, TK_ROUTER, TK_EXP_GATE_UP, TK_EXP_DOWN, TK_SH_GATE_UP, TK_SH_DOWN,
+                  TK_EMBED = 32, TK_OUTPUT_NORM, TK_LM_HEAD, TK_MTP_ENORM, TK_MTP_HNORM, TK_MTP_EH_PROJ, TK_MTP_HEAD_NORM };
+
+class Engine {
+public:
+    static constexpr int MAXR = 32, MAXS = 8;
+    explicit Engine(const hp_model_cfg& cfg);
+    ~Engine();
+    int init();                                              // allocate + generate weights; HP_* status
+    int forward(const hp_slot_req* reqs, int S, float* ms);  // Qwen35::forward(const SlotReq*, int) (qwen35.h:62)
+    int accept(int slot, int m);                             // Qwen35::accept (qwen35.h:66)
+    int mtp_forward(const int* tokens, const float* h_dev, int T, int pos0, int slot, bool want_logits);   // qwen35.h:70
+    int topk(int which, int T, int* ids, float* vals);       // k = 1 (qwen35.h:87)
+    int reset(); int reset_slot(int slot);
+    int flush_commits();                                     // apply every pending accept to the stored state
+    int tensor(int layer, int kind, void** ptr, size_t* bytes) const;
+    int gdn_state(int slot, int gdn_layer, float** ptr, size_t* bytes);
+    int spec_begin(int slot, int id_last, int pos, const float* h_pending_dev);
+    int spec_round(int slot, int n_draft, const int* subst_host, int* out_tokens, int* out_count);
+    const hp_model_cfg& cfg() const { return c_; }
+    float* logits() const { return logits_; } float* h_nextn() const { return h_; }
+    float* mtp_logits() const { return mlogits_; } float* mtp_h() const { return mh_; }
+    size_t weight_bytes() const { return weight_bytes_; } float last_ms() const { return last_ms_; }
+    size_t pass_weight_bytes(bool mtp, bool with_head) const;
+private:
+    struct Desc;   // device-visible pass descriptor (see engine.cu)
+    int alloc(void** p, size_t bytes);
+    int gen_lin(Lin& l, int N, int K, uint64_t tid);
+    int gen_bf16(uint16_t** p, size_t n, uint64_t tid, float mean, float std);
+    int gen_f32(float** p, size_t n, uint64_t tid, float mean, float std, bool neg_abs);
+    int lin(const Lin& l, float* out, int ld, int R);        // GEMV; P > 1 planes are reduced into out
+    int lin_parts(const Lin& l, int R);                      // GEMV into the plane buffer yparts_ (consumer adds the planes)
+    int norm_in(const Lin* prev, bool have_y, const uint16_t* w, float* xn, int R);
+    int attn_block(const LayerW& L, uint16_t* kc, uint16_t* vc, size_t kv_stride, int R, int ngroups);
+    int ffn_block(const LayerW& L, int R);
+    int run_pass(int R, int nseq, int ngroups);              // trunk over the rows described by desc_ (already uploaded)
+    int run_mtp(int R, int ngroups, const float* h_dev, int ldh, bool want_logits);
+    int upload_desc();
+    int enqueue_round(int slot, int n);
+    int nattn() const; int ngdn() const;
+    hp_model_cfg c_;
+    std::vector<LayerW> layers_; LayerW mtp_;
+    uint16_t *embed_ = nullptr, *output_norm_ = nullptr, *mtp_enorm_ = nullptr, *mtp_hnorm_ = nullptr, *mtp_head_norm_ = nullptr;
+    Lin lm_head_, eh_proj_;
+    float* rope_ = nullptr;
+    // state
+    float *gdn_state_ = nullptr, *conv_state_ = nullptr; size_t st_stride_ = 0, cs_stride_ = 0, st_layer_ = 0, cs_layer_ = 0;
+    uint16_t *kc_ = nullptr, *vc_ = nullptr, *mkc_ = nullptr, *mvc_ = nullptr; size_t kv_slot_ = 0, kv_layer_ = 0;
+    float* saved_ = nullptr; size_t sv_layer_ = 0, sv_stride_ = 0; int ld_in_ = 0;   // raw GDN inputs of the last pass (for the deferred commit)
+    int* replay_n_ = nullptr; std::vector<int> pend_, last_r0_, last_T_;
+    // work
+    float *x_ = nullptr, *xn_ = nullptr, *big_ = nullptr, *act_ = nullptr, *yparts_ = nullptr, *logits_ = nullptr, *mlogits_ = nullptr, *h_ = nullptr, *mh_ = nullptr, *cat_ = nullptr, *emb_ = nullptr;
+    float *pO_ = nullptr, *pm_ = nullptr, *pl_ = nullptr; int nsplit_max_ = 0;
+    XQ8F xq_{nullptr, nullptr};
+    int *d_desc_ = nullptr, *h_desc_ = nullptr;                  // device / pinned host descriptor
+    int *d_ids_ = nullptr, *d_mids_ = nullptr; float *d_vals_ = nullptr, *d_mvals_ = nullptr; void* am_scratch_ = nullptr;
+    int *d_spec_ = nullptr, *h_spec_ = nullptr;                   // fused round state (device) / results (pinned host)
+    float* hpend_ = nullptr; int spec_pos_ = 0, spec_slot_ = -1;
+    cudaGraphExec_t graphs_[64] = {}; bool warmed_[64] = {};
+    int* err_ = nullptr;
+    cudaStream_t s_ = nullptr; cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
+    std::vector<void*> allocs_;
+    size_t weight_bytes_ = 0; float last_ms_ = 0;
+    int last_rows_ = 0;
+};
+
+}  // namespace hp

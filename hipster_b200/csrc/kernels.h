@@ -60,6 +60,40 @@ int quantize_x_q8(const float* x, int ldx, XQ8F out, int R, int K, cudaStream_t 
 int xq8_unpack(XQ8F in, int R, int K, int8_t* q, float* d, float* sm, cudaStream_t s);
 int dequant_q4k(const void* W, size_t nblk, float* out, cudaStream_t s);
 
+// ---- ops.cu ----
+int embed_bf16(const int* tok, const void* table_bf16, float* out, int R, int E, int V, cudaStream_t s);
+// x += sum_p y_p (nullable y); xn = rmsnorm(x) * w; xq = q8(xn)   (reference add_rmsnorm_quant, ops.h:14)
+int add_rmsnorm_quant(float* x, const float* y, int P, size_t part_stride, int ldy, const void* w_bf16, float* xn, XQ8F xq, int R, int n, float eps, cudaStream_t s);
+// out[r] = [rmsnorm(a[r]) * wa | rmsnorm(b[r]) * wb] quantised   (reference norm2_concat_quant, ops.h:16)
+int norm2_concat_quant(const float* a, const void* wa, const float* b, int ldb, const void* wb, float* out, XQ8F xq, int R, int n, float eps, cudaStream_t s);
+// xq = q8(silu(gu[:, :F]) * gu[:, F:2F])   (reference silu_mul_quant, ops.h:25)
+int silu_mul_quant(const float* gu, int ldg, int F, XQ8F xq, int R, cudaStream_t s);
+// Gated DeltaNet conv + recurrent step with deferred commit (reference gdn_conv + gdn_step, ops.h:41-51, and the
+// replay of Qwen35::accept, qwen35.cpp:383-403)
+struct GdnParams {
+    const float* rows; float* saved; size_t saved_stride; int ld, off_z, off_b, off_a, n_qk, n_v;
+    const float* conv_w; const void* dt_bias; const void* a_neg; const void* norm_w;
+    float* state; float* conv_state; size_t state_stride, conv_stride;
+    const int* seq; const int* replay_n;
+    float* out; XQ8F xq; float* snap; size_t snap_row_stride; float eps; int sigmoid_gate;
+};
+int gdn_forward(const GdnParams& p, int nseq, cudaStream_t s);
+
+// ---- attn.cu ----
+constexpr int ATTN_SPLIT = 128, ATTN_MAX_PAIRS = 48;   // keys per split; (row, q-head) pairs per kv head and row group
+struct AttnParams {
+    float* qkv; int ld, n_head, n_kv, n_rot;            // rows [q_full n_head x 512 | k n_kv x 256 | v n_kv x 256]
+    const void* q_norm; const void* k_norm; const void* rope;   // bf16 [256] x 2; float2 (cos, sin) [max_ctx][n_rot/2]
+    const int* row_pos; const int* row_slot; const int* row_group; const int* groups;   // device descriptors; group = {r0, T, slot, pos0}
+    void* kc; void* vc; size_t kv_stride; int max_ctx;   // f16 [slot][n_kv][max_ctx][256] for this layer
+    float* pO; float* pm; float* pl; int nsplit_max;     // split partials
+    float* out; XQ8F xq; float eps;
+};
+size_t attn_smem_bytes();
+size_t attn_partial_floats(int ngroups, int n_kv, int nsplit_max);
+int attn_rope_kv(const AttnParams& p, int rows, cudaStream_t s);          // reference k_qk_norm_rope_kv (ops.hip:363-411)
+int attn_decode(const AttnParams& p, int rows, int ngroups, cudaStream_t s);   // reference attn_decode_mq (ops.h:72)
+
 // ---- argmax.cu ----
 // per-row argmax (max value, lowest index) of logits [R][ld] -> ids/vals on device
 int argmax_rows(const float* logits, int R, int n, int ld, int* ids, float* vals, void* scratch, cudaStream_t s);

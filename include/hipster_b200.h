@@ -70,6 +70,67 @@ int hp_argmax_noalloc_max_n(void);
  * ids_dev holds n_draft+1 target argmaxes. Replaces the host loop of engine/bench/spec27b.cpp:92-97. */
 int hp_accept_greedy(const int* ids_dev, const int* drafts_dev, int n_draft, int* out_dev, void* stream);
 
+/* ------------------------------------------------------------------ engine level (engine/src/qwen35.h, qwen4exp.h) */
+
+/* Shapes of the hybrid Gated-DeltaNet / attention model. The reference fixes them at compile time (struct Qwen35Dims,
+ * qwen35.h:15-26; struct FnDims, qwen4exp.h:18-28); here they are run-time so that reduced-depth models can be checked
+ * against the CPU oracle. head_dim is 256 and gdn_dim 128 (as in both reference models); conv kernel 4. */
+typedef struct hp_model_cfg {
+    int n_embd, n_layer, n_ff, n_vocab;
+    int n_head, n_head_kv, n_rot;
+    int gdn_qk_heads, gdn_v_heads;
+    int attn_every;              /* layer il is full attention when (il + 1) % attn_every == 0 (qwen35.h:25) */
+    int max_ctx, n_slots;
+    int n_expert, n_expert_used, expert_ff;   /* n_expert = 0: dense SwiGLU FFN; else routed experts + 1 shared expert */
+    int gdn_sigmoid_gate;        /* GDN output gate: 0 = silu(z) (27B), 1 = sigmoid(z) (Flash-Next) */
+    int has_mtp;
+    float rms_eps, rope_base;
+    unsigned long long seed;     /* weights are random-init, generated on the device from this seed */
+} hp_model_cfg;
+/* One sequence's contribution to a pass: T tokens continuing that slot's sequence at positions pos..pos+T-1
+ * (struct SlotReq, engine/kernels/ops.h:40). tokens is a host pointer borrowed for the call. */
+typedef struct hp_slot_req { int slot; const int* tokens; int T; int pos; } hp_slot_req;
+typedef struct hp_engine hp_engine;
+
+/* preset: "qwen35-27b" (BASELINE config 3), "flash-next" (config 4), "tiny" / "tiny-moe" (reduced models for parity tests) */
+int hp_model_preset(const char* preset, hp_model_cfg* out);
+/* Replaces Qwen35::Qwen35(path, max_ctx, n_slots) (qwen35.h:53): no checkpoint is read, weights are generated. */
+int hp_load(const hp_model_cfg* cfg, hp_engine** out);
+int hp_free(hp_engine* e);
+int hp_n_slots(const hp_engine* e);                        /* qwen35.h:67 */
+size_t hp_weight_bytes(const hp_engine* e);                /* qwen35.h:91 */
+float hp_last_ms(const hp_engine* e);                      /* qwen35.h:93 */
+int hp_reset(hp_engine* e);                                /* qwen35.h:88 */
+int hp_reset_slot(hp_engine* e, int slot);                 /* qwen35.h:89 */
+/* A pass over S slots, rows = sum of T <= 32 (8 per slot): logits [rows][n_vocab] and h_nextn [rows][n_embd] stay on the
+ * device. Replaces Qwen35::forward(const SlotReq*, int) (qwen35.h:57-62); *ms_out (nullable) = GPU milliseconds. */
+int hp_forward(hp_engine* e, const hp_slot_req* reqs, int S, float* ms_out);
+/* Commit the first m (1..T) rows of that slot in the last pass; the recurrent state is rolled back to that prefix.
+ * Replaces Qwen35::accept (qwen35.h:63-66, qwen35.cpp:383-403). */
+int hp_accept(hp_engine* e, int slot, int m);
+/* MTP draft block over T (token, h) pairs at positions pos0.. of `slot`; h_dev [T][n_embd] device rows (may alias
+ * hp_h_nextn_dev / hp_mtp_h_dev). Replaces Qwen35::mtp_forward (qwen35.h:68-70, qwen35.cpp:405-424). */
+int hp_mtp_forward(hp_engine* e, int slot, const int* tokens_host, const float* h_dev, int T, int pos0);
+/* Argmax of the first T rows of the target (which = 0) or MTP (which = 1) logits -> host arrays.
+ * Replaces Qwen35::topk with k = 1 (qwen35.h:87, qwen35.cpp:426-430). */
+int hp_topk(hp_engine* e, int which, int T, int* ids_host, float* vals_host);
+const float* hp_logits_dev(const hp_engine* e);            /* qwen35.h:82 */
+const float* hp_h_nextn_dev(const hp_engine* e);           /* qwen35.h:83 */
+const float* hp_mtp_logits_dev(const hp_engine* e);        /* qwen35.h:84 */
+const float* hp_mtp_h_dev(const hp_engine* e);             /* qwen35.h:85 */
+/* Test/diagnostic access: device pointer and size of a generated tensor (layer = -1 for model-level tensors) and of a
+ * slot's committed GDN state [gdn_v_heads][128][128] (pending accepts are applied first). */
+int hp_tensor_dev(const hp_engine* e, int layer, int kind, void** ptr_out, size_t* bytes_out);
+int hp_gdn_state_dev(hp_engine* e, int slot, int gdn_layer, float** ptr_out, size_t* bytes_out);
+/* The whole MTP round on the device: n_draft draft steps, one verify pass of n_draft+1 rows, argmax, greedy acceptance,
+ * commit and MTP catch-up, with no logits or ids crossing to the host; only the emitted tokens come back.
+ * hp_spec_begin seeds it with the last emitted token, its position and the pending hidden row (device pointer, n_embd).
+ * subst_host (nullable, n_draft ints): >= 0 replaces that draft (seeded acceptance control), -1 keeps the MTP's argmax.
+ * out_tokens_host receives the accepted drafts followed by the bonus token; *out_count = their number (mm + 1).
+ * Replaces the host loop of engine/bench/spec27b.cpp:77-103. */
+int hp_spec_begin(hp_engine* e, int slot, int id_last, int pos, const float* h_pending_dev);
+int hp_spec_round(hp_engine* e, int slot, int n_draft, const int* subst_host, int* out_tokens_host, int* out_count);
+
 #ifdef __cplusplus
 }
 #endif

@@ -97,3 +97,77 @@ def accept(ids, drafts):
     bonus = ctypes.c_int(0)
     mm = lib().orc_accept(P(ids), P(drafts), int(drafts.size), ctypes.byref(bonus))
     return mm, bonus.value
+
+
+# ---------------------------------------------------------------- engine oracle (hp_oracle_model.cpp)
+class OrcCfg(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int) for n in ("n_embd", "n_layer", "n_ff", "n_vocab", "n_head", "n_head_kv", "n_rot", "gdn_qk_heads", "gdn_v_heads",
+                                             "attn_every", "max_ctx", "n_slots", "n_expert", "n_expert_used", "expert_ff", "gdn_sigmoid_gate", "has_mtp")] + \
+               [("rms_eps", ctypes.c_float), ("rope_base", ctypes.c_float), ("seed", ctypes.c_ulonglong)]
+
+
+class Model:
+    """CPU restatement of the reference engine (engine/src/qwen35.cpp) on the same seeded weights."""
+
+    def __init__(self, cfg):
+        L = lib()
+        L.orc_model_create.restype = ctypes.c_void_p
+        for n in ("orc_model_logits", "orc_model_h", "orc_model_mtp_logits", "orc_model_mtp_h", "orc_model_gdn_state"):
+            getattr(L, n).restype = ctypes.POINTER(ctypes.c_float)
+        L.orc_model_tensor.restype = ctypes.c_size_t
+        c = OrcCfg()
+        for f, _ in OrcCfg._fields_:
+            setattr(c, f, getattr(cfg, f))
+        self.c = c
+        self.h = ctypes.c_void_p(L.orc_model_create(ctypes.byref(c)))
+        assert self.h
+
+    def __del__(self):
+        try:
+            lib().orc_model_free(self.h)
+        except Exception:
+            pass
+
+    def reset(self):
+        lib().orc_model_reset(self.h)
+
+    def reset_slot(self, s):
+        lib().orc_model_reset_slot(self.h, s)
+
+    def forward(self, reqs):
+        S = len(reqs)
+        slots = (ctypes.c_int * S)(*[r[0] for r in reqs]); Ts = (ctypes.c_int * S)(*[len(r[1]) for r in reqs]); poss = (ctypes.c_int * S)(*[r[2] for r in reqs])
+        bufs = [(ctypes.c_int * len(r[1]))(*[int(x) for x in r[1]]) for r in reqs]
+        toks = (ctypes.POINTER(ctypes.c_int) * S)(*[ctypes.cast(b, ctypes.POINTER(ctypes.c_int)) for b in bufs])
+        lib().orc_model_forward(self.h, slots, toks, Ts, poss, S)
+
+    def accept(self, slot, m):
+        assert lib().orc_model_accept(self.h, slot, m) == 0
+
+    def mtp_forward(self, slot, tokens, h_in, pos0):
+        t = (ctypes.c_int * len(tokens))(*[int(x) for x in tokens])
+        h_in = np.ascontiguousarray(h_in, dtype=np.float32)
+        lib().orc_model_mtp_forward(self.h, slot, t, P(h_in), len(tokens), pos0)
+
+    def _arr(self, fn, n, *a):
+        return np.ctypeslib.as_array(getattr(lib(), fn)(self.h, *a), shape=(n,)).copy()
+
+    def logits(self, T):
+        return self._arr("orc_model_logits", T * self.c.n_vocab).reshape(T, -1)
+
+    def h_nextn(self, T):
+        return self._arr("orc_model_h", T * self.c.n_embd).reshape(T, -1)
+
+    def mtp_logits(self, T):
+        return self._arr("orc_model_mtp_logits", T * self.c.n_vocab).reshape(T, -1)
+
+    def mtp_h(self, T):
+        return self._arr("orc_model_mtp_h", T * self.c.n_embd).reshape(T, -1)
+
+    def gdn_state(self, slot, gdn_layer):
+        return self._arr("orc_model_gdn_state", self.c.gdn_v_heads * 128 * 128, slot, gdn_layer)
+
+    def tensor(self, layer, kind_id):
+        p = ctypes.c_void_p()
+        n = lib().orc_model_tensor(self.h, layer, kind_id, ctypes.byref(p))
+        return np.ctypeslib.as_array(ctypes.cast(p, ctypes.POINTER(ctypes.c_uint8)), shape=(n,)).copy()
