@@ -1,11 +1,14 @@
 """Benchmark of the MTP speculative-decode hot path on B200.
 
-python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload dense27b|gemv]
 
-Prints ONE JSON line (rank 0). Workloads:
+Prints ONE JSON line (rank 0). A "step" is one MTP round (n draft steps, one verify pass of n+1 rows, device argmax +
+greedy acceptance, commit, MTP catch-up) over seeded synthetic input. Workloads:
+  dense27b  BASELINE config 3: Qwen3.8-27B-shaped dense hybrid, random-init Q4_K, 4096-token seeded prompt, MTP n=5,
+            seeded acceptance 0.7 (default; the metric is quoted on this configuration and it fits one GPU)
   gemv      BASELINE config 1: Q4_K 17408 x 5120 verify GEMV over 3 rows + argmax + greedy acceptance
-A "step" is one pass of the hot path over one batch of seeded synthetic input. Inputs larger than L2: the
-weight matrix is rotated through enough device copies (> 512 MB) that no step finds its weights in the 126 MB L2.
+L2: every step streams 20 GB of weights, far beyond the 126 MB L2 (dense27b); the gemv workload rotates weight copies.
+N > 1 runs N independent replicas of the dense path (the dense trunk does not shard: "replicas only").
 """
 import argparse
 import json
@@ -20,7 +23,9 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+METRIC = "MTP-spec decode tokens/s (Q4_K); verify-GEMV HBM GB/s vs B200 peak"
 PEAKS_FALLBACK = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+N_DRAFT, ACCEPT_RATE, PROMPT_LEN = 5, 0.7, 4096
 
 
 def peaks():
@@ -36,7 +41,6 @@ class ClockSampler:
 
     def __init__(self, gpu_index):
         self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
-        self.p = None
         try:
             self.p = subprocess.Popen(["nvidia-smi", f"--id={gpu_index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200"], stdout=self.f, stderr=subprocess.DEVNULL)
         except Exception:
@@ -80,36 +84,191 @@ def dist_env():
     return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
 
 
-# --------------------------------------------------------------------------------------------- workload: gemv
+def expected_tokens_per_round(n, p):
+    return 1.0 + sum(p ** k for k in range(1, n + 1))
+
+
+# ------------------------------------------------------------------------------------------ CPU arm (oracle port)
+def cpu_round_sample(rounds, warm):
+    """The CPU restatement of the reference engine on the host cores, on a BOUNDED sample of the dense27b workload:
+    a 27B-shaped model cut to 4 layers (3 GDN + 1 attention, full widths, full 248320 vocabulary, MTP block), short
+    context. One step = one MTP round (5 draft steps + 6-row verify + accept + catch-up)."""
+    import hipster_b200 as hb
+    from oracle import orc
+    cfg = hb.ModelCfg.preset("qwen35-27b", n_layer=4, max_ctx=256)
+    m = orc.Model(cfg)
+    E = cfg.n_embd
+    m.forward([(0, [11, 12, 13, 14], 0)]); m.accept(0, 4)
+    id_last, pos = 15, 4
+    h_pending = m.h_nextn(4)[3].copy()
+
+    def one_round():
+        nonlocal id_last, pos, h_pending
+        tok, h = id_last, h_pending[None, :]
+        drafts = []
+        for i in range(N_DRAFT):
+            m.mtp_forward(0, [tok], h, pos + i)
+            tok = int(orc.argmax(m.mtp_logits(1))[0][0]); drafts.append(tok); h = m.mtp_h(1)
+        m.forward([(0, [id_last] + drafts, pos)])
+        ids = orc.argmax(m.logits(N_DRAFT + 1))[0]
+        mm = 2                                       # fixed acceptance for the timing sample
+        m.accept(0, mm + 1)
+        m.mtp_forward(0, drafts[:mm], m.h_nextn(mm), pos + 1)
+        h_pending = m.h_nextn(mm + 1)[mm].copy()
+        id_last = int(ids[mm]); pos += mm + 1
+    for _ in range(warm):
+        one_round()
+    t0 = time.perf_counter()
+    for _ in range(rounds):
+        one_round()
+    dt = (time.perf_counter() - t0) / rounds
+    return dt, orc.lib().orc_num_threads()
+
+
+CPU_SAMPLE = ("CPU restatement of the reference engine (its HIP kernels cannot be built without ROCm), one MTP round n=5 on a 27B-shaped "
+              "model cut to 4 of 64 layers (3 GDN + 1 attention, full widths, full vocabulary, MTP block), context < 64; tokens/s = 2.941 expected "
+              "tokens per round / measured round time of THIS reduced model (the full trunk has 16x the layer work)")
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return None
+    k = max(1, min(args.steps, 5)); w = 1
+    dt, th = cpu_round_sample(k, w)
+    v = expected_tokens_per_round(N_DRAFT, ACCEPT_RATE) / dt
+    return {"impl": "reference", "metric": METRIC, "value": v, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u4 x i8 -> i32, f32 epilogue/state", "data": "synthetic",
+            "config": dense_config(world),
+            "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": th, "kind": "port", "sample": CPU_SAMPLE + f"; {k} timed rounds"},
+            "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+
+
+def dense_config(world):
+    return {"workload": "config3: Qwen3.8-27B-shaped dense hybrid (64 layers, hidden 5120, FFN 17408, vocab 248320), random-init Q4_K, "
+                        "batch 1, 4096-token seeded prompt, MTP n=5, seeded acceptance 0.7",
+            "l2": "inputs larger than L2: 20 GB of weights streamed per step", "parallelism": f"replicas x{world}"}
+
+
+# ------------------------------------------------------------------------------------------ dense27b
+def run_dense(args, rank, local_rank, world):
+    import torch
+    import torch.distributed as dist
+    import hipster_b200 as hb
+    from hipster_b200 import spec
+    from hipster_b200.engine import _as_tensor
+    torch.cuda.set_device(local_rank)
+    n, rate = N_DRAFT, ACCEPT_RATE
+    total_rounds = args.warmup + args.steps
+    n_plain = total_rounds * (n + 1) + n + 2
+    cfg = hb.ModelCfg.preset(args.preset)
+    prompt_len = min(args.prompt_len, cfg.max_ctx // 2)
+    assert prompt_len + n_plain + 2 * n + 4 <= cfg.max_ctx, "too many steps for the context window"
+    eng = hb.Engine(cfg)
+    E = cfg.n_embd
+    rng = np.random.default_rng(1234 + rank)
+    prompt = [int(x) for x in rng.integers(0, cfg.n_vocab, size=prompt_len)]
+    hview = _as_tensor(eng.h_nextn_ptr(), 32 * E * 4).view(torch.float32).view(32, E)
+    hbuf = torch.zeros((8, E), dtype=torch.float32, device="cuda")
+
+    def h_shift(prev, T):
+        torch.cuda.synchronize()
+        hbuf[0] = prev if prev is not None else 0
+        if T > 1:
+            hbuf[1:T] = hview[0:T - 1]
+        last = hview[T - 1].clone()
+        torch.cuda.synchronize()
+        return hbuf.data_ptr(), last
+
+    class A:
+        forward = staticmethod(eng.forward); accept = staticmethod(eng.accept); mtp_forward = staticmethod(eng.mtp_forward)
+
+    t_setup = time.perf_counter()
+    # 1. plain greedy stream (engine/bench/spec27b.cpp:34-40): the source of the seeded substitutions and the check
+    pos = spec.prefill(A, prompt, h_shift=h_shift, with_mtp=False)
+    T_last = prompt_len % 8 or 8
+    plain = [int(eng.topk(0, T_last)[0][T_last - 1])]
+    for i in range(n_plain):
+        eng.forward([(0, [plain[-1]], pos + i)]); eng.accept(0, 1)
+        plain.append(int(eng.topk(0, 1)[0][0]))
+    # 2. speculative run from the same prefix
+    eng.reset()
+    pos = spec.prefill(A, prompt, h_shift=h_shift, with_mtp=True)
+    id_last = int(eng.topk(0, T_last)[0][T_last - 1])
+    assert id_last == plain[0]
+    eng.spec_begin(0, id_last, pos, eng.h_nextn_ptr() + (T_last - 1) * E * 4)
+    out = [id_last]
+    srng = np.random.default_rng(99 + rank)
+    t_setup = time.perf_counter() - t_setup
+
+    def one_round():
+        sub = spec.seeded_substitutions(plain, len(out), n, rate, srng, cfg.n_vocab)
+        got = eng.spec_round(0, n, sub)
+        out.extend(got)
+        return len(got), eng.last_ms()
+
+    for _ in range(args.warmup):
+        one_round()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    toks = 0; dev_ms = 0.0
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        c, ms = one_round(); toks += c; dev_ms += ms
+    torch.cuda.synchronize()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    clocks = sampler.stop() if sampler else None
+    exact = out[:len(plain)] == plain[:len(out)]
+    # dominant kernel alone: the GEMV launches of one 6-row verify pass, CUDA events on the engine's stream
+    gemv_ms = eng.profile_pass(n + 1, 1, 5)
+    pass_ms = eng.profile_pass(n + 1, 0, 5)
+    verify_bytes = eng.pass_weight_bytes(False, True)
+    mtp_bytes = eng.pass_weight_bytes(True, False)
+    head_bytes = verify_bytes - eng.pass_weight_bytes(False, False)
+    round_bytes = verify_bytes + n * (mtp_bytes + head_bytes) + mtp_bytes
+    if world > 1:
+        t = torch.tensor([dev_ms, wall_ms], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX); dev_ms, wall_ms = float(t[0]), float(t[1])
+        tt = torch.tensor([toks], device="cuda", dtype=torch.float64); dist.all_reduce(tt); toks = float(tt.item())
+        dist.barrier()
+    eng.close()
+    if rank != 0:
+        return None
+    pk = peaks()
+    achieved = verify_bytes / (gemv_ms / 1e3) / 1e9
+    tok_per_round = toks / (args.steps * world)
+    bytes_per_token = round_bytes / tok_per_round
+    value = toks / (dev_ms / 1e3)
+    line = {
+        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "u4 x i8 -> i32, f32 epilogue/state", "data": "synthetic",
+        "config": dense_config(world),
+        "e2e": {"value": toks / (wall_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 4 * n, "d2h_bytes_per_step": 256,
+                "note": "hp_spec_round with host token buffers; wall clock over the timed rounds, one stream synchronise per round"},
+        "gpu_launches": args.steps * world * (570 + n * 21 + 20),
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"], "traffic": None,
+                     "kernel": "k_gemv_q4k_sk: all GEMV launches of one 6-row verify pass (129 launches + LM head), timed alone with CUDA events",
+                     "algorithmic_bytes": verify_bytes, "ms": gemv_ms, "full_pass_ms": pass_ms, "peak_source": pk["_src"],
+                     "bytes_per_token_roofline": {"round_bytes": round_bytes, "tokens_per_round": tok_per_round, "bytes_per_token": bytes_per_token,
+                                                  "roofline_tokens_per_s": pk["hbm_gbs"] * 1e9 / bytes_per_token, "frac_of_roofline": value / (pk["hbm_gbs"] * 1e9 / bytes_per_token)}},
+        "clocks": clocks,
+        "checks": {"spec_stream_equals_plain_greedy": bool(exact), "tokens": int(toks), "accepted_drafts_per_round": tok_per_round - 1, "prompt_len": prompt_len, "setup_s": t_setup},
+    }
+    if world == 1 and not args.no_cpu:
+        dt, th = cpu_round_sample(3, 1)
+        line["cpu_baseline"] = {"value": expected_tokens_per_round(n, rate) / dt, "unit": "tokens/s", "cores": th, "kind": "port", "sample": CPU_SAMPLE + "; 3 timed rounds"}
+    return line
+
+
+# ------------------------------------------------------------------------------------------ gemv (config 1)
 GEMV_N, GEMV_K, GEMV_R = 17408, 5120, 3
 GEMV_BYTES = GEMV_N * (GEMV_K // 256) * 144 + GEMV_R * GEMV_K * 4 + GEMV_R * GEMV_N * 4   # 50,405,376 algorithmic bytes
 
 
-def gemv_cpu(steps, warmup, threads_note=True):
-    """The CPU oracle's restatement of the same step (quantise -> W4A8 GEMV -> argmax -> accept) on the host cores."""
-    from oracle import orc
-    from hipster_b200 import synth
-    W = synth.q4k_matrix(GEMV_N, GEMV_K, seed=0); x = synth.activations(GEMV_R, GEMV_K, seed=0)
-    drafts = np.array([1, 2], dtype=np.int32)
-
-    def step():
-        q, d, s = orc.quantize_x_q8(x)
-        y = orc.gemv_q4k_q8(W, q, d, s, GEMV_N, GEMV_K)
-        ids, _ = orc.argmax(y)
-        return orc.accept(ids, drafts)
-    for _ in range(warmup):
-        step()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        step()
-    dt = (time.perf_counter() - t0) / steps
-    return dt, orc.lib().orc_num_threads()
-
-
 def run_gemv(args, rank, local_rank, world):
     import torch
-    import torch.distributed as dist
-    from hipster_b200 import kernels as K_, synth, lib, check, ptr
+    from hipster_b200 import kernels as K_, synth
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     W_h = synth.q4k_matrix(GEMV_N, GEMV_K, seed=0)
@@ -134,32 +293,25 @@ def run_gemv(args, rank, local_rank, world):
         K_.quantize_x_q8(xd, xq)
         K_.gemv_q4k_q8(Ws[it[0] % ncopy], xq, GEMV_N, GEMV_K, y); it[0] += 1
         ids, _ = K_.argmax(y)
-        out = K_.accept_greedy(ids, dd)
-        out_h.copy_(out, non_blocking=True)
+        out_h.copy_(K_.accept_greedy(ids, dd), non_blocking=True)
         torch.cuda.current_stream().synchronize()
-        return out_h
 
     def timed(fn, steps, warmup):
         for _ in range(warmup):
             fn()
-        if world > 1:
-            dist.barrier()
         torch.cuda.synchronize()
         e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(steps):
             fn()
         e1.record(); torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            t = torch.tensor([ms], device=dev); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms = float(t.item()); dist.barrier()
-        return ms
+        return e0.elapsed_time(e1)
 
     sampler = ClockSampler(local_rank) if rank == 0 else None
     ms = timed(step_resident, args.steps, args.warmup)
     ms_e2e = timed(step_e2e, args.steps, args.warmup)
-    # dominant kernel alone, CUDA events on the launching stream, weights rotated past L2
     K_.quantize_x_q8(x_d, xq)
+
     def gemv_only():
         K_.gemv_q4k_q8(Ws[it[0] % ncopy], xq, GEMV_N, GEMV_K, y); it[0] += 1
     n_k = max(args.steps, 50)
@@ -169,51 +321,28 @@ def run_gemv(args, rank, local_rank, world):
     if rank != 0:
         return None
     pk = peaks()
-    rows_per_s = world * GEMV_R * args.steps / (ms / 1e3)
     achieved = GEMV_BYTES / (ms_k / 1e3) / 1e9
-    line = {
-        "metric": "MTP-spec decode tokens/s (Q4_K); verify-GEMV HBM GB/s vs B200 peak",
-        "value": rows_per_s, "unit": "verify rows/s",
-        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u4 x i8 -> i32, f32 epilogue", "data": "synthetic",
-        "config": {"workload": "config1: Q4_K 17408x5120 verify GEMV, 3 rows, argmax + greedy acceptance",
-                   "l2": f"weights rotated through {ncopy} device copies ({ncopy * W_h.nbytes >> 20} MiB > L2)", "parallelism": f"replicas x{world}"},
-        "e2e": {"value": world * GEMV_R * args.steps / (ms_e2e / 1e3), "unit": "verify rows/s",
-                "h2d_bytes_per_step": int(x_h.numel() * 4 + drafts_h.numel() * 4), "d2h_bytes_per_step": 8},
-        "gpu_launches": 5 * args.steps,
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
-                     "traffic": None, "kernel": "k_gemv_q4k_q8<1>", "us_per_launch": ms_k * 1e3, "peak_source": pk["_src"]},
-        "clocks": clocks,
-    }
-    if world == 1 and not args.no_cpu:
-        dt, th = gemv_cpu(3, 1)
-        line["cpu_baseline"] = {"value": GEMV_R / dt, "unit": "verify rows/s", "cores": th, "kind": "port",
-                                "sample": "full config-1 step (quantise, 17408x5120 W4A8 GEMV over 3 rows, argmax, accept), mean of 3"}
-    return line
-
-
-def run_reference(args, rank, world):
-    if rank != 0:
-        return None
-    dt, th = gemv_cpu(max(1, min(args.steps, 10)), max(1, min(args.warmup, 2)))
-    v = GEMV_R / dt
-    return {"impl": "reference", "metric": "MTP-spec decode tokens/s (Q4_K); verify-GEMV HBM GB/s vs B200 peak", "value": v, "unit": "verify rows/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "u4 x i8 -> i32, f32 epilogue", "data": "synthetic",
-            "config": {"workload": "config1: Q4_K 17408x5120 verify GEMV, 3 rows, argmax + greedy acceptance"},
-            "cpu_baseline": {"value": v, "unit": "verify rows/s", "cores": th, "kind": "port",
-                             "sample": "CPU restatement of the reference's kernels (its HIP kernels cannot be built without ROCm); full config-1 step"},
-            "e2e": {"value": v, "unit": "verify rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    return {"metric": METRIC, "value": world * GEMV_R * args.steps / (ms / 1e3), "unit": "verify rows/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u4 x i8 -> i32, f32 epilogue", "data": "synthetic",
+            "config": {"workload": "config1: Q4_K 17408x5120 verify GEMV, 3 rows, argmax + greedy acceptance",
+                       "l2": f"weights rotated through {ncopy} device copies ({ncopy * W_h.nbytes >> 20} MiB > L2)", "parallelism": f"replicas x{world}"},
+            "e2e": {"value": world * GEMV_R * args.steps / (ms_e2e / 1e3), "unit": "verify rows/s", "h2d_bytes_per_step": int(x_h.numel() * 4 + 8), "d2h_bytes_per_step": 8},
+            "gpu_launches": 6 * args.steps,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"], "traffic": None,
+                         "kernel": "k_gemv_q4k_sk<1,2> (+ plane reduction), launch-bound when driven from Python", "us_per_launch": ms_k * 1e3, "peak_source": pk["_src"]},
+            "clocks": clocks}
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=87)     # ~256 emitted tokens at 2.94 tokens per round
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="gemv")
+    ap.add_argument("--workload", default="dense27b", choices=["dense27b", "gemv"])
+    ap.add_argument("--preset", default="qwen35-27b")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="shorter prompts are for profiling captures only")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank, local_rank, world = dist_env()
@@ -227,7 +356,7 @@ def main():
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    line = run_gemv(args, rank, local_rank, world)
+    line = run_dense(args, rank, local_rank, world) if args.workload == "dense27b" else run_gemv(args, rank, local_rank, world)
     if line:
         print(json.dumps(line), flush=True)
     if world > 1:

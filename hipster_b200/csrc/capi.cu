@@ -120,6 +120,42 @@ int hp_accept_greedy(const int* ids_dev, const int* drafts_dev, int n_draft, int
     HP_GUARD_END
 }
 
+// ------------------------------------------------------------------ layer kernels
+int hp_add_rmsnorm_quant(float* x_dev, const float* y_dev, int n_planes, size_t plane_stride, const void* w_bf16_dev, float* xn_dev, void* xq_q_dev, void* xq_sc_dev, int R, int n, float eps, void* stream) {
+    HP_GUARD_BEGIN
+    HP_REQUIRE(x_dev && w_bf16_dev && xq_q_dev && xq_sc_dev && (y_dev || n_planes == 0), "hp_add_rmsnorm_quant: null pointer");
+    return hp::add_rmsnorm_quant(x_dev, y_dev, n_planes, plane_stride, n, w_bf16_dev, xn_dev, hp::XQ8F{xq_q_dev, xq_sc_dev}, R, n, eps, (cudaStream_t)stream);
+    HP_GUARD_END
+}
+int hp_silu_mul_quant(const float* gate_up_dev, int ld, int F, void* xq_q_dev, void* xq_sc_dev, int R, void* stream) {
+    HP_GUARD_BEGIN
+    HP_REQUIRE(gate_up_dev && xq_q_dev && xq_sc_dev, "hp_silu_mul_quant: null pointer");
+    return hp::silu_mul_quant(gate_up_dev, ld, F, hp::XQ8F{xq_q_dev, xq_sc_dev}, R, (cudaStream_t)stream);
+    HP_GUARD_END
+}
+size_t hp_gdn_conv_state_floats(int n_v) { return (size_t)n_v * 3 * 384; }
+size_t hp_gdn_saved_floats(int n_v) { return (size_t)n_v * 8 * 388; }
+int hp_gdn_layer(const float* rows_dev, int ld, int T, int n_replay, int n_qk, int n_v, const float* conv_w_dev, const void* dt_bias_bf16_dev, const void* a_neg_bf16_dev,
+                 const void* norm_w_bf16_dev, float* state_dev, float* conv_state_dev, float* saved_dev, float* out_dev, void* xq_q_dev, void* xq_sc_dev,
+                 float* snap_dev, float eps, int sigmoid_gate, void* stream) {
+    HP_GUARD_BEGIN
+    HP_REQUIRE(T >= 0 && T <= 8 && n_replay >= 0 && n_replay <= 8 && T + n_replay >= 1, "hp_gdn_layer: 0 <= T, n_replay <= 8 and T + n_replay >= 1");
+    HP_REQUIRE((rows_dev || T == 0) && conv_w_dev && dt_bias_bf16_dev && a_neg_bf16_dev && norm_w_bf16_dev && state_dev && conv_state_dev && saved_dev, "hp_gdn_layer: null pointer");
+    HP_REQUIRE(n_qk >= 1 && n_v >= n_qk && n_v % n_qk == 0 && ld >= (2 * n_qk + 2 * n_v) * 128 + 2 * n_v, "hp_gdn_layer: bad shape");
+    static int* d_desc = nullptr;   // {r0, T, slot, -} + replay count
+    if (!d_desc) HP_CUDA(cudaMalloc(&d_desc, 8 * sizeof(int)));
+    const int h[5] = {0, T, 0, 0, n_replay};
+    HP_CUDA(cudaMemcpyAsync(d_desc, h, sizeof h, cudaMemcpyHostToDevice, (cudaStream_t)stream));
+    HP_CUDA(cudaStreamSynchronize((cudaStream_t)stream));   // h lives on this stack frame
+    hp::GdnParams g; g.rows = rows_dev ? rows_dev : state_dev; g.saved = saved_dev; g.saved_stride = 0; g.ld = ld; g.n_qk = n_qk; g.n_v = n_v;
+    g.off_z = (2 * n_qk + n_v) * 128; g.off_b = g.off_z + n_v * 128; g.off_a = g.off_b + n_v;
+    g.conv_w = conv_w_dev; g.dt_bias = dt_bias_bf16_dev; g.a_neg = a_neg_bf16_dev; g.norm_w = norm_w_bf16_dev;
+    g.state = state_dev; g.conv_state = conv_state_dev; g.state_stride = 0; g.conv_stride = 0; g.seq = d_desc; g.replay_n = d_desc + 4;
+    g.out = out_dev; g.xq = hp::XQ8F{xq_q_dev, xq_sc_dev}; g.snap = snap_dev; g.snap_row_stride = (size_t)n_v * 128 * 128; g.eps = eps; g.sigmoid_gate = sigmoid_gate;
+    return hp::gdn_forward(g, 1, (cudaStream_t)stream);
+    HP_GUARD_END
+}
+
 // ------------------------------------------------------------------ engine
 struct hp_engine { hp::Engine impl; explicit hp_engine(const hp_model_cfg& c) : impl(c) {} };
 
@@ -176,6 +212,8 @@ int hp_tensor_dev(const hp_engine* e, int layer, int kind, void** ptr_out, size_
 int hp_gdn_state_dev(hp_engine* e, int slot, int gdn_layer, float** ptr_out, size_t* bytes_out) {
     HP_GUARD_BEGIN HP_REQUIRE(e && ptr_out && bytes_out, "hp_gdn_state_dev: null pointer"); return e->impl.gdn_state(slot, gdn_layer, ptr_out, bytes_out); HP_GUARD_END
 }
+int hp_profile_pass(hp_engine* e, int R, int what, int reps, float* ms_out) { HP_ENGINE_CALL(e->impl.profile_pass(R, what, reps, ms_out)) }
+size_t hp_pass_weight_bytes(const hp_engine* e, int mtp, int with_head) { return e ? e->impl.pass_weight_bytes(mtp != 0, with_head != 0) : 0; }
 int hp_spec_begin(hp_engine* e, int slot, int id_last, int pos, const float* h_pending_dev) { HP_ENGINE_CALL(e->impl.spec_begin(slot, id_last, pos, h_pending_dev)) }
 int hp_spec_round(hp_engine* e, int slot, int n_draft, const int* subst_host, int* out_tokens_host, int* out_count) {
     HP_ENGINE_CALL(e->impl.spec_round(slot, n_draft, subst_host, out_tokens_host, out_count))

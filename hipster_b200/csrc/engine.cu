@@ -262,16 +262,17 @@ int Engine::reset_slot(int slot) {
 int Engine::upload_desc() { HP_CUDA(cudaMemcpyAsync(d_desc_, h_desc_, D_INTS * 4, cudaMemcpyHostToDevice, s_)); return HP_OK; }
 
 int Engine::lin_parts(const Lin& l, int R) {
-    return gemv_q4k_q8_parts(l.w, xq_, yparts_, l.N, l.K, R, l.N, (size_t)R * l.N, err_, s_, false);
+    return gemv_q4k_q8_parts(l.w, xq_, yparts_, l.N, l.K, R, l.N, (size_t)R * l.N, err_, s_, pdl_);
 }
 int Engine::lin(const Lin& l, float* out, int ld, int R) {
-    if (l.P == 1) return gemv_q4k_q8_parts(l.w, xq_, out, l.N, l.K, R, ld, 0, err_, s_, false);
+    if (l.P == 1) return gemv_q4k_q8_parts(l.w, xq_, out, l.N, l.K, R, ld, 0, err_, s_, pdl_);
     HP_TRY(lin_parts(l, R));
     k_reduce_planes<<<dim3((l.N + 255) / 256, R), 256, 0, s_>>>(yparts_, (size_t)R * l.N, l.P, out, l.N, ld);
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 // residual add of the previous projection's planes + RMSNorm + quantise (qwen35.cpp:311-315)
 int Engine::norm_in(const Lin* prev, bool have_y, const uint16_t* w, float* xn, int R) {
+    if (gemv_only_) return HP_OK;
     return add_rmsnorm_quant(x_, have_y ? yparts_ : nullptr, have_y ? prev->P : 0, have_y ? (size_t)R * prev->N : 0, have_y ? prev->N : 0, w, xn, xq_, R, c_.n_embd, c_.rms_eps, s_);
 }
 // qwen35.cpp:247-276
@@ -282,22 +283,21 @@ int Engine::attn_block(const LayerW& L, uint16_t* kc, uint16_t* vc, size_t kv_st
     p.q_norm = L.q_norm; p.k_norm = L.k_norm; p.rope = rope_; p.row_pos = d_desc_ + D_POS; p.row_slot = d_desc_ + D_SLOT; p.row_group = d_desc_ + D_RGROUP; p.groups = d_desc_ + D_GROUPS;
     p.kc = kc; p.vc = vc; p.kv_stride = kv_stride; p.max_ctx = c_.max_ctx; p.pO = pO_; p.pm = pm_; p.pl = pl_; p.nsplit_max = nsplit_max_;
     p.out = nullptr; p.xq = xq_; p.eps = c_.rms_eps;
-    HP_TRY(attn_rope_kv(p, R, s_));
-    HP_TRY(attn_decode(p, R, ngroups, s_));
+    if (!gemv_only_) { HP_TRY(attn_rope_kv(p, R, s_)); HP_TRY(attn_decode(p, R, ngroups, s_)); }
     return lin_parts(L.out_proj, R);
 }
 // qwen35.cpp:278-287
 int Engine::ffn_block(const LayerW& L, int R) {
     const int F = c_.n_ff;
     HP_TRY(lin(L.gate_up, big_, 2 * F, R));
-    HP_TRY(silu_mul_quant(big_, 2 * F, F, xq_, R, s_));
+    if (!gemv_only_) HP_TRY(silu_mul_quant(big_, 2 * F, F, xq_, R, s_));
     return lin_parts(L.down, R);
 }
 
 // qwen35.cpp:309-376
 int Engine::run_pass(int R, int nseq, int ngroups) {
     const hp_model_cfg& c = c_;
-    HP_TRY(embed_bf16(d_desc_ + D_TOK, embed_, x_, R, c.n_embd, c.n_vocab, s_));
+    if (!gemv_only_) HP_TRY(embed_bf16(d_desc_ + D_TOK, embed_, x_, R, c.n_embd, c.n_vocab, s_));
     const Lin* prev = nullptr; int gi = 0, ai = 0;
     for (int il = 0; il < c.n_layer; ++il) {
         const LayerW& L = layers_[il];
@@ -310,7 +310,7 @@ int Engine::run_pass(int R, int nseq, int ngroups) {
             g.conv_w = L.conv_w; g.dt_bias = L.dt_bias; g.a_neg = L.a_neg; g.norm_w = L.ssm_norm;
             g.state = gdn_state_ + (size_t)gi * st_layer_; g.conv_state = conv_state_ + (size_t)gi * cs_layer_; g.state_stride = st_stride_; g.conv_stride = cs_stride_;
             g.seq = d_desc_ + D_SEQS; g.replay_n = replay_n_; g.out = nullptr; g.xq = xq_; g.snap = nullptr; g.snap_row_stride = 0; g.eps = c.rms_eps; g.sigmoid_gate = c.gdn_sigmoid_gate;
-            HP_TRY(gdn_forward(g, nseq, s_));
+            if (!gemv_only_) HP_TRY(gdn_forward(g, nseq, s_));
             HP_TRY(lin_parts(L.out_proj, R));
             ++gi;
         } else {
@@ -323,6 +323,7 @@ int Engine::run_pass(int R, int nseq, int ngroups) {
     }
     HP_TRY(norm_in(prev, true, output_norm_, h_, R));      // h for all rows (+ q8 of all rows), qwen35.cpp:370
     HP_TRY(lin(lm_head_, logits_, c.n_vocab, R));
+    if (gemv_only_) return HP_OK;
     return argmax_rows(logits_, R, c.n_vocab, c.n_vocab, d_ids_, d_vals_, am_scratch_, s_);
 }
 
@@ -481,6 +482,27 @@ size_t Engine::pass_weight_bytes(bool mtp, bool with_head) const {
     return b;
 }
 
+// Diagnostic: device time of `reps` back-to-back verify passes of R rows over whatever tokens / state are current
+// (what = 0), or of only the GEMV launches of such passes (what = 1). State and KV are not committed.
+int Engine::profile_pass(int R, int what, int reps, float* ms) {
+    HP_REQUIRE(R >= 1 && R <= 8 && reps >= 1 && ms, "profile_pass: bad arguments");
+    int* d = h_desc_;
+    for (int t = 0; t < R; ++t) { d[D_TOK + t] = (t * 7919 + 13) % c_.n_vocab; d[D_POS + t] = t; d[D_SLOT + t] = 0; d[D_RGROUP + t] = 0; }
+    d[D_GROUPS] = 0; d[D_GROUPS + 1] = R; d[D_GROUPS + 2] = 0; d[D_GROUPS + 3] = 0;
+    d[D_SEQS] = 0; d[D_SEQS + 1] = R; d[D_SEQS + 2] = 0; d[D_SEQS + 3] = 0;
+    HP_TRY(upload_desc());
+    gemv_only_ = what == 1;
+    int rc = run_pass(R, 1, 1);                     // warm-up (also sets kernel attributes)
+    HP_CUDA(cudaEventRecord(ev0_, s_));
+    for (int i = 0; i < reps && rc == HP_OK; ++i) rc = run_pass(R, 1, 1);
+    HP_CUDA(cudaEventRecord(ev1_, s_));
+    gemv_only_ = false;
+    HP_CUDA(cudaStreamSynchronize(s_));
+    if (rc != HP_OK) return rc;
+    float t = 0; HP_CUDA(cudaEventElapsedTime(&t, ev0_, ev1_)); *ms = t / reps;
+    return HP_OK;
+}
+
 // ------------------------------------------------------------------ fused device-side round
 int Engine::spec_begin(int slot, int id_last, int pos, const float* h_pending_dev) {
     HP_REQUIRE(c_.has_mtp, "model has no MTP block");
@@ -515,6 +537,7 @@ int Engine::spec_round(int slot, int n, const int* subst, int* out_tokens, int* 
     for (int i = 0; i < 8; ++i) h_spec_[i] = (subst && i < n) ? subst[i] : -1;
     static const bool no_graph = getenv("HIPSTER_B200_NO_GRAPH") != nullptr;
     const int key = slot * 8 + n;
+    HP_CUDA(cudaEventRecord(ev0_, s_));
     if (no_graph) HP_TRY(enqueue_round(slot, n));
     else {
         if (!graphs_[key]) {
@@ -531,7 +554,9 @@ int Engine::spec_round(int slot, int n, const int* subst, int* out_tokens, int* 
         HP_CUDA(cudaGraphLaunch(graphs_[key], s_));
     }
 done:
+    HP_CUDA(cudaEventRecord(ev1_, s_));
     HP_CUDA(cudaStreamSynchronize(s_));
+    HP_CUDA(cudaEventElapsedTime(&last_ms_, ev0_, ev1_));
     {
         int herr = 0; HP_CUDA(cudaMemcpy(&herr, err_, 4, cudaMemcpyDeviceToHost));
         if (herr) { cudaMemset(err_, 0, 4); set_error("a kernel gave up a bounded wait (device status %d)", herr); return herr; }

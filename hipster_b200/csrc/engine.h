@@ -8,6 +8,7 @@
 #include "../../include/hipster_b200.h"
 #include <vector>
 #include <string>
+#include <cstdlib>
 
 namespace hp {
 
@@ -50,6 +51,7 @@ public:
     float* mtp_logits() const { return mlogits_; } float* mtp_h() const { return mh_; }
     size_t weight_bytes() const { return weight_bytes_; } float last_ms() const { return last_ms_; }
     size_t pass_weight_bytes(bool mtp, bool with_head) const;
+    int profile_pass(int R, int what, int reps, float* ms);
 private:
     struct Desc;   // device-visible pass descriptor (see engine.cu)
     int alloc(void** p, size_t bytes);
@@ -89,7 +91,7 @@ private:
     cudaStream_t s_ = nullptr; cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
     std::vector<void*> allocs_;
     size_t weight_bytes_ = 0; float last_ms_ = 0;
-    int last_rows_ = 0;
+    int last_rows_ = 0; bool gemv_only_ = false; bool pdl_ = getenv("HIPSTER_B200_NO_PDL") == nullptr;
 };
 
 }  // namespace hp

@@ -86,6 +86,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
     constexpr uint32_t unit_bytes = CB * 144u;
     y += (size_t)ct.part * part_stride;
 
+    pdl_launch_dependents();   // the next kernel may be scheduled; it waits for this one to finish before using its output
     if (lane == 0) {
         for (int s = 0; s < SK_STAGES; ++s) mbar_init(bar0 + 8 * s, 1);
         if (warp == 0) mbar_init(xbar, 1);
@@ -119,7 +120,6 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
             bulk_g2s(smem_u32(smem + Geo::FIXED + NT * nbp * 2048 + n * nbp * 512), xsc + ((size_t)n * nb + kb0) * 32, nbp * 512u, xbar);
         }
     }
-    pdl_launch_dependents();
 
     float2 acc[NT][2];   // [n][0] = row g, cols 2t,2t+1 ; [n][1] = row g+8
     auto zero_acc = [&]() {

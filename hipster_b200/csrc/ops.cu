@@ -38,53 +38,82 @@ __global__ void __launch_bounds__(256) k_embed_bf16(const int* __restrict__ tok,
 }
 
 // ---- x += y (y = sum of P K-part planes in part order); xn = x * (1/sqrt(mean x^2 + eps)) * w; xq = q8(xn) ----
-// One 256-thread block per row. Thread i owns elements i, i+256, ...; sum of squares: per-thread fmaf chain in that
-// order, then block_sum_det. Quantisation per 32 consecutive elements (one warp).
-__global__ void __launch_bounds__(256) k_add_rmsnorm_quant(float* __restrict__ x, const float* __restrict__ y, int P, size_t part_stride, int ldy,
-                                                            const uint16_t* __restrict__ w, float* __restrict__ xn, int8_t* __restrict__ q, float* __restrict__ sc,
-                                                            int n, float eps) {
-    __shared__ float sh[8];
+// One 1024-thread block per row. Thread i owns elements i, i+1024, ... (kept in registers); sum of squares: per-thread
+// fmaf chain in that order, then block_sum_det over the 32 warps. Quantisation per 32 consecutive elements (one warp).
+constexpr int NORM_THREADS = 1024, NORM_MAXE = 10;   // rows of up to 10240 elements
+__global__ void __launch_bounds__(NORM_THREADS) k_add_rmsnorm_quant(float* __restrict__ x, const float* __restrict__ y, int P, size_t part_stride, int ldy,
+                                                                     const uint16_t* __restrict__ w, float* __restrict__ xn, int8_t* __restrict__ q, float* __restrict__ sc,
+                                                                     int n, float eps) {
+    __shared__ float sh[32];
+    pdl_launch_dependents();
     const int r = blockIdx.x, lane = threadIdx.x & 31;
     float* xr = x + (size_t)r * n;
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < n; i += 256) {
-        float t = xr[i];
-        if (y) {
-            float s = y[(size_t)r * ldy + i];
-            for (int p = 1; p < P; ++p) s = s + y[(size_t)p * part_stride + (size_t)r * ldy + i];
-            t = t + s; xr[i] = t;
-        }
-        ss = fmaf(t, t, ss);
+    float wv[NORM_MAXE];
+#pragma unroll
+    for (int k = 0; k < NORM_MAXE; ++k) { const int i = threadIdx.x + k * NORM_THREADS; wv[k] = i < n ? bf2f(w[i]) : 0.f; }   // weights do not depend on the previous kernel
+    pdl_wait();
+    float v[NORM_MAXE];
+#pragma unroll
+    for (int k = 0; k < NORM_MAXE; ++k) { const int i = threadIdx.x + k * NORM_THREADS; v[k] = i < n ? xr[i] : 0.f; }
+    if (y) {
+        float s[NORM_MAXE];
+#pragma unroll
+        for (int k = 0; k < NORM_MAXE; ++k) { const int i = threadIdx.x + k * NORM_THREADS; s[k] = i < n ? y[(size_t)r * ldy + i] : 0.f; }
+        for (int p = 1; p < P; ++p)
+#pragma unroll
+            for (int k = 0; k < NORM_MAXE; ++k) { const int i = threadIdx.x + k * NORM_THREADS; if (i < n) s[k] = s[k] + y[(size_t)p * part_stride + (size_t)r * ldy + i]; }
+#pragma unroll
+        for (int k = 0; k < NORM_MAXE; ++k) { const int i = threadIdx.x + k * NORM_THREADS; if (i < n) { v[k] = v[k] + s[k]; xr[i] = v[k]; } }
     }
-    ss = block_sum_det<8>(ss, sh);
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < NORM_MAXE; ++k) { const int i = threadIdx.x + k * NORM_THREADS; if (i < n) ss = fmaf(v[k], v[k], ss); }
+    ss = block_sum_det<32>(ss, sh);
     const float scl = 1.0f / sqrtf(ss / (float)n + eps);
-    for (int i = threadIdx.x; i < n; i += 256) {
-        const float v = (xr[i] * scl) * bf2f(w[i]);
-        if (xn) xn[(size_t)r * n + i] = v;
-        warp_quant32_store(v, r, i >> 5, n, q, sc, lane);
+#pragma unroll
+    for (int k = 0; k < NORM_MAXE; ++k) {
+        const int i = threadIdx.x + k * NORM_THREADS;
+        if (i < n) {   // n is a multiple of 32: a warp is wholly inside or wholly outside
+            const float o = (v[k] * scl) * wv[k];
+            if (xn) xn[(size_t)r * n + i] = o;
+            warp_quant32_store(o, r, i >> 5, n, q, sc, lane);
+        }
     }
 }
 
 // ---- MTP input: out[r] = [rmsnorm(a[r]) * wa | rmsnorm(b[r]) * wb], quantised (ops.hip:99-116) ----
-__global__ void __launch_bounds__(256) k_norm2_concat_quant(const float* __restrict__ a, const uint16_t* __restrict__ wa, const float* __restrict__ b, int ldb,
-                                                             const uint16_t* __restrict__ wb, float* __restrict__ out, int8_t* __restrict__ q, float* __restrict__ sc,
-                                                             int n, float eps) {
-    __shared__ float sh[8];
+__global__ void __launch_bounds__(NORM_THREADS) k_norm2_concat_quant(const float* __restrict__ a, const uint16_t* __restrict__ wa, const float* __restrict__ b, int ldb,
+                                                                      const uint16_t* __restrict__ wb, float* __restrict__ out, int8_t* __restrict__ q, float* __restrict__ sc,
+                                                                      int n, float eps) {
+    __shared__ float sh[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x, lane = threadIdx.x & 31;
     const float* ar = a + (size_t)r * n; const float* br = b + (size_t)r * ldb;
+    float va[NORM_MAXE], vb[NORM_MAXE];
     float sa = 0.f, sb = 0.f;
-    for (int i = threadIdx.x; i < n; i += 256) { sa = fmaf(ar[i], ar[i], sa); sb = fmaf(br[i], br[i], sb); }
-    sa = block_sum_det<8>(sa, sh); sb = block_sum_det<8>(sb, sh);
+#pragma unroll
+    for (int k = 0; k < NORM_MAXE; ++k) { const int i = threadIdx.x + k * NORM_THREADS; va[k] = i < n ? ar[i] : 0.f; vb[k] = i < n ? br[i] : 0.f; }
+#pragma unroll
+    for (int k = 0; k < NORM_MAXE; ++k) { const int i = threadIdx.x + k * NORM_THREADS; if (i < n) { sa = fmaf(va[k], va[k], sa); sb = fmaf(vb[k], vb[k], sb); } }
+    sa = block_sum_det<32>(sa, sh); sb = block_sum_det<32>(sb, sh);
     const float ca = 1.0f / sqrtf(sa / (float)n + eps), cb = 1.0f / sqrtf(sb / (float)n + eps);
-    for (int i = threadIdx.x; i < 2 * n; i += 256) {
-        const float v = i < n ? (ar[i] * ca) * bf2f(wa[i]) : (br[i - n] * cb) * bf2f(wb[i - n]);
-        if (out) out[(size_t)r * 2 * n + i] = v;
-        warp_quant32_store(v, r, i >> 5, 2 * n, q, sc, lane);
+#pragma unroll
+    for (int k = 0; k < NORM_MAXE; ++k) {
+        const int i = threadIdx.x + k * NORM_THREADS;
+        if (i < n) {
+            const float oa = (va[k] * ca) * bf2f(wa[i]), ob = (vb[k] * cb) * bf2f(wb[i]);
+            if (out) { out[(size_t)r * 2 * n + i] = oa; out[(size_t)r * 2 * n + n + i] = ob; }
+            warp_quant32_store(oa, r, i >> 5, 2 * n, q, sc, lane);
+            warp_quant32_store(ob, r, (n + i) >> 5, 2 * n, q, sc, lane);
+        }
     }
 }
 
 // ---- xq = q8(silu(gate) * up); gate = columns [0, F), up = [F, 2F) of gu [R][ldg] (ops.hip:146-151) ----
 __global__ void __launch_bounds__(256) k_silu_mul_quant(const float* __restrict__ gu, int ldg, int F, int8_t* __restrict__ q, float* __restrict__ sc) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.y, sb = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (sb * 32 >= F) return;
     const int i = sb * 32 + lane;
@@ -116,19 +145,24 @@ struct GdnArgs {
     float* snap; size_t snap_row_stride;                          // optional state snapshots after each new row
     float eps; int sigmoid_gate;
 };
+constexpr int GDN_MAXROWS = 16;   // replayed rows (<= 8) + new rows (<= 8) of one sequence
 __global__ void __launch_bounds__(256) k_gdn(GdnArgs a) {
     constexpr int D = 128;
-    __shared__ float sq[D], sk[D], sv[D], sout[D], sh[8];
-    const int h = blockIdx.x, hk = h % a.n_qk, tid = threadIdx.x;
-    const int r0 = a.seq[blockIdx.y * 4 + 0], T = a.seq[blockIdx.y * 4 + 1], slot = a.seq[blockIdx.y * 4 + 2];
+    __shared__ float sq[GDN_MAXROWS][D], sk[GDN_MAXROWS][D], sv[GDN_MAXROWS][D], sout[8][D];
+    __shared__ float red[GDN_MAXROWS * 2][8], tot[GDN_MAXROWS * 2], sbeta[GDN_MAXROWS], sdecay[GDN_MAXROWS];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int h = blockIdx.x, hk = h % a.n_qk, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int r0 = a.seq[blockIdx.y * 4 + 0], T = min(a.seq[blockIdx.y * 4 + 1], 8), slot = a.seq[blockIdx.y * 4 + 2];
     float* sav = a.saved + (size_t)slot * a.saved_stride + (size_t)h * 8 * 388;   // [8][q 128 | k 128 | v 128 | beta | alpha | pad]
-    const int nrep = a.replay_n ? a.replay_n[slot] : 0;
+    const int nrep = a.replay_n ? min(a.replay_n[slot], 8) : 0;
+    const int nrows = nrep + T;
     const int Z = a.n_v * D;
     const int j = tid >> 1, ih = tid & 1;
     float* Mst = a.state + (size_t)slot * a.state_stride + ((size_t)h * D + j) * D + 64 * ih;
     // conv history of this head: [3 taps][q 128 | k 128 | v 128]; private per v-head so that no CTA reads what another writes
     float* cst = a.conv_state + (size_t)slot * a.conv_stride + (size_t)h * 3 * 384;
-    const int sa_ = tid < D ? tid : D + tid, sb_ = D + (tid & (D - 1));   // history slots of channels ca / cb
+    const int sa_ = tid < D ? tid : D + tid, sb_ = D + (tid & (D - 1));   // history / saved-row slots of channels ca / cb
     float m[64];
 #pragma unroll
     for (int i = 0; i < 64; ++i) m[i] = Mst[i];
@@ -140,76 +174,126 @@ __global__ void __launch_bounds__(256) k_gdn(GdnArgs a) {
     if (tid < D) { hb0 = cst[sb_]; hb1 = cst[384 + sb_]; hb2 = cst[768 + sb_]; }
     const float wa0 = a.conv_w[ca * 4 + 0], wa1 = a.conv_w[ca * 4 + 1], wa2 = a.conv_w[ca * 4 + 2], wa3 = a.conv_w[ca * 4 + 3];
     const float wb0 = a.conv_w[cb * 4 + 0], wb1 = a.conv_w[cb * 4 + 1], wb2 = a.conv_w[cb * 4 + 2], wb3 = a.conv_w[cb * 4 + 3];
-    const float dtb = bf2f(a.dt_bias[h]), aneg = bf2f(a.a_neg[h]);
 
-    for (int it = 0; it < nrep + T; ++it) {
-        const bool replay = it < nrep;
-        const int t = r0 + (it - nrep);                      // row of this pass (new rows only)
-        const float* row = a.rows + (size_t)(replay ? 0 : t) * a.ld;
-        float* srow = sav + (replay ? it : it - nrep) * 388;
-        if (it == nrep) {   // the accepted prefix has been applied: commit state and conv history (also when nrep == 0: no-op values)
-            if (nrep > 0) {
+    // ---- phase 1: raw inputs of all rows (one round of loads), conv + SiLU, squared norms, gates
+    float xa[GDN_MAXROWS], xb[GDN_MAXROWS];
 #pragma unroll
-                for (int i = 0; i < 64; ++i) Mst[i] = m[i];
+    for (int it = 0; it < GDN_MAXROWS; ++it) {
+        xa[it] = 0.f; xb[it] = 0.f;
+        if (it < nrows) {
+            const bool replay = it < nrep;
+            const float* row = a.rows + (size_t)(replay ? 0 : r0 + (it - nrep)) * a.ld;
+            const float* srow = sav + (replay ? it : 0) * 388;
+            xa[it] = replay ? srow[sa_] : row[ca];
+            if (tid < D) xb[it] = replay ? srow[sb_] : row[cb];
+        }
+    }
+    if (tid < nrows) {
+        const bool replay = tid < nrep;
+        const float* row = a.rows + (size_t)(replay ? 0 : r0 + (tid - nrep)) * a.ld;
+        const float braw = replay ? sav[tid * 388 + 384] : row[a.off_b + h], araw = replay ? sav[tid * 388 + 385] : row[a.off_a + h];
+        sbeta[tid] = sigmoid_det(braw);
+        sdecay[tid] = expf_det(bf2f(a.a_neg[h]) * softplus_det(araw + bf2f(a.dt_bias[h])));
+        sq[tid][0] = braw; sk[tid][0] = araw;   // parked until the save below (overwritten afterwards)
+    }
+    __syncthreads();
+    // keep the raw inputs of the new rows for a later commit (after every replayed row has been read)
+#pragma unroll
+    for (int it = 0; it < GDN_MAXROWS; ++it)
+        if (it >= nrep && it < nrows) {
+            float* srow = sav + (it - nrep) * 388;
+            srow[sa_] = xa[it]; if (tid < D) srow[sb_] = xb[it];
+            if (tid == 0) { srow[384] = sq[it][0]; srow[385] = sk[it][0]; }
+        }
+    __syncthreads();
+    float va[GDN_MAXROWS], vb[GDN_MAXROWS];
+#pragma unroll
+    for (int it = 0; it < GDN_MAXROWS; ++it) {
+        va[it] = 0.f; vb[it] = 0.f;
+        if (it < nrows) {
+            if (it == nrep && nrep > 0) {   // history after the accepted prefix: committed
                 cst[sa_] = ha0; cst[384 + sa_] = ha1; cst[768 + sa_] = ha2;
                 if (tid < D) { cst[sb_] = hb0; cst[384 + sb_] = hb1; cst[768 + sb_] = hb2; }
             }
+            float t = wa0 * ha0; t = fmaf(wa1, ha1, t); t = fmaf(wa2, ha2, t); t = fmaf(wa3, xa[it], t);
+            va[it] = silu_det(t); ha0 = ha1; ha1 = ha2; ha2 = xa[it];
+            if (tid < D) {
+                float u = wb0 * hb0; u = fmaf(wb1, hb1, u); u = fmaf(wb2, hb2, u); u = fmaf(wb3, xb[it], u);
+                vb[it] = silu_det(u); hb0 = hb1; hb1 = hb2; hb2 = xb[it];
+            }
+            // squared l2 norms: xor tree inside the warp, warp sums added in warp order afterwards
+            float pq = tid < D ? va[it] * va[it] : 0.f, pk = tid < D ? vb[it] * vb[it] : 0.f;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) { pq = pq + __shfl_xor_sync(0xffffffffu, pq, off); pk = pk + __shfl_xor_sync(0xffffffffu, pk, off); }
+            if (lane == 0) { red[2 * it][warp] = pq; red[2 * it + 1][warp] = pk; }
         }
-        // conv + silu
-        const float xa = replay ? srow[sa_] : row[ca];
-        float va = wa0 * ha0; va = fmaf(wa1, ha1, va); va = fmaf(wa2, ha2, va); va = fmaf(wa3, xa, va);
-        va = silu_det(va); ha0 = ha1; ha1 = ha2; ha2 = xa;
-        float vb = 0.f, vb_raw = 0.f;
-        if (tid < D) {
-            const float xb = replay ? srow[sb_] : row[cb];
-            vb = wb0 * hb0; vb = fmaf(wb1, hb1, vb); vb = fmaf(wb2, hb2, vb); vb = fmaf(wb3, xb, vb);
-            vb = silu_det(vb); hb0 = hb1; hb1 = hb2; hb2 = xb; vb_raw = xb;
+    }
+    if (T == 0 && nrep > 0) {   // pure commit: the loop above never reached it == nrep
+        cst[sa_] = ha0; cst[384 + sa_] = ha1; cst[768 + sa_] = ha2;
+        if (tid < D) { cst[sb_] = hb0; cst[384 + sb_] = hb1; cst[768 + sb_] = hb2; }
+    }
+    __syncthreads();
+    if (tid < 2 * nrows) { float t = red[tid][0]; for (int w = 1; w < 8; ++w) t = t + red[tid][w]; tot[tid] = t; }
+    __syncthreads();
+#pragma unroll
+    for (int it = 0; it < GDN_MAXROWS; ++it)
+        if (it < nrows) {
+            if (tid < D) { sq[it][tid] = va[it] / fmaxf(sqrtf(tot[2 * it]), a.eps); sk[it][tid] = vb[it] / fmaxf(sqrtf(tot[2 * it + 1]), a.eps); }
+            else sv[it][tid - D] = va[it];
         }
-        const float qn = block_sum_det<8>(tid < D ? va * va : 0.f, sh);
-        const float kn = block_sum_det<8>(tid < D ? vb * vb : 0.f, sh);
-        if (tid < D) { sq[tid] = va / fmaxf(sqrtf(qn), a.eps); sk[tid] = vb / fmaxf(sqrtf(kn), a.eps); }
-        else sv[tid - D] = va;
-        __syncthreads();
-        const float braw = replay ? srow[384] : row[a.off_b + h], araw = replay ? srow[385] : row[a.off_a + h];
-        if (!replay) {   // keep the raw inputs of this row for a later commit (rows beyond 8 per sequence are never replayed)
-            srow[sa_] = xa; if (tid < D) srow[sb_] = vb_raw; if (tid == 0) { srow[384] = braw; srow[385] = araw; }
+    __syncthreads();
+
+    // ---- phase 2: the recurrence, row after row, state in registers; no block-wide synchronisation inside
+    for (int it = 0; it < nrows; ++it) {
+        if (it == nrep && nrep > 0) {
+#pragma unroll
+            for (int i = 0; i < 64; ++i) Mst[i] = m[i];
         }
-        const float beta = sigmoid_det(braw);
-        const float decay = expf_det(aneg * softplus_det(araw + dtb));
+        const float beta = sbeta[it], decay = sdecay[it];
+        const float* kk = &sk[it][64 * ih]; const float* qq = &sq[it][64 * ih];
         float dot = 0.f;
 #pragma unroll
-        for (int i = 0; i < 64; ++i) { m[i] = m[i] * decay; dot = fmaf(m[i], sk[64 * ih + i], dot); }
+        for (int i = 0; i < 64; ++i) { m[i] = m[i] * decay; dot = fmaf(m[i], kk[i], dot); }
         dot = dot + __shfl_xor_sync(0xffffffffu, dot, 1);
-        const float delta = (sv[j] - dot) * beta;
+        const float delta = (sv[it][j] - dot) * beta;
         float o = 0.f;
 #pragma unroll
-        for (int i = 0; i < 64; ++i) { m[i] = fmaf(delta, sk[64 * ih + i], m[i]); o = fmaf(m[i], sq[64 * ih + i], o); }
+        for (int i = 0; i < 64; ++i) { m[i] = fmaf(delta, kk[i], m[i]); o = fmaf(m[i], qq[i], o); }
         o = o + __shfl_xor_sync(0xffffffffu, o, 1);
-        if (!replay) {
-            if (ih == 0) sout[j] = o * 0.08838834764831845f;
-            __syncthreads();
-            const float ss = block_sum_det<8>(tid < D ? sout[tid] * sout[tid] : 0.f, sh);
-            if (tid < D) {
-                const size_t oi = (size_t)t * Z + h * D + tid;
-                const float zz = row[a.off_z + h * D + tid];
-                const float v = ((sout[tid] * (1.0f / sqrtf(ss / (float)D + a.eps))) * bf2f(a.norm_w[tid])) * (a.sigmoid_gate ? sigmoid_det(zz) : silu_det(zz));
-                if (a.out) a.out[oi] = v;
-                if (a.oq) warp_quant32_store(v, t, (h * D + tid) >> 5, Z, a.oq, a.osc, tid & 31);
-            }
+        if (it >= nrep) {
+            if (ih == 0) sout[it - nrep][j] = o * 0.08838834764831845f;
             if (a.snap) {
                 float* sp = a.snap + (size_t)(it - nrep) * a.snap_row_stride + ((size_t)h * D + j) * D + 64 * ih;
 #pragma unroll
                 for (int i = 0; i < 64; ++i) sp[i] = m[i];
             }
         }
-        __syncthreads();
     }
-    if (T == 0 && nrep > 0) {   // pure commit (no new rows): the loop above never reached it == nrep
+    if (T == 0 && nrep > 0) {
 #pragma unroll
         for (int i = 0; i < 64; ++i) Mst[i] = m[i];
-        cst[sa_] = ha0; cst[384 + sa_] = ha1; cst[768 + sa_] = ha2;
-        if (tid < D) { cst[sb_] = hb0; cst[384 + sb_] = hb1; cst[768 + sb_] = hb2; }
     }
+    __syncthreads();
+
+    // ---- phase 3: per-head RMSNorm * w * gate(z) + quantisation of the new rows
+    for (int t = 0; t < T; ++t) {
+        float ps = tid < D ? sout[t][tid] * sout[t][tid] : 0.f;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) ps = ps + __shfl_xor_sync(0xffffffffu, ps, off);
+        if (lane == 0) red[t][warp] = ps;
+    }
+    __syncthreads();
+    if (tid < T) { float t = red[tid][0]; for (int w = 1; w < 8; ++w) t = t + red[tid][w]; tot[tid] = t; }
+    __syncthreads();
+    if (tid < D)
+        for (int t = 0; t < T; ++t) {
+            const int row = r0 + t;
+            const size_t oi = (size_t)row * Z + h * D + tid;
+            const float zz = a.rows[(size_t)row * a.ld + a.off_z + h * D + tid];
+            const float v = ((sout[t][tid] * (1.0f / sqrtf(tot[t] / (float)D + a.eps))) * bf2f(a.norm_w[tid])) * (a.sigmoid_gate ? sigmoid_det(zz) : silu_det(zz));
+            if (a.out) a.out[oi] = v;
+            if (a.oq) warp_quant32_store(v, row, (h * D + tid) >> 5, Z, a.oq, a.osc, lane);
+        }
 }
 
 }  // namespace
@@ -221,17 +305,19 @@ int embed_bf16(const int* tok, const void* table, float* out, int R, int E, int 
 }
 int add_rmsnorm_quant(float* x, const float* y, int P, size_t part_stride, int ldy, const void* w_bf16, float* xn, XQ8F xq, int R, int n, float eps, cudaStream_t s) {
     HP_REQUIRE(R >= 1 && n > 0 && n % 64 == 0, "add_rmsnorm_quant: n=%d must be a positive multiple of 64", n);
-    k_add_rmsnorm_quant<<<R, 256, 0, s>>>(x, y, P, part_stride, ldy, (const uint16_t*)w_bf16, xn, (int8_t*)xq.q, (float*)xq.sc, n, eps);
+    HP_REQUIRE(n <= NORM_THREADS * NORM_MAXE, "add_rmsnorm_quant: n=%d exceeds %d", n, NORM_THREADS * NORM_MAXE);
+    launch_pdl(k_add_rmsnorm_quant, dim3(R), dim3(NORM_THREADS), 0, s, x, y, P, part_stride, ldy, (const uint16_t*)w_bf16, xn, (int8_t*)xq.q, (float*)xq.sc, n, eps);
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 int norm2_concat_quant(const float* a, const void* wa, const float* b, int ldb, const void* wb, float* out, XQ8F xq, int R, int n, float eps, cudaStream_t s) {
     HP_REQUIRE(R >= 1 && n > 0 && n % 64 == 0, "norm2_concat_quant: n=%d must be a positive multiple of 64", n);
-    k_norm2_concat_quant<<<R, 256, 0, s>>>(a, (const uint16_t*)wa, b, ldb, (const uint16_t*)wb, out, (int8_t*)xq.q, (float*)xq.sc, n, eps);
+    HP_REQUIRE(n <= NORM_THREADS * NORM_MAXE, "norm2_concat_quant: n=%d exceeds %d", n, NORM_THREADS * NORM_MAXE);
+    launch_pdl(k_norm2_concat_quant, dim3(R), dim3(NORM_THREADS), 0, s, a, (const uint16_t*)wa, b, ldb, (const uint16_t*)wb, out, (int8_t*)xq.q, (float*)xq.sc, n, eps);
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 int silu_mul_quant(const float* gu, int ldg, int F, XQ8F xq, int R, cudaStream_t s) {
     HP_REQUIRE(R >= 1 && F > 0 && F % 64 == 0 && ldg >= 2 * F, "silu_mul_quant: bad shape F=%d ldg=%d", F, ldg);
-    k_silu_mul_quant<<<dim3((F / 32 + 7) / 8, R), 256, 0, s>>>(gu, ldg, F, (int8_t*)xq.q, (float*)xq.sc);
+    launch_pdl(k_silu_mul_quant, dim3((F / 32 + 7) / 8, R), dim3(256), 0, s, gu, ldg, F, (int8_t*)xq.q, (float*)xq.sc);
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 int gdn_forward(const GdnParams& p, int nseq, cudaStream_t s) {
@@ -242,7 +328,7 @@ int gdn_forward(const GdnParams& p, int nseq, cudaStream_t s) {
     a.state = p.state; a.conv_state = p.conv_state; a.state_stride = p.state_stride; a.conv_stride = p.conv_stride;
     a.seq = p.seq; a.replay_n = p.replay_n; a.out = p.out; a.oq = (int8_t*)p.xq.q; a.osc = (float*)p.xq.sc;
     a.snap = p.snap; a.snap_row_stride = p.snap_row_stride; a.eps = p.eps; a.sigmoid_gate = p.sigmoid_gate;
-    k_gdn<<<dim3(p.n_v, nseq), 256, 0, s>>>(a);
+    launch_pdl(k_gdn, dim3(p.n_v, nseq), dim3(256), 0, s, a);
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 

@@ -138,6 +138,15 @@ class Engine:
         check(lib().hp_gdn_state_dev(self._h, slot, gdn_layer, ctypes.byref(p), ctypes.byref(n)))
         return self._fetch(p.value, n.value // 4)
 
+    def profile_pass(self, R, what, reps):
+        ms = ctypes.c_float(0)
+        check(lib().hp_profile_pass(self._h, R, what, reps, ctypes.byref(ms)))
+        return ms.value
+
+    def pass_weight_bytes(self, mtp, with_head):
+        lib().hp_pass_weight_bytes.restype = ctypes.c_size_t
+        return lib().hp_pass_weight_bytes(self._h, int(mtp), int(with_head))
+
     # ---- fused device-side round
     def spec_begin(self, slot, id_last, pos, h_pending_ptr):
         check(lib().hp_spec_begin(self._h, slot, int(id_last), int(pos), ctypes.c_void_p(h_pending_ptr)))

@@ -70,6 +70,27 @@ int hp_argmax_noalloc_max_n(void);
  * ids_dev holds n_draft+1 target argmaxes. Replaces the host loop of engine/bench/spec27b.cpp:92-97. */
 int hp_accept_greedy(const int* ids_dev, const int* drafts_dev, int n_draft, int* out_dev, void* stream);
 
+/* x += sum of n_planes planes of y (plane p at y_dev + p * plane_stride, rows of n floats; n_planes = 0: no add);
+ * xn = x * rsqrt(mean(x^2) + eps) * w (bf16 weights); xq = int8 quantisation of xn. One call for R rows.
+ * Replaces add_rmsnorm_quant (ops.h:14, ops.hip:79-98). xn_dev may be NULL. */
+int hp_add_rmsnorm_quant(float* x_dev, const float* y_dev, int n_planes, size_t plane_stride, const void* w_bf16_dev, float* xn_dev, void* xq_q_dev, void* xq_sc_dev, int R, int n, float eps, void* stream);
+/* xq = q8(silu(gate) * up), gate = columns [0, F) and up = [F, 2F) of gate_up [R][ld]. Replaces silu_mul_quant (ops.h:25, ops.hip:146-151). */
+int hp_silu_mul_quant(const float* gate_up_dev, int ld, int F, void* xq_q_dev, void* xq_sc_dev, int R, void* stream);
+/* One Gated-DeltaNet layer step for one sequence: causal 4-tap conv + SiLU and the gated delta rule over T new rows
+ * (rows [T][ld] = qkv | z | beta | alpha, the in-projection output), with per-row state snapshots and rollback.
+ * First the first n_replay rows of the PREVIOUS call (their raw inputs are kept in saved_dev) are applied to the
+ * committed state in state_dev / conv_state_dev and written back: that is "accept n_replay rows" (rollback to that
+ * prefix; Qwen35::accept, qwen35.cpp:383-403). Then the T new rows are processed from that state: out [T][n_v*128]
+ * (nullable), quantised out (nullable), snap_dev (nullable) = the state after each new row [T][n_v][128][128]. The
+ * committed state is not advanced by the new rows until a later call accepts them. T = 0 only commits.
+ * conv_state_dev: hp_gdn_conv_state_floats(n_v) floats, [n_v][3 taps][q 128 | k 128 | v 128] (each value head keeps the
+ * history of its own q/k head); saved_dev: hp_gdn_saved_floats(n_v) floats. Replaces gdn_conv + gdn_step (ops.h:41-51). */
+size_t hp_gdn_conv_state_floats(int n_v);
+size_t hp_gdn_saved_floats(int n_v);
+int hp_gdn_layer(const float* rows_dev, int ld, int T, int n_replay, int n_qk, int n_v, const float* conv_w_dev, const void* dt_bias_bf16_dev, const void* a_neg_bf16_dev,
+                 const void* norm_w_bf16_dev, float* state_dev, float* conv_state_dev, float* saved_dev, float* out_dev, void* xq_q_dev, void* xq_sc_dev,
+                 float* snap_dev, float eps, int sigmoid_gate, void* stream);
+
 /* ------------------------------------------------------------------ engine level (engine/src/qwen35.h, qwen4exp.h) */
 
 /* Shapes of the hybrid Gated-DeltaNet / attention model. The reference fixes them at compile time (struct Qwen35Dims,
@@ -122,6 +143,12 @@ const float* hp_mtp_h_dev(const hp_engine* e);             /* qwen35.h:85 */
  * slot's committed GDN state [gdn_v_heads][128][128] (pending accepts are applied first). */
 int hp_tensor_dev(const hp_engine* e, int layer, int kind, void** ptr_out, size_t* bytes_out);
 int hp_gdn_state_dev(hp_engine* e, int slot, int gdn_layer, float** ptr_out, size_t* bytes_out);
+/* Measurement hooks (the reference's HIPSTER_TIMING categories, qwen35.h:95, qwen35.cpp:181-186): mean device time of
+ * `reps` verify passes of R rows (what = 0) or of only their GEMV launches (what = 1); nothing is committed.
+ * hp_pass_weight_bytes: Q4_K bytes one trunk pass (mtp = 0) or one MTP-block pass (mtp = 1) reads, with or without the
+ * LM head: the algorithmic bytes of the roofline. */
+int hp_profile_pass(hp_engine* e, int R, int what, int reps, float* ms_out);
+size_t hp_pass_weight_bytes(const hp_engine* e, int mtp, int with_head);
 /* The whole MTP round on the device: n_draft draft steps, one verify pass of n_draft+1 rows, argmax, greedy acceptance,
  * commit and MTP catch-up, with no logits or ids crossing to the host; only the emitted tokens come back.
  * hp_spec_begin seeds it with the last emitted token, its position and the pending hidden row (device pointer, n_embd).

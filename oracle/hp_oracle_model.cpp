@@ -50,6 +50,7 @@ inline float irwin(uint64_t u) {
 inline uint16_t f32_to_bf16(float f) { uint32_t u = fbits(f); u += 0x7FFFu + ((u >> 16) & 1u); return (uint16_t)(u >> 16); }
 void gen_q4k(std::vector<uint8_t>& w, int N, int K, uint64_t seed, uint64_t tid) {
     const size_t nwords = (size_t)N * (K / 256) * 18; w.resize(nwords * 8);
+#pragma omp parallel for schedule(static)
     for (size_t i = 0; i < nwords; ++i) {
         uint64_t v = rnd64(seed, tid, i);
         if (i % 18 == 0) {
@@ -62,7 +63,9 @@ void gen_q4k(std::vector<uint8_t>& w, int N, int K, uint64_t seed, uint64_t tid)
     }
 }
 void gen_bf16(std::vector<uint16_t>& p, size_t n, uint64_t seed, uint64_t tid, float mean, float sd) {
-    p.resize(n); for (size_t i = 0; i < n; ++i) p[i] = f32_to_bf16(mean + sd * irwin(rnd64(seed, tid, i)));
+    p.resize(n);
+#pragma omp parallel for schedule(static)
+    for (size_t i = 0; i < n; ++i) p[i] = f32_to_bf16(mean + sd * irwin(rnd64(seed, tid, i)));
 }
 void gen_f32(std::vector<float>& p, size_t n, uint64_t seed, uint64_t tid, float mean, float sd, bool neg_abs) {
     p.resize(n); for (size_t i = 0; i < n; ++i) { float v = mean + sd * irwin(rnd64(seed, tid, i)); if (neg_abs) v = -fabsf(v); p[i] = v; }
@@ -74,22 +77,22 @@ struct XQ { std::vector<int8_t> q; std::vector<float> d, s; int K = 0; void set(
 
 // ---------------------------------------------------------------- layer kernels (row layout)
 // ops.hip:79-98: x += y; xn = x * rsqrt(mean x^2 + eps) * w; q8. Here y = sum of P planes in plane order; the sum of
-// squares: 256 workers, worker i takes elements i, i+256, ... (fmaf chain), then det_block_sum.
+// squares: 1024 workers, worker i takes elements i, i+1024, ... (fmaf chain), then det_block_sum.
 extern "C" void orc_add_rmsnorm_quant(float* x, const float* y, int P, size_t part_stride, int ldy, const uint16_t* w, float* xn,
                                       int8_t* q, float* d, float* s, int R, int n, float eps) {
     std::vector<float> v(n);
     for (int r = 0; r < R; ++r) {
-        float* xr = x + (size_t)r * n; float part[256];
-        for (int t = 0; t < 256; ++t) {
+        float* xr = x + (size_t)r * n; float part[1024];
+        for (int t = 0; t < 1024; ++t) {
             float ss = 0.f;
-            for (int i = t; i < n; i += 256) {
+            for (int i = t; i < n; i += 1024) {
                 float a = xr[i];
                 if (y) { float sum = y[(size_t)r * ldy + i]; for (int p = 1; p < P; ++p) sum = sum + y[(size_t)p * part_stride + (size_t)r * ldy + i]; a = a + sum; xr[i] = a; }
                 ss = fmaf(a, a, ss);
             }
             part[t] = ss;
         }
-        const float tot = det_block_sum(part, 256);
+        const float tot = det_block_sum(part, 1024);
         const float scl = 1.0f / sqrtf(tot / (float)n + eps);
         for (int i = 0; i < n; ++i) { v[i] = (xr[i] * scl) * bf2f(w[i]); if (xn) xn[(size_t)r * n + i] = v[i]; }
         orc_quantize_x_q8(v.data(), 1, n, q + (size_t)r * n, d + (size_t)r * (n / 32), s + (size_t)r * (n / 32));
@@ -100,9 +103,9 @@ extern "C" void orc_norm2_concat_quant(const float* a, const uint16_t* wa, const
                                        int8_t* q, float* d, float* s, int R, int n, float eps) {
     std::vector<float> v(2 * n);
     for (int r = 0; r < R; ++r) {
-        const float* ar = a + (size_t)r * n; const float* br = b + (size_t)r * ldb; float pa[256], pb[256];
-        for (int t = 0; t < 256; ++t) { float sa = 0.f, sb = 0.f; for (int i = t; i < n; i += 256) { sa = fmaf(ar[i], ar[i], sa); sb = fmaf(br[i], br[i], sb); } pa[t] = sa; pb[t] = sb; }
-        const float ca = 1.0f / sqrtf(det_block_sum(pa, 256) / (float)n + eps), cb = 1.0f / sqrtf(det_block_sum(pb, 256) / (float)n + eps);
+        const float* ar = a + (size_t)r * n; const float* br = b + (size_t)r * ldb; float pa[1024], pb[1024];
+        for (int t = 0; t < 1024; ++t) { float sa = 0.f, sb = 0.f; for (int i = t; i < n; i += 1024) { sa = fmaf(ar[i], ar[i], sa); sb = fmaf(br[i], br[i], sb); } pa[t] = sa; pb[t] = sb; }
+        const float ca = 1.0f / sqrtf(det_block_sum(pa, 1024) / (float)n + eps), cb = 1.0f / sqrtf(det_block_sum(pb, 1024) / (float)n + eps);
         for (int i = 0; i < n; ++i) { v[i] = (ar[i] * ca) * bf2f(wa[i]); v[n + i] = (br[i] * cb) * bf2f(wb[i]); }
         if (out) memcpy(out + (size_t)r * 2 * n, v.data(), (size_t)2 * n * 4);
         orc_quantize_x_q8(v.data(), 1, 2 * n, q + (size_t)r * 2 * n, d + (size_t)r * (2 * n / 32), s + (size_t)r * (2 * n / 32));

@@ -171,3 +171,13 @@ class Model:
         p = ctypes.c_void_p()
         n = lib().orc_model_tensor(self.h, layer, kind_id, ctypes.byref(p))
         return np.ctypeslib.as_array(ctypes.cast(p, ctypes.POINTER(ctypes.c_uint8)), shape=(n,)).copy()
+
+
+def gdn_rows(rows, n_qk, n_v, conv_w, dt_bias, a_neg, norm_w, state, conv_hist, eps, sigmoid_gate, want_snap=False):
+    """Sequential conv + delta-rule step over the rows of one sequence (updates state / conv_hist in place)."""
+    rows = np.ascontiguousarray(rows, dtype=np.float32); T, ld = rows.shape
+    out = np.empty((T, n_v * 128), dtype=np.float32)
+    snap = np.empty((T, n_v, 128, 128), dtype=np.float32) if want_snap else None
+    lib().orc_gdn_rows(P(rows), ld, T, n_qk, n_v, P(conv_w), P(dt_bias), P(a_neg), P(norm_w), P(state), P(conv_hist), P(out),
+                       P(snap) if want_snap else ctypes.c_void_p(0), ctypes.c_float(eps), int(sigmoid_gate))
+    return out, snap
