@@ -200,7 +200,7 @@ int attn_rope_kv(const AttnParams& p, int rows, cudaStream_t s) {
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 int attn_decode(const AttnParams& p, int rows, int ngroups, cudaStream_t s) {
-    HP_REQUIRE(rows >= 1 && ngroups >= 1 && p.n_head % p.n_kv == 0 && (p.n_head / p.n_kv) * 8 <= MAXP, "attn_decode: at most %d (row, head) pairs per kv head and group", MAXP);
+    HP_REQUIRE(rows >= 1 && ngroups >= 1 && p.n_head % p.n_kv == 0 && (p.n_head / p.n_kv) <= MAXP, "attn_decode: at most %d (row, head) pairs per kv head and group", MAXP);
     static bool attr = false;
     if (!attr) { HP_CUDA(cudaFuncSetAttribute(k_attn_split, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem_bytes())); attr = true; }
     AttnArgs a; a.qkv = p.qkv; a.ld = p.ld; a.n_head = p.n_head; a.n_kv = p.n_kv; a.kc = (const uint16_t*)p.kc; a.vc = (const uint16_t*)p.vc;

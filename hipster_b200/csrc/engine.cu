@@ -131,6 +131,15 @@ int Engine::gen_lin(Lin& l, int N, int K, uint64_t tid) {
     HP_CUDA(cudaGetLastError());
     weight_bytes_ += l.bytes; return HP_OK;
 }
+int Engine::gen_raw_q4k(Lin& l, size_t rows, int K, uint64_t tid) {   // expert stacks: no GEMV partition attached
+    l.N = (int)std::min<size_t>(rows, 0x7fffffff); l.K = K; l.P = 1; l.bytes = rows * (K / 256) * 144;
+    HP_REQUIRE(K % 256 == 0, "expert tensor K=%d is not a multiple of 256", K);
+    if (int rc = alloc((void**)&l.w, l.bytes)) return rc;
+    const size_t nwords = l.bytes / 8;
+    k_gen_q4k<<<(unsigned)((nwords + 255) / 256), 256, 0, s_>>>((uint64_t*)l.w, nwords, c_.seed, tid);
+    HP_CUDA(cudaGetLastError());
+    weight_bytes_ += l.bytes; return HP_OK;
+}
 int Engine::gen_bf16(uint16_t** p, size_t n, uint64_t tid, float mean, float std) {
     if (int rc = alloc((void**)p, n * 2)) return rc;
     k_gen_bf16<<<(unsigned)((n + 255) / 256), 256, 0, s_>>>(*p, n, c_.seed, tid, mean, std);
@@ -148,7 +157,7 @@ static inline uint64_t tensor_id(int layer, int kind) { return (uint64_t)(layer 
 int Engine::init() {
     const hp_model_cfg& c = c_;
     HP_REQUIRE(c.n_embd > 0 && c.n_embd % 256 == 0 && c.n_layer >= 1 && c.n_vocab > 0, "bad model shape");
-    HP_REQUIRE(c.n_head >= 1 && c.n_head_kv >= 1 && c.n_head % c.n_head_kv == 0 && (c.n_head / c.n_head_kv) * 8 <= ATTN_MAX_PAIRS, "bad attention head counts");
+    HP_REQUIRE(c.n_head >= 1 && c.n_head_kv >= 1 && c.n_head % c.n_head_kv == 0 && (c.n_head / c.n_head_kv) <= ATTN_MAX_PAIRS, "bad attention head counts");
     HP_REQUIRE(c.gdn_qk_heads >= 1 && c.gdn_v_heads % c.gdn_qk_heads == 0 && (c.gdn_v_heads * 128) % 256 == 0, "bad GDN head counts");
     HP_REQUIRE(c.attn_every >= 1 && c.n_slots >= 1 && c.n_slots <= MAXS && c.max_ctx >= 16 && c.n_rot % 2 == 0 && c.n_rot <= 256, "bad configuration");
     HP_REQUIRE(c.n_expert == 0 ? (c.n_ff > 0 && c.n_ff % 256 == 0) : (c.expert_ff % 256 == 0 && c.n_expert_used >= 1 && c.n_expert_used <= 15), "bad FFN shape");
@@ -177,6 +186,13 @@ int Engine::init() {
         if (c.n_expert == 0) {
             HP_TRY(gen_lin(L.gate_up, 2 * c.n_ff, E, tensor_id(il, TK_GATE_UP)));
             HP_TRY(gen_lin(L.down, E, c.n_ff, tensor_id(il, TK_DOWN)));
+        } else {   // routed experts (contiguous per tensor, qwen4exp weights layout [512*N][K]) + one shared expert + f32 router
+            const int F = c.expert_ff;
+            HP_TRY(gen_f32(&L.router, (size_t)(c.n_expert + 1) * E, tensor_id(il, TK_ROUTER), 0.f, 1.0f / sqrtf((float)E), false));
+            HP_TRY(gen_raw_q4k(L.exp_gate_up, (size_t)c.n_expert * 2 * F, E, tensor_id(il, TK_EXP_GATE_UP)));
+            HP_TRY(gen_raw_q4k(L.exp_down, (size_t)c.n_expert * E, F, tensor_id(il, TK_EXP_DOWN)));
+            HP_TRY(gen_raw_q4k(L.sh_gate_up, (size_t)2 * F, E, tensor_id(il, TK_SH_GATE_UP)));
+            HP_TRY(gen_raw_q4k(L.sh_down, (size_t)E, F, tensor_id(il, TK_SH_DOWN)));
         }
         return HP_OK;
     };
@@ -231,8 +247,19 @@ int Engine::init() {
     HP_CUDA(cudaMemsetAsync(h_, 0, (size_t)MAXR * E * 4, s_)); HP_CUDA(cudaMemsetAsync(mh_, 0, (size_t)MAXR * E * 4, s_));
     HP_TRY(alloc(&xq_.q, xq_q_bytes(MAXR, (int)kmax))); HP_TRY(alloc(&xq_.sc, xq_sc_floats(MAXR, (int)kmax) * 4));
     HP_CUDA(cudaMemsetAsync(xq_.q, 0, xq_q_bytes(MAXR, (int)kmax), s_)); HP_CUDA(cudaMemsetAsync(xq_.sc, 0, xq_sc_floats(MAXR, (int)kmax) * 4, s_));
+    if (c.n_expert) {
+        const int ns = c.n_expert_used + 1, pairs = MAXR * ns;
+        HP_TRY(alloc((void**)&xn_, (size_t)MAXR * E * 4));
+        HP_TRY(alloc((void**)&rlogits_, (size_t)MAXR * (c.n_expert + 1) * 4));
+        HP_TRY(alloc((void**)&moe_ids_, (size_t)pairs * 4)); HP_TRY(alloc((void**)&moe_w_, (size_t)pairs * 4));
+        HP_TRY(alloc((void**)&moe_gu_, (size_t)pairs * 2 * F * 4)); HP_TRY(alloc((void**)&moe_v_, (size_t)pairs * E * 4));
+        HP_TRY(alloc(&xq2_.q, xq_q_bytes(pairs, F))); HP_TRY(alloc(&xq2_.sc, xq_sc_floats(pairs, F) * 4));
+        HP_CUDA(cudaMemsetAsync(xq2_.q, 0, xq_q_bytes(pairs, F), s_)); HP_CUDA(cudaMemsetAsync(xq2_.sc, 0, xq_sc_floats(pairs, F) * 4, s_));
+        moe_out_.N = E; moe_out_.K = F; moe_out_.P = 1;
+        e_lo_ = 0; e_hi_ = c.n_expert; own_shared_ = 1;
+    }
     nsplit_max_ = (c.max_ctx + ATTN_SPLIT - 1) / ATTN_SPLIT;
-    const size_t np = attn_partial_floats(MAXR / 8 + MAXS, c.n_head_kv, nsplit_max_);
+    const size_t np = attn_partial_floats(MAXR, c.n_head_kv, nsplit_max_);
     HP_TRY(alloc((void**)&pO_, np * 256 * 4)); HP_TRY(alloc((void**)&pm_, np * 4)); HP_TRY(alloc((void**)&pl_, np * 4));
     HP_TRY(alloc((void**)&d_desc_, D_INTS * 4)); HP_CUDA(cudaMallocHost((void**)&h_desc_, D_INTS * 4)); memset(h_desc_, 0, D_INTS * 4);
     HP_TRY(alloc((void**)&d_ids_, MAXR * 4)); HP_TRY(alloc((void**)&d_mids_, MAXR * 4)); HP_TRY(alloc((void**)&d_vals_, MAXR * 4)); HP_TRY(alloc((void**)&d_mvals_, MAXR * 4));
@@ -288,10 +315,31 @@ int Engine::attn_block(const LayerW& L, uint16_t* kc, uint16_t* vc, size_t kv_st
 }
 // qwen35.cpp:278-287
 int Engine::ffn_block(const LayerW& L, int R) {
+    if (c_.n_expert) return moe_block(L, R);
     const int F = c_.n_ff;
     HP_TRY(lin(L.gate_up, big_, 2 * F, R));
     if (!gemv_only_) HP_TRY(silu_mul_quant(big_, 2 * F, F, xq_, R, s_));
     return lin_parts(L.down, R);
+}
+
+// Qwen4Exp::moe_layer (qwen4exp.cpp:345-354): router -> route -> gate|up for the k+1 slots -> silu*mul+q8 -> down + in-order combine
+int Engine::moe_block(const LayerW& L, int R) {
+    const hp_model_cfg& c = c_; const int E = c.n_embd, F = c.expert_ff, ns = c.n_expert_used + 1;
+    if (gemv_only_) return HP_OK;
+    HP_TRY(router_gemv(L.router, xn_, rlogits_, c.n_expert + 1, E, R, s_));
+    HP_TRY(moe_route(rlogits_, moe_ids_, moe_w_, R, c.n_expert, c.n_expert_used, s_));
+    MoeParams p; p.w_exp = L.exp_gate_up.w; p.w_sh = L.sh_gate_up.w; p.ebytes = (size_t)2 * F * (E / 256) * 144; p.N = 2 * F; p.K = E;
+    p.ids = moe_ids_; p.slotw = nullptr; p.nslot = ns; p.xq = xq_; p.y = moe_gu_; p.T = R; p.e_lo = e_lo_; p.e_hi = e_hi_; p.own_shared = own_shared_;
+    HP_TRY(moe_gemv_up(p, s_));
+    HP_TRY(moe_silu_quant(moe_gu_, F, moe_ids_, e_lo_, e_hi_, own_shared_, xq2_, R * ns, s_));
+    MoeParams d = p; d.w_exp = L.exp_down.w; d.w_sh = L.sh_down.w; d.ebytes = (size_t)E * (F / 256) * 144; d.N = E; d.K = F; d.xq = xq2_; d.slotw = moe_w_;
+    if (ep_world_ <= 1) { d.y = yparts_; return moe_down_combine(d, s_); }
+    // expert parallel: per-pair outputs of the experts this GPU owns (exact zeros elsewhere), exchanged, then combined in
+    // slot order on every GPU (identical arithmetic to the single-GPU combine)
+    d.y = moe_v_;
+    HP_TRY(moe_down_pairs(d, s_));
+    HP_TRY(ep_exchange(moe_v_, (size_t)R * ns * E));
+    return moe_combine(moe_v_, moe_w_, ns, yparts_, R, E, s_);
 }
 
 // qwen35.cpp:309-376
@@ -317,9 +365,9 @@ int Engine::run_pass(int R, int nseq, int ngroups) {
             HP_TRY(attn_block(L, kc_ + (size_t)ai * kv_layer_, vc_ + (size_t)ai * kv_layer_, kv_slot_, R, ngroups));
             ++ai;
         }
-        HP_TRY(norm_in(&L.out_proj, true, L.post_norm, nullptr, R));
+        HP_TRY(norm_in(&L.out_proj, true, L.post_norm, c.n_expert ? xn_ : nullptr, R));
         HP_TRY(ffn_block(L, R));
-        prev = &L.down;
+        prev = c.n_expert ? &moe_out_ : &L.down;
     }
     HP_TRY(norm_in(prev, true, output_norm_, h_, R));      // h for all rows (+ q8 of all rows), qwen35.cpp:370
     HP_TRY(lin(lm_head_, logits_, c.n_vocab, R));
@@ -364,9 +412,16 @@ int Engine::forward(const hp_slot_req* reqs, int S, float* ms) {
     for (int i = 0; i < S; ++i) {
         const hp_slot_req& r = reqs[i];
         d[D_SEQS + i * 4] = r0; d[D_SEQS + i * 4 + 1] = r.T; d[D_SEQS + i * 4 + 2] = r.slot; d[D_SEQS + i * 4 + 3] = 0;
-        d[D_GROUPS + ng * 4] = r0; d[D_GROUPS + ng * 4 + 1] = r.T; d[D_GROUPS + ng * 4 + 2] = r.slot; d[D_GROUPS + ng * 4 + 3] = r.pos;
-        for (int t = 0; t < r.T; ++t) { d[D_TOK + r0 + t] = r.tokens[t]; d[D_POS + r0 + t] = r.pos + t; d[D_SLOT + r0 + t] = r.slot; d[D_RGROUP + r0 + t] = ng; }
-        ++ng; r0 += r.T;
+        // attention row groups: rows of one slot, at most ATTN_MAX_PAIRS (row, q-head) pairs per kv head
+        const int gr = std::max(1, std::min(8, ATTN_MAX_PAIRS / (c_.n_head / c_.n_head_kv)));
+        for (int t0 = 0; t0 < r.T; t0 += gr) {
+            const int tn = std::min(gr, r.T - t0);
+            d[D_GROUPS + ng * 4] = r0 + t0; d[D_GROUPS + ng * 4 + 1] = tn; d[D_GROUPS + ng * 4 + 2] = r.slot; d[D_GROUPS + ng * 4 + 3] = r.pos + t0;
+            for (int t = t0; t < t0 + tn; ++t) d[D_RGROUP + r0 + t] = ng;
+            ++ng;
+        }
+        for (int t = 0; t < r.T; ++t) { d[D_TOK + r0 + t] = r.tokens[t]; d[D_POS + r0 + t] = r.pos + t; d[D_SLOT + r0 + t] = r.slot; }
+        r0 += r.T;
     }
     HP_CUDA(cudaEventRecord(ev0_, s_));
     HP_TRY(upload_desc());
@@ -403,9 +458,9 @@ int Engine::run_mtp(int R, int ngroups, const float* h_dev, int ldh, bool want_l
     HP_TRY(lin(eh_proj_, x_, c.n_embd, R));
     HP_TRY(norm_in(nullptr, false, mtp_.attn_norm, nullptr, R));
     HP_TRY(attn_block(mtp_, mkc_, mvc_, kv_layer_, R, ngroups));
-    HP_TRY(norm_in(&mtp_.out_proj, true, mtp_.post_norm, nullptr, R));
+    HP_TRY(norm_in(&mtp_.out_proj, true, mtp_.post_norm, c.n_expert ? xn_ : nullptr, R));
     HP_TRY(ffn_block(mtp_, R));
-    HP_TRY(norm_in(&mtp_.down, true, mtp_head_norm_, mh_, R));
+    HP_TRY(norm_in(c.n_expert ? &moe_out_ : &mtp_.down, true, mtp_head_norm_, mh_, R));
     if (want_logits) {
         HP_TRY(lin(lm_head_, mlogits_, c.n_vocab, R));
         HP_TRY(argmax_rows(mlogits_, R, c.n_vocab, c.n_vocab, d_mids_, d_mvals_, am_scratch_, s_));
@@ -416,10 +471,16 @@ int Engine::mtp_forward(const int* tokens, const float* h_dev, int T, int pos0, 
     HP_REQUIRE(c_.has_mtp, "model has no MTP block");
     HP_REQUIRE(tokens && h_dev && T >= 1 && T <= 8 && slot >= 0 && slot < c_.n_slots && pos0 >= 0 && pos0 + T <= c_.max_ctx, "bad T");   // qwen35.cpp:406
     int* d = h_desc_;
-    for (int t = 0; t < T; ++t) { d[D_TOK + t] = tokens[t]; d[D_POS + t] = pos0 + t; d[D_SLOT + t] = slot; d[D_RGROUP + t] = 0; }
-    d[D_GROUPS] = 0; d[D_GROUPS + 1] = T; d[D_GROUPS + 2] = slot; d[D_GROUPS + 3] = pos0;
+    const int gr = std::max(1, std::min(8, ATTN_MAX_PAIRS / (c_.n_head / c_.n_head_kv))); int ng = 0;
+    for (int t0 = 0; t0 < T; t0 += gr) {
+        const int tn = std::min(gr, T - t0);
+        d[D_GROUPS + ng * 4] = t0; d[D_GROUPS + ng * 4 + 1] = tn; d[D_GROUPS + ng * 4 + 2] = slot; d[D_GROUPS + ng * 4 + 3] = pos0 + t0;
+        for (int t = t0; t < t0 + tn; ++t) d[D_RGROUP + t] = ng;
+        ++ng;
+    }
+    for (int t = 0; t < T; ++t) { d[D_TOK + t] = tokens[t]; d[D_POS + t] = pos0 + t; d[D_SLOT + t] = slot; }
     HP_TRY(upload_desc());
-    HP_TRY(run_mtp(T, 1, h_dev, c_.n_embd, want_logits));
+    HP_TRY(run_mtp(T, ng, h_dev, c_.n_embd, want_logits));
     HP_CUDA(cudaStreamSynchronize(s_));
     return HP_OK;
 }
@@ -463,6 +524,11 @@ int Engine::tensor(int layer, int kind, void** ptr, size_t* bytes) const {
         case TK_SSM_NORM: return set(L.ssm_norm, 256);
         case TK_Q_NORM: return set(L.q_norm, 512);
         case TK_K_NORM: return set(L.k_norm, 512);
+        case TK_ROUTER: return set(L.router, (size_t)(c.n_expert + 1) * E * 4);
+        case TK_EXP_GATE_UP: return set(L.exp_gate_up.w, L.exp_gate_up.bytes);
+        case TK_EXP_DOWN: return set(L.exp_down.w, L.exp_down.bytes);
+        case TK_SH_GATE_UP: return set(L.sh_gate_up.w, L.sh_gate_up.bytes);
+        case TK_SH_DOWN: return set(L.sh_down.w, L.sh_down.bytes);
     }
     set_error("unknown layer tensor %d", kind); return HP_EINVAL;
 }
@@ -476,8 +542,9 @@ int Engine::gdn_state(int slot, int gdn_layer, float** ptr, size_t* bytes) {
 
 size_t Engine::pass_weight_bytes(bool mtp, bool with_head) const {
     size_t b = 0;
-    if (!mtp) for (const LayerW& L : layers_) b += L.in_proj.bytes + L.out_proj.bytes + L.gate_up.bytes + L.down.bytes;
-    else b += eh_proj_.bytes + mtp_.in_proj.bytes + mtp_.out_proj.bytes + mtp_.gate_up.bytes + mtp_.down.bytes;
+    // dense part only; routed-expert bytes depend on the routing (count the distinct (layer, expert) pairs touched)
+    if (!mtp) for (const LayerW& L : layers_) b += L.in_proj.bytes + L.out_proj.bytes + L.gate_up.bytes + L.down.bytes + L.sh_gate_up.bytes + L.sh_down.bytes;
+    else b += eh_proj_.bytes + mtp_.in_proj.bytes + mtp_.out_proj.bytes + mtp_.gate_up.bytes + mtp_.down.bytes + mtp_.sh_gate_up.bytes + mtp_.sh_down.bytes;
     if (with_head) b += lm_head_.bytes;
     return b;
 }
@@ -501,6 +568,14 @@ int Engine::profile_pass(int R, int what, int reps, float* ms) {
     if (rc != HP_OK) return rc;
     float t = 0; HP_CUDA(cudaEventElapsedTime(&t, ev0_, ev1_)); *ms = t / reps;
     return HP_OK;
+}
+
+// Expert-parallel exchange of the per-(row, slot) expert outputs. Every element of the buffer is produced by exactly one
+// GPU (the owner of that slot's expert) and is an exact zero on the others, so the result is the owner's value bit for
+// bit whatever order the library adds in: an all-gather of a permuted buffer expressed as one NCCL call.
+int Engine::ep_exchange(float* buf, size_t n) {
+    if (ep_world_ <= 1) return HP_OK;
+    return ep_allreduce(buf, n);
 }
 
 // ------------------------------------------------------------------ fused device-side round
@@ -534,6 +609,7 @@ int Engine::spec_round(int slot, int n, const int* subst, int* out_tokens, int* 
     HP_REQUIRE(c_.has_mtp, "model has no MTP block");
     HP_REQUIRE(slot == spec_slot_ && n >= 1 && n <= 7 && out_tokens && out_count, "spec_round: bad arguments (call hp_spec_begin first; 1 <= n_draft <= 7)");
     HP_REQUIRE(spec_pos_ + 2 * n + 2 <= c_.max_ctx, "spec_round: context exhausted");
+    HP_REQUIRE((n + 1) * (c_.n_head / c_.n_head_kv) <= ATTN_MAX_PAIRS, "spec_round: n_draft + 1 rows exceed one attention row group for this head geometry");
     for (int i = 0; i < 8; ++i) h_spec_[i] = (subst && i < n) ? subst[i] : -1;
     static const bool no_graph = getenv("HIPSTER_B200_NO_GRAPH") != nullptr;
     const int key = slot * 8 + n;
@@ -569,3 +645,7 @@ done:
 }
 
 }  // namespace hp
+
+namespace hp {
+int Engine::ep_allreduce(float*, size_t) { set_error("expert parallelism is not initialised"); return HP_ECOMM; }
+}

@@ -56,6 +56,7 @@ private:
     struct Desc;   // device-visible pass descriptor (see engine.cu)
     int alloc(void** p, size_t bytes);
     int gen_lin(Lin& l, int N, int K, uint64_t tid);
+    int gen_raw_q4k(Lin& l, size_t rows, int K, uint64_t tid);
     int gen_bf16(uint16_t** p, size_t n, uint64_t tid, float mean, float std);
     int gen_f32(float** p, size_t n, uint64_t tid, float mean, float std, bool neg_abs);
     int lin(const Lin& l, float* out, int ld, int R);        // GEMV; P > 1 planes are reduced into out
@@ -63,6 +64,9 @@ private:
     int norm_in(const Lin* prev, bool have_y, const uint16_t* w, float* xn, int R);
     int attn_block(const LayerW& L, uint16_t* kc, uint16_t* vc, size_t kv_stride, int R, int ngroups);
     int ffn_block(const LayerW& L, int R);
+    int moe_block(const LayerW& L, int R);
+    int ep_exchange(float* buf, size_t n);
+    int ep_allreduce(float* buf, size_t n);
     int run_pass(int R, int nseq, int ngroups);              // trunk over the rows described by desc_ (already uploaded)
     int run_mtp(int R, int ngroups, const float* h_dev, int ldh, bool want_logits);
     int upload_desc();
@@ -81,7 +85,9 @@ private:
     // work
     float *x_ = nullptr, *xn_ = nullptr, *big_ = nullptr, *act_ = nullptr, *yparts_ = nullptr, *logits_ = nullptr, *mlogits_ = nullptr, *h_ = nullptr, *mh_ = nullptr, *cat_ = nullptr, *emb_ = nullptr;
     float *pO_ = nullptr, *pm_ = nullptr, *pl_ = nullptr; int nsplit_max_ = 0;
-    XQ8F xq_{nullptr, nullptr};
+    XQ8F xq_{nullptr, nullptr}, xq2_{nullptr, nullptr};
+    float *rlogits_ = nullptr, *moe_w_ = nullptr, *moe_gu_ = nullptr, *moe_v_ = nullptr; int* moe_ids_ = nullptr; Lin moe_out_;
+    int e_lo_ = 0, e_hi_ = 0, own_shared_ = 1, ep_world_ = 1, ep_rank_ = 0; void* nccl_comm_ = nullptr;
     int *d_desc_ = nullptr, *h_desc_ = nullptr;                  // device / pinned host descriptor
     int *d_ids_ = nullptr, *d_mids_ = nullptr; float *d_vals_ = nullptr, *d_mvals_ = nullptr; void* am_scratch_ = nullptr;
     int *d_spec_ = nullptr, *h_spec_ = nullptr;                   // fused round state (device) / results (pinned host)

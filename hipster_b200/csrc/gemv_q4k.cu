@@ -113,13 +113,19 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
     for (int i = 0; i < SK_STAGES && i < nunits; ++i) issue();
 
     pdl_wait();
-    if (threadIdx.x == 0) {   // quantised activations of blocks [kb0, kb0 + nbp), all NT column tiles, by bulk copies
-        mbar_expect_tx(xbar, (uint32_t)NT * nbp * 2560u);
-        for (int n = 0; n < NT; ++n) {
-            bulk_g2s(smem_u32(smem + Geo::FIXED + n * nbp * 2048), xq + ((size_t)n * nb + kb0) * 128, nbp * 2048u, xbar);
-            bulk_g2s(smem_u32(smem + Geo::FIXED + NT * nbp * 2048 + n * nbp * 512), xsc + ((size_t)n * nb + kb0) * 32, nbp * 512u, xbar);
+#ifndef HP_DBG_NOX
+    if (warp == 0) {   // quantised activations of blocks [kb0, kb0 + nbp), all NT column tiles, by bulk copies: one block
+        // (2048 + 512 B) per copy pair, lanes in parallel, each CTA starting at a different block so that the 148 CTAs do
+        // not walk the same L2 lines in lockstep
+        if (lane == 0) mbar_expect_tx(xbar, (uint32_t)NT * nbp * 2560u);
+        __syncwarp();
+        for (int i = lane; i < NT * nbp; i += 32) {
+            const int n = i / nbp, b = (i % nbp + blockIdx.x) % nbp;
+            bulk_g2s(smem_u32(smem + Geo::FIXED + (n * nbp + b) * 2048), xq + ((size_t)n * nb + kb0 + b) * 128, 2048u, xbar);
+            bulk_g2s(smem_u32(smem + Geo::FIXED + NT * nbp * 2048 + (n * nbp + b) * 512), xsc + ((size_t)n * nb + kb0 + b) * 32, 512u, xbar);
         }
     }
+#endif
 
     float2 acc[NT][2];   // [n][0] = row g, cols 2t,2t+1 ; [n][1] = row g+8
     auto zero_acc = [&]() {
@@ -162,7 +168,11 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
 
     int cur_tile = first_tile, chunk = nunits ? u0 % C : 0;
     bool cur_from_start = chunk == 0;
+#ifndef HP_DBG_NOX
     bool ok = mbar_wait(xbar, 0, err);
+#else
+    bool ok = true;
+#endif
     for (int i = 0; i < nunits && ok; ++i) {
         const int s = i % SK_STAGES;
         ok = mbar_wait(bar0 + 8 * s, (i / SK_STAGES) & 1, err);
@@ -170,6 +180,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
         const uint8_t* st = ring + s * Geo::STAGE_BYTES;
         const uint4* xqp = xq_s + (chunk * CB) * 128 + lane;
         const float4* xsp = xsc_s + (chunk * CB) * 32 + t;
+#ifndef HP_DBG_NOCOMPUTE
 #pragma unroll
         for (int blk = 0; blk < CB; ++blk) {
             {   // scale pre-pass: lane -> (row = lane/2, half = lane&1) decodes sub-blocks 4hf..4hf+3 of its row
@@ -221,6 +232,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
             }
             __syncwarp();
         }
+#endif
         if (it_i < nunits) issue();
         if (++chunk == C) {
             flush(cur_tile, cur_from_start);
@@ -230,6 +242,9 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
             flush(cur_tile, false);
         }
     }
+#ifdef HP_DBG_NOFLUSH
+    return;
+#endif
     // ---------------- tiles shared by several warps of this CTA: combine through shared memory in warp order
     __syncthreads();   // every ring is drained: its memory becomes the exchange buffer [warp][slot][NT*4][32]
 #pragma unroll
@@ -247,17 +262,23 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
         const int tile = part_tile[sl], tl = tile - ct.t0;
         if ((tl + 1) * C > u1) continue;                     // the tile ends in a later warp: that warp finishes it
         const int w_first = gemv_warp_owner(cu, weff, tl * C);
+        // exchange-buffer rows of the contributors (slot 0 when the tile is the contributor's first tile)
+        int src[GEMV_WARPS];
+#pragma unroll
+        for (int ww = 0; ww < GEMV_WARPS; ++ww)
+            src[ww] = (ww >= w_first && ww <= warp) ? (ww * 2 + ((gemv_warp_start(cu, weff, ww) / C == tl) ? 0 : 1)) * NT * 4 : -1;
         float v[NT][4];
 #pragma unroll
         for (int n = 0; n < NT; ++n)
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 float a = 0.f;
-                for (int ww = w_first; ww <= warp; ++ww) {
-                    const int wsl = (gemv_warp_start(cu, weff, ww) / C == tl) ? 0 : 1;
-                    const float pv = red[((ww * 2 + wsl) * NT * 4 + n * 4 + k) * 32 + lane];
-                    a = ww == w_first ? pv : a + pv;
-                }
+#pragma unroll
+                for (int ww = 0; ww < GEMV_WARPS; ++ww)
+                    if (src[ww] >= 0) {
+                        const float pv = red[(src[ww] + n * 4 + k) * 32 + lane];
+                        a = ww == w_first ? pv : a + pv;
+                    }
                 v[n][k] = a;
             }
         store_tile(tile, v);

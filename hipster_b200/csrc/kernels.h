@@ -45,8 +45,9 @@ __host__ __device__ inline GemvCta gemv_cta(int N, int nb, int P, int c) {
     GemvCta r; r.part = c / gc; r.t0 = (int)((long long)cg * tiles / gc); r.t1 = (int)((long long)(cg + 1) * tiles / gc); return r;
 }
 // inside a CTA the cu units are split evenly and contiguously over weff = min(12, cu) warps
-__host__ __device__ inline int gemv_warp_start(int cu, int weff, int w) { return (int)((long long)w * cu / weff); }
-__host__ __device__ inline int gemv_warp_owner(int cu, int weff, int u) { return (int)((((long long)u + 1) * weff - 1) / cu); }
+// (cu < 2^20 units per CTA, so 32-bit arithmetic is exact)
+__host__ __device__ inline int gemv_warp_start(int cu, int weff, int w) { return (int)((unsigned)w * (unsigned)cu / (unsigned)weff); }
+__host__ __device__ inline int gemv_warp_owner(int cu, int weff, int u) { return (int)((((unsigned)u + 1u) * (unsigned)weff - 1u) / (unsigned)cu); }
 // scratch for the K-part planes of the public (single-output) entry point
 struct GemvWorkspace { float* part; size_t part_bytes; int* err; };
 int gemv_parts(int N, int K);
@@ -93,6 +94,21 @@ size_t attn_smem_bytes();
 size_t attn_partial_floats(int ngroups, int n_kv, int nsplit_max);
 int attn_rope_kv(const AttnParams& p, int rows, cudaStream_t s);          // reference k_qk_norm_rope_kv (ops.hip:363-411)
 int attn_decode(const AttnParams& p, int rows, int ngroups, cudaStream_t s);   // reference attn_decode_mq (ops.h:72)
+
+// ---- moe.cu ----
+int router_gemv(const float* W, const float* x, float* y, int N, int K, int T, cudaStream_t s);          // reference f32_gemv (fn.hip:252-277)
+int moe_route(const float* logits, int* ids, float* w, int T, int E, int k, cudaStream_t s);                // reference k_moe_route (fn.hip:167-205)
+struct MoeParams {
+    const void* w_exp; const void* w_sh; size_t ebytes; int N, K;   // expert matrices [E][N][K/256 blocks] and the shared expert's [N][K/256]
+    const int* ids; const float* slotw; int nslot;                    // [T][nslot] expert ids (-1 = shared) and combine weights
+    XQ8F xq; float* y; int T;
+    int e_lo, e_hi, own_shared;                                        // routed experts owned by this GPU, and whether it computes the shared slot
+};
+int moe_gemv_up(const MoeParams& p, cudaStream_t s);                  // reference gemv_moe, xrow_te = false (gemv.h:46)
+int moe_silu_quant(const float* gu, int F, const int* ids, int e_lo, int e_hi, int own_shared, XQ8F xq, int pairs, cudaStream_t s);   // fn.hip:206-211
+int moe_down_combine(const MoeParams& p, cudaStream_t s);             // reference gemv_moe with slotw (gemv.hip:1095-1114)
+int moe_down_pairs(const MoeParams& p, cudaStream_t s);               // expert-parallel form: per-pair outputs, zeros for experts owned elsewhere
+int moe_combine(const float* v, const float* slotw, int nslot, float* y, int T, int N, cudaStream_t s);
 
 // ---- argmax.cu ----
 // per-row argmax (max value, lowest index) of logits [R][ld] -> ids/vals on device

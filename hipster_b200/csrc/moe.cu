@@ -1,0 +1,260 @@
+// Mixture-of-experts FFN of the Flash-Next-shaped model: exact f32 router GEMV, softmax top-k routing with a shared
+// expert slot, grouped routed-expert GEMV (gate|up), SiLU-gated product + quantisation per (row, slot), and the
+// down-projection with the in-order weighted combine (no atomics: deterministic and independent of the row count).
+//
+// Reference: k_f32_gemv (engine/kernels/fn.hip:252-266), k_moe_route (fn.hip:167-205), k_moe_silu_quant (fn.hip:206-211),
+// k_gemv_moe / k_gemv_moe_down (engine/kernels/gemv.hip:1075-1129), Qwen4Exp::moe_layer (engine/src/qwen4exp.cpp:345-354).
+//
+// Expert GEMV numerics: exact int32 dot per 32-element sub-block (int8 tensor-core tile), one fp32 update per sub-block,
+// blocks in order along K, no split: acc = fmaf((d*sc)*xd, idot, acc); acc = fmaf(-(dmin*mn), xs, acc).
+#include "hp_common.cuh"
+#include "kernels.h"
+
+namespace hp {
+namespace {
+
+// ---- router: logits[t][e] = sum_k W[e][k] x[t][k], f32. One warp per weight row; lane l takes k = 4l + 128 i (float4),
+// four fmaf per step in element order, then the xor-shuffle tree (offsets 16..1). ----
+__global__ void __launch_bounds__(256) k_router_gemv(const float* __restrict__ W, const float* __restrict__ x, float* __restrict__ y, int N, int K, int T) {
+    const int n = (blockIdx.x * 256 + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (n >= N) return;
+    const float* w = W + (size_t)n * K;
+    for (int t = 0; t < T; ++t) {
+        const float* xr = x + (size_t)t * K;
+        float acc = 0.f;
+        for (int i = lane * 4; i < K; i += 128) {
+            const float4 a = *reinterpret_cast<const float4*>(w + i), b = *reinterpret_cast<const float4*>(xr + i);
+            acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc); acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) acc = acc + __shfl_xor_sync(0xffffffffu, acc, off);
+        if (lane == 0) y[(size_t)t * N + n] = acc;
+    }
+}
+
+// ---- routing: softmax over the first E logits, top-k by (value desc, index asc), weights renormalised by the sum of the
+// selected probabilities taken in rank order; slot k = shared expert (id -1) with weight sigmoid(logit[E]). ----
+__device__ __forceinline__ void better(float& bv, int& bi, float v, int i) { if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; } }
+__global__ void __launch_bounds__(1024) k_moe_route(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ w, int E, int k) {
+    __shared__ float sh[32]; __shared__ int shi[32]; __shared__ float selp[16]; __shared__ int seli[16];
+    const int t = blockIdx.x, i = threadIdx.x, warp = i >> 5, lane = i & 31;
+    const float v = i < E ? logits[(size_t)t * (E + 1) + i] : -INFINITY;
+    float mx = v;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    if (lane == 0) sh[warp] = mx;
+    __syncthreads();
+    mx = sh[0]; for (int q = 1; q < 32; ++q) mx = fmaxf(mx, sh[q]);
+    __syncthreads();
+    const float e = i < E ? expf_det(v - mx) : 0.f;
+    float s = e;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) s = s + __shfl_xor_sync(0xffffffffu, s, off);
+    if (lane == 0) sh[warp] = s;
+    __syncthreads();
+    float sum = sh[0]; for (int q = 1; q < 32; ++q) sum = sum + sh[q];
+    __syncthreads();
+    float p = i < E ? e / sum : -2.f;
+    for (int r = 0; r < k; ++r) {
+        float bv = p; int bi = i;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) { const float ov = __shfl_xor_sync(0xffffffffu, bv, off); const int oi = __shfl_xor_sync(0xffffffffu, bi, off); better(bv, bi, ov, oi); }
+        if (lane == 0) { sh[warp] = bv; shi[warp] = bi; }
+        __syncthreads();
+        if (warp == 0) {
+            bv = sh[lane]; bi = shi[lane];
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) { const float ov = __shfl_xor_sync(0xffffffffu, bv, off); const int oi = __shfl_xor_sync(0xffffffffu, bi, off); better(bv, bi, ov, oi); }
+            if (lane == 0) { selp[r] = bv; seli[r] = bi; }
+        }
+        __syncthreads();
+        if (i == seli[r]) p = -1.f;
+        __syncthreads();
+    }
+    if (i == 0) {
+        float wsum = 0.f; for (int r = 0; r < k; ++r) wsum = wsum + selp[r];
+        for (int r = 0; r < k; ++r) { ids[t * (k + 1) + r] = seli[r]; w[t * (k + 1) + r] = selp[r] / wsum; }
+        ids[t * (k + 1) + k] = -1; w[t * (k + 1) + k] = sigmoid_det(logits[(size_t)t * (E + 1) + E]);
+    }
+}
+
+// ---- one 16-row tile of an expert matrix against one activation row: blocks in order, weights read straight from
+// global memory (each expert tile is touched once). Returns the column of interest in out[0..1] (rows g, g+8). ----
+__device__ __forceinline__ void expert_tile(const uint8_t* __restrict__ W, int row_bytes, int nb, const uint4* __restrict__ xq, const float4* __restrict__ xsc,
+                                            int xtile, int xcol, float4* scr, int lane, float& r0, float& r1) {
+    const int g = lane >> 2, t = lane & 3, hf = lane & 1;
+    float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+    const uint8_t* hrow = W + (size_t)(lane >> 1) * row_bytes;
+    const uint8_t* w0p = W + (size_t)g * row_bytes + 16 + 8 * t;
+    const uint8_t* w1p = W + (size_t)(g + 8) * row_bytes + 16 + 8 * t;
+    for (int b = 0; b < nb; ++b) {
+        {
+            const uint4 hdr = __ldg(reinterpret_cast<const uint4*>(hrow + (size_t)b * 144));
+            const float d = h2f((uint16_t)(hdr.x & 0xFFFF)), nd = -h2f((uint16_t)(hdr.x >> 16));
+            const uint32_t scv = hf ? ((hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u)) : (hdr.y & 0x3F3F3F3Fu);
+            const uint32_t mnv = hf ? (((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u)) : (hdr.z & 0x3F3F3F3Fu);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                float s0 = d * (float)((scv >> (8 * k)) & 0xFFu);
+                if (k & 1) s0 = s0 * 0.0625f;
+                const float nm = nd * (float)((mnv >> (8 * k)) & 0xFFu);
+                scr[(4 * hf + k) * 16 + (lane >> 1)] = make_float4(s0, s0, nm, nm);
+            }
+        }
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint2 w0 = __ldg(reinterpret_cast<const uint2*>(w0p + (size_t)b * 144 + 32 * j));
+            const uint2 w1 = __ldg(reinterpret_cast<const uint2*>(w1p + (size_t)b * 144 + 32 * j));
+            const uint32_t alo[4] = {w0.x & 0x0F0F0F0Fu, w1.x & 0x0F0F0F0Fu, w0.y & 0x0F0F0F0Fu, w1.y & 0x0F0F0F0Fu};
+            const uint32_t ahi[4] = {w0.x & 0xF0F0F0F0u, w1.x & 0xF0F0F0F0u, w0.y & 0xF0F0F0F0u, w1.y & 0xF0F0F0F0u};
+            const float4 sa0 = scr[(2 * j) * 16 + g], sb0 = scr[(2 * j) * 16 + g + 8], sa1 = scr[(2 * j + 1) * 16 + g], sb1 = scr[(2 * j + 1) * 16 + g + 8];
+            const uint4 xf = __ldg(xq + ((size_t)xtile * nb * 4 + b * 4 + j) * 32 + lane);
+            const float4 x0 = __ldg(xsc + ((size_t)xtile * nb * 8 + b * 8 + 2 * j) * 4 + t), x1 = __ldg(xsc + ((size_t)xtile * nb * 8 + b * 8 + 2 * j + 1) * 4 + t);
+            int c0[4], c1[4];
+            asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                         : "=r"(c0[0]), "=r"(c0[1]), "=r"(c0[2]), "=r"(c0[3]) : "r"(alo[0]), "r"(alo[1]), "r"(alo[2]), "r"(alo[3]), "r"(xf.x), "r"(xf.y), "r"(0));
+            asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                         : "=r"(c1[0]), "=r"(c1[1]), "=r"(c1[2]), "=r"(c1[3]) : "r"(ahi[0]), "r"(ahi[1]), "r"(ahi[2]), "r"(ahi[3]), "r"(xf.z), "r"(xf.w), "r"(0));
+            // columns 2t, 2t+1 of the activation tile; only column xcol is kept at the end
+            acc0.x = fmaf(sa0.x * x0.x, (float)c0[0], acc0.x); acc0.x = fmaf(sa0.z, x0.z, acc0.x);
+            acc0.y = fmaf(sa0.x * x0.y, (float)c0[1], acc0.y); acc0.y = fmaf(sa0.z, x0.w, acc0.y);
+            acc1.x = fmaf(sb0.x * x0.x, (float)c0[2], acc1.x); acc1.x = fmaf(sb0.z, x0.z, acc1.x);
+            acc1.y = fmaf(sb0.x * x0.y, (float)c0[3], acc1.y); acc1.y = fmaf(sb0.z, x0.w, acc1.y);
+            acc0.x = fmaf(sa1.x * x1.x, (float)c1[0], acc0.x); acc0.x = fmaf(sa1.z, x1.z, acc0.x);
+            acc0.y = fmaf(sa1.x * x1.y, (float)c1[1], acc0.y); acc0.y = fmaf(sa1.z, x1.w, acc0.y);
+            acc1.x = fmaf(sb1.x * x1.x, (float)c1[2], acc1.x); acc1.x = fmaf(sb1.z, x1.z, acc1.x);
+            acc1.y = fmaf(sb1.x * x1.y, (float)c1[3], acc1.y); acc1.y = fmaf(sb1.z, x1.w, acc1.y);
+        }
+        __syncwarp();
+    }
+    // hand column xcol to every lane of its row group: it lives in lane (g, xcol/2), component xcol & 1
+    const float m0 = (xcol & 1) ? acc0.y : acc0.x, m1 = (xcol & 1) ? acc1.y : acc1.x;
+    r0 = __shfl_sync(0xffffffffu, m0, (lane & ~3) | (xcol >> 1));
+    r1 = __shfl_sync(0xffffffffu, m1, (lane & ~3) | (xcol >> 1));
+}
+
+struct MoeArgs {
+    const uint8_t* w_exp; const uint8_t* w_sh; size_t ebytes; int N, K;     // expert matrices [E][N][K/256 blocks], shared [N][K/256]
+    const int* ids; const float* slotw; int nslot;                           // [T][nslot]
+    const uint4* xq; const float4* xsc;                                      // quantised activations (rows = T, or T*nslot for the down projection)
+    float* y; int T;
+    int e_lo, e_hi, own_shared;                                              // routed experts owned by this GPU [e_lo, e_hi) and whether it computes the shared slot
+};
+__device__ __forceinline__ bool moe_owned(const MoeArgs& a, int id) { return id >= 0 ? (id >= a.e_lo && id < a.e_hi) : a.own_shared != 0; }
+// gate|up: y[(t,e)][N] = W[ids[t,e]] . x[t]; one warp per (pair, 16-row tile)
+__global__ void __launch_bounds__(256) k_moe_gemv(MoeArgs a) {
+    __shared__ float4 scr_all[8][128];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles = a.N / 16, unit = blockIdx.x * 8 + warp;
+    if (unit >= a.T * a.nslot * tiles) return;
+    const int pair = unit / tiles, tile = unit % tiles, t = pair / a.nslot;
+    const int id = a.ids[pair];
+    if (!moe_owned(a, id)) return;                                           // expert lives on another GPU
+    const int nb = a.K / 256, row_bytes = nb * 144;
+    const uint8_t* W = (id >= 0 ? a.w_exp + (size_t)id * a.ebytes : a.w_sh) + (size_t)tile * 16 * row_bytes;
+    float r0, r1;
+    expert_tile(W, row_bytes, nb, a.xq, a.xsc, t >> 3, t & 7, scr_all[warp], lane, r0, r1);
+    const int g = lane >> 2;
+    if ((lane & 3) == 0) { a.y[(size_t)pair * a.N + tile * 16 + g] = r0; a.y[(size_t)pair * a.N + tile * 16 + g + 8] = r1; }
+}
+// per-pair expert output of the down projection: v[(t,e)][N] = W_down[ids[t,e]] . act[(t,e)] (expert-parallel form)
+__global__ void __launch_bounds__(256) k_moe_down_pairs(MoeArgs a) {
+    __shared__ float4 scr_all[8][128];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles = a.N / 16, unit = blockIdx.x * 8 + warp;
+    if (unit >= a.T * a.nslot * tiles) return;
+    const int pair = unit / tiles, tile = unit % tiles;
+    const int id = a.ids[pair];
+    const int g = lane >> 2;
+    if (!moe_owned(a, id)) {   // not ours: contribute exact zeros to the exchange buffer
+        if ((lane & 3) == 0) { a.y[(size_t)pair * a.N + tile * 16 + g] = 0.f; a.y[(size_t)pair * a.N + tile * 16 + g + 8] = 0.f; }
+        return;
+    }
+    const int nb = a.K / 256, row_bytes = nb * 144;
+    const uint8_t* W = (id >= 0 ? a.w_exp + (size_t)id * a.ebytes : a.w_sh) + (size_t)tile * 16 * row_bytes;
+    float r0, r1;
+    expert_tile(W, row_bytes, nb, a.xq, a.xsc, pair >> 3, pair & 7, scr_all[warp], lane, r0, r1);
+    if ((lane & 3) == 0) { a.y[(size_t)pair * a.N + tile * 16 + g] = r0; a.y[(size_t)pair * a.N + tile * 16 + g + 8] = r1; }
+}
+// down + combine: y[t][row] = sum_e slotw[t,e] * (W_down[ids[t,e]] . act[(t,e)]) in slot order (gemv.hip:1104-1112)
+__global__ void __launch_bounds__(256) k_moe_down(MoeArgs a) {
+    __shared__ float4 scr_all[8][128];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles = a.N / 16, unit = blockIdx.x * 8 + warp;
+    if (unit >= a.T * tiles) return;
+    const int t = unit / tiles, tile = unit % tiles;
+    const int nb = a.K / 256, row_bytes = nb * 144;
+    float acc0 = 0.f, acc1 = 0.f;
+    for (int e = 0; e < a.nslot; ++e) {
+        const int pair = t * a.nslot + e, id = a.ids[pair];
+        const uint8_t* W = (id >= 0 ? a.w_exp + (size_t)id * a.ebytes : a.w_sh) + (size_t)tile * 16 * row_bytes;
+        float r0, r1;
+        expert_tile(W, row_bytes, nb, a.xq, a.xsc, pair >> 3, pair & 7, scr_all[warp], lane, r0, r1);
+        const float w = a.slotw[pair];
+        acc0 = fmaf(w, r0, acc0); acc1 = fmaf(w, r1, acc1);
+    }
+    const int g = lane >> 2;
+    if ((lane & 3) == 0) { a.y[(size_t)t * a.N + tile * 16 + g] = acc0; a.y[(size_t)t * a.N + tile * 16 + g + 8] = acc1; }
+}
+// combine of exchanged per-pair outputs (expert-parallel): y[t][n] = sum_e slotw[t,e] * v[(t,e)][n], slot order
+__global__ void __launch_bounds__(256) k_moe_combine(const float* __restrict__ v, const float* __restrict__ slotw, int nslot, float* __restrict__ y, int N) {
+    const int t = blockIdx.y, n = blockIdx.x * 256 + threadIdx.x; if (n >= N) return;
+    float acc = 0.f;
+    for (int e = 0; e < nslot; ++e) acc = fmaf(slotw[t * nslot + e], v[(size_t)(t * nslot + e) * N + n], acc);
+    y[(size_t)t * N + n] = acc;
+}
+// q8(silu(g) * u) per (t,e) row: gu [pairs][2F] (fn.hip:206-211); pairs of experts that live elsewhere are skipped
+__global__ void __launch_bounds__(256) k_moe_silu_quant(const float* __restrict__ gu, int F, const int* __restrict__ ids, int e_lo, int e_hi, int own_shared, int8_t* __restrict__ q, float* __restrict__ sc) {
+    const int pair = blockIdx.y, sb = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (sb * 32 >= F) return;
+    const int id = ids[pair]; if (id >= 0 ? (id < e_lo || id >= e_hi) : !own_shared) return;
+    const int i = sb * 32 + lane;
+    warp_quant32_store(silu_det(gu[(size_t)pair * 2 * F + i]) * gu[(size_t)pair * 2 * F + F + i], pair, sb, F, q, sc, lane);
+}
+
+}  // namespace
+
+int router_gemv(const float* W, const float* x, float* y, int N, int K, int T, cudaStream_t s) {
+    HP_REQUIRE(N >= 1 && K > 0 && K % 128 == 0 && T >= 1, "router_gemv: bad shape N=%d K=%d T=%d", N, K, T);
+    k_router_gemv<<<(N * 32 + 255) / 256, 256, 0, s>>>(W, x, y, N, K, T);
+    HP_CUDA(cudaGetLastError()); return HP_OK;
+}
+int moe_route(const float* logits, int* ids, float* w, int T, int E, int k, cudaStream_t s) {
+    HP_REQUIRE(T >= 1 && E >= 1 && E <= 1024 && k >= 1 && k <= 15 && k <= E, "moe_route: bad shape E=%d k=%d", E, k);
+    k_moe_route<<<T, 1024, 0, s>>>(logits, ids, w, E, k);
+    HP_CUDA(cudaGetLastError()); return HP_OK;
+}
+static MoeArgs moe_args(const MoeParams& p) {
+    MoeArgs a; a.w_exp = (const uint8_t*)p.w_exp; a.w_sh = (const uint8_t*)p.w_sh; a.ebytes = p.ebytes; a.N = p.N; a.K = p.K; a.ids = p.ids; a.slotw = p.slotw; a.nslot = p.nslot;
+    a.xq = (const uint4*)p.xq.q; a.xsc = (const float4*)p.xq.sc; a.y = p.y; a.T = p.T; a.e_lo = p.e_lo; a.e_hi = p.e_hi; a.own_shared = p.own_shared; return a;
+}
+int moe_gemv_up(const MoeParams& p, cudaStream_t s) {
+    HP_REQUIRE(p.N % 16 == 0 && p.K % 256 == 0 && p.T >= 1 && p.nslot >= 1, "moe_gemv_up: bad shape");
+    const int units = p.T * p.nslot * (p.N / 16);
+    k_moe_gemv<<<(units + 7) / 8, 256, 0, s>>>(moe_args(p));
+    HP_CUDA(cudaGetLastError()); return HP_OK;
+}
+int moe_silu_quant(const float* gu, int F, const int* ids, int e_lo, int e_hi, int own_shared, XQ8F xq, int pairs, cudaStream_t s) {
+    HP_REQUIRE(F % 64 == 0 && pairs >= 1, "moe_silu_quant: bad shape");
+    k_moe_silu_quant<<<dim3((F / 32 + 7) / 8, pairs), 256, 0, s>>>(gu, F, ids, e_lo, e_hi, own_shared, (int8_t*)xq.q, (float*)xq.sc);
+    HP_CUDA(cudaGetLastError()); return HP_OK;
+}
+int moe_down_combine(const MoeParams& p, cudaStream_t s) {
+    HP_REQUIRE(p.N % 16 == 0 && p.K % 256 == 0 && p.T >= 1 && p.nslot >= 1 && p.slotw, "moe_down_combine: bad shape");
+    const int units = p.T * (p.N / 16);
+    k_moe_down<<<(units + 7) / 8, 256, 0, s>>>(moe_args(p));
+    HP_CUDA(cudaGetLastError()); return HP_OK;
+}
+int moe_down_pairs(const MoeParams& p, cudaStream_t s) {
+    HP_REQUIRE(p.N % 16 == 0 && p.K % 256 == 0 && p.T >= 1 && p.nslot >= 1, "moe_down_pairs: bad shape");
+    const int units = p.T * p.nslot * (p.N / 16);
+    k_moe_down_pairs<<<(units + 7) / 8, 256, 0, s>>>(moe_args(p));
+    HP_CUDA(cudaGetLastError()); return HP_OK;
+}
+int moe_combine(const float* v, const float* slotw, int nslot, float* y, int T, int N, cudaStream_t s) {
+    k_moe_combine<<<dim3((N + 255) / 256, T), 256, 0, s>>>(v, slotw, nslot, y, N);
+    HP_CUDA(cudaGetLastError()); return HP_OK;
+}
+
+}  // namespace hp

@@ -228,6 +228,63 @@ extern "C" void orc_attn_row(float* qkv, int n_head, int n_kv, int n_rot, const 
     }
 }
 
+// ---------------------------------------------------------------- mixture of experts
+// fn.hip:252-266: one 32-lane worker group per weight row; lane l takes k = 4l + 128i, four fmaf per step, xor tree.
+extern "C" void orc_router_gemv(const float* W, const float* x, float* y, int N, int K, int T) {
+    for (int t = 0; t < T; ++t)
+        for (int n = 0; n < N; ++n) {
+            float a[32], b[32];
+            for (int l = 0; l < 32; ++l) {
+                float acc = 0.f;
+                for (int i = l * 4; i < K; i += 128) for (int e = 0; e < 4; ++e) acc = fmaf(W[(size_t)n * K + i + e], x[(size_t)t * K + i + e], acc);
+                a[l] = acc;
+            }
+            for (int off = 16; off > 0; off >>= 1) { for (int l = 0; l < 32; ++l) b[l] = a[l] + a[l ^ off]; memcpy(a, b, sizeof a); }
+            y[(size_t)t * N + n] = a[0];
+        }
+}
+// fn.hip:167-205: softmax over E logits, top-k (value desc, index asc), renormalise by the sum of the selected
+// probabilities in rank order; slot k = shared expert, id -1, weight sigmoid(logit[E]). Arrays [T][k+1].
+extern "C" void orc_moe_route(const float* logits, int* ids, float* w, int T, int E, int k) {
+    std::vector<float> p(E); float part[1024];
+    for (int t = 0; t < T; ++t) {
+        const float* lg = logits + (size_t)t * (E + 1);
+        float mx = -INFINITY; for (int i = 0; i < E; ++i) mx = fmaxf(mx, lg[i]);
+        for (int i = 0; i < 1024; ++i) part[i] = i < E ? orc_expf(lg[i] - mx) : 0.f;
+        const float sum = det_block_sum(part, 1024);
+        for (int i = 0; i < E; ++i) p[i] = part[i] / sum;
+        float wsum = 0.f; float sel[16];
+        for (int r = 0; r < k; ++r) {
+            int bi = 0; float bv = p[0];
+            for (int i = 1; i < E; ++i) if (p[i] > bv) { bv = p[i]; bi = i; }
+            ids[t * (k + 1) + r] = bi; sel[r] = bv; p[bi] = -1.f; wsum = wsum + bv;
+        }
+        for (int r = 0; r < k; ++r) w[t * (k + 1) + r] = sel[r] / wsum;
+        ids[t * (k + 1) + k] = -1; w[t * (k + 1) + k] = orc_sigmoid(lg[E]);
+    }
+}
+// gemv.hip:1075-1114 numerics for one activation row against one expert matrix: blocks in order, no split.
+extern "C" void orc_gemv_q4k_q8_seq(const uint8_t* W, const int8_t* q, const float* xd, const float* xs, float* y, int N, int K) {
+    const int nb = K / 256;
+#pragma omp parallel for schedule(static)
+    for (int row = 0; row < N; ++row) {
+        const uint8_t* wrow = W + (size_t)row * nb * 144; float acc = 0.f;
+        for (int b = 0; b < nb; ++b) {
+            const uint8_t* bp = wrow + (size_t)b * 144;
+            uint16_t dh, mh; memcpy(&dh, bp, 2); memcpy(&mh, bp + 2, 2);
+            const float d = orc_f16_to_f32(dh), dmin = orc_f16_to_f32(mh);
+            uint8_t sc[8], mn[8]; orc_q4k_scale_min(bp + 4, sc, mn);
+            for (int sb = 0; sb < 8; ++sb) {
+                const int grp = sb >> 1, hi = sb & 1; const uint8_t* qs = bp + 16 + 32 * grp; const int8_t* xe = q + (size_t)b * 256 + 32 * sb;
+                int idot = 0; for (int e = 0; e < 32; ++e) idot += (int)(hi ? (qs[e] >> 4) : (qs[e] & 0xF)) * (int)xe[e];
+                acc = fmaf((d * (float)sc[sb]) * xd[b * 8 + sb], (float)idot, acc);
+                acc = fmaf(-(dmin * (float)mn[sb]), xs[b * 8 + sb], acc);
+            }
+        }
+        y[row] = acc;
+    }
+}
+
 // ---------------------------------------------------------------- engine (engine/src/qwen35.cpp restated on the CPU)
 struct OrcCfg {   // mirrors hp_model_cfg field for field
     int n_embd, n_layer, n_ff, n_vocab, n_head, n_head_kv, n_rot, gdn_qk_heads, gdn_v_heads, attn_every, max_ctx, n_slots;
@@ -238,8 +295,10 @@ struct OLin { std::vector<uint8_t> w; int N = 0, K = 0; };
 struct OLayer {
     bool is_attn = false; std::vector<uint16_t> attn_norm, post_norm, dt_bias, a_neg, ssm_norm, q_norm, k_norm; std::vector<float> conv_w;
     OLin in_proj, out_proj, gate_up, down;
+    std::vector<float> router; OLin exp_gate_up, exp_down, sh_gate_up, sh_down;
 };
 enum { TK_ATTN_NORM = 0, TK_POST_NORM, TK_IN_PROJ, TK_OUT_PROJ, TK_GATE_UP, TK_DOWN, TK_CONV_W, TK_DT_BIAS, TK_A_NEG, TK_SSM_NORM, TK_Q_NORM, TK_K_NORM,
+       TK_ROUTER, TK_EXP_GATE_UP, TK_EXP_DOWN, TK_SH_GATE_UP, TK_SH_DOWN,
        TK_EMBED = 32, TK_OUTPUT_NORM, TK_LM_HEAD, TK_MTP_ENORM, TK_MTP_HNORM, TK_MTP_EH_PROJ, TK_MTP_HEAD_NORM };
 inline uint64_t tensor_id(int layer, int kind) { return (uint64_t)(layer + 1) * 64 + (uint64_t)kind; }
 }
@@ -268,8 +327,17 @@ struct OrcModel {
             gen_bf16(L.dt_bias, nv, c.seed, tensor_id(il, TK_DT_BIAS), 0.f, 0.5f); gen_bf16(L.a_neg, nv, c.seed, tensor_id(il, TK_A_NEG), -0.8f, 0.4f);
             gen_bf16(L.ssm_norm, 128, c.seed, tensor_id(il, TK_SSM_NORM), 1.f, 0.3f);
         }
-        L.gate_up.N = 2 * c.n_ff; L.gate_up.K = E; gen_q4k(L.gate_up.w, 2 * c.n_ff, E, c.seed, tensor_id(il, TK_GATE_UP));
-        L.down.N = E; L.down.K = c.n_ff; gen_q4k(L.down.w, E, c.n_ff, c.seed, tensor_id(il, TK_DOWN));
+        if (c.n_expert == 0) {
+            L.gate_up.N = 2 * c.n_ff; L.gate_up.K = E; gen_q4k(L.gate_up.w, 2 * c.n_ff, E, c.seed, tensor_id(il, TK_GATE_UP));
+            L.down.N = E; L.down.K = c.n_ff; gen_q4k(L.down.w, E, c.n_ff, c.seed, tensor_id(il, TK_DOWN));
+        } else {
+            const int F = c.expert_ff;
+            gen_f32(L.router, (size_t)(c.n_expert + 1) * E, c.seed, tensor_id(il, TK_ROUTER), 0.f, 1.0f / sqrtf((float)E), false);
+            L.exp_gate_up.N = c.n_expert * 2 * F; L.exp_gate_up.K = E; gen_q4k(L.exp_gate_up.w, c.n_expert * 2 * F, E, c.seed, tensor_id(il, TK_EXP_GATE_UP));
+            L.exp_down.N = c.n_expert * E; L.exp_down.K = F; gen_q4k(L.exp_down.w, c.n_expert * E, F, c.seed, tensor_id(il, TK_EXP_DOWN));
+            L.sh_gate_up.N = 2 * F; L.sh_gate_up.K = E; gen_q4k(L.sh_gate_up.w, 2 * F, E, c.seed, tensor_id(il, TK_SH_GATE_UP));
+            L.sh_down.N = E; L.sh_down.K = F; gen_q4k(L.sh_down.w, E, F, c.seed, tensor_id(il, TK_SH_DOWN));
+        }
     }
     explicit OrcModel(const OrcCfg& cfg) : c(cfg) {
         const int E = c.n_embd, nv = c.gdn_v_heads, nq = c.gdn_qk_heads;
@@ -318,6 +386,30 @@ struct OrcModel {
         y.assign((size_t)R * c.n_embd, 0.f); gemv(L.out_proj, xq, y.data(), R, c.n_embd);
     }
     // qwen35.cpp:278-287
+    // Qwen4Exp::moe_layer (qwen4exp.cpp:345-354); xn = the normalised f32 rows the router reads
+    void moe_block(const OLayer& L, XQ& xq, const std::vector<float>& xn, int R, std::vector<float>& y) {
+        const int E = c.n_embd, F = c.expert_ff, ns = c.n_expert_used + 1, nb = E / 256, nsb = E / 32;
+        std::vector<float> lg((size_t)R * (c.n_expert + 1)), w((size_t)R * ns); std::vector<int> ids((size_t)R * ns);
+        orc_router_gemv(L.router.data(), xn.data(), lg.data(), c.n_expert + 1, E, R);
+        orc_moe_route(lg.data(), ids.data(), w.data(), R, c.n_expert, c.n_expert_used);
+        const size_t eb_up = (size_t)2 * F * nb * 144, eb_dn = (size_t)E * (F / 256) * 144;
+        y.assign((size_t)R * E, 0.f);
+        std::vector<float> gu(2 * F), act(F), v(E); std::vector<int8_t> aq(F); std::vector<float> ad(F / 32), as(F / 32);
+        for (int t = 0; t < R; ++t) {
+            std::vector<float> acc(E, 0.f);
+            for (int e = 0; e < ns; ++e) {
+                const int id = ids[t * ns + e];
+                const uint8_t* Wu = id >= 0 ? L.exp_gate_up.w.data() + (size_t)id * eb_up : L.sh_gate_up.w.data();
+                const uint8_t* Wd = id >= 0 ? L.exp_down.w.data() + (size_t)id * eb_dn : L.sh_down.w.data();
+                orc_gemv_q4k_q8_seq(Wu, xq.q.data() + (size_t)t * E, xq.d.data() + (size_t)t * nsb, xq.s.data() + (size_t)t * nsb, gu.data(), 2 * F, E);
+                for (int i = 0; i < F; ++i) act[i] = orc_silu(gu[i]) * gu[F + i];
+                orc_quantize_x_q8(act.data(), 1, F, aq.data(), ad.data(), as.data());
+                orc_gemv_q4k_q8_seq(Wd, aq.data(), ad.data(), as.data(), v.data(), E, F);
+                for (int i = 0; i < E; ++i) acc[i] = fmaf(w[t * ns + e], v[i], acc[i]);   // slot order (gemv.hip:1104-1112)
+            }
+            memcpy(y.data() + (size_t)t * E, acc.data(), (size_t)E * 4);
+        }
+    }
     void ffn_block(const OLayer& L, XQ& xq, int R, std::vector<float>& y) {
         const int F = c.n_ff; std::vector<float> gu((size_t)R * 2 * F);
         gemv(L.gate_up, xq, gu.data(), R, 2 * F);
@@ -360,8 +452,8 @@ struct OrcModel {
             } else {
                 attn_block(L, xq, kc, vc, (size_t)ai * kvl, pos.data(), slot.data(), R, y); ++ai;
             }
-            norm_in(x, y.data(), L.post_norm, nullptr, xq, R);
-            ffn_block(L, xq, R, y);
+            if (c.n_expert) { std::vector<float> xn((size_t)R * E); norm_in(x, y.data(), L.post_norm, xn.data(), xq, R); moe_block(L, xq, xn, R, y); }
+            else { norm_in(x, y.data(), L.post_norm, nullptr, xq, R); ffn_block(L, xq, R, y); }
             have_y = true;
         }
         norm_in(x, y.data(), output_norm, h.data(), xq, R);
@@ -395,8 +487,8 @@ struct OrcModel {
         std::vector<int> pos(T), sl(T, slot); for (int t = 0; t < T; ++t) pos[t] = pos0 + t;
         norm_in(x, nullptr, mtp.attn_norm, nullptr, xq, T);
         attn_block(mtp, xq, mkc, mvc, 0, pos.data(), sl.data(), T, y);
-        norm_in(x, y.data(), mtp.post_norm, nullptr, xq, T);
-        ffn_block(mtp, xq, T, y);
+        if (c.n_expert) { std::vector<float> xn((size_t)T * E); norm_in(x, y.data(), mtp.post_norm, xn.data(), xq, T); moe_block(mtp, xq, xn, T, y); }
+        else { norm_in(x, y.data(), mtp.post_norm, nullptr, xq, T); ffn_block(mtp, xq, T, y); }
         norm_in(x, y.data(), head_norm, mh.data(), xq, T);
         gemv(lm_head, xq, mlogits.data(), T, c.n_vocab);
     }
@@ -427,7 +519,9 @@ size_t orc_model_tensor(OrcModel* m, int layer, int kind, const void** ptr) {
     const OLayer& L = layer == m->c.n_layer ? m->mtp : m->layers[layer];
     switch (kind) { case TK_ATTN_NORM: return v16(L.attn_norm); case TK_POST_NORM: return v16(L.post_norm); case TK_IN_PROJ: return v8(L.in_proj.w); case TK_OUT_PROJ: return v8(L.out_proj.w);
                     case TK_GATE_UP: return v8(L.gate_up.w); case TK_DOWN: return v8(L.down.w); case TK_CONV_W: *ptr = L.conv_w.data(); return L.conv_w.size() * 4;
-                    case TK_DT_BIAS: return v16(L.dt_bias); case TK_A_NEG: return v16(L.a_neg); case TK_SSM_NORM: return v16(L.ssm_norm); case TK_Q_NORM: return v16(L.q_norm); case TK_K_NORM: return v16(L.k_norm); }
+                    case TK_DT_BIAS: return v16(L.dt_bias); case TK_A_NEG: return v16(L.a_neg); case TK_SSM_NORM: return v16(L.ssm_norm); case TK_Q_NORM: return v16(L.q_norm); case TK_K_NORM: return v16(L.k_norm);
+                    case TK_ROUTER: *ptr = L.router.data(); return L.router.size() * 4; case TK_EXP_GATE_UP: return v8(L.exp_gate_up.w); case TK_EXP_DOWN: return v8(L.exp_down.w);
+                    case TK_SH_GATE_UP: return v8(L.sh_gate_up.w); case TK_SH_DOWN: return v8(L.sh_down.w); }
     return 0;
 }
 }
