@@ -26,6 +26,13 @@ sys.path.insert(0, ROOT)
 METRIC = "MTP-spec decode tokens/s (Q4_K); verify-GEMV HBM GB/s vs B200 peak"
 PEAKS_FALLBACK = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 N_DRAFT, ACCEPT_RATE, PROMPT_LEN = 5, 0.7, 4096
+# workload -> (preset, n_draft, prompt length, description)
+WORKLOADS = {
+    "dense27b": ("qwen35-27b", 5, 4096, "config3: Qwen3.8-27B-shaped dense hybrid (64 layers, hidden 5120, FFN 17408, vocab 248320), random-init Q4_K, "
+                                        "batch 1, 4096-token seeded prompt, MTP n=5, seeded acceptance 0.7"),
+    "moe": ("flash-next", 2, 2048, "config4: Flash-Next-shaped MoE hybrid (48 layers, hidden 2048, 512 experts top-10 + shared, expert FFN 512, vocab 248320), "
+                                   "random-init Q4_K, batch 1, 2048-token seeded prompt, MTP n=2, seeded acceptance 0.7"),
+}
 
 
 def peaks():
@@ -143,10 +150,9 @@ def run_reference(args, rank, world):
             "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
 
 
-def dense_config(world):
-    return {"workload": "config3: Qwen3.8-27B-shaped dense hybrid (64 layers, hidden 5120, FFN 17408, vocab 248320), random-init Q4_K, "
-                        "batch 1, 4096-token seeded prompt, MTP n=5, seeded acceptance 0.7",
-            "l2": "inputs larger than L2: 20 GB of weights streamed per step", "parallelism": f"replicas x{world}"}
+def dense_config(world, workload="dense27b"):
+    return {"workload": WORKLOADS[workload][3],
+            "l2": "inputs larger than L2: GBs of weights streamed per step", "parallelism": f"replicas x{world}"}
 
 
 # ------------------------------------------------------------------------------------------ dense27b
@@ -157,11 +163,12 @@ def run_dense(args, rank, local_rank, world):
     from hipster_b200 import spec
     from hipster_b200.engine import _as_tensor
     torch.cuda.set_device(local_rank)
-    n, rate = N_DRAFT, ACCEPT_RATE
+    preset, n, wl_prompt, _ = WORKLOADS[args.workload]
+    rate = ACCEPT_RATE
     total_rounds = args.warmup + args.steps
     n_plain = total_rounds * (n + 1) + n + 2
-    cfg = hb.ModelCfg.preset(args.preset)
-    prompt_len = min(args.prompt_len, cfg.max_ctx // 2)
+    cfg = hb.ModelCfg.preset(args.preset or preset, n_slots=1)
+    prompt_len = min(args.prompt_len or wl_prompt, cfg.max_ctx // 2)
     assert prompt_len + n_plain + 2 * n + 4 <= cfg.max_ctx, "too many steps for the context window"
     eng = hb.Engine(cfg)
     E = cfg.n_embd
@@ -243,7 +250,7 @@ def run_dense(args, rank, local_rank, world):
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "u4 x i8 -> i32, f32 epilogue/state", "data": "synthetic",
-        "config": dense_config(world),
+        "config": dense_config(world, args.workload),
         "e2e": {"value": toks / (wall_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 4 * n, "d2h_bytes_per_step": 256,
                 "note": "hp_spec_round with host token buffers; wall clock over the timed rounds, one stream synchronise per round"},
         "gpu_launches": args.steps * world * (570 + n * 21 + 20),
@@ -259,6 +266,140 @@ def run_dense(args, rank, local_rank, world):
         dt, th = cpu_round_sample(3, 1)
         line["cpu_baseline"] = {"value": expected_tokens_per_round(n, rate) / dt, "unit": "tokens/s", "cores": th, "kind": "port", "sample": CPU_SAMPLE + "; 3 timed rounds"}
     return line
+
+
+# ------------------------------------------------------------------------------------------ moe-ep (config 5)
+def run_moe_ep(args, rank, local_rank, world):
+    """Config 5: the Flash-Next-shaped MoE model, 8 slots with distinct seeded prompts in lock-step MTP n=2 rounds
+    (24 verify rows per pass; engine/bench/batchfn.cpp:96-117), routed experts sharded over the `world` GPUs, one NCCL
+    exchange per MoE layer. Every rank runs the same loop (the trunk is replicated); value = aggregate tokens/s."""
+    import torch
+    import torch.distributed as dist
+    import hipster_b200 as hb
+    from hipster_b200 import ep
+    from hipster_b200.engine import _as_tensor
+    torch.cuda.set_device(local_rank)
+    n, rate, S = 2, ACCEPT_RATE, 8
+    prompt_len = args.prompt_len or 2048
+    cfg = hb.ModelCfg.preset(args.preset or "flash-next", n_slots=S, ep_rank=rank, ep_world=world)
+    eng = hb.Engine(cfg)
+    if world > 1:
+        eng.ep_init(ep.broadcast_unique_id(dist, rank))
+    E = cfg.n_embd
+    hview = _as_tensor(eng.h_nextn_ptr(), 32 * E * 4).view(torch.float32).view(32, E)
+    mhview = _as_tensor(eng.mtp_h_ptr(), 32 * E * 4).view(torch.float32).view(32, E)
+    hbuf = torch.zeros((32, E), dtype=torch.float32, device="cuda")
+    hpend = torch.zeros((S, E), dtype=torch.float32, device="cuda")
+    prompts = [[int(x) for x in np.random.default_rng(1000 + s).integers(0, cfg.n_vocab, size=prompt_len)] for s in range(S)]
+    rounds = args.warmup + args.steps
+    n_plain = rounds * (n + 1) + n + 2
+
+    def prefill_all(with_mtp):
+        prev = [None] * S
+        for p0 in range(0, prompt_len, 4):          # 4 rows per slot per pass: 32 rows
+            T = min(4, prompt_len - p0)
+            eng.forward([(s, prompts[s][p0:p0 + T], p0) for s in range(S)])
+            for s in range(S):
+                eng.accept(s, T)
+            if with_mtp:
+                torch.cuda.synchronize()
+                for s in range(S):
+                    hbuf[s * T] = prev[s] if prev[s] is not None else 0
+                    if T > 1:
+                        hbuf[s * T + 1:s * T + T] = hview[s * T:s * T + T - 1]
+                    prev[s] = hview[s * T + T - 1].clone()
+                torch.cuda.synchronize()
+                eng.mtp_forward_slots([(s, prompts[s][p0:p0 + T], p0) for s in range(S)], hbuf.data_ptr())
+        T_last = (prompt_len - 1) % 4 + 1
+        return T_last
+
+    t_setup = time.perf_counter()
+    # plain greedy streams of all slots, computed in lock-step T=1 passes (each slot's rows are independent of the others)
+    T_last = prefill_all(False)
+    ids = eng.topk(0, S * T_last)[0]
+    plain = [[int(ids[s * T_last + T_last - 1])] for s in range(S)]
+    for i in range(n_plain):
+        eng.forward([(s, [plain[s][-1]], prompt_len + i) for s in range(S)])
+        for s in range(S):
+            eng.accept(s, 1)
+        ids = eng.topk(0, S)[0]
+        for s in range(S):
+            plain[s].append(int(ids[s]))
+    eng.reset()
+    T_last = prefill_all(True)
+    ids = eng.topk(0, S * T_last)[0]
+    torch.cuda.synchronize()
+    for s in range(S):
+        hpend[s] = hview[s * T_last + T_last - 1]
+    out = [[int(ids[s * T_last + T_last - 1])] for s in range(S)]
+    pos = [prompt_len] * S
+    srng = np.random.default_rng(7)
+    t_setup = time.perf_counter() - t_setup
+
+    def one_round():
+        drafts = [[] for _ in range(S)]
+        toks = [out[s][-1] for s in range(S)]
+        hptr = hpend.data_ptr()
+        for i in range(n):                           # draft, chained on the MTP's own h (batchfn.cpp:98-104)
+            eng.mtp_forward_slots([(s, [toks[s]], pos[s] + i) for s in range(S)], hptr)
+            ids = eng.topk(1, S)[0]
+            for s in range(S):
+                k = len(out[s]) - 1
+                good = plain[s][k + 1 + i]
+                d = good if srng.random() < rate else (good + 1) % cfg.n_vocab   # seeded substitution
+                drafts[s].append(d); toks[s] = d
+            hptr = eng.mtp_h_ptr()
+        eng.forward([(s, [out[s][-1]] + drafts[s], pos[s]) for s in range(S)])   # verify: 24 rows
+        ids = eng.topk(0, S * (n + 1))[0]
+        emitted = 0; reqs = []; rows = []
+        for s in range(S):
+            r0 = s * (n + 1); mm = 0
+            while mm < n and ids[r0 + mm] == drafts[s][mm]:
+                mm += 1
+            eng.accept(s, mm + 1)
+            out[s] += drafts[s][:mm] + [int(ids[r0 + mm])]
+            if mm > 0:
+                reqs.append((s, drafts[s][:mm], pos[s] + 1)); rows += list(range(r0, r0 + mm))
+            hpend[s] = hview[r0 + mm]
+            pos[s] += mm + 1; emitted += mm + 1
+        if reqs:                                     # MTP catch-up with the target's h rows (batchfn.cpp:110-114)
+            idx = torch.tensor(rows, device="cuda")
+            hbuf[:len(rows)] = hview[idx]
+            torch.cuda.synchronize()
+            eng.mtp_forward_slots(reqs, hbuf.data_ptr())
+        return emitted
+
+    for _ in range(args.warmup):
+        one_round()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter(); e0.record()
+    toks = 0
+    for _ in range(args.steps):
+        toks += one_round()
+    e1.record(); torch.cuda.synchronize()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    clocks = sampler.stop() if sampler else None
+    exact = all(out[s][:len(plain[s])] == plain[s][:len(out[s])] for s in range(S))
+    if world > 1:
+        t = torch.tensor([wall_ms], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX); wall_ms = float(t[0]); dist.barrier()
+    eng.close()
+    if rank != 0:
+        return None
+    pk = peaks()
+    v = toks / (wall_ms / 1e3)
+    return {"metric": METRIC, "value": v, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": wall_ms / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u4 x i8 -> i32, f32 epilogue/state", "data": "synthetic",
+            "config": {"workload": "config5: Flash-Next-shaped MoE, 8 slots x distinct 2048-token seeded prompts, lock-step MTP n=2 (24 verify rows per pass), "
+                                   "seeded acceptance 0.7, aggregate tokens/s", "parallelism": f"ep{world} (routed experts sharded, trunk replicated)",
+                       "l2": "inputs larger than L2", "prompt_len": prompt_len},
+            "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 4 * S * (2 * n + 1 + n), "d2h_bytes_per_step": 4 * S * (2 * n + 1),
+                    "note": "host-driven lock-step loop through hp_forward / hp_accept / hp_mtp_forward_slots / hp_topk; value and e2e are the same measurement"},
+            "gpu_launches": None, "roofline": {"bound": "hbm", "achieved": None, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": None, "traffic": None},
+            "clocks": clocks, "checks": {"slot_streams_equal_solo_plain_greedy": bool(exact), "tokens": int(toks), "setup_s": t_setup}}
 
 
 # ------------------------------------------------------------------------------------------ gemv (config 1)
@@ -339,10 +480,10 @@ def main():
     ap.add_argument("--steps", type=int, default=87)     # ~256 emitted tokens at 2.94 tokens per round
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="dense27b", choices=["dense27b", "gemv"])
-    ap.add_argument("--preset", default="qwen35-27b")
+    ap.add_argument("--workload", default="dense27b", choices=["dense27b", "moe", "moe-ep", "gemv"])
+    ap.add_argument("--preset", default=None)
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="shorter prompts are for profiling captures only")
+    ap.add_argument("--prompt-len", type=int, default=0, help="override the workload's prompt length (shorter prompts are for profiling captures only)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank, local_rank, world = dist_env()
@@ -356,7 +497,12 @@ def main():
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    line = run_dense(args, rank, local_rank, world) if args.workload == "dense27b" else run_gemv(args, rank, local_rank, world)
+    if args.workload in ("dense27b", "moe"):
+        line = run_dense(args, rank, local_rank, world)
+    elif args.workload == "moe-ep":
+        line = run_moe_ep(args, rank, local_rank, world)
+    else:
+        line = run_gemv(args, rank, local_rank, world)
     if line:
         print(json.dumps(line), flush=True)
     if world > 1:

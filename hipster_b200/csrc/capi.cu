@@ -163,6 +163,7 @@ int hp_model_preset(const char* preset, hp_model_cfg* o) {
     HP_GUARD_BEGIN
     HP_REQUIRE(preset && o, "hp_model_preset: null pointer");
     memset(o, 0, sizeof *o);
+    o->ep_rank = 0; o->ep_world = 1;
     o->rms_eps = 1e-6f; o->rope_base = 1e7f; o->n_rot = 64; o->attn_every = 4; o->has_mtp = 1; o->n_slots = 1;
     if (!strcmp(preset, "qwen35-27b")) {          // struct Qwen35Dims, engine/src/qwen35.h:15-26
         o->n_embd = 5120; o->n_layer = 64; o->n_ff = 17408; o->n_vocab = 248320; o->n_head = 24; o->n_head_kv = 4;
@@ -212,6 +213,9 @@ int hp_tensor_dev(const hp_engine* e, int layer, int kind, void** ptr_out, size_
 int hp_gdn_state_dev(hp_engine* e, int slot, int gdn_layer, float** ptr_out, size_t* bytes_out) {
     HP_GUARD_BEGIN HP_REQUIRE(e && ptr_out && bytes_out, "hp_gdn_state_dev: null pointer"); return e->impl.gdn_state(slot, gdn_layer, ptr_out, bytes_out); HP_GUARD_END
 }
+int hp_mtp_forward_slots(hp_engine* e, const hp_slot_req* reqs, int S, const float* h_dev) { HP_ENGINE_CALL(e->impl.mtp_forward_reqs(reqs, S, h_dev, true)) }
+int hp_ep_unique_id(void* id128_out) { HP_GUARD_BEGIN HP_REQUIRE(id128_out, "hp_ep_unique_id: null pointer"); return hp::Engine::ep_unique_id(id128_out); HP_GUARD_END }
+int hp_ep_init(hp_engine* e, const void* id128) { HP_GUARD_BEGIN HP_REQUIRE(e && id128, "hp_ep_init: null pointer"); return e->impl.ep_init(id128); HP_GUARD_END }
 int hp_profile_pass(hp_engine* e, int R, int what, int reps, float* ms_out) { HP_ENGINE_CALL(e->impl.profile_pass(R, what, reps, ms_out)) }
 size_t hp_pass_weight_bytes(const hp_engine* e, int mtp, int with_head) { return e ? e->impl.pass_weight_bytes(mtp != 0, with_head != 0) : 0; }
 int hp_spec_begin(hp_engine* e, int slot, int id_last, int pos, const float* h_pending_dev) { HP_ENGINE_CALL(e->impl.spec_begin(slot, id_last, pos, h_pending_dev)) }

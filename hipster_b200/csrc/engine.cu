@@ -30,8 +30,9 @@ __host__ __device__ inline uint16_t f32_to_f16_bits(float f) {   // same roundin
 __host__ __device__ inline uint16_t f32_to_bf16_bits(float f) { uint32_t u = f_bits(f); u += 0x7FFFu + ((u >> 16) & 1u); return (uint16_t)(u >> 16); }
 
 // Q4_K blocks: quants uniform 0..15, the 6-bit scales/mins uniform 0..63 (any 12 bytes), d and dmin = f16(|N(0, 0.01)|)
-__global__ void k_gen_q4k(uint64_t* __restrict__ w, size_t nwords, uint64_t seed, uint64_t tid) {
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; if (i >= nwords) return;
+__global__ void k_gen_q4k(uint64_t* __restrict__ w, size_t nwords, uint64_t seed, uint64_t tid, size_t word0) {
+    const size_t li = (size_t)blockIdx.x * blockDim.x + threadIdx.x; if (li >= nwords) return;
+    const size_t i = li + word0;   // global word index of the tensor (a GPU may hold only a slice of it)
     uint64_t v = rnd64(seed, tid, i);
     if (i % 18 == 0) {
         const size_t b = i / 18;
@@ -39,7 +40,7 @@ __global__ void k_gen_q4k(uint64_t* __restrict__ w, size_t nwords, uint64_t seed
         const uint16_t dm = f32_to_f16_bits(fabsf(irwin(rnd64(seed, tid ^ 0xE00Eull, b))) * 0.01f);
         v = (v & 0xFFFFFFFF00000000ull) | (uint64_t)d | ((uint64_t)dm << 16);
     }
-    w[i] = v;
+    w[li] = v;
 }
 __global__ void k_gen_bf16(uint16_t* __restrict__ p, size_t n, uint64_t seed, uint64_t tid, float mean, float std) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; if (i >= n) return;
@@ -127,17 +128,23 @@ int Engine::gen_lin(Lin& l, int N, int K, uint64_t tid) {
     HP_REQUIRE(K % 256 == 0 && l.P > 0, "tensor %d x %d is not a valid Q4_K GEMV shape", N, K);
     if (int rc = alloc((void**)&l.w, l.bytes)) return rc;
     const size_t nwords = l.bytes / 8;
-    k_gen_q4k<<<(unsigned)((nwords + 255) / 256), 256, 0, s_>>>((uint64_t*)l.w, nwords, c_.seed, tid);
+    k_gen_q4k<<<(unsigned)((nwords + 255) / 256), 256, 0, s_>>>((uint64_t*)l.w, nwords, c_.seed, tid, 0);
     HP_CUDA(cudaGetLastError());
     weight_bytes_ += l.bytes; return HP_OK;
 }
-int Engine::gen_raw_q4k(Lin& l, size_t rows, int K, uint64_t tid) {   // expert stacks: no GEMV partition attached
-    l.N = (int)std::min<size_t>(rows, 0x7fffffff); l.K = K; l.P = 1; l.bytes = rows * (K / 256) * 144;
+int Engine::gen_raw_q4k(Lin& l, size_t rows, int K, uint64_t tid, size_t row0, size_t nrows_local) {   // expert stacks: no GEMV partition attached
+    // rows [row0, row0 + nrows_local) of a tensor of `rows` rows are generated; l.w is offset so that it can be indexed
+    // with global row numbers (a GPU that holds a shard of the experts never dereferences the rows of other shards)
+    if (nrows_local == (size_t)-1) nrows_local = rows;
+    const size_t rb = (size_t)(K / 256) * 144;
+    l.N = (int)std::min<size_t>(rows, 0x7fffffff); l.K = K; l.P = 1; l.bytes = nrows_local * rb;
     HP_REQUIRE(K % 256 == 0, "expert tensor K=%d is not a multiple of 256", K);
-    if (int rc = alloc((void**)&l.w, l.bytes)) return rc;
+    uint8_t* base = nullptr;
+    if (int rc = alloc((void**)&base, l.bytes)) return rc;
     const size_t nwords = l.bytes / 8;
-    k_gen_q4k<<<(unsigned)((nwords + 255) / 256), 256, 0, s_>>>((uint64_t*)l.w, nwords, c_.seed, tid);
+    k_gen_q4k<<<(unsigned)((nwords + 255) / 256), 256, 0, s_>>>((uint64_t*)base, nwords, c_.seed, tid, row0 * rb / 8);
     HP_CUDA(cudaGetLastError());
+    l.w = base - row0 * rb;
     weight_bytes_ += l.bytes; return HP_OK;
 }
 int Engine::gen_bf16(uint16_t** p, size_t n, uint64_t tid, float mean, float std) {
@@ -160,6 +167,7 @@ int Engine::init() {
     HP_REQUIRE(c.n_head >= 1 && c.n_head_kv >= 1 && c.n_head % c.n_head_kv == 0 && (c.n_head / c.n_head_kv) <= ATTN_MAX_PAIRS, "bad attention head counts");
     HP_REQUIRE(c.gdn_qk_heads >= 1 && c.gdn_v_heads % c.gdn_qk_heads == 0 && (c.gdn_v_heads * 128) % 256 == 0, "bad GDN head counts");
     HP_REQUIRE(c.attn_every >= 1 && c.n_slots >= 1 && c.n_slots <= MAXS && c.max_ctx >= 16 && c.n_rot % 2 == 0 && c.n_rot <= 256, "bad configuration");
+    HP_REQUIRE(c.ep_world <= 1 || (c.n_expert > 0 && c.ep_rank >= 0 && c.ep_rank < c.ep_world && c.n_expert % c.ep_world == 0), "bad expert-parallel configuration");
     HP_REQUIRE(c.n_expert == 0 ? (c.n_ff > 0 && c.n_ff % 256 == 0) : (c.expert_ff % 256 == 0 && c.n_expert_used >= 1 && c.n_expert_used <= 15), "bad FFN shape");
     HP_CUDA(cudaStreamCreateWithFlags(&s_, cudaStreamNonBlocking));
     HP_CUDA(cudaEventCreate(&ev0_)); HP_CUDA(cudaEventCreate(&ev1_));
@@ -189,8 +197,9 @@ int Engine::init() {
         } else {   // routed experts (contiguous per tensor, qwen4exp weights layout [512*N][K]) + one shared expert + f32 router
             const int F = c.expert_ff;
             HP_TRY(gen_f32(&L.router, (size_t)(c.n_expert + 1) * E, tensor_id(il, TK_ROUTER), 0.f, 1.0f / sqrtf((float)E), false));
-            HP_TRY(gen_raw_q4k(L.exp_gate_up, (size_t)c.n_expert * 2 * F, E, tensor_id(il, TK_EXP_GATE_UP)));
-            HP_TRY(gen_raw_q4k(L.exp_down, (size_t)c.n_expert * E, F, tensor_id(il, TK_EXP_DOWN)));
+            const int w = std::max(1, c.ep_world), elo = (int)((long long)c.ep_rank * c.n_expert / w), ehi = (int)((long long)(c.ep_rank + 1) * c.n_expert / w);
+            HP_TRY(gen_raw_q4k(L.exp_gate_up, (size_t)c.n_expert * 2 * F, E, tensor_id(il, TK_EXP_GATE_UP), (size_t)elo * 2 * F, (size_t)(ehi - elo) * 2 * F));
+            HP_TRY(gen_raw_q4k(L.exp_down, (size_t)c.n_expert * E, F, tensor_id(il, TK_EXP_DOWN), (size_t)elo * E, (size_t)(ehi - elo) * E));
             HP_TRY(gen_raw_q4k(L.sh_gate_up, (size_t)2 * F, E, tensor_id(il, TK_SH_GATE_UP)));
             HP_TRY(gen_raw_q4k(L.sh_down, (size_t)E, F, tensor_id(il, TK_SH_DOWN)));
         }
@@ -256,7 +265,7 @@ int Engine::init() {
         HP_TRY(alloc(&xq2_.q, xq_q_bytes(pairs, F))); HP_TRY(alloc(&xq2_.sc, xq_sc_floats(pairs, F) * 4));
         HP_CUDA(cudaMemsetAsync(xq2_.q, 0, xq_q_bytes(pairs, F), s_)); HP_CUDA(cudaMemsetAsync(xq2_.sc, 0, xq_sc_floats(pairs, F) * 4, s_));
         moe_out_.N = E; moe_out_.K = F; moe_out_.P = 1;
-        e_lo_ = 0; e_hi_ = c.n_expert; own_shared_ = 1;
+        { const int w = std::max(1, c.ep_world); e_lo_ = (int)((long long)c.ep_rank * c.n_expert / w); e_hi_ = (int)((long long)(c.ep_rank + 1) * c.n_expert / w); own_shared_ = 1; }
     }
     nsplit_max_ = (c.max_ctx + ATTN_SPLIT - 1) / ATTN_SPLIT;
     const size_t np = attn_partial_floats(MAXR, c.n_head_kv, nsplit_max_);
@@ -485,6 +494,29 @@ int Engine::mtp_forward(const int* tokens, const float* h_dev, int T, int pos0, 
     return HP_OK;
 }
 
+int Engine::mtp_forward_reqs(const hp_slot_req* reqs, int S, const float* h_dev, bool want_logits) {
+    HP_REQUIRE(c_.has_mtp, "model has no MTP block");
+    HP_REQUIRE(reqs && h_dev && S >= 1 && S <= c_.n_slots, "bad S");
+    int* d = h_desc_; int r0 = 0, ng = 0;
+    const int gr = std::max(1, std::min(8, ATTN_MAX_PAIRS / (c_.n_head / c_.n_head_kv)));
+    for (int i = 0; i < S; ++i) {
+        const hp_slot_req& r = reqs[i];
+        HP_REQUIRE(r.slot >= 0 && r.slot < c_.n_slots && r.T >= 1 && r.T <= 8 && r.pos >= 0 && r.pos + r.T <= c_.max_ctx && r.tokens && r0 + r.T <= MAXR, "bad request");
+        for (int t0 = 0; t0 < r.T; t0 += gr) {
+            const int tn = std::min(gr, r.T - t0);
+            d[D_GROUPS + ng * 4] = r0 + t0; d[D_GROUPS + ng * 4 + 1] = tn; d[D_GROUPS + ng * 4 + 2] = r.slot; d[D_GROUPS + ng * 4 + 3] = r.pos + t0;
+            for (int t = t0; t < t0 + tn; ++t) d[D_RGROUP + r0 + t] = ng;
+            ++ng;
+        }
+        for (int t = 0; t < r.T; ++t) { d[D_TOK + r0 + t] = r.tokens[t]; d[D_POS + r0 + t] = r.pos + t; d[D_SLOT + r0 + t] = r.slot; }
+        r0 += r.T;
+    }
+    HP_TRY(upload_desc());
+    HP_TRY(run_mtp(r0, ng, h_dev, c_.n_embd, want_logits));
+    HP_CUDA(cudaStreamSynchronize(s_));
+    return HP_OK;
+}
+
 int Engine::topk(int which, int T, int* ids, float* vals) {
     HP_REQUIRE(T >= 1 && T <= MAXR && ids, "topk: bad arguments");
     HP_CUDA(cudaStreamSynchronize(s_));
@@ -525,8 +557,8 @@ int Engine::tensor(int layer, int kind, void** ptr, size_t* bytes) const {
         case TK_Q_NORM: return set(L.q_norm, 512);
         case TK_K_NORM: return set(L.k_norm, 512);
         case TK_ROUTER: return set(L.router, (size_t)(c.n_expert + 1) * E * 4);
-        case TK_EXP_GATE_UP: return set(L.exp_gate_up.w, L.exp_gate_up.bytes);
-        case TK_EXP_DOWN: return set(L.exp_down.w, L.exp_down.bytes);
+        case TK_EXP_GATE_UP: return set(L.exp_gate_up.w + (size_t)e_lo_ * 2 * c.expert_ff * (E / 256) * 144, L.exp_gate_up.bytes);   // this GPU's shard
+        case TK_EXP_DOWN: return set(L.exp_down.w + (size_t)e_lo_ * E * (c.expert_ff / 256) * 144, L.exp_down.bytes);
         case TK_SH_GATE_UP: return set(L.sh_gate_up.w, L.sh_gate_up.bytes);
         case TK_SH_DOWN: return set(L.sh_down.w, L.sh_down.bytes);
     }
@@ -646,6 +678,49 @@ done:
 
 }  // namespace hp
 
+// ------------------------------------------------------------------ NCCL (loaded at run time; only the expert-parallel path needs it)
+#include <dlfcn.h>
 namespace hp {
-int Engine::ep_allreduce(float*, size_t) { set_error("expert parallelism is not initialised"); return HP_ECOMM; }
+namespace {
+struct NcclId { char b[128]; };   // ncclUniqueId is 128 opaque bytes, passed by value
+struct NcclApi {
+    void* lib = nullptr;
+    int (*GetUniqueId)(void*) = nullptr;
+    int (*CommInitRank)(void**, int, NcclId, int) = nullptr;
+    int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+    int (*CommDestroy)(void*) = nullptr;
+    const char* (*GetErrorString)(int) = nullptr;
+};
+NcclApi g_nccl;
+int nccl_load() {
+    if (g_nccl.lib) return HP_OK;
+    void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) { set_error("cannot load libnccl.so.2: %s", dlerror()); return HP_ECOMM; }
+    g_nccl.GetUniqueId = (decltype(g_nccl.GetUniqueId))dlsym(h, "ncclGetUniqueId");
+    g_nccl.CommInitRank = (decltype(g_nccl.CommInitRank))dlsym(h, "ncclCommInitRank");
+    g_nccl.AllReduce = (decltype(g_nccl.AllReduce))dlsym(h, "ncclAllReduce");
+    g_nccl.CommDestroy = (decltype(g_nccl.CommDestroy))dlsym(h, "ncclCommDestroy");
+    g_nccl.GetErrorString = (decltype(g_nccl.GetErrorString))dlsym(h, "ncclGetErrorString");
+    if (!g_nccl.GetUniqueId || !g_nccl.CommInitRank || !g_nccl.AllReduce || !g_nccl.CommDestroy) { set_error("libnccl lacks a required symbol"); return HP_ECOMM; }
+    g_nccl.lib = h; return HP_OK;
+}
+int nccl_check(int rc, const char* what) {
+    if (rc == 0) return HP_OK;
+    set_error("NCCL error %d (%s) in %s", rc, g_nccl.GetErrorString ? g_nccl.GetErrorString(rc) : "?", what); return HP_ECOMM;
+}
+}  // namespace
+int Engine::ep_unique_id(void* id128) { HP_TRY(nccl_load()); return nccl_check(g_nccl.GetUniqueId(id128), "ncclGetUniqueId"); }
+int Engine::ep_init(const void* id128) {
+    HP_REQUIRE(c_.n_expert > 0 && c_.ep_world > 1, "ep_init: the model was not loaded with ep_world > 1");
+    HP_TRY(nccl_load());
+    NcclId id; memcpy(id.b, id128, 128);
+    HP_TRY(nccl_check(g_nccl.CommInitRank(&nccl_comm_, c_.ep_world, id, c_.ep_rank), "ncclCommInitRank"));
+    ep_world_ = c_.ep_world; ep_rank_ = c_.ep_rank; own_shared_ = c_.ep_rank == 0 ? 1 : 0;
+    return HP_OK;
+}
+int Engine::ep_allreduce(float* buf, size_t n) {
+    HP_REQUIRE(nccl_comm_, "expert parallelism is not initialised (hp_ep_init)");
+    return nccl_check(g_nccl.AllReduce(buf, buf, n, /* ncclFloat32 */ 7, /* ncclSum */ 0, nccl_comm_, s_), "ncclAllReduce");
+}
 }

@@ -39,6 +39,8 @@ public:
     int forward(const hp_slot_req* reqs, int S, float* ms);  // Qwen35::forward(const SlotReq*, int) (qwen35.h:62)
     int accept(int slot, int m);                             // Qwen35::accept (qwen35.h:66)
     int mtp_forward(const int* tokens, const float* h_dev, int T, int pos0, int slot, bool want_logits);   // qwen35.h:70
+    int mtp_forward_reqs(const hp_slot_req* reqs, int S, const float* h_dev, bool want_logits);   // qwen4exp.h:66-70
+    static int ep_unique_id(void* id128); int ep_init(const void* id128);
     int topk(int which, int T, int* ids, float* vals);       // k = 1 (qwen35.h:87)
     int reset(); int reset_slot(int slot);
     int flush_commits();                                     // apply every pending accept to the stored state
@@ -56,7 +58,7 @@ private:
     struct Desc;   // device-visible pass descriptor (see engine.cu)
     int alloc(void** p, size_t bytes);
     int gen_lin(Lin& l, int N, int K, uint64_t tid);
-    int gen_raw_q4k(Lin& l, size_t rows, int K, uint64_t tid);
+    int gen_raw_q4k(Lin& l, size_t rows, int K, uint64_t tid, size_t row0 = 0, size_t nrows_local = (size_t)-1);
     int gen_bf16(uint16_t** p, size_t n, uint64_t tid, float mean, float std);
     int gen_f32(float** p, size_t n, uint64_t tid, float mean, float std, bool neg_abs);
     int lin(const Lin& l, float* out, int ld, int R);        // GEMV; P > 1 planes are reduced into out

@@ -14,7 +14,7 @@ TENSOR_KINDS = dict(attn_norm=0, post_norm=1, in_proj=2, out_proj=3, gate_up=4, 
 class ModelCfg(ctypes.Structure):
     """struct hp_model_cfg (include/hipster_b200.h)."""
     _fields_ = [(n, ctypes.c_int) for n in ("n_embd", "n_layer", "n_ff", "n_vocab", "n_head", "n_head_kv", "n_rot", "gdn_qk_heads", "gdn_v_heads",
-                                             "attn_every", "max_ctx", "n_slots", "n_expert", "n_expert_used", "expert_ff", "gdn_sigmoid_gate", "has_mtp")] + \
+                                             "attn_every", "max_ctx", "n_slots", "n_expert", "n_expert_used", "expert_ff", "gdn_sigmoid_gate", "has_mtp", "ep_rank", "ep_world")] + \
                [("rms_eps", ctypes.c_float), ("rope_base", ctypes.c_float), ("seed", ctypes.c_ulonglong)]
 
     @classmethod
@@ -71,6 +71,19 @@ class Engine:
     def mtp_forward(self, slot, tokens, h_dev_ptr, pos0):
         t = (ctypes.c_int * len(tokens))(*[int(x) for x in tokens])
         check(lib().hp_mtp_forward(self._h, slot, t, ctypes.c_void_p(h_dev_ptr), len(tokens), pos0))
+
+    def mtp_forward_slots(self, reqs, h_dev_ptr):
+        """reqs: list of (slot, tokens, pos); h_dev_ptr: one row of n_embd floats per request row. Qwen4Exp::mtp_forward(reqs, S, h)."""
+        arr = (SlotReq * len(reqs))()
+        keep = []
+        for i, (slot, toks, pos) in enumerate(reqs):
+            t = (ctypes.c_int * len(toks))(*[int(x) for x in toks]); keep.append(t)
+            arr[i] = SlotReq(slot, t, len(toks), pos)
+        check(lib().hp_mtp_forward_slots(self._h, arr, len(reqs), ctypes.c_void_p(h_dev_ptr)))
+
+    def ep_init(self, id128):
+        buf = (ctypes.c_char * 128).from_buffer_copy(bytes(id128))
+        check(lib().hp_ep_init(self._h, buf))
 
     def topk(self, which, T):
         ids = (ctypes.c_int * T)(); vals = (ctypes.c_float * T)()

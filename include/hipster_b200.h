@@ -105,6 +105,7 @@ typedef struct hp_model_cfg {
     int n_expert, n_expert_used, expert_ff;   /* n_expert = 0: dense SwiGLU FFN; else routed experts + 1 shared expert */
     int gdn_sigmoid_gate;        /* GDN output gate: 0 = silu(z) (27B), 1 = sigmoid(z) (Flash-Next) */
     int has_mtp;
+    int ep_rank, ep_world;       /* expert parallelism: this GPU holds routed experts [ep_rank*n_expert/ep_world, ...); 0, 1 = all */
     float rms_eps, rope_base;
     unsigned long long seed;     /* weights are random-init, generated on the device from this seed */
 } hp_model_cfg;
@@ -139,6 +140,16 @@ const float* hp_logits_dev(const hp_engine* e);            /* qwen35.h:82 */
 const float* hp_h_nextn_dev(const hp_engine* e);           /* qwen35.h:83 */
 const float* hp_mtp_logits_dev(const hp_engine* e);        /* qwen35.h:84 */
 const float* hp_mtp_h_dev(const hp_engine* e);             /* qwen35.h:85 */
+/* MTP block over the rows of S slots in one pass (rows in request order, h_dev holds one row of n_embd floats per
+ * request row). Replaces Qwen4Exp::mtp_forward(reqs, S, h) (qwen4exp.h:66-70). */
+int hp_mtp_forward_slots(hp_engine* e, const hp_slot_req* reqs, int S, const float* h_dev);
+/* Expert parallelism for the MoE configuration (no counterpart in the single-GPU reference): the routed experts are
+ * sharded over ep_world GPUs of one node (cfg.ep_rank / cfg.ep_world at load), everything else is replicated. Per MoE
+ * layer the per-(row, slot) expert outputs are exchanged with one NCCL collective and combined in slot order on every
+ * GPU, so each slot's stream stays bit-identical to its single-GPU run. hp_ep_unique_id fills 128 bytes on one rank;
+ * the caller distributes them (e.g. through torch.distributed) and every rank calls hp_ep_init with the same bytes. */
+int hp_ep_unique_id(void* id128_out);
+int hp_ep_init(hp_engine* e, const void* id128);
 /* Test/diagnostic access: device pointer and size of a generated tensor (layer = -1 for model-level tensors) and of a
  * slot's committed GDN state [gdn_v_heads][128][128] (pending accepts are applied first). */
 int hp_tensor_dev(const hp_engine* e, int layer, int kind, void** ptr_out, size_t* bytes_out);

@@ -288,7 +288,7 @@ extern "C" void orc_gemv_q4k_q8_seq(const uint8_t* W, const int8_t* q, const flo
 // ---------------------------------------------------------------- engine (engine/src/qwen35.cpp restated on the CPU)
 struct OrcCfg {   // mirrors hp_model_cfg field for field
     int n_embd, n_layer, n_ff, n_vocab, n_head, n_head_kv, n_rot, gdn_qk_heads, gdn_v_heads, attn_every, max_ctx, n_slots;
-    int n_expert, n_expert_used, expert_ff, gdn_sigmoid_gate, has_mtp; float rms_eps, rope_base; unsigned long long seed;
+    int n_expert, n_expert_used, expert_ff, gdn_sigmoid_gate, has_mtp, ep_rank, ep_world; float rms_eps, rope_base; unsigned long long seed;
 };
 namespace {
 struct OLin { std::vector<uint8_t> w; int N = 0, K = 0; };
