@@ -105,6 +105,7 @@ __global__ void k_spec_catchup_setup(const int* __restrict__ sp, int* __restrict
     if (t == 0) { d[D_GROUPS] = 0; d[D_GROUPS + 1] = n; d[D_GROUPS + 2] = slot; d[D_GROUPS + 3] = sp[SP_POS_OLD] + 1; }
 }
 
+#define HP_TRY(x) do { const int rc_ = (x); if (rc_ != HP_OK) return rc_; } while (0)
 // descriptor layout (ints)
 Engine::Engine(const hp_model_cfg& cfg) : c_(cfg) {}
 Engine::~Engine() {
@@ -130,7 +131,17 @@ int Engine::gen_lin(Lin& l, int N, int K, uint64_t tid) {
     const size_t nwords = l.bytes / 8;
     k_gen_q4k<<<(unsigned)((nwords + 255) / 256), 256, 0, s_>>>((uint64_t*)l.w, nwords, c_.seed, tid, 0);
     HP_CUDA(cudaGetLastError());
-    weight_bytes_ += l.bytes; return HP_OK;
+    weight_bytes_ += l.bytes;
+    if (tiled_) {   // the GEMV streams the tile-major copy; the row-major original is kept only for small (test) models
+        HP_TRY(alloc((void**)&l.wt, gemv_tiled_bytes(N, K)));
+        HP_TRY(gemv_repack_tiled(l.w, l.wt, N, K, s_));
+        if (!keep_rowmajor_) {
+            HP_CUDA(cudaStreamSynchronize(s_));
+            for (size_t i = 0; i < allocs_.size(); ++i) if (allocs_[i] == l.w) { allocs_.erase(allocs_.begin() + i); break; }
+            HP_CUDA(cudaFree(l.w)); l.w = nullptr;
+        }
+    }
+    return HP_OK;
 }
 int Engine::gen_raw_q4k(Lin& l, size_t rows, int K, uint64_t tid, size_t row0, size_t nrows_local) {   // expert stacks: no GEMV partition attached
     // rows [row0, row0 + nrows_local) of a tensor of `rows` rows are generated; l.w is offset so that it can be indexed
@@ -158,7 +169,6 @@ int Engine::gen_f32(float** p, size_t n, uint64_t tid, float mean, float std, bo
     HP_CUDA(cudaGetLastError()); weight_bytes_ += n * 4; return HP_OK;
 }
 
-#define HP_TRY(x) do { const int rc_ = (x); if (rc_ != HP_OK) return rc_; } while (0)
 static inline uint64_t tensor_id(int layer, int kind) { return (uint64_t)(layer + 1) * 64 + (uint64_t)kind; }
 
 int Engine::init() {
@@ -170,6 +180,8 @@ int Engine::init() {
     HP_REQUIRE(c.ep_world <= 1 || (c.n_expert > 0 && c.ep_rank >= 0 && c.ep_rank < c.ep_world && c.n_expert % c.ep_world == 0), "bad expert-parallel configuration");
     HP_REQUIRE(c.n_expert == 0 ? (c.n_ff > 0 && c.n_ff % 256 == 0) : (c.expert_ff % 256 == 0 && c.n_expert_used >= 1 && c.n_expert_used <= 15), "bad FFN shape");
     HP_CUDA(cudaStreamCreateWithFlags(&s_, cudaStreamNonBlocking));
+    tiled_ = getenv("HIPSTER_B200_ROWMAJOR") == nullptr;
+    keep_rowmajor_ = (size_t)c.n_layer * c.n_embd * (size_t)std::max(c.n_ff, 1) < ((size_t)1 << 28);   // small models keep both layouts (tensor access in tests)
     HP_CUDA(cudaEventCreate(&ev0_)); HP_CUDA(cudaEventCreate(&ev1_));
     const int E = c.n_embd, nv = c.gdn_v_heads, nq = c.gdn_qk_heads;
     const int gdn_in = (2 * nq + nv) * 128 + nv * 128 + 2 * nv, attn_in = c.n_head * 512 + 2 * c.n_head_kv * 256;
@@ -298,10 +310,10 @@ int Engine::reset_slot(int slot) {
 int Engine::upload_desc() { HP_CUDA(cudaMemcpyAsync(d_desc_, h_desc_, D_INTS * 4, cudaMemcpyHostToDevice, s_)); return HP_OK; }
 
 int Engine::lin_parts(const Lin& l, int R) {
-    return gemv_q4k_q8_parts(l.w, xq_, yparts_, l.N, l.K, R, l.N, (size_t)R * l.N, err_, s_, pdl_);
+    return gemv_q4k_q8_parts(l.wt ? l.wt : l.w, xq_, yparts_, l.N, l.K, R, l.N, (size_t)R * l.N, err_, s_, pdl_, l.wt != nullptr);
 }
 int Engine::lin(const Lin& l, float* out, int ld, int R) {
-    if (l.P == 1) return gemv_q4k_q8_parts(l.w, xq_, out, l.N, l.K, R, ld, 0, err_, s_, pdl_);
+    if (l.P == 1) return gemv_q4k_q8_parts(l.wt ? l.wt : l.w, xq_, out, l.N, l.K, R, ld, 0, err_, s_, pdl_, l.wt != nullptr);
     HP_TRY(lin_parts(l, R));
     k_reduce_planes<<<dim3((l.N + 255) / 256, R), 256, 0, s_>>>(yparts_, (size_t)R * l.N, l.P, out, l.N, ld);
     HP_CUDA(cudaGetLastError()); return HP_OK;
@@ -546,7 +558,7 @@ int Engine::tensor(int layer, int kind, void** ptr, size_t* bytes) const {
     switch (kind) {
         case TK_ATTN_NORM: return set(L.attn_norm, (size_t)E * 2);
         case TK_POST_NORM: return set(L.post_norm, (size_t)E * 2);
-        case TK_IN_PROJ: return set(L.in_proj.w, L.in_proj.bytes);
+        case TK_IN_PROJ: HP_REQUIRE(L.in_proj.w, "the row-major copy of this tensor was released after repacking"); return set(L.in_proj.w, L.in_proj.bytes);
         case TK_OUT_PROJ: return set(L.out_proj.w, L.out_proj.bytes);
         case TK_GATE_UP: return set(L.gate_up.w, L.gate_up.bytes);
         case TK_DOWN: return set(L.down.w, L.down.bytes);

@@ -12,7 +12,7 @@
 
 namespace hp {
 
-struct Lin { uint8_t* w = nullptr; int N = 0, K = 0, P = 1; size_t bytes = 0; };   // merged Q4_K matrix [N][K/256 blocks]
+struct Lin { uint8_t* w = nullptr; uint8_t* wt = nullptr; int N = 0, K = 0, P = 1; size_t bytes = 0; };   // merged Q4_K matrix [N][K/256 blocks]; wt = tile-major copy
 
 struct LayerW {
     bool is_attn = false;
@@ -99,7 +99,7 @@ private:
     cudaStream_t s_ = nullptr; cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
     std::vector<void*> allocs_;
     size_t weight_bytes_ = 0; float last_ms_ = 0;
-    int last_rows_ = 0; bool gemv_only_ = false; bool pdl_ = getenv("HIPSTER_B200_NO_PDL") == nullptr;
+    int last_rows_ = 0; bool gemv_only_ = false, tiled_ = true, keep_rowmajor_ = true; bool pdl_ = getenv("HIPSTER_B200_NO_PDL") == nullptr;
 };
 
 }  // namespace hp

@@ -29,9 +29,13 @@ namespace {
 constexpr int SK_STAGES = GEMV_STAGES;
 constexpr int SK_THREADS = GEMV_WARPS * 32;
 constexpr int SK_SCR_BYTES = 8 * 16 * 16;          // per warp: [8 sub-blocks][16 rows] float4 {s0, s0, -m, -m}
-template <int CB> struct SkGeom {
+// Two weight layouts. Row-major ggml (TILED = false): a stage holds 16 row pieces of CB blocks, one bulk copy per row.
+// Tile-major (TILED = true, the engine repacks to it at load; same bytes, permuted): for every 16-row tile and block a
+// contiguous 2304-byte chunk = 16 headers (16 B each) + nibbles stored [j][lane][row g 8 B | row g+8 8 B], so a stage
+// is ONE bulk copy and every lane fetches its two rows of a 64-element group with one 128-bit shared-memory load.
+template <int CB, bool TILED> struct SkGeom {
     static constexpr int ROW_STRIDE = CB == 2 ? 288 : 160;   // 288 = 2*128+32, 160 = 128+32: rows land on distinct 32-byte bank groups
-    static constexpr int STAGE_BYTES = 16 * ROW_STRIDE;
+    static constexpr int STAGE_BYTES = TILED ? CB * 2304 : 16 * ROW_STRIDE;
     static constexpr int FIXED = GEMV_WARPS * SK_STAGES * STAGE_BYTES + GEMV_WARPS * SK_SCR_BYTES + 1024;
 };
 
@@ -58,11 +62,11 @@ __device__ __forceinline__ void fma2(float2& acc, float2 a, float2 b) {   // acc
         : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)));
 }
 
-template <int NT, int CB>
+template <int NT, int CB, bool TILED>
 __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __restrict__ W, const uint4* __restrict__ xq, const float4* __restrict__ xsc,
                                                                 float* __restrict__ y, int N, int nb, int P, int R, int ldy, size_t part_stride,
                                                                 int* __restrict__ err) {
-    using Geo = SkGeom<CB>;
+    using Geo = SkGeom<CB, TILED>;
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* ring_all = smem;
     float4* scr_all = reinterpret_cast<float4*>(smem + GEMV_WARPS * SK_STAGES * Geo::STAGE_BYTES);
@@ -97,17 +101,24 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
     // issue cursor (tile, chunk) of the next unit to fetch; advanced incrementally, no divisions in the loop
     const int first_tile = ct.t0 + (nunits ? u0 / C : 0);
     int it_tile = first_tile, it_chunk = nunits ? u0 % C : 0, it_i = 0;
-    const uint8_t* it_src = W + ((size_t)it_tile * 16 + (lane & 15)) * row_bytes + (size_t)(kb0 + it_chunk * CB) * 144;
-    const uint32_t ring_lane = smem_u32(ring) + (lane & 15) * Geo::ROW_STRIDE;
+    const uint8_t* it_src = TILED ? W + ((size_t)it_tile * nb + kb0 + it_chunk * CB) * 2304
+                                  : W + ((size_t)it_tile * 16 + (lane & 15)) * row_bytes + (size_t)(kb0 + it_chunk * CB) * 144;
+    const uint32_t ring_lane = smem_u32(ring) + (TILED ? 0 : (lane & 15) * Geo::ROW_STRIDE);
     auto issue = [&]() {
         const int s = it_i % SK_STAGES;
-        const int nrows = min(16, N - it_tile * 16);
         const uint32_t bar = bar0 + 8 * s;
-        if (lane == 0) mbar_expect_tx(bar, unit_bytes * (uint32_t)nrows);
-        __syncwarp();
-        if (lane < nrows) bulk_g2s(ring_lane + s * Geo::STAGE_BYTES, it_src, unit_bytes, bar);
-        ++it_i; ++it_chunk; it_src += unit_bytes;
-        if (it_chunk == C) { it_chunk = 0; ++it_tile; it_src += (size_t)16 * row_bytes - (size_t)C * unit_bytes; }
+        if constexpr (TILED) {
+            if (lane == 0) { mbar_expect_tx(bar, CB * 2304u); bulk_g2s(ring_lane + s * Geo::STAGE_BYTES, it_src, CB * 2304u, bar); }
+            ++it_i; ++it_chunk; it_src += CB * 2304;
+            if (it_chunk == C) { it_chunk = 0; ++it_tile; it_src += (size_t)(nb - C * CB) * 2304; }
+        } else {
+            const int nrows = min(16, N - it_tile * 16);
+            if (lane == 0) mbar_expect_tx(bar, unit_bytes * (uint32_t)nrows);
+            __syncwarp();
+            if (lane < nrows) bulk_g2s(ring_lane + s * Geo::STAGE_BYTES, it_src, unit_bytes, bar);
+            ++it_i; ++it_chunk; it_src += unit_bytes;
+            if (it_chunk == C) { it_chunk = 0; ++it_tile; it_src += (size_t)16 * row_bytes - (size_t)C * unit_bytes; }
+        }
     };
     // the weight stream does not depend on the previous kernel: prime the ring before waiting for it
     for (int i = 0; i < SK_STAGES && i < nunits; ++i) issue();
@@ -160,8 +171,9 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
     };
 
     // per-lane constant offsets
-    const uint32_t w_lane = g * Geo::ROW_STRIDE + 16 + 8 * t;            // weights: row g (+8 rows: + 8*ROW_STRIDE)
-    const uint32_t hdr_lane = (lane >> 1) * Geo::ROW_STRIDE;             // pre-pass: row lane/2
+    const uint32_t w_lane = TILED ? 256 + lane * 16 : g * Geo::ROW_STRIDE + 16 + 8 * t;   // weights: row g (+8 rows: + 8*ROW_STRIDE)
+    const uint32_t hdr_lane = TILED ? (lane >> 1) * 16 : (lane >> 1) * Geo::ROW_STRIDE;  // pre-pass: row lane/2
+    constexpr int BLK_STRIDE = TILED ? 2304 : 144;
     const int hf = lane & 1;
     float4* scr_w = scr + (4 * hf) * 16 + (lane >> 1);                   // pre-pass writes sub-blocks 4hf..4hf+3 of its row
     const float4* scr_r = scr + g;
@@ -184,7 +196,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
 #pragma unroll
         for (int blk = 0; blk < CB; ++blk) {
             {   // scale pre-pass: lane -> (row = lane/2, half = lane&1) decodes sub-blocks 4hf..4hf+3 of its row
-                const uint4 hdr = *reinterpret_cast<const uint4*>(st + hdr_lane + blk * 144);
+                const uint4 hdr = *reinterpret_cast<const uint4*>(st + hdr_lane + blk * BLK_STRIDE);
                 const float d = h2f((uint16_t)(hdr.x & 0xFFFF)), nd = -h2f((uint16_t)(hdr.x >> 16));
                 const uint32_t scv = hf ? ((hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u)) : (hdr.y & 0x3F3F3F3Fu);
                 const uint32_t mnv = hf ? (((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u)) : (hdr.z & 0x3F3F3F3Fu);
@@ -200,8 +212,14 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
             __syncwarp();
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const uint2 w0 = *reinterpret_cast<const uint2*>(st + w_lane + blk * 144 + 32 * j);
-                const uint2 w1 = *reinterpret_cast<const uint2*>(st + w_lane + 8 * Geo::ROW_STRIDE + blk * 144 + 32 * j);
+                uint2 w0, w1;
+                if constexpr (TILED) {
+                    const uint4 ww = *reinterpret_cast<const uint4*>(st + w_lane + blk * 2304 + 512 * j);
+                    w0 = make_uint2(ww.x, ww.y); w1 = make_uint2(ww.z, ww.w);
+                } else {
+                    w0 = *reinterpret_cast<const uint2*>(st + w_lane + blk * 144 + 32 * j);
+                    w1 = *reinterpret_cast<const uint2*>(st + w_lane + 8 * Geo::ROW_STRIDE + blk * 144 + 32 * j);
+                }
                 const uint32_t alo[4] = {w0.x & 0x0F0F0F0Fu, w1.x & 0x0F0F0F0Fu, w0.y & 0x0F0F0F0Fu, w1.y & 0x0F0F0F0Fu};
                 const uint32_t ahi[4] = {w0.x & 0xF0F0F0F0u, w1.x & 0xF0F0F0F0u, w0.y & 0xF0F0F0F0u, w1.y & 0xF0F0F0F0u};
                 const float4 sa0 = scr_r[(2 * j) * 16], sb0 = scr_r[(2 * j) * 16 + 8];          // low-nibble sub-block: rows g, g+8
@@ -331,27 +349,46 @@ __global__ void __launch_bounds__(256) k_gemv_q4k_f32(const uint8_t* __restrict_
         for (int c = 0; c < NCOL; ++c) y[(size_t)c * N + row] = acc[c];
 }
 
-template <int NT, int CB>
+template <int NT, int CB, bool TILED>
 int launch_sk2(const uint8_t* W, const void* xq, const void* xsc, float* y, int N, int nb, int P, int R, int ldy, size_t part_stride,
                int* err, cudaStream_t s, bool pdl) {
-    const size_t smem = SkGeom<CB>::FIXED + (size_t)NT * (nb / P) * 2560;
+    const size_t smem = SkGeom<CB, TILED>::FIXED + (size_t)NT * (nb / P) * 2560;
     static size_t attr_smem = 0;
-    if (smem > attr_smem) { HP_CUDA(cudaFuncSetAttribute(k_gemv_q4k_sk<NT, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr_smem = smem; }
+    if (smem > attr_smem) { HP_CUDA(cudaFuncSetAttribute(k_gemv_q4k_sk<NT, CB, TILED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr_smem = smem; }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(GEMV_NCTA); cfg.blockDim = dim3(SK_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = s;
     cudaLaunchAttribute at[1]; at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at; cfg.numAttrs = pdl ? 1 : 0;
-    HP_CUDA(cudaLaunchKernelEx(&cfg, k_gemv_q4k_sk<NT, CB>, W, (const uint4*)xq, (const float4*)xsc, y, N, nb, P, R, ldy, part_stride, err));
+    HP_CUDA(cudaLaunchKernelEx(&cfg, k_gemv_q4k_sk<NT, CB, TILED>, W, (const uint4*)xq, (const float4*)xsc, y, N, nb, P, R, ldy, part_stride, err));
     return HP_OK;
 }
 template <int NT>
-int launch_sk(const uint8_t* W, const void* xq, const void* xsc, float* y, int N, int nb, int P, int R, int ldy, size_t part_stride,
+int launch_sk(const uint8_t* W, bool tiled, const void* xq, const void* xsc, float* y, int N, int nb, int P, int R, int ldy, size_t part_stride,
               int* err, cudaStream_t s, bool pdl) {
+    const bool cb2 = (nb / P) % 2 == 0;
 #ifdef HP_FORCE_CB1
-    return launch_sk2<NT, 1>(W, xq, xsc, y, N, nb, P, R, ldy, part_stride, err, s, pdl);
+    if (tiled) return launch_sk2<NT, 1, true>(W, xq, xsc, y, N, nb, P, R, ldy, part_stride, err, s, pdl);
 #endif
-    return ((nb / P) % 2 == 0) ? launch_sk2<NT, 2>(W, xq, xsc, y, N, nb, P, R, ldy, part_stride, err, s, pdl)
-                               : launch_sk2<NT, 1>(W, xq, xsc, y, N, nb, P, R, ldy, part_stride, err, s, pdl);
+    if (tiled) return cb2 ? launch_sk2<NT, 2, true>(W, xq, xsc, y, N, nb, P, R, ldy, part_stride, err, s, pdl)
+                          : launch_sk2<NT, 1, true>(W, xq, xsc, y, N, nb, P, R, ldy, part_stride, err, s, pdl);
+    return cb2 ? launch_sk2<NT, 2, false>(W, xq, xsc, y, N, nb, P, R, ldy, part_stride, err, s, pdl)
+               : launch_sk2<NT, 1, false>(W, xq, xsc, y, N, nb, P, R, ldy, part_stride, err, s, pdl);
+}
+
+// row-major ggml blocks -> tile-major chunks (see SkGeom); rows beyond N are zero (they contribute nothing)
+__global__ void __launch_bounds__(256) k_repack_tiled(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int N, int nb) {
+    const size_t chunk = blockIdx.x;                       // (tile, block)
+    const int tile = (int)(chunk / nb), b = (int)(chunk % nb);
+    uint8_t* out = dst + chunk * 2304;
+    for (int i = threadIdx.x; i < 2304 / 4; i += 256) {    // one 32-bit word per step
+        const int o = i * 4; uint32_t v = 0;
+        int row, off;                                      // source row in the tile and byte offset in its 144-byte block
+        if (o < 256) { row = o / 16; off = o % 16; }
+        else { const int q = o - 256, j = q / 512, lane = (q % 512) / 16, w = q % 16, g = lane >> 2, t = lane & 3; row = g + (w >= 8 ? 8 : 0); off = 16 + 32 * j + 8 * t + (w & 7); }
+        const int r = tile * 16 + row;
+        if (r < N) v = *reinterpret_cast<const uint32_t*>(src + ((size_t)r * nb + b) * 144 + off);
+        *reinterpret_cast<uint32_t*>(out + o) = v;
+    }
 }
 
 // sum the K-part planes in part order: y[r][n] = ((p0 + p1) + p2) + p3
@@ -367,7 +404,14 @@ __global__ void k_reduce_parts(const float* __restrict__ parts, size_t part_stri
 
 int gemv_parts(int N, int K) { return gemv_num_parts(N, K / 256); }
 
-int gemv_q4k_q8_parts(const void* W, const XQ8F& x, float* yparts, int N, int K, int R, int ldy, size_t part_stride, int* err, cudaStream_t s, bool pdl) {
+size_t gemv_tiled_bytes(int N, int K) { return (size_t)((N + 15) / 16) * (K / 256) * 2304; }
+int gemv_repack_tiled(const void* src, void* dst, int N, int K, cudaStream_t s) {
+    HP_REQUIRE(N > 0 && K > 0 && K % 256 == 0, "gemv_repack_tiled: bad shape");
+    k_repack_tiled<<<(unsigned)(((size_t)(N + 15) / 16) * (K / 256)), 256, 0, s>>>((const uint8_t*)src, (uint8_t*)dst, N, K / 256);
+    HP_CUDA(cudaGetLastError()); return HP_OK;
+}
+
+int gemv_q4k_q8_parts(const void* W, const XQ8F& x, float* yparts, int N, int K, int R, int ldy, size_t part_stride, int* err, cudaStream_t s, bool pdl, bool tiled) {
     HP_REQUIRE(K > 0 && K % 256 == 0, "gemv_q4k_q8: K=%d must be a positive multiple of 256", K);
     HP_REQUIRE(N > 0 && R >= 1 && R <= 32 && ldy >= N, "gemv_q4k_q8: bad shape N=%d R=%d ldy=%d", N, R, ldy);
     const int nb = K / 256, P = gemv_num_parts(N, nb);
@@ -375,7 +419,7 @@ int gemv_q4k_q8_parts(const void* W, const XQ8F& x, float* yparts, int N, int K,
     const int ntile = (R + 7) / 8, nbp = nb / P;
     // all column tiles in one launch when their activations fit in shared memory beside the rings; otherwise one
     // launch per tile of 8 columns (same per-column arithmetic either way)
-    const bool fused = ntile == 1 || (size_t)SkGeom<2>::FIXED + (size_t)ntile * nbp * 2560 <= (size_t)GEMV_SMEM_LIMIT;
+    const bool fused = ntile == 1 || (size_t)SkGeom<2, false>::FIXED + (size_t)ntile * nbp * 2560 <= (size_t)GEMV_SMEM_LIMIT;
     for (int c0 = 0; c0 < ntile; c0 += fused ? ntile : 1) {
         const int nt = fused ? ntile : 1;
         const int Rl = min(R - c0 * 8, nt * 8);
@@ -384,10 +428,10 @@ int gemv_q4k_q8_parts(const void* W, const XQ8F& x, float* yparts, int N, int K,
         float* yp = yparts + (size_t)c0 * 8 * ldy;
         int rc;
         switch (nt) {
-            case 1: rc = launch_sk<1>((const uint8_t*)W, xqp, xsp, yp, N, nb, P, Rl, ldy, part_stride, err, s, pdl); break;
-            case 2: rc = launch_sk<2>((const uint8_t*)W, xqp, xsp, yp, N, nb, P, Rl, ldy, part_stride, err, s, pdl); break;
-            case 3: rc = launch_sk<3>((const uint8_t*)W, xqp, xsp, yp, N, nb, P, Rl, ldy, part_stride, err, s, pdl); break;
-            default: rc = launch_sk<4>((const uint8_t*)W, xqp, xsp, yp, N, nb, P, Rl, ldy, part_stride, err, s, pdl); break;
+            case 1: rc = launch_sk<1>((const uint8_t*)W, tiled, xqp, xsp, yp, N, nb, P, Rl, ldy, part_stride, err, s, pdl); break;
+            case 2: rc = launch_sk<2>((const uint8_t*)W, tiled, xqp, xsp, yp, N, nb, P, Rl, ldy, part_stride, err, s, pdl); break;
+            case 3: rc = launch_sk<3>((const uint8_t*)W, tiled, xqp, xsp, yp, N, nb, P, Rl, ldy, part_stride, err, s, pdl); break;
+            default: rc = launch_sk<4>((const uint8_t*)W, tiled, xqp, xsp, yp, N, nb, P, Rl, ldy, part_stride, err, s, pdl); break;
         }
         if (rc != HP_OK) return rc;
     }
@@ -397,10 +441,10 @@ int gemv_q4k_q8_parts(const void* W, const XQ8F& x, float* yparts, int N, int K,
 int gemv_q4k_q8(const void* W, const XQ8F& x, float* y, int N, int K, int R, int ldy, const GemvWorkspace& ws, cudaStream_t s, bool pdl) {
     HP_REQUIRE(K > 0 && K % 256 == 0 && N > 0, "gemv_q4k_q8: bad shape N=%d K=%d", N, K);
     const int P = gemv_num_parts(N, K / 256);
-    if (P == 1) return gemv_q4k_q8_parts(W, x, y, N, K, R, ldy, 0, ws.err, s, pdl);
+    if (P == 1) return gemv_q4k_q8_parts(W, x, y, N, K, R, ldy, 0, ws.err, s, pdl, false);
     HP_REQUIRE(ws.part && (size_t)P * R * N * sizeof(float) <= ws.part_bytes, "gemv_q4k_q8: workspace too small for %d K-part planes of %d x %d", P, R, N);
     const size_t stride = (size_t)R * N;
-    const int rc = gemv_q4k_q8_parts(W, x, ws.part, N, K, R, N, stride, ws.err, s, pdl);
+    const int rc = gemv_q4k_q8_parts(W, x, ws.part, N, K, R, N, stride, ws.err, s, pdl, false);
     if (rc != HP_OK) return rc;
     k_reduce_parts<<<dim3((N + 255) / 256, R), 256, 0, s>>>(ws.part, stride, P, y, N, R, N, ldy);
     HP_CUDA(cudaGetLastError());

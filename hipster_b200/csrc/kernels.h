@@ -52,7 +52,10 @@ __host__ __device__ inline int gemv_warp_owner(int cu, int weff, int u) { return
 struct GemvWorkspace { float* part; size_t part_bytes; int* err; };
 int gemv_parts(int N, int K);
 // raw form: part p of the K split writes plane yparts + p * part_stride ([R][ldy] each); the caller adds the planes in order
-int gemv_q4k_q8_parts(const void* W, const XQ8F& x, float* yparts, int N, int K, int R, int ldy, size_t part_stride, int* err, cudaStream_t s, bool pdl);
+// tiled = true: W is in the tile-major layout produced by gemv_repack_tiled (gemv_tiled_bytes(N, K) bytes)
+int gemv_q4k_q8_parts(const void* W, const XQ8F& x, float* yparts, int N, int K, int R, int ldy, size_t part_stride, int* err, cudaStream_t s, bool pdl, bool tiled);
+size_t gemv_tiled_bytes(int N, int K);
+int gemv_repack_tiled(const void* src, void* dst, int N, int K, cudaStream_t s);
 int gemv_q4k_q8(const void* W, const XQ8F& x, float* y, int N, int K, int R, int ldy, const GemvWorkspace& ws, cudaStream_t s, bool pdl);
 int gemv_q4k_f32(const void* W, const float* x, float* y, int N, int K, int R, cudaStream_t s);
 
