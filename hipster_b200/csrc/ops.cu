@@ -145,10 +145,10 @@ struct GdnArgs {
     float* snap; size_t snap_row_stride;                          // optional state snapshots after each new row
     float eps; int sigmoid_gate;
 };
-constexpr int GDN_MAXROWS = 16;   // replayed rows (<= 8) + new rows (<= 8) of one sequence
+constexpr int GDN_MAXROWS = 16, GDN_STG_LD = 132;   // replayed rows (<= 8) + new rows (<= 8) of one sequence
 __global__ void __launch_bounds__(256) k_gdn(GdnArgs a) {
     constexpr int D = 128;
-    __shared__ float sq[GDN_MAXROWS][D], sk[GDN_MAXROWS][D], sv[GDN_MAXROWS][D], sout[8][D];
+    __shared__ __align__(16) float sq[GDN_MAXROWS][D], sk[GDN_MAXROWS][D], sv[GDN_MAXROWS][D], sout[8][D];
     __shared__ float red[GDN_MAXROWS * 2][8], tot[GDN_MAXROWS * 2], sbeta[GDN_MAXROWS], sdecay[GDN_MAXROWS];
     pdl_launch_dependents();
     pdl_wait();
@@ -159,13 +159,32 @@ __global__ void __launch_bounds__(256) k_gdn(GdnArgs a) {
     const int nrows = nrep + T;
     const int Z = a.n_v * D;
     const int j = tid >> 1, ih = tid & 1;
-    float* Mst = a.state + (size_t)slot * a.state_stride + ((size_t)h * D + j) * D + 64 * ih;
     // conv history of this head: [3 taps][q 128 | k 128 | v 128]; private per v-head so that no CTA reads what another writes
     float* cst = a.conv_state + (size_t)slot * a.conv_stride + (size_t)h * 3 * 384;
     const int sa_ = tid < D ? tid : D + tid, sb_ = D + (tid & (D - 1));   // history / saved-row slots of channels ca / cb
+    // the 64 KB state of this head moves between HBM and registers through shared memory, so that global accesses are
+    // fully coalesced 128-bit rows (each thread owns 64 consecutive floats of one state row)
+    extern __shared__ __align__(16) float stg[];                 // [128][GDN_STG_LD]
+    float* Mhead = a.state + (size_t)slot * a.state_stride + (size_t)h * D * D;
+    for (int idx = tid; idx < D * D / 4; idx += 256) {
+        const float4 v = reinterpret_cast<const float4*>(Mhead)[idx];
+        *reinterpret_cast<float4*>(stg + (idx >> 5) * GDN_STG_LD + (idx & 31) * 4) = v;
+    }
+    __syncthreads();
     float m[64];
 #pragma unroll
-    for (int i = 0; i < 64; ++i) m[i] = Mst[i];
+    for (int i = 0; i < 64; i += 4) {
+        const float4 v = *reinterpret_cast<const float4*>(stg + j * GDN_STG_LD + 64 * ih + i);
+        m[i] = v.x; m[i + 1] = v.y; m[i + 2] = v.z; m[i + 3] = v.w;
+    }
+    auto commit_state = [&]() {   // block-uniform call sites only
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 64; i += 4) *reinterpret_cast<float4*>(stg + j * GDN_STG_LD + 64 * ih + i) = make_float4(m[i], m[i + 1], m[i + 2], m[i + 3]);
+        __syncthreads();
+        for (int idx = tid; idx < D * D / 4; idx += 256)
+            reinterpret_cast<float4*>(Mhead)[idx] = *reinterpret_cast<const float4*>(stg + (idx >> 5) * GDN_STG_LD + (idx & 31) * 4);
+    };
     // conv channels of this thread: ca (q for tid < 128, v otherwise), cb (k, tid < 128 only)
     const int ca = tid < D ? hk * D + tid : 2 * a.n_qk * D + h * D + (tid - D);
     const int cb = a.n_qk * D + hk * D + (tid & (D - 1));
@@ -245,20 +264,26 @@ __global__ void __launch_bounds__(256) k_gdn(GdnArgs a) {
 
     // ---- phase 2: the recurrence, row after row, state in registers; no block-wide synchronisation inside
     for (int it = 0; it < nrows; ++it) {
-        if (it == nrep && nrep > 0) {
-#pragma unroll
-            for (int i = 0; i < 64; ++i) Mst[i] = m[i];
-        }
+        if (it == nrep && nrep > 0) commit_state();
         const float beta = sbeta[it], decay = sdecay[it];
         const float* kk = &sk[it][64 * ih]; const float* qq = &sq[it][64 * ih];
+        float kr[64];
+#pragma unroll
+        for (int i = 0; i < 64; i += 4) { const float4 v = *reinterpret_cast<const float4*>(kk + i); kr[i] = v.x; kr[i + 1] = v.y; kr[i + 2] = v.z; kr[i + 3] = v.w; }
         float dot = 0.f;
 #pragma unroll
-        for (int i = 0; i < 64; ++i) { m[i] = m[i] * decay; dot = fmaf(m[i], kk[i], dot); }
+        for (int i = 0; i < 64; ++i) { m[i] = m[i] * decay; dot = fmaf(m[i], kr[i], dot); }
         dot = dot + __shfl_xor_sync(0xffffffffu, dot, 1);
         const float delta = (sv[it][j] - dot) * beta;
         float o = 0.f;
 #pragma unroll
-        for (int i = 0; i < 64; ++i) { m[i] = fmaf(delta, kk[i], m[i]); o = fmaf(m[i], qq[i], o); }
+        for (int i = 0; i < 64; i += 4) {
+            const float4 qv = *reinterpret_cast<const float4*>(qq + i);
+            m[i] = fmaf(delta, kr[i], m[i]); o = fmaf(m[i], qv.x, o);
+            m[i + 1] = fmaf(delta, kr[i + 1], m[i + 1]); o = fmaf(m[i + 1], qv.y, o);
+            m[i + 2] = fmaf(delta, kr[i + 2], m[i + 2]); o = fmaf(m[i + 2], qv.z, o);
+            m[i + 3] = fmaf(delta, kr[i + 3], m[i + 3]); o = fmaf(m[i + 3], qv.w, o);
+        }
         o = o + __shfl_xor_sync(0xffffffffu, o, 1);
         if (it >= nrep) {
             if (ih == 0) sout[it - nrep][j] = o * 0.08838834764831845f;
@@ -269,10 +294,7 @@ __global__ void __launch_bounds__(256) k_gdn(GdnArgs a) {
             }
         }
     }
-    if (T == 0 && nrep > 0) {
-#pragma unroll
-        for (int i = 0; i < 64; ++i) Mst[i] = m[i];
-    }
+    if (T == 0 && nrep > 0) commit_state();
     __syncthreads();
 
     // ---- phase 3: per-head RMSNorm * w * gate(z) + quantisation of the new rows
@@ -328,7 +350,9 @@ int gdn_forward(const GdnParams& p, int nseq, cudaStream_t s) {
     a.state = p.state; a.conv_state = p.conv_state; a.state_stride = p.state_stride; a.conv_stride = p.conv_stride;
     a.seq = p.seq; a.replay_n = p.replay_n; a.out = p.out; a.oq = (int8_t*)p.xq.q; a.osc = (float*)p.xq.sc;
     a.snap = p.snap; a.snap_row_stride = p.snap_row_stride; a.eps = p.eps; a.sigmoid_gate = p.sigmoid_gate;
-    launch_pdl(k_gdn, dim3(p.n_v, nseq), dim3(256), 0, s, a);
+    static bool attr = false;
+    if (!attr) { HP_CUDA(cudaFuncSetAttribute(k_gdn, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * GDN_STG_LD * 4)); attr = true; }
+    HP_CUDA(launch_pdl(k_gdn, dim3(p.n_v, nseq), dim3(256), 128 * GDN_STG_LD * 4, s, a));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 
