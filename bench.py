@@ -220,11 +220,13 @@ def run_dense(args, rank, local_rank, world):
     torch.cuda.synchronize()
     sampler = ClockSampler(local_rank) if rank == 0 else None
     toks = 0; dev_ms = 0.0
+    torch.cuda.profiler.start()      # lets `ncu --profile-from-start off` capture exactly the timed rounds
     t0 = time.perf_counter()
     for _ in range(args.steps):
         c, ms = one_round(); toks += c; dev_ms += ms
     torch.cuda.synchronize()
     wall_ms = (time.perf_counter() - t0) * 1e3
+    torch.cuda.profiler.stop()
     clocks = sampler.stop() if sampler else None
     exact = out[:len(plain)] == plain[:len(out)]
     # dominant kernel alone: the GEMV launches of one 6-row verify pass, CUDA events on the engine's stream

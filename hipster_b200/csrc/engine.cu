@@ -354,12 +354,11 @@ int Engine::moe_block(const LayerW& L, int R) {
     HP_TRY(moe_gemv_up(p, s_));
     HP_TRY(moe_silu_quant(moe_gu_, F, moe_ids_, e_lo_, e_hi_, own_shared_, xq2_, R * ns, s_));
     MoeParams d = p; d.w_exp = L.exp_down.w; d.w_sh = L.sh_down.w; d.ebytes = (size_t)E * (F / 256) * 144; d.N = E; d.K = F; d.xq = xq2_; d.slotw = moe_w_;
-    if (ep_world_ <= 1) { d.y = yparts_; return moe_down_combine(d, s_); }
-    // expert parallel: per-pair outputs of the experts this GPU owns (exact zeros elsewhere), exchanged, then combined in
-    // slot order on every GPU (identical arithmetic to the single-GPU combine)
+    // per-(row, slot) outputs of the experts this GPU owns (exact zeros for experts owned elsewhere), exchanged when
+    // the experts are sharded, then combined in slot order (the arithmetic of gemv.hip:1104-1112 on every GPU)
     d.y = moe_v_;
     HP_TRY(moe_down_pairs(d, s_));
-    HP_TRY(ep_exchange(moe_v_, (size_t)R * ns * E));
+    if (ep_world_ > 1) HP_TRY(ep_exchange(moe_v_, (size_t)R * ns * E));
     return moe_combine(moe_v_, moe_w_, ns, yparts_, R, E, s_);
 }
 

@@ -15,21 +15,19 @@ namespace {
 
 // ---- router: logits[t][e] = sum_k W[e][k] x[t][k], f32. One warp per weight row; lane l takes k = 4l + 128 i (float4),
 // four fmaf per step in element order, then the xor-shuffle tree (offsets 16..1). ----
-__global__ void __launch_bounds__(256) k_router_gemv(const float* __restrict__ W, const float* __restrict__ x, float* __restrict__ y, int N, int K, int T) {
-    const int n = (blockIdx.x * 256 + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+__global__ void __launch_bounds__(256) k_router_gemv(const float* __restrict__ W, const float* __restrict__ x, float* __restrict__ y, int N, int K) {
+    const int n = (blockIdx.x * 256 + threadIdx.x) >> 5, lane = threadIdx.x & 31, t = blockIdx.y;
     if (n >= N) return;
-    const float* w = W + (size_t)n * K;
-    for (int t = 0; t < T; ++t) {
-        const float* xr = x + (size_t)t * K;
-        float acc = 0.f;
-        for (int i = lane * 4; i < K; i += 128) {
-            const float4 a = *reinterpret_cast<const float4*>(w + i), b = *reinterpret_cast<const float4*>(xr + i);
-            acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc); acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
-        }
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) acc = acc + __shfl_xor_sync(0xffffffffu, acc, off);
-        if (lane == 0) y[(size_t)t * N + n] = acc;
+    const float* w = W + (size_t)n * K; const float* xr = x + (size_t)t * K;
+    float acc = 0.f;
+#pragma unroll 4
+    for (int i = lane * 4; i < K; i += 128) {
+        const float4 a = __ldg(reinterpret_cast<const float4*>(w + i)), b = *reinterpret_cast<const float4*>(xr + i);
+        acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc); acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
     }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc = acc + __shfl_xor_sync(0xffffffffu, acc, off);
+    if (lane == 0) y[(size_t)t * N + n] = acc;
 }
 
 // ---- routing: softmax over the first E logits, top-k by (value desc, index asc), weights renormalised by the sum of the
@@ -217,7 +215,7 @@ __global__ void __launch_bounds__(256) k_moe_silu_quant(const float* __restrict_
 
 int router_gemv(const float* W, const float* x, float* y, int N, int K, int T, cudaStream_t s) {
     HP_REQUIRE(N >= 1 && K > 0 && K % 128 == 0 && T >= 1, "router_gemv: bad shape N=%d K=%d T=%d", N, K, T);
-    k_router_gemv<<<(N * 32 + 255) / 256, 256, 0, s>>>(W, x, y, N, K, T);
+    k_router_gemv<<<dim3((N * 32 + 255) / 256, T), 256, 0, s>>>(W, x, y, N, K);
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 int moe_route(const float* logits, int* ids, float* w, int T, int E, int k, cudaStream_t s) {

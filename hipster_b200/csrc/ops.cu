@@ -148,8 +148,8 @@ struct GdnArgs {
 constexpr int GDN_MAXROWS = 16, GDN_STG_LD = 132;   // replayed rows (<= 8) + new rows (<= 8) of one sequence
 __global__ void __launch_bounds__(256) k_gdn(GdnArgs a) {
     constexpr int D = 128;
-    __shared__ __align__(16) float sq[GDN_MAXROWS][D], sk[GDN_MAXROWS][D], sv[GDN_MAXROWS][D], sout[8][D];
-    __shared__ float red[GDN_MAXROWS * 2][8], tot[GDN_MAXROWS * 2], sbeta[GDN_MAXROWS], sdecay[GDN_MAXROWS];
+    __shared__ __align__(16) float sall[GDN_MAXROWS][3 * D], sout[8][D];
+    __shared__ float red[GDN_MAXROWS * 2][8], tot[GDN_MAXROWS * 2], sbeta[GDN_MAXROWS], sdecay[GDN_MAXROWS], sraw_b[GDN_MAXROWS], sraw_a[GDN_MAXROWS];
     pdl_launch_dependents();
     pdl_wait();
     const int h = blockIdx.x, hk = h % a.n_qk, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -194,58 +194,49 @@ __global__ void __launch_bounds__(256) k_gdn(GdnArgs a) {
     const float wa0 = a.conv_w[ca * 4 + 0], wa1 = a.conv_w[ca * 4 + 1], wa2 = a.conv_w[ca * 4 + 2], wa3 = a.conv_w[ca * 4 + 3];
     const float wb0 = a.conv_w[cb * 4 + 0], wb1 = a.conv_w[cb * 4 + 1], wb2 = a.conv_w[cb * 4 + 2], wb3 = a.conv_w[cb * 4 + 3];
 
-    // ---- phase 1: raw inputs of all rows (one round of loads), conv + SiLU, squared norms, gates
-    float xa[GDN_MAXROWS], xb[GDN_MAXROWS];
-#pragma unroll
-    for (int it = 0; it < GDN_MAXROWS; ++it) {
-        xa[it] = 0.f; xb[it] = 0.f;
-        if (it < nrows) {
-            const bool replay = it < nrep;
-            const float* row = a.rows + (size_t)(replay ? 0 : r0 + (it - nrep)) * a.ld;
-            const float* srow = sav + (replay ? it : 0) * 388;
-            xa[it] = replay ? srow[sa_] : row[ca];
-            if (tid < D) xb[it] = replay ? srow[sb_] : row[cb];
-        }
+    // ---- phase 1: raw inputs of all rows fetched with asynchronous 4-byte copies (all in flight at once, compact
+    // code), then conv + SiLU in place, squared norms, gates. sall[it] = [q 128 | k 128 | v 128] of row it.
+    for (int it = 0; it < nrows; ++it) {
+        const bool replay = it < nrep;
+        const float* row = a.rows + (size_t)(replay ? 0 : r0 + (it - nrep)) * a.ld;
+        const float* srow = sav + (replay ? it : 0) * 388;
+        cp_async4(&sall[it][sa_], replay ? srow + sa_ : row + ca);
+        if (tid < D) cp_async4(&sall[it][sb_], replay ? srow + sb_ : row + cb);
+        if (tid == 0) { cp_async4(&sraw_b[it], replay ? srow + 384 : row + a.off_b + h); cp_async4(&sraw_a[it], replay ? srow + 385 : row + a.off_a + h); }
     }
+    cp_async_wait_all();
+    __syncthreads();
     if (tid < nrows) {
-        const bool replay = tid < nrep;
-        const float* row = a.rows + (size_t)(replay ? 0 : r0 + (tid - nrep)) * a.ld;
-        const float braw = replay ? sav[tid * 388 + 384] : row[a.off_b + h], araw = replay ? sav[tid * 388 + 385] : row[a.off_a + h];
-        sbeta[tid] = sigmoid_det(braw);
-        sdecay[tid] = expf_det(bf2f(a.a_neg[h]) * softplus_det(araw + bf2f(a.dt_bias[h])));
-        sq[tid][0] = braw; sk[tid][0] = araw;   // parked until the save below (overwritten afterwards)
+        sbeta[tid] = sigmoid_det(sraw_b[tid]);
+        sdecay[tid] = expf_det(bf2f(a.a_neg[h]) * softplus_det(sraw_a[tid] + bf2f(a.dt_bias[h])));
     }
-    __syncthreads();
-    // keep the raw inputs of the new rows for a later commit (after every replayed row has been read)
-#pragma unroll
-    for (int it = 0; it < GDN_MAXROWS; ++it)
-        if (it >= nrep && it < nrows) {
-            float* srow = sav + (it - nrep) * 388;
-            srow[sa_] = xa[it]; if (tid < D) srow[sb_] = xb[it];
-            if (tid == 0) { srow[384] = sq[it][0]; srow[385] = sk[it][0]; }
+    // keep the raw inputs of the new rows for a later commit (every replayed row has been read: they are in shared memory)
+    for (int it = nrep; it < nrows; ++it) {
+        float* srow = sav + (it - nrep) * 388;
+        srow[sa_] = sall[it][sa_]; if (tid < D) srow[sb_] = sall[it][sb_];
+        if (tid == 0) { srow[384] = sraw_b[it]; srow[385] = sraw_a[it]; }
+    }
+    for (int it = 0; it < nrows; ++it) {
+        if (it == nrep && nrep > 0) {   // history after the accepted prefix: committed
+            cst[sa_] = ha0; cst[384 + sa_] = ha1; cst[768 + sa_] = ha2;
+            if (tid < D) { cst[sb_] = hb0; cst[384 + sb_] = hb1; cst[768 + sb_] = hb2; }
         }
-    __syncthreads();
-    float va[GDN_MAXROWS], vb[GDN_MAXROWS];
-#pragma unroll
-    for (int it = 0; it < GDN_MAXROWS; ++it) {
-        va[it] = 0.f; vb[it] = 0.f;
-        if (it < nrows) {
-            if (it == nrep && nrep > 0) {   // history after the accepted prefix: committed
-                cst[sa_] = ha0; cst[384 + sa_] = ha1; cst[768 + sa_] = ha2;
-                if (tid < D) { cst[sb_] = hb0; cst[384 + sb_] = hb1; cst[768 + sb_] = hb2; }
-            }
-            float t = wa0 * ha0; t = fmaf(wa1, ha1, t); t = fmaf(wa2, ha2, t); t = fmaf(wa3, xa[it], t);
-            va[it] = silu_det(t); ha0 = ha1; ha1 = ha2; ha2 = xa[it];
-            if (tid < D) {
-                float u = wb0 * hb0; u = fmaf(wb1, hb1, u); u = fmaf(wb2, hb2, u); u = fmaf(wb3, xb[it], u);
-                vb[it] = silu_det(u); hb0 = hb1; hb1 = hb2; hb2 = xb[it];
-            }
-            // squared l2 norms: xor tree inside the warp, warp sums added in warp order afterwards
-            float pq = tid < D ? va[it] * va[it] : 0.f, pk = tid < D ? vb[it] * vb[it] : 0.f;
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) { pq = pq + __shfl_xor_sync(0xffffffffu, pq, off); pk = pk + __shfl_xor_sync(0xffffffffu, pk, off); }
-            if (lane == 0) { red[2 * it][warp] = pq; red[2 * it + 1][warp] = pk; }
+        const float xa = sall[it][sa_];
+        float t = wa0 * ha0; t = fmaf(wa1, ha1, t); t = fmaf(wa2, ha2, t); t = fmaf(wa3, xa, t);
+        const float va = silu_det(t); ha0 = ha1; ha1 = ha2; ha2 = xa;
+        sall[it][sa_] = va;
+        float vb = 0.f;
+        if (tid < D) {
+            const float xb = sall[it][sb_];
+            float u = wb0 * hb0; u = fmaf(wb1, hb1, u); u = fmaf(wb2, hb2, u); u = fmaf(wb3, xb, u);
+            vb = silu_det(u); hb0 = hb1; hb1 = hb2; hb2 = xb;
+            sall[it][sb_] = vb;
         }
+        // squared l2 norms: xor tree inside the warp, warp sums added in warp order afterwards
+        float pq = tid < D ? va * va : 0.f, pk = tid < D ? vb * vb : 0.f;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) { pq = pq + __shfl_xor_sync(0xffffffffu, pq, off); pk = pk + __shfl_xor_sync(0xffffffffu, pk, off); }
+        if (lane == 0) { red[2 * it][warp] = pq; red[2 * it + 1][warp] = pk; }
     }
     if (T == 0 && nrep > 0) {   // pure commit: the loop above never reached it == nrep
         cst[sa_] = ha0; cst[384 + sa_] = ha1; cst[768 + sa_] = ha2;
@@ -254,11 +245,10 @@ __global__ void __launch_bounds__(256) k_gdn(GdnArgs a) {
     __syncthreads();
     if (tid < 2 * nrows) { float t = red[tid][0]; for (int w = 1; w < 8; ++w) t = t + red[tid][w]; tot[tid] = t; }
     __syncthreads();
-#pragma unroll
-    for (int it = 0; it < GDN_MAXROWS; ++it)
-        if (it < nrows) {
-            if (tid < D) { sq[it][tid] = va[it] / fmaxf(sqrtf(tot[2 * it]), a.eps); sk[it][tid] = vb[it] / fmaxf(sqrtf(tot[2 * it + 1]), a.eps); }
-            else sv[it][tid - D] = va[it];
+    if (tid < D)
+        for (int it = 0; it < nrows; ++it) {
+            sall[it][tid] = sall[it][tid] / fmaxf(sqrtf(tot[2 * it]), a.eps);
+            sall[it][D + tid] = sall[it][D + tid] / fmaxf(sqrtf(tot[2 * it + 1]), a.eps);
         }
     __syncthreads();
 
@@ -266,7 +256,7 @@ __global__ void __launch_bounds__(256) k_gdn(GdnArgs a) {
     for (int it = 0; it < nrows; ++it) {
         if (it == nrep && nrep > 0) commit_state();
         const float beta = sbeta[it], decay = sdecay[it];
-        const float* kk = &sk[it][64 * ih]; const float* qq = &sq[it][64 * ih];
+        const float* kk = &sall[it][D + 64 * ih]; const float* qq = &sall[it][64 * ih];
         float kr[64];
 #pragma unroll
         for (int i = 0; i < 64; i += 4) { const float4 v = *reinterpret_cast<const float4*>(kk + i); kr[i] = v.x; kr[i + 1] = v.y; kr[i + 2] = v.z; kr[i + 3] = v.w; }
@@ -274,7 +264,7 @@ __global__ void __launch_bounds__(256) k_gdn(GdnArgs a) {
 #pragma unroll
         for (int i = 0; i < 64; ++i) { m[i] = m[i] * decay; dot = fmaf(m[i], kr[i], dot); }
         dot = dot + __shfl_xor_sync(0xffffffffu, dot, 1);
-        const float delta = (sv[it][j] - dot) * beta;
+        const float delta = (sall[it][2 * D + j] - dot) * beta;
         float o = 0.f;
 #pragma unroll
         for (int i = 0; i < 64; i += 4) {
