@@ -35,6 +35,10 @@ WORKLOADS = {
 }
 
 
+# kernel launches of one round (counted from the ncu launch lists under profiles/)
+ROUND_LAUNCHES = {"dense27b": 689, "moe": 636}
+
+
 def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -168,6 +172,8 @@ def run_dense(args, rank, local_rank, world):
     total_rounds = args.warmup + args.steps
     n_plain = total_rounds * (n + 1) + n + 2
     cfg = hb.ModelCfg.preset(args.preset or preset, n_slots=1)
+    if args.layers:
+        cfg.n_layer = args.layers
     prompt_len = min(args.prompt_len or wl_prompt, cfg.max_ctx // 2)
     assert prompt_len + n_plain + 2 * n + 4 <= cfg.max_ctx, "too many steps for the context window"
     eng = hb.Engine(cfg)
@@ -255,7 +261,7 @@ def run_dense(args, rank, local_rank, world):
         "config": dense_config(world, args.workload),
         "e2e": {"value": toks / (wall_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 4 * n, "d2h_bytes_per_step": 256,
                 "note": "hp_spec_round with host token buffers; wall clock over the timed rounds, one stream synchronise per round"},
-        "gpu_launches": args.steps * world * (570 + n * 21 + 20),
+        "gpu_launches": args.steps * world * ROUND_LAUNCHES.get(args.workload, 0) if not args.layers else None,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"], "traffic": None,
                      "kernel": "k_gemv_q4k_sk: all GEMV launches of one 6-row verify pass (129 launches + LM head), timed alone with CUDA events",
                      "algorithmic_bytes": verify_bytes, "ms": gemv_ms, "full_pass_ms": pass_ms, "peak_source": pk["_src"],
@@ -485,6 +491,7 @@ def main():
     ap.add_argument("--workload", default="dense27b", choices=["dense27b", "moe", "moe-ep", "gemv"])
     ap.add_argument("--preset", default=None)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--layers", type=int, default=0, help="override the trunk depth (profiling captures only: keeps the device footprint at a few GB)")
     ap.add_argument("--prompt-len", type=int, default=0, help="override the workload's prompt length (shorter prompts are for profiling captures only)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
