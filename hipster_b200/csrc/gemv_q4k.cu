@@ -28,7 +28,7 @@ namespace {
 
 constexpr int SK_STAGES = GEMV_STAGES;
 constexpr int SK_THREADS = GEMV_WARPS * 32;
-constexpr int SK_SCR_BYTES = 8 * 16 * 16;          // per warp: [8 sub-blocks][16 rows] float4 {s0, s0, -m, -m}
+constexpr int SK_SCR_BYTES = 0;
 // Two weight layouts. Row-major ggml (TILED = false): a stage holds 16 row pieces of CB blocks, one bulk copy per row.
 // Tile-major (TILED = true, the engine repacks to it at load; same bytes, permuted): for every 16-row tile and block a
 // contiguous 2304-byte chunk = 16 headers (16 B each) + nibbles stored [j][lane][row g 8 B | row g+8 8 B], so a stage
@@ -62,6 +62,29 @@ __device__ __forceinline__ void fma2(float2& acc, float2 a, float2 b) {   // acc
         : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)));
 }
 
+// Scales of one row of one block: {d*sc, d*sc, -(dmin*mn), -(dmin*mn)} per sub-block, computed on demand.
+struct RowScales {
+    float d, cd, dq, cdq, nd, cnd;          // d, -(d*2^23), d/16, -(d/16*2^23), -dmin, dmin*2^23
+    uint32_t sc[2], mn[2];                  // 6-bit scales / mins of sub-blocks 0-3 and 4-7, one per byte
+    __device__ __forceinline__ float4 get(int k) const {
+        const float fs = __uint_as_float(__byte_perm(sc[k >> 2], 0x4B000000u, 0x7540u | (k & 3)));
+        const float fm = __uint_as_float(__byte_perm(mn[k >> 2], 0x4B000000u, 0x7540u | (k & 3)));
+        const float s0 = (k & 1) ? fmaf(dq, fs, cdq) : fmaf(d, fs, cd);
+        const float nm = fmaf(nd, fm, cnd);
+        return make_float4(s0, s0, nm, nm);
+    }
+};
+__device__ __forceinline__ RowScales decode_scales(const uint4 hdr) {
+    RowScales r;
+    r.d = h2f((uint16_t)(hdr.x & 0xFFFF)); r.nd = -h2f((uint16_t)(hdr.x >> 16));
+    r.dq = r.d * 0.0625f;
+    r.cd = -(r.d * 8388608.f); r.cdq = -(r.dq * 8388608.f); r.cnd = -(r.nd * 8388608.f);
+    r.sc[0] = hdr.y & 0x3F3F3F3Fu; r.mn[0] = hdr.z & 0x3F3F3F3Fu;
+    r.sc[1] = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
+    r.mn[1] = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
+    return r;
+}
+
 template <int NT, int CB, bool TILED>
 __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __restrict__ W, const uint4* __restrict__ xq, const float4* __restrict__ xsc,
                                                                 float* __restrict__ y, int N, int nb, int P, int R, int ldy, size_t part_stride,
@@ -69,7 +92,6 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
     using Geo = SkGeom<CB, TILED>;
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* ring_all = smem;
-    float4* scr_all = reinterpret_cast<float4*>(smem + GEMV_WARPS * SK_STAGES * Geo::STAGE_BYTES);
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + GEMV_WARPS * SK_STAGES * Geo::STAGE_BYTES + GEMV_WARPS * SK_SCR_BYTES);
     const int nbp = nb / P;                                // blocks of this CTA's K part
     const uint4* xq_s = reinterpret_cast<const uint4*>(smem + Geo::FIXED);
@@ -83,7 +105,6 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
     const int u0 = warp < weff ? gemv_warp_start(cu, weff, warp) : 0, u1 = warp < weff ? gemv_warp_start(cu, weff, warp + 1) : 0;
     const int nunits = u1 - u0;
     uint8_t* ring = ring_all + warp * SK_STAGES * Geo::STAGE_BYTES;
-    float4* scr = scr_all + warp * (SK_SCR_BYTES / 16);
     const uint32_t bar0 = smem_u32(&bars[warp * SK_STAGES]);
     const uint32_t xbar = smem_u32(&bars[GEMV_WARPS * SK_STAGES]);
     const uint32_t row_bytes = (uint32_t)nb * 144u;
@@ -172,11 +193,9 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
 
     // per-lane constant offsets
     const uint32_t w_lane = TILED ? 256 + lane * 16 : g * Geo::ROW_STRIDE + 16 + 8 * t;   // weights: row g (+8 rows: + 8*ROW_STRIDE)
-    const uint32_t hdr_lane = TILED ? (lane >> 1) * 16 : (lane >> 1) * Geo::ROW_STRIDE;  // pre-pass: row lane/2
+    const uint32_t hdr_lane = TILED ? g * 16 : g * Geo::ROW_STRIDE;      // header of row g (+8 rows: + HDR8)
+    constexpr int HDR8 = TILED ? 128 : 8 * Geo::ROW_STRIDE;
     constexpr int BLK_STRIDE = TILED ? 2304 : 144;
-    const int hf = lane & 1;
-    float4* scr_w = scr + (4 * hf) * 16 + (lane >> 1);                   // pre-pass writes sub-blocks 4hf..4hf+3 of its row
-    const float4* scr_r = scr + g;
 
     int cur_tile = first_tile, chunk = nunits ? u0 % C : 0;
     bool cur_from_start = chunk == 0;
@@ -195,21 +214,12 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
 #ifndef HP_DBG_NOCOMPUTE
 #pragma unroll
         for (int blk = 0; blk < CB; ++blk) {
-            {   // scale pre-pass: lane -> (row = lane/2, half = lane&1) decodes sub-blocks 4hf..4hf+3 of its row
-                const uint4 hdr = *reinterpret_cast<const uint4*>(st + hdr_lane + blk * BLK_STRIDE);
-                const float d = h2f((uint16_t)(hdr.x & 0xFFFF)), nd = -h2f((uint16_t)(hdr.x >> 16));
-                const uint32_t scv = hf ? ((hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u)) : (hdr.y & 0x3F3F3F3Fu);
-                const uint32_t mnv = hf ? (((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u)) : (hdr.z & 0x3F3F3F3Fu);
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    float s0 = d * (float)((scv >> (8 * k)) & 0xFFu);
-                    // odd sub-blocks take the high nibbles unshifted (16 * q): their scale carries the exact 1/16
-                    if (k & 1) s0 = s0 * 0.0625f;
-                    const float nm = nd * (float)((mnv >> (8 * k)) & 0xFFu);   // -(dmin * mn), exact sign flip
-                    scr_w[k * 16] = make_float4(s0, s0, nm, nm);
-                }
-            }
-            __syncwarp();
+            // Scales of this lane's two rows (g, g+8), decoded in registers from the 16-byte headers. A 6-bit value v
+            // becomes the float 8388608 + v by a byte permute into the mantissa of 0x4B000000, and
+            // fmaf(d, 8388608 + v, -(d * 8388608)) is exactly d * v (one rounding of an exactly representable
+            // product). Odd sub-blocks take the high nibbles unshifted (16 * q): their d carries the exact 1/16.
+            const RowScales ra = decode_scales(*reinterpret_cast<const uint4*>(st + hdr_lane + blk * BLK_STRIDE));
+            const RowScales rb = decode_scales(*reinterpret_cast<const uint4*>(st + hdr_lane + HDR8 + blk * BLK_STRIDE));
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 uint2 w0, w1;
@@ -222,8 +232,8 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
                 }
                 const uint32_t alo[4] = {w0.x & 0x0F0F0F0Fu, w1.x & 0x0F0F0F0Fu, w0.y & 0x0F0F0F0Fu, w1.y & 0x0F0F0F0Fu};
                 const uint32_t ahi[4] = {w0.x & 0xF0F0F0F0u, w1.x & 0xF0F0F0F0u, w0.y & 0xF0F0F0F0u, w1.y & 0xF0F0F0F0u};
-                const float4 sa0 = scr_r[(2 * j) * 16], sb0 = scr_r[(2 * j) * 16 + 8];          // low-nibble sub-block: rows g, g+8
-                const float4 sa1 = scr_r[(2 * j + 1) * 16], sb1 = scr_r[(2 * j + 1) * 16 + 8];  // high-nibble sub-block
+                const float4 sa0 = ra.get(2 * j), sb0 = rb.get(2 * j);           // low-nibble sub-block: rows g, g+8
+                const float4 sa1 = ra.get(2 * j + 1), sb1 = rb.get(2 * j + 1);   // high-nibble sub-block
 #pragma unroll
                 for (int n = 0; n < NT; ++n) {
                     const uint4 xf = xqp[n * nbp * 128 + (blk * 4 + j) * 32];
@@ -248,8 +258,8 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
                     fma2(acc[n][1], make_float2(sb1.z, sb1.w), xs1);
                 }
             }
-            __syncwarp();
         }
+        __syncwarp();   // every lane has read the stage before it is refilled
 #endif
         if (it_i < nunits) issue();
         if (++chunk == C) {
