@@ -320,7 +320,7 @@ int Engine::lin(const Lin& l, float* out, int ld, int R) {
 }
 // residual add of the previous projection's planes + RMSNorm + quantise (qwen35.cpp:311-315)
 int Engine::norm_in(const Lin* prev, bool have_y, const uint16_t* w, float* xn, int R) {
-    if (gemv_only_) return HP_OK;
+    if (gemv_only_ || (prof_skip_ & 2)) return HP_OK;
     return add_rmsnorm_quant(x_, have_y ? yparts_ : nullptr, have_y ? prev->P : 0, have_y ? (size_t)R * prev->N : 0, have_y ? prev->N : 0, w, xn, xq_, R, c_.n_embd, c_.rms_eps, s_);
 }
 // qwen35.cpp:247-276
@@ -331,7 +331,7 @@ int Engine::attn_block(const LayerW& L, uint16_t* kc, uint16_t* vc, size_t kv_st
     p.q_norm = L.q_norm; p.k_norm = L.k_norm; p.rope = rope_; p.row_pos = d_desc_ + D_POS; p.row_slot = d_desc_ + D_SLOT; p.row_group = d_desc_ + D_RGROUP; p.groups = d_desc_ + D_GROUPS;
     p.kc = kc; p.vc = vc; p.kv_stride = kv_stride; p.max_ctx = c_.max_ctx; p.pO = pO_; p.pm = pm_; p.pl = pl_; p.nsplit_max = nsplit_max_;
     p.out = nullptr; p.xq = xq_; p.eps = c_.rms_eps;
-    if (!gemv_only_) { HP_TRY(attn_rope_kv(p, R, s_)); HP_TRY(attn_decode(p, R, ngroups, s_)); }
+    if (!gemv_only_ && !(prof_skip_ & 4)) { HP_TRY(attn_rope_kv(p, R, s_)); HP_TRY(attn_decode(p, R, ngroups, s_)); }
     return lin_parts(L.out_proj, R);
 }
 // qwen35.cpp:278-287
@@ -339,7 +339,7 @@ int Engine::ffn_block(const LayerW& L, int R) {
     if (c_.n_expert) return moe_block(L, R);
     const int F = c_.n_ff;
     HP_TRY(lin(L.gate_up, big_, 2 * F, R));
-    if (!gemv_only_) HP_TRY(silu_mul_quant(big_, 2 * F, F, xq_, R, s_));
+    if (!gemv_only_ && !(prof_skip_ & 8)) HP_TRY(silu_mul_quant(big_, 2 * F, F, xq_, R, s_));
     return lin_parts(L.down, R);
 }
 
@@ -378,7 +378,7 @@ int Engine::run_pass(int R, int nseq, int ngroups) {
             g.conv_w = L.conv_w; g.dt_bias = L.dt_bias; g.a_neg = L.a_neg; g.norm_w = L.ssm_norm;
             g.state = gdn_state_ + (size_t)gi * st_layer_; g.conv_state = conv_state_ + (size_t)gi * cs_layer_; g.state_stride = st_stride_; g.conv_stride = cs_stride_;
             g.seq = d_desc_ + D_SEQS; g.replay_n = replay_n_; g.out = nullptr; g.xq = xq_; g.snap = nullptr; g.snap_row_stride = 0; g.eps = c.rms_eps; g.sigmoid_gate = c.gdn_sigmoid_gate;
-            if (!gemv_only_) HP_TRY(gdn_forward(g, nseq, s_));
+            if (!gemv_only_ && !(prof_skip_ & 1)) HP_TRY(gdn_forward(g, nseq, s_));
             HP_TRY(lin_parts(L.out_proj, R));
             ++gi;
         } else {
@@ -593,7 +593,8 @@ size_t Engine::pass_weight_bytes(bool mtp, bool with_head) const {
 }
 
 // Diagnostic: device time of `reps` back-to-back verify passes of R rows over whatever tokens / state are current
-// (what = 0), or of only the GEMV launches of such passes (what = 1). State and KV are not committed.
+// (what = 0), of only the GEMV launches of such passes (what = 1), or of passes that leave out kernel classes
+// (what = 16 + mask: 1 GDN, 2 norms, 4 attention, 8 SiLU; results are then meaningless, only the time is). State and KV are not committed.
 int Engine::profile_pass(int R, int what, int reps, float* ms) {
     HP_REQUIRE(R >= 1 && R <= 8 && reps >= 1 && ms, "profile_pass: bad arguments");
     int* d = h_desc_;
@@ -601,12 +602,12 @@ int Engine::profile_pass(int R, int what, int reps, float* ms) {
     d[D_GROUPS] = 0; d[D_GROUPS + 1] = R; d[D_GROUPS + 2] = 0; d[D_GROUPS + 3] = 0;
     d[D_SEQS] = 0; d[D_SEQS + 1] = R; d[D_SEQS + 2] = 0; d[D_SEQS + 3] = 0;
     HP_TRY(upload_desc());
-    gemv_only_ = what == 1;
+    gemv_only_ = what == 1; prof_skip_ = what >= 16 ? what - 16 : 0;
     int rc = run_pass(R, 1, 1);                     // warm-up (also sets kernel attributes)
     HP_CUDA(cudaEventRecord(ev0_, s_));
     for (int i = 0; i < reps && rc == HP_OK; ++i) rc = run_pass(R, 1, 1);
     HP_CUDA(cudaEventRecord(ev1_, s_));
-    gemv_only_ = false;
+    gemv_only_ = false; prof_skip_ = 0;
     HP_CUDA(cudaStreamSynchronize(s_));
     if (rc != HP_OK) return rc;
     float t = 0; HP_CUDA(cudaEventElapsedTime(&t, ev0_, ev1_)); *ms = t / reps;

@@ -99,7 +99,7 @@ private:
     cudaStream_t s_ = nullptr; cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
     std::vector<void*> allocs_;
     size_t weight_bytes_ = 0; float last_ms_ = 0;
-    int last_rows_ = 0; bool gemv_only_ = false, tiled_ = true, keep_rowmajor_ = true; bool pdl_ = getenv("HIPSTER_B200_NO_PDL") == nullptr;
+    int last_rows_ = 0, prof_skip_ = 0; bool gemv_only_ = false, tiled_ = true, keep_rowmajor_ = true; bool pdl_ = getenv("HIPSTER_B200_NO_PDL") == nullptr;
 };
 
 }  // namespace hp

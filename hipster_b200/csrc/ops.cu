@@ -7,6 +7,7 @@
 // Qwen35::accept (engine/src/qwen35.cpp:383-403).
 //
 // Every reduction has a fixed order (stated at each kernel) so that the CPU oracle reproduces the results bit for bit.
+#include <type_traits>
 #include "hp_common.cuh"
 #include "kernels.h"
 
@@ -37,75 +38,164 @@ __global__ void __launch_bounds__(256) k_embed_bf16(const int* __restrict__ tok,
     for (int i = threadIdx.x; i < E; i += 256) out[(size_t)r * E + i] = bf2f(src[i]);
 }
 
+// ---- row norms. A cluster of 4 CTAs x 320 threads per row: thread t (0..1279 over the cluster) owns the 4-element
+// groups t, t+1280, ... (128-bit accesses, kept in registers), so that the row's traffic is spread over four SMs.
+// Sum of squares: per-thread fmaf chain over its elements in index order, xor tree inside each warp, then the 40 warp
+// sums (warp index over the cluster) added in order by every thread after the cluster barrier. Quantisation: a
+// 32-element sub-block is held by 8 consecutive lanes.
+constexpr int NORM_CL = 4, NORM_TPB = 320, NORM_ROWT = NORM_CL * NORM_TPB, NORM_NW = NORM_ROWT / 32, NORM_MAXG = 2;   // rows of up to 10240 elements
+#ifdef HP_GDN_TIMING
+__device__ long long g_norm_clk[16];
+#define NORM_TICK(i) do { if (threadIdx.x == 0 && blockIdx.x == 0) g_norm_clk[i] = clock64(); } while (0)
+#else
+#define NORM_TICK(i) do { } while (0)
+#endif
+// warp part of the cluster-wide sum: leaves this warp's sum in slot (10 * rank + warp) of every CTA's table
+__device__ __forceinline__ void norm_publish(float v, float* tab, int rank) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = v + __shfl_xor_sync(0xffffffffu, v, off);
+    const int lane = threadIdx.x & 31;
+    if (lane < NORM_CL) st_cluster_f32(&tab[rank * (NORM_TPB / 32) + (threadIdx.x >> 5)], (uint32_t)lane, v);
+}
+__device__ __forceinline__ float norm_total(const float* tab) {
+    float tot = tab[0];
+#pragma unroll
+    for (int i = 1; i < NORM_NW; ++i) tot = tot + tab[i];
+    return tot;
+}
+// 4 consecutive activations of row r starting at element i0 (a multiple of 4), owned by one lane; the 8 lanes of a
+// sub-block are consecutive. Same arithmetic as warp_quant32_store.
+__device__ __forceinline__ void quant4_store(const float (&o)[4], int r, int i0, int K, int8_t* __restrict__ q, float* __restrict__ sc, int lane) {
+    float amax = fmaxf(fmaxf(fabsf(o[0]), fabsf(o[1])), fmaxf(fabsf(o[2]), fabsf(o[3])));
+#pragma unroll
+    for (int off = 1; off < 8; off <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    const float dd = amax / 127.f, id = amax > 0.f ? 127.f / amax : 0.f;
+    const int q0 = __float2int_rn(o[0] * id), q1 = __float2int_rn(o[1] * id), q2 = __float2int_rn(o[2] * id), q3 = __float2int_rn(o[3] * id);
+    int sum = (q0 + q1) + (q2 + q3);
+#pragma unroll
+    for (int off = 1; off < 8; off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    *reinterpret_cast<uint32_t*>(q + xq_q_index(r, i0, K)) = (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) | ((uint32_t)(q3 & 0xFF) << 24);
+    if ((lane & 7) == 0) { const size_t di = xq_d_index(r, i0 >> 5, K); sc[di] = dd; sc[di + 2] = dd * (float)sum; }
+}
+__device__ __forceinline__ void bf4(const uint16_t* w, float (&o)[4]) {
+    const uint2 u = *reinterpret_cast<const uint2*>(w);
+    o[0] = __uint_as_float(u.x << 16); o[1] = __uint_as_float(u.x & 0xFFFF0000u); o[2] = __uint_as_float(u.y << 16); o[3] = __uint_as_float(u.y & 0xFFFF0000u);
+}
+
 // ---- x += y (y = sum of P K-part planes in part order); xn = x * (1/sqrt(mean x^2 + eps)) * w; xq = q8(xn) ----
-// One 1024-thread block per row. Thread i owns elements i, i+1024, ... (kept in registers); sum of squares: per-thread
-// fmaf chain in that order, then block_sum_det over the 32 warps. Quantisation per 32 consecutive elements (one warp).
-constexpr int NORM_THREADS = 1024, NORM_MAXE = 10;   // rows of up to 10240 elements
-__global__ void __launch_bounds__(NORM_THREADS) k_add_rmsnorm_quant(float* __restrict__ x, const float* __restrict__ y, int P, size_t part_stride, int ldy,
+template <int PT, int NG>   // PT > 0: the number of planes, known at compile time so that every load is in flight at once; 0: run-time P. NG: groups per thread
+__global__ void __cluster_dims__(NORM_CL, 1, 1) __launch_bounds__(NORM_TPB) k_add_rmsnorm_quant(float* __restrict__ x, const float* __restrict__ y, int P, size_t part_stride, int ldy,
                                                                      const uint16_t* __restrict__ w, float* __restrict__ xn, int8_t* __restrict__ q, float* __restrict__ sc,
                                                                      int n, float eps) {
-    __shared__ float sh[32];
+    __shared__ float tab[NORM_NW];
+    NORM_TICK(0);
     pdl_launch_dependents();
-    const int r = blockIdx.x, lane = threadIdx.x & 31;
+    cluster_arrive_relaxed();   // matched by cluster_wait() before the first store into another CTA
+    const int rank = blockIdx.x % NORM_CL, r = blockIdx.x / NORM_CL, lane = threadIdx.x & 31, t = rank * NORM_TPB + threadIdx.x;
     float* xr = x + (size_t)r * n;
-    float wv[NORM_MAXE];
+    float wv[NG][4];
 #pragma unroll
-    for (int k = 0; k < NORM_MAXE; ++k) { const int i = threadIdx.x + k * NORM_THREADS; wv[k] = i < n ? bf2f(w[i]) : 0.f; }   // weights do not depend on the previous kernel
+    for (int k = 0; k < NG; ++k) { const int i = 4 * (t + k * NORM_ROWT); if (i < n) bf4(w + i, wv[k]); }   // weights do not depend on the previous kernel
+    NORM_TICK(1);
     pdl_wait();
-    float v[NORM_MAXE];
+    NORM_TICK(2);
+    float4 v[NG];
 #pragma unroll
-    for (int k = 0; k < NORM_MAXE; ++k) { const int i = threadIdx.x + k * NORM_THREADS; v[k] = i < n ? xr[i] : 0.f; }
+    for (int k = 0; k < NG; ++k) { const int i = 4 * (t + k * NORM_ROWT); v[k] = i < n ? *reinterpret_cast<const float4*>(xr + i) : make_float4(0.f, 0.f, 0.f, 0.f); }
     if (y) {
-        float s[NORM_MAXE];
+        float4 s[NG];
 #pragma unroll
-        for (int k = 0; k < NORM_MAXE; ++k) { const int i = threadIdx.x + k * NORM_THREADS; s[k] = i < n ? y[(size_t)r * ldy + i] : 0.f; }
-        for (int p = 1; p < P; ++p)
+        for (int k = 0; k < NG; ++k) { const int i = 4 * (t + k * NORM_ROWT); s[k] = i < n ? *reinterpret_cast<const float4*>(y + (size_t)r * ldy + i) : make_float4(0.f, 0.f, 0.f, 0.f); }
+        if constexpr (PT > 0) {
+            float4 u[PT > 1 ? PT - 1 : 1][NG];
 #pragma unroll
-            for (int k = 0; k < NORM_MAXE; ++k) { const int i = threadIdx.x + k * NORM_THREADS; if (i < n) s[k] = s[k] + y[(size_t)p * part_stride + (size_t)r * ldy + i]; }
+            for (int p = 1; p < PT; ++p)
 #pragma unroll
-        for (int k = 0; k < NORM_MAXE; ++k) { const int i = threadIdx.x + k * NORM_THREADS; if (i < n) { v[k] = v[k] + s[k]; xr[i] = v[k]; } }
-    }
-    float ss = 0.f;
+                for (int k = 0; k < NG; ++k) { const int i = 4 * (t + k * NORM_ROWT); u[p - 1][k] = i < n ? *reinterpret_cast<const float4*>(y + (size_t)p * part_stride + (size_t)r * ldy + i) : make_float4(0.f, 0.f, 0.f, 0.f); }
 #pragma unroll
-    for (int k = 0; k < NORM_MAXE; ++k) { const int i = threadIdx.x + k * NORM_THREADS; if (i < n) ss = fmaf(v[k], v[k], ss); }
-    ss = block_sum_det<32>(ss, sh);
-    const float scl = 1.0f / sqrtf(ss / (float)n + eps);
+            for (int p = 1; p < PT; ++p)
 #pragma unroll
-    for (int k = 0; k < NORM_MAXE; ++k) {
-        const int i = threadIdx.x + k * NORM_THREADS;
-        if (i < n) {   // n is a multiple of 32: a warp is wholly inside or wholly outside
-            const float o = (v[k] * scl) * wv[k];
-            if (xn) xn[(size_t)r * n + i] = o;
-            warp_quant32_store(o, r, i >> 5, n, q, sc, lane);
+                for (int k = 0; k < NG; ++k) { s[k].x = s[k].x + u[p - 1][k].x; s[k].y = s[k].y + u[p - 1][k].y; s[k].z = s[k].z + u[p - 1][k].z; s[k].w = s[k].w + u[p - 1][k].w; }
+        } else {
+            for (int p = 1; p < P; ++p)
+#pragma unroll
+                for (int k = 0; k < NG; ++k) {
+                    const int i = 4 * (t + k * NORM_ROWT);
+                    if (i < n) { const float4 uu = *reinterpret_cast<const float4*>(y + (size_t)p * part_stride + (size_t)r * ldy + i); s[k].x = s[k].x + uu.x; s[k].y = s[k].y + uu.y; s[k].z = s[k].z + uu.z; s[k].w = s[k].w + uu.w; }
+                }
+        }
+#pragma unroll
+        for (int k = 0; k < NG; ++k) {
+            const int i = 4 * (t + k * NORM_ROWT);
+            if (i < n) { v[k].x = v[k].x + s[k].x; v[k].y = v[k].y + s[k].y; v[k].z = v[k].z + s[k].z; v[k].w = v[k].w + s[k].w; *reinterpret_cast<float4*>(xr + i) = v[k]; }
         }
     }
+    NORM_TICK(3);
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < NG; ++k) { ss = fmaf(v[k].x, v[k].x, ss); ss = fmaf(v[k].y, v[k].y, ss); ss = fmaf(v[k].z, v[k].z, ss); ss = fmaf(v[k].w, v[k].w, ss); }   // absent groups hold zeros
+    cluster_wait();
+    NORM_TICK(4);
+    norm_publish(ss, tab, rank);
+    cluster_sync_all();
+    ss = norm_total(tab);
+    NORM_TICK(5);
+    const float scl = 1.0f / sqrtf(ss / (float)n + eps);
+#pragma unroll
+    for (int k = 0; k < NG; ++k) {
+        const int i = 4 * (t + k * NORM_ROWT);
+        if (i < n) {   // n is a multiple of 32: the 8 lanes of a sub-block are wholly inside or wholly outside
+            const float o[4] = {(v[k].x * scl) * wv[k][0], (v[k].y * scl) * wv[k][1], (v[k].z * scl) * wv[k][2], (v[k].w * scl) * wv[k][3]};
+            if (xn) *reinterpret_cast<float4*>(xn + (size_t)r * n + i) = make_float4(o[0], o[1], o[2], o[3]);
+            quant4_store(o, r, i, n, q, sc, lane);
+        }
+    }
+    NORM_TICK(6);
 }
 
 // ---- MTP input: out[r] = [rmsnorm(a[r]) * wa | rmsnorm(b[r]) * wb], quantised (ops.hip:99-116) ----
-__global__ void __launch_bounds__(NORM_THREADS) k_norm2_concat_quant(const float* __restrict__ a, const uint16_t* __restrict__ wa, const float* __restrict__ b, int ldb,
+template <int NG>
+__global__ void __cluster_dims__(NORM_CL, 1, 1) __launch_bounds__(NORM_TPB) k_norm2_concat_quant(const float* __restrict__ a, const uint16_t* __restrict__ wa, const float* __restrict__ b, int ldb,
                                                                       const uint16_t* __restrict__ wb, float* __restrict__ out, int8_t* __restrict__ q, float* __restrict__ sc,
                                                                       int n, float eps) {
-    __shared__ float sh[32];
+    __shared__ float taba[NORM_NW], tabb[NORM_NW];
     pdl_launch_dependents();
+    cluster_arrive_relaxed();
+    const int rank = blockIdx.x % NORM_CL, r = blockIdx.x / NORM_CL, lane = threadIdx.x & 31, t = rank * NORM_TPB + threadIdx.x;
+    float wav[NG][4], wbv[NG][4];
+#pragma unroll
+    for (int k = 0; k < NG; ++k) { const int i = 4 * (t + k * NORM_ROWT); if (i < n) { bf4(wa + i, wav[k]); bf4(wb + i, wbv[k]); } }
     pdl_wait();
-    const int r = blockIdx.x, lane = threadIdx.x & 31;
     const float* ar = a + (size_t)r * n; const float* br = b + (size_t)r * ldb;
-    float va[NORM_MAXE], vb[NORM_MAXE];
+    float4 va[NG], vb[NG];
     float sa = 0.f, sb = 0.f;
 #pragma unroll
-    for (int k = 0; k < NORM_MAXE; ++k) { const int i = threadIdx.x + k * NORM_THREADS; va[k] = i < n ? ar[i] : 0.f; vb[k] = i < n ? br[i] : 0.f; }
+    for (int k = 0; k < NG; ++k) {
+        const int i = 4 * (t + k * NORM_ROWT);
+        va[k] = i < n ? *reinterpret_cast<const float4*>(ar + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        vb[k] = i < n ? *reinterpret_cast<const float4*>(br + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
 #pragma unroll
-    for (int k = 0; k < NORM_MAXE; ++k) { const int i = threadIdx.x + k * NORM_THREADS; if (i < n) { sa = fmaf(va[k], va[k], sa); sb = fmaf(vb[k], vb[k], sb); } }
-    sa = block_sum_det<32>(sa, sh); sb = block_sum_det<32>(sb, sh);
-    const float ca = 1.0f / sqrtf(sa / (float)n + eps), cb = 1.0f / sqrtf(sb / (float)n + eps);
+    for (int k = 0; k < NG; ++k) {
+        sa = fmaf(va[k].x, va[k].x, sa); sa = fmaf(va[k].y, va[k].y, sa); sa = fmaf(va[k].z, va[k].z, sa); sa = fmaf(va[k].w, va[k].w, sa);
+        sb = fmaf(vb[k].x, vb[k].x, sb); sb = fmaf(vb[k].y, vb[k].y, sb); sb = fmaf(vb[k].z, vb[k].z, sb); sb = fmaf(vb[k].w, vb[k].w, sb);
+    }
+    cluster_wait();
+    norm_publish(sa, taba, rank); norm_publish(sb, tabb, rank);
+    cluster_sync_all();
+    const float ca = 1.0f / sqrtf(norm_total(taba) / (float)n + eps), cb = 1.0f / sqrtf(norm_total(tabb) / (float)n + eps);
 #pragma unroll
-    for (int k = 0; k < NORM_MAXE; ++k) {
-        const int i = threadIdx.x + k * NORM_THREADS;
+    for (int k = 0; k < NG; ++k) {
+        const int i = 4 * (t + k * NORM_ROWT);
         if (i < n) {
-            const float oa = (va[k] * ca) * bf2f(wa[i]), ob = (vb[k] * cb) * bf2f(wb[i]);
-            if (out) { out[(size_t)r * 2 * n + i] = oa; out[(size_t)r * 2 * n + n + i] = ob; }
-            warp_quant32_store(oa, r, i >> 5, 2 * n, q, sc, lane);
-            warp_quant32_store(ob, r, (n + i) >> 5, 2 * n, q, sc, lane);
+            const float oa[4] = {(va[k].x * ca) * wav[k][0], (va[k].y * ca) * wav[k][1], (va[k].z * ca) * wav[k][2], (va[k].w * ca) * wav[k][3]};
+            const float ob[4] = {(vb[k].x * cb) * wbv[k][0], (vb[k].y * cb) * wbv[k][1], (vb[k].z * cb) * wbv[k][2], (vb[k].w * cb) * wbv[k][3]};
+            if (out) {
+                *reinterpret_cast<float4*>(out + (size_t)r * 2 * n + i) = make_float4(oa[0], oa[1], oa[2], oa[3]);
+                *reinterpret_cast<float4*>(out + (size_t)r * 2 * n + n + i) = make_float4(ob[0], ob[1], ob[2], ob[3]);
+            }
+            quant4_store(oa, r, i, 2 * n, q, sc, lane);
+            quant4_store(ob, r, n + i, 2 * n, q, sc, lane);
         }
     }
 }
@@ -122,16 +212,21 @@ __global__ void __launch_bounds__(256) k_silu_mul_quant(const float* __restrict_
 }
 
 // ---- Gated DeltaNet: causal 4-tap depthwise conv + SiLU, then the gated delta rule, for one (v-head, sequence) ----
-// 256 threads. Threads 0..127 own q channel c and k channel c of q/k head hk = h % n_qk, threads 128..255 own v channel
-// c of head h. State M[j][i] (j = value row, i = key index): thread tid holds row j = tid/2, columns 64*(tid&1)..+63.
+// A cluster of 4 CTAs per (v-head, sequence); CTA `rank` owns value rows 32*rank .. 32*rank+31 of the head's state
+// M[j][i] (j = value row, i = key index). 256 threads: thread tid holds columns 16*(tid&7) .. +15 of row 32*rank + tid/8
+// in registers, read and written straight from / to HBM (a warp covers 2 KB of consecutive state). Every CTA convolves
+// and normalises the head's 128 q and 128 k channels itself (thread tid: q channel tid, or k channel tid-128) and its
+// own 32 v channels (threads 0..31).
 // Rows are processed in order: first `n_replay` rows of the previous pass (their raw inputs were saved per head by
 // that pass; no output) -- this is the deferred commit of the accepted prefix: the state and conv history reached
 // after them are written back --, then the T new rows (outputs only; state stays in registers, optional snapshots),
-// whose raw inputs are saved in turn.
+// whose raw inputs are saved in turn. The saved rows and the history are shared by the cluster: a cluster barrier
+// separates everybody's reads from the writes (q|k parts written by rank 0, v parts by their owner).
 // Row math (ops.hip:221-250): q,k <- x / max(||x||, eps); beta = sigmoid(b); decay = exp(a_neg * softplus(alpha + dt));
 // M *= decay; dot_j = sum_i M[j][i] k[i]; delta_j = (v_j - dot_j) beta; M[j][i] += delta_j k[i];
 // o_j = sum_i M[j][i] q[i] / sqrt(128); out = rmsnorm_128(o) * w * gate(z). Sums over i: fmaf chain over the thread's
-// 64 columns in index order, the two halves added; sums over 128 channels: block_sum_det.
+// 16 columns in index order, the 8 partial sums combined by an xor tree (1, 2, 4); sums over 128 channels: xor tree
+// inside each warp of 32 channels, the four warp sums added in channel order.
 struct GdnArgs {
     const float* rows; int ld;                                    // merged GEMV output [rows][ld]: qkv | z | beta | alpha
     float* saved; size_t saved_stride;                            // per slot: [n_v][8 rows][388]: raw q|k|v channels, beta, alpha of the last pass
@@ -145,167 +240,171 @@ struct GdnArgs {
     float* snap; size_t snap_row_stride;                          // optional state snapshots after each new row
     float eps; int sigmoid_gate;
 };
-constexpr int GDN_MAXROWS = 16, GDN_STG_LD = 132;   // replayed rows (<= 8) + new rows (<= 8) of one sequence
-__global__ void __launch_bounds__(256) k_gdn(GdnArgs a) {
+constexpr int GDN_MAXROWS = 16, GDN_CL = 4;   // replayed rows (<= 8) + new rows (<= 8) of one sequence; CTAs per head
+#ifdef HP_GDN_TIMING
+__device__ long long g_gdn_clk[16];
+#define GDN_TICK(i) do { if (threadIdx.x == 0 && blockIdx.x == 5 && blockIdx.y == 0) g_gdn_clk[i] = clock64(); } while (0)
+#else
+#define GDN_TICK(i) do { } while (0)
+#endif
+__global__ void __cluster_dims__(GDN_CL, 1, 1) __launch_bounds__(256) k_gdn(GdnArgs a) {
     constexpr int D = 128;
-    __shared__ __align__(16) float sall[GDN_MAXROWS][3 * D], sout[8][D];
-    __shared__ float red[GDN_MAXROWS * 2][8], tot[GDN_MAXROWS * 2], sbeta[GDN_MAXROWS], sdecay[GDN_MAXROWS], sraw_b[GDN_MAXROWS], sraw_a[GDN_MAXROWS];
+    // normalised q | k of every row (filled by all four CTAs); 16-float chunks padded to 20 so that the eight chunk
+    // owners of a state row read 128 bits each from distinct banks
+    __shared__ __align__(16) float sqk[GDN_MAXROWS][2 * 160];
+    __shared__ float raw[GDN_MAXROWS + 3][96], cown[GDN_MAXROWS][64], sv[GDN_MAXROWS][32], sout[8][32];
+    __shared__ float csum[GDN_MAXROWS][2][GDN_CL], sbeta[GDN_MAXROWS], sdecay[GDN_MAXROWS], sraw_b[GDN_MAXROWS], sraw_a[GDN_MAXROWS];
+    __shared__ float cred[8][GDN_CL];
     pdl_launch_dependents();
+    GDN_TICK(0);
+    cluster_arrive_relaxed();   // matched by cluster_wait() before the first store into another CTA: every CTA has started by then
     pdl_wait();
-    const int h = blockIdx.x, hk = h % a.n_qk, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    GDN_TICK(1);
+    const int rank = blockIdx.x % GDN_CL, h = blockIdx.x / GDN_CL, hk = h % a.n_qk, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int r0 = a.seq[blockIdx.y * 4 + 0], T = min(a.seq[blockIdx.y * 4 + 1], 8), slot = a.seq[blockIdx.y * 4 + 2];
     float* sav = a.saved + (size_t)slot * a.saved_stride + (size_t)h * 8 * 388;   // [8][q 128 | k 128 | v 128 | beta | alpha | pad]
     const int nrep = a.replay_n ? min(a.replay_n[slot], 8) : 0;
     const int nrows = nrep + T;
     const int Z = a.n_v * D;
-    const int j = tid >> 1, ih = tid & 1;
-    // conv history of this head: [3 taps][q 128 | k 128 | v 128]; private per v-head so that no CTA reads what another writes
-    float* cst = a.conv_state + (size_t)slot * a.conv_stride + (size_t)h * 3 * 384;
-    const int sa_ = tid < D ? tid : D + tid, sb_ = D + (tid & (D - 1));   // history / saved-row slots of channels ca / cb
-    // the 64 KB state of this head moves between HBM and registers through shared memory, so that global accesses are
-    // fully coalesced 128-bit rows (each thread owns 64 consecutive floats of one state row)
-    extern __shared__ __align__(16) float stg[];                 // [128][GDN_STG_LD]
-    float* Mhead = a.state + (size_t)slot * a.state_stride + (size_t)h * D * D;
-    for (int idx = tid; idx < D * D / 4; idx += 256) {
-        const float4 v = reinterpret_cast<const float4*>(Mhead)[idx];
-        *reinterpret_cast<float4*>(stg + (idx >> 5) * GDN_STG_LD + (idx & 31) * 4) = v;
-    }
-    __syncthreads();
-    float m[64];
+    const int jl = tid >> 3, ck = tid & 7, j = 32 * rank + jl;
+    float* Mrow = a.state + (size_t)slot * a.state_stride + ((size_t)h * D + j) * D + 16 * ck;
+    float m[16];
 #pragma unroll
-    for (int i = 0; i < 64; i += 4) {
-        const float4 v = *reinterpret_cast<const float4*>(stg + j * GDN_STG_LD + 64 * ih + i);
-        m[i] = v.x; m[i + 1] = v.y; m[i + 2] = v.z; m[i + 3] = v.w;
-    }
-    auto commit_state = [&]() {   // block-uniform call sites only
-        __syncthreads();
+    for (int i = 0; i < 16; i += 4) { const float4 v = *reinterpret_cast<const float4*>(Mrow + i); m[i] = v.x; m[i + 1] = v.y; m[i + 2] = v.z; m[i + 3] = v.w; }
+    auto commit_state = [&]() {
 #pragma unroll
-        for (int i = 0; i < 64; i += 4) *reinterpret_cast<float4*>(stg + j * GDN_STG_LD + 64 * ih + i) = make_float4(m[i], m[i + 1], m[i + 2], m[i + 3]);
-        __syncthreads();
-        for (int idx = tid; idx < D * D / 4; idx += 256)
-            reinterpret_cast<float4*>(Mhead)[idx] = *reinterpret_cast<const float4*>(stg + (idx >> 5) * GDN_STG_LD + (idx & 31) * 4);
+        for (int i = 0; i < 16; i += 4) *reinterpret_cast<float4*>(Mrow + i) = make_float4(m[i], m[i + 1], m[i + 2], m[i + 3]);
     };
-    // conv channels of this thread: ca (q for tid < 128, v otherwise), cb (k, tid < 128 only)
-    const int ca = tid < D ? hk * D + tid : 2 * a.n_qk * D + h * D + (tid - D);
-    const int cb = a.n_qk * D + hk * D + (tid & (D - 1));
-    float ha0 = cst[sa_], ha1 = cst[384 + sa_], ha2 = cst[768 + sa_];
-    float hb0 = 0.f, hb1 = 0.f, hb2 = 0.f;
-    if (tid < D) { hb0 = cst[sb_]; hb1 = cst[384 + sb_]; hb2 = cst[768 + sb_]; }
-    const float wa0 = a.conv_w[ca * 4 + 0], wa1 = a.conv_w[ca * 4 + 1], wa2 = a.conv_w[ca * 4 + 2], wa3 = a.conv_w[ca * 4 + 3];
-    const float wb0 = a.conv_w[cb * 4 + 0], wb1 = a.conv_w[cb * 4 + 1], wb2 = a.conv_w[cb * 4 + 2], wb3 = a.conv_w[cb * 4 + 3];
+    // conv history of this head: [3 taps][q 128 | k 128 | v 128]; private per v-head
+    float* cst = a.conv_state + (size_t)slot * a.conv_stride + (size_t)h * 3 * 384;
+    // Local channel c of this CTA (0..95): group c/32 = q, k, v; channel 32*rank + c%32 of the head. Its slot in a
+    // history / saved row and its column in a row of the merged projection:
+    auto ch_slot = [&](int c) { return (c >> 5) * D + 32 * rank + (c & 31); };
+    auto ch_col = [&](int c) { const int g3 = c >> 5, cl = 32 * rank + (c & 31); return g3 == 0 ? hk * D + cl : g3 == 1 ? a.n_qk * D + hk * D + cl : 2 * a.n_qk * D + h * D + cl; };
 
-    // ---- phase 1: raw inputs of all rows fetched with asynchronous 4-byte copies (all in flight at once, compact
-    // code), then conv + SiLU in place, squared norms, gates. sall[it] = [q 128 | k 128 | v 128] of row it.
-    for (int it = 0; it < nrows; ++it) {
-        const bool replay = it < nrep;
-        const float* row = a.rows + (size_t)(replay ? 0 : r0 + (it - nrep)) * a.ld;
-        const float* srow = sav + (replay ? it : 0) * 388;
-        cp_async4(&sall[it][sa_], replay ? srow + sa_ : row + ca);
-        if (tid < D) cp_async4(&sall[it][sb_], replay ? srow + sb_ : row + cb);
-        if (tid == 0) { cp_async4(&sraw_b[it], replay ? srow + 384 : row + a.off_b + h); cp_async4(&sraw_a[it], replay ? srow + 385 : row + a.off_a + h); }
+    // ---- phase 1: history (3 taps) + raw inputs of all rows -> raw[tap or 3 + row][c], by asynchronous 4-byte copies
+    for (int e = tid; e < (nrows + 3) * 96; e += 256) {
+        const int rr = e / 96, c = e - rr * 96, it = rr - 3;
+        const float* src = rr < 3 ? cst + rr * 384 + ch_slot(c)
+                         : it < nrep ? sav + it * 388 + ch_slot(c) : a.rows + (size_t)(r0 + it - nrep) * a.ld + ch_col(c);
+        cp_async4(&raw[rr][c], src);
     }
+    if (rank == 0 && tid < nrows) {
+        const bool replay = tid < nrep;
+        const float* row = a.rows + (size_t)(replay ? 0 : r0 + (tid - nrep)) * a.ld;
+        cp_async4(&sraw_b[tid], replay ? sav + tid * 388 + 384 : row + a.off_b + h);
+        cp_async4(&sraw_a[tid], replay ? sav + tid * 388 + 385 : row + a.off_a + h);
+    }
+    GDN_TICK(2);
     cp_async_wait_all();
     __syncthreads();
-    if (tid < nrows) {
-        sbeta[tid] = sigmoid_det(sraw_b[tid]);
-        sdecay[tid] = expf_det(bf2f(a.a_neg[h]) * softplus_det(sraw_a[tid] + bf2f(a.dt_bias[h])));
-    }
-    // keep the raw inputs of the new rows for a later commit (every replayed row has been read: they are in shared memory)
-    for (int it = nrep; it < nrows; ++it) {
-        float* srow = sav + (it - nrep) * 388;
-        srow[sa_] = sall[it][sa_]; if (tid < D) srow[sb_] = sall[it][sb_];
-        if (tid == 0) { srow[384] = sraw_b[it]; srow[385] = sraw_a[it]; }
-    }
-    for (int it = 0; it < nrows; ++it) {
-        if (it == nrep && nrep > 0) {   // history after the accepted prefix: committed
-            cst[sa_] = ha0; cst[384 + sa_] = ha1; cst[768 + sa_] = ha2;
-            if (tid < D) { cst[sb_] = hb0; cst[384 + sb_] = hb1; cst[768 + sb_] = hb2; }
-        }
-        const float xa = sall[it][sa_];
-        float t = wa0 * ha0; t = fmaf(wa1, ha1, t); t = fmaf(wa2, ha2, t); t = fmaf(wa3, xa, t);
-        const float va = silu_det(t); ha0 = ha1; ha1 = ha2; ha2 = xa;
-        sall[it][sa_] = va;
-        float vb = 0.f;
-        if (tid < D) {
-            const float xb = sall[it][sb_];
-            float u = wb0 * hb0; u = fmaf(wb1, hb1, u); u = fmaf(wb2, hb2, u); u = fmaf(wb3, xb, u);
-            vb = silu_det(u); hb0 = hb1; hb1 = hb2; hb2 = xb;
-            sall[it][sb_] = vb;
-        }
-        // squared l2 norms: xor tree inside the warp, warp sums added in warp order afterwards
-        float pq = tid < D ? va * va : 0.f, pk = tid < D ? vb * vb : 0.f;
+    GDN_TICK(3);
+    // Every CTA reads and writes only its own channels of the saved rows and of the history (beta / alpha: rank 0), so
+    // they can be rewritten at once: raw inputs of the new rows for a later commit, history after the accepted prefix.
+    for (int e = tid; e < T * 96; e += 256) { const int t = e / 96, c = e - t * 96; sav[t * 388 + ch_slot(c)] = raw[3 + nrep + t][c]; }
+    if (rank == 0 && tid < T) { sav[tid * 388 + 384] = sraw_b[nrep + tid]; sav[tid * 388 + 385] = sraw_a[nrep + tid]; }
+    if (nrep > 0)
+        for (int e = tid; e < 3 * 96; e += 256) { const int tap = e / 96, c = e - tap * 96; cst[tap * 384 + ch_slot(c)] = raw[nrep + tap][c]; }
+    cluster_wait();
+    GDN_TICK(4);
+    if (rank == 0 && tid < nrows) {   // gates of every row, sent to the four CTAs
+        const float be = sigmoid_det(sraw_b[tid]);
+        const float de = expf_det(bf2f(a.a_neg[h]) * softplus_det(sraw_a[tid] + bf2f(a.dt_bias[h])));
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) { pq = pq + __shfl_xor_sync(0xffffffffu, pq, off); pk = pk + __shfl_xor_sync(0xffffffffu, pk, off); }
-        if (lane == 0) { red[2 * it][warp] = pq; red[2 * it + 1][warp] = pk; }
+        for (int r = 0; r < GDN_CL; ++r) { st_cluster_f32(&sbeta[tid], r, be); st_cluster_f32(&sdecay[tid], r, de); }
     }
-    if (T == 0 && nrep > 0) {   // pure commit: the loop above never reached it == nrep
-        cst[sa_] = ha0; cst[384 + sa_] = ha1; cst[768 + sa_] = ha2;
-        if (tid < D) { cst[sb_] = hb0; cst[384 + sb_] = hb1; cst[768 + sb_] = hb2; }
+    GDN_TICK(5);
+    // conv + SiLU of every (row, channel) independently; squared l2 norms of q and k: xor tree over the warp's 32
+    // channels, the warp sum goes to all four CTAs (slot = this CTA's rank)
+    for (int e = tid; e < nrows * 96; e += 256) {
+        const int it = e / 96, c = e - it * 96;
+        const float4 w = *reinterpret_cast<const float4*>(a.conv_w + (size_t)ch_col(c) * 4);
+        float t = w.x * raw[it][c]; t = fmaf(w.y, raw[it + 1][c], t); t = fmaf(w.z, raw[it + 2][c], t); t = fmaf(w.w, raw[it + 3][c], t);
+        const float v = silu_det(t);
+        if (c >= 64) { sv[it][c - 64] = v; continue; }   // warp-uniform: a warp covers one group of one row
+        cown[it][c] = v;
+        float p = v * v;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) p = p + __shfl_xor_sync(0xffffffffu, p, off);
+        if (lane < GDN_CL) st_cluster_f32(&csum[it][c >> 5][rank], (uint32_t)lane, p);
     }
-    __syncthreads();
-    if (tid < 2 * nrows) { float t = red[tid][0]; for (int w = 1; w < 8; ++w) t = t + red[tid][w]; tot[tid] = t; }
-    __syncthreads();
-    if (tid < D)
-        for (int it = 0; it < nrows; ++it) {
-            sall[it][tid] = sall[it][tid] / fmaxf(sqrtf(tot[2 * it]), a.eps);
-            sall[it][D + tid] = sall[it][D + tid] / fmaxf(sqrtf(tot[2 * it + 1]), a.eps);
-        }
-    __syncthreads();
+    GDN_TICK(6);
+    cluster_sync_all();
+    GDN_TICK(7);
+    // normalise the own 32 q and 32 k channels of every row and hand them to all four CTAs
+    for (int e = tid; e < nrows * 64; e += 256) {
+        const int it = e >> 6, c = e & 63, g2 = c >> 5;
+        float tot = csum[it][g2][0]; tot = tot + csum[it][g2][1]; tot = tot + csum[it][g2][2]; tot = tot + csum[it][g2][3];
+        const float v = cown[it][c] / fmaxf(sqrtf(tot), a.eps);
+        const int ch = 32 * rank + (c & 31);
+        float* dst = &sqk[it][g2 * 160 + (ch >> 4) * 20 + (ch & 15)];
+#pragma unroll
+        for (int r = 0; r < GDN_CL; ++r) st_cluster_f32(dst, r, v);
+    }
+    GDN_TICK(8);
+    cluster_sync_all();
+    GDN_TICK(9);
 
     // ---- phase 2: the recurrence, row after row, state in registers; no block-wide synchronisation inside
     for (int it = 0; it < nrows; ++it) {
         if (it == nrep && nrep > 0) commit_state();
         const float beta = sbeta[it], decay = sdecay[it];
-        const float* kk = &sall[it][D + 64 * ih]; const float* qq = &sall[it][64 * ih];
-        float kr[64];
+        const float* kk = &sqk[it][160 + 20 * ck]; const float* qq = &sqk[it][20 * ck];
+        float kr[16];
 #pragma unroll
-        for (int i = 0; i < 64; i += 4) { const float4 v = *reinterpret_cast<const float4*>(kk + i); kr[i] = v.x; kr[i + 1] = v.y; kr[i + 2] = v.z; kr[i + 3] = v.w; }
+        for (int i = 0; i < 16; i += 4) { const float4 v = *reinterpret_cast<const float4*>(kk + i); kr[i] = v.x; kr[i + 1] = v.y; kr[i + 2] = v.z; kr[i + 3] = v.w; }
         float dot = 0.f;
 #pragma unroll
-        for (int i = 0; i < 64; ++i) { m[i] = m[i] * decay; dot = fmaf(m[i], kr[i], dot); }
-        dot = dot + __shfl_xor_sync(0xffffffffu, dot, 1);
-        const float delta = (sall[it][2 * D + j] - dot) * beta;
+        for (int i = 0; i < 16; ++i) { m[i] = m[i] * decay; dot = fmaf(m[i], kr[i], dot); }
+#pragma unroll
+        for (int off = 1; off < 8; off <<= 1) dot = dot + __shfl_xor_sync(0xffffffffu, dot, off);
+        const float delta = (sv[it][jl] - dot) * beta;
         float o = 0.f;
 #pragma unroll
-        for (int i = 0; i < 64; i += 4) {
+        for (int i = 0; i < 16; i += 4) {
             const float4 qv = *reinterpret_cast<const float4*>(qq + i);
             m[i] = fmaf(delta, kr[i], m[i]); o = fmaf(m[i], qv.x, o);
             m[i + 1] = fmaf(delta, kr[i + 1], m[i + 1]); o = fmaf(m[i + 1], qv.y, o);
             m[i + 2] = fmaf(delta, kr[i + 2], m[i + 2]); o = fmaf(m[i + 2], qv.z, o);
             m[i + 3] = fmaf(delta, kr[i + 3], m[i + 3]); o = fmaf(m[i + 3], qv.w, o);
         }
-        o = o + __shfl_xor_sync(0xffffffffu, o, 1);
-        if (it >= nrep) {
-            if (ih == 0) sout[it - nrep][j] = o * 0.08838834764831845f;
-            if (a.snap) {
-                float* sp = a.snap + (size_t)(it - nrep) * a.snap_row_stride + ((size_t)h * D + j) * D + 64 * ih;
 #pragma unroll
-                for (int i = 0; i < 64; ++i) sp[i] = m[i];
+        for (int off = 1; off < 8; off <<= 1) o = o + __shfl_xor_sync(0xffffffffu, o, off);
+        if (it >= nrep) {
+            if (ck == 0) sout[it - nrep][jl] = o * 0.08838834764831845f;
+            if (a.snap) {
+                float* sp = a.snap + (size_t)(it - nrep) * a.snap_row_stride + ((size_t)h * D + j) * D + 16 * ck;
+#pragma unroll
+                for (int i = 0; i < 16; i += 4) *reinterpret_cast<float4*>(sp + i) = make_float4(m[i], m[i + 1], m[i + 2], m[i + 3]);
             }
         }
     }
     if (T == 0 && nrep > 0) commit_state();
+    GDN_TICK(10);
     __syncthreads();
+    GDN_TICK(11);
 
-    // ---- phase 3: per-head RMSNorm * w * gate(z) + quantisation of the new rows
-    for (int t = 0; t < T; ++t) {
-        float ps = tid < D ? sout[t][tid] * sout[t][tid] : 0.f;
+    // ---- phase 3: per-head RMSNorm * w * gate(z) + quantisation of the new rows; warp t takes row t, lane = channel.
+    // The sum of squares over the head's 128 channels: every CTA sends its warp sum to all four CTAs of the cluster.
+    if (warp < T) {
+        float ps = sout[warp][lane] * sout[warp][lane];
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) ps = ps + __shfl_xor_sync(0xffffffffu, ps, off);
-        if (lane == 0) red[t][warp] = ps;
+        if (lane < GDN_CL) st_cluster_f32(&cred[warp][rank], (uint32_t)lane, ps);
     }
-    __syncthreads();
-    if (tid < T) { float t = red[tid][0]; for (int w = 1; w < 8; ++w) t = t + red[tid][w]; tot[tid] = t; }
-    __syncthreads();
-    if (tid < D)
-        for (int t = 0; t < T; ++t) {
-            const int row = r0 + t;
-            const size_t oi = (size_t)row * Z + h * D + tid;
-            const float zz = a.rows[(size_t)row * a.ld + a.off_z + h * D + tid];
-            const float v = ((sout[t][tid] * (1.0f / sqrtf(tot[t] / (float)D + a.eps))) * bf2f(a.norm_w[tid])) * (a.sigmoid_gate ? sigmoid_det(zz) : silu_det(zz));
-            if (a.out) a.out[oi] = v;
-            if (a.oq) warp_quant32_store(v, row, (h * D + tid) >> 5, Z, a.oq, a.osc, lane);
-        }
+    GDN_TICK(12);
+    cluster_sync_all();
+    GDN_TICK(13);
+    if (warp < T) {
+        float ss = cred[warp][0]; ss = ss + cred[warp][1]; ss = ss + cred[warp][2]; ss = ss + cred[warp][3];
+        const int row = r0 + warp, c = 32 * rank + lane;
+        const size_t oi = (size_t)row * Z + h * D + c;
+        const float zz = a.rows[(size_t)row * a.ld + a.off_z + h * D + c];
+        const float v = ((sout[warp][lane] * (1.0f / sqrtf(ss / (float)D + a.eps))) * bf2f(a.norm_w[c])) * (a.sigmoid_gate ? sigmoid_det(zz) : silu_det(zz));
+        if (a.out) a.out[oi] = v;
+        if (a.oq) warp_quant32_store(v, row, (h * D + c) >> 5, Z, a.oq, a.osc, lane);
+    }
+    GDN_TICK(14);
 }
 
 }  // namespace
@@ -317,14 +416,22 @@ int embed_bf16(const int* tok, const void* table, float* out, int R, int E, int 
 }
 int add_rmsnorm_quant(float* x, const float* y, int P, size_t part_stride, int ldy, const void* w_bf16, float* xn, XQ8F xq, int R, int n, float eps, cudaStream_t s) {
     HP_REQUIRE(R >= 1 && n > 0 && n % 64 == 0, "add_rmsnorm_quant: n=%d must be a positive multiple of 64", n);
-    HP_REQUIRE(n <= NORM_THREADS * NORM_MAXE, "add_rmsnorm_quant: n=%d exceeds %d", n, NORM_THREADS * NORM_MAXE);
-    launch_pdl(k_add_rmsnorm_quant, dim3(R), dim3(NORM_THREADS), 0, s, x, y, P, part_stride, ldy, (const uint16_t*)w_bf16, xn, (int8_t*)xq.q, (float*)xq.sc, n, eps);
+    HP_REQUIRE(n <= NORM_ROWT * 4 * NORM_MAXG, "add_rmsnorm_quant: n=%d exceeds %d", n, NORM_ROWT * 4 * NORM_MAXG);
+    HP_REQUIRE(!y || (ldy % 4 == 0 && part_stride % 4 == 0), "add_rmsnorm_quant: plane strides must be multiples of 4 floats");
+    const int pt = !y || P == 1 ? 1 : P == 2 ? 2 : P == 4 ? 4 : 0;
+    auto pick = [&](auto ng_tag) {
+        constexpr int NG = decltype(ng_tag)::value;
+        return pt == 1 ? k_add_rmsnorm_quant<1, NG> : pt == 2 ? k_add_rmsnorm_quant<2, NG> : pt == 4 ? k_add_rmsnorm_quant<4, NG> : k_add_rmsnorm_quant<0, NG>;
+    };
+    auto kern = n <= NORM_ROWT * 4 ? pick(std::integral_constant<int, 1>()) : pick(std::integral_constant<int, NORM_MAXG>());
+    HP_CUDA(launch_pdl(kern, dim3(R * NORM_CL), dim3(NORM_TPB), 0, s, x, y, P, part_stride, ldy, (const uint16_t*)w_bf16, xn, (int8_t*)xq.q, (float*)xq.sc, n, eps));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 int norm2_concat_quant(const float* a, const void* wa, const float* b, int ldb, const void* wb, float* out, XQ8F xq, int R, int n, float eps, cudaStream_t s) {
-    HP_REQUIRE(R >= 1 && n > 0 && n % 64 == 0, "norm2_concat_quant: n=%d must be a positive multiple of 64", n);
-    HP_REQUIRE(n <= NORM_THREADS * NORM_MAXE, "norm2_concat_quant: n=%d exceeds %d", n, NORM_THREADS * NORM_MAXE);
-    launch_pdl(k_norm2_concat_quant, dim3(R), dim3(NORM_THREADS), 0, s, a, (const uint16_t*)wa, b, ldb, (const uint16_t*)wb, out, (int8_t*)xq.q, (float*)xq.sc, n, eps);
+    HP_REQUIRE(R >= 1 && n > 0 && n % 64 == 0 && ldb % 4 == 0, "norm2_concat_quant: n=%d must be a positive multiple of 64 (ldb a multiple of 4)", n);
+    HP_REQUIRE(n <= NORM_ROWT * 4 * NORM_MAXG, "norm2_concat_quant: n=%d exceeds %d", n, NORM_ROWT * 4 * NORM_MAXG);
+    auto kern = n <= NORM_ROWT * 4 ? k_norm2_concat_quant<1> : k_norm2_concat_quant<NORM_MAXG>;
+    HP_CUDA(launch_pdl(kern, dim3(R * NORM_CL), dim3(NORM_TPB), 0, s, a, (const uint16_t*)wa, b, ldb, (const uint16_t*)wb, out, (int8_t*)xq.q, (float*)xq.sc, n, eps));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 int silu_mul_quant(const float* gu, int ldg, int F, XQ8F xq, int R, cudaStream_t s) {
@@ -332,6 +439,10 @@ int silu_mul_quant(const float* gu, int ldg, int F, XQ8F xq, int R, cudaStream_t
     launch_pdl(k_silu_mul_quant, dim3((F / 32 + 7) / 8, R), dim3(256), 0, s, gu, ldg, F, (int8_t*)xq.q, (float*)xq.sc);
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
+#ifdef HP_GDN_TIMING
+extern "C" int hp_debug_norm_clocks(long long* out) { return (int)cudaMemcpyFromSymbol(out, g_norm_clk, sizeof(long long) * 16); }
+extern "C" int hp_debug_gdn_clocks(long long* out) { return (int)cudaMemcpyFromSymbol(out, g_gdn_clk, sizeof(long long) * 16); }
+#endif
 int gdn_forward(const GdnParams& p, int nseq, cudaStream_t s) {
     HP_REQUIRE(nseq >= 1 && nseq <= 8 && p.n_qk >= 1 && p.n_v >= p.n_qk, "gdn_forward: bad shape");
     GdnArgs a;
@@ -340,9 +451,7 @@ int gdn_forward(const GdnParams& p, int nseq, cudaStream_t s) {
     a.state = p.state; a.conv_state = p.conv_state; a.state_stride = p.state_stride; a.conv_stride = p.conv_stride;
     a.seq = p.seq; a.replay_n = p.replay_n; a.out = p.out; a.oq = (int8_t*)p.xq.q; a.osc = (float*)p.xq.sc;
     a.snap = p.snap; a.snap_row_stride = p.snap_row_stride; a.eps = p.eps; a.sigmoid_gate = p.sigmoid_gate;
-    static bool attr = false;
-    if (!attr) { HP_CUDA(cudaFuncSetAttribute(k_gdn, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * GDN_STG_LD * 4)); attr = true; }
-    HP_CUDA(launch_pdl(k_gdn, dim3(p.n_v, nseq), dim3(256), 128 * GDN_STG_LD * 4, s, a));
+    HP_CUDA(launch_pdl(k_gdn, dim3(p.n_v * GDN_CL, nseq), dim3(256), 0, s, a));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 

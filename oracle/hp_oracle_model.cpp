@@ -77,22 +77,23 @@ struct XQ { std::vector<int8_t> q; std::vector<float> d, s; int K = 0; void set(
 
 // ---------------------------------------------------------------- layer kernels (row layout)
 // ops.hip:79-98: x += y; xn = x * rsqrt(mean x^2 + eps) * w; q8. Here y = sum of P planes in plane order; the sum of
-// squares: 1024 workers, worker i takes elements i, i+1024, ... (fmaf chain), then det_block_sum.
+// squares: 1280 workers, worker t takes the 4-element groups t, t+1280, ... (fmaf chain in index order), then det_block_sum.
 extern "C" void orc_add_rmsnorm_quant(float* x, const float* y, int P, size_t part_stride, int ldy, const uint16_t* w, float* xn,
                                       int8_t* q, float* d, float* s, int R, int n, float eps) {
     std::vector<float> v(n);
     for (int r = 0; r < R; ++r) {
-        float* xr = x + (size_t)r * n; float part[1024];
-        for (int t = 0; t < 1024; ++t) {
+        float* xr = x + (size_t)r * n; float part[1280];
+        for (int t = 0; t < 1280; ++t) {
             float ss = 0.f;
-            for (int i = t; i < n; i += 1024) {
-                float a = xr[i];
-                if (y) { float sum = y[(size_t)r * ldy + i]; for (int p = 1; p < P; ++p) sum = sum + y[(size_t)p * part_stride + (size_t)r * ldy + i]; a = a + sum; xr[i] = a; }
-                ss = fmaf(a, a, ss);
-            }
+            for (int g = t; g < n / 4; g += 1280)
+                for (int i = 4 * g; i < 4 * g + 4; ++i) {
+                    float a = xr[i];
+                    if (y) { float sum = y[(size_t)r * ldy + i]; for (int p = 1; p < P; ++p) sum = sum + y[(size_t)p * part_stride + (size_t)r * ldy + i]; a = a + sum; xr[i] = a; }
+                    ss = fmaf(a, a, ss);
+                }
             part[t] = ss;
         }
-        const float tot = det_block_sum(part, 1024);
+        const float tot = det_block_sum(part, 1280);
         const float scl = 1.0f / sqrtf(tot / (float)n + eps);
         for (int i = 0; i < n; ++i) { v[i] = (xr[i] * scl) * bf2f(w[i]); if (xn) xn[(size_t)r * n + i] = v[i]; }
         orc_quantize_x_q8(v.data(), 1, n, q + (size_t)r * n, d + (size_t)r * (n / 32), s + (size_t)r * (n / 32));
@@ -103,9 +104,13 @@ extern "C" void orc_norm2_concat_quant(const float* a, const uint16_t* wa, const
                                        int8_t* q, float* d, float* s, int R, int n, float eps) {
     std::vector<float> v(2 * n);
     for (int r = 0; r < R; ++r) {
-        const float* ar = a + (size_t)r * n; const float* br = b + (size_t)r * ldb; float pa[1024], pb[1024];
-        for (int t = 0; t < 1024; ++t) { float sa = 0.f, sb = 0.f; for (int i = t; i < n; i += 1024) { sa = fmaf(ar[i], ar[i], sa); sb = fmaf(br[i], br[i], sb); } pa[t] = sa; pb[t] = sb; }
-        const float ca = 1.0f / sqrtf(det_block_sum(pa, 1024) / (float)n + eps), cb = 1.0f / sqrtf(det_block_sum(pb, 1024) / (float)n + eps);
+        const float* ar = a + (size_t)r * n; const float* br = b + (size_t)r * ldb; float pa[1280], pb[1280];
+        for (int t = 0; t < 1280; ++t) {
+            float sa = 0.f, sb = 0.f;
+            for (int g = t; g < n / 4; g += 1280) for (int i = 4 * g; i < 4 * g + 4; ++i) { sa = fmaf(ar[i], ar[i], sa); sb = fmaf(br[i], br[i], sb); }
+            pa[t] = sa; pb[t] = sb;
+        }
+        const float ca = 1.0f / sqrtf(det_block_sum(pa, 1280) / (float)n + eps), cb = 1.0f / sqrtf(det_block_sum(pb, 1280) / (float)n + eps);
         for (int i = 0; i < n; ++i) { v[i] = (ar[i] * ca) * bf2f(wa[i]); v[n + i] = (br[i] * cb) * bf2f(wb[i]); }
         if (out) memcpy(out + (size_t)r * 2 * n, v.data(), (size_t)2 * n * 4);
         orc_quantize_x_q8(v.data(), 1, 2 * n, q + (size_t)r * 2 * n, d + (size_t)r * (2 * n / 32), s + (size_t)r * (2 * n / 32));
@@ -150,12 +155,12 @@ extern "C" void orc_gdn_rows(const float* rows, int ld, int T, int n_qk, int n_v
             const float decay = orc_expf(bf2f(a_neg[h]) * orc_softplus(row[off_a + h] + bf2f(dt_bias[h])));
             float* M = state + (size_t)h * D * D;
             for (int j = 0; j < D; ++j) {
-                float dd[2];
-                for (int ih = 0; ih < 2; ++ih) { float dot = 0.f; float* m = M + (size_t)j * D + 64 * ih; for (int i = 0; i < 64; ++i) { m[i] = m[i] * decay; dot = fmaf(m[i], sk[64 * ih + i], dot); } dd[ih] = dot; }
-                const float delta = (v[j] - (dd[0] + dd[1])) * beta;
-                float oo[2];
-                for (int ih = 0; ih < 2; ++ih) { float o = 0.f; float* m = M + (size_t)j * D + 64 * ih; for (int i = 0; i < 64; ++i) { m[i] = fmaf(delta, sk[64 * ih + i], m[i]); o = fmaf(m[i], sq[64 * ih + i], o); } oo[ih] = o; }
-                so[j] = (oo[0] + oo[1]) * 0.08838834764831845f;
+                // 8 partial sums over 16 consecutive key indices each, combined by an xor tree (offsets 1, 2, 4)
+                float dd[8], oo[8];
+                for (int c = 0; c < 8; ++c) { float dot = 0.f; float* m = M + (size_t)j * D + 16 * c; for (int i = 0; i < 16; ++i) { m[i] = m[i] * decay; dot = fmaf(m[i], sk[16 * c + i], dot); } dd[c] = dot; }
+                const float delta = (v[j] - (((dd[0] + dd[1]) + (dd[2] + dd[3])) + ((dd[4] + dd[5]) + (dd[6] + dd[7])))) * beta;
+                for (int c = 0; c < 8; ++c) { float o = 0.f; float* m = M + (size_t)j * D + 16 * c; for (int i = 0; i < 16; ++i) { m[i] = fmaf(delta, sk[16 * c + i], m[i]); o = fmaf(m[i], sq[16 * c + i], o); } oo[c] = o; }
+                so[j] = (((oo[0] + oo[1]) + (oo[2] + oo[3])) + ((oo[4] + oo[5]) + (oo[6] + oo[7]))) * 0.08838834764831845f;
             }
             if (out) {
                 for (int i = 0; i < 256; ++i) part[i] = i < D ? so[i] * so[i] : 0.f;
