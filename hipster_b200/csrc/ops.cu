@@ -242,140 +242,182 @@ struct GdnArgs {
 };
 constexpr int GDN_MAXROWS = 16, GDN_CL = 4;   // replayed rows (<= 8) + new rows (<= 8) of one sequence; CTAs per head
 #ifdef HP_GDN_TIMING
-__device__ long long g_gdn_clk[16];
+__device__ long long g_gdn_clk[32];
 #define GDN_TICK(i) do { if (threadIdx.x == 0 && blockIdx.x == 5 && blockIdx.y == 0) g_gdn_clk[i] = clock64(); } while (0)
 #else
 #define GDN_TICK(i) do { } while (0)
 #endif
+__device__ __forceinline__ float2 gdn_mul2(float2 a, float2 b) {
+    float2 r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(reinterpret_cast<unsigned long long&>(r)) : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)));
+    return r;
+}
+__device__ __forceinline__ float2 gdn_fma2(float2 a, float2 b, float2 c) {   // a * b + c per lane, one rounding each
+    float2 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(reinterpret_cast<unsigned long long&>(r))
+        : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)), "l"(reinterpret_cast<unsigned long long&>(c)));
+    return r;
+}
 __global__ void __cluster_dims__(GDN_CL, 1, 1) __launch_bounds__(256) k_gdn(GdnArgs a) {
-    constexpr int D = 128;
-    // normalised q | k of every row (filled by all four CTAs); 16-float chunks padded to 20 so that the eight chunk
-    // owners of a state row read 128 bits each from distinct banks
+    constexpr int D = 128, NLD = 8, NCV = 6;   // items per thread: (16 + 3) * 96 <= 8 * 256 raw values, 16 * 96 = 6 * 256 conv outputs
+    // conv'ed, then normalised q | k of every row (filled by all four CTAs); 16-float chunks padded to 20 so that the
+    // eight chunk owners of a state row read 128 bits each from distinct banks
     __shared__ __align__(16) float sqk[GDN_MAXROWS][2 * 160];
-    __shared__ float raw[GDN_MAXROWS + 3][96], cown[GDN_MAXROWS][64], sv[GDN_MAXROWS][32], sout[8][32];
-    __shared__ float csum[GDN_MAXROWS][2][GDN_CL], sbeta[GDN_MAXROWS], sdecay[GDN_MAXROWS], sraw_b[GDN_MAXROWS], sraw_a[GDN_MAXROWS];
+    __shared__ float raw[GDN_MAXROWS + 3][96], sv[GDN_MAXROWS][32], sout[8][32];
+    __shared__ float csum[GDN_MAXROWS][2][GDN_CL], snrm[GDN_MAXROWS][2], sbeta[GDN_MAXROWS], sdecay[GDN_MAXROWS];
     __shared__ float cred[8][GDN_CL];
     pdl_launch_dependents();
     GDN_TICK(0);
     cluster_arrive_relaxed();   // matched by cluster_wait() before the first store into another CTA: every CTA has started by then
+    const int rank = blockIdx.x % GDN_CL, h = blockIdx.x / GDN_CL, hk = h % a.n_qk, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // Item e = tid + 256 k of this thread is (row index e / 96, local channel c = e % 96) both for the raw loads and for
+    // the conv outputs. Local channel c: group c/32 = q, k, v; channel 32*rank + c%32 of the head. Its slot in a
+    // history / saved row, its column in a row of the merged projection, its conv taps (independent of the predecessor):
+    int e_rr[NLD], e_c[NLD], e_slot[NLD], e_col[NLD];
+    float4 cw[NCV];
+#pragma unroll
+    for (int k = 0; k < NLD; ++k) {
+        const int e = tid + 256 * k, rr = e / 96, c = e - rr * 96, g3 = c >> 5, cl = 32 * rank + (c & 31);
+        e_rr[k] = rr; e_c[k] = c; e_slot[k] = g3 * D + cl;
+        e_col[k] = g3 == 0 ? hk * D + cl : g3 == 1 ? a.n_qk * D + hk * D + cl : 2 * a.n_qk * D + h * D + cl;
+        if (k < NCV) cw[k] = *reinterpret_cast<const float4*>(a.conv_w + (size_t)e_col[k] * 4);
+    }
+    const float nw = bf2f(a.norm_w[32 * rank + lane]);
     pdl_wait();
     GDN_TICK(1);
-    const int rank = blockIdx.x % GDN_CL, h = blockIdx.x / GDN_CL, hk = h % a.n_qk, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int r0 = a.seq[blockIdx.y * 4 + 0], T = min(a.seq[blockIdx.y * 4 + 1], 8), slot = a.seq[blockIdx.y * 4 + 2];
     float* sav = a.saved + (size_t)slot * a.saved_stride + (size_t)h * 8 * 388;   // [8][q 128 | k 128 | v 128 | beta | alpha | pad]
-    const int nrep = a.replay_n ? min(a.replay_n[slot], 8) : 0;
-    const int nrows = nrep + T;
-    const int Z = a.n_v * D;
     const int jl = tid >> 3, ck = tid & 7, j = 32 * rank + jl;
     float* Mrow = a.state + (size_t)slot * a.state_stride + ((size_t)h * D + j) * D + 16 * ck;
-    float m[16];
+    float2 m[8];
 #pragma unroll
-    for (int i = 0; i < 16; i += 4) { const float4 v = *reinterpret_cast<const float4*>(Mrow + i); m[i] = v.x; m[i + 1] = v.y; m[i + 2] = v.z; m[i + 3] = v.w; }
+    for (int i = 0; i < 8; i += 2) { const float4 v = *reinterpret_cast<const float4*>(Mrow + 2 * i); m[i] = make_float2(v.x, v.y); m[i + 1] = make_float2(v.z, v.w); }
     auto commit_state = [&]() {
 #pragma unroll
-        for (int i = 0; i < 16; i += 4) *reinterpret_cast<float4*>(Mrow + i) = make_float4(m[i], m[i + 1], m[i + 2], m[i + 3]);
+        for (int i = 0; i < 8; i += 2) *reinterpret_cast<float4*>(Mrow + 2 * i) = make_float4(m[i].x, m[i].y, m[i + 1].x, m[i + 1].y);
     };
     // conv history of this head: [3 taps][q 128 | k 128 | v 128]; private per v-head
     float* cst = a.conv_state + (size_t)slot * a.conv_stride + (size_t)h * 3 * 384;
-    // Local channel c of this CTA (0..95): group c/32 = q, k, v; channel 32*rank + c%32 of the head. Its slot in a
-    // history / saved row and its column in a row of the merged projection:
-    auto ch_slot = [&](int c) { return (c >> 5) * D + 32 * rank + (c & 31); };
-    auto ch_col = [&](int c) { const int g3 = c >> 5, cl = 32 * rank + (c & 31); return g3 == 0 ? hk * D + cl : g3 == 1 ? a.n_qk * D + hk * D + cl : 2 * a.n_qk * D + h * D + cl; };
+    const int nrep = a.replay_n ? min(a.replay_n[slot], 8) : 0;
+    const int nrows = nrep + T;
+    const int Z = a.n_v * D;
+    // gate input z of this lane's channel for the row that warp `warp` finishes in phase 3
+    const float zz = warp < T ? a.rows[(size_t)(r0 + warp) * a.ld + a.off_z + h * D + 32 * rank + lane] : 0.f;
 
-    // ---- phase 1: history (3 taps) + raw inputs of all rows -> raw[tap or 3 + row][c], by asynchronous 4-byte copies
-    for (int e = tid; e < (nrows + 3) * 96; e += 256) {
-        const int rr = e / 96, c = e - rr * 96, it = rr - 3;
-        const float* src = rr < 3 ? cst + rr * 384 + ch_slot(c)
-                         : it < nrep ? sav + it * 388 + ch_slot(c) : a.rows + (size_t)(r0 + it - nrep) * a.ld + ch_col(c);
-        cp_async4(&raw[rr][c], src);
+    // ---- phase 1: history (3 taps) + raw inputs of all rows -> raw[tap or 3 + row][c]; all loads in flight at once
+    {
+        float tmp[NLD];
+#pragma unroll
+        for (int k = 0; k < NLD; ++k) {
+            const int rr = e_rr[k], it = rr - 3;
+            if (rr < nrows + 3) {
+                const float* src = rr < 3 ? cst + rr * 384 + e_slot[k] : it < nrep ? sav + it * 388 + e_slot[k] : a.rows + (size_t)(r0 + it - nrep) * a.ld + e_col[k];
+                tmp[k] = *src;
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < NLD; ++k) if (e_rr[k] < nrows + 3) raw[e_rr[k]][e_c[k]] = tmp[k];
     }
-    if (rank == 0 && tid < nrows) {
-        const bool replay = tid < nrep;
-        const float* row = a.rows + (size_t)(replay ? 0 : r0 + (tid - nrep)) * a.ld;
-        cp_async4(&sraw_b[tid], replay ? sav + tid * 388 + 384 : row + a.off_b + h);
-        cp_async4(&sraw_a[tid], replay ? sav + tid * 388 + 385 : row + a.off_a + h);
+    // gates of every row (all four CTAs compute them: no exchange), by the last warp, which has the fewest conv items
+    float raw_b = 0.f, raw_a = 0.f;
+    if (warp == 7 && lane < nrows) {
+        const bool replay = lane < nrep;
+        const float* row = a.rows + (size_t)(replay ? 0 : r0 + (lane - nrep)) * a.ld;
+        raw_b = replay ? sav[lane * 388 + 384] : row[a.off_b + h];
+        raw_a = replay ? sav[lane * 388 + 385] : row[a.off_a + h];
+        sbeta[lane] = sigmoid_det(raw_b);
+        sdecay[lane] = expf_det(bf2f(a.a_neg[h]) * softplus_det(raw_a + bf2f(a.dt_bias[h])));
     }
     GDN_TICK(2);
-    cp_async_wait_all();
     __syncthreads();
     GDN_TICK(3);
-    // Every CTA reads and writes only its own channels of the saved rows and of the history (beta / alpha: rank 0), so
-    // they can be rewritten at once: raw inputs of the new rows for a later commit, history after the accepted prefix.
-    for (int e = tid; e < T * 96; e += 256) { const int t = e / 96, c = e - t * 96; sav[t * 388 + ch_slot(c)] = raw[3 + nrep + t][c]; }
-    if (rank == 0 && tid < T) { sav[tid * 388 + 384] = sraw_b[nrep + tid]; sav[tid * 388 + 385] = sraw_a[nrep + tid]; }
-    if (nrep > 0)
-        for (int e = tid; e < 3 * 96; e += 256) { const int tap = e / 96, c = e - tap * 96; cst[tap * 384 + ch_slot(c)] = raw[nrep + tap][c]; }
+    // Every CTA reads and writes only its own channels of the saved rows and of the history, so they can be rewritten at
+    // once: raw inputs of the new rows for a later commit, history after the accepted prefix. (beta / alpha are read by
+    // all four CTAs and rewritten by rank 0 after the first cluster barrier.)
+#pragma unroll
+    for (int k = 0; k < 3; ++k) { const int t = e_rr[k]; if (t < T) sav[t * 388 + e_slot[k]] = raw[3 + nrep + t][e_c[k]]; }
+    if (nrep > 0) {
+#pragma unroll
+        for (int k = 0; k < 2; ++k) { const int tap = e_rr[k]; if (tap < 3) cst[tap * 384 + e_slot[k]] = raw[nrep + tap][e_c[k]]; }
+    }
     cluster_wait();
     GDN_TICK(4);
-    if (rank == 0 && tid < nrows) {   // gates of every row, sent to the four CTAs
-        const float be = sigmoid_det(sraw_b[tid]);
-        const float de = expf_det(bf2f(a.a_neg[h]) * softplus_det(sraw_a[tid] + bf2f(a.dt_bias[h])));
+    // conv + SiLU of every (row, channel) independently. q and k go to all four CTAs; their squared l2 norms: xor tree
+    // over the warp's 32 channels, the warp sum goes to all four CTAs (slot = this CTA's rank)
 #pragma unroll
-        for (int r = 0; r < GDN_CL; ++r) { st_cluster_f32(&sbeta[tid], r, be); st_cluster_f32(&sdecay[tid], r, de); }
-    }
-    GDN_TICK(5);
-    // conv + SiLU of every (row, channel) independently; squared l2 norms of q and k: xor tree over the warp's 32
-    // channels, the warp sum goes to all four CTAs (slot = this CTA's rank)
-    for (int e = tid; e < nrows * 96; e += 256) {
-        const int it = e / 96, c = e - it * 96;
-        const float4 w = *reinterpret_cast<const float4*>(a.conv_w + (size_t)ch_col(c) * 4);
-        float t = w.x * raw[it][c]; t = fmaf(w.y, raw[it + 1][c], t); t = fmaf(w.z, raw[it + 2][c], t); t = fmaf(w.w, raw[it + 3][c], t);
-        const float v = silu_det(t);
-        if (c >= 64) { sv[it][c - 64] = v; continue; }   // warp-uniform: a warp covers one group of one row
-        cown[it][c] = v;
-        float p = v * v;
+    for (int k = 0; k < NCV; ++k) {
+        const int it = e_rr[k], c = e_c[k];
+        if (it < nrows) {   // warp-uniform: a warp covers one group of one row
+            const float4 w = cw[k];
+            float t = w.x * raw[it][c]; t = fmaf(w.y, raw[it + 1][c], t); t = fmaf(w.z, raw[it + 2][c], t); t = fmaf(w.w, raw[it + 3][c], t);
+            const float v = silu_det(t);
+            if (c >= 64) sv[it][c - 64] = v;
+            else {
+                const int g2 = c >> 5, ch = 32 * rank + (c & 31);
+                float* dst = &sqk[it][g2 * 160 + (ch >> 4) * 20 + (ch & 15)];
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) p = p + __shfl_xor_sync(0xffffffffu, p, off);
-        if (lane < GDN_CL) st_cluster_f32(&csum[it][c >> 5][rank], (uint32_t)lane, p);
+                for (int r = 0; r < GDN_CL; ++r) st_cluster_f32(dst, r, v);
+                float p = v * v;
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) p = p + __shfl_xor_sync(0xffffffffu, p, off);
+                if (lane < GDN_CL) st_cluster_f32(&csum[it][g2][rank], (uint32_t)lane, p);
+            }
+        }
     }
     GDN_TICK(6);
     cluster_sync_all();
     GDN_TICK(7);
-    // normalise the own 32 q and 32 k channels of every row and hand them to all four CTAs
-    for (int e = tid; e < nrows * 64; e += 256) {
-        const int it = e >> 6, c = e & 63, g2 = c >> 5;
-        float tot = csum[it][g2][0]; tot = tot + csum[it][g2][1]; tot = tot + csum[it][g2][2]; tot = tot + csum[it][g2][3];
-        const float v = cown[it][c] / fmaxf(sqrtf(tot), a.eps);
-        const int ch = 32 * rank + (c & 31);
-        float* dst = &sqk[it][g2 * 160 + (ch >> 4) * 20 + (ch & 15)];
-#pragma unroll
-        for (int r = 0; r < GDN_CL; ++r) st_cluster_f32(dst, r, v);
+    if (rank == 0 && warp == 7 && lane >= nrep && lane < nrows) { sav[(lane - nrep) * 388 + 384] = raw_b; sav[(lane - nrep) * 388 + 385] = raw_a; }
+    if (tid < 2 * nrows) {
+        const float* cs = &csum[tid >> 1][tid & 1][0];
+        float tot = cs[0]; tot = tot + cs[1]; tot = tot + cs[2]; tot = tot + cs[3];
+        snrm[tid >> 1][tid & 1] = fmaxf(sqrtf(tot), a.eps);
+    }
+    __syncthreads();
+    {   // normalise q | k of every row in place: thread tid owns channel tid (q for tid < 128, k otherwise)
+        const int off = (tid >> 7) * 160 + ((tid & 127) >> 4) * 20 + (tid & 15);
+        for (int it = 0; it < nrows; ++it) sqk[it][off] = sqk[it][off] / snrm[it][tid >> 7];
     }
     GDN_TICK(8);
-    cluster_sync_all();
+    __syncthreads();
     GDN_TICK(9);
 
     // ---- phase 2: the recurrence, row after row, state in registers; no block-wide synchronisation inside
     for (int it = 0; it < nrows; ++it) {
+        if (it == 1) GDN_TICK(20);
         if (it == nrep && nrep > 0) commit_state();
         const float beta = sbeta[it], decay = sdecay[it];
         const float* kk = &sqk[it][160 + 20 * ck]; const float* qq = &sqk[it][20 * ck];
-        float kr[16];
+        float2 kr[8];
 #pragma unroll
-        for (int i = 0; i < 16; i += 4) { const float4 v = *reinterpret_cast<const float4*>(kk + i); kr[i] = v.x; kr[i + 1] = v.y; kr[i + 2] = v.z; kr[i + 3] = v.w; }
+        for (int i = 0; i < 8; i += 2) { const float4 v = *reinterpret_cast<const float4*>(kk + 2 * i); kr[i] = make_float2(v.x, v.y); kr[i + 1] = make_float2(v.z, v.w); }
+        const float2 dc2 = make_float2(decay, decay);
         float dot = 0.f;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) { m[i] = m[i] * decay; dot = fmaf(m[i], kr[i], dot); }
+        for (int i = 0; i < 8; ++i) { m[i] = gdn_mul2(m[i], dc2); dot = fmaf(m[i].x, kr[i].x, dot); dot = fmaf(m[i].y, kr[i].y, dot); }
+        if (it == 1) GDN_TICK(21);
 #pragma unroll
         for (int off = 1; off < 8; off <<= 1) dot = dot + __shfl_xor_sync(0xffffffffu, dot, off);
+        if (it == 1) GDN_TICK(22);
         const float delta = (sv[it][jl] - dot) * beta;
+        const float2 dl2 = make_float2(delta, delta);
         float o = 0.f;
 #pragma unroll
-        for (int i = 0; i < 16; i += 4) {
-            const float4 qv = *reinterpret_cast<const float4*>(qq + i);
-            m[i] = fmaf(delta, kr[i], m[i]); o = fmaf(m[i], qv.x, o);
-            m[i + 1] = fmaf(delta, kr[i + 1], m[i + 1]); o = fmaf(m[i + 1], qv.y, o);
-            m[i + 2] = fmaf(delta, kr[i + 2], m[i + 2]); o = fmaf(m[i + 2], qv.z, o);
-            m[i + 3] = fmaf(delta, kr[i + 3], m[i + 3]); o = fmaf(m[i + 3], qv.w, o);
+        for (int i = 0; i < 8; i += 2) {
+            const float4 qv = *reinterpret_cast<const float4*>(qq + 2 * i);
+            m[i] = gdn_fma2(dl2, kr[i], m[i]); o = fmaf(m[i].x, qv.x, o); o = fmaf(m[i].y, qv.y, o);
+            m[i + 1] = gdn_fma2(dl2, kr[i + 1], m[i + 1]); o = fmaf(m[i + 1].x, qv.z, o); o = fmaf(m[i + 1].y, qv.w, o);
         }
+        if (it == 1) GDN_TICK(23);
 #pragma unroll
         for (int off = 1; off < 8; off <<= 1) o = o + __shfl_xor_sync(0xffffffffu, o, off);
+        if (it == 1) GDN_TICK(24);
         if (it >= nrep) {
             if (ck == 0) sout[it - nrep][jl] = o * 0.08838834764831845f;
             if (a.snap) {
                 float* sp = a.snap + (size_t)(it - nrep) * a.snap_row_stride + ((size_t)h * D + j) * D + 16 * ck;
 #pragma unroll
-                for (int i = 0; i < 16; i += 4) *reinterpret_cast<float4*>(sp + i) = make_float4(m[i], m[i + 1], m[i + 2], m[i + 3]);
+                for (int i = 0; i < 8; i += 2) *reinterpret_cast<float4*>(sp + 2 * i) = make_float4(m[i].x, m[i].y, m[i + 1].x, m[i + 1].y);
             }
         }
     }
@@ -392,6 +434,7 @@ __global__ void __cluster_dims__(GDN_CL, 1, 1) __launch_bounds__(256) k_gdn(GdnA
         for (int off = 16; off > 0; off >>= 1) ps = ps + __shfl_xor_sync(0xffffffffu, ps, off);
         if (lane < GDN_CL) st_cluster_f32(&cred[warp][rank], (uint32_t)lane, ps);
     }
+    const float gate = warp < T ? (a.sigmoid_gate ? sigmoid_det(zz) : silu_det(zz)) : 0.f;
     GDN_TICK(12);
     cluster_sync_all();
     GDN_TICK(13);
@@ -399,8 +442,7 @@ __global__ void __cluster_dims__(GDN_CL, 1, 1) __launch_bounds__(256) k_gdn(GdnA
         float ss = cred[warp][0]; ss = ss + cred[warp][1]; ss = ss + cred[warp][2]; ss = ss + cred[warp][3];
         const int row = r0 + warp, c = 32 * rank + lane;
         const size_t oi = (size_t)row * Z + h * D + c;
-        const float zz = a.rows[(size_t)row * a.ld + a.off_z + h * D + c];
-        const float v = ((sout[warp][lane] * (1.0f / sqrtf(ss / (float)D + a.eps))) * bf2f(a.norm_w[c])) * (a.sigmoid_gate ? sigmoid_det(zz) : silu_det(zz));
+        const float v = ((sout[warp][lane] * (1.0f / sqrtf(ss / (float)D + a.eps))) * nw) * gate;
         if (a.out) a.out[oi] = v;
         if (a.oq) warp_quant32_store(v, row, (h * D + c) >> 5, Z, a.oq, a.osc, lane);
     }
@@ -441,7 +483,7 @@ int silu_mul_quant(const float* gu, int ldg, int F, XQ8F xq, int R, cudaStream_t
 }
 #ifdef HP_GDN_TIMING
 extern "C" int hp_debug_norm_clocks(long long* out) { return (int)cudaMemcpyFromSymbol(out, g_norm_clk, sizeof(long long) * 16); }
-extern "C" int hp_debug_gdn_clocks(long long* out) { return (int)cudaMemcpyFromSymbol(out, g_gdn_clk, sizeof(long long) * 16); }
+extern "C" int hp_debug_gdn_clocks(long long* out) { return (int)cudaMemcpyFromSymbol(out, g_gdn_clk, sizeof(long long) * 32); }
 #endif
 int gdn_forward(const GdnParams& p, int nseq, cudaStream_t s) {
     HP_REQUIRE(nseq >= 1 && nseq <= 8 && p.n_qk >= 1 && p.n_v >= p.n_qk, "gdn_forward: bad shape");
