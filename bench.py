@@ -35,6 +35,7 @@ WORKLOADS = {
 }
 
 
+GEMV_TRAFFIC_RATIO = 1.033   # DRAM bytes / algorithmic weight bytes of k_gemv_q4k_sk, from the ncu capture under profiles/
 # kernel launches of one round (counted from the ncu launch lists under profiles/)
 ROUND_LAUNCHES = {"dense27b": 689, "moe": 636}
 
@@ -262,7 +263,8 @@ def run_dense(args, rank, local_rank, world):
         "e2e": {"value": toks / (wall_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 4 * n, "d2h_bytes_per_step": 256,
                 "note": "hp_spec_round with host token buffers; wall clock over the timed rounds, one stream synchronise per round"},
         "gpu_launches": args.steps * world * ROUND_LAUNCHES.get(args.workload, 0) if not args.layers else None,
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"], "traffic": None,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"], "traffic": verify_bytes * GEMV_TRAFFIC_RATIO,
+                     "traffic_note": "ncu dram read+write of the four GEMV launches of one layer / their weight bytes (profiles/gemv_q4k_sk_dense27b_layer.md), scaled to the pass",
                      "kernel": "k_gemv_q4k_sk: all GEMV launches of one 6-row verify pass (129 launches + LM head), timed alone with CUDA events",
                      "algorithmic_bytes": verify_bytes, "ms": gemv_ms, "full_pass_ms": pass_ms, "peak_source": pk["_src"],
                      "bytes_per_token_roofline": {"round_bytes": round_bytes, "tokens_per_round": tok_per_round, "bytes_per_token": bytes_per_token,
