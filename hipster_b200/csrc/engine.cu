@@ -309,10 +309,16 @@ int Engine::reset_slot(int slot) {
 
 int Engine::upload_desc() { HP_CUDA(cudaMemcpyAsync(d_desc_, h_desc_, D_INTS * 4, cudaMemcpyHostToDevice, s_)); return HP_OK; }
 
+// profiling only: class bit of a linear by its shape (16 gate|up, 32 down, 64 LM head, 128 input projections, 256 the rest)
+static int lin_class_bit(const Lin& l, const hp_model_cfg& c) {
+    return l.N == 2 * c.n_ff ? 16 : l.K == c.n_ff ? 32 : l.N == c.n_vocab ? 64 : l.K == c.n_embd ? 128 : 256;
+}
 int Engine::lin_parts(const Lin& l, int R) {
+    if (prof_skip_ & lin_class_bit(l, c_)) return HP_OK;
     return gemv_q4k_q8_parts(l.wt ? l.wt : l.w, xq_, yparts_, l.N, l.K, R, l.N, (size_t)R * l.N, err_, s_, pdl_, l.wt != nullptr);
 }
 int Engine::lin(const Lin& l, float* out, int ld, int R) {
+    if (prof_skip_ & lin_class_bit(l, c_)) return HP_OK;
     if (l.P == 1) return gemv_q4k_q8_parts(l.wt ? l.wt : l.w, xq_, out, l.N, l.K, R, ld, 0, err_, s_, pdl_, l.wt != nullptr);
     HP_TRY(lin_parts(l, R));
     k_reduce_planes<<<dim3((l.N + 255) / 256, R), 256, 0, s_>>>(yparts_, (size_t)R * l.N, l.P, out, l.N, ld);
@@ -594,7 +600,7 @@ size_t Engine::pass_weight_bytes(bool mtp, bool with_head) const {
 
 // Diagnostic: device time of `reps` back-to-back verify passes of R rows over whatever tokens / state are current
 // (what = 0), of only the GEMV launches of such passes (what = 1), or of passes that leave out kernel classes
-// (what = 16 + mask: 1 GDN, 2 norms, 4 attention, 8 SiLU; results are then meaningless, only the time is). State and KV are not committed.
+// (what = 16 + mask: 1 GDN, 2 norms, 4 attention, 8 SiLU, 16 gate|up, 32 down, 64 LM head, 128 input projections, 256 other GEMVs; results are then meaningless, only the time is). State and KV are not committed.
 int Engine::profile_pass(int R, int what, int reps, float* ms) {
     HP_REQUIRE(R >= 1 && R <= 8 && reps >= 1 && ms, "profile_pass: bad arguments");
     int* d = h_desc_;

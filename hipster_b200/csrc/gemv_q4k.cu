@@ -111,6 +111,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
     constexpr uint32_t unit_bytes = CB * 144u;
     y += (size_t)ct.part * part_stride;
 
+    HP_TRACE_BEGIN();
     pdl_launch_dependents();   // the next kernel may be scheduled; it waits for this one to finish before using its output
     if (lane == 0) {
         for (int s = 0; s < SK_STAGES; ++s) mbar_init(bar0 + 8 * s, 1);
@@ -145,6 +146,8 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
     for (int i = 0; i < SK_STAGES && i < nunits; ++i) issue();
 
     pdl_wait();
+    HP_TRACE_WAITED();
+
 #ifndef HP_DBG_NOX
     if (warp == 0) {   // quantised activations of blocks [kb0, kb0 + nbp), all NT column tiles, by bulk copies: one block
         // (2048 + 512 B) per copy pair, lanes in parallel, each CTA starting at a different block so that the 148 CTAs do
@@ -311,6 +314,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
             }
         store_tile(tile, v);
     }
+    HP_TRACE_END(1000 + N / 16);
 }
 
 // ---- f32-activation baseline: lane l of TPR takes blocks l, l+TPR, ...; xor-shuffle tree (gemv.hip:1177-1216) ----
@@ -411,6 +415,7 @@ __global__ void k_reduce_parts(const float* __restrict__ parts, size_t part_stri
 }
 
 }  // namespace
+HP_TRACE_READER(hp_debug_trace_gemv)
 
 int gemv_parts(int N, int K) { return gemv_num_parts(N, K / 256); }
 

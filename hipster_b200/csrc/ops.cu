@@ -44,12 +44,6 @@ __global__ void __launch_bounds__(256) k_embed_bf16(const int* __restrict__ tok,
 // sums (warp index over the cluster) added in order by every thread after the cluster barrier. Quantisation: a
 // 32-element sub-block is held by 8 consecutive lanes.
 constexpr int NORM_CL = 4, NORM_TPB = 320, NORM_ROWT = NORM_CL * NORM_TPB, NORM_NW = NORM_ROWT / 32, NORM_MAXG = 2;   // rows of up to 10240 elements
-#ifdef HP_GDN_TIMING
-__device__ long long g_norm_clk[16];
-#define NORM_TICK(i) do { if (threadIdx.x == 0 && blockIdx.x == 0) g_norm_clk[i] = clock64(); } while (0)
-#else
-#define NORM_TICK(i) do { } while (0)
-#endif
 // warp part of the cluster-wide sum: leaves this warp's sum in slot (10 * rank + warp) of every CTA's table
 __device__ __forceinline__ void norm_publish(float v, float* tab, int rank) {
 #pragma unroll
@@ -88,7 +82,7 @@ __global__ void __cluster_dims__(NORM_CL, 1, 1) __launch_bounds__(NORM_TPB) k_ad
                                                                      const uint16_t* __restrict__ w, float* __restrict__ xn, int8_t* __restrict__ q, float* __restrict__ sc,
                                                                      int n, float eps) {
     __shared__ float tab[NORM_NW];
-    NORM_TICK(0);
+    HP_TRACE_BEGIN();
     pdl_launch_dependents();
     cluster_arrive_relaxed();   // matched by cluster_wait() before the first store into another CTA
     const int rank = blockIdx.x % NORM_CL, r = blockIdx.x / NORM_CL, lane = threadIdx.x & 31, t = rank * NORM_TPB + threadIdx.x;
@@ -96,9 +90,8 @@ __global__ void __cluster_dims__(NORM_CL, 1, 1) __launch_bounds__(NORM_TPB) k_ad
     float wv[NG][4];
 #pragma unroll
     for (int k = 0; k < NG; ++k) { const int i = 4 * (t + k * NORM_ROWT); if (i < n) bf4(w + i, wv[k]); }   // weights do not depend on the previous kernel
-    NORM_TICK(1);
     pdl_wait();
-    NORM_TICK(2);
+    HP_TRACE_WAITED();
     float4 v[NG];
 #pragma unroll
     for (int k = 0; k < NG; ++k) { const int i = 4 * (t + k * NORM_ROWT); v[k] = i < n ? *reinterpret_cast<const float4*>(xr + i) : make_float4(0.f, 0.f, 0.f, 0.f); }
@@ -130,16 +123,13 @@ __global__ void __cluster_dims__(NORM_CL, 1, 1) __launch_bounds__(NORM_TPB) k_ad
             if (i < n) { v[k].x = v[k].x + s[k].x; v[k].y = v[k].y + s[k].y; v[k].z = v[k].z + s[k].z; v[k].w = v[k].w + s[k].w; *reinterpret_cast<float4*>(xr + i) = v[k]; }
         }
     }
-    NORM_TICK(3);
     float ss = 0.f;
 #pragma unroll
     for (int k = 0; k < NG; ++k) { ss = fmaf(v[k].x, v[k].x, ss); ss = fmaf(v[k].y, v[k].y, ss); ss = fmaf(v[k].z, v[k].z, ss); ss = fmaf(v[k].w, v[k].w, ss); }   // absent groups hold zeros
     cluster_wait();
-    NORM_TICK(4);
     norm_publish(ss, tab, rank);
     cluster_sync_all();
     ss = norm_total(tab);
-    NORM_TICK(5);
     const float scl = 1.0f / sqrtf(ss / (float)n + eps);
 #pragma unroll
     for (int k = 0; k < NG; ++k) {
@@ -150,7 +140,7 @@ __global__ void __cluster_dims__(NORM_CL, 1, 1) __launch_bounds__(NORM_TPB) k_ad
             quant4_store(o, r, i, n, q, sc, lane);
         }
     }
-    NORM_TICK(6);
+    HP_TRACE_END(2);
 }
 
 // ---- MTP input: out[r] = [rmsnorm(a[r]) * wa | rmsnorm(b[r]) * wb], quantised (ops.hip:99-116) ----
@@ -202,13 +192,16 @@ __global__ void __cluster_dims__(NORM_CL, 1, 1) __launch_bounds__(NORM_TPB) k_no
 
 // ---- xq = q8(silu(gate) * up); gate = columns [0, F), up = [F, 2F) of gu [R][ldg] (ops.hip:146-151) ----
 __global__ void __launch_bounds__(256) k_silu_mul_quant(const float* __restrict__ gu, int ldg, int F, int8_t* __restrict__ q, float* __restrict__ sc) {
+    HP_TRACE_BEGIN();
     pdl_launch_dependents();
     pdl_wait();
+    HP_TRACE_WAITED();
     const int r = blockIdx.y, sb = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (sb * 32 >= F) return;
     const int i = sb * 32 + lane;
     const float g = gu[(size_t)r * ldg + i], u = gu[(size_t)r * ldg + F + i];
     warp_quant32_store(silu_det(g) * u, r, sb, F, q, sc, lane);
+    HP_TRACE_END(3);
 }
 
 // ---- Gated DeltaNet: causal 4-tap depthwise conv + SiLU, then the gated delta rule, for one (v-head, sequence) ----
@@ -241,12 +234,6 @@ struct GdnArgs {
     float eps; int sigmoid_gate;
 };
 constexpr int GDN_MAXROWS = 16, GDN_CL = 4;   // replayed rows (<= 8) + new rows (<= 8) of one sequence; CTAs per head
-#ifdef HP_GDN_TIMING
-__device__ long long g_gdn_clk[32];
-#define GDN_TICK(i) do { if (threadIdx.x == 0 && blockIdx.x == 5 && blockIdx.y == 0) g_gdn_clk[i] = clock64(); } while (0)
-#else
-#define GDN_TICK(i) do { } while (0)
-#endif
 __device__ __forceinline__ float2 gdn_mul2(float2 a, float2 b) {
     float2 r;
     asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(reinterpret_cast<unsigned long long&>(r)) : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)));
@@ -266,8 +253,8 @@ __global__ void __cluster_dims__(GDN_CL, 1, 1) __launch_bounds__(256) k_gdn(GdnA
     __shared__ float raw[GDN_MAXROWS + 3][96], sv[GDN_MAXROWS][32], sout[8][32];
     __shared__ float csum[GDN_MAXROWS][2][GDN_CL], snrm[GDN_MAXROWS][2], sbeta[GDN_MAXROWS], sdecay[GDN_MAXROWS];
     __shared__ float cred[8][GDN_CL];
+    HP_TRACE_BEGIN();
     pdl_launch_dependents();
-    GDN_TICK(0);
     cluster_arrive_relaxed();   // matched by cluster_wait() before the first store into another CTA: every CTA has started by then
     const int rank = blockIdx.x % GDN_CL, h = blockIdx.x / GDN_CL, hk = h % a.n_qk, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // Item e = tid + 256 k of this thread is (row index e / 96, local channel c = e % 96) both for the raw loads and for
@@ -284,7 +271,7 @@ __global__ void __cluster_dims__(GDN_CL, 1, 1) __launch_bounds__(256) k_gdn(GdnA
     }
     const float nw = bf2f(a.norm_w[32 * rank + lane]);
     pdl_wait();
-    GDN_TICK(1);
+    HP_TRACE_WAITED();
     const int r0 = a.seq[blockIdx.y * 4 + 0], T = min(a.seq[blockIdx.y * 4 + 1], 8), slot = a.seq[blockIdx.y * 4 + 2];
     float* sav = a.saved + (size_t)slot * a.saved_stride + (size_t)h * 8 * 388;   // [8][q 128 | k 128 | v 128 | beta | alpha | pad]
     const int jl = tid >> 3, ck = tid & 7, j = 32 * rank + jl;
@@ -328,9 +315,7 @@ __global__ void __cluster_dims__(GDN_CL, 1, 1) __launch_bounds__(256) k_gdn(GdnA
         sbeta[lane] = sigmoid_det(raw_b);
         sdecay[lane] = expf_det(bf2f(a.a_neg[h]) * softplus_det(raw_a + bf2f(a.dt_bias[h])));
     }
-    GDN_TICK(2);
     __syncthreads();
-    GDN_TICK(3);
     // Every CTA reads and writes only its own channels of the saved rows and of the history, so they can be rewritten at
     // once: raw inputs of the new rows for a later commit, history after the accepted prefix. (beta / alpha are read by
     // all four CTAs and rewritten by rank 0 after the first cluster barrier.)
@@ -341,7 +326,6 @@ __global__ void __cluster_dims__(GDN_CL, 1, 1) __launch_bounds__(256) k_gdn(GdnA
         for (int k = 0; k < 2; ++k) { const int tap = e_rr[k]; if (tap < 3) cst[tap * 384 + e_slot[k]] = raw[nrep + tap][e_c[k]]; }
     }
     cluster_wait();
-    GDN_TICK(4);
     // conv + SiLU of every (row, channel) independently. q and k go to all four CTAs; their squared l2 norms: xor tree
     // over the warp's 32 channels, the warp sum goes to all four CTAs (slot = this CTA's rank)
 #pragma unroll
@@ -364,9 +348,7 @@ __global__ void __cluster_dims__(GDN_CL, 1, 1) __launch_bounds__(256) k_gdn(GdnA
             }
         }
     }
-    GDN_TICK(6);
     cluster_sync_all();
-    GDN_TICK(7);
     if (rank == 0 && warp == 7 && lane >= nrep && lane < nrows) { sav[(lane - nrep) * 388 + 384] = raw_b; sav[(lane - nrep) * 388 + 385] = raw_a; }
     if (tid < 2 * nrows) {
         const float* cs = &csum[tid >> 1][tid & 1][0];
@@ -378,13 +360,10 @@ __global__ void __cluster_dims__(GDN_CL, 1, 1) __launch_bounds__(256) k_gdn(GdnA
         const int off = (tid >> 7) * 160 + ((tid & 127) >> 4) * 20 + (tid & 15);
         for (int it = 0; it < nrows; ++it) sqk[it][off] = sqk[it][off] / snrm[it][tid >> 7];
     }
-    GDN_TICK(8);
     __syncthreads();
-    GDN_TICK(9);
 
     // ---- phase 2: the recurrence, row after row, state in registers; no block-wide synchronisation inside
     for (int it = 0; it < nrows; ++it) {
-        if (it == 1) GDN_TICK(20);
         if (it == nrep && nrep > 0) commit_state();
         const float beta = sbeta[it], decay = sdecay[it];
         const float* kk = &sqk[it][160 + 20 * ck]; const float* qq = &sqk[it][20 * ck];
@@ -395,10 +374,8 @@ __global__ void __cluster_dims__(GDN_CL, 1, 1) __launch_bounds__(256) k_gdn(GdnA
         float dot = 0.f;
 #pragma unroll
         for (int i = 0; i < 8; ++i) { m[i] = gdn_mul2(m[i], dc2); dot = fmaf(m[i].x, kr[i].x, dot); dot = fmaf(m[i].y, kr[i].y, dot); }
-        if (it == 1) GDN_TICK(21);
 #pragma unroll
         for (int off = 1; off < 8; off <<= 1) dot = dot + __shfl_xor_sync(0xffffffffu, dot, off);
-        if (it == 1) GDN_TICK(22);
         const float delta = (sv[it][jl] - dot) * beta;
         const float2 dl2 = make_float2(delta, delta);
         float o = 0.f;
@@ -408,10 +385,8 @@ __global__ void __cluster_dims__(GDN_CL, 1, 1) __launch_bounds__(256) k_gdn(GdnA
             m[i] = gdn_fma2(dl2, kr[i], m[i]); o = fmaf(m[i].x, qv.x, o); o = fmaf(m[i].y, qv.y, o);
             m[i + 1] = gdn_fma2(dl2, kr[i + 1], m[i + 1]); o = fmaf(m[i + 1].x, qv.z, o); o = fmaf(m[i + 1].y, qv.w, o);
         }
-        if (it == 1) GDN_TICK(23);
 #pragma unroll
         for (int off = 1; off < 8; off <<= 1) o = o + __shfl_xor_sync(0xffffffffu, o, off);
-        if (it == 1) GDN_TICK(24);
         if (it >= nrep) {
             if (ck == 0) sout[it - nrep][jl] = o * 0.08838834764831845f;
             if (a.snap) {
@@ -422,9 +397,7 @@ __global__ void __cluster_dims__(GDN_CL, 1, 1) __launch_bounds__(256) k_gdn(GdnA
         }
     }
     if (T == 0 && nrep > 0) commit_state();
-    GDN_TICK(10);
     __syncthreads();
-    GDN_TICK(11);
 
     // ---- phase 3: per-head RMSNorm * w * gate(z) + quantisation of the new rows; warp t takes row t, lane = channel.
     // The sum of squares over the head's 128 channels: every CTA sends its warp sum to all four CTAs of the cluster.
@@ -435,9 +408,7 @@ __global__ void __cluster_dims__(GDN_CL, 1, 1) __launch_bounds__(256) k_gdn(GdnA
         if (lane < GDN_CL) st_cluster_f32(&cred[warp][rank], (uint32_t)lane, ps);
     }
     const float gate = warp < T ? (a.sigmoid_gate ? sigmoid_det(zz) : silu_det(zz)) : 0.f;
-    GDN_TICK(12);
     cluster_sync_all();
-    GDN_TICK(13);
     if (warp < T) {
         float ss = cred[warp][0]; ss = ss + cred[warp][1]; ss = ss + cred[warp][2]; ss = ss + cred[warp][3];
         const int row = r0 + warp, c = 32 * rank + lane;
@@ -446,7 +417,7 @@ __global__ void __cluster_dims__(GDN_CL, 1, 1) __launch_bounds__(256) k_gdn(GdnA
         if (a.out) a.out[oi] = v;
         if (a.oq) warp_quant32_store(v, row, (h * D + c) >> 5, Z, a.oq, a.osc, lane);
     }
-    GDN_TICK(14);
+    HP_TRACE_END(4);
 }
 
 }  // namespace
@@ -481,10 +452,7 @@ int silu_mul_quant(const float* gu, int ldg, int F, XQ8F xq, int R, cudaStream_t
     launch_pdl(k_silu_mul_quant, dim3((F / 32 + 7) / 8, R), dim3(256), 0, s, gu, ldg, F, (int8_t*)xq.q, (float*)xq.sc);
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
-#ifdef HP_GDN_TIMING
-extern "C" int hp_debug_norm_clocks(long long* out) { return (int)cudaMemcpyFromSymbol(out, g_norm_clk, sizeof(long long) * 16); }
-extern "C" int hp_debug_gdn_clocks(long long* out) { return (int)cudaMemcpyFromSymbol(out, g_gdn_clk, sizeof(long long) * 32); }
-#endif
+HP_TRACE_READER(hp_debug_trace_ops)
 int gdn_forward(const GdnParams& p, int nseq, cudaStream_t s) {
     HP_REQUIRE(nseq >= 1 && nseq <= 8 && p.n_qk >= 1 && p.n_v >= p.n_qk, "gdn_forward: bad shape");
     GdnArgs a;
