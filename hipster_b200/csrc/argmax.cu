@@ -32,6 +32,8 @@ __device__ __forceinline__ void am_block_reduce(float& bv, int& bi, float* sv, i
     }
 }
 __global__ void __launch_bounds__(256) k_argmax_part(const float* __restrict__ x, int n, int ld, float* __restrict__ pv, int* __restrict__ pi) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float sv[8]; __shared__ int si[8];
     const int r = blockIdx.y, c0 = blockIdx.x * AM_CHUNK, c1 = min(n, c0 + AM_CHUNK);
     const float* xr = x + (size_t)r * ld;
@@ -41,6 +43,8 @@ __global__ void __launch_bounds__(256) k_argmax_part(const float* __restrict__ x
     if (threadIdx.x == 0) { pv[(size_t)r * gridDim.x + blockIdx.x] = bv; pi[(size_t)r * gridDim.x + blockIdx.x] = bi; }
 }
 __global__ void __launch_bounds__(256) k_argmax_final(const float* __restrict__ pv, const int* __restrict__ pi, int np, int* __restrict__ ids, float* __restrict__ vals) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float sv[8]; __shared__ int si[8];
     const int r = blockIdx.x;
     float bv = -INFINITY; int bi = -1;
@@ -72,8 +76,8 @@ int argmax_rows(const float* logits, int R, int n, int ld, int* ids, float* vals
     HP_REQUIRE(R >= 1 && n >= 1 && ld >= n && scratch, "argmax_rows: bad arguments R=%d n=%d ld=%d", R, n, ld);
     const int np = (n + AM_CHUNK - 1) / AM_CHUNK;
     float* pv = (float*)scratch; int* pi = (int*)(pv + (size_t)R * np);
-    k_argmax_part<<<dim3(np, R), 256, 0, s>>>(logits, n, ld, pv, pi);
-    k_argmax_final<<<R, 256, 0, s>>>(pv, pi, np, ids, vals);
+    HP_CUDA(launch_pdl<1>(k_argmax_part, dim3(np, R), dim3(256), 0, s, logits, n, ld, pv, pi));
+    HP_CUDA(launch_pdl<1>(k_argmax_final, dim3(R), dim3(256), 0, s, pv, pi, np, ids, vals));
     HP_CUDA(cudaGetLastError());
     return HP_OK;
 }
@@ -96,8 +100,8 @@ int argmax_rows_static(const float* logits, int R, int n, int ld, int* ids, floa
     }
     const int np = (n + AM_CHUNK - 1) / AM_CHUNK;
     float* pv = (float*)g_argmax_scratch_addr[dev]; int* pi = (int*)(pv + (size_t)R * np);
-    k_argmax_part<<<dim3(np, R), 256, 0, s>>>(logits, n, ld, pv, pi);
-    k_argmax_final<<<R, 256, 0, s>>>(pv, pi, np, ids, vals);
+    HP_CUDA(launch_pdl<1>(k_argmax_part, dim3(np, R), dim3(256), 0, s, logits, n, ld, pv, pi));
+    HP_CUDA(launch_pdl<1>(k_argmax_final, dim3(R), dim3(256), 0, s, pv, pi, np, ids, vals));
     HP_CUDA(cudaGetLastError());
     return HP_OK;
 }

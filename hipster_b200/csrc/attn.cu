@@ -37,6 +37,8 @@ __device__ __forceinline__ float block_sum_det(float v, float* sh) {
 __global__ void __launch_bounds__(256) k_qk_norm_rope_kv(float* __restrict__ qkv, int ld, int n_head, int n_kv, const uint16_t* __restrict__ qw, const uint16_t* __restrict__ kw,
                                                           const float2* __restrict__ rope, int n_rot, const int* __restrict__ row_pos, const int* __restrict__ row_slot,
                                                           uint16_t* __restrict__ kc, uint16_t* __restrict__ vc, size_t kv_stride, int max_ctx, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float sh[8]; __shared__ float buf[HD];
     const int t = threadIdx.x, hb = blockIdx.x % (n_head + n_kv), r = blockIdx.x / (n_head + n_kv);
     const int pos = row_pos[r], slot = row_slot[r];
@@ -70,6 +72,8 @@ struct AttnArgs {
 };
 // grid (nsplit_max, n_kv, ngroups), 256 threads, dynamic smem
 __global__ void __launch_bounds__(256) k_attn_split(AttnArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ __align__(16) uint8_t sm_raw[];
     float* sQ = reinterpret_cast<float*>(sm_raw);                                   // [MAXP][256]
     float* sE = sQ + MAXP * HD;                                                     // [SPL][MAXP] scores, then weights
@@ -166,6 +170,8 @@ __global__ void __launch_bounds__(256) k_attn_split(AttnArgs a) {
 __global__ void __launch_bounds__(256) k_attn_merge(const float* __restrict__ qkv, int ld, int n_head, int n_kv, const int* __restrict__ groups, const int* __restrict__ row_group,
                                                      const float* __restrict__ pO, const float* __restrict__ pm, const float* __restrict__ pl, int nsplit_max,
                                                      float* __restrict__ out, int8_t* __restrict__ oq, float* __restrict__ osc) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x / n_head, head = blockIdx.x % n_head, d = threadIdx.x;
     const int gi = row_group[r];
     const int r0 = groups[gi * 4], pos0 = groups[gi * 4 + 3];
@@ -195,8 +201,8 @@ size_t attn_partial_floats(int ngroups, int n_kv, int nsplit_max) { return (size
 
 int attn_rope_kv(const AttnParams& p, int rows, cudaStream_t s) {
     HP_REQUIRE(rows >= 1 && p.n_head % p.n_kv == 0 && p.n_rot % 2 == 0 && p.n_rot <= HD, "attn_rope_kv: bad shape");
-    k_qk_norm_rope_kv<<<rows * (p.n_head + p.n_kv), 256, 0, s>>>(p.qkv, p.ld, p.n_head, p.n_kv, (const uint16_t*)p.q_norm, (const uint16_t*)p.k_norm, (const float2*)p.rope, p.n_rot,
-                                                                 p.row_pos, p.row_slot, (uint16_t*)p.kc, (uint16_t*)p.vc, p.kv_stride, p.max_ctx, p.eps);
+    HP_CUDA(launch_pdl<4>(k_qk_norm_rope_kv, dim3(rows * (p.n_head + p.n_kv)), dim3(256), 0, s, p.qkv, p.ld, p.n_head, p.n_kv, (const uint16_t*)p.q_norm, (const uint16_t*)p.k_norm, (const float2*)p.rope, p.n_rot,
+                       p.row_pos, p.row_slot, (uint16_t*)p.kc, (uint16_t*)p.vc, p.kv_stride, p.max_ctx, p.eps));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 int attn_decode(const AttnParams& p, int rows, int ngroups, cudaStream_t s) {
@@ -205,8 +211,8 @@ int attn_decode(const AttnParams& p, int rows, int ngroups, cudaStream_t s) {
     if (!attr) { HP_CUDA(cudaFuncSetAttribute(k_attn_split, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem_bytes())); attr = true; }
     AttnArgs a; a.qkv = p.qkv; a.ld = p.ld; a.n_head = p.n_head; a.n_kv = p.n_kv; a.kc = (const uint16_t*)p.kc; a.vc = (const uint16_t*)p.vc;
     a.kv_stride = p.kv_stride; a.max_ctx = p.max_ctx; a.groups = p.groups; a.pO = p.pO; a.pm = p.pm; a.pl = p.pl; a.nsplit_max = p.nsplit_max;
-    k_attn_split<<<dim3(p.nsplit_max, p.n_kv, ngroups), 256, attn_smem_bytes(), s>>>(a);
-    k_attn_merge<<<rows * p.n_head, 256, 0, s>>>(p.qkv, p.ld, p.n_head, p.n_kv, p.groups, p.row_group, p.pO, p.pm, p.pl, p.nsplit_max, p.out, (int8_t*)p.xq.q, (float*)p.xq.sc);
+    HP_CUDA(launch_pdl<4>(k_attn_split, dim3(p.nsplit_max, p.n_kv, ngroups), dim3(256), attn_smem_bytes(), s, a));
+    HP_CUDA(launch_pdl<4>(k_attn_merge, dim3(rows * p.n_head), dim3(256), 0, s, p.qkv, p.ld, p.n_head, p.n_kv, p.groups, p.row_group, p.pO, p.pm, p.pl, p.nsplit_max, p.out, (int8_t*)p.xq.q, (float*)p.xq.sc));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 

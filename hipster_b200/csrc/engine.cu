@@ -53,6 +53,8 @@ __global__ void k_gen_f32(float* __restrict__ p, size_t n, uint64_t seed, uint64
 }
 __global__ void k_set_ints(int* p, int n, int v) { const int i = blockIdx.x * blockDim.x + threadIdx.x; if (i < n) p[i] = v; }
 __global__ void k_reduce_planes(const float* __restrict__ parts, size_t part_stride, int P, float* __restrict__ y, int N, int ldy) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int n = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y; if (n >= N) return;
     float v = parts[(size_t)r * N + n];
     for (int p = 1; p < P; ++p) v = v + parts[(size_t)p * part_stride + (size_t)r * N + n];
@@ -64,17 +66,23 @@ enum { SP_ID_LAST = 0, SP_POS = 1, SP_MM = 2, SP_COUNT = 3, SP_POS_OLD = 4, SP_D
 enum { D_TOK = 0, D_POS = 32, D_SLOT = 64, D_RGROUP = 96, D_GROUPS = 128, D_SEQS = 160, D_INTS = 256 };
 // draft step i: one row (token = last emitted token or the previous draft) at position pos + i (spec27b.cpp:81-85)
 __global__ void k_spec_draft_setup(const int* __restrict__ sp, int* __restrict__ d, int i, int slot) {
+    pdl_launch_dependents();
+    pdl_wait();
     if (threadIdx.x) return;
     d[D_TOK] = i == 0 ? sp[SP_ID_LAST] : sp[SP_DRAFTS + i - 1]; d[D_POS] = sp[SP_POS] + i; d[D_SLOT] = slot; d[D_RGROUP] = 0;
     d[D_GROUPS] = 0; d[D_GROUPS + 1] = 1; d[D_GROUPS + 2] = slot; d[D_GROUPS + 3] = sp[SP_POS] + i;
 }
 // the draft is the MTP argmax unless the caller substitutes it (seeded acceptance control)
 __global__ void k_spec_take(int* __restrict__ sp, const int* __restrict__ mids, int i) {
+    pdl_launch_dependents();
+    pdl_wait();
     if (threadIdx.x) return;
     const int sub = sp[SP_SUBST + i]; sp[SP_DRAFTS + i] = sub >= 0 ? sub : mids[0];
 }
 // verify rows [id_last, d1..dn] at positions pos.. (spec27b.cpp:88-90)
 __global__ void k_spec_verify_setup(const int* __restrict__ sp, int* __restrict__ d, int n, int slot) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = threadIdx.x;
     if (t <= n) { d[D_TOK + t] = t == 0 ? sp[SP_ID_LAST] : sp[SP_DRAFTS + t - 1]; d[D_POS + t] = sp[SP_POS] + t; d[D_SLOT + t] = slot; d[D_RGROUP + t] = 0; }
     if (t == 0) { d[D_GROUPS] = 0; d[D_GROUPS + 1] = n + 1; d[D_GROUPS + 2] = slot; d[D_GROUPS + 3] = sp[SP_POS];
@@ -83,6 +91,8 @@ __global__ void k_spec_verify_setup(const int* __restrict__ sp, int* __restrict_
 // greedy prefix acceptance (spec27b.cpp:92-102): mm accepted drafts, bonus = ids[mm], commit mm+1 rows, h_pending = h row mm
 __global__ void __launch_bounds__(256) k_spec_accept(int* __restrict__ sp, const int* __restrict__ ids, int* __restrict__ replay_n, int n, int slot,
                                                       const float* __restrict__ h, float* __restrict__ hpend, int E) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ int smm;
     if (threadIdx.x == 0) {
         int mm = 0; while (mm < n && ids[mm] == sp[SP_DRAFTS + mm]) ++mm;
@@ -100,6 +110,8 @@ __global__ void __launch_bounds__(256) k_spec_accept(int* __restrict__ sp, const
 // MTP catch-up rows: drafts at positions pos_old + 1 .. with the target's h rows (spec27b.cpp:99). All n rows run; rows
 // beyond the accepted prefix only write KV entries that the next round rewrites before reading them.
 __global__ void k_spec_catchup_setup(const int* __restrict__ sp, int* __restrict__ d, int n, int slot) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = threadIdx.x;
     if (t < n) { d[D_TOK + t] = sp[SP_DRAFTS + t]; d[D_POS + t] = sp[SP_POS_OLD] + 1 + t; d[D_SLOT + t] = slot; d[D_RGROUP + t] = 0; }
     if (t == 0) { d[D_GROUPS] = 0; d[D_GROUPS + 1] = n; d[D_GROUPS + 2] = slot; d[D_GROUPS + 3] = sp[SP_POS_OLD] + 1; }
@@ -321,7 +333,7 @@ int Engine::lin(const Lin& l, float* out, int ld, int R) {
     if (prof_skip_ & lin_class_bit(l, c_)) return HP_OK;
     if (l.P == 1) return gemv_q4k_q8_parts(l.wt ? l.wt : l.w, xq_, out, l.N, l.K, R, ld, 0, err_, s_, pdl_, l.wt != nullptr);
     HP_TRY(lin_parts(l, R));
-    k_reduce_planes<<<dim3((l.N + 255) / 256, R), 256, 0, s_>>>(yparts_, (size_t)R * l.N, l.P, out, l.N, ld);
+    HP_CUDA(launch_pdl<16>(k_reduce_planes, dim3((l.N + 255) / 256, R), dim3(256), 0, s_, yparts_, (size_t)R * l.N, l.P, out, l.N, ld));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 // residual add of the previous projection's planes + RMSNorm + quantise (qwen35.cpp:311-315)
@@ -642,14 +654,14 @@ int Engine::spec_begin(int slot, int id_last, int pos, const float* h_pending_de
 int Engine::enqueue_round(int slot, int n) {
     HP_CUDA(cudaMemcpyAsync(d_spec_ + SP_SUBST, h_spec_, 8 * 4, cudaMemcpyHostToDevice, s_));
     for (int i = 0; i < n; ++i) {   // draft, chained on the MTP's own h (spec27b.cpp:81-85)
-        k_spec_draft_setup<<<1, 32, 0, s_>>>(d_spec_, d_desc_, i, slot);
+        HP_CUDA(launch_pdl<2>(k_spec_draft_setup, dim3(1), dim3(32), 0, s_, d_spec_, d_desc_, i, slot));
         HP_TRY(run_mtp(1, 1, i == 0 ? hpend_ : mh_, c_.n_embd, true));
-        k_spec_take<<<1, 32, 0, s_>>>(d_spec_, d_mids_, i);
+        HP_CUDA(launch_pdl<2>(k_spec_take, dim3(1), dim3(32), 0, s_, d_spec_, d_mids_, i));
     }
-    k_spec_verify_setup<<<1, 32, 0, s_>>>(d_spec_, d_desc_, n, slot);
+    HP_CUDA(launch_pdl<2>(k_spec_verify_setup, dim3(1), dim3(32), 0, s_, d_spec_, d_desc_, n, slot));
     HP_TRY(run_pass(n + 1, 1, 1));
-    k_spec_accept<<<1, 256, 0, s_>>>(d_spec_, d_ids_, replay_n_, n, slot, h_, hpend_, c_.n_embd);
-    k_spec_catchup_setup<<<1, 32, 0, s_>>>(d_spec_, d_desc_, n, slot);
+    HP_CUDA(launch_pdl<2>(k_spec_accept, dim3(1), dim3(256), 0, s_, d_spec_, d_ids_, replay_n_, n, slot, h_, hpend_, c_.n_embd));
+    HP_CUDA(launch_pdl<2>(k_spec_catchup_setup, dim3(1), dim3(32), 0, s_, d_spec_, d_desc_, n, slot));
     HP_TRY(run_mtp(n, 1, h_, c_.n_embd, false));
     HP_CUDA(cudaMemcpyAsync(h_spec_ + SP_INTS, d_spec_, SP_INTS * 4, cudaMemcpyDeviceToHost, s_));
     HP_CUDA(cudaGetLastError());

@@ -2,6 +2,7 @@
 // Compiled with --fmad=false: every fused multiply-add in this code base is an explicit fmaf, so the rounding
 // sequence of each kernel is fixed by its source and can be restated operation by operation on a CPU.
 #pragma once
+#include <cstdlib>
 #include <cuda_runtime.h>
 #include <cuda_fp16.h>
 #include <stdint.h>
@@ -173,12 +174,13 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 
 // Launch with the programmatic-dependent-launch attribute: the kernel may start while its predecessor in the stream is
 // still running; it must execute pdl_wait() before touching anything the predecessor writes.
-template <typename... KArgs, typename... Args>
+inline int pdl_off_mask() { static const int m = [] { const char* e = getenv("HIPSTER_B200_PDL_OFF"); return e ? atoi(e) : 0; }(); return m; }
+template <int CLS = 0, typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
     cudaLaunchAttribute at[1]; at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = at; cfg.numAttrs = 1;
+    cfg.attrs = at; cfg.numAttrs = (pdl_off_mask() & (CLS ? CLS : 32)) ? 0 : 1;
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 

@@ -16,6 +16,8 @@ namespace {
 // ---- router: logits[t][e] = sum_k W[e][k] x[t][k], f32. One warp per weight row; lane l takes k = 4l + 128 i (float4),
 // four fmaf per step in element order, then the xor-shuffle tree (offsets 16..1). ----
 __global__ void __launch_bounds__(256) k_router_gemv(const float* __restrict__ W, const float* __restrict__ x, float* __restrict__ y, int N, int K) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int n = (blockIdx.x * 256 + threadIdx.x) >> 5, lane = threadIdx.x & 31, t = blockIdx.y;
     if (n >= N) return;
     const float* w = W + (size_t)n * K; const float* xr = x + (size_t)t * K;
@@ -34,6 +36,8 @@ __global__ void __launch_bounds__(256) k_router_gemv(const float* __restrict__ W
 // selected probabilities taken in rank order; slot k = shared expert (id -1) with weight sigmoid(logit[E]). ----
 __device__ __forceinline__ void better(float& bv, int& bi, float v, int i) { if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; } }
 __global__ void __launch_bounds__(1024) k_moe_route(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ w, int E, int k) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float sh[32]; __shared__ int shi[32]; __shared__ float selp[16]; __shared__ int seli[16];
     const int t = blockIdx.x, i = threadIdx.x, warp = i >> 5, lane = i & 31;
     const float v = i < E ? logits[(size_t)t * (E + 1) + i] : -INFINITY;
@@ -142,6 +146,8 @@ struct MoeArgs {
 __device__ __forceinline__ bool moe_owned(const MoeArgs& a, int id) { return id >= 0 ? (id >= a.e_lo && id < a.e_hi) : a.own_shared != 0; }
 // gate|up: y[(t,e)][N] = W[ids[t,e]] . x[t]; one warp per (pair, 16-row tile)
 __global__ void __launch_bounds__(256) k_moe_gemv(MoeArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float4 scr_all[8][128];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles = a.N / 16, unit = blockIdx.x * 8 + warp;
@@ -158,6 +164,8 @@ __global__ void __launch_bounds__(256) k_moe_gemv(MoeArgs a) {
 }
 // per-pair expert output of the down projection: v[(t,e)][N] = W_down[ids[t,e]] . act[(t,e)] (expert-parallel form)
 __global__ void __launch_bounds__(256) k_moe_down_pairs(MoeArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float4 scr_all[8][128];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles = a.N / 16, unit = blockIdx.x * 8 + warp;
@@ -177,6 +185,8 @@ __global__ void __launch_bounds__(256) k_moe_down_pairs(MoeArgs a) {
 }
 // down + combine: y[t][row] = sum_e slotw[t,e] * (W_down[ids[t,e]] . act[(t,e)]) in slot order (gemv.hip:1104-1112)
 __global__ void __launch_bounds__(256) k_moe_down(MoeArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float4 scr_all[8][128];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles = a.N / 16, unit = blockIdx.x * 8 + warp;
@@ -197,6 +207,8 @@ __global__ void __launch_bounds__(256) k_moe_down(MoeArgs a) {
 }
 // combine of exchanged per-pair outputs (expert-parallel): y[t][n] = sum_e slotw[t,e] * v[(t,e)][n], slot order
 __global__ void __launch_bounds__(256) k_moe_combine(const float* __restrict__ v, const float* __restrict__ slotw, int nslot, float* __restrict__ y, int N) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.y, n = blockIdx.x * 256 + threadIdx.x; if (n >= N) return;
     float acc = 0.f;
     for (int e = 0; e < nslot; ++e) acc = fmaf(slotw[t * nslot + e], v[(size_t)(t * nslot + e) * N + n], acc);
@@ -204,6 +216,8 @@ __global__ void __launch_bounds__(256) k_moe_combine(const float* __restrict__ v
 }
 // q8(silu(g) * u) per (t,e) row: gu [pairs][2F] (fn.hip:206-211); pairs of experts that live elsewhere are skipped
 __global__ void __launch_bounds__(256) k_moe_silu_quant(const float* __restrict__ gu, int F, const int* __restrict__ ids, int e_lo, int e_hi, int own_shared, int8_t* __restrict__ q, float* __restrict__ sc) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int pair = blockIdx.y, sb = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (sb * 32 >= F) return;
     const int id = ids[pair]; if (id >= 0 ? (id < e_lo || id >= e_hi) : !own_shared) return;
@@ -215,12 +229,12 @@ __global__ void __launch_bounds__(256) k_moe_silu_quant(const float* __restrict_
 
 int router_gemv(const float* W, const float* x, float* y, int N, int K, int T, cudaStream_t s) {
     HP_REQUIRE(N >= 1 && K > 0 && K % 128 == 0 && T >= 1, "router_gemv: bad shape N=%d K=%d T=%d", N, K, T);
-    k_router_gemv<<<dim3((N * 32 + 255) / 256, T), 256, 0, s>>>(W, x, y, N, K);
+    HP_CUDA(launch_pdl<8>(k_router_gemv, dim3((N * 32 + 255) / 256, T), dim3(256), 0, s, W, x, y, N, K));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 int moe_route(const float* logits, int* ids, float* w, int T, int E, int k, cudaStream_t s) {
     HP_REQUIRE(T >= 1 && E >= 1 && E <= 1024 && k >= 1 && k <= 15 && k <= E, "moe_route: bad shape E=%d k=%d", E, k);
-    k_moe_route<<<T, 1024, 0, s>>>(logits, ids, w, E, k);
+    HP_CUDA(launch_pdl<8>(k_moe_route, dim3(T), dim3(1024), 0, s, logits, ids, w, E, k));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 static MoeArgs moe_args(const MoeParams& p) {
@@ -230,28 +244,28 @@ static MoeArgs moe_args(const MoeParams& p) {
 int moe_gemv_up(const MoeParams& p, cudaStream_t s) {
     HP_REQUIRE(p.N % 16 == 0 && p.K % 256 == 0 && p.T >= 1 && p.nslot >= 1, "moe_gemv_up: bad shape");
     const int units = p.T * p.nslot * (p.N / 16);
-    k_moe_gemv<<<(units + 7) / 8, 256, 0, s>>>(moe_args(p));
+    HP_CUDA(launch_pdl<8>(k_moe_gemv, dim3((units + 7) / 8), dim3(256), 0, s, moe_args(p)));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 int moe_silu_quant(const float* gu, int F, const int* ids, int e_lo, int e_hi, int own_shared, XQ8F xq, int pairs, cudaStream_t s) {
     HP_REQUIRE(F % 64 == 0 && pairs >= 1, "moe_silu_quant: bad shape");
-    k_moe_silu_quant<<<dim3((F / 32 + 7) / 8, pairs), 256, 0, s>>>(gu, F, ids, e_lo, e_hi, own_shared, (int8_t*)xq.q, (float*)xq.sc);
+    HP_CUDA(launch_pdl<8>(k_moe_silu_quant, dim3((F / 32 + 7) / 8, pairs), dim3(256), 0, s, gu, F, ids, e_lo, e_hi, own_shared, (int8_t*)xq.q, (float*)xq.sc));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 int moe_down_combine(const MoeParams& p, cudaStream_t s) {
     HP_REQUIRE(p.N % 16 == 0 && p.K % 256 == 0 && p.T >= 1 && p.nslot >= 1 && p.slotw, "moe_down_combine: bad shape");
     const int units = p.T * (p.N / 16);
-    k_moe_down<<<(units + 7) / 8, 256, 0, s>>>(moe_args(p));
+    HP_CUDA(launch_pdl<8>(k_moe_down, dim3((units + 7) / 8), dim3(256), 0, s, moe_args(p)));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 int moe_down_pairs(const MoeParams& p, cudaStream_t s) {
     HP_REQUIRE(p.N % 16 == 0 && p.K % 256 == 0 && p.T >= 1 && p.nslot >= 1, "moe_down_pairs: bad shape");
     const int units = p.T * p.nslot * (p.N / 16);
-    k_moe_down_pairs<<<(units + 7) / 8, 256, 0, s>>>(moe_args(p));
+    HP_CUDA(launch_pdl<8>(k_moe_down_pairs, dim3((units + 7) / 8), dim3(256), 0, s, moe_args(p)));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 int moe_combine(const float* v, const float* slotw, int nslot, float* y, int T, int N, cudaStream_t s) {
-    k_moe_combine<<<dim3((N + 255) / 256, T), 256, 0, s>>>(v, slotw, nslot, y, N);
+    HP_CUDA(launch_pdl<8>(k_moe_combine, dim3((N + 255) / 256, T), dim3(256), 0, s, v, slotw, nslot, y, N));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 

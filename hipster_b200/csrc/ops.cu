@@ -33,6 +33,8 @@ __device__ __forceinline__ float block_sum_det(float v, float* sh) {
 // ---- embedding gather: bf16 table [V][E] -> f32 rows (reference: k_embed_q4_K, ops.hip:154-171; this build's
 // configurations keep embeddings in bf16) ----
 __global__ void __launch_bounds__(256) k_embed_bf16(const int* __restrict__ tok, const uint16_t* __restrict__ table, float* __restrict__ out, int E, int V) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x; int id = tok[r]; if (id < 0 || id >= V) id = 0;
     const uint16_t* src = table + (size_t)id * E;
     for (int i = threadIdx.x; i < E; i += 256) out[(size_t)r * E + i] = bf2f(src[i]);
@@ -424,7 +426,7 @@ __global__ void __cluster_dims__(GDN_CL, 1, 1) __launch_bounds__(256) k_gdn(GdnA
 
 int embed_bf16(const int* tok, const void* table, float* out, int R, int E, int V, cudaStream_t s) {
     HP_REQUIRE(R >= 1 && E > 0 && V > 0, "embed_bf16: bad shape");
-    k_embed_bf16<<<R, 256, 0, s>>>(tok, (const uint16_t*)table, out, E, V);
+    HP_CUDA(launch_pdl<16>(k_embed_bf16, dim3(R), dim3(256), 0, s, tok, (const uint16_t*)table, out, E, V));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 int add_rmsnorm_quant(float* x, const float* y, int P, size_t part_stride, int ldy, const void* w_bf16, float* xn, XQ8F xq, int R, int n, float eps, cudaStream_t s) {
@@ -449,7 +451,7 @@ int norm2_concat_quant(const float* a, const void* wa, const float* b, int ldb, 
 }
 int silu_mul_quant(const float* gu, int ldg, int F, XQ8F xq, int R, cudaStream_t s) {
     HP_REQUIRE(R >= 1 && F > 0 && F % 64 == 0 && ldg >= 2 * F, "silu_mul_quant: bad shape F=%d ldg=%d", F, ldg);
-    launch_pdl(k_silu_mul_quant, dim3((F / 32 + 7) / 8, R), dim3(256), 0, s, gu, ldg, F, (int8_t*)xq.q, (float*)xq.sc);
+    launch_pdl<256>(k_silu_mul_quant, dim3((F / 32 + 7) / 8, R), dim3(256), 0, s, gu, ldg, F, (int8_t*)xq.q, (float*)xq.sc);
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 HP_TRACE_READER(hp_debug_trace_ops)
@@ -461,7 +463,7 @@ int gdn_forward(const GdnParams& p, int nseq, cudaStream_t s) {
     a.state = p.state; a.conv_state = p.conv_state; a.state_stride = p.state_stride; a.conv_stride = p.conv_stride;
     a.seq = p.seq; a.replay_n = p.replay_n; a.out = p.out; a.oq = (int8_t*)p.xq.q; a.osc = (float*)p.xq.sc;
     a.snap = p.snap; a.snap_row_stride = p.snap_row_stride; a.eps = p.eps; a.sigmoid_gate = p.sigmoid_gate;
-    HP_CUDA(launch_pdl(k_gdn, dim3(p.n_v * GDN_CL, nseq), dim3(256), 0, s, a));
+    HP_CUDA(launch_pdl<128>(k_gdn, dim3(p.n_v * GDN_CL, nseq), dim3(256), 0, s, a));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 
