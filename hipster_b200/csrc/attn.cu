@@ -64,6 +64,12 @@ __global__ void __launch_bounds__(256) k_qk_norm_rope_kv(float* __restrict__ qkv
     }
 }
 
+__device__ __forceinline__ float2 attn_fma2(float2 a, float2 b, float2 c) {   // a * b + c per lane
+    float2 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(reinterpret_cast<unsigned long long&>(r))
+        : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)), "l"(reinterpret_cast<unsigned long long&>(c)));
+    return r;
+}
 struct AttnArgs {
     const float* qkv; int ld, n_head, n_kv;
     const uint16_t* kc; const uint16_t* vc; size_t kv_stride; int max_ctx;
@@ -133,36 +139,52 @@ __global__ void __launch_bounds__(256) k_attn_split(AttnArgs a) {
             for (int jx = 0; jx < 6; ++jx) { const int p = pq * 6 + jx; if (p < MAXP) sE[(kq + 32 * i) * MAXP + p] = s[i][jx] * 0.0625f; }
     }
     __syncthreads();
-    // softmax pieces per pair (one thread each): row t of the group sees keys <= pos0 + t
-    if (tid < npairs) {
-        const int tr = tid / G;
-        const int nk = min(nkeys, pos0 + tr + 1 - k_lo);
-        float mx = -INFINITY;
-        for (int k = 0; k < nk; ++k) mx = fmaxf(mx, sE[k * MAXP + tid]);
-        float l = 0.f;
-        for (int k = 0; k < nkeys; ++k) {
-            const float e = k < nk ? expf_det(sE[k * MAXP + tid] - mx) : 0.f;
-            sE[k * MAXP + tid] = e; l = l + e;
+    // softmax pieces per pair: warp w takes pairs w, w+8, ...; lane l takes keys l, l+32, l+64, l+96. Row t of the group
+    // sees keys <= pos0 + t. Maximum: exact in any order. Sum: the lane's keys in ascending order, then the xor tree (16..1).
+    {
+        const int warp = tid >> 5, lane = tid & 31;
+        for (int p = warp; p < npairs; p += 8) {
+            const int tr = p / G;
+            const int nk = min(nkeys, pos0 + tr + 1 - k_lo);
+            float sc[4]; float mx = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { const int k = lane + 32 * i; sc[i] = k < nk ? sE[k * MAXP + p] : -INFINITY; mx = fmaxf(mx, sc[i]); }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+            float l = 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int k = lane + 32 * i;
+                const float e = k < nk ? expf_det(sc[i] - mx) : 0.f;
+                if (k < nkeys) sE[k * MAXP + p] = e;
+                l = i == 0 ? e : l + e;
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) l = l + __shfl_xor_sync(0xffffffffu, l, off);
+            if (lane == 0) { a.pm[pbase + p] = mx; a.pl[pbase + p] = l; }   // nk <= 0: mx = -inf, l = 0 (the merge skips it)
         }
-        a.pm[pbase + tid] = mx; a.pl[pbase + tid] = l;   // nk <= 0: mx = -inf, l = 0 (the merge skips it)
     }
     __syncthreads();
     // o[pair][d] = sum_k e[k][pair] * v[k][d], keys in position order; thread = dim d
     {
-        float o[MAXP];
+        float2 o[MAXP / 2];   // packed pairs of (row, head) accumulators: two fp32 fmaf per instruction, each rounded once
 #pragma unroll
-        for (int p = 0; p < MAXP; ++p) o[p] = 0.f;
+        for (int p = 0; p < MAXP / 2; ++p) o[p] = make_float2(0.f, 0.f);
         for (int k = 0; k < nkeys; ++k) {
             const float v = h2f(sV[k * KSTRIDE + tid]);
+            const float2 vv = make_float2(v, v);
 #pragma unroll
             for (int p4 = 0; p4 < MAXP / 4; ++p4) {
                 const float4 e = *reinterpret_cast<const float4*>(sE + k * MAXP + p4 * 4);
-                o[p4 * 4 + 0] = fmaf(e.x, v, o[p4 * 4 + 0]); o[p4 * 4 + 1] = fmaf(e.y, v, o[p4 * 4 + 1]);
-                o[p4 * 4 + 2] = fmaf(e.z, v, o[p4 * 4 + 2]); o[p4 * 4 + 3] = fmaf(e.w, v, o[p4 * 4 + 3]);
+                o[p4 * 2] = attn_fma2(make_float2(e.x, e.y), vv, o[p4 * 2]);
+                o[p4 * 2 + 1] = attn_fma2(make_float2(e.z, e.w), vv, o[p4 * 2 + 1]);
             }
         }
 #pragma unroll
-        for (int p = 0; p < MAXP; ++p) if (p < npairs) a.pO[(pbase + p) * HD + tid] = o[p];
+        for (int p = 0; p < MAXP / 2; ++p) {
+            if (2 * p < npairs) a.pO[(pbase + 2 * p) * HD + tid] = o[p].x;
+            if (2 * p + 1 < npairs) a.pO[(pbase + 2 * p + 1) * HD + tid] = o[p].y;
+        }
     }
 }
 

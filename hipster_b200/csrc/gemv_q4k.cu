@@ -372,7 +372,7 @@ int launch_sk2(const uint8_t* W, const void* xq, const void* xsc, float* y, int 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(GEMV_NCTA); cfg.blockDim = dim3(SK_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = s;
     cudaLaunchAttribute at[1]; at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = at; cfg.numAttrs = pdl && !(pdl_off_mask() & 64) ? 1 : 0;
+    cfg.attrs = at; cfg.numAttrs = pdl && !(pdl_off_mask(s) & 64) ? 1 : 0;
     HP_CUDA(cudaLaunchKernelEx(&cfg, k_gemv_q4k_sk<NT, CB, TILED>, W, (const uint4*)xq, (const float4*)xsc, y, N, nb, P, R, ldy, part_stride, err));
     return HP_OK;
 }

@@ -215,8 +215,11 @@ extern "C" void orc_attn_row(float* qkv, int n_head, int n_kv, int n_rot, const 
                 float sc = 0.f; for (int d = 0; d < HD; ++d) sc = fmaf(q[d], orc_f16_to_f32(kr[d]), sc);
                 e[k] = sc * 0.0625f; mx = fmaxf(mx, e[k]);
             }
-            float l = 0.f;
-            for (int k = 0; k < nk; ++k) { e[k] = orc_expf(e[k] - mx); l = l + e[k]; }
+            // sum of the weights: 32 partial sums over keys l, l+32, l+64, l+96 (ascending), then an xor tree (offsets 16..1)
+            float part[32];
+            for (int k = 0; k < nk; ++k) e[k] = orc_expf(e[k] - mx);
+            for (int ln = 0; ln < 32; ++ln) { float a = ln < nk ? e[ln] : 0.f; for (int i = 1; i < 4; ++i) a = a + (ln + 32 * i < nk ? e[ln + 32 * i] : 0.f); part[ln] = a; }
+            const float l = det_block_sum(part, 32);
             for (int d = 0; d < HD; ++d) {
                 float o = 0.f;
                 for (int k = 0; k < nk; ++k) o = fmaf(e[k], orc_f16_to_f32(vc[((size_t)kh * max_ctx + k_lo + k) * HD + d]), o);
