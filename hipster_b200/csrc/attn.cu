@@ -34,7 +34,10 @@ __device__ __forceinline__ float block_sum_det(float v, float* sh) {
 }
 
 // grid: rows * (n_head + n_kv) blocks of 256 threads; row layout: [q_full: n_head x (256 q | 256 gate) | k: n_kv x 256 | v: n_kv x 256]
-__global__ void __launch_bounds__(256) k_qk_norm_rope_kv(float* __restrict__ qkv, int ld, int n_head, int n_kv, const uint16_t* __restrict__ qw, const uint16_t* __restrict__ kw,
+// planes != nullptr: the projection arrives as P K-part planes ([rows][ld] each, part_stride apart); they are added in
+// part order here (q, gate, k and v slices of this block) and q / gate are written to qkv for the attention kernels.
+__global__ void __launch_bounds__(256) k_qk_norm_rope_kv(float* __restrict__ qkv, const float* __restrict__ planes, int P, size_t part_stride,
+                                                          int ld, int n_head, int n_kv, const uint16_t* __restrict__ qw, const uint16_t* __restrict__ kw,
                                                           const float2* __restrict__ rope, int n_rot, const int* __restrict__ row_pos, const int* __restrict__ row_slot,
                                                           uint16_t* __restrict__ kc, uint16_t* __restrict__ vc, size_t kv_stride, int max_ctx, float eps) {
     pdl_launch_dependents();
@@ -43,8 +46,16 @@ __global__ void __launch_bounds__(256) k_qk_norm_rope_kv(float* __restrict__ qkv
     const int t = threadIdx.x, hb = blockIdx.x % (n_head + n_kv), r = blockIdx.x / (n_head + n_kv);
     const int pos = row_pos[r], slot = row_slot[r];
     const bool isq = hb < n_head;
-    float* x = isq ? qkv + (size_t)r * ld + hb * 512 : qkv + (size_t)r * ld + n_head * 512 + (hb - n_head) * HD;
-    const float xv = x[t];
+    const size_t xoff = (isq ? (size_t)r * ld + hb * 512 : (size_t)r * ld + n_head * 512 + (hb - n_head) * HD) + t;
+    // second slice of this block: the gate of a q head, the v of a kv head
+    const size_t yoff = isq ? xoff + HD : (size_t)r * ld + n_head * 512 + n_kv * HD + (hb - n_head) * HD + t;
+    float* x = qkv + (xoff - t);
+    float xv, yv;
+    if (planes) {
+        xv = planes[xoff]; yv = planes[yoff];
+        for (int p = 1; p < P; ++p) { xv = xv + planes[(size_t)p * part_stride + xoff]; yv = yv + planes[(size_t)p * part_stride + yoff]; }
+        if (isq) qkv[yoff] = yv;
+    } else { xv = x[t]; yv = qkv[yoff]; }
     const float ss = block_sum_det<8>(xv * xv, sh);
     float n = (xv * (1.0f / sqrtf(ss / (float)HD + eps))) * bf2f((isq ? qw : kw)[t]);
     buf[t] = n;
@@ -58,7 +69,7 @@ __global__ void __launch_bounds__(256) k_qk_norm_rope_kv(float* __restrict__ qkv
     x[t] = n;
     if (!isq) {
         const int kh = hb - n_head;
-        const float vv = qkv[(size_t)r * ld + n_head * 512 + n_kv * HD + kh * HD + t];
+        const float vv = yv;
         const size_t o = (size_t)slot * kv_stride + ((size_t)kh * max_ctx + pos) * HD + t;
         kc[o] = f2h(n); vc[o] = f2h(vv);
     }
@@ -223,7 +234,7 @@ size_t attn_partial_floats(int ngroups, int n_kv, int nsplit_max) { return (size
 
 int attn_rope_kv(const AttnParams& p, int rows, cudaStream_t s) {
     HP_REQUIRE(rows >= 1 && p.n_head % p.n_kv == 0 && p.n_rot % 2 == 0 && p.n_rot <= HD, "attn_rope_kv: bad shape");
-    HP_CUDA(launch_pdl<4>(k_qk_norm_rope_kv, dim3(rows * (p.n_head + p.n_kv)), dim3(256), 0, s, p.qkv, p.ld, p.n_head, p.n_kv, (const uint16_t*)p.q_norm, (const uint16_t*)p.k_norm, (const float2*)p.rope, p.n_rot,
+    HP_CUDA(launch_pdl<4>(k_qk_norm_rope_kv, dim3(rows * (p.n_head + p.n_kv)), dim3(256), 0, s, p.qkv, p.planes, p.P, p.part_stride, p.ld, p.n_head, p.n_kv, (const uint16_t*)p.q_norm, (const uint16_t*)p.k_norm, (const float2*)p.rope, p.n_rot,
                        p.row_pos, p.row_slot, (uint16_t*)p.kc, (uint16_t*)p.vc, p.kv_stride, p.max_ctx, p.eps));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }

@@ -344,8 +344,11 @@ int Engine::norm_in(const Lin* prev, bool have_y, const uint16_t* w, float* xn, 
 // qwen35.cpp:247-276
 int Engine::attn_block(const LayerW& L, uint16_t* kc, uint16_t* vc, size_t kv_stride, int R, int ngroups) {
     const int ld = L.in_proj.N;
-    HP_TRY(lin(L.in_proj, big_, ld, R));
-    AttnParams p; p.qkv = big_; p.ld = ld; p.n_head = c_.n_head; p.n_kv = c_.n_head_kv; p.n_rot = c_.n_rot;
+    AttnParams p; p.qkv = big_;
+    if (L.in_proj.P > 1 && !(prof_skip_ & 4) && !gemv_only_) {   // the rope kernel adds the K-part planes itself
+        HP_TRY(lin_parts(L.in_proj, R));
+        p.planes = yparts_; p.P = L.in_proj.P; p.part_stride = (size_t)R * ld;
+    } else HP_TRY(lin(L.in_proj, big_, ld, R)); p.ld = ld; p.n_head = c_.n_head; p.n_kv = c_.n_head_kv; p.n_rot = c_.n_rot;
     p.q_norm = L.q_norm; p.k_norm = L.k_norm; p.rope = rope_; p.row_pos = d_desc_ + D_POS; p.row_slot = d_desc_ + D_SLOT; p.row_group = d_desc_ + D_RGROUP; p.groups = d_desc_ + D_GROUPS;
     p.kc = kc; p.vc = vc; p.kv_stride = kv_stride; p.max_ctx = c_.max_ctx; p.pO = pO_; p.pm = pm_; p.pl = pl_; p.nsplit_max = nsplit_max_;
     p.out = nullptr; p.xq = xq_; p.eps = c_.rms_eps;
@@ -493,8 +496,8 @@ int Engine::run_mtp(int R, int ngroups, const float* h_dev, int ldh, bool want_l
     const hp_model_cfg& c = c_;
     HP_TRY(embed_bf16(d_desc_ + D_TOK, embed_, emb_, R, c.n_embd, c.n_vocab, s_));
     HP_TRY(norm2_concat_quant(emb_, mtp_enorm_, h_dev, ldh, mtp_hnorm_, nullptr, xq_, R, c.n_embd, c.rms_eps, s_));
-    HP_TRY(lin(eh_proj_, x_, c.n_embd, R));
-    HP_TRY(norm_in(nullptr, false, mtp_.attn_norm, nullptr, R));
+    HP_TRY(lin_parts(eh_proj_, R));   // x = eh_proj(...) : the norm kernel adds the K-part planes itself
+    HP_TRY(add_rmsnorm_quant(x_, yparts_, eh_proj_.P, (size_t)R * eh_proj_.N, eh_proj_.N, mtp_.attn_norm, nullptr, xq_, R, c.n_embd, c.rms_eps, s_, true));
     HP_TRY(attn_block(mtp_, mkc_, mvc_, kv_layer_, R, ngroups));
     HP_TRY(norm_in(&mtp_.out_proj, true, mtp_.post_norm, c.n_expert ? xn_ : nullptr, R));
     HP_TRY(ffn_block(mtp_, R));

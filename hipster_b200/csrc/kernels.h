@@ -67,7 +67,7 @@ int dequant_q4k(const void* W, size_t nblk, float* out, cudaStream_t s);
 // ---- ops.cu ----
 int embed_bf16(const int* tok, const void* table_bf16, float* out, int R, int E, int V, cudaStream_t s);
 // x += sum_p y_p (nullable y); xn = rmsnorm(x) * w; xq = q8(xn)   (reference add_rmsnorm_quant, ops.h:14)
-int add_rmsnorm_quant(float* x, const float* y, int P, size_t part_stride, int ldy, const void* w_bf16, float* xn, XQ8F xq, int R, int n, float eps, cudaStream_t s);
+int add_rmsnorm_quant(float* x, const float* y, int P, size_t part_stride, int ldy, const void* w_bf16, float* xn, XQ8F xq, int R, int n, float eps, cudaStream_t s, bool assign = false);   // assign: x = sum_p y_p instead of x += ...
 // out[r] = [rmsnorm(a[r]) * wa | rmsnorm(b[r]) * wb] quantised   (reference norm2_concat_quant, ops.h:16)
 int norm2_concat_quant(const float* a, const void* wa, const float* b, int ldb, const void* wb, float* out, XQ8F xq, int R, int n, float eps, cudaStream_t s);
 // xq = q8(silu(gu[:, :F]) * gu[:, F:2F])   (reference silu_mul_quant, ops.h:25)
@@ -87,6 +87,7 @@ int gdn_forward(const GdnParams& p, int nseq, cudaStream_t s);
 constexpr int ATTN_SPLIT = 128, ATTN_MAX_PAIRS = 48;   // keys per split; (row, q-head) pairs per kv head and row group
 struct AttnParams {
     float* qkv; int ld, n_head, n_kv, n_rot;            // rows [q_full n_head x 512 | k n_kv x 256 | v n_kv x 256]
+    const float* planes = nullptr; int P = 0; size_t part_stride = 0;   // optional: the projection as K-part planes, summed by the rope kernel into qkv
     const void* q_norm; const void* k_norm; const void* rope;   // bf16 [256] x 2; float2 (cos, sin) [max_ctx][n_rot/2]
     const int* row_pos; const int* row_slot; const int* row_group; const int* groups;   // device descriptors; group = {r0, T, slot, pos0}
     void* kc; void* vc; size_t kv_stride; int max_ctx;   // f16 [slot][n_kv][max_ctx][256] for this layer

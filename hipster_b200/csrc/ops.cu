@@ -61,7 +61,7 @@ __device__ __forceinline__ float norm_total(const float* tab) {
 }
 // 4 consecutive activations of row r starting at element i0 (a multiple of 4), owned by one lane; the 8 lanes of a
 // sub-block are consecutive. Same arithmetic as warp_quant32_store.
-__device__ __forceinline__ void quant4_store(const float (&o)[4], int r, int i0, int K, int8_t* __restrict__ q, float* __restrict__ sc, int lane) {
+__device__ __forceinline__ void quant4_store(const float (&o)[4], int r, int i0, int K, int8_t* __restrict__ q, float* __restrict__ sc, int lane, bool live = true) {
     float amax = fmaxf(fmaxf(fabsf(o[0]), fabsf(o[1])), fmaxf(fabsf(o[2]), fabsf(o[3])));
 #pragma unroll
     for (int off = 1; off < 8; off <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
@@ -70,6 +70,7 @@ __device__ __forceinline__ void quant4_store(const float (&o)[4], int r, int i0,
     int sum = (q0 + q1) + (q2 + q3);
 #pragma unroll
     for (int off = 1; off < 8; off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    if (!live) return;   // every lane of the warp took part in the shuffles above
     *reinterpret_cast<uint32_t*>(q + xq_q_index(r, i0, K)) = (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) | ((uint32_t)(q3 & 0xFF) << 24);
     if ((lane & 7) == 0) { const size_t di = xq_d_index(r, i0 >> 5, K); sc[di] = dd; sc[di + 2] = dd * (float)sum; }
 }
@@ -82,7 +83,7 @@ __device__ __forceinline__ void bf4(const uint16_t* w, float (&o)[4]) {
 template <int PT, int NG>   // PT > 0: the number of planes, known at compile time so that every load is in flight at once; 0: run-time P. NG: groups per thread
 __global__ void __cluster_dims__(NORM_CL, 1, 1) __launch_bounds__(NORM_TPB) k_add_rmsnorm_quant(float* __restrict__ x, const float* __restrict__ y, int P, size_t part_stride, int ldy,
                                                                      const uint16_t* __restrict__ w, float* __restrict__ xn, int8_t* __restrict__ q, float* __restrict__ sc,
-                                                                     int n, float eps) {
+                                                                     int n, float eps, int assign) {
     __shared__ float tab[NORM_NW];
     HP_TRACE_BEGIN();
     pdl_launch_dependents();
@@ -96,7 +97,7 @@ __global__ void __cluster_dims__(NORM_CL, 1, 1) __launch_bounds__(NORM_TPB) k_ad
     HP_TRACE_WAITED();
     float4 v[NG];
 #pragma unroll
-    for (int k = 0; k < NG; ++k) { const int i = 4 * (t + k * NORM_ROWT); v[k] = i < n ? *reinterpret_cast<const float4*>(xr + i) : make_float4(0.f, 0.f, 0.f, 0.f); }
+    for (int k = 0; k < NG; ++k) { const int i = 4 * (t + k * NORM_ROWT); v[k] = (i < n && !assign) ? *reinterpret_cast<const float4*>(xr + i) : make_float4(0.f, 0.f, 0.f, 0.f); }
     if (y) {
         float4 s[NG];
 #pragma unroll
@@ -122,7 +123,11 @@ __global__ void __cluster_dims__(NORM_CL, 1, 1) __launch_bounds__(NORM_TPB) k_ad
 #pragma unroll
         for (int k = 0; k < NG; ++k) {
             const int i = 4 * (t + k * NORM_ROWT);
-            if (i < n) { v[k].x = v[k].x + s[k].x; v[k].y = v[k].y + s[k].y; v[k].z = v[k].z + s[k].z; v[k].w = v[k].w + s[k].w; *reinterpret_cast<float4*>(xr + i) = v[k]; }
+            if (i < n) {
+                if (assign) v[k] = s[k];   // x = y exactly (no 0 + y: it would turn -0 into +0)
+                else { v[k].x = v[k].x + s[k].x; v[k].y = v[k].y + s[k].y; v[k].z = v[k].z + s[k].z; v[k].w = v[k].w + s[k].w; }
+                *reinterpret_cast<float4*>(xr + i) = v[k];
+            }
         }
     }
     float ss = 0.f;
@@ -136,11 +141,10 @@ __global__ void __cluster_dims__(NORM_CL, 1, 1) __launch_bounds__(NORM_TPB) k_ad
 #pragma unroll
     for (int k = 0; k < NG; ++k) {
         const int i = 4 * (t + k * NORM_ROWT);
-        if (i < n) {   // n is a multiple of 32: the 8 lanes of a sub-block are wholly inside or wholly outside
-            const float o[4] = {(v[k].x * scl) * wv[k][0], (v[k].y * scl) * wv[k][1], (v[k].z * scl) * wv[k][2], (v[k].w * scl) * wv[k][3]};
-            if (xn) *reinterpret_cast<float4*>(xn + (size_t)r * n + i) = make_float4(o[0], o[1], o[2], o[3]);
-            quant4_store(o, r, i, n, q, sc, lane);
-        }
+        const bool live = i < n;   // n is a multiple of 32: the 8 lanes of a sub-block are live together; dead lanes still shuffle
+        const float o[4] = {live ? (v[k].x * scl) * wv[k][0] : 0.f, live ? (v[k].y * scl) * wv[k][1] : 0.f, live ? (v[k].z * scl) * wv[k][2] : 0.f, live ? (v[k].w * scl) * wv[k][3] : 0.f};
+        if (live && xn) *reinterpret_cast<float4*>(xn + (size_t)r * n + i) = make_float4(o[0], o[1], o[2], o[3]);
+        quant4_store(o, r, i, n, q, sc, lane, live);
     }
     HP_TRACE_END(2);
 }
@@ -179,30 +183,31 @@ __global__ void __cluster_dims__(NORM_CL, 1, 1) __launch_bounds__(NORM_TPB) k_no
 #pragma unroll
     for (int k = 0; k < NG; ++k) {
         const int i = 4 * (t + k * NORM_ROWT);
-        if (i < n) {
-            const float oa[4] = {(va[k].x * ca) * wav[k][0], (va[k].y * ca) * wav[k][1], (va[k].z * ca) * wav[k][2], (va[k].w * ca) * wav[k][3]};
-            const float ob[4] = {(vb[k].x * cb) * wbv[k][0], (vb[k].y * cb) * wbv[k][1], (vb[k].z * cb) * wbv[k][2], (vb[k].w * cb) * wbv[k][3]};
-            if (out) {
-                *reinterpret_cast<float4*>(out + (size_t)r * 2 * n + i) = make_float4(oa[0], oa[1], oa[2], oa[3]);
-                *reinterpret_cast<float4*>(out + (size_t)r * 2 * n + n + i) = make_float4(ob[0], ob[1], ob[2], ob[3]);
-            }
-            quant4_store(oa, r, i, 2 * n, q, sc, lane);
-            quant4_store(ob, r, n + i, 2 * n, q, sc, lane);
+        const bool live = i < n;
+        const float oa[4] = {live ? (va[k].x * ca) * wav[k][0] : 0.f, live ? (va[k].y * ca) * wav[k][1] : 0.f, live ? (va[k].z * ca) * wav[k][2] : 0.f, live ? (va[k].w * ca) * wav[k][3] : 0.f};
+        const float ob[4] = {live ? (vb[k].x * cb) * wbv[k][0] : 0.f, live ? (vb[k].y * cb) * wbv[k][1] : 0.f, live ? (vb[k].z * cb) * wbv[k][2] : 0.f, live ? (vb[k].w * cb) * wbv[k][3] : 0.f};
+        if (live && out) {
+            *reinterpret_cast<float4*>(out + (size_t)r * 2 * n + i) = make_float4(oa[0], oa[1], oa[2], oa[3]);
+            *reinterpret_cast<float4*>(out + (size_t)r * 2 * n + n + i) = make_float4(ob[0], ob[1], ob[2], ob[3]);
         }
+        quant4_store(oa, r, i, 2 * n, q, sc, lane, live);
+        quant4_store(ob, r, n + i, 2 * n, q, sc, lane, live);
     }
 }
 
 // ---- xq = q8(silu(gate) * up); gate = columns [0, F), up = [F, 2F) of gu [R][ldg] (ops.hip:146-151) ----
+// one thread per 4 consecutive features (128-bit loads), 8 consecutive lanes per 32-element sub-block
 __global__ void __launch_bounds__(256) k_silu_mul_quant(const float* __restrict__ gu, int ldg, int F, int8_t* __restrict__ q, float* __restrict__ sc) {
     HP_TRACE_BEGIN();
     pdl_launch_dependents();
     pdl_wait();
     HP_TRACE_WAITED();
-    const int r = blockIdx.y, sb = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (sb * 32 >= F) return;
-    const int i = sb * 32 + lane;
-    const float g = gu[(size_t)r * ldg + i], u = gu[(size_t)r * ldg + F + i];
-    warp_quant32_store(silu_det(g) * u, r, sb, F, q, sc, lane);
+    const int r = blockIdx.y, i = (blockIdx.x * 256 + threadIdx.x) * 4, lane = threadIdx.x & 31;
+    const bool live = i < F;   // F is a multiple of 32: the 8 lanes of a sub-block are live together
+    const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 g = live ? *reinterpret_cast<const float4*>(gu + (size_t)r * ldg + i) : z4, u = live ? *reinterpret_cast<const float4*>(gu + (size_t)r * ldg + F + i) : z4;
+    const float o[4] = {silu_det(g.x) * u.x, silu_det(g.y) * u.y, silu_det(g.z) * u.z, silu_det(g.w) * u.w};
+    quant4_store(o, r, i, F, q, sc, lane, live);
     HP_TRACE_END(3);
 }
 
@@ -429,7 +434,8 @@ int embed_bf16(const int* tok, const void* table, float* out, int R, int E, int 
     HP_CUDA(launch_pdl<16>(k_embed_bf16, dim3(R), dim3(256), 0, s, tok, (const uint16_t*)table, out, E, V));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
-int add_rmsnorm_quant(float* x, const float* y, int P, size_t part_stride, int ldy, const void* w_bf16, float* xn, XQ8F xq, int R, int n, float eps, cudaStream_t s) {
+int add_rmsnorm_quant(float* x, const float* y, int P, size_t part_stride, int ldy, const void* w_bf16, float* xn, XQ8F xq, int R, int n, float eps, cudaStream_t s, bool assign) {
+    HP_REQUIRE(!assign || y, "add_rmsnorm_quant: assign needs planes");
     HP_REQUIRE(R >= 1 && n > 0 && n % 64 == 0, "add_rmsnorm_quant: n=%d must be a positive multiple of 64", n);
     HP_REQUIRE(n <= NORM_ROWT * 4 * NORM_MAXG, "add_rmsnorm_quant: n=%d exceeds %d", n, NORM_ROWT * 4 * NORM_MAXG);
     HP_REQUIRE(!y || (ldy % 4 == 0 && part_stride % 4 == 0), "add_rmsnorm_quant: plane strides must be multiples of 4 floats");
@@ -439,7 +445,7 @@ int add_rmsnorm_quant(float* x, const float* y, int P, size_t part_stride, int l
         return pt == 1 ? k_add_rmsnorm_quant<1, NG> : pt == 2 ? k_add_rmsnorm_quant<2, NG> : pt == 4 ? k_add_rmsnorm_quant<4, NG> : k_add_rmsnorm_quant<0, NG>;
     };
     auto kern = n <= NORM_ROWT * 4 ? pick(std::integral_constant<int, 1>()) : pick(std::integral_constant<int, NORM_MAXG>());
-    HP_CUDA(launch_pdl(kern, dim3(R * NORM_CL), dim3(NORM_TPB), 0, s, x, y, P, part_stride, ldy, (const uint16_t*)w_bf16, xn, (int8_t*)xq.q, (float*)xq.sc, n, eps));
+    HP_CUDA(launch_pdl(kern, dim3(R * NORM_CL), dim3(NORM_TPB), 0, s, x, y, P, part_stride, ldy, (const uint16_t*)w_bf16, xn, (int8_t*)xq.q, (float*)xq.sc, n, eps, assign ? 1 : 0));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 int norm2_concat_quant(const float* a, const void* wa, const float* b, int ldb, const void* wb, float* out, XQ8F xq, int R, int n, float eps, cudaStream_t s) {
@@ -451,7 +457,8 @@ int norm2_concat_quant(const float* a, const void* wa, const float* b, int ldb, 
 }
 int silu_mul_quant(const float* gu, int ldg, int F, XQ8F xq, int R, cudaStream_t s) {
     HP_REQUIRE(R >= 1 && F > 0 && F % 64 == 0 && ldg >= 2 * F, "silu_mul_quant: bad shape F=%d ldg=%d", F, ldg);
-    launch_pdl<256>(k_silu_mul_quant, dim3((F / 32 + 7) / 8, R), dim3(256), 0, s, gu, ldg, F, (int8_t*)xq.q, (float*)xq.sc);
+    HP_REQUIRE(ldg % 4 == 0, "silu_mul_quant: ldg must be a multiple of 4");
+    launch_pdl<256>(k_silu_mul_quant, dim3((F / 4 + 255) / 256, R), dim3(256), 0, s, gu, ldg, F, (int8_t*)xq.q, (float*)xq.sc);
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 HP_TRACE_READER(hp_debug_trace_ops)
