@@ -386,12 +386,14 @@ def run_moe_ep(args, rank, local_rank, world):
     torch.cuda.synchronize()
     sampler = ClockSampler(local_rank) if rank == 0 else None
     e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+    torch.cuda.profiler.start()
     t0 = time.perf_counter(); e0.record()
     toks = 0
     for _ in range(args.steps):
         toks += one_round()
     e1.record(); torch.cuda.synchronize()
     wall_ms = (time.perf_counter() - t0) * 1e3
+    torch.cuda.profiler.stop()
     clocks = sampler.stop() if sampler else None
     exact = all(out[s][:len(plain[s])] == plain[s][:len(out[s])] for s in range(S))
     if world > 1:

@@ -22,7 +22,7 @@ __global__ void __launch_bounds__(256) k_router_gemv(const float* __restrict__ W
     if (n >= N) return;
     const float* w = W + (size_t)n * K; const float* xr = x + (size_t)t * K;
     float acc = 0.f;
-#pragma unroll 4
+#pragma unroll 8
     for (int i = lane * 4; i < K; i += 128) {
         const float4 a = __ldg(reinterpret_cast<const float4*>(w + i)), b = *reinterpret_cast<const float4*>(xr + i);
         acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc); acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
@@ -56,23 +56,28 @@ __global__ void __launch_bounds__(1024) k_moe_route(const float* __restrict__ lo
     __syncthreads();
     float sum = sh[0]; for (int q = 1; q < 32; ++q) sum = sum + sh[q];
     __syncthreads();
-    float p = i < E ? e / sum : -2.f;
-    for (int r = 0; r < k; ++r) {
-        float bv = p; int bi = i;
+    // top-k by (value desc, index asc): the winner of every round is unique, so any reduction order finds it. The
+    // probabilities go to shared memory and warp 0 alone runs the k rounds (lane l owns indices l, l+32, ...): no
+    // block-wide barrier per round.
+    __shared__ float sp[1024];
+    sp[i] = i < E ? e / sum : -2.f;
+    __syncthreads();
+    if (warp == 0) {
+        float pv[32];
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) { const float ov = __shfl_xor_sync(0xffffffffu, bv, off); const int oi = __shfl_xor_sync(0xffffffffu, bi, off); better(bv, bi, ov, oi); }
-        if (lane == 0) { sh[warp] = bv; shi[warp] = bi; }
-        __syncthreads();
-        if (warp == 0) {
-            bv = sh[lane]; bi = shi[lane];
+        for (int q = 0; q < 32; ++q) pv[q] = sp[lane + 32 * q];
+        for (int r = 0; r < k; ++r) {
+            float bv = pv[0]; int bi = lane;
+#pragma unroll
+            for (int q = 1; q < 32; ++q) better(bv, bi, pv[q], lane + 32 * q);
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) { const float ov = __shfl_xor_sync(0xffffffffu, bv, off); const int oi = __shfl_xor_sync(0xffffffffu, bi, off); better(bv, bi, ov, oi); }
             if (lane == 0) { selp[r] = bv; seli[r] = bi; }
+#pragma unroll
+            for (int q = 0; q < 32; ++q) if (bi == lane + 32 * q) pv[q] = -1.f;
         }
-        __syncthreads();
-        if (i == seli[r]) p = -1.f;
-        __syncthreads();
     }
+    __syncthreads();
     if (i == 0) {
         float wsum = 0.f; for (int r = 0; r < k; ++r) wsum = wsum + selp[r];
         for (int r = 0; r < k; ++r) { ids[t * (k + 1) + r] = seli[r]; w[t * (k + 1) + r] = selp[r] / wsum; }
@@ -81,54 +86,79 @@ __global__ void __launch_bounds__(1024) k_moe_route(const float* __restrict__ lo
 }
 
 // ---- one 16-row tile of an expert matrix against one activation row: blocks in order, weights read straight from
-// global memory (each expert tile is touched once). Returns the column of interest in out[0..1] (rows g, g+8). ----
+// global memory (each expert tile is touched once), CH blocks per batch so that their loads share one round trip.
+// Returns the column of interest in r0 / r1 (rows g, g+8). Scales are decoded in registers per lane (rows g, g+8):
+// a 6-bit value v becomes the float 2^23 + v by a byte permute, and fmaf(d, 2^23 + v, -(d * 2^23)) is exactly d * v;
+// odd sub-blocks take the high nibbles unshifted (16 * q), their d carries the exact 1/16. ----
+struct MoeRowScales {
+    float d, cd, dq, cdq, nd, cnd; uint32_t sc[2], mn[2];
+    __device__ __forceinline__ void get(int k, float& s0, float& nm) const {
+        const float fs = __uint_as_float(__byte_perm(sc[k >> 2], 0x4B000000u, 0x7540u | (k & 3)));
+        const float fm = __uint_as_float(__byte_perm(mn[k >> 2], 0x4B000000u, 0x7540u | (k & 3)));
+        s0 = (k & 1) ? fmaf(dq, fs, cdq) : fmaf(d, fs, cd);
+        nm = fmaf(nd, fm, cnd);
+    }
+};
+__device__ __forceinline__ MoeRowScales moe_decode_scales(const uint4 hdr) {
+    MoeRowScales r;
+    r.d = h2f((uint16_t)(hdr.x & 0xFFFF)); r.nd = -h2f((uint16_t)(hdr.x >> 16));
+    r.dq = r.d * 0.0625f;
+    r.cd = -(r.d * 8388608.f); r.cdq = -(r.dq * 8388608.f); r.cnd = -(r.nd * 8388608.f);
+    r.sc[0] = hdr.y & 0x3F3F3F3Fu; r.mn[0] = hdr.z & 0x3F3F3F3Fu;
+    r.sc[1] = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
+    r.mn[1] = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
+    return r;
+}
+template <int CH>
 __device__ __forceinline__ void expert_tile(const uint8_t* __restrict__ W, int row_bytes, int nb, const uint4* __restrict__ xq, const float4* __restrict__ xsc,
-                                            int xtile, int xcol, float4* scr, int lane, float& r0, float& r1) {
-    const int g = lane >> 2, t = lane & 3, hf = lane & 1;
+                                            int xtile, int xcol, int lane, float& r0, float& r1) {
+    const int g = lane >> 2, t = lane & 3;
     float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
-    const uint8_t* hrow = W + (size_t)(lane >> 1) * row_bytes;
-    const uint8_t* w0p = W + (size_t)g * row_bytes + 16 + 8 * t;
-    const uint8_t* w1p = W + (size_t)(g + 8) * row_bytes + 16 + 8 * t;
-    for (int b = 0; b < nb; ++b) {
-        {
-            const uint4 hdr = __ldg(reinterpret_cast<const uint4*>(hrow + (size_t)b * 144));
-            const float d = h2f((uint16_t)(hdr.x & 0xFFFF)), nd = -h2f((uint16_t)(hdr.x >> 16));
-            const uint32_t scv = hf ? ((hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u)) : (hdr.y & 0x3F3F3F3Fu);
-            const uint32_t mnv = hf ? (((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u)) : (hdr.z & 0x3F3F3F3Fu);
+    const uint8_t* rowa = W + (size_t)g * row_bytes;
+    const uint8_t* rowb = W + (size_t)(g + 8) * row_bytes;
+    for (int b0 = 0; b0 < nb; b0 += CH) {
+        uint4 ha[CH], hb[CH]; uint2 wa[CH][4], wb[CH][4];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                float s0 = d * (float)((scv >> (8 * k)) & 0xFFu);
-                if (k & 1) s0 = s0 * 0.0625f;
-                const float nm = nd * (float)((mnv >> (8 * k)) & 0xFFu);
-                scr[(4 * hf + k) * 16 + (lane >> 1)] = make_float4(s0, s0, nm, nm);
+        for (int c = 0; c < CH; ++c) {
+            const int b = b0 + c < nb ? b0 + c : nb - 1;
+            ha[c] = __ldg(reinterpret_cast<const uint4*>(rowa + (size_t)b * 144)); hb[c] = __ldg(reinterpret_cast<const uint4*>(rowb + (size_t)b * 144));
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                wa[c][j] = __ldg(reinterpret_cast<const uint2*>(rowa + (size_t)b * 144 + 16 + 8 * t + 32 * j));
+                wb[c][j] = __ldg(reinterpret_cast<const uint2*>(rowb + (size_t)b * 144 + 16 + 8 * t + 32 * j));
             }
         }
-        __syncwarp();
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const uint2 w0 = __ldg(reinterpret_cast<const uint2*>(w0p + (size_t)b * 144 + 32 * j));
-            const uint2 w1 = __ldg(reinterpret_cast<const uint2*>(w1p + (size_t)b * 144 + 32 * j));
-            const uint32_t alo[4] = {w0.x & 0x0F0F0F0Fu, w1.x & 0x0F0F0F0Fu, w0.y & 0x0F0F0F0Fu, w1.y & 0x0F0F0F0Fu};
-            const uint32_t ahi[4] = {w0.x & 0xF0F0F0F0u, w1.x & 0xF0F0F0F0u, w0.y & 0xF0F0F0F0u, w1.y & 0xF0F0F0F0u};
-            const float4 sa0 = scr[(2 * j) * 16 + g], sb0 = scr[(2 * j) * 16 + g + 8], sa1 = scr[(2 * j + 1) * 16 + g], sb1 = scr[(2 * j + 1) * 16 + g + 8];
-            const uint4 xf = __ldg(xq + ((size_t)xtile * nb * 4 + b * 4 + j) * 32 + lane);
-            const float4 x0 = __ldg(xsc + ((size_t)xtile * nb * 8 + b * 8 + 2 * j) * 4 + t), x1 = __ldg(xsc + ((size_t)xtile * nb * 8 + b * 8 + 2 * j + 1) * 4 + t);
-            int c0[4], c1[4];
-            asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-                         : "=r"(c0[0]), "=r"(c0[1]), "=r"(c0[2]), "=r"(c0[3]) : "r"(alo[0]), "r"(alo[1]), "r"(alo[2]), "r"(alo[3]), "r"(xf.x), "r"(xf.y), "r"(0));
-            asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-                         : "=r"(c1[0]), "=r"(c1[1]), "=r"(c1[2]), "=r"(c1[3]) : "r"(ahi[0]), "r"(ahi[1]), "r"(ahi[2]), "r"(ahi[3]), "r"(xf.z), "r"(xf.w), "r"(0));
-            // columns 2t, 2t+1 of the activation tile; only column xcol is kept at the end
-            acc0.x = fmaf(sa0.x * x0.x, (float)c0[0], acc0.x); acc0.x = fmaf(sa0.z, x0.z, acc0.x);
-            acc0.y = fmaf(sa0.x * x0.y, (float)c0[1], acc0.y); acc0.y = fmaf(sa0.z, x0.w, acc0.y);
-            acc1.x = fmaf(sb0.x * x0.x, (float)c0[2], acc1.x); acc1.x = fmaf(sb0.z, x0.z, acc1.x);
-            acc1.y = fmaf(sb0.x * x0.y, (float)c0[3], acc1.y); acc1.y = fmaf(sb0.z, x0.w, acc1.y);
-            acc0.x = fmaf(sa1.x * x1.x, (float)c1[0], acc0.x); acc0.x = fmaf(sa1.z, x1.z, acc0.x);
-            acc0.y = fmaf(sa1.x * x1.y, (float)c1[1], acc0.y); acc0.y = fmaf(sa1.z, x1.w, acc0.y);
-            acc1.x = fmaf(sb1.x * x1.x, (float)c1[2], acc1.x); acc1.x = fmaf(sb1.z, x1.z, acc1.x);
-            acc1.y = fmaf(sb1.x * x1.y, (float)c1[3], acc1.y); acc1.y = fmaf(sb1.z, x1.w, acc1.y);
+        for (int c = 0; c < CH; ++c) {
+            const int b = b0 + c;
+            if (b < nb) {
+                const MoeRowScales ra = moe_decode_scales(ha[c]), rb = moe_decode_scales(hb[c]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint2 w0 = wa[c][j], w1 = wb[c][j];
+                    const uint32_t alo[4] = {w0.x & 0x0F0F0F0Fu, w1.x & 0x0F0F0F0Fu, w0.y & 0x0F0F0F0Fu, w1.y & 0x0F0F0F0Fu};
+                    const uint32_t ahi[4] = {w0.x & 0xF0F0F0F0u, w1.x & 0xF0F0F0F0u, w0.y & 0xF0F0F0F0u, w1.y & 0xF0F0F0F0u};
+                    float sa0, na0, sb0, nb0, sa1, na1, sb1, nb1;
+                    ra.get(2 * j, sa0, na0); rb.get(2 * j, sb0, nb0); ra.get(2 * j + 1, sa1, na1); rb.get(2 * j + 1, sb1, nb1);
+                    const uint4 xf = __ldg(xq + ((size_t)xtile * nb * 4 + b * 4 + j) * 32 + lane);
+                    const float4 x0 = __ldg(xsc + ((size_t)xtile * nb * 8 + b * 8 + 2 * j) * 4 + t), x1 = __ldg(xsc + ((size_t)xtile * nb * 8 + b * 8 + 2 * j + 1) * 4 + t);
+                    int c0[4], c1[4];
+                    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                                 : "=r"(c0[0]), "=r"(c0[1]), "=r"(c0[2]), "=r"(c0[3]) : "r"(alo[0]), "r"(alo[1]), "r"(alo[2]), "r"(alo[3]), "r"(xf.x), "r"(xf.y), "r"(0));
+                    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                                 : "=r"(c1[0]), "=r"(c1[1]), "=r"(c1[2]), "=r"(c1[3]) : "r"(ahi[0]), "r"(ahi[1]), "r"(ahi[2]), "r"(ahi[3]), "r"(xf.z), "r"(xf.w), "r"(0));
+                    // columns 2t, 2t+1 of the activation tile; only column xcol is kept at the end
+                    acc0.x = fmaf(sa0 * x0.x, (float)c0[0], acc0.x); acc0.x = fmaf(na0, x0.z, acc0.x);
+                    acc0.y = fmaf(sa0 * x0.y, (float)c0[1], acc0.y); acc0.y = fmaf(na0, x0.w, acc0.y);
+                    acc1.x = fmaf(sb0 * x0.x, (float)c0[2], acc1.x); acc1.x = fmaf(nb0, x0.z, acc1.x);
+                    acc1.y = fmaf(sb0 * x0.y, (float)c0[3], acc1.y); acc1.y = fmaf(nb0, x0.w, acc1.y);
+                    acc0.x = fmaf(sa1 * x1.x, (float)c1[0], acc0.x); acc0.x = fmaf(na1, x1.z, acc0.x);
+                    acc0.y = fmaf(sa1 * x1.y, (float)c1[1], acc0.y); acc0.y = fmaf(na1, x1.w, acc0.y);
+                    acc1.x = fmaf(sb1 * x1.x, (float)c1[2], acc1.x); acc1.x = fmaf(nb1, x1.z, acc1.x);
+                    acc1.y = fmaf(sb1 * x1.y, (float)c1[3], acc1.y); acc1.y = fmaf(nb1, x1.w, acc1.y);
+                }
+            }
         }
-        __syncwarp();
     }
     // hand column xcol to every lane of its row group: it lives in lane (g, xcol/2), component xcol & 1
     const float m0 = (xcol & 1) ? acc0.y : acc0.x, m1 = (xcol & 1) ? acc1.y : acc1.x;
@@ -148,7 +178,6 @@ __device__ __forceinline__ bool moe_owned(const MoeArgs& a, int id) { return id 
 __global__ void __launch_bounds__(256) k_moe_gemv(MoeArgs a) {
     pdl_launch_dependents();
     pdl_wait();
-    __shared__ float4 scr_all[8][128];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles = a.N / 16, unit = blockIdx.x * 8 + warp;
     if (unit >= a.T * a.nslot * tiles) return;
@@ -158,7 +187,7 @@ __global__ void __launch_bounds__(256) k_moe_gemv(MoeArgs a) {
     const int nb = a.K / 256, row_bytes = nb * 144;
     const uint8_t* W = (id >= 0 ? a.w_exp + (size_t)id * a.ebytes : a.w_sh) + (size_t)tile * 16 * row_bytes;
     float r0, r1;
-    expert_tile(W, row_bytes, nb, a.xq, a.xsc, t >> 3, t & 7, scr_all[warp], lane, r0, r1);
+    expert_tile<4>(W, row_bytes, nb, a.xq, a.xsc, t >> 3, t & 7, lane, r0, r1);
     const int g = lane >> 2;
     if ((lane & 3) == 0) { a.y[(size_t)pair * a.N + tile * 16 + g] = r0; a.y[(size_t)pair * a.N + tile * 16 + g + 8] = r1; }
 }
@@ -166,7 +195,6 @@ __global__ void __launch_bounds__(256) k_moe_gemv(MoeArgs a) {
 __global__ void __launch_bounds__(256) k_moe_down_pairs(MoeArgs a) {
     pdl_launch_dependents();
     pdl_wait();
-    __shared__ float4 scr_all[8][128];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles = a.N / 16, unit = blockIdx.x * 8 + warp;
     if (unit >= a.T * a.nslot * tiles) return;
@@ -180,14 +208,13 @@ __global__ void __launch_bounds__(256) k_moe_down_pairs(MoeArgs a) {
     const int nb = a.K / 256, row_bytes = nb * 144;
     const uint8_t* W = (id >= 0 ? a.w_exp + (size_t)id * a.ebytes : a.w_sh) + (size_t)tile * 16 * row_bytes;
     float r0, r1;
-    expert_tile(W, row_bytes, nb, a.xq, a.xsc, pair >> 3, pair & 7, scr_all[warp], lane, r0, r1);
+    expert_tile<2>(W, row_bytes, nb, a.xq, a.xsc, pair >> 3, pair & 7, lane, r0, r1);
     if ((lane & 3) == 0) { a.y[(size_t)pair * a.N + tile * 16 + g] = r0; a.y[(size_t)pair * a.N + tile * 16 + g + 8] = r1; }
 }
 // down + combine: y[t][row] = sum_e slotw[t,e] * (W_down[ids[t,e]] . act[(t,e)]) in slot order (gemv.hip:1104-1112)
 __global__ void __launch_bounds__(256) k_moe_down(MoeArgs a) {
     pdl_launch_dependents();
     pdl_wait();
-    __shared__ float4 scr_all[8][128];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles = a.N / 16, unit = blockIdx.x * 8 + warp;
     if (unit >= a.T * tiles) return;
@@ -198,7 +225,7 @@ __global__ void __launch_bounds__(256) k_moe_down(MoeArgs a) {
         const int pair = t * a.nslot + e, id = a.ids[pair];
         const uint8_t* W = (id >= 0 ? a.w_exp + (size_t)id * a.ebytes : a.w_sh) + (size_t)tile * 16 * row_bytes;
         float r0, r1;
-        expert_tile(W, row_bytes, nb, a.xq, a.xsc, pair >> 3, pair & 7, scr_all[warp], lane, r0, r1);
+        expert_tile<2>(W, row_bytes, nb, a.xq, a.xsc, pair >> 3, pair & 7, lane, r0, r1);
         const float w = a.slotw[pair];
         acc0 = fmaf(w, r0, acc0); acc1 = fmaf(w, r1, acc1);
     }
