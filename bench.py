@@ -101,13 +101,13 @@ def expected_tokens_per_round(n, p):
 
 
 # ------------------------------------------------------------------------------------------ CPU arm (oracle port)
-def cpu_round_sample(rounds, warm):
+def cpu_round_layers(rounds, warm, n_layer):
     """The CPU restatement of the reference engine on the host cores, on a BOUNDED sample of the dense27b workload:
-    a 27B-shaped model cut to 4 layers (3 GDN + 1 attention, full widths, full 248320 vocabulary, MTP block), short
-    context. One step = one MTP round (5 draft steps + 6-row verify + accept + catch-up)."""
+    a 27B-shaped model cut to n_layer layers (3 GDN + 1 attention per four, full widths, full 248320 vocabulary, MTP
+    block), short context. One step = one MTP round (5 draft steps + 6-row verify + accept + catch-up)."""
     import hipster_b200 as hb
     from oracle import orc
-    cfg = hb.ModelCfg.preset("qwen35-27b", n_layer=4, max_ctx=256)
+    cfg = hb.ModelCfg.preset("qwen35-27b", n_layer=n_layer, max_ctx=256)
     m = orc.Model(cfg)
     E = cfg.n_embd
     m.forward([(0, [11, 12, 13, 14], 0)]); m.accept(0, 4)
@@ -134,12 +134,21 @@ def cpu_round_sample(rounds, warm):
     for _ in range(rounds):
         one_round()
     dt = (time.perf_counter() - t0) / rounds
+    del m
     return dt, orc.lib().orc_num_threads()
 
 
+def cpu_round_sample(rounds, warm):
+    """Round time of the full 64-layer model on the host cores, extrapolated from two bounded samples: the same round on
+    the model cut to 4 and to 8 layers gives the time of four more layers; 64 layers = t4 + 15 * (t8 - t4)."""
+    t4, th = cpu_round_layers(rounds, warm, 4)
+    t8, _ = cpu_round_layers(rounds, warm, 8)
+    return t4 + 15.0 * (t8 - t4), th
+
+
 CPU_SAMPLE = ("CPU restatement of the reference engine (its HIP kernels cannot be built without ROCm), one MTP round n=5 on a 27B-shaped "
-              "model cut to 4 of 64 layers (3 GDN + 1 attention, full widths, full vocabulary, MTP block), context < 64; tokens/s = 2.941 expected "
-              "tokens per round / measured round time of THIS reduced model (the full trunk has 16x the layer work)")
+              "model (full widths, full vocabulary, MTP block, context < 64) cut to 4 and to 8 of its 64 layers; the 64-layer round time is "
+              "extrapolated as t4 + 15 * (t8 - t4); tokens/s = 2.941 expected tokens per round / that time")
 
 
 def run_reference(args, rank, world):
