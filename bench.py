@@ -251,7 +251,10 @@ def run_dense(args, rank, local_rank, world):
     verify_bytes = eng.pass_weight_bytes(False, True)
     mtp_bytes = eng.pass_weight_bytes(True, False)
     head_bytes = verify_bytes - eng.pass_weight_bytes(False, False)
-    round_bytes = verify_bytes + n * (mtp_bytes + head_bytes) + mtp_bytes
+    # the catch-up of the fused round only refreshes the MTP block's K/V rows: eh_proj and the attention input projection
+    q4k = lambda N, K: N * (K // 256) * 144
+    catchup_bytes = q4k(cfg.n_embd, 2 * cfg.n_embd) + q4k(cfg.n_head * 512 + 2 * cfg.n_head_kv * 256, cfg.n_embd)
+    round_bytes = verify_bytes + n * (mtp_bytes + head_bytes) + catchup_bytes
     if world > 1:
         t = torch.tensor([dev_ms, wall_ms], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX); dev_ms, wall_ms = float(t[0]), float(t[1])
         tt = torch.tensor([toks], device="cuda", dtype=torch.float64); dist.all_reduce(tt); toks = float(tt.item())

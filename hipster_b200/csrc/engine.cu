@@ -342,7 +342,7 @@ int Engine::norm_in(const Lin* prev, bool have_y, const uint16_t* w, float* xn, 
     return add_rmsnorm_quant(x_, have_y ? yparts_ : nullptr, have_y ? prev->P : 0, have_y ? (size_t)R * prev->N : 0, have_y ? prev->N : 0, w, xn, xq_, R, c_.n_embd, c_.rms_eps, s_);
 }
 // qwen35.cpp:247-276
-int Engine::attn_block(const LayerW& L, uint16_t* kc, uint16_t* vc, size_t kv_stride, int R, int ngroups) {
+int Engine::attn_block(const LayerW& L, uint16_t* kc, uint16_t* vc, size_t kv_stride, int R, int ngroups, bool kv_only) {
     const int ld = L.in_proj.N;
     AttnParams p; p.qkv = big_;
     if (L.in_proj.P > 1 && !(prof_skip_ & 4) && !gemv_only_) {   // the rope kernel adds the K-part planes itself
@@ -352,6 +352,7 @@ int Engine::attn_block(const LayerW& L, uint16_t* kc, uint16_t* vc, size_t kv_st
     p.q_norm = L.q_norm; p.k_norm = L.k_norm; p.rope = rope_; p.row_pos = d_desc_ + D_POS; p.row_slot = d_desc_ + D_SLOT; p.row_group = d_desc_ + D_RGROUP; p.groups = d_desc_ + D_GROUPS;
     p.kc = kc; p.vc = vc; p.kv_stride = kv_stride; p.max_ctx = c_.max_ctx; p.pO = pO_; p.pm = pm_; p.pl = pl_; p.nsplit_max = nsplit_max_;
     p.out = nullptr; p.xq = xq_; p.eps = c_.rms_eps;
+    if (kv_only) return attn_rope_kv(p, R, s_);   // only this layer's K/V rows are wanted
     if (!gemv_only_ && !(prof_skip_ & 4)) { HP_TRY(attn_rope_kv(p, R, s_)); HP_TRY(attn_decode(p, R, ngroups, s_)); }
     return lin_parts(L.out_proj, R);
 }
@@ -492,13 +493,16 @@ int Engine::accept(int slot, int m) {
 }
 
 // qwen35.cpp:405-424
-int Engine::run_mtp(int R, int ngroups, const float* h_dev, int ldh, bool want_logits) {
+// kv_only: stop once the block's K/V rows of these positions are in its cache (the catch-up of the fused round needs
+// nothing else: the next draft takes its hidden row from the trunk)
+int Engine::run_mtp(int R, int ngroups, const float* h_dev, int ldh, bool want_logits, bool kv_only) {
     const hp_model_cfg& c = c_;
     HP_TRY(embed_bf16(d_desc_ + D_TOK, embed_, emb_, R, c.n_embd, c.n_vocab, s_));
     HP_TRY(norm2_concat_quant(emb_, mtp_enorm_, h_dev, ldh, mtp_hnorm_, nullptr, xq_, R, c.n_embd, c.rms_eps, s_));
     HP_TRY(lin_parts(eh_proj_, R));   // x = eh_proj(...) : the norm kernel adds the K-part planes itself
     HP_TRY(add_rmsnorm_quant(x_, yparts_, eh_proj_.P, (size_t)R * eh_proj_.N, eh_proj_.N, mtp_.attn_norm, nullptr, xq_, R, c.n_embd, c.rms_eps, s_, true));
-    HP_TRY(attn_block(mtp_, mkc_, mvc_, kv_layer_, R, ngroups));
+    HP_TRY(attn_block(mtp_, mkc_, mvc_, kv_layer_, R, ngroups, kv_only));
+    if (kv_only) return HP_OK;
     HP_TRY(norm_in(&mtp_.out_proj, true, mtp_.post_norm, c.n_expert ? xn_ : nullptr, R));
     HP_TRY(ffn_block(mtp_, R));
     HP_TRY(norm_in(c.n_expert ? &moe_out_ : &mtp_.down, true, mtp_head_norm_, mh_, R));
@@ -665,7 +669,7 @@ int Engine::enqueue_round(int slot, int n) {
     HP_TRY(run_pass(n + 1, 1, 1));
     HP_CUDA(launch_pdl<2>(k_spec_accept, dim3(1), dim3(256), 0, s_, d_spec_, d_ids_, replay_n_, n, slot, h_, hpend_, c_.n_embd));
     HP_CUDA(launch_pdl<2>(k_spec_catchup_setup, dim3(1), dim3(32), 0, s_, d_spec_, d_desc_, n, slot));
-    HP_TRY(run_mtp(n, 1, h_, c_.n_embd, false));
+    HP_TRY(run_mtp(n, 1, h_, c_.n_embd, false, true));
     HP_CUDA(cudaMemcpyAsync(h_spec_ + SP_INTS, d_spec_, SP_INTS * 4, cudaMemcpyDeviceToHost, s_));
     HP_CUDA(cudaGetLastError());
     return HP_OK;

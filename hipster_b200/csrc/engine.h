@@ -64,13 +64,13 @@ private:
     int lin(const Lin& l, float* out, int ld, int R);        // GEMV; P > 1 planes are reduced into out
     int lin_parts(const Lin& l, int R);                      // GEMV into the plane buffer yparts_ (consumer adds the planes)
     int norm_in(const Lin* prev, bool have_y, const uint16_t* w, float* xn, int R);
-    int attn_block(const LayerW& L, uint16_t* kc, uint16_t* vc, size_t kv_stride, int R, int ngroups);
+    int attn_block(const LayerW& L, uint16_t* kc, uint16_t* vc, size_t kv_stride, int R, int ngroups, bool kv_only = false);
     int ffn_block(const LayerW& L, int R);
     int moe_block(const LayerW& L, int R);
     int ep_exchange(float* buf, size_t n);
     int ep_allreduce(float* buf, size_t n);
     int run_pass(int R, int nseq, int ngroups);              // trunk over the rows described by desc_ (already uploaded)
-    int run_mtp(int R, int ngroups, const float* h_dev, int ldh, bool want_logits);
+    int run_mtp(int R, int ngroups, const float* h_dev, int ldh, bool want_logits, bool kv_only = false);
     int upload_desc();
     int enqueue_round(int slot, int n);
     int nattn() const; int ngdn() const;
