@@ -154,6 +154,9 @@ CPU_SAMPLE = ("CPU restatement of the reference engine (its HIP kernels cannot b
 def run_reference(args, rank, world):
     if rank != 0:
         return None
+    # all the host threads this process may use (a launcher may have pinned OpenMP to one thread); set before the
+    # oracle library, and with it the OpenMP runtime, is loaded
+    os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
     k = max(1, min(args.steps, 5)); w = 1
     dt, th = cpu_round_sample(k, w)
     v = expected_tokens_per_round(N_DRAFT, ACCEPT_RATE) / dt
@@ -280,7 +283,7 @@ def run_dense(args, rank, local_rank, world):
                      "kernel": "k_gemv_q4k_sk: all GEMV launches of one 6-row verify pass (129 launches + LM head), timed alone with CUDA events",
                      "algorithmic_bytes": verify_bytes, "ms": gemv_ms, "full_pass_ms": pass_ms, "peak_source": pk["_src"],
                      "bytes_per_token_roofline": {"round_bytes": round_bytes, "tokens_per_round": tok_per_round, "bytes_per_token": bytes_per_token,
-                                                  "roofline_tokens_per_s": pk["hbm_gbs"] * 1e9 / bytes_per_token, "frac_of_roofline": value / (pk["hbm_gbs"] * 1e9 / bytes_per_token)}},
+                                                  "roofline_tokens_per_s": world * pk["hbm_gbs"] * 1e9 / bytes_per_token, "frac_of_roofline": value / (world * pk["hbm_gbs"] * 1e9 / bytes_per_token)}},
         "clocks": clocks,
         "checks": {"spec_stream_equals_plain_greedy": bool(exact), "tokens": int(toks), "accepted_drafts_per_round": tok_per_round - 1, "prompt_len": prompt_len, "setup_s": t_setup},
     }
