@@ -45,7 +45,10 @@ __global__ void __launch_bounds__(256) k_embed_bf16(const int* __restrict__ tok,
 // Sum of squares: per-thread fmaf chain over its elements in index order, xor tree inside each warp, then the 40 warp
 // sums (warp index over the cluster) added in order by every thread after the cluster barrier. Quantisation: a
 // 32-element sub-block is held by 8 consecutive lanes.
-constexpr int NORM_CL = 4, NORM_TPB = 320, NORM_ROWT = NORM_CL * NORM_TPB, NORM_NW = NORM_ROWT / 32, NORM_MAXG = 2;   // rows of up to 10240 elements
+#ifndef HP_NORM_CL
+#define HP_NORM_CL 4
+#endif
+constexpr int NORM_CL = HP_NORM_CL, NORM_TPB = 1280 / HP_NORM_CL, NORM_ROWT = NORM_CL * NORM_TPB, NORM_NW = NORM_ROWT / 32, NORM_MAXG = 2;   // rows of up to 10240 elements
 // warp part of the cluster-wide sum: leaves this warp's sum in slot (10 * rank + warp) of every CTA's table
 __device__ __forceinline__ void norm_publish(float v, float* tab, int rank) {
 #pragma unroll
