@@ -37,7 +37,7 @@ WORKLOADS = {
 
 GEMV_TRAFFIC_RATIO = 1.033   # DRAM bytes / algorithmic weight bytes of k_gemv_q4k_sk, from the ncu capture under profiles/
 # kernel launches of one round (counted from the ncu launch lists under profiles/)
-ROUND_LAUNCHES = {"dense27b": 653, "moe": 610}
+ROUND_LAUNCHES = {"dense27b": 653, "moe": 510}
 
 
 def peaks():

@@ -285,6 +285,7 @@ int Engine::init() {
         HP_TRY(alloc((void**)&xn_, (size_t)MAXR * E * 4));
         HP_TRY(alloc((void**)&rlogits_, (size_t)MAXR * (c.n_expert + 1) * 4));
         HP_TRY(alloc((void**)&moe_ids_, (size_t)pairs * 4)); HP_TRY(alloc((void**)&moe_w_, (size_t)pairs * 4));
+        HP_TRY(alloc((void**)&route_cnt_, (size_t)MAXR * 4)); HP_CUDA(cudaMemsetAsync(route_cnt_, 0, (size_t)MAXR * 4, s_));
         HP_TRY(alloc((void**)&moe_gu_, (size_t)pairs * 2 * F * 4)); HP_TRY(alloc((void**)&moe_v_, (size_t)pairs * E * 4));
         HP_TRY(alloc(&xq2_.q, xq_q_bytes(pairs, F))); HP_TRY(alloc(&xq2_.sc, xq_sc_floats(pairs, F) * 4));
         HP_CUDA(cudaMemsetAsync(xq2_.q, 0, xq_q_bytes(pairs, F), s_)); HP_CUDA(cudaMemsetAsync(xq2_.sc, 0, xq_sc_floats(pairs, F) * 4, s_));
@@ -339,6 +340,8 @@ int Engine::lin(const Lin& l, float* out, int ld, int R) {
 // residual add of the previous projection's planes + RMSNorm + quantise (qwen35.cpp:311-315)
 int Engine::norm_in(const Lin* prev, bool have_y, const uint16_t* w, float* xn, int R) {
     if (gemv_only_ || (prof_skip_ & 2)) return HP_OK;
+    if (have_y && prev == &moe_out_)   // the MoE combine runs inside the norm: weighted sum of the per-(row, slot) expert outputs
+        return add_rmsnorm_quant(x_, moe_v_, 0, 0, c_.n_embd, w, xn, xq_, R, c_.n_embd, c_.rms_eps, s_, false, moe_w_, c_.n_expert_used + 1);
     return add_rmsnorm_quant(x_, have_y ? yparts_ : nullptr, have_y ? prev->P : 0, have_y ? (size_t)R * prev->N : 0, have_y ? prev->N : 0, w, xn, xq_, R, c_.n_embd, c_.rms_eps, s_);
 }
 // qwen35.cpp:247-276
@@ -369,8 +372,7 @@ int Engine::ffn_block(const LayerW& L, int R) {
 int Engine::moe_block(const LayerW& L, int R) {
     const hp_model_cfg& c = c_; const int E = c.n_embd, F = c.expert_ff, ns = c.n_expert_used + 1;
     if (gemv_only_) return HP_OK;
-    HP_TRY(router_gemv(L.router, xn_, rlogits_, c.n_expert + 1, E, R, s_));
-    HP_TRY(moe_route(rlogits_, moe_ids_, moe_w_, R, c.n_expert, c.n_expert_used, s_));
+    HP_TRY(router_route(L.router, xn_, rlogits_, moe_ids_, moe_w_, route_cnt_, c.n_expert, E, c.n_expert_used, R, s_));
     MoeParams p; p.w_exp = L.exp_gate_up.w; p.w_sh = L.sh_gate_up.w; p.ebytes = (size_t)2 * F * (E / 256) * 144; p.N = 2 * F; p.K = E;
     p.ids = moe_ids_; p.slotw = nullptr; p.nslot = ns; p.xq = xq_; p.y = moe_gu_; p.T = R; p.e_lo = e_lo_; p.e_hi = e_hi_; p.own_shared = own_shared_;
     HP_TRY(moe_gemv_up(p, s_));
@@ -381,7 +383,7 @@ int Engine::moe_block(const LayerW& L, int R) {
     d.y = moe_v_;
     HP_TRY(moe_down_pairs(d, s_));
     if (ep_world_ > 1) HP_TRY(ep_exchange(moe_v_, (size_t)R * ns * E));
-    return moe_combine(moe_v_, moe_w_, ns, yparts_, R, E, s_);
+    return HP_OK;   // combined in slot order by the norm that follows (norm_in)
 }
 
 // qwen35.cpp:309-376

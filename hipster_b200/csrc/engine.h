@@ -88,7 +88,7 @@ private:
     float *x_ = nullptr, *xn_ = nullptr, *big_ = nullptr, *act_ = nullptr, *yparts_ = nullptr, *logits_ = nullptr, *mlogits_ = nullptr, *h_ = nullptr, *mh_ = nullptr, *cat_ = nullptr, *emb_ = nullptr;
     float *pO_ = nullptr, *pm_ = nullptr, *pl_ = nullptr; int nsplit_max_ = 0;
     XQ8F xq_{nullptr, nullptr}, xq2_{nullptr, nullptr};
-    float *rlogits_ = nullptr, *moe_w_ = nullptr, *moe_gu_ = nullptr, *moe_v_ = nullptr; int* moe_ids_ = nullptr; Lin moe_out_;
+    float *rlogits_ = nullptr, *moe_w_ = nullptr, *moe_gu_ = nullptr, *moe_v_ = nullptr; int* moe_ids_ = nullptr; int* route_cnt_ = nullptr; Lin moe_out_;
     int e_lo_ = 0, e_hi_ = 0, own_shared_ = 1, ep_world_ = 1, ep_rank_ = 0; void* nccl_comm_ = nullptr;
     int *d_desc_ = nullptr, *h_desc_ = nullptr;                  // device / pinned host descriptor
     int *d_ids_ = nullptr, *d_mids_ = nullptr; float *d_vals_ = nullptr, *d_mvals_ = nullptr; void* am_scratch_ = nullptr;

@@ -67,7 +67,8 @@ int dequant_q4k(const void* W, size_t nblk, float* out, cudaStream_t s);
 // ---- ops.cu ----
 int embed_bf16(const int* tok, const void* table_bf16, float* out, int R, int E, int V, cudaStream_t s);
 // x += sum_p y_p (nullable y); xn = rmsnorm(x) * w; xq = q8(xn)   (reference add_rmsnorm_quant, ops.h:14)
-int add_rmsnorm_quant(float* x, const float* y, int P, size_t part_stride, int ldy, const void* w_bf16, float* xn, XQ8F xq, int R, int n, float eps, cudaStream_t s, bool assign = false);   // assign: x = sum_p y_p instead of x += ...
+int add_rmsnorm_quant(float* x, const float* y, int P, size_t part_stride, int ldy, const void* w_bf16, float* xn, XQ8F xq, int R, int n, float eps, cudaStream_t s, bool assign = false,
+                      const float* slotw = nullptr, int nslot = 0);   // assign: x = sum_p y_p instead of x += ...; slotw: y = [R * nslot][ldy] expert outputs, x += sum_e fmaf(slotw, y) in slot order
 // out[r] = [rmsnorm(a[r]) * wa | rmsnorm(b[r]) * wb] quantised   (reference norm2_concat_quant, ops.h:16)
 int norm2_concat_quant(const float* a, const void* wa, const float* b, int ldb, const void* wb, float* out, XQ8F xq, int R, int n, float eps, cudaStream_t s);
 // xq = q8(silu(gu[:, :F]) * gu[:, F:2F])   (reference silu_mul_quant, ops.h:25)
@@ -101,7 +102,9 @@ int attn_decode(const AttnParams& p, int rows, int ngroups, cudaStream_t s);   /
 
 // ---- moe.cu ----
 int router_gemv(const float* W, const float* x, float* y, int N, int K, int T, cudaStream_t s);          // reference f32_gemv (fn.hip:252-277)
-int moe_route(const float* logits, int* ids, float* w, int T, int E, int k, cudaStream_t s);                // reference k_moe_route (fn.hip:167-205)
+int moe_route(const float* logits, int* ids, float* w, int T, int E, int k, cudaStream_t s);
+// both in one launch; counters: T zero-initialised ints (left zero)
+int router_route(const float* W, const float* x, float* logits, int* ids, float* w, int* counters, int E, int K, int k, int T, cudaStream_t s);                // reference k_moe_route (fn.hip:167-205)
 struct MoeParams {
     const void* w_exp; const void* w_sh; size_t ebytes; int N, K;   // expert matrices [E][N][K/256 blocks] and the shared expert's [N][K/256]
     const int* ids; const float* slotw; int nslot;                    // [T][nslot] expert ids (-1 = shared) and combine weights

@@ -85,6 +85,86 @@ __global__ void __launch_bounds__(1024) k_moe_route(const float* __restrict__ lo
     }
 }
 
+// ---- router + routing in one launch: the CTA that finishes a row's logits last (ticket counter per row) routes that row.
+// Same arithmetic as k_router_gemv and k_moe_route: a 256-thread CTA stands in for the 1024 threads of the routing kernel,
+// warp w doing the 32-element groups w, w+8, w+16, w+24 (xor tree inside a group, the 32 group results combined in order).
+__global__ void __launch_bounds__(256) k_router_route(const float* __restrict__ W, const float* __restrict__ x, float* __restrict__ y, int N, int K,
+                                                     int* __restrict__ ids, float* __restrict__ w, int E, int k, int* __restrict__ cnt) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float sh[32]; __shared__ float selp[16]; __shared__ int seli[16]; __shared__ float sp[1024]; __shared__ int s_last;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, t = blockIdx.y;
+    const int n = (blockIdx.x * 256 + tid) >> 5;
+    if (n < N) {
+        const float* wr = W + (size_t)n * K; const float* xr = x + (size_t)t * K;
+        float acc = 0.f;
+#pragma unroll 8
+        for (int i = lane * 4; i < K; i += 128) {
+            const float4 a = __ldg(reinterpret_cast<const float4*>(wr + i)), b = *reinterpret_cast<const float4*>(xr + i);
+            acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc); acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) acc = acc + __shfl_xor_sync(0xffffffffu, acc, off);
+        if (lane == 0) { y[(size_t)t * N + n] = acc; __threadfence(); }
+    }
+    __syncthreads();
+    if (tid == 0) s_last = atomicAdd(&cnt[t], 1) == (int)gridDim.x - 1;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const float* lg = y + (size_t)t * N;   // N = E + 1 logits of this row, written by all the CTAs of the row
+    float v[4], e[4];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int i = 32 * (warp + 8 * j) + lane;
+        v[j] = i < E ? __ldcg(lg + i) : -INFINITY;
+        float m = v[j];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+        if (lane == 0) sh[warp + 8 * j] = m;
+    }
+    __syncthreads();
+    mx = sh[0]; for (int q = 1; q < 32; ++q) mx = fmaxf(mx, sh[q]);
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int i = 32 * (warp + 8 * j) + lane;
+        e[j] = i < E ? expf_det(v[j] - mx) : 0.f;
+        float sacc = e[j];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) sacc = sacc + __shfl_xor_sync(0xffffffffu, sacc, off);
+        if (lane == 0) sh[warp + 8 * j] = sacc;
+    }
+    __syncthreads();
+    float sum = sh[0]; for (int q = 1; q < 32; ++q) sum = sum + sh[q];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { const int i = 32 * (warp + 8 * j) + lane; sp[i] = i < E ? e[j] / sum : -2.f; }
+    __syncthreads();
+    if (warp == 0) {   // top-k by (value desc, index asc); lane l owns indices l, l+32, ...
+        float pv[32];
+#pragma unroll
+        for (int q = 0; q < 32; ++q) pv[q] = sp[lane + 32 * q];
+        for (int r = 0; r < k; ++r) {
+            float bv = pv[0]; int bi = lane;
+#pragma unroll
+            for (int q = 1; q < 32; ++q) better(bv, bi, pv[q], lane + 32 * q);
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) { const float ov = __shfl_xor_sync(0xffffffffu, bv, off); const int oi = __shfl_xor_sync(0xffffffffu, bi, off); better(bv, bi, ov, oi); }
+            if (lane == 0) { selp[r] = bv; seli[r] = bi; }
+#pragma unroll
+            for (int q = 0; q < 32; ++q) if (bi == lane + 32 * q) pv[q] = -1.f;
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        float wsum = 0.f; for (int r = 0; r < k; ++r) wsum = wsum + selp[r];
+        for (int r = 0; r < k; ++r) { ids[t * (k + 1) + r] = seli[r]; w[t * (k + 1) + r] = selp[r] / wsum; }
+        ids[t * (k + 1) + k] = -1; w[t * (k + 1) + k] = sigmoid_det(__ldcg(lg + E));
+        cnt[t] = 0;   // ready for the next launch
+    }
+}
+
 // ---- one 16-row tile of an expert matrix against one activation row: blocks in order, weights read straight from
 // global memory (each expert tile is touched once), CH blocks per batch so that their loads share one round trip.
 // Returns the column of interest in r0 / r1 (rows g, g+8). Scales are decoded in registers per lane (rows g, g+8):
@@ -257,6 +337,12 @@ __global__ void __launch_bounds__(256) k_moe_silu_quant(const float* __restrict_
 int router_gemv(const float* W, const float* x, float* y, int N, int K, int T, cudaStream_t s) {
     HP_REQUIRE(N >= 1 && K > 0 && K % 128 == 0 && T >= 1, "router_gemv: bad shape N=%d K=%d T=%d", N, K, T);
     HP_CUDA(launch_pdl<8>(k_router_gemv, dim3((N * 32 + 255) / 256, T), dim3(256), 0, s, W, x, y, N, K));
+    HP_CUDA(cudaGetLastError()); return HP_OK;
+}
+int router_route(const float* W, const float* x, float* logits, int* ids, float* w, int* counters, int E, int K, int k, int T, cudaStream_t s) {
+    HP_REQUIRE(E >= 1 && E <= 1024 && k >= 1 && k <= 15 && k <= E && K > 0 && K % 128 == 0 && T >= 1 && T <= 32 && counters, "router_route: bad shape E=%d K=%d k=%d T=%d", E, K, k, T);
+    const int N = E + 1;
+    HP_CUDA(launch_pdl<8>(k_router_route, dim3((N * 32 + 255) / 256, T), dim3(256), 0, s, W, x, logits, N, K, ids, w, E, k, counters));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 int moe_route(const float* logits, int* ids, float* w, int T, int E, int k, cudaStream_t s) {

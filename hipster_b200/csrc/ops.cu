@@ -86,7 +86,7 @@ __device__ __forceinline__ void bf4(const uint16_t* w, float (&o)[4]) {
 template <int PT, int NG>   // PT > 0: the number of planes, known at compile time so that every load is in flight at once; 0: run-time P. NG: groups per thread
 __global__ void __cluster_dims__(NORM_CL, 1, 1) __launch_bounds__(NORM_TPB) k_add_rmsnorm_quant(float* __restrict__ x, const float* __restrict__ y, int P, size_t part_stride, int ldy,
                                                                      const uint16_t* __restrict__ w, float* __restrict__ xn, int8_t* __restrict__ q, float* __restrict__ sc,
-                                                                     int n, float eps, int assign) {
+                                                                     int n, float eps, int assign, const float* __restrict__ slotw, int nslot) {
     __shared__ float tab[NORM_NW];
     HP_TRACE_BEGIN();
     pdl_launch_dependents();
@@ -104,7 +104,7 @@ __global__ void __cluster_dims__(NORM_CL, 1, 1) __launch_bounds__(NORM_TPB) k_ad
     if (y) {
         float4 s[NG];
 #pragma unroll
-        for (int k = 0; k < NG; ++k) { const int i = 4 * (t + k * NORM_ROWT); s[k] = i < n ? *reinterpret_cast<const float4*>(y + (size_t)r * ldy + i) : make_float4(0.f, 0.f, 0.f, 0.f); }
+        for (int k = 0; k < NG; ++k) { const int i = 4 * (t + k * NORM_ROWT); s[k] = (i < n && !slotw) ? *reinterpret_cast<const float4*>(y + (size_t)r * ldy + i) : make_float4(0.f, 0.f, 0.f, 0.f); }
         if constexpr (PT > 0) {
             float4 u[PT > 1 ? PT - 1 : 1][NG];
 #pragma unroll
@@ -115,6 +115,19 @@ __global__ void __cluster_dims__(NORM_CL, 1, 1) __launch_bounds__(NORM_TPB) k_ad
             for (int p = 1; p < PT; ++p)
 #pragma unroll
                 for (int k = 0; k < NG; ++k) { s[k].x = s[k].x + u[p - 1][k].x; s[k].y = s[k].y + u[p - 1][k].y; s[k].z = s[k].z + u[p - 1][k].z; s[k].w = s[k].w + u[p - 1][k].w; }
+        } else if (slotw) {
+            // MoE combine (gemv.hip:1104-1112): y holds one row per (row, slot) pair; acc = fmaf(weight, value, acc) in slot order
+#pragma unroll
+            for (int k = 0; k < NG; ++k) s[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+            for (int e = 0; e < nslot; ++e) {
+                const float we = slotw[r * nslot + e];
+#pragma unroll
+                for (int k = 0; k < NG; ++k) {
+                    const int i = 4 * (t + k * NORM_ROWT);
+                    if (i < n) { const float4 uu = *reinterpret_cast<const float4*>(y + (size_t)(r * nslot + e) * ldy + i); s[k].x = fmaf(we, uu.x, s[k].x); s[k].y = fmaf(we, uu.y, s[k].y); s[k].z = fmaf(we, uu.z, s[k].z); s[k].w = fmaf(we, uu.w, s[k].w); }
+                }
+            }
         } else {
             for (int p = 1; p < P; ++p)
 #pragma unroll
@@ -437,18 +450,20 @@ int embed_bf16(const int* tok, const void* table, float* out, int R, int E, int 
     HP_CUDA(launch_pdl<16>(k_embed_bf16, dim3(R), dim3(256), 0, s, tok, (const uint16_t*)table, out, E, V));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
-int add_rmsnorm_quant(float* x, const float* y, int P, size_t part_stride, int ldy, const void* w_bf16, float* xn, XQ8F xq, int R, int n, float eps, cudaStream_t s, bool assign) {
+int add_rmsnorm_quant(float* x, const float* y, int P, size_t part_stride, int ldy, const void* w_bf16, float* xn, XQ8F xq, int R, int n, float eps, cudaStream_t s, bool assign,
+                      const float* slotw, int nslot) {
     HP_REQUIRE(!assign || y, "add_rmsnorm_quant: assign needs planes");
+    HP_REQUIRE(!slotw || (y && nslot >= 1), "add_rmsnorm_quant: the slot-weighted form needs the per-pair rows");
     HP_REQUIRE(R >= 1 && n > 0 && n % 64 == 0, "add_rmsnorm_quant: n=%d must be a positive multiple of 64", n);
     HP_REQUIRE(n <= NORM_ROWT * 4 * NORM_MAXG, "add_rmsnorm_quant: n=%d exceeds %d", n, NORM_ROWT * 4 * NORM_MAXG);
     HP_REQUIRE(!y || (ldy % 4 == 0 && part_stride % 4 == 0), "add_rmsnorm_quant: plane strides must be multiples of 4 floats");
-    const int pt = !y || P == 1 ? 1 : P == 2 ? 2 : P == 4 ? 4 : 0;
+    const int pt = slotw ? 0 : !y || P == 1 ? 1 : P == 2 ? 2 : P == 4 ? 4 : 0;
     auto pick = [&](auto ng_tag) {
         constexpr int NG = decltype(ng_tag)::value;
         return pt == 1 ? k_add_rmsnorm_quant<1, NG> : pt == 2 ? k_add_rmsnorm_quant<2, NG> : pt == 4 ? k_add_rmsnorm_quant<4, NG> : k_add_rmsnorm_quant<0, NG>;
     };
     auto kern = n <= NORM_ROWT * 4 ? pick(std::integral_constant<int, 1>()) : pick(std::integral_constant<int, NORM_MAXG>());
-    HP_CUDA(launch_pdl(kern, dim3(R * NORM_CL), dim3(NORM_TPB), 0, s, x, y, P, part_stride, ldy, (const uint16_t*)w_bf16, xn, (int8_t*)xq.q, (float*)xq.sc, n, eps, assign ? 1 : 0));
+    HP_CUDA(launch_pdl(kern, dim3(R * NORM_CL), dim3(NORM_TPB), 0, s, x, y, P, part_stride, ldy, (const uint16_t*)w_bf16, xn, (int8_t*)xq.q, (float*)xq.sc, n, eps, assign ? 1 : 0, slotw, nslot));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 int norm2_concat_quant(const float* a, const void* wa, const float* b, int ldb, const void* wb, float* out, XQ8F xq, int R, int n, float eps, cudaStream_t s) {
