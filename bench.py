@@ -4,9 +4,9 @@ python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--w
 
 Prints ONE JSON line (rank 0). A "step" is one MTP round (n draft steps, one verify pass of n+1 rows, device argmax +
 greedy acceptance, commit, MTP catch-up) over seeded synthetic input. Workloads:
-  dense27b  BASELINE config 3: Qwen3.8-27B-shaped dense hybrid, random-init Q4_K, 4096-token seeded prompt, MTP n=5,
+  dense27b  benchmark configuration 3: Qwen3.8-27B-shaped dense hybrid, random-init Q4_K, 4096-token seeded prompt, MTP n=5,
             seeded acceptance 0.7 (default; the metric is quoted on this configuration and it fits one GPU)
-  gemv      BASELINE config 1: Q4_K 17408 x 5120 verify GEMV over 3 rows + argmax + greedy acceptance
+  gemv      benchmark configuration 1: Q4_K 17408 x 5120 verify GEMV over 3 rows + argmax + greedy acceptance
 L2: every step streams 20 GB of weights, far beyond the 126 MB L2 (dense27b); the gemv workload rotates weight copies.
 N > 1 runs N independent replicas of the dense path (the dense trunk does not shard: "replicas only").
 """

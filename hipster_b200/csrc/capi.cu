@@ -168,7 +168,7 @@ int hp_model_preset(const char* preset, hp_model_cfg* o) {
     if (!strcmp(preset, "qwen35-27b")) {          // struct Qwen35Dims, engine/src/qwen35.h:15-26
         o->n_embd = 5120; o->n_layer = 64; o->n_ff = 17408; o->n_vocab = 248320; o->n_head = 24; o->n_head_kv = 4;
         o->gdn_qk_heads = 16; o->gdn_v_heads = 48; o->max_ctx = 8192; o->seed = 27;
-    } else if (!strcmp(preset, "flash-next")) {   // BASELINE config 4 shape (head geometry from struct FnDims, qwen4exp.h:18-28)
+    } else if (!strcmp(preset, "flash-next")) {   // benchmark configuration 4 shape (head geometry from struct FnDims, qwen4exp.h:18-28)
         o->n_embd = 2048; o->n_layer = 48; o->n_ff = 0; o->n_vocab = 248320; o->n_head = 24; o->n_head_kv = 2;
         o->gdn_qk_heads = 16; o->gdn_v_heads = 48; o->max_ctx = 4096; o->n_slots = 8; o->seed = 48;
         o->n_expert = 512; o->n_expert_used = 10; o->expert_ff = 512; o->gdn_sigmoid_gate = 1;

@@ -6,7 +6,7 @@ from ._lib import lib, check
 
 
 def expert_range(rank, world, n_expert):
-    """Routed experts [lo, hi) held by `rank` (contiguous blocks, SURVEY 8e: e lives on GPU e // (E / G))."""
+    """Routed experts [lo, hi) held by `rank`: contiguous blocks, expert e lives on GPU e // (E / G)."""
     return rank * n_expert // world, (rank + 1) * n_expert // world
 
 

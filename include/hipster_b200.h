@@ -114,7 +114,7 @@ typedef struct hp_model_cfg {
 typedef struct hp_slot_req { int slot; const int* tokens; int T; int pos; } hp_slot_req;
 typedef struct hp_engine hp_engine;
 
-/* preset: "qwen35-27b" (BASELINE config 3), "flash-next" (config 4), "tiny" / "tiny-moe" (reduced models for parity tests) */
+/* preset: "qwen35-27b" (benchmark configuration 3), "flash-next" (configuration 4), "tiny" / "tiny-moe" (reduced models for parity tests) */
 int hp_model_preset(const char* preset, hp_model_cfg* out);
 /* Replaces Qwen35::Qwen35(path, max_ctx, n_slots) (qwen35.h:53): no checkpoint is read, weights are generated. */
 int hp_load(const hp_model_cfg* cfg, hp_engine** out);

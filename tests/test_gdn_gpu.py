@@ -1,4 +1,4 @@
-"""BASELINE config 2: one Gated-DeltaNet layer verify step at full size (hidden 5120 -> 16 key heads, 48 value heads,
+"""Benchmark configuration 2: one Gated-DeltaNet layer verify step at full size (hidden 5120 -> 16 key heads, 48 value heads,
 dim 128, conv 4), fp32 state ~ N(0, 0.1), 6 bf16-rounded input rows ~ N(0, 1): per-row state snapshots, rollback to
 accepted length k in {0..5}, compared with the sequential one-row-at-a-time scan (GPU and CPU oracle).
 The stated tolerance is 1e-5 relative; the CUDA kernel and the oracle actually agree bit for bit.

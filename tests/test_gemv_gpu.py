@@ -81,7 +81,7 @@ def test_argmax_and_accept():
 
 
 def test_config1_kernel_check_full_size():
-    """BASELINE config 1: N=17408 x K=5120 Q4_K, 3 f32 activation rows, seed 0 -> GEMV, per-row argmax, greedy
+    """Benchmark configuration 1: N=17408 x K=5120 Q4_K, 3 f32 activation rows, seed 0 -> GEMV, per-row argmax, greedy
     acceptance against 2 seeded draft ids; CUDA vs the CPU restatement, plus the reference's own tolerance rule."""
     N, K, R = 17408, 5120, 3
     W = synth.q4k_matrix(N, K, seed=0); x = synth.activations(R, K, seed=0)
