@@ -87,8 +87,13 @@ struct AttnArgs {
     const int* groups;        // device: per group {r0, T, slot, pos0}
     float* pO; float* pm; float* pl; int nsplit_max;   // partials [group][kv head][split][MAXP] (x 256 for pO)
 };
-// grid (nsplit_max, n_kv, ngroups), 256 threads, dynamic smem
+// grid (nsplit_max, n_kv, ngroups), 256 threads, dynamic smem. PPT = (row, head) pairs per thread in the score phase
+// (warp w takes pairs w*PPT .. w*PPT+PPT-1): 6 covers the 48 pairs of a full verify group, 1 the <= 8 pairs of a
+// single-row pass, where the wider tile would spend seven warps on absent pairs. Every score and every output element
+// is the same fmaf chain whatever PPT is.
+template <int PPT>
 __global__ void __launch_bounds__(256) k_attn_split(AttnArgs a) {
+    constexpr int NP = 8 * PPT;   // pairs this instantiation can hold
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(16) uint8_t sm_raw[];
@@ -117,14 +122,14 @@ __global__ void __launch_bounds__(256) k_attn_split(AttnArgs a) {
         uint2* dv = reinterpret_cast<uint2*>(sV + k * KSTRIDE + c * 8); dv[0] = make_uint2(vv.x, vv.y); dv[1] = make_uint2(vv.z, vv.w);
     }
     __syncthreads();
-    // scores: thread (kq = tid % 32, pq = tid / 32) -> keys kq + 32*i (i < 4), pairs pq*6 + jx (jx < 6); fmaf chain over d
+    // scores: thread (kq = tid % 32, pq = tid / 32) -> keys kq + 32*i (i < 4), pairs pq*PPT + jx (jx < PPT); fmaf chain over d
     {
         const int kq = tid & 31, pq = tid >> 5;
-        float s[4][6];
+        float s[4][PPT];
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
-            for (int jx = 0; jx < 6; ++jx) s[i][jx] = 0.f;
+            for (int jx = 0; jx < PPT; ++jx) s[i][jx] = 0.f;
         for (int d = 0; d < HD; d += 4) {
             float kf[4][4];
 #pragma unroll
@@ -134,8 +139,8 @@ __global__ void __launch_bounds__(256) k_attn_split(AttnArgs a) {
                 kf[i][2] = h2f((uint16_t)(kk.y & 0xFFFF)); kf[i][3] = h2f((uint16_t)(kk.y >> 16));
             }
 #pragma unroll
-            for (int jx = 0; jx < 6; ++jx) {
-                const int p = pq * 6 + jx;
+            for (int jx = 0; jx < PPT; ++jx) {
+                const int p = pq * PPT + jx;
                 const float4 qv = p < npairs ? *reinterpret_cast<const float4*>(sQ + p * HD + d) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -147,7 +152,7 @@ __global__ void __launch_bounds__(256) k_attn_split(AttnArgs a) {
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
-            for (int jx = 0; jx < 6; ++jx) { const int p = pq * 6 + jx; if (p < MAXP) sE[(kq + 32 * i) * MAXP + p] = s[i][jx] * 0.0625f; }
+            for (int jx = 0; jx < PPT; ++jx) { const int p = pq * PPT + jx; if (p < MAXP) sE[(kq + 32 * i) * MAXP + p] = s[i][jx] * 0.0625f; }
     }
     __syncthreads();
     // softmax pieces per pair: warp w takes pairs w, w+8, ...; lane l takes keys l, l+32, l+64, l+96. Row t of the group
@@ -178,21 +183,21 @@ __global__ void __launch_bounds__(256) k_attn_split(AttnArgs a) {
     __syncthreads();
     // o[pair][d] = sum_k e[k][pair] * v[k][d], keys in position order; thread = dim d
     {
-        float2 o[MAXP / 2];   // packed pairs of (row, head) accumulators: two fp32 fmaf per instruction, each rounded once
+        float2 o[NP / 2];   // packed pairs of (row, head) accumulators: two fp32 fmaf per instruction, each rounded once
 #pragma unroll
-        for (int p = 0; p < MAXP / 2; ++p) o[p] = make_float2(0.f, 0.f);
+        for (int p = 0; p < NP / 2; ++p) o[p] = make_float2(0.f, 0.f);
         for (int k = 0; k < nkeys; ++k) {
             const float v = h2f(sV[k * KSTRIDE + tid]);
             const float2 vv = make_float2(v, v);
 #pragma unroll
-            for (int p4 = 0; p4 < MAXP / 4; ++p4) {
+            for (int p4 = 0; p4 < NP / 4; ++p4) {
                 const float4 e = *reinterpret_cast<const float4*>(sE + k * MAXP + p4 * 4);
                 o[p4 * 2] = attn_fma2(make_float2(e.x, e.y), vv, o[p4 * 2]);
                 o[p4 * 2 + 1] = attn_fma2(make_float2(e.z, e.w), vv, o[p4 * 2 + 1]);
             }
         }
 #pragma unroll
-        for (int p = 0; p < MAXP / 2; ++p) {
+        for (int p = 0; p < NP / 2; ++p) {
             if (2 * p < npairs) a.pO[(pbase + 2 * p) * HD + tid] = o[p].x;
             if (2 * p + 1 < npairs) a.pO[(pbase + 2 * p + 1) * HD + tid] = o[p].y;
         }
@@ -241,10 +246,16 @@ int attn_rope_kv(const AttnParams& p, int rows, cudaStream_t s) {
 int attn_decode(const AttnParams& p, int rows, int ngroups, cudaStream_t s) {
     HP_REQUIRE(rows >= 1 && ngroups >= 1 && p.n_head % p.n_kv == 0 && (p.n_head / p.n_kv) <= MAXP, "attn_decode: at most %d (row, head) pairs per kv head and group", MAXP);
     static bool attr = false;
-    if (!attr) { HP_CUDA(cudaFuncSetAttribute(k_attn_split, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem_bytes())); attr = true; }
+    if (!attr) {
+        HP_CUDA(cudaFuncSetAttribute(k_attn_split<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem_bytes()));
+        HP_CUDA(cudaFuncSetAttribute(k_attn_split<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem_bytes()));
+        attr = true;
+    }
     AttnArgs a; a.qkv = p.qkv; a.ld = p.ld; a.n_head = p.n_head; a.n_kv = p.n_kv; a.kc = (const uint16_t*)p.kc; a.vc = (const uint16_t*)p.vc;
     a.kv_stride = p.kv_stride; a.max_ctx = p.max_ctx; a.groups = p.groups; a.pO = p.pO; a.pm = p.pm; a.pl = p.pl; a.nsplit_max = p.nsplit_max;
-    HP_CUDA(launch_pdl<4>(k_attn_split, dim3(p.nsplit_max, p.n_kv, ngroups), dim3(256), attn_smem_bytes(), s, a));
+    // group sizes live on the device; `rows` bounds the rows of any group, so rows * G <= 8 selects the narrow score tile
+    if (rows * (p.n_head / p.n_kv) <= 8) HP_CUDA(launch_pdl<4>(k_attn_split<1>, dim3(p.nsplit_max, p.n_kv, ngroups), dim3(256), attn_smem_bytes(), s, a));
+    else HP_CUDA(launch_pdl<4>(k_attn_split<6>, dim3(p.nsplit_max, p.n_kv, ngroups), dim3(256), attn_smem_bytes(), s, a));
     HP_CUDA(launch_pdl<4>(k_attn_merge, dim3(rows * p.n_head), dim3(256), 0, s, p.qkv, p.ld, p.n_head, p.n_kv, p.groups, p.row_group, p.pO, p.pm, p.pl, p.nsplit_max, p.out, (int8_t*)p.xq.q, (float*)p.xq.sc));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
