@@ -155,7 +155,9 @@ int hp_ep_init(hp_engine* e, const void* id128);
 int hp_tensor_dev(const hp_engine* e, int layer, int kind, void** ptr_out, size_t* bytes_out);
 int hp_gdn_state_dev(hp_engine* e, int slot, int gdn_layer, float** ptr_out, size_t* bytes_out);
 /* Measurement hooks (the reference's HIPSTER_TIMING categories, qwen35.h:95, qwen35.cpp:181-186): mean device time of
- * `reps` verify passes of R rows (what = 0) or of only their GEMV launches (what = 1); nothing is committed.
+ * `reps` verify passes of R rows (what = 0), of only their GEMV launches (what = 1), or of passes that leave kernel
+ * classes out to price them in place (what = 16 + mask: 1 GDN, 2 row norms, 4 attention, 8 SiLU, 16 gate|up, 32 down,
+ * 64 LM head, 128 input projections, 256 other GEMVs; only the time means anything then); nothing is committed.
  * hp_pass_weight_bytes: Q4_K bytes one trunk pass (mtp = 0) or one MTP-block pass (mtp = 1) reads, with or without the
  * LM head: the algorithmic bytes of the roofline. */
 int hp_profile_pass(hp_engine* e, int R, int what, int reps, float* ms_out);
