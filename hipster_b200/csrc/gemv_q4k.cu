@@ -9,10 +9,12 @@
 // K is cut into P equal parts (P = 1, 2 or 4, a function of the tensor shape only, chosen so that the 16-row tiles
 // divide evenly over the SMs); the 148/P CTAs of part p share the tiles evenly, and inside a CTA the stream of units
 // (16 rows x 2 blocks, tile-major then along K) is divided evenly and contiguously over the 12 warps. Each warp runs
-// its own ring of 1-D bulk async copies (cp.async.bulk + mbarrier, 16 row pieces of 288 B per stage), unpacks the
-// nibbles in registers and feeds the int8 tensor-core tile mma.m16n8k32 (weights on M, verify rows on N = 8), which
-// yields the exact int32 dot of every 32-element sub-block. The quantised activations of the CTA's K part are staged
-// once per CTA in shared memory by bulk copies. One fp32 update per sub-block follows, in block order:
+// its own ring of 1-D bulk async copies (cp.async.bulk + mbarrier; 16 row pieces of 288 B per stage in the ggml layout,
+// one 4608-byte copy per stage in the engine's tile-major layout), unpacks the nibbles in registers and feeds the int8
+// tensor-core tile mma.m16n8k32 (weights on M, verify rows on N = 8), which yields the exact int32 dot of every
+// 32-element sub-block. The 6-bit scales of a lane's two rows are decoded in registers. The quantised activations of
+// the CTA's K part are staged once per CTA in shared memory by bulk copies. One fp32 update per sub-block follows, in
+// block order:
 //     acc = fmaf((d*sc) * xd, (float)idot, acc);  acc = fmaf(-(dmin*mn), xs, acc);
 // A tile whose blocks are spread over several warps of the CTA is finished through shared memory: the partial sums
 // are added in warp order. Each K part writes its own output plane; the planes are added in part order by the
@@ -28,7 +30,6 @@ namespace {
 
 constexpr int SK_STAGES = GEMV_STAGES;
 constexpr int SK_THREADS = GEMV_WARPS * 32;
-constexpr int SK_SCR_BYTES = 0;
 // Two weight layouts. Row-major ggml (TILED = false): a stage holds 16 row pieces of CB blocks, one bulk copy per row.
 // Tile-major (TILED = true, the engine repacks to it at load; same bytes, permuted): for every 16-row tile and block a
 // contiguous 2304-byte chunk = 16 headers (16 B each) + nibbles stored [j][lane][row g 8 B | row g+8 8 B], so a stage
@@ -36,7 +37,7 @@ constexpr int SK_SCR_BYTES = 0;
 template <int CB, bool TILED> struct SkGeom {
     static constexpr int ROW_STRIDE = CB == 2 ? 288 : 160;   // 288 = 2*128+32, 160 = 128+32: rows land on distinct 32-byte bank groups
     static constexpr int STAGE_BYTES = TILED ? CB * 2304 : 16 * ROW_STRIDE;
-    static constexpr int FIXED = GEMV_WARPS * SK_STAGES * STAGE_BYTES + GEMV_WARPS * SK_SCR_BYTES + 1024;
+    static constexpr int FIXED = GEMV_WARPS * SK_STAGES * STAGE_BYTES + 1024;
 };
 
 __device__ __forceinline__ float2 mul2(float2 a, float2 b) {
@@ -92,7 +93,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
     using Geo = SkGeom<CB, TILED>;
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* ring_all = smem;
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + GEMV_WARPS * SK_STAGES * Geo::STAGE_BYTES + GEMV_WARPS * SK_SCR_BYTES);
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + GEMV_WARPS * SK_STAGES * Geo::STAGE_BYTES);
     const int nbp = nb / P;                                // blocks of this CTA's K part
     const uint4* xq_s = reinterpret_cast<const uint4*>(smem + Geo::FIXED);
     const float4* xsc_s = reinterpret_cast<const float4*>(smem + Geo::FIXED + NT * nbp * 2048);

@@ -308,26 +308,28 @@ __global__ void __cluster_dims__(GDN_CL, 1, 1) __launch_bounds__(256) k_gdn(GdnA
     };
     // conv history of this head: [3 taps][q 128 | k 128 | v 128]; private per v-head
     float* cst = a.conv_state + (size_t)slot * a.conv_stride + (size_t)h * 3 * 384;
-    const int nrep = a.replay_n ? min(a.replay_n[slot], 8) : 0;
-    const int nrows = nrep + T;
     const int Z = a.n_v * D;
     // gate input z of this lane's channel for the row that warp `warp` finishes in phase 3
     const float zz = warp < T ? a.rows[(size_t)(r0 + warp) * a.ld + a.off_z + h * D + 32 * rank + lane] : 0.f;
 
-    // ---- phase 1: history (3 taps) + raw inputs of all rows -> raw[tap or 3 + row][c]; all loads in flight at once
-    {
-        float tmp[NLD];
+    // ---- phase 1: history (3 taps) + raw inputs of all rows -> raw[tap or 3 + row][c]. The history and the new rows do
+    // not depend on the replay count: their loads go out first, together with the load of the count itself; the saved
+    // rows of the accepted prefix follow once the count is known.
+    constexpr int NLA = 5, NLB = 3;   // (8 + 3) * 96 <= 5 * 256 history + new values, 8 * 96 = 3 * 256 replayed values
+    float tmpa[NLA], tmpb[NLB];
 #pragma unroll
-        for (int k = 0; k < NLD; ++k) {
-            const int rr = e_rr[k], it = rr - 3;
-            if (rr < nrows + 3) {
-                const float* src = rr < 3 ? cst + rr * 384 + e_slot[k] : it < nrep ? sav + it * 388 + e_slot[k] : a.rows + (size_t)(r0 + it - nrep) * a.ld + e_col[k];
-                tmp[k] = *src;
-            }
-        }
-#pragma unroll
-        for (int k = 0; k < NLD; ++k) if (e_rr[k] < nrows + 3) raw[e_rr[k]][e_c[k]] = tmp[k];
+    for (int k = 0; k < NLA; ++k) {
+        const int rr = e_rr[k];
+        if (rr < T + 3) tmpa[k] = rr < 3 ? cst[rr * 384 + e_slot[k]] : a.rows[(size_t)(r0 + rr - 3) * a.ld + e_col[k]];
     }
+    const int nrep = a.replay_n ? min(a.replay_n[slot], 8) : 0;
+    const int nrows = nrep + T;
+#pragma unroll
+    for (int k = 0; k < NLB; ++k) { const int it = e_rr[k]; if (it < nrep) tmpb[k] = sav[it * 388 + e_slot[k]]; }
+#pragma unroll
+    for (int k = 0; k < NLA; ++k) { const int rr = e_rr[k]; if (rr < T + 3) raw[rr < 3 ? rr : rr + nrep][e_c[k]] = tmpa[k]; }
+#pragma unroll
+    for (int k = 0; k < NLB; ++k) { const int it = e_rr[k]; if (it < nrep) raw[3 + it][e_c[k]] = tmpb[k]; }
     // gates of every row (all four CTAs compute them: no exchange), by the last warp, which has the fewest conv items
     float raw_b = 0.f, raw_a = 0.f;
     if (warp == 7 && lane < nrows) {
@@ -381,6 +383,7 @@ __global__ void __cluster_dims__(GDN_CL, 1, 1) __launch_bounds__(256) k_gdn(GdnA
     __syncthreads();
     {   // normalise q | k of every row in place: thread tid owns channel tid (q for tid < 128, k otherwise)
         const int off = (tid >> 7) * 160 + ((tid & 127) >> 4) * 20 + (tid & 15);
+#pragma unroll 4
         for (int it = 0; it < nrows; ++it) sqk[it][off] = sqk[it][off] / snrm[it][tid >> 7];
     }
     __syncthreads();
