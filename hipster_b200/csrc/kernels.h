@@ -101,10 +101,8 @@ int attn_rope_kv(const AttnParams& p, int rows, cudaStream_t s);          // ref
 int attn_decode(const AttnParams& p, int rows, int ngroups, cudaStream_t s);   // reference attn_decode_mq (ops.h:72)
 
 // ---- moe.cu ----
-int router_gemv(const float* W, const float* x, float* y, int N, int K, int T, cudaStream_t s);          // reference f32_gemv (fn.hip:252-277)
-int moe_route(const float* logits, int* ids, float* w, int T, int E, int k, cudaStream_t s);
-// both in one launch; counters: T zero-initialised ints (left zero)
-int router_route(const float* W, const float* x, float* logits, int* ids, float* w, int* counters, int E, int K, int k, int T, cudaStream_t s);                // reference k_moe_route (fn.hip:167-205)
+// router (reference f32_gemv, fn.hip:252-277) and routing (k_moe_route, fn.hip:167-205) in one launch; counters: T zero-initialised ints (left zero)
+int router_route(const float* W, const float* x, float* logits, int* ids, float* w, int* counters, int E, int K, int k, int T, cudaStream_t s);
 struct MoeParams {
     const void* w_exp; const void* w_sh; size_t ebytes; int N, K;   // expert matrices [E][N][K/256 blocks] and the shared expert's [N][K/256]
     const int* ids; const float* slotw; int nslot;                    // [T][nslot] expert ids (-1 = shared) and combine weights
@@ -113,9 +111,7 @@ struct MoeParams {
 };
 int moe_gemv_up(const MoeParams& p, cudaStream_t s);                  // reference gemv_moe, xrow_te = false (gemv.h:46)
 int moe_silu_quant(const float* gu, int F, const int* ids, int e_lo, int e_hi, int own_shared, XQ8F xq, int pairs, cudaStream_t s);   // fn.hip:206-211
-int moe_down_combine(const MoeParams& p, cudaStream_t s);             // reference gemv_moe with slotw (gemv.hip:1095-1114)
 int moe_down_pairs(const MoeParams& p, cudaStream_t s);               // expert-parallel form: per-pair outputs, zeros for experts owned elsewhere
-int moe_combine(const float* v, const float* slotw, int nslot, float* y, int T, int N, cudaStream_t s);
 
 // ---- argmax.cu ----
 // per-row argmax (max value, lowest index) of logits [R][ld] -> ids/vals on device

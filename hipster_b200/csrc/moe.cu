@@ -13,81 +13,14 @@
 namespace hp {
 namespace {
 
-// ---- router: logits[t][e] = sum_k W[e][k] x[t][k], f32. One warp per weight row; lane l takes k = 4l + 128 i (float4),
-// four fmaf per step in element order, then the xor-shuffle tree (offsets 16..1). ----
-__global__ void __launch_bounds__(256) k_router_gemv(const float* __restrict__ W, const float* __restrict__ x, float* __restrict__ y, int N, int K) {
-    pdl_launch_dependents();
-    pdl_wait();
-    const int n = (blockIdx.x * 256 + threadIdx.x) >> 5, lane = threadIdx.x & 31, t = blockIdx.y;
-    if (n >= N) return;
-    const float* w = W + (size_t)n * K; const float* xr = x + (size_t)t * K;
-    float acc = 0.f;
-#pragma unroll 8
-    for (int i = lane * 4; i < K; i += 128) {
-        const float4 a = __ldg(reinterpret_cast<const float4*>(w + i)), b = *reinterpret_cast<const float4*>(xr + i);
-        acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc); acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
-    }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) acc = acc + __shfl_xor_sync(0xffffffffu, acc, off);
-    if (lane == 0) y[(size_t)t * N + n] = acc;
-}
-
-// ---- routing: softmax over the first E logits, top-k by (value desc, index asc), weights renormalised by the sum of the
-// selected probabilities taken in rank order; slot k = shared expert (id -1) with weight sigmoid(logit[E]). ----
+// ---- router (exact f32: one warp per weight row; lane l takes k = 4l + 128 i as float4, four fmaf per step in element
+// order, then the xor-shuffle tree 16..1) and routing (softmax over the first E logits, top-k by (value desc, index asc),
+// weights renormalised by the sum of the selected probabilities taken in rank order; slot k = shared expert, id -1, with
+// weight sigmoid(logit[E])). Reference: k_f32_gemv (fn.hip:252-266), k_moe_route (fn.hip:167-205). ----
 __device__ __forceinline__ void better(float& bv, int& bi, float v, int i) { if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; } }
-__global__ void __launch_bounds__(1024) k_moe_route(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ w, int E, int k) {
-    pdl_launch_dependents();
-    pdl_wait();
-    __shared__ float sh[32]; __shared__ int shi[32]; __shared__ float selp[16]; __shared__ int seli[16];
-    const int t = blockIdx.x, i = threadIdx.x, warp = i >> 5, lane = i & 31;
-    const float v = i < E ? logits[(size_t)t * (E + 1) + i] : -INFINITY;
-    float mx = v;
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-    if (lane == 0) sh[warp] = mx;
-    __syncthreads();
-    mx = sh[0]; for (int q = 1; q < 32; ++q) mx = fmaxf(mx, sh[q]);
-    __syncthreads();
-    const float e = i < E ? expf_det(v - mx) : 0.f;
-    float s = e;
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) s = s + __shfl_xor_sync(0xffffffffu, s, off);
-    if (lane == 0) sh[warp] = s;
-    __syncthreads();
-    float sum = sh[0]; for (int q = 1; q < 32; ++q) sum = sum + sh[q];
-    __syncthreads();
-    // top-k by (value desc, index asc): the winner of every round is unique, so any reduction order finds it. The
-    // probabilities go to shared memory and warp 0 alone runs the k rounds (lane l owns indices l, l+32, ...): no
-    // block-wide barrier per round.
-    __shared__ float sp[1024];
-    sp[i] = i < E ? e / sum : -2.f;
-    __syncthreads();
-    if (warp == 0) {
-        float pv[32];
-#pragma unroll
-        for (int q = 0; q < 32; ++q) pv[q] = sp[lane + 32 * q];
-        for (int r = 0; r < k; ++r) {
-            float bv = pv[0]; int bi = lane;
-#pragma unroll
-            for (int q = 1; q < 32; ++q) better(bv, bi, pv[q], lane + 32 * q);
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) { const float ov = __shfl_xor_sync(0xffffffffu, bv, off); const int oi = __shfl_xor_sync(0xffffffffu, bi, off); better(bv, bi, ov, oi); }
-            if (lane == 0) { selp[r] = bv; seli[r] = bi; }
-#pragma unroll
-            for (int q = 0; q < 32; ++q) if (bi == lane + 32 * q) pv[q] = -1.f;
-        }
-    }
-    __syncthreads();
-    if (i == 0) {
-        float wsum = 0.f; for (int r = 0; r < k; ++r) wsum = wsum + selp[r];
-        for (int r = 0; r < k; ++r) { ids[t * (k + 1) + r] = seli[r]; w[t * (k + 1) + r] = selp[r] / wsum; }
-        ids[t * (k + 1) + k] = -1; w[t * (k + 1) + k] = sigmoid_det(logits[(size_t)t * (E + 1) + E]);
-    }
-}
-
-// ---- router + routing in one launch: the CTA that finishes a row's logits last (ticket counter per row) routes that row.
-// Same arithmetic as k_router_gemv and k_moe_route: a 256-thread CTA stands in for the 1024 threads of the routing kernel,
-// warp w doing the 32-element groups w, w+8, w+16, w+24 (xor tree inside a group, the 32 group results combined in order).
+// Both in one launch: the CTA that finishes a row's logits last (ticket counter per row) routes that row. The softmax
+// sums follow a fixed order: xor tree inside each 32-element group, the 32 group results combined in group order (warp w
+// of the 256-thread CTA does groups w, w+8, w+16, w+24).
 __global__ void __launch_bounds__(256) k_router_route(const float* __restrict__ W, const float* __restrict__ x, float* __restrict__ y, int N, int K,
                                                      int* __restrict__ ids, float* __restrict__ w, int E, int k, int* __restrict__ cnt) {
     pdl_launch_dependents();
@@ -291,36 +224,6 @@ __global__ void __launch_bounds__(256) k_moe_down_pairs(MoeArgs a) {
     expert_tile<2>(W, row_bytes, nb, a.xq, a.xsc, pair >> 3, pair & 7, lane, r0, r1);
     if ((lane & 3) == 0) { a.y[(size_t)pair * a.N + tile * 16 + g] = r0; a.y[(size_t)pair * a.N + tile * 16 + g + 8] = r1; }
 }
-// down + combine: y[t][row] = sum_e slotw[t,e] * (W_down[ids[t,e]] . act[(t,e)]) in slot order (gemv.hip:1104-1112)
-__global__ void __launch_bounds__(256) k_moe_down(MoeArgs a) {
-    pdl_launch_dependents();
-    pdl_wait();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tiles = a.N / 16, unit = blockIdx.x * 8 + warp;
-    if (unit >= a.T * tiles) return;
-    const int t = unit / tiles, tile = unit % tiles;
-    const int nb = a.K / 256, row_bytes = nb * 144;
-    float acc0 = 0.f, acc1 = 0.f;
-    for (int e = 0; e < a.nslot; ++e) {
-        const int pair = t * a.nslot + e, id = a.ids[pair];
-        const uint8_t* W = (id >= 0 ? a.w_exp + (size_t)id * a.ebytes : a.w_sh) + (size_t)tile * 16 * row_bytes;
-        float r0, r1;
-        expert_tile<2>(W, row_bytes, nb, a.xq, a.xsc, pair >> 3, pair & 7, lane, r0, r1);
-        const float w = a.slotw[pair];
-        acc0 = fmaf(w, r0, acc0); acc1 = fmaf(w, r1, acc1);
-    }
-    const int g = lane >> 2;
-    if ((lane & 3) == 0) { a.y[(size_t)t * a.N + tile * 16 + g] = acc0; a.y[(size_t)t * a.N + tile * 16 + g + 8] = acc1; }
-}
-// combine of exchanged per-pair outputs (expert-parallel): y[t][n] = sum_e slotw[t,e] * v[(t,e)][n], slot order
-__global__ void __launch_bounds__(256) k_moe_combine(const float* __restrict__ v, const float* __restrict__ slotw, int nslot, float* __restrict__ y, int N) {
-    pdl_launch_dependents();
-    pdl_wait();
-    const int t = blockIdx.y, n = blockIdx.x * 256 + threadIdx.x; if (n >= N) return;
-    float acc = 0.f;
-    for (int e = 0; e < nslot; ++e) acc = fmaf(slotw[t * nslot + e], v[(size_t)(t * nslot + e) * N + n], acc);
-    y[(size_t)t * N + n] = acc;
-}
 // q8(silu(g) * u) per (t,e) row: gu [pairs][2F] (fn.hip:206-211); pairs of experts that live elsewhere are skipped
 __global__ void __launch_bounds__(256) k_moe_silu_quant(const float* __restrict__ gu, int F, const int* __restrict__ ids, int e_lo, int e_hi, int own_shared, int8_t* __restrict__ q, float* __restrict__ sc) {
     pdl_launch_dependents();
@@ -334,20 +237,10 @@ __global__ void __launch_bounds__(256) k_moe_silu_quant(const float* __restrict_
 
 }  // namespace
 
-int router_gemv(const float* W, const float* x, float* y, int N, int K, int T, cudaStream_t s) {
-    HP_REQUIRE(N >= 1 && K > 0 && K % 128 == 0 && T >= 1, "router_gemv: bad shape N=%d K=%d T=%d", N, K, T);
-    HP_CUDA(launch_pdl<8>(k_router_gemv, dim3((N * 32 + 255) / 256, T), dim3(256), 0, s, W, x, y, N, K));
-    HP_CUDA(cudaGetLastError()); return HP_OK;
-}
 int router_route(const float* W, const float* x, float* logits, int* ids, float* w, int* counters, int E, int K, int k, int T, cudaStream_t s) {
     HP_REQUIRE(E >= 1 && E <= 1024 && k >= 1 && k <= 15 && k <= E && K > 0 && K % 128 == 0 && T >= 1 && T <= 32 && counters, "router_route: bad shape E=%d K=%d k=%d T=%d", E, K, k, T);
     const int N = E + 1;
     HP_CUDA(launch_pdl<8>(k_router_route, dim3((N * 32 + 255) / 256, T), dim3(256), 0, s, W, x, logits, N, K, ids, w, E, k, counters));
-    HP_CUDA(cudaGetLastError()); return HP_OK;
-}
-int moe_route(const float* logits, int* ids, float* w, int T, int E, int k, cudaStream_t s) {
-    HP_REQUIRE(T >= 1 && E >= 1 && E <= 1024 && k >= 1 && k <= 15 && k <= E, "moe_route: bad shape E=%d k=%d", E, k);
-    HP_CUDA(launch_pdl<8>(k_moe_route, dim3(T), dim3(1024), 0, s, logits, ids, w, E, k));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 static MoeArgs moe_args(const MoeParams& p) {
@@ -365,20 +258,10 @@ int moe_silu_quant(const float* gu, int F, const int* ids, int e_lo, int e_hi, i
     HP_CUDA(launch_pdl<8>(k_moe_silu_quant, dim3((F / 32 + 7) / 8, pairs), dim3(256), 0, s, gu, F, ids, e_lo, e_hi, own_shared, (int8_t*)xq.q, (float*)xq.sc));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
-int moe_down_combine(const MoeParams& p, cudaStream_t s) {
-    HP_REQUIRE(p.N % 16 == 0 && p.K % 256 == 0 && p.T >= 1 && p.nslot >= 1 && p.slotw, "moe_down_combine: bad shape");
-    const int units = p.T * (p.N / 16);
-    HP_CUDA(launch_pdl<8>(k_moe_down, dim3((units + 7) / 8), dim3(256), 0, s, moe_args(p)));
-    HP_CUDA(cudaGetLastError()); return HP_OK;
-}
 int moe_down_pairs(const MoeParams& p, cudaStream_t s) {
     HP_REQUIRE(p.N % 16 == 0 && p.K % 256 == 0 && p.T >= 1 && p.nslot >= 1, "moe_down_pairs: bad shape");
     const int units = p.T * p.nslot * (p.N / 16);
     HP_CUDA(launch_pdl<8>(k_moe_down_pairs, dim3((units + 7) / 8), dim3(256), 0, s, moe_args(p)));
-    HP_CUDA(cudaGetLastError()); return HP_OK;
-}
-int moe_combine(const float* v, const float* slotw, int nslot, float* y, int T, int N, cudaStream_t s) {
-    HP_CUDA(launch_pdl<8>(k_moe_combine, dim3((N + 255) / 256, T), dim3(256), 0, s, v, slotw, nslot, y, N));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 
