@@ -149,7 +149,6 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
     pdl_wait();
     HP_TRACE_WAITED();
 
-#ifndef HP_DBG_NOX
     if (warp == 0) {   // quantised activations of blocks [kb0, kb0 + nbp), all NT column tiles, by bulk copies: one block
         // (2048 + 512 B) per copy pair, lanes in parallel, each CTA starting at a different block so that the 148 CTAs do
         // not walk the same L2 lines in lockstep
@@ -161,7 +160,6 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
             bulk_g2s(smem_u32(smem + Geo::FIXED + NT * nbp * 2048 + (n * nbp + b) * 512), xsc + ((size_t)n * nb + kb0 + b) * 32, 512u, xbar);
         }
     }
-#endif
 
     float2 acc[NT][2];   // [n][0] = row g, cols 2t,2t+1 ; [n][1] = row g+8
     auto zero_acc = [&]() {
@@ -203,11 +201,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
 
     int cur_tile = first_tile, chunk = nunits ? u0 % C : 0;
     bool cur_from_start = chunk == 0;
-#ifndef HP_DBG_NOX
     bool ok = mbar_wait(xbar, 0, err);
-#else
-    bool ok = true;
-#endif
     for (int i = 0; i < nunits && ok; ++i) {
         const int s = i % SK_STAGES;
         ok = mbar_wait(bar0 + 8 * s, (i / SK_STAGES) & 1, err);
@@ -215,7 +209,6 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
         const uint8_t* st = ring + s * Geo::STAGE_BYTES;
         const uint4* xqp = xq_s + (chunk * CB) * 128 + lane;
         const float4* xsp = xsc_s + (chunk * CB) * 32 + t;
-#ifndef HP_DBG_NOCOMPUTE
 #pragma unroll
         for (int blk = 0; blk < CB; ++blk) {
             // Scales of this lane's two rows (g, g+8), decoded in registers from the 16-byte headers. A 6-bit value v
@@ -264,7 +257,6 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
             }
         }
         __syncwarp();   // every lane has read the stage before it is refilled
-#endif
         if (it_i < nunits) issue();
         if (++chunk == C) {
             flush(cur_tile, cur_from_start);
@@ -274,9 +266,6 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
             flush(cur_tile, false);
         }
     }
-#ifdef HP_DBG_NOFLUSH
-    return;
-#endif
     // ---------------- tiles shared by several warps of this CTA: combine through shared memory in warp order
     __syncthreads();   // every ring is drained: its memory becomes the exchange buffer [warp][slot][NT*4][32]
 #pragma unroll
@@ -381,9 +370,6 @@ template <int NT>
 int launch_sk(const uint8_t* W, bool tiled, const void* xq, const void* xsc, float* y, int N, int nb, int P, int R, int ldy, size_t part_stride,
               int* err, cudaStream_t s, bool pdl) {
     const bool cb2 = (nb / P) % 2 == 0;
-#ifdef HP_FORCE_CB1
-    if (tiled) return launch_sk2<NT, 1, true>(W, xq, xsc, y, N, nb, P, R, ldy, part_stride, err, s, pdl);
-#endif
     if (tiled) return cb2 ? launch_sk2<NT, 2, true>(W, xq, xsc, y, N, nb, P, R, ldy, part_stride, err, s, pdl)
                           : launch_sk2<NT, 1, true>(W, xq, xsc, y, N, nb, P, R, ldy, part_stride, err, s, pdl);
     return cb2 ? launch_sk2<NT, 2, false>(W, xq, xsc, y, N, nb, P, R, ldy, part_stride, err, s, pdl)
