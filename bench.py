@@ -514,11 +514,19 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=0, help="override the workload's prompt length (shorter prompts are for profiling captures only)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    # stdout carries the one JSON line and nothing else: whatever libraries print there meanwhile (NCCL's version banner,
+    # for one) is sent to stderr, and the line is written to the saved descriptor at the end
+    sys.stdout.flush()
+    out_fd = os.dup(1); os.dup2(2, 1)
+
+    def emit(line):
+        sys.stdout.flush()
+        os.write(out_fd, (json.dumps(line) + "\n").encode())
     rank, local_rank, world = dist_env()
     if args.impl == "reference":
         line = run_reference(args, rank, world)
         if line:
-            print(json.dumps(line), flush=True)
+            emit(line)
         return
     import torch
     if world > 1:
@@ -532,7 +540,7 @@ def main():
     else:
         line = run_gemv(args, rank, local_rank, world)
     if line:
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         import torch.distributed as dist
         dist.destroy_process_group()
