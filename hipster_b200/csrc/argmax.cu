@@ -65,8 +65,7 @@ __global__ void k_accept(const int* __restrict__ ids, const int* __restrict__ dr
 // 16 KiB until the process exits. In host code the name below is only a handle for cudaGetSymbolAddress.
 constexpr int AM_STATIC_ROWS = 32, AM_STATIC_PARTS = 64;
 static __device__ __align__(256) unsigned char g_argmax_scratch[AM_STATIC_ROWS * AM_STATIC_PARTS * 8];
-constexpr int AM_MAX_DEVICES = 64;
-static void* g_argmax_scratch_addr[AM_MAX_DEVICES] = {};
+static void* g_argmax_scratch_addr[MAX_DEVICES] = {};   // per device ordinal; written without a lock (see the header: first call per device from one thread)
 
 }  // namespace
 
@@ -90,9 +89,13 @@ int argmax_rows_static(const float* logits, int R, int n, int ld, int* ids, floa
     HP_REQUIRE(R >= 1 && n >= 1 && ld >= n, "argmax_rows_static: bad arguments R=%d n=%d ld=%d", R, n, ld);
     HP_REQUIRE(R <= AM_STATIC_ROWS && n <= AM_STATIC_PARTS * AM_CHUNK,
                "argmax_rows_static: R=%d n=%d exceed the built-in scratch (at most %d rows of %d entries)", R, n, AM_STATIC_ROWS, AM_STATIC_PARTS * AM_CHUNK);
-    int dev = -1;
-    HP_CUDA(cudaGetDevice(&dev));
-    HP_REQUIRE(dev >= 0 && dev < AM_MAX_DEVICES, "argmax_rows_static: device ordinal %d not supported", dev);
+    // The array whose address is needed is the copy on the device that owns the stream. A kernel can only be launched
+    // into a stream of the current device, so a stream that belongs to another device is refused here rather than
+    // handed the wrong device's address.
+    const int cur = current_device();
+    int dev = cur;
+    if (s != nullptr && s != cudaStreamLegacy && s != cudaStreamPerThread) HP_CUDA(cudaStreamGetDevice(s, &dev));
+    HP_REQUIRE(cur >= 0 && dev == cur, "argmax_rows_static: the stream belongs to device %d but device %d is current", dev, cur);
     if (!g_argmax_scratch_addr[dev]) {
         void* p = nullptr;
         HP_CUDA(cudaGetSymbolAddress(&p, g_argmax_scratch));

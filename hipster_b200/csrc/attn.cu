@@ -245,7 +245,9 @@ int attn_rope_kv(const AttnParams& p, int rows, cudaStream_t s) {
 }
 int attn_decode(const AttnParams& p, int rows, int ngroups, cudaStream_t s) {
     HP_REQUIRE(rows >= 1 && ngroups >= 1 && p.n_head % p.n_kv == 0 && (p.n_head / p.n_kv) <= MAXP, "attn_decode: at most %d (row, head) pairs per kv head and group", MAXP);
-    static bool attr = false;
+    static bool attr_dev[MAX_DEVICES] = {};   // per device: the opt-in belongs to the device's copy of the kernel
+    const int dev = current_device(); if (dev < 0) return HP_ECUDA;
+    bool& attr = attr_dev[dev];
     if (!attr) {
         HP_CUDA(cudaFuncSetAttribute(k_attn_split<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem_bytes()));
         HP_CUDA(cudaFuncSetAttribute(k_attn_split<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem_bytes()));

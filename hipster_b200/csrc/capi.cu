@@ -19,23 +19,27 @@ int cuda_fail(cudaError_t e, const char* what, const char* file, int line) {
     set_error("CUDA error %d (%s) in %s @%s:%d", (int)e, cudaGetErrorString(e), what, file, line);
     return HP_ECUDA;
 }
-// one status word per process, set by kernels whose bounded waits gave up
-static int* g_dev_err = nullptr;
+// one status word per device, set by kernels whose bounded waits gave up
+static int* g_dev_err[MAX_DEVICES] = {};
 int* device_err_flag() {
-    if (!g_dev_err) { if (cudaMalloc(&g_dev_err, sizeof(int)) != cudaSuccess) return nullptr; cudaMemset(g_dev_err, 0, sizeof(int)); }
-    return g_dev_err;
+    const int dev = current_device(); if (dev < 0) return nullptr;
+    if (!g_dev_err[dev]) { if (cudaMalloc(&g_dev_err[dev], sizeof(int)) != cudaSuccess) return nullptr; cudaMemset(g_dev_err[dev], 0, sizeof(int)); }
+    return g_dev_err[dev];
 }
-// workspace of the kernel-level GEMV entry point (allocated on first use; the engine owns its own)
-static GemvWorkspace g_ws = {nullptr, 0, nullptr};
+// workspace of the kernel-level GEMV entry point (per device, allocated on first use; the engine owns its own)
+static GemvWorkspace g_ws[MAX_DEVICES] = {};
 int default_gemv_workspace(GemvWorkspace* out, size_t need) {
-    if (need > g_ws.part_bytes) {
-        if (g_ws.part) HP_CUDA(cudaFree(g_ws.part));
-        g_ws.part = nullptr; g_ws.part_bytes = 0;
-        HP_CUDA(cudaMalloc(&g_ws.part, need));
-        g_ws.part_bytes = need;
+    const int dev = current_device();
+    HP_REQUIRE(dev >= 0, "no usable current CUDA device");
+    GemvWorkspace& ws = g_ws[dev];
+    if (need > ws.part_bytes) {
+        if (ws.part) HP_CUDA(cudaFree(ws.part));
+        ws.part = nullptr; ws.part_bytes = 0;
+        HP_CUDA(cudaMalloc(&ws.part, need));
+        ws.part_bytes = need;
     }
-    g_ws.err = device_err_flag();
-    *out = g_ws; return HP_OK;
+    ws.err = device_err_flag();
+    *out = ws; return HP_OK;
 }
 }  // namespace hp
 
@@ -95,7 +99,7 @@ int hp_gemv_q4k_f32(const void* w_dev, const float* x_dev, float* y_dev, int N, 
     HP_GUARD_BEGIN
     HP_REQUIRE(w_dev && x_dev && y_dev, "hp_gemv_q4k_f32: null pointer");
     HP_REQUIRE(((uintptr_t)w_dev & 15) == 0, "hp_gemv_q4k_f32: weights must be 16-byte aligned");
-    return hp::gemv_q4k_f32(w_dev, x_dev, y_dev, N, K, R, (cudaStream_t)stream);
+    return hp::gemv_q4k_f32(w_dev, x_dev, y_dev, N, K, R, hp::device_err_flag(), (cudaStream_t)stream);
     HP_GUARD_END
 }
 size_t hp_argmax_scratch_bytes(int R, int n) { return (R < 1 || n < 1) ? 0 : hp::argmax_scratch_bytes(R, n); }
@@ -142,15 +146,10 @@ int hp_gdn_layer(const float* rows_dev, int ld, int T, int n_replay, int n_qk, i
     HP_REQUIRE(T >= 0 && T <= 8 && n_replay >= 0 && n_replay <= 8 && T + n_replay >= 1, "hp_gdn_layer: 0 <= T, n_replay <= 8 and T + n_replay >= 1");
     HP_REQUIRE((rows_dev || T == 0) && conv_w_dev && dt_bias_bf16_dev && a_neg_bf16_dev && norm_w_bf16_dev && state_dev && conv_state_dev && saved_dev, "hp_gdn_layer: null pointer");
     HP_REQUIRE(n_qk >= 1 && n_v >= n_qk && n_v % n_qk == 0 && ld >= (2 * n_qk + 2 * n_v) * 128 + 2 * n_v, "hp_gdn_layer: bad shape");
-    static int* d_desc = nullptr;   // {r0, T, slot, -} + replay count
-    if (!d_desc) HP_CUDA(cudaMalloc(&d_desc, 8 * sizeof(int)));
-    const int h[5] = {0, T, 0, 0, n_replay};
-    HP_CUDA(cudaMemcpyAsync(d_desc, h, sizeof h, cudaMemcpyHostToDevice, (cudaStream_t)stream));
-    HP_CUDA(cudaStreamSynchronize((cudaStream_t)stream));   // h lives on this stack frame
     hp::GdnParams g; g.rows = rows_dev ? rows_dev : state_dev; g.saved = saved_dev; g.saved_stride = 0; g.ld = ld; g.n_qk = n_qk; g.n_v = n_v;
     g.off_z = (2 * n_qk + n_v) * 128; g.off_b = g.off_z + n_v * 128; g.off_a = g.off_b + n_v;
     g.conv_w = conv_w_dev; g.dt_bias = dt_bias_bf16_dev; g.a_neg = a_neg_bf16_dev; g.norm_w = norm_w_bf16_dev;
-    g.state = state_dev; g.conv_state = conv_state_dev; g.state_stride = 0; g.conv_stride = 0; g.seq = d_desc; g.replay_n = d_desc + 4;
+    g.state = state_dev; g.conv_state = conv_state_dev; g.state_stride = 0; g.conv_stride = 0; g.seq = nullptr; g.replay_n = nullptr; g.imm_T = T; g.imm_replay = n_replay;   // one sequence, described by value
     g.out = out_dev; g.xq = hp::XQ8F{xq_q_dev, xq_sc_dev}; g.snap = snap_dev; g.snap_row_stride = (size_t)n_v * 128 * 128; g.eps = eps; g.sigmoid_gate = sigmoid_gate;
     return hp::gdn_forward(g, 1, (cudaStream_t)stream);
     HP_GUARD_END

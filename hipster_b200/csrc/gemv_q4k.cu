@@ -111,8 +111,6 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
     const uint32_t row_bytes = (uint32_t)nb * 144u;
     constexpr uint32_t unit_bytes = CB * 144u;
     y += (size_t)ct.part * part_stride;
-
-    HP_TRACE_BEGIN();
     pdl_launch_dependents();   // the next kernel may be scheduled; it waits for this one to finish before using its output
     if (lane == 0) {
         for (int s = 0; s < SK_STAGES; ++s) mbar_init(bar0 + 8 * s, 1);
@@ -147,7 +145,6 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
     for (int i = 0; i < SK_STAGES && i < nunits; ++i) issue();
 
     pdl_wait();
-    HP_TRACE_WAITED();
 
     if (warp == 0) {   // quantised activations of blocks [kb0, kb0 + nbp), all NT column tiles, by bulk copies: one block
         // (2048 + 512 B) per copy pair, lanes in parallel, each CTA starting at a different block so that the 148 CTAs do
@@ -304,61 +301,108 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
             }
         store_tile(tile, v);
     }
-    HP_TRACE_END(1000 + N / 16);
 }
 
-// ---- f32-activation baseline: lane l of TPR takes blocks l, l+TPR, ...; xor-shuffle tree (gemv.hip:1177-1216) ----
-template <int TPR, int NCOL>
-__global__ void __launch_bounds__(256) k_gemv_q4k_f32(const uint8_t* __restrict__ W, const float* __restrict__ x, float* __restrict__ y, int N, int K) {
-    constexpr int ROWS = 256 / TPR;
-    const int lane = threadIdx.x % TPR, row = blockIdx.x * ROWS + threadIdx.x / TPR;
-    const int nb = K / 256;
-    const bool live = row < N;
-    const uint8_t* wrow = W + (size_t)(live ? row : 0) * nb * 144;
+// ---- f32-activation GEMV (the arithmetic of the reference's k_gemv_q4_K_f32, gemv.hip:1177-1216, kept as a numerics
+// contract: four partial sums per output row, partial l over blocks l, l+4, ... in order; per 64-element group
+// t = d0*s0 - m0*sx0 + d1*s1 - m1*sx1 with s = fmaf chain over the 32 elements and sx = their serial sum; the four
+// partials combined by the xor tree 2, 1). Structure for sm_100a: one CTA per 32 output rows, thread = (row, partial);
+// the 32 row pieces of a 4-block K chunk and the matching activations arrive by bulk async copies into a 2-stage
+// shared-memory ring (HBM sees 576-byte coalesced row pieces instead of per-thread 16-byte loads strided by the row
+// size), activation blocks padded to 260 floats so that the four partials of a row read distinct banks, and the
+// weight-independent sums sx computed once per chunk for all rows. ----
+constexpr int F32_ROWS = 32, F32_THREADS = 128, F32_XPAD = 260, F32_CHUNK = 4;
+template <int NCOL>
+__global__ void __launch_bounds__(F32_THREADS) k_gemv_q4k_f32(const uint8_t* __restrict__ W, const float* __restrict__ x, float* __restrict__ y, int N, int K, int* __restrict__ err) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t* wst = smem;                                                          // [2][32 rows][4 blocks * 144]
+    float* xst = reinterpret_cast<float*>(smem + 2 * F32_ROWS * F32_CHUNK * 144);  // [2][NCOL][4][260]
+    float* sxs = xst + 2 * NCOL * F32_CHUNK * F32_XPAD;                           // [NCOL][4 blocks * 8 sub-blocks]
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(sxs + NCOL * 32);
+    const int tid = threadIdx.x, r = tid >> 2, l = tid & 3;
+    const int nb = K / 256, nch = (nb + F32_CHUNK - 1) / F32_CHUNK, row0 = blockIdx.x * F32_ROWS, nrows = min(F32_ROWS, N - row0);
+    const uint32_t bar0 = smem_u32(bars);
+    if (tid == 0) { mbar_init(bar0, 1); mbar_init(bar0 + 8, 1); fence_barrier_init(); }
+    __syncthreads();
+    auto issue = [&](int ci) {   // warp 0: one copy per row piece, one per (column, block) of activations
+        if (tid >= 32) return;
+        const int s = ci & 1, b0 = ci * F32_CHUNK, cb = min(F32_CHUNK, nb - b0);
+        const uint32_t bar = bar0 + 8 * s;
+        if (tid == 0) mbar_expect_tx(bar, (uint32_t)(nrows * cb * 144 + NCOL * cb * 1024));
+        __syncwarp();
+        if (tid < nrows) bulk_g2s(smem_u32(wst + (s * F32_ROWS + tid) * F32_CHUNK * 144), W + ((size_t)(row0 + tid) * nb + b0) * 144, (uint32_t)cb * 144u, bar);
+        for (int i = tid; i < NCOL * cb; i += 32) {
+            const int c = i / cb, bl = i - c * cb;
+            bulk_g2s(smem_u32(xst + ((s * NCOL + c) * F32_CHUNK + bl) * F32_XPAD), x + (size_t)c * K + (size_t)(b0 + bl) * 256, 1024u, bar);
+        }
+    };
     float acc[NCOL];
 #pragma unroll
     for (int c = 0; c < NCOL; ++c) acc[c] = 0.f;
-    for (int b = lane; b < nb && live; b += TPR) {
-        const uint4* blk = reinterpret_cast<const uint4*>(wrow + (size_t)b * 144);
-        const uint4 hdr = __ldg(blk);
-        const float d = h2f((uint16_t)(hdr.x & 0xFFFF)), dmin = h2f((uint16_t)(hdr.x >> 16));
+    issue(0);
+    if (nch > 1) issue(1);
+    bool ok = true;
+    for (int ci = 0; ci < nch; ++ci) {
+        const int s = ci & 1, cb = min(F32_CHUNK, nb - ci * F32_CHUNK);
+        ok = __syncthreads_and(mbar_wait(bar0 + 8 * s, (ci >> 1) & 1, err) ? 1 : 0) != 0;
+        if (!ok) break;
+        for (int i = tid; i < NCOL * cb * 8; i += F32_THREADS) {   // sx of (column, block, sub-block): serial sum in element order
+            const int c = i / (cb * 8), rem = i - c * (cb * 8), bl = rem >> 3, k = rem & 7;
+            const float* xp = xst + ((s * NCOL + c) * F32_CHUNK + bl) * F32_XPAD + 32 * k;
+            float a = 0.f;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            uint32_t sc0, mn0, sc1, mn1; q4k_scale_min(hdr, 2 * j, sc0, mn0); q4k_scale_min(hdr, 2 * j + 1, sc1, mn1);
-            const float d0 = d * (float)sc0, m0 = dmin * (float)mn0, d1 = d * (float)sc1, m1 = dmin * (float)mn1;
-            const uint4 qa = __ldg(blk + 1 + 2 * j), qb = __ldg(blk + 2 + 2 * j);
-            const uint32_t qw[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+            for (int e = 0; e < 32; ++e) a = a + xp[e];
+            sxs[c * 32 + bl * 8 + k] = a;
+        }
+        __syncthreads();
+        if (r < nrows && l < cb) {
+            const uint8_t* blk = wst + (s * F32_ROWS + r) * F32_CHUNK * 144 + l * 144;
+            const uint4 hdr = *reinterpret_cast<const uint4*>(blk);
+            const float d = h2f((uint16_t)(hdr.x & 0xFFFF)), dmin = h2f((uint16_t)(hdr.x >> 16));
 #pragma unroll
-            for (int c = 0; c < NCOL; ++c) {
-                const float* xc = x + (size_t)c * K + (size_t)b * 256 + 64 * j;
-                float s0 = 0.f, s1 = 0.f, sx0 = 0.f, sx1 = 0.f;
+            for (int j = 0; j < 4; ++j) {
+                uint32_t sc0, mn0, sc1, mn1; q4k_scale_min(hdr, 2 * j, sc0, mn0); q4k_scale_min(hdr, 2 * j + 1, sc1, mn1);
+                const float d0 = d * (float)sc0, m0 = dmin * (float)mn0, d1 = d * (float)sc1, m1 = dmin * (float)mn1;
+                const uint4 qa = *reinterpret_cast<const uint4*>(blk + 16 + 32 * j), qb = *reinterpret_cast<const uint4*>(blk + 32 + 32 * j);
+                const uint32_t qw[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
 #pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    const uint32_t q = (qw[e >> 2] >> (8 * (e & 3))) & 0xFFu;
-                    const float x0 = __ldg(xc + e), x1 = __ldg(xc + 32 + e);
-                    s0 = fmaf(x0, (float)(q & 0xFu), s0); s1 = fmaf(x1, (float)(q >> 4), s1);
-                    sx0 = sx0 + x0; sx1 = sx1 + x1;
+                for (int c = 0; c < NCOL; ++c) {
+                    const float* xc = xst + ((s * NCOL + c) * F32_CHUNK + l) * F32_XPAD + 64 * j;
+                    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+                    for (int e4 = 0; e4 < 8; ++e4) {
+                        const float4 x0 = *reinterpret_cast<const float4*>(xc + 4 * e4), x1 = *reinterpret_cast<const float4*>(xc + 32 + 4 * e4);
+                        const uint32_t q = qw[e4];
+                        s0 = fmaf(x0.x, (float)(q & 0xFu), s0); s1 = fmaf(x1.x, (float)((q >> 4) & 0xFu), s1);
+                        s0 = fmaf(x0.y, (float)((q >> 8) & 0xFu), s0); s1 = fmaf(x1.y, (float)((q >> 12) & 0xFu), s1);
+                        s0 = fmaf(x0.z, (float)((q >> 16) & 0xFu), s0); s1 = fmaf(x1.z, (float)((q >> 20) & 0xFu), s1);
+                        s0 = fmaf(x0.w, (float)((q >> 24) & 0xFu), s0); s1 = fmaf(x1.w, (float)(q >> 28), s1);
+                    }
+                    const float sx0 = sxs[c * 32 + l * 8 + 2 * j], sx1 = sxs[c * 32 + l * 8 + 2 * j + 1];
+                    float tt = d0 * s0; tt = tt - m0 * sx0; tt = tt + d1 * s1; tt = tt - m1 * sx1;
+                    acc[c] = acc[c] + tt;
                 }
-                float tt = d0 * s0; tt = tt - m0 * sx0; tt = tt + d1 * s1; tt = tt - m1 * sx1;
-                acc[c] = acc[c] + tt;
             }
         }
+        __syncthreads();   // the stage and sxs are free again
+        if (ci + 2 < nch) issue(ci + 2);
     }
+    if (!ok) return;
 #pragma unroll
-    for (int c = 0; c < NCOL; ++c)
-#pragma unroll
-        for (int off = TPR / 2; off > 0; off >>= 1) acc[c] = acc[c] + __shfl_xor_sync(0xffffffffu, acc[c], off, TPR);
-    if (lane == 0 && live)
-#pragma unroll
-        for (int c = 0; c < NCOL; ++c) y[(size_t)c * N + row] = acc[c];
+    for (int c = 0; c < NCOL; ++c) {
+        acc[c] = acc[c] + __shfl_xor_sync(0xffffffffu, acc[c], 2);
+        acc[c] = acc[c] + __shfl_xor_sync(0xffffffffu, acc[c], 1);
+        if (l == 0 && r < nrows) y[(size_t)c * N + row0 + r] = acc[c];
+    }
 }
 
 template <int NT, int CB, bool TILED>
 int launch_sk2(const uint8_t* W, const void* xq, const void* xsc, float* y, int N, int nb, int P, int R, int ldy, size_t part_stride,
                int* err, cudaStream_t s, bool pdl) {
     const size_t smem = SkGeom<CB, TILED>::FIXED + (size_t)NT * (nb / P) * 2560;
-    static size_t attr_smem = 0;
-    if (smem > attr_smem) { HP_CUDA(cudaFuncSetAttribute(k_gemv_q4k_sk<NT, CB, TILED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr_smem = smem; }
+    static size_t attr_smem[MAX_DEVICES] = {};   // per device: the opt-in belongs to the device's copy of the kernel
+    const int dev = current_device(); if (dev < 0) return HP_ECUDA;
+    if (smem > attr_smem[dev]) { HP_CUDA(cudaFuncSetAttribute(k_gemv_q4k_sk<NT, CB, TILED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr_smem[dev] = smem; }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(GEMV_NCTA); cfg.blockDim = dim3(SK_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = s;
     cudaLaunchAttribute at[1]; at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
@@ -402,7 +446,6 @@ __global__ void k_reduce_parts(const float* __restrict__ parts, size_t part_stri
 }
 
 }  // namespace
-HP_TRACE_READER(hp_debug_trace_gemv)
 
 int gemv_parts(int N, int K) { return gemv_num_parts(N, K / 256); }
 
@@ -453,16 +496,27 @@ int gemv_q4k_q8(const void* W, const XQ8F& x, float* y, int N, int K, int R, int
     return HP_OK;
 }
 
-int gemv_q4k_f32(const void* W, const float* x, float* y, int N, int K, int R, cudaStream_t s) {
-    HP_REQUIRE(K > 0 && K % 256 == 0, "gemv_q4k_f32: K=%d must be a positive multiple of 256", K);
-    HP_REQUIRE(N > 0 && R >= 1 && R <= 8, "gemv_q4k_f32: bad shape N=%d R=%d (R <= 8)", N, R);
-    constexpr int TPR = 4; const int grid = (N + 256 / TPR - 1) / (256 / TPR);
-#define HP_F32(NC) k_gemv_q4k_f32<TPR, NC><<<grid, 256, 0, s>>>((const uint8_t*)W, x, y, N, K)
-    switch (R) { case 1: HP_F32(1); break; case 2: HP_F32(2); break; case 3: HP_F32(3); break; case 4: HP_F32(4); break;
-                 case 5: HP_F32(5); break; case 6: HP_F32(6); break; case 7: HP_F32(7); break; default: HP_F32(8); break; }
-#undef HP_F32
+template <int NCOL>
+static int launch_f32(const uint8_t* W, const float* x, float* y, int N, int K, int* err, cudaStream_t s) {
+    const size_t smem = (size_t)2 * F32_ROWS * F32_CHUNK * 144 + (size_t)2 * NCOL * F32_CHUNK * F32_XPAD * 4 + (size_t)NCOL * 32 * 4 + 16;
+    static bool attr[MAX_DEVICES] = {};
+    const int dev = current_device(); if (dev < 0) return HP_ECUDA;
+    if (!attr[dev]) { HP_CUDA(cudaFuncSetAttribute(k_gemv_q4k_f32<NCOL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr[dev] = true; }
+    k_gemv_q4k_f32<NCOL><<<(N + F32_ROWS - 1) / F32_ROWS, F32_THREADS, smem, s>>>(W, x, y, N, K, err);
     HP_CUDA(cudaGetLastError());
     return HP_OK;
+}
+int gemv_q4k_f32(const void* W, const float* x, float* y, int N, int K, int R, int* err, cudaStream_t s) {
+    HP_REQUIRE(K > 0 && K % 256 == 0, "gemv_q4k_f32: K=%d must be a positive multiple of 256", K);
+    HP_REQUIRE(N > 0 && R >= 1 && R <= 8, "gemv_q4k_f32: bad shape N=%d R=%d (R <= 8)", N, R);
+    HP_REQUIRE(((uintptr_t)x & 15) == 0, "gemv_q4k_f32: activations must be 16-byte aligned");
+    const uint8_t* w = (const uint8_t*)W;
+    switch (R) {
+        case 1: return launch_f32<1>(w, x, y, N, K, err, s); case 2: return launch_f32<2>(w, x, y, N, K, err, s);
+        case 3: return launch_f32<3>(w, x, y, N, K, err, s); case 4: return launch_f32<4>(w, x, y, N, K, err, s);
+        case 5: return launch_f32<5>(w, x, y, N, K, err, s); case 6: return launch_f32<6>(w, x, y, N, K, err, s);
+        case 7: return launch_f32<7>(w, x, y, N, K, err, s); default: return launch_f32<8>(w, x, y, N, K, err, s);
+    }
 }
 
 }  // namespace hp

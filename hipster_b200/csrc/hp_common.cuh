@@ -150,24 +150,6 @@ __device__ __forceinline__ void st_cluster_f32(float* local_smem, uint32_t rank,
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local_smem)), "r"(rank));
     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }
-// Optional in-kernel tracer (variant builds with -DHP_TRACE only): block 0 thread 0 of every instrumented kernel appends
-// {kernel id, start, after the dependency wait, end} in global-timer nanoseconds to a per-source-file ring.
-#ifdef HP_TRACE
-static __device__ unsigned long long g_trace[4096 * 4];
-static __device__ unsigned int g_trace_n;
-__device__ __forceinline__ unsigned long long hp_gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-#define HP_TRACE_BEGIN() unsigned long long _tr0 = 0, _tr1 = 0; const bool _tr = threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0; if (_tr) _tr0 = hp_gtime()
-#define HP_TRACE_WAITED() do { if (_tr) _tr1 = hp_gtime(); } while (0)
-#define HP_TRACE_END(id) do { if (_tr) { const unsigned _i = atomicAdd(&g_trace_n, 1u) & 4095u; g_trace[4 * _i] = (id); g_trace[4 * _i + 1] = _tr0; g_trace[4 * _i + 2] = _tr1; g_trace[4 * _i + 3] = hp_gtime(); } } while (0)
-#define HP_TRACE_READER(name) extern "C" int name(unsigned long long* out, unsigned int* n) { \
-    if (cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace)) != cudaSuccess) return 1; \
-    if (cudaMemcpyFromSymbol(n, g_trace_n, 4) != cudaSuccess) return 1; unsigned int z = 0; return (int)cudaMemcpyToSymbol(g_trace_n, &z, 4); }
-#else
-#define HP_TRACE_BEGIN() do { } while (0)
-#define HP_TRACE_WAITED() do { } while (0)
-#define HP_TRACE_END(id) do { } while (0)
-#define HP_TRACE_READER(name)
-#endif
 // programmatic dependent launch (no-ops when the kernel was not launched with the attribute)
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

@@ -10,19 +10,16 @@ namespace hp {
 // Quantised activations in the fragment-major layout described in hp_common.cuh (reference: struct XQ8, gemv.h:8).
 struct XQ8F { void* q; void* sc; };
 
-// device status word (set by kernels whose bounded waits gave up); nullptr if it cannot be allocated
+// Per-device library state is kept in tables indexed by the device ordinal (a process may drive several GPUs).
+constexpr int MAX_DEVICES = 64;
+inline int current_device() { int d = -1; return (cudaGetDevice(&d) == cudaSuccess && d >= 0 && d < MAX_DEVICES) ? d : -1; }
+// device status word of the current device (set by kernels whose bounded waits gave up); nullptr if it cannot be allocated
 int* device_err_flag();
 
 // ---- gemv_q4k.cu ----
 // Work partition of the tensor-core GEMV. It is part of the numerics contract (it fixes the fp32 summation order)
 // and depends on the tensor shape only.
-#ifndef HP_GEMV_WARPS
-#define HP_GEMV_WARPS 12
-#endif
-#ifndef HP_GEMV_STAGES
-#define HP_GEMV_STAGES 2
-#endif
-constexpr int GEMV_NCTA = 148, GEMV_WARPS = HP_GEMV_WARPS, GEMV_STAGES = HP_GEMV_STAGES;
+constexpr int GEMV_NCTA = 148, GEMV_WARPS = 12, GEMV_STAGES = 2;
 constexpr int GEMV_SMEM_LIMIT = 227 * 1024, GEMV_MAX_PART_BLOCKS = 36;
 // number of K parts: P in {1, 2, 4} dividing K/256 with at most 36 blocks per part, maximising
 //   1000 * tiles / (ctas_per_part * ceil(tiles / ctas_per_part)) - 20 * log2(P) - (50 if K/256/P is odd)
@@ -57,7 +54,7 @@ int gemv_q4k_q8_parts(const void* W, const XQ8F& x, float* yparts, int N, int K,
 size_t gemv_tiled_bytes(int N, int K);
 int gemv_repack_tiled(const void* src, void* dst, int N, int K, cudaStream_t s);
 int gemv_q4k_q8(const void* W, const XQ8F& x, float* y, int N, int K, int R, int ldy, const GemvWorkspace& ws, cudaStream_t s, bool pdl);
-int gemv_q4k_f32(const void* W, const float* x, float* y, int N, int K, int R, cudaStream_t s);
+int gemv_q4k_f32(const void* W, const float* x, float* y, int N, int K, int R, int* err, cudaStream_t s);
 
 // ---- quant_ops.cu ----
 int quantize_x_q8(const float* x, int ldx, XQ8F out, int R, int K, cudaStream_t s);
@@ -79,7 +76,8 @@ struct GdnParams {
     const float* rows; float* saved; size_t saved_stride; int ld, off_z, off_b, off_a, n_qk, n_v;
     const float* conv_w; const void* dt_bias; const void* a_neg; const void* norm_w;
     float* state; float* conv_state; size_t state_stride, conv_stride;
-    const int* seq; const int* replay_n;
+    const int* seq; const int* replay_n;                 // device descriptors; seq == nullptr: one sequence {r0 = 0, T = imm_T, slot 0} with imm_replay rows to commit
+    int imm_T = 0, imm_replay = 0;
     float* out; XQ8F xq; float* snap; size_t snap_row_stride; float eps; int sigmoid_gate;
 };
 int gdn_forward(const GdnParams& p, int nseq, cudaStream_t s);

@@ -45,10 +45,7 @@ __global__ void __launch_bounds__(256) k_embed_bf16(const int* __restrict__ tok,
 // Sum of squares: per-thread fmaf chain over its elements in index order, xor tree inside each warp, then the 40 warp
 // sums (warp index over the cluster) added in order by every thread after the cluster barrier. Quantisation: a
 // 32-element sub-block is held by 8 consecutive lanes.
-#ifndef HP_NORM_CL
-#define HP_NORM_CL 4
-#endif
-constexpr int NORM_CL = HP_NORM_CL, NORM_TPB = 1280 / HP_NORM_CL, NORM_ROWT = NORM_CL * NORM_TPB, NORM_NW = NORM_ROWT / 32, NORM_MAXG = 2;   // rows of up to 10240 elements
+constexpr int NORM_CL = 4, NORM_TPB = 1280 / NORM_CL, NORM_ROWT = NORM_CL * NORM_TPB, NORM_NW = NORM_ROWT / 32, NORM_MAXG = 2;   // rows of up to 10240 elements
 // warp part of the cluster-wide sum: leaves this warp's sum in slot (10 * rank + warp) of every CTA's table
 __device__ __forceinline__ void norm_publish(float v, float* tab, int rank) {
 #pragma unroll
@@ -88,7 +85,6 @@ __global__ void __cluster_dims__(NORM_CL, 1, 1) __launch_bounds__(NORM_TPB) k_ad
                                                                      const uint16_t* __restrict__ w, float* __restrict__ xn, int8_t* __restrict__ q, float* __restrict__ sc,
                                                                      int n, float eps, int assign, const float* __restrict__ slotw, int nslot) {
     __shared__ float tab[NORM_NW];
-    HP_TRACE_BEGIN();
     pdl_launch_dependents();
     cluster_arrive_relaxed();   // matched by cluster_wait() before the first store into another CTA
     const int rank = blockIdx.x % NORM_CL, r = blockIdx.x / NORM_CL, lane = threadIdx.x & 31, t = rank * NORM_TPB + threadIdx.x;
@@ -97,7 +93,6 @@ __global__ void __cluster_dims__(NORM_CL, 1, 1) __launch_bounds__(NORM_TPB) k_ad
 #pragma unroll
     for (int k = 0; k < NG; ++k) { const int i = 4 * (t + k * NORM_ROWT); if (i < n) bf4(w + i, wv[k]); }   // weights do not depend on the previous kernel
     pdl_wait();
-    HP_TRACE_WAITED();
     float4 v[NG];
 #pragma unroll
     for (int k = 0; k < NG; ++k) { const int i = 4 * (t + k * NORM_ROWT); v[k] = (i < n && !assign) ? *reinterpret_cast<const float4*>(xr + i) : make_float4(0.f, 0.f, 0.f, 0.f); }
@@ -162,7 +157,6 @@ __global__ void __cluster_dims__(NORM_CL, 1, 1) __launch_bounds__(NORM_TPB) k_ad
         if (live && xn) *reinterpret_cast<float4*>(xn + (size_t)r * n + i) = make_float4(o[0], o[1], o[2], o[3]);
         quant4_store(o, r, i, n, q, sc, lane, live);
     }
-    HP_TRACE_END(2);
 }
 
 // ---- MTP input: out[r] = [rmsnorm(a[r]) * wa | rmsnorm(b[r]) * wb], quantised (ops.hip:99-116) ----
@@ -214,17 +208,14 @@ __global__ void __cluster_dims__(NORM_CL, 1, 1) __launch_bounds__(NORM_TPB) k_no
 // ---- xq = q8(silu(gate) * up); gate = columns [0, F), up = [F, 2F) of gu [R][ldg] (ops.hip:146-151) ----
 // one thread per 4 consecutive features (128-bit loads), 8 consecutive lanes per 32-element sub-block
 __global__ void __launch_bounds__(256) k_silu_mul_quant(const float* __restrict__ gu, int ldg, int F, int8_t* __restrict__ q, float* __restrict__ sc) {
-    HP_TRACE_BEGIN();
     pdl_launch_dependents();
     pdl_wait();
-    HP_TRACE_WAITED();
     const int r = blockIdx.y, i = (blockIdx.x * 256 + threadIdx.x) * 4, lane = threadIdx.x & 31;
     const bool live = i < F;   // F is a multiple of 32: the 8 lanes of a sub-block are live together
     const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
     const float4 g = live ? *reinterpret_cast<const float4*>(gu + (size_t)r * ldg + i) : z4, u = live ? *reinterpret_cast<const float4*>(gu + (size_t)r * ldg + F + i) : z4;
     const float o[4] = {silu_det(g.x) * u.x, silu_det(g.y) * u.y, silu_det(g.z) * u.z, silu_det(g.w) * u.w};
     quant4_store(o, r, i, F, q, sc, lane, live);
-    HP_TRACE_END(3);
 }
 
 // ---- Gated DeltaNet: causal 4-tap depthwise conv + SiLU, then the gated delta rule, for one (v-head, sequence) ----
@@ -252,6 +243,7 @@ struct GdnArgs {
     float* state; float* conv_state; size_t state_stride, conv_stride;   // per slot: [n_v][128][128], [n_v][3][384] (each v-head keeps its own q|k|v history)
     const int* seq;                                               // device descriptors: per sequence {r0, T, slot, -}
     const int* replay_n;                                          // device: rows of the previous pass to commit, per slot
+    int imm_T, imm_replay;                                        // used instead when seq == nullptr (a single sequence described by value)
     float* out; int8_t* oq; float* osc;                           // out f32 [rows][n_v*128] (nullable), quantised out
     float* snap; size_t snap_row_stride;                          // optional state snapshots after each new row
     float eps; int sigmoid_gate;
@@ -276,7 +268,6 @@ __global__ void __cluster_dims__(GDN_CL, 1, 1) __launch_bounds__(256) k_gdn(GdnA
     __shared__ float raw[GDN_MAXROWS + 3][96], sv[GDN_MAXROWS][32], sout[8][32];
     __shared__ float csum[GDN_MAXROWS][2][GDN_CL], snrm[GDN_MAXROWS][2], sbeta[GDN_MAXROWS], sdecay[GDN_MAXROWS];
     __shared__ float cred[8][GDN_CL];
-    HP_TRACE_BEGIN();
     pdl_launch_dependents();
     cluster_arrive_relaxed();   // matched by cluster_wait() before the first store into another CTA: every CTA has started by then
     const int rank = blockIdx.x % GDN_CL, h = blockIdx.x / GDN_CL, hk = h % a.n_qk, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -294,8 +285,7 @@ __global__ void __cluster_dims__(GDN_CL, 1, 1) __launch_bounds__(256) k_gdn(GdnA
     }
     const float nw = bf2f(a.norm_w[32 * rank + lane]);
     pdl_wait();
-    HP_TRACE_WAITED();
-    const int r0 = a.seq[blockIdx.y * 4 + 0], T = min(a.seq[blockIdx.y * 4 + 1], 8), slot = a.seq[blockIdx.y * 4 + 2];
+    const int r0 = a.seq ? a.seq[blockIdx.y * 4 + 0] : 0, T = min(a.seq ? a.seq[blockIdx.y * 4 + 1] : a.imm_T, 8), slot = a.seq ? a.seq[blockIdx.y * 4 + 2] : 0;
     float* sav = a.saved + (size_t)slot * a.saved_stride + (size_t)h * 8 * 388;   // [8][q 128 | k 128 | v 128 | beta | alpha | pad]
     const int jl = tid >> 3, ck = tid & 7, j = 32 * rank + jl;
     float* Mrow = a.state + (size_t)slot * a.state_stride + ((size_t)h * D + j) * D + 16 * ck;
@@ -322,7 +312,7 @@ __global__ void __cluster_dims__(GDN_CL, 1, 1) __launch_bounds__(256) k_gdn(GdnA
         const int rr = e_rr[k];
         if (rr < T + 3) tmpa[k] = rr < 3 ? cst[rr * 384 + e_slot[k]] : a.rows[(size_t)(r0 + rr - 3) * a.ld + e_col[k]];
     }
-    const int nrep = a.replay_n ? min(a.replay_n[slot], 8) : 0;
+    const int nrep = min(a.seq ? (a.replay_n ? a.replay_n[slot] : 0) : a.imm_replay, 8);
     const int nrows = nrep + T;
 #pragma unroll
     for (int k = 0; k < NLB; ++k) { const int it = e_rr[k]; if (it < nrep) tmpb[k] = sav[it * 388 + e_slot[k]]; }
@@ -443,7 +433,6 @@ __global__ void __cluster_dims__(GDN_CL, 1, 1) __launch_bounds__(256) k_gdn(GdnA
         if (a.out) a.out[oi] = v;
         if (a.oq) warp_quant32_store(v, row, (h * D + c) >> 5, Z, a.oq, a.osc, lane);
     }
-    HP_TRACE_END(4);
 }
 
 }  // namespace
@@ -482,14 +471,13 @@ int silu_mul_quant(const float* gu, int ldg, int F, XQ8F xq, int R, cudaStream_t
     launch_pdl<256>(k_silu_mul_quant, dim3((F / 4 + 255) / 256, R), dim3(256), 0, s, gu, ldg, F, (int8_t*)xq.q, (float*)xq.sc);
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
-HP_TRACE_READER(hp_debug_trace_ops)
 int gdn_forward(const GdnParams& p, int nseq, cudaStream_t s) {
     HP_REQUIRE(nseq >= 1 && nseq <= 8 && p.n_qk >= 1 && p.n_v >= p.n_qk, "gdn_forward: bad shape");
     GdnArgs a;
     a.rows = p.rows; a.saved = p.saved; a.saved_stride = p.saved_stride; a.ld = p.ld; a.off_z = p.off_z; a.off_b = p.off_b; a.off_a = p.off_a;
     a.n_qk = p.n_qk; a.n_v = p.n_v; a.conv_w = p.conv_w; a.dt_bias = (const uint16_t*)p.dt_bias; a.a_neg = (const uint16_t*)p.a_neg; a.norm_w = (const uint16_t*)p.norm_w;
     a.state = p.state; a.conv_state = p.conv_state; a.state_stride = p.state_stride; a.conv_stride = p.conv_stride;
-    a.seq = p.seq; a.replay_n = p.replay_n; a.out = p.out; a.oq = (int8_t*)p.xq.q; a.osc = (float*)p.xq.sc;
+    a.seq = p.seq; a.replay_n = p.replay_n; a.imm_T = p.imm_T; a.imm_replay = p.imm_replay; a.out = p.out; a.oq = (int8_t*)p.xq.q; a.osc = (float*)p.xq.sc;
     a.snap = p.snap; a.snap_row_stride = p.snap_row_stride; a.eps = p.eps; a.sigmoid_gate = p.sigmoid_gate;
     HP_CUDA(launch_pdl<128>(k_gdn, dim3(p.n_v * GDN_CL, nseq), dim3(256), 0, s, a));
     HP_CUDA(cudaGetLastError()); return HP_OK;
