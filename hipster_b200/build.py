@@ -55,15 +55,32 @@ def build(verbose=False, force=False):
             with open(o + ".ptxas.txt", "w") as f:
                 f.write(r.stderr)
     if force or _stale(LIB, objs):
-        extra = []
-        if any("nccl" in open(os.path.join(CSRC, s)).read() for s in sources()):
-            extra = ["-lnccl"]
-        cmd = [nvcc, "-shared", "-o", LIB] + objs + ["-cudart", "static"] + extra
+        # NCCL is loaded with dlopen at run time (expert parallelism only): nothing but libdl is linked for it
+        cmd = [nvcc, "-shared", "-o", LIB] + objs + ["-cudart", "static", "-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True, env=env)
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)
             raise RuntimeError("link failed")
+    build_driver(force)
     return LIB
+
+
+DRIVER_SRC = os.path.join(HERE, "driver", "spec_driver.cpp")
+DRIVER = os.path.join(HERE, "driver", "spec_driver")
+
+
+def build_driver(force=False):
+    """The C++ MTP driver: compiled against include/hipster_b200.h and linked with libhipster_b200.so only."""
+    if not (force or _stale(DRIVER, [DRIVER_SRC, LIB, os.path.join(HERE, "..", "include", "hipster_b200.h")])):
+        return DRIVER
+    cxx = shutil.which("g++") or "g++"
+    cmd = [cxx, "-O2", "-std=c++17", "-I", os.path.join(HERE, "..", "include"), DRIVER_SRC, "-o", DRIVER,
+           "-L", HERE, "-lhipster_b200", "-Wl,-rpath,$ORIGIN/.."]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout + r.stderr)
+        raise RuntimeError("building the C++ driver failed")
+    return DRIVER
 
 
 if __name__ == "__main__":

@@ -52,6 +52,46 @@ __global__ void __launch_bounds__(256) k_argmax_final(const float* __restrict__ 
     am_block_reduce(bv, bi, sv, si);
     if (threadIdx.x == 0) { ids[r] = bi; if (vals) vals[r] = bv; }
 }
+// ---- top-k per row (k <= TOPK_MAX), values descending, ties -> lower index (reference k_topk, ops.hip:702-716: k rounds
+// of a masked arg-max). Stage 1: each block holds a chunk of the row in shared memory and extracts the chunk's own top k by
+// k rounds of a block arg-max, masking each winner; stage 2 merges the np * k candidates of a row the same way. The k
+// largest of the row are among the k largest of every chunk, so the result equals k rounds over the whole row.
+constexpr int TOPK_MAX = 32;
+__global__ void __launch_bounds__(256) k_topk_part(const float* __restrict__ x, int n, int ld, int k, float* __restrict__ pv, int* __restrict__ pi) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float buf[AM_CHUNK]; __shared__ float sv[8]; __shared__ int si[8]; __shared__ int s_win;
+    const int r = blockIdx.y, c0 = blockIdx.x * AM_CHUNK, cn = min(n - c0, AM_CHUNK);
+    const float* xr = x + (size_t)r * ld + c0;
+    for (int i = threadIdx.x; i < cn; i += 256) buf[i] = xr[i];
+    __syncthreads();
+    for (int rd = 0; rd < k; ++rd) {
+        float bv = -INFINITY; int bi = -1;
+        for (int i = threadIdx.x; i < cn; i += 256) { const float v = buf[i]; if (v > bv) { bv = v; bi = c0 + i; } }
+        am_block_reduce(bv, bi, sv, si);
+        if (threadIdx.x == 0) { const size_t o = ((size_t)r * gridDim.x + blockIdx.x) * k + rd; pv[o] = bv; pi[o] = bi; s_win = bi; }
+        __syncthreads();
+        if (threadIdx.x == 0 && s_win >= 0) buf[s_win - c0] = -INFINITY;   // taken (an entry equal to -inf is never selected, as in the reference)
+        __syncthreads();
+    }
+}
+__global__ void __launch_bounds__(256) k_topk_final(const float* __restrict__ pv, const int* __restrict__ pi, int nc, int k, int* __restrict__ ids, float* __restrict__ vals) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float cv[64 * TOPK_MAX]; __shared__ int ci[64 * TOPK_MAX]; __shared__ float sv[8]; __shared__ int si[8]; __shared__ int s_win;
+    const int r = blockIdx.x;
+    for (int i = threadIdx.x; i < nc; i += 256) { cv[i] = pv[(size_t)r * nc + i]; ci[i] = pi[(size_t)r * nc + i]; }
+    __syncthreads();
+    for (int rd = 0; rd < k; ++rd) {
+        float bv = -INFINITY; int bi = -1;
+        for (int i = threadIdx.x; i < nc; i += 256) if (ci[i] >= 0) am_better(bv, bi, cv[i], ci[i]);
+        am_block_reduce(bv, bi, sv, si);
+        if (threadIdx.x == 0) { ids[(size_t)r * k + rd] = bi; if (vals) vals[(size_t)r * k + rd] = bv; s_win = bi; }
+        __syncthreads();
+        for (int i = threadIdx.x; i < nc; i += 256) if (ci[i] == s_win) ci[i] = -1;   // taken
+        __syncthreads();
+    }
+}
 // out[0] = mm (accepted drafts), out[1] = bonus token ids[mm]
 __global__ void k_accept(const int* __restrict__ ids, const int* __restrict__ drafts, int n_draft, int* __restrict__ out) {
     if (threadIdx.x == 0 && blockIdx.x == 0) {
@@ -77,6 +117,18 @@ int argmax_rows(const float* logits, int R, int n, int ld, int* ids, float* vals
     float* pv = (float*)scratch; int* pi = (int*)(pv + (size_t)R * np);
     HP_CUDA(launch_pdl<1>(k_argmax_part, dim3(np, R), dim3(256), 0, s, logits, n, ld, pv, pi));
     HP_CUDA(launch_pdl<1>(k_argmax_final, dim3(R), dim3(256), 0, s, pv, pi, np, ids, vals));
+    HP_CUDA(cudaGetLastError());
+    return HP_OK;
+}
+size_t topk_scratch_bytes(int R, int n, int k) { return (size_t)R * ((n + AM_CHUNK - 1) / AM_CHUNK) * k * 8; }
+int topk_max_k() { return TOPK_MAX; }
+int topk_rows(const float* logits, int R, int n, int ld, int k, int* ids, float* vals, void* scratch, cudaStream_t s) {
+    HP_REQUIRE(R >= 1 && n >= 1 && ld >= n && scratch && ids, "topk_rows: bad arguments R=%d n=%d ld=%d", R, n, ld);
+    const int np = (n + AM_CHUNK - 1) / AM_CHUNK;
+    HP_REQUIRE(k >= 1 && k <= TOPK_MAX && k <= n && np <= 64, "topk_rows: k=%d must be in 1..%d (and the row at most %d entries)", k, TOPK_MAX, 64 * AM_CHUNK);
+    float* pv = (float*)scratch; int* pi = (int*)(pv + (size_t)R * np * k);
+    HP_CUDA(launch_pdl<1>(k_topk_part, dim3(np, R), dim3(256), 0, s, logits, n, ld, k, pv, pi));
+    HP_CUDA(launch_pdl<1>(k_topk_final, dim3(R), dim3(256), 0, s, (const float*)pv, (const int*)pi, np * k, k, ids, vals));
     HP_CUDA(cudaGetLastError());
     return HP_OK;
 }

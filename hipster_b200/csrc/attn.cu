@@ -12,6 +12,7 @@
 // fp32 is affordable, and it avoids the tensor-core rounding hazard the reference documents (docs/decode-27b.md:117-126).
 #include "hp_common.cuh"
 #include "kernels.h"
+#include <algorithm>
 
 namespace hp {
 namespace {
@@ -232,6 +233,13 @@ __global__ void __launch_bounds__(256) k_attn_merge(const float* __restrict__ qk
     if (oq) warp_quant32_store(v, r, (head * HD + d) >> 5, n_head * HD, oq, osc, d & 31);
 }
 
+// descriptors of one sequence of R consecutive rows at pos0.. (slot 0), cut into row groups of gr rows
+__global__ void k_attn_desc(int* __restrict__ d, int R, int pos0, int gr) {
+    const int t = threadIdx.x; if (t >= R) return;
+    d[t] = pos0 + t; d[32 + t] = 0; d[64 + t] = t / gr;
+    if (t % gr == 0) { int* g = d + 96 + 4 * (t / gr); g[0] = t; g[1] = min(gr, R - t); g[2] = 0; g[3] = pos0 + t; }
+}
+
 }  // namespace
 
 size_t attn_smem_bytes() { return (size_t)MAXP * HD * 4 + (size_t)SPL * MAXP * 4 + 2 * (size_t)SPL * KSTRIDE * 2; }
@@ -262,4 +270,31 @@ int attn_decode(const AttnParams& p, int rows, int ngroups, cudaStream_t s) {
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 
+}  // namespace hp
+
+namespace hp {
+// Kernel-level form for one sequence: rows r = 0..R-1 at positions pos0 + r. The workspace holds the device-side
+// descriptors (256 ints) followed by the split partials.
+static int attn_seq_groups(int R, int n_head, int n_kv) { const int gr = std::max(1, std::min(8, ATTN_MAX_PAIRS / (n_head / n_kv))); return (R + gr - 1) / gr; }
+size_t attn_seq_workspace_bytes(int R, int n_head, int n_kv, int max_ctx) {
+    const size_t np = attn_partial_floats(attn_seq_groups(R, n_head, n_kv), n_kv, (max_ctx + ATTN_SPLIT - 1) / ATTN_SPLIT);
+    return 1024 + np * (HD + 2) * sizeof(float);
+}
+int attn_decode_seq(float* qkv, int ld, int R, int pos0, int n_head, int n_kv, int n_rot, const void* q_norm, const void* k_norm, const void* rope, void* kc, void* vc, int max_ctx,
+                    float* out, XQ8F xq, float eps, void* workspace, cudaStream_t s) {
+    HP_REQUIRE(R >= 1 && R <= 8 && pos0 >= 0 && pos0 + R <= max_ctx, "attn_decode_seq: 1 <= R <= 8 rows inside the context");
+    HP_REQUIRE(n_kv >= 1 && n_head % n_kv == 0 && n_head / n_kv <= ATTN_MAX_PAIRS && ld >= n_head * 512 + 2 * n_kv * HD, "attn_decode_seq: bad head geometry");
+    const int gr = std::max(1, std::min(8, ATTN_MAX_PAIRS / (n_head / n_kv))), ng = attn_seq_groups(R, n_head, n_kv);
+    int* d = (int*)workspace;
+    k_attn_desc<<<1, 32, 0, s>>>(d, R, pos0, gr);
+    HP_CUDA(cudaGetLastError());
+    AttnParams p; p.qkv = qkv; p.ld = ld; p.n_head = n_head; p.n_kv = n_kv; p.n_rot = n_rot; p.q_norm = q_norm; p.k_norm = k_norm; p.rope = rope;
+    p.row_pos = d; p.row_slot = d + 32; p.row_group = d + 64; p.groups = d + 96;
+    p.kc = kc; p.vc = vc; p.kv_stride = 0; p.max_ctx = max_ctx; p.nsplit_max = (max_ctx + ATTN_SPLIT - 1) / ATTN_SPLIT;
+    const size_t np = attn_partial_floats(ng, n_kv, p.nsplit_max);
+    p.pO = (float*)((char*)workspace + 1024); p.pm = p.pO + np * HD; p.pl = p.pm + np;
+    p.out = out; p.xq = xq; p.eps = eps;
+    const int rc = attn_rope_kv(p, R, s);
+    return rc != HP_OK ? rc : attn_decode(p, R, ng, s);
+}
 }  // namespace hp

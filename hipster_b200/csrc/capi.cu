@@ -155,6 +155,60 @@ int hp_gdn_layer(const float* rows_dev, int ld, int T, int n_replay, int n_qk, i
     HP_GUARD_END
 }
 
+size_t hp_attn_workspace_bytes(int R, int n_head, int n_kv, int max_ctx) {
+    return (R < 1 || n_kv < 1 || n_head < n_kv || max_ctx < 1) ? 0 : hp::attn_seq_workspace_bytes(R, n_head, n_kv, max_ctx);
+}
+int hp_attn_decode(float* qkv_dev, int ld, int R, int pos0, int n_head, int n_kv, int n_rot, const void* q_norm_bf16_dev, const void* k_norm_bf16_dev, const float* rope_dev,
+                   void* k_cache_dev, void* v_cache_dev, int max_ctx, float* out_dev, void* xq_q_dev, void* xq_sc_dev, float eps, void* workspace_dev, void* stream) {
+    HP_GUARD_BEGIN
+    HP_REQUIRE(qkv_dev && q_norm_bf16_dev && k_norm_bf16_dev && rope_dev && k_cache_dev && v_cache_dev && workspace_dev && (out_dev || xq_q_dev), "hp_attn_decode: null pointer");
+    HP_REQUIRE((xq_q_dev == nullptr) == (xq_sc_dev == nullptr), "hp_attn_decode: give both quantised-output buffers or neither");
+    HP_REQUIRE(n_rot >= 2 && n_rot % 2 == 0 && n_rot <= 256 && ld % 4 == 0, "hp_attn_decode: bad n_rot / ld");
+    return hp::attn_decode_seq(qkv_dev, ld, R, pos0, n_head, n_kv, n_rot, q_norm_bf16_dev, k_norm_bf16_dev, rope_dev, k_cache_dev, v_cache_dev, max_ctx, out_dev,
+                               hp::XQ8F{xq_q_dev, xq_sc_dev}, eps, workspace_dev, (cudaStream_t)stream);
+    HP_GUARD_END
+}
+// workspace of hp_moe_layer: router logits | ticket counters | gate|up rows | per-pair outputs | quantised activations of the pairs
+namespace {
+struct MoeWs { size_t logits, cnt, gu, v, q2, sc2, total; };
+MoeWs moe_ws(int T, int E, int F, int n_expert, int k) {
+    auto al = [](size_t x) { return (x + 255) & ~(size_t)255; };
+    const size_t pairs = (size_t)T * (k + 1);
+    MoeWs w; size_t o = 0;
+    w.logits = o; o += al((size_t)T * (n_expert + 1) * 4);
+    w.cnt = o; o += al((size_t)T * 4);
+    w.gu = o; o += al(pairs * 2 * F * 4);
+    w.v = o; o += al(pairs * E * 4);
+    w.q2 = o; o += al(hp::xq_q_bytes((int)pairs, F));
+    w.sc2 = o; o += al(hp::xq_sc_floats((int)pairs, F) * 4);
+    w.total = o; return w;
+}
+}
+size_t hp_moe_workspace_bytes(int T, int E, int F, int n_expert, int k) { return (T < 1 || E < 1 || F < 1 || n_expert < 1 || k < 1) ? 0 : moe_ws(T, E, F, n_expert, k).total; }
+int hp_moe_layer(const float* xn_dev, const void* xq_q_dev, const void* xq_sc_dev, const float* router_dev, const void* exp_gate_up_dev, const void* exp_down_dev,
+                 const void* sh_gate_up_dev, const void* sh_down_dev, int T, int E, int F, int n_expert, int k, int* ids_dev, float* weights_dev, float* y_dev,
+                 void* workspace_dev, void* stream) {
+    HP_GUARD_BEGIN
+    HP_REQUIRE(xn_dev && xq_q_dev && xq_sc_dev && router_dev && exp_gate_up_dev && exp_down_dev && sh_gate_up_dev && sh_down_dev && ids_dev && weights_dev && y_dev && workspace_dev, "hp_moe_layer: null pointer");
+    HP_REQUIRE(T >= 1 && T <= 32 && E % 256 == 0 && F % 256 == 0 && n_expert >= k && k >= 1 && k <= 15, "hp_moe_layer: bad shape T=%d E=%d F=%d experts=%d k=%d", T, E, F, n_expert, k);
+    cudaStream_t s = (cudaStream_t)stream;
+    const MoeWs w = moe_ws(T, E, F, n_expert, k);
+    char* ws = (char*)workspace_dev; const int ns = k + 1;
+    float* logits = (float*)(ws + w.logits); int* cnt = (int*)(ws + w.cnt); float* gu = (float*)(ws + w.gu); float* v = (float*)(ws + w.v);
+    hp::XQ8F xq2{ws + w.q2, ws + w.sc2};
+    HP_CUDA(cudaMemsetAsync(cnt, 0, (size_t)T * 4, s));
+    HP_CUDA(cudaMemsetAsync(ws + w.q2, 0, w.total - w.q2, s));
+    { const int rc = hp::router_route(router_dev, xn_dev, logits, ids_dev, weights_dev, cnt, n_expert, E, k, T, s); if (rc) return rc; }
+    hp::MoeParams p; p.w_exp = exp_gate_up_dev; p.w_sh = sh_gate_up_dev; p.ebytes = (size_t)2 * F * (E / 256) * 144; p.N = 2 * F; p.K = E;
+    p.ids = ids_dev; p.slotw = nullptr; p.nslot = ns; p.xq = hp::XQ8F{(void*)xq_q_dev, (void*)xq_sc_dev}; p.y = gu; p.T = T; p.e_lo = 0; p.e_hi = n_expert; p.own_shared = 1;
+    { const int rc = hp::moe_gemv_up(p, s); if (rc) return rc; }
+    { const int rc = hp::moe_silu_quant(gu, F, ids_dev, 0, n_expert, 1, xq2, T * ns, s); if (rc) return rc; }
+    hp::MoeParams d = p; d.w_exp = exp_down_dev; d.w_sh = sh_down_dev; d.ebytes = (size_t)E * (F / 256) * 144; d.N = E; d.K = F; d.xq = xq2; d.slotw = weights_dev; d.y = v;
+    { const int rc = hp::moe_down_pairs(d, s); if (rc) return rc; }
+    return hp::moe_combine(v, weights_dev, y_dev, T, ns, E, s);
+    HP_GUARD_END
+}
+
 // ------------------------------------------------------------------ engine
 struct hp_engine { hp::Engine impl; explicit hp_engine(const hp_model_cfg& c) : impl(c) {} };
 
@@ -201,7 +255,8 @@ int hp_reset_slot(hp_engine* e, int slot) { HP_ENGINE_CALL(e->impl.reset_slot(sl
 int hp_forward(hp_engine* e, const hp_slot_req* reqs, int S, float* ms_out) { HP_ENGINE_CALL(e->impl.forward(reqs, S, ms_out)) }
 int hp_accept(hp_engine* e, int slot, int m) { HP_ENGINE_CALL(e->impl.accept(slot, m)) }
 int hp_mtp_forward(hp_engine* e, int slot, const int* tokens_host, const float* h_dev, int T, int pos0) { HP_ENGINE_CALL(e->impl.mtp_forward(tokens_host, h_dev, T, pos0, slot, true)) }
-int hp_topk(hp_engine* e, int which, int T, int* ids_host, float* vals_host) { HP_ENGINE_CALL(e->impl.topk(which, T, ids_host, vals_host)) }
+int hp_topk(hp_engine* e, int which, int T, int k, int* ids_host, float* vals_host) { HP_ENGINE_CALL(e->impl.topk(which, T, k, ids_host, vals_host)) }
+int hp_prefill(hp_engine* e, int slot, const int* tokens_host, int n, int pos0, int with_mtp) { HP_ENGINE_CALL(e->impl.prefill(slot, tokens_host, n, pos0, with_mtp)) }
 const float* hp_logits_dev(const hp_engine* e) { return e ? e->impl.logits() : nullptr; }
 const float* hp_h_nextn_dev(const hp_engine* e) { return e ? e->impl.h_nextn() : nullptr; }
 const float* hp_mtp_logits_dev(const hp_engine* e) { return e ? e->impl.mtp_logits() : nullptr; }
@@ -218,8 +273,11 @@ int hp_ep_init(hp_engine* e, const void* id128) { HP_GUARD_BEGIN HP_REQUIRE(e &&
 int hp_profile_pass(hp_engine* e, int R, int what, int reps, float* ms_out) { HP_ENGINE_CALL(e->impl.profile_pass(R, what, reps, ms_out)) }
 size_t hp_pass_weight_bytes(const hp_engine* e, int mtp, int with_head) { return e ? e->impl.pass_weight_bytes(mtp != 0, with_head != 0) : 0; }
 int hp_spec_begin(hp_engine* e, int slot, int id_last, int pos, const float* h_pending_dev) { HP_ENGINE_CALL(e->impl.spec_begin(slot, id_last, pos, h_pending_dev)) }
-int hp_spec_round(hp_engine* e, int slot, int n_draft, const int* subst_host, int* out_tokens_host, int* out_count) {
-    HP_ENGINE_CALL(e->impl.spec_round(slot, n_draft, subst_host, out_tokens_host, out_count))
+int hp_spec_round(hp_engine* e, const int* slot_ids_host, int S, int n_draft, const int* subst_host, int* out_tokens_host, int* out_counts_host) {
+    HP_ENGINE_CALL(e->impl.spec_round(slot_ids_host, S, n_draft, subst_host, out_tokens_host, out_counts_host))
+}
+int hp_ep_wait_poll(int (*stream_query)(void*), int (*comm_error)(void*), void* ctx, int limit_ms) {
+    HP_GUARD_BEGIN return hp::ep_wait_poll(stream_query, comm_error, ctx, limit_ms); HP_GUARD_END
 }
 
 }  // extern "C"

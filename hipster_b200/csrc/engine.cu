@@ -61,66 +61,85 @@ __global__ void k_reduce_planes(const float* __restrict__ parts, size_t part_str
     y[(size_t)r * ldy + n] = v;
 }
 
-// ---- fused speculative round: tiny device-side bookkeeping kernels (the host loop of engine/bench/spec27b.cpp:77-103) ----
-enum { SP_ID_LAST = 0, SP_POS = 1, SP_MM = 2, SP_COUNT = 3, SP_POS_OLD = 4, SP_DRAFTS = 8, SP_IDS = 16, SP_OUT = 32, SP_SUBST = 48, SP_INTS = 64 };
-enum { D_TOK = 0, D_POS = 32, D_SLOT = 64, D_RGROUP = 96, D_GROUPS = 128, D_SEQS = 160, D_INTS = 256 };
-// draft step i: one row (token = last emitted token or the previous draft) at position pos + i (spec27b.cpp:81-85)
-__global__ void k_spec_draft_setup(const int* __restrict__ sp, int* __restrict__ d, int i, int slot) {
+// ---- pass descriptor (ints, device + pinned host copy): per row token / position / slot / attention row group, per
+// attention row group {r0, T, slot, pos0}, per sequence {r0, T, slot, -}. A pass has at most MAXR rows, so at most MAXR
+// row groups (one per row in the worst head geometry) and MAXS sequences.
+enum { D_TOK = 0, D_POS = 32, D_SLOT = 64, D_RGROUP = 96, D_GROUPS = 128, D_SEQS = 256, D_INTS = 320 };
+static_assert(D_POS - D_TOK >= Engine::MAXR && D_SLOT - D_POS >= Engine::MAXR && D_RGROUP - D_SLOT >= Engine::MAXR && D_GROUPS - D_RGROUP >= Engine::MAXR, "row tables hold MAXR rows");
+static_assert(D_SEQS - D_GROUPS >= 4 * Engine::MAXR && D_INTS - D_SEQS >= 4 * Engine::MAXS, "group / sequence tables hold MAXR groups and MAXS sequences");
+
+// ---- fused speculative round over S slots: device-side bookkeeping (the host loops of engine/bench/spec27b.cpp:77-103
+// and engine/bench/batchfn.cpp:96-117). Per-slot state block of SP_INTS ints; the round's inputs (slot list, seeded
+// substitutions) arrive in a separate block so that one captured graph serves every round of the same (S, n). ----
+enum { SP_ID_LAST = 0, SP_POS = 1, SP_MM = 2, SP_COUNT = 3, SP_POS_OLD = 4, SP_DRAFTS = 8, SP_IDS = 16, SP_OUT = 24, SP_INTS = 32 };
+enum { SI_SLOTS = 0, SI_SUBST = 8, SI_INTS = 8 + 8 * 8 };   // inputs: slots[S], subst[request][8]
+// Rows of a pass of the round. mode 0: draft step i (one row per slot: the last emitted token or the previous draft, at
+// pos + i; spec27b.cpp:81-85); mode 1: verify rows [id_last, d1..dn] at pos.. (spec27b.cpp:88-90); mode 2: MTP catch-up
+// rows d1..dn at pos_old + 1.. (spec27b.cpp:99). Request j (slot slots[j]) owns rows j*Tm ..; its rows are cut into
+// attention row groups of at most gr rows.
+__global__ void k_spec_setup(const int* __restrict__ sp, const int* __restrict__ in, int* __restrict__ d, int mode, int i, int n, int S, int gr) {
     pdl_launch_dependents();
     pdl_wait();
-    if (threadIdx.x) return;
-    d[D_TOK] = i == 0 ? sp[SP_ID_LAST] : sp[SP_DRAFTS + i - 1]; d[D_POS] = sp[SP_POS] + i; d[D_SLOT] = slot; d[D_RGROUP] = 0;
-    d[D_GROUPS] = 0; d[D_GROUPS + 1] = 1; d[D_GROUPS + 2] = slot; d[D_GROUPS + 3] = sp[SP_POS] + i;
+    const int Tm = mode == 0 ? 1 : mode == 1 ? n + 1 : n, gps = (Tm + gr - 1) / gr;
+    for (int e = threadIdx.x; e < S * Tm; e += blockDim.x) {
+        const int j = e / Tm, t = e - j * Tm, slot = in[SI_SLOTS + j];
+        const int* st = sp + slot * SP_INTS;
+        int tok, pos;
+        if (mode == 0) { tok = i == 0 ? st[SP_ID_LAST] : st[SP_DRAFTS + i - 1]; pos = st[SP_POS] + i; }
+        else if (mode == 1) { tok = t == 0 ? st[SP_ID_LAST] : st[SP_DRAFTS + t - 1]; pos = st[SP_POS] + t; }
+        else { tok = st[SP_DRAFTS + t]; pos = st[SP_POS_OLD] + 1 + t; }
+        d[D_TOK + e] = tok; d[D_POS + e] = pos; d[D_SLOT + e] = slot; d[D_RGROUP + e] = j * gps + t / gr;
+        if (t % gr == 0) { int* g = d + D_GROUPS + 4 * (j * gps + t / gr); g[0] = e; g[1] = min(gr, Tm - t); g[2] = slot; g[3] = pos; }
+        if (t == 0) { int* q = d + D_SEQS + 4 * j; q[0] = e; q[1] = Tm; q[2] = slot; q[3] = 0; }
+    }
 }
-// the draft is the MTP argmax unless the caller substitutes it (seeded acceptance control)
-__global__ void k_spec_take(int* __restrict__ sp, const int* __restrict__ mids, int i) {
+// rows of hstage (request order) <- per-slot pending hidden rows (draft step 0), or <- rows of the verify pass' h
+// (catch-up: rows t < n of each request)
+__global__ void __launch_bounds__(256) k_spec_gather_h(const int* __restrict__ in, const float* __restrict__ hpend, const float* __restrict__ h, float* __restrict__ dst, int mode, int n, int E) {
     pdl_launch_dependents();
     pdl_wait();
-    if (threadIdx.x) return;
-    const int sub = sp[SP_SUBST + i]; sp[SP_DRAFTS + i] = sub >= 0 ? sub : mids[0];
+    const int e = blockIdx.x;   // destination row
+    const float* src;
+    if (mode == 0) src = hpend + (size_t)in[SI_SLOTS + e] * E;
+    else { const int j = e / n, t = e - j * n; src = h + (size_t)(j * (n + 1) + t) * E; }
+    for (int i = threadIdx.x; i < E; i += 256) dst[(size_t)e * E + i] = src[i];
 }
-// verify rows [id_last, d1..dn] at positions pos.. (spec27b.cpp:88-90)
-__global__ void k_spec_verify_setup(const int* __restrict__ sp, int* __restrict__ d, int n, int slot) {
+// the draft of request j is the MTP argmax unless the caller substitutes it (seeded acceptance control)
+__global__ void k_spec_take(int* __restrict__ sp, const int* __restrict__ in, const int* __restrict__ mids, int i, int S) {
     pdl_launch_dependents();
     pdl_wait();
-    const int t = threadIdx.x;
-    if (t <= n) { d[D_TOK + t] = t == 0 ? sp[SP_ID_LAST] : sp[SP_DRAFTS + t - 1]; d[D_POS + t] = sp[SP_POS] + t; d[D_SLOT + t] = slot; d[D_RGROUP + t] = 0; }
-    if (t == 0) { d[D_GROUPS] = 0; d[D_GROUPS + 1] = n + 1; d[D_GROUPS + 2] = slot; d[D_GROUPS + 3] = sp[SP_POS];
-                  d[D_SEQS] = 0; d[D_SEQS + 1] = n + 1; d[D_SEQS + 2] = slot; d[D_SEQS + 3] = 0; }
+    const int j = threadIdx.x; if (j >= S) return;
+    const int sub = in[SI_SUBST + 8 * j + i];
+    sp[in[SI_SLOTS + j] * SP_INTS + SP_DRAFTS + i] = sub >= 0 ? sub : mids[j];
 }
-// greedy prefix acceptance (spec27b.cpp:92-102): mm accepted drafts, bonus = ids[mm], commit mm+1 rows, h_pending = h row mm
-__global__ void __launch_bounds__(256) k_spec_accept(int* __restrict__ sp, const int* __restrict__ ids, int* __restrict__ replay_n, int n, int slot,
+// greedy prefix acceptance per slot (spec27b.cpp:92-102): mm accepted drafts, bonus = ids[mm], commit mm+1 rows,
+// h_pending = h row mm of the slot. One block per request.
+__global__ void __launch_bounds__(256) k_spec_accept(int* __restrict__ sp, const int* __restrict__ in, const int* __restrict__ ids, int* __restrict__ replay_n, int n,
                                                       const float* __restrict__ h, float* __restrict__ hpend, int E) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ int smm;
+    const int j = blockIdx.x, slot = in[SI_SLOTS + j];
+    int* st = sp + slot * SP_INTS; const int* id = ids + j * (n + 1);
     if (threadIdx.x == 0) {
-        int mm = 0; while (mm < n && ids[mm] == sp[SP_DRAFTS + mm]) ++mm;
-        for (int i = 0; i <= n; ++i) sp[SP_IDS + i] = ids[i];
-        for (int i = 0; i < mm; ++i) sp[SP_OUT + i] = sp[SP_DRAFTS + i];
-        sp[SP_OUT + mm] = ids[mm];
-        sp[SP_MM] = mm; sp[SP_COUNT] = mm + 1; sp[SP_POS_OLD] = sp[SP_POS]; sp[SP_POS] = sp[SP_POS] + mm + 1; sp[SP_ID_LAST] = ids[mm];
+        int mm = 0; while (mm < n && id[mm] == st[SP_DRAFTS + mm]) ++mm;
+        for (int i = 0; i <= n; ++i) st[SP_IDS + i] = id[i];
+        for (int i = 0; i < mm; ++i) st[SP_OUT + i] = st[SP_DRAFTS + i];
+        st[SP_OUT + mm] = id[mm];
+        st[SP_MM] = mm; st[SP_COUNT] = mm + 1; st[SP_POS_OLD] = st[SP_POS]; st[SP_POS] = st[SP_POS] + mm + 1; st[SP_ID_LAST] = id[mm];
         replay_n[slot] = mm + 1;
         smm = mm;
     }
     __syncthreads();
-    const float* src = h + (size_t)smm * E;
-    for (int i = threadIdx.x; i < E; i += 256) hpend[i] = src[i];
-}
-// MTP catch-up rows: drafts at positions pos_old + 1 .. with the target's h rows (spec27b.cpp:99). All n rows run; rows
-// beyond the accepted prefix only write KV entries that the next round rewrites before reading them.
-__global__ void k_spec_catchup_setup(const int* __restrict__ sp, int* __restrict__ d, int n, int slot) {
-    pdl_launch_dependents();
-    pdl_wait();
-    const int t = threadIdx.x;
-    if (t < n) { d[D_TOK + t] = sp[SP_DRAFTS + t]; d[D_POS + t] = sp[SP_POS_OLD] + 1 + t; d[D_SLOT + t] = slot; d[D_RGROUP + t] = 0; }
-    if (t == 0) { d[D_GROUPS] = 0; d[D_GROUPS + 1] = n; d[D_GROUPS + 2] = slot; d[D_GROUPS + 3] = sp[SP_POS_OLD] + 1; }
+    const float* src = h + (size_t)(j * (n + 1) + smm) * E; float* dst = hpend + (size_t)slot * E;
+    for (int i = threadIdx.x; i < E; i += 256) dst[i] = src[i];
 }
 
 #define HP_TRY(x) do { const int rc_ = (x); if (rc_ != HP_OK) return rc_; } while (0)
 // descriptor layout (ints)
 Engine::Engine(const hp_model_cfg& cfg) : c_(cfg) {}
 Engine::~Engine() {
+    ep_destroy();
     for (cudaGraphExec_t g : graphs_) if (g) cudaGraphExecDestroy(g);
     for (void* p : allocs_) cudaFree(p);
     if (h_desc_) cudaFreeHost(h_desc_);
@@ -290,7 +309,7 @@ int Engine::init() {
         HP_TRY(alloc(&xq2_.q, xq_q_bytes(pairs, F))); HP_TRY(alloc(&xq2_.sc, xq_sc_floats(pairs, F) * 4));
         HP_CUDA(cudaMemsetAsync(xq2_.q, 0, xq_q_bytes(pairs, F), s_)); HP_CUDA(cudaMemsetAsync(xq2_.sc, 0, xq_sc_floats(pairs, F) * 4, s_));
         moe_out_.N = E; moe_out_.K = F; moe_out_.P = 1;
-        { const int w = std::max(1, c.ep_world); e_lo_ = (int)((long long)c.ep_rank * c.n_expert / w); e_hi_ = (int)((long long)(c.ep_rank + 1) * c.n_expert / w); own_shared_ = 1; }
+        { const int w = std::max(1, c.ep_world); e_lo_ = (int)((long long)c.ep_rank * c.n_expert / w); e_hi_ = (int)((long long)(c.ep_rank + 1) * c.n_expert / w); own_shared_ = (w == 1 || c.ep_rank == 0) ? 1 : 0; }
     }
     nsplit_max_ = (c.max_ctx + ATTN_SPLIT - 1) / ATTN_SPLIT;
     const size_t np = attn_partial_floats(MAXR, c.n_head_kv, nsplit_max_);
@@ -298,9 +317,16 @@ int Engine::init() {
     HP_TRY(alloc((void**)&d_desc_, D_INTS * 4)); HP_CUDA(cudaMallocHost((void**)&h_desc_, D_INTS * 4)); memset(h_desc_, 0, D_INTS * 4);
     HP_TRY(alloc((void**)&d_ids_, MAXR * 4)); HP_TRY(alloc((void**)&d_mids_, MAXR * 4)); HP_TRY(alloc((void**)&d_vals_, MAXR * 4)); HP_TRY(alloc((void**)&d_mvals_, MAXR * 4));
     HP_TRY(alloc(&am_scratch_, argmax_scratch_bytes(MAXR, c.n_vocab)));
-    HP_TRY(alloc((void**)&d_spec_, SP_INTS * 4)); HP_CUDA(cudaMallocHost((void**)&h_spec_, 2 * SP_INTS * 4));
-    HP_CUDA(cudaMemsetAsync(d_spec_, 0, SP_INTS * 4, s_));
-    HP_TRY(alloc((void**)&hpend_, (size_t)E * 4)); HP_CUDA(cudaMemsetAsync(hpend_, 0, (size_t)E * 4, s_));
+    HP_TRY(alloc(&topk_scratch_, topk_scratch_bytes(MAXR, c.n_vocab, topk_max_k())));
+    HP_TRY(alloc((void**)&d_topk_ids_, (size_t)MAXR * topk_max_k() * 4)); HP_TRY(alloc((void**)&d_topk_vals_, (size_t)MAXR * topk_max_k() * 4));
+    HP_TRY(alloc((void**)&prof_kv_, (size_t)2 * nattn() * c.n_head_kv * 8 * 256 * 2 + 16));
+    HP_TRY(alloc((void**)&d_spec_, MAXS * SP_INTS * 4)); HP_TRY(alloc((void**)&d_specin_, SI_INTS * 4));
+    HP_CUDA(cudaMallocHost((void**)&h_spec_, (SI_INTS + MAXS * SP_INTS) * 4)); memset(h_spec_, 0, (SI_INTS + MAXS * SP_INTS) * 4);
+    HP_CUDA(cudaMemsetAsync(d_spec_, 0, MAXS * SP_INTS * 4, s_)); HP_CUDA(cudaMemsetAsync(d_specin_, 0, SI_INTS * 4, s_));
+    HP_TRY(alloc((void**)&hpend_, (size_t)MAXS * E * 4)); HP_CUDA(cudaMemsetAsync(hpend_, 0, (size_t)MAXS * E * 4, s_));
+    HP_TRY(alloc((void**)&hstage_, (size_t)MAXR * E * 4)); HP_CUDA(cudaMemsetAsync(hstage_, 0, (size_t)MAXR * E * 4, s_));
+    HP_TRY(alloc((void**)&hprev_, (size_t)MAXS * E * 4)); HP_CUDA(cudaMemsetAsync(hprev_, 0, (size_t)MAXS * E * 4, s_));
+    spec_pos_.assign(c.n_slots, 0); spec_on_.assign(c.n_slots, 0);
     HP_TRY(alloc((void**)&err_, 4)); HP_CUDA(cudaMemsetAsync(err_, 0, 4, s_));
     HP_TRY(reset());
     HP_CUDA(cudaStreamSynchronize(s_));
@@ -382,7 +408,7 @@ int Engine::moe_block(const LayerW& L, int R) {
     // the experts are sharded, then combined in slot order (the arithmetic of gemv.hip:1104-1112 on every GPU)
     d.y = moe_v_;
     HP_TRY(moe_down_pairs(d, s_));
-    if (ep_world_ > 1) HP_TRY(ep_exchange(moe_v_, (size_t)R * ns * E));
+    if (c.ep_world > 1) { HP_TRY(ep_ready()); HP_TRY(ep_exchange(moe_v_, (size_t)R * ns * E)); }
     return HP_OK;   // combined in slot order by the norm that follows (norm_in)
 }
 
@@ -442,24 +468,17 @@ int Engine::flush_commits() {
     return HP_OK;
 }
 
-int Engine::forward(const hp_slot_req* reqs, int S, float* ms) {
-    HP_REQUIRE(reqs && S >= 1 && S <= c_.n_slots, "bad S");                                  // qwen35.cpp:290
-    int T = 0; for (int i = 0; i < S; ++i) T += reqs[i].T;
-    HP_REQUIRE(T >= 1 && T <= MAXR, "bad T");                                                // qwen35.cpp:293
-    std::vector<char> in_pass(c_.n_slots, 0);
-    for (int i = 0; i < S; ++i) {
-        const hp_slot_req& r = reqs[i];
-        HP_REQUIRE(r.slot >= 0 && r.slot < c_.n_slots && r.T >= 1 && r.T <= 8 && r.pos >= 0 && r.pos + r.T <= c_.max_ctx && r.tokens && !in_pass[r.slot], "bad request");   // qwen35.cpp:298
-        in_pass[r.slot] = 1;
-    }
+// rows of a pass in request order: per-row tables, attention row groups (rows of one slot, at most ATTN_MAX_PAIRS
+// (row, q-head) pairs per kv head) and, for the trunk, the per-sequence table of the GDN kernels
+int Engine::fill_desc(const hp_slot_req* reqs, int S, int* rows, int* ngroups, bool with_seqs) {
     int* d = h_desc_; int r0 = 0, ng = 0;
+    const int gr = attn_rows_per_group();
     for (int i = 0; i < S; ++i) {
         const hp_slot_req& r = reqs[i];
-        d[D_SEQS + i * 4] = r0; d[D_SEQS + i * 4 + 1] = r.T; d[D_SEQS + i * 4 + 2] = r.slot; d[D_SEQS + i * 4 + 3] = 0;
-        // attention row groups: rows of one slot, at most ATTN_MAX_PAIRS (row, q-head) pairs per kv head
-        const int gr = std::max(1, std::min(8, ATTN_MAX_PAIRS / (c_.n_head / c_.n_head_kv)));
+        if (with_seqs) { d[D_SEQS + i * 4] = r0; d[D_SEQS + i * 4 + 1] = r.T; d[D_SEQS + i * 4 + 2] = r.slot; d[D_SEQS + i * 4 + 3] = 0; }
         for (int t0 = 0; t0 < r.T; t0 += gr) {
             const int tn = std::min(gr, r.T - t0);
+            HP_REQUIRE(ng < MAXR, "pass needs more than %d attention row groups", MAXR);   // cannot happen while rows <= MAXR; keeps the table write in bounds
             d[D_GROUPS + ng * 4] = r0 + t0; d[D_GROUPS + ng * 4 + 1] = tn; d[D_GROUPS + ng * 4 + 2] = r.slot; d[D_GROUPS + ng * 4 + 3] = r.pos + t0;
             for (int t = t0; t < t0 + tn; ++t) d[D_RGROUP + r0 + t] = ng;
             ++ng;
@@ -467,21 +486,37 @@ int Engine::forward(const hp_slot_req* reqs, int S, float* ms) {
         for (int t = 0; t < r.T; ++t) { d[D_TOK + r0 + t] = r.tokens[t]; d[D_POS + r0 + t] = r.pos + t; d[D_SLOT + r0 + t] = r.slot; }
         r0 += r.T;
     }
+    *rows = r0; *ngroups = ng;
+    return HP_OK;
+}
+
+int Engine::forward(const hp_slot_req* reqs, int S, float* ms) {
+    HP_REQUIRE(reqs && S >= 1 && S <= c_.n_slots, "bad S");                                  // qwen35.cpp:290
+    int T = 0; for (int i = 0; i < S; ++i) T += reqs[i].T > 0 ? reqs[i].T : MAXR + 1;
+    HP_REQUIRE(T >= 1 && T <= MAXR, "bad T");                                                // qwen35.cpp:293
+    std::vector<char> in_pass(c_.n_slots, 0);
+    for (int i = 0; i < S; ++i) {
+        const hp_slot_req& r = reqs[i];
+        HP_REQUIRE(r.slot >= 0 && r.slot < c_.n_slots && r.T >= 1 && r.T <= 8 && r.pos >= 0 && r.pos + r.T <= c_.max_ctx && r.tokens && !in_pass[r.slot], "bad request");   // qwen35.cpp:298
+        in_pass[r.slot] = 1;
+    }
+    if (c_.ep_world > 1) HP_TRY(ep_ready());
+    int ng = 0;
+    HP_TRY(fill_desc(reqs, S, &T, &ng, true));
     HP_CUDA(cudaEventRecord(ev0_, s_));
     HP_TRY(upload_desc());
     HP_TRY(run_pass(T, S, ng));
     // the accepted prefixes of the previous pass are now part of the stored state
-    r0 = 0;
+    int r0 = 0;
     for (int i = 0; i < S; ++i) {
         const hp_slot_req& r = reqs[i];
         HP_CUDA(cudaMemsetAsync(replay_n_ + r.slot, 0, 4, s_)); pend_[r.slot] = 0;
         last_r0_[r.slot] = r0; last_T_[r.slot] = r.T; r0 += r.T;
     }
     last_rows_ = T;
-    HP_CUDA(cudaEventRecord(ev1_, s_)); HP_CUDA(cudaEventSynchronize(ev1_));
+    HP_CUDA(cudaEventRecord(ev1_, s_)); HP_TRY(sync_stream());
     HP_CUDA(cudaEventElapsedTime(&last_ms_, ev0_, ev1_));
-    int herr = 0; HP_CUDA(cudaMemcpy(&herr, err_, 4, cudaMemcpyDeviceToHost));
-    if (herr) { cudaMemset(err_, 0, 4); set_error("a kernel gave up a bounded wait (device status %d)", herr); return herr; }
+    HP_TRY(check_device_status());
     if (ms) *ms = last_ms_;
     return HP_OK;
 }
@@ -515,51 +550,86 @@ int Engine::run_mtp(int R, int ngroups, const float* h_dev, int ldh, bool want_l
     return HP_OK;
 }
 int Engine::mtp_forward(const int* tokens, const float* h_dev, int T, int pos0, int slot, bool want_logits) {
-    HP_REQUIRE(c_.has_mtp, "model has no MTP block");
-    HP_REQUIRE(tokens && h_dev && T >= 1 && T <= 8 && slot >= 0 && slot < c_.n_slots && pos0 >= 0 && pos0 + T <= c_.max_ctx, "bad T");   // qwen35.cpp:406
-    int* d = h_desc_;
-    const int gr = std::max(1, std::min(8, ATTN_MAX_PAIRS / (c_.n_head / c_.n_head_kv))); int ng = 0;
-    for (int t0 = 0; t0 < T; t0 += gr) {
-        const int tn = std::min(gr, T - t0);
-        d[D_GROUPS + ng * 4] = t0; d[D_GROUPS + ng * 4 + 1] = tn; d[D_GROUPS + ng * 4 + 2] = slot; d[D_GROUPS + ng * 4 + 3] = pos0 + t0;
-        for (int t = t0; t < t0 + tn; ++t) d[D_RGROUP + t] = ng;
-        ++ng;
-    }
-    for (int t = 0; t < T; ++t) { d[D_TOK + t] = tokens[t]; d[D_POS + t] = pos0 + t; d[D_SLOT + t] = slot; }
-    HP_TRY(upload_desc());
-    HP_TRY(run_mtp(T, ng, h_dev, c_.n_embd, want_logits));
-    HP_CUDA(cudaStreamSynchronize(s_));
-    return HP_OK;
+    HP_REQUIRE(tokens && T >= 1 && T <= 8, "bad T");                                          // qwen35.cpp:406
+    const hp_slot_req r{slot, tokens, T, pos0};
+    return mtp_forward_reqs(&r, 1, h_dev, want_logits);
 }
 
 int Engine::mtp_forward_reqs(const hp_slot_req* reqs, int S, const float* h_dev, bool want_logits) {
     HP_REQUIRE(c_.has_mtp, "model has no MTP block");
     HP_REQUIRE(reqs && h_dev && S >= 1 && S <= c_.n_slots, "bad S");
-    int* d = h_desc_; int r0 = 0, ng = 0;
-    const int gr = std::max(1, std::min(8, ATTN_MAX_PAIRS / (c_.n_head / c_.n_head_kv)));
+    int rows = 0;
     for (int i = 0; i < S; ++i) {
         const hp_slot_req& r = reqs[i];
-        HP_REQUIRE(r.slot >= 0 && r.slot < c_.n_slots && r.T >= 1 && r.T <= 8 && r.pos >= 0 && r.pos + r.T <= c_.max_ctx && r.tokens && r0 + r.T <= MAXR, "bad request");
-        for (int t0 = 0; t0 < r.T; t0 += gr) {
-            const int tn = std::min(gr, r.T - t0);
-            d[D_GROUPS + ng * 4] = r0 + t0; d[D_GROUPS + ng * 4 + 1] = tn; d[D_GROUPS + ng * 4 + 2] = r.slot; d[D_GROUPS + ng * 4 + 3] = r.pos + t0;
-            for (int t = t0; t < t0 + tn; ++t) d[D_RGROUP + r0 + t] = ng;
-            ++ng;
-        }
-        for (int t = 0; t < r.T; ++t) { d[D_TOK + r0 + t] = r.tokens[t]; d[D_POS + r0 + t] = r.pos + t; d[D_SLOT + r0 + t] = r.slot; }
-        r0 += r.T;
+        HP_REQUIRE(r.slot >= 0 && r.slot < c_.n_slots && r.T >= 1 && r.T <= 8 && r.pos >= 0 && r.pos + r.T <= c_.max_ctx && r.tokens && rows + r.T <= MAXR, "bad request");
+        rows += r.T;
     }
+    if (c_.ep_world > 1) HP_TRY(ep_ready());
+    int ng = 0;
+    HP_TRY(fill_desc(reqs, S, &rows, &ng, false));
     HP_TRY(upload_desc());
-    HP_TRY(run_mtp(r0, ng, h_dev, c_.n_embd, want_logits));
-    HP_CUDA(cudaStreamSynchronize(s_));
+    HP_TRY(run_mtp(rows, ng, h_dev, c_.n_embd, want_logits));
+    HP_TRY(sync_stream());
+    return check_device_status();
+}
+
+// Qwen35::topk (qwen35.cpp:426-430): ids / vals [T][k], values descending, ties -> lower index
+int Engine::topk(int which, int T, int k, int* ids, float* vals) {
+    HP_REQUIRE(T >= 1 && T <= MAXR && ids && k >= 1 && k <= topk_max_k() && k <= c_.n_vocab, "topk: bad arguments (1 <= T <= %d, 1 <= k <= %d)", MAXR, topk_max_k());
+    if (k == 1) {   // the arg-max of every row was taken on the device at the end of the pass
+        HP_TRY(sync_stream());
+        HP_CUDA(cudaMemcpy(ids, which ? d_mids_ : d_ids_, T * 4, cudaMemcpyDeviceToHost));
+        if (vals) HP_CUDA(cudaMemcpy(vals, which ? d_mvals_ : d_vals_, T * 4, cudaMemcpyDeviceToHost));
+        return HP_OK;
+    }
+    HP_TRY(topk_rows(which ? mlogits_ : logits_, T, c_.n_vocab, c_.n_vocab, k, d_topk_ids_, d_topk_vals_, topk_scratch_, s_));
+    HP_TRY(sync_stream());
+    HP_CUDA(cudaMemcpy(ids, d_topk_ids_, (size_t)T * k * 4, cudaMemcpyDeviceToHost));
+    if (vals) HP_CUDA(cudaMemcpy(vals, d_topk_vals_, (size_t)T * k * 4, cudaMemcpyDeviceToHost));
     return HP_OK;
 }
 
-int Engine::topk(int which, int T, int* ids, float* vals) {
-    HP_REQUIRE(T >= 1 && T <= MAXR && ids, "topk: bad arguments");
-    HP_CUDA(cudaStreamSynchronize(s_));
-    HP_CUDA(cudaMemcpy(ids, which ? d_mids_ : d_ids_, T * 4, cudaMemcpyDeviceToHost));
-    if (vals) HP_CUDA(cudaMemcpy(vals, which ? d_mvals_ : d_vals_, T * 4, cudaMemcpyDeviceToHost));
+// Prompt ingestion for one slot (Qwen4Exp::prefill + mtp_catchup, qwen4exp.h:57-60,72-74; Backend::prefill,
+// front/serve.cpp:29): n tokens at positions pos0.., committed. This build runs them through the verify path in chunks
+// of 8 rows; with_mtp also runs the MTP block over the same rows, row p paired with the trunk's hidden row of position
+// p - 1 (zeros at position 0; the last row of the previous chunk / call otherwise), so that the draft block's KV cache
+// covers the prompt (spec27b.cpp:62-71). Afterwards row 0 of logits / h_nextn / the arg-max ids holds the LAST prompt row.
+__global__ void k_prefill_shift(const float* __restrict__ h, const float* __restrict__ hprev, float* __restrict__ dst, int E, int zero_first) {
+    const int t = blockIdx.x;   // dst row t = h row t - 1, row 0 = the remembered row (or zeros at position 0)
+    const float* src = t == 0 ? hprev : h + (size_t)(t - 1) * E;
+    for (int i = threadIdx.x; i < E; i += 256) dst[(size_t)t * E + i] = (t == 0 && zero_first) ? 0.f : src[i];
+}
+__global__ void k_prefill_remember(const float* __restrict__ h, float* __restrict__ hprev, int T, int E) {
+    for (int i = threadIdx.x; i < E; i += 256) hprev[i] = h[(size_t)(T - 1) * E + i];
+}
+__global__ void k_prefill_last(float* __restrict__ logits, float* __restrict__ h, int* __restrict__ ids, float* __restrict__ vals, int last, int V, int E) {
+    for (int i = blockIdx.x * 256 + threadIdx.x; i < V; i += gridDim.x * 256) logits[i] = logits[(size_t)last * V + i];
+    if (blockIdx.x == 0) { for (int i = threadIdx.x; i < E; i += 256) h[i] = h[(size_t)last * E + i]; if (threadIdx.x == 0) { ids[0] = ids[last]; vals[0] = vals[last]; } }
+}
+int Engine::prefill(int slot, const int* tokens, int n, int pos0, int with_mtp) {
+    HP_REQUIRE(slot >= 0 && slot < c_.n_slots && tokens && n >= 1 && pos0 >= 0 && pos0 + n <= c_.max_ctx, "prefill: bad arguments (slot %d, n %d, pos0 %d)", slot, n, pos0);
+    HP_REQUIRE(!with_mtp || c_.has_mtp, "model has no MTP block");
+    const int E = c_.n_embd;
+    int T = 0;
+    for (int p = 0; p < n; p += T) {
+        T = std::min(8, n - p);
+        const hp_slot_req r{slot, tokens + p, T, pos0 + p};
+        HP_TRY(forward(&r, 1, nullptr));
+        HP_TRY(accept(slot, T));
+        if (with_mtp) {
+            float* hp = hprev_ + (size_t)slot * E;
+            k_prefill_shift<<<T, 256, 0, s_>>>(h_, hp, hstage_, E, pos0 + p == 0 ? 1 : 0);
+            k_prefill_remember<<<1, 256, 0, s_>>>(h_, hp, T, E);   // after the shift (stream order): this chunk's last row pairs with the next chunk's first token
+            HP_CUDA(cudaGetLastError());
+            HP_TRY(mtp_forward_reqs(&r, 1, hstage_, false));
+        }
+    }
+    if (T > 1) {
+        k_prefill_last<<<64, 256, 0, s_>>>(logits_, h_, d_ids_, d_vals_, T - 1, c_.n_vocab, E);
+        HP_CUDA(cudaGetLastError());
+    }
+    HP_TRY(sync_stream());
+    last_T_[slot] = 0;
     return HP_OK;
 }
 
@@ -619,26 +689,48 @@ size_t Engine::pass_weight_bytes(bool mtp, bool with_head) const {
     return b;
 }
 
-// Diagnostic: device time of `reps` back-to-back verify passes of R rows over whatever tokens / state are current
-// (what = 0), of only the GEMV launches of such passes (what = 1), or of passes that leave out kernel classes
-// (what = 16 + mask: 1 GDN, 2 norms, 4 attention, 8 SiLU, 16 gate|up, 32 down, 64 LM head, 128 input projections, 256 other GEMVs; results are then meaningless, only the time is). State and KV are not committed.
+// Diagnostic: device time of `reps` back-to-back verify passes of R rows (what = 0), of only the GEMV launches of such
+// passes (what = 1), or of passes that leave out kernel classes (what = 16 + mask: 1 GDN, 2 norms, 4 attention, 8 SiLU,
+// 16 gate|up, 32 down, 64 LM head, 128 input projections, 256 other GEMVs; results are then meaningless, only the time is).
+// The passes run on slot 0 at its current position (the position of a running speculative stream, else 0). The context
+// survives: pending accepts are applied to the stored state first, so that the passes replay nothing and leave the
+// recurrent state alone (a pass never advances it), and the K/V rows the passes write are saved before and put back
+// afterwards. What does not survive is the right to accept the pass that came before the call: its saved inputs are
+// overwritten, so hp_accept for slot 0 is refused until the next hp_forward.
 int Engine::profile_pass(int R, int what, int reps, float* ms) {
     HP_REQUIRE(R >= 1 && R <= 8 && reps >= 1 && ms, "profile_pass: bad arguments");
+    HP_REQUIRE(c_.ep_world <= 1, "profile_pass: not available on an expert-parallel engine");
+    HP_TRY(flush_commits());
+    const int pos0 = std::max(0, std::min(spec_on_[0] ? spec_pos_[0] : 0, c_.max_ctx - R));
+    // K/V rows [pos0, pos0 + R) of slot 0 in every attention layer and kv head: one strided copy each way
+    const size_t row_b = 256 * 2, pitch = (size_t)c_.max_ctx * row_b, height = (size_t)nattn() * c_.n_head_kv, width = (size_t)R * row_b;
+    uint16_t* sk = prof_kv_; uint16_t* sv = prof_kv_ + height * 8 * 256;
+    if (height) {
+        HP_CUDA(cudaMemcpy2DAsync(sk, width, kc_ + (size_t)pos0 * 256, pitch, width, height, cudaMemcpyDeviceToDevice, s_));
+        HP_CUDA(cudaMemcpy2DAsync(sv, width, vc_ + (size_t)pos0 * 256, pitch, width, height, cudaMemcpyDeviceToDevice, s_));
+    }
     int* d = h_desc_;
-    for (int t = 0; t < R; ++t) { d[D_TOK + t] = (t * 7919 + 13) % c_.n_vocab; d[D_POS + t] = t; d[D_SLOT + t] = 0; d[D_RGROUP + t] = 0; }
-    d[D_GROUPS] = 0; d[D_GROUPS + 1] = R; d[D_GROUPS + 2] = 0; d[D_GROUPS + 3] = 0;
-    d[D_SEQS] = 0; d[D_SEQS + 1] = R; d[D_SEQS + 2] = 0; d[D_SEQS + 3] = 0;
+    for (int t = 0; t < R; ++t) d[D_TOK + t] = (t * 7919 + 13) % c_.n_vocab;
+    std::vector<int> toks(d + D_TOK, d + D_TOK + R);
+    const hp_slot_req rq{0, toks.data(), R, pos0};
+    int rows = 0, ng = 0;
+    HP_TRY(fill_desc(&rq, 1, &rows, &ng, true));
     HP_TRY(upload_desc());
     gemv_only_ = what == 1; prof_skip_ = what >= 16 ? what - 16 : 0;
-    int rc = run_pass(R, 1, 1);                     // warm-up (also sets kernel attributes)
+    int rc = run_pass(R, 1, ng);                     // warm-up (also sets kernel attributes)
     HP_CUDA(cudaEventRecord(ev0_, s_));
-    for (int i = 0; i < reps && rc == HP_OK; ++i) rc = run_pass(R, 1, 1);
+    for (int i = 0; i < reps && rc == HP_OK; ++i) rc = run_pass(R, 1, ng);
     HP_CUDA(cudaEventRecord(ev1_, s_));
     gemv_only_ = false; prof_skip_ = 0;
+    if (height) {
+        HP_CUDA(cudaMemcpy2DAsync(kc_ + (size_t)pos0 * 256, pitch, sk, width, width, height, cudaMemcpyDeviceToDevice, s_));
+        HP_CUDA(cudaMemcpy2DAsync(vc_ + (size_t)pos0 * 256, pitch, sv, width, width, height, cudaMemcpyDeviceToDevice, s_));
+    }
     HP_CUDA(cudaStreamSynchronize(s_));
+    last_T_[0] = 0;
     if (rc != HP_OK) return rc;
     float t = 0; HP_CUDA(cudaEventElapsedTime(&t, ev0_, ev1_)); *ms = t / reps;
-    return HP_OK;
+    return check_device_status();
 }
 
 // Expert-parallel exchange of the per-(row, slot) expert outputs. Every element of the buffer is produced by exactly one
@@ -654,44 +746,61 @@ int Engine::spec_begin(int slot, int id_last, int pos, const float* h_pending_de
     HP_REQUIRE(c_.has_mtp, "model has no MTP block");
     HP_REQUIRE(slot >= 0 && slot < c_.n_slots && pos >= 0 && pos < c_.max_ctx && h_pending_dev, "spec_begin: bad arguments");
     h_spec_[0] = id_last; h_spec_[1] = pos;
-    HP_CUDA(cudaMemcpyAsync(d_spec_, h_spec_, 8, cudaMemcpyHostToDevice, s_));
-    HP_CUDA(cudaMemcpyAsync(hpend_, h_pending_dev, (size_t)c_.n_embd * 4, cudaMemcpyDeviceToDevice, s_));
+    HP_CUDA(cudaMemcpyAsync(d_spec_ + slot * SP_INTS, h_spec_, 8, cudaMemcpyHostToDevice, s_));
+    HP_CUDA(cudaMemcpyAsync(hpend_ + (size_t)slot * c_.n_embd, h_pending_dev, (size_t)c_.n_embd * 4, cudaMemcpyDeviceToDevice, s_));
     HP_CUDA(cudaStreamSynchronize(s_));
-    spec_pos_ = pos; spec_slot_ = slot; last_T_[slot] = 0;
+    spec_pos_[slot] = pos; spec_on_[slot] = 1; last_T_[slot] = 0;
     return HP_OK;
 }
-int Engine::enqueue_round(int slot, int n) {
-    HP_CUDA(cudaMemcpyAsync(d_spec_ + SP_SUBST, h_spec_, 8 * 4, cudaMemcpyHostToDevice, s_));
-    for (int i = 0; i < n; ++i) {   // draft, chained on the MTP's own h (spec27b.cpp:81-85)
-        HP_CUDA(launch_pdl<2>(k_spec_draft_setup, dim3(1), dim3(32), 0, s_, d_spec_, d_desc_, i, slot));
-        HP_TRY(run_mtp(1, 1, i == 0 ? hpend_ : mh_, c_.n_embd, true));
-        HP_CUDA(launch_pdl<2>(k_spec_take, dim3(1), dim3(32), 0, s_, d_spec_, d_mids_, i));
+int Engine::attn_rows_per_group() const { return std::max(1, std::min(8, ATTN_MAX_PAIRS / (c_.n_head / c_.n_head_kv))); }
+int Engine::enqueue_round(int S, int n) {
+    const int E = c_.n_embd, gr = attn_rows_per_group();
+    auto groups = [&](int Tm) { return S * ((Tm + gr - 1) / gr); };
+    HP_CUDA(cudaMemcpyAsync(d_specin_, h_spec_, SI_INTS * 4, cudaMemcpyHostToDevice, s_));
+    for (int i = 0; i < n; ++i) {   // draft, chained on the MTP's own h (spec27b.cpp:81-85, batchfn.cpp:98-104)
+        HP_CUDA(launch_pdl<2>(k_spec_setup, dim3(1), dim3(32), 0, s_, d_spec_, d_specin_, d_desc_, 0, i, n, S, gr));
+        if (i == 0) HP_CUDA(launch_pdl<2>(k_spec_gather_h, dim3(S), dim3(256), 0, s_, d_specin_, hpend_, h_, hstage_, 0, n, E));
+        HP_TRY(run_mtp(S, groups(1), i == 0 ? hstage_ : mh_, E, true));
+        HP_CUDA(launch_pdl<2>(k_spec_take, dim3(1), dim3(32), 0, s_, d_spec_, d_specin_, d_mids_, i, S));
     }
-    HP_CUDA(launch_pdl<2>(k_spec_verify_setup, dim3(1), dim3(32), 0, s_, d_spec_, d_desc_, n, slot));
-    HP_TRY(run_pass(n + 1, 1, 1));
-    HP_CUDA(launch_pdl<2>(k_spec_accept, dim3(1), dim3(256), 0, s_, d_spec_, d_ids_, replay_n_, n, slot, h_, hpend_, c_.n_embd));
-    HP_CUDA(launch_pdl<2>(k_spec_catchup_setup, dim3(1), dim3(32), 0, s_, d_spec_, d_desc_, n, slot));
-    HP_TRY(run_mtp(n, 1, h_, c_.n_embd, false, true));
-    HP_CUDA(cudaMemcpyAsync(h_spec_ + SP_INTS, d_spec_, SP_INTS * 4, cudaMemcpyDeviceToHost, s_));
+    HP_CUDA(launch_pdl<2>(k_spec_setup, dim3(1), dim3(32), 0, s_, d_spec_, d_specin_, d_desc_, 1, 0, n, S, gr));
+    HP_TRY(run_pass(S * (n + 1), S, groups(n + 1)));
+    HP_CUDA(launch_pdl<2>(k_spec_accept, dim3(S), dim3(256), 0, s_, d_spec_, d_specin_, d_ids_, replay_n_, n, h_, hpend_, E));
+    // MTP catch-up over the drafts with the target's h rows. All n rows of every slot run; rows beyond a slot's accepted
+    // prefix only write KV entries that the next round rewrites before reading them.
+    HP_CUDA(launch_pdl<2>(k_spec_setup, dim3(1), dim3(32), 0, s_, d_spec_, d_specin_, d_desc_, 2, 0, n, S, gr));
+    const float* hc = h_;
+    if (S > 1) { HP_CUDA(launch_pdl<2>(k_spec_gather_h, dim3(S * n), dim3(256), 0, s_, d_specin_, hpend_, h_, hstage_, 1, n, E)); hc = hstage_; }
+    HP_TRY(run_mtp(S * n, groups(n), hc, E, false, true));
+    HP_CUDA(cudaMemcpyAsync(h_spec_ + SI_INTS, d_spec_, MAXS * SP_INTS * 4, cudaMemcpyDeviceToHost, s_));
     HP_CUDA(cudaGetLastError());
     return HP_OK;
 }
-int Engine::spec_round(int slot, int n, const int* subst, int* out_tokens, int* out_count) {
+int Engine::spec_round(const int* slots, int S, int n, const int* subst, int* out_tokens, int* out_counts) {
     HP_REQUIRE(c_.has_mtp, "model has no MTP block");
-    HP_REQUIRE(slot == spec_slot_ && n >= 1 && n <= 7 && out_tokens && out_count, "spec_round: bad arguments (call hp_spec_begin first; 1 <= n_draft <= 7)");
-    HP_REQUIRE(spec_pos_ + 2 * n + 2 <= c_.max_ctx, "spec_round: context exhausted");
-    HP_REQUIRE((n + 1) * (c_.n_head / c_.n_head_kv) <= ATTN_MAX_PAIRS, "spec_round: n_draft + 1 rows exceed one attention row group for this head geometry");
-    for (int i = 0; i < 8; ++i) h_spec_[i] = (subst && i < n) ? subst[i] : -1;
+    HP_REQUIRE(slots && S >= 1 && S <= c_.n_slots && n >= 1 && n <= 7 && out_tokens && out_counts, "spec_round: bad arguments (1 <= S <= n_slots, 1 <= n_draft <= 7)");
+    HP_REQUIRE(S * (n + 1) <= MAXR, "spec_round: %d slots x %d rows exceed %d rows per pass", S, n + 1, MAXR);
+    for (int j = 0; j < S; ++j) {
+        const int sl = slots[j];
+        HP_REQUIRE(sl >= 0 && sl < c_.n_slots && spec_on_[sl], "spec_round: slot %d was not started with hp_spec_begin", sl);
+        for (int q = 0; q < j; ++q) HP_REQUIRE(slots[q] != sl, "spec_round: slot %d listed twice", sl);
+        HP_REQUIRE(spec_pos_[sl] + 2 * n + 2 <= c_.max_ctx, "spec_round: context of slot %d exhausted", sl);
+    }
+    if (c_.ep_world > 1) HP_TRY(ep_ready());
+    for (int j = 0; j < 8; ++j) {
+        h_spec_[SI_SLOTS + j] = j < S ? slots[j] : 0;
+        for (int i = 0; i < 8; ++i) h_spec_[SI_SUBST + 8 * j + i] = (subst && j < S && i < n) ? subst[j * n + i] : -1;
+    }
     static const bool no_graph = getenv("HIPSTER_B200_NO_GRAPH") != nullptr;
-    const int key = slot * 8 + n;
+    const int key = (S - 1) * 8 + n;
     HP_CUDA(cudaEventRecord(ev0_, s_));
-    if (no_graph) HP_TRY(enqueue_round(slot, n));
+    if (no_graph) HP_TRY(enqueue_round(S, n));
     else {
         if (!graphs_[key]) {
-            if (!warmed_[key]) { HP_TRY(enqueue_round(slot, n)); HP_CUDA(cudaStreamSynchronize(s_)); warmed_[key] = true; goto done; }   // first call: eager (sets kernel attributes)
+            if (!warmed_[key]) { HP_TRY(enqueue_round(S, n)); HP_TRY(sync_stream()); warmed_[key] = true; goto done; }   // first call: eager (sets kernel attributes)
             cudaGraph_t g = nullptr;
             HP_CUDA(cudaStreamBeginCapture(s_, cudaStreamCaptureModeThreadLocal));
-            const int rc = enqueue_round(slot, n);
+            const int rc = enqueue_round(S, n);
             const cudaError_t ce = cudaStreamEndCapture(s_, &g);
             if (rc != HP_OK) { if (g) cudaGraphDestroy(g); return rc; }
             HP_CUDA(ce);
@@ -702,16 +811,20 @@ int Engine::spec_round(int slot, int n, const int* subst, int* out_tokens, int* 
     }
 done:
     HP_CUDA(cudaEventRecord(ev1_, s_));
-    HP_CUDA(cudaStreamSynchronize(s_));
+    HP_TRY(sync_stream());
     HP_CUDA(cudaEventElapsedTime(&last_ms_, ev0_, ev1_));
-    {
-        int herr = 0; HP_CUDA(cudaMemcpy(&herr, err_, 4, cudaMemcpyDeviceToHost));
-        if (herr) { cudaMemset(err_, 0, 4); set_error("a kernel gave up a bounded wait (device status %d)", herr); return herr; }
+    HP_TRY(check_device_status());
+    for (int j = 0; j < S; ++j) {
+        const int* r = h_spec_ + SI_INTS + slots[j] * SP_INTS;
+        out_counts[j] = r[SP_COUNT];
+        for (int i = 0; i < r[SP_COUNT]; ++i) out_tokens[j * (n + 1) + i] = r[SP_OUT + i];
+        spec_pos_[slots[j]] = r[SP_POS]; last_T_[slots[j]] = 0; pend_[slots[j]] = r[SP_COUNT];
     }
-    const int* r = h_spec_ + SP_INTS;
-    *out_count = r[SP_COUNT];
-    for (int i = 0; i < r[SP_COUNT]; ++i) out_tokens[i] = r[SP_OUT + i];
-    spec_pos_ = r[SP_POS];
+    return HP_OK;
+}
+int Engine::check_device_status() {
+    int herr = 0; HP_CUDA(cudaMemcpy(&herr, err_, 4, cudaMemcpyDeviceToHost));
+    if (herr) { cudaMemset(err_, 0, 4); set_error("a kernel gave up a bounded wait (device status %d)", herr); return herr; }
     return HP_OK;
 }
 
@@ -719,6 +832,8 @@ done:
 
 // ------------------------------------------------------------------ NCCL (loaded at run time; only the expert-parallel path needs it)
 #include <dlfcn.h>
+#include <chrono>
+#include <thread>
 namespace hp {
 namespace {
 struct NcclId { char b[128]; };   // ncclUniqueId is 128 opaque bytes, passed by value
@@ -727,7 +842,11 @@ struct NcclApi {
     int (*GetUniqueId)(void*) = nullptr;
     int (*CommInitRank)(void**, int, NcclId, int) = nullptr;
     int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+    int (*AllGather)(const void*, void*, size_t, int, void*, cudaStream_t) = nullptr;
+    int (*ReduceScatter)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
     int (*CommDestroy)(void*) = nullptr;
+    int (*CommAbort)(void*) = nullptr;
+    int (*CommGetAsyncError)(void*, int*) = nullptr;
     const char* (*GetErrorString)(int) = nullptr;
 };
 NcclApi g_nccl;
@@ -739,9 +858,15 @@ int nccl_load() {
     g_nccl.GetUniqueId = (decltype(g_nccl.GetUniqueId))dlsym(h, "ncclGetUniqueId");
     g_nccl.CommInitRank = (decltype(g_nccl.CommInitRank))dlsym(h, "ncclCommInitRank");
     g_nccl.AllReduce = (decltype(g_nccl.AllReduce))dlsym(h, "ncclAllReduce");
+    g_nccl.AllGather = (decltype(g_nccl.AllGather))dlsym(h, "ncclAllGather");
+    g_nccl.ReduceScatter = (decltype(g_nccl.ReduceScatter))dlsym(h, "ncclReduceScatter");
     g_nccl.CommDestroy = (decltype(g_nccl.CommDestroy))dlsym(h, "ncclCommDestroy");
+    g_nccl.CommAbort = (decltype(g_nccl.CommAbort))dlsym(h, "ncclCommAbort");
+    g_nccl.CommGetAsyncError = (decltype(g_nccl.CommGetAsyncError))dlsym(h, "ncclCommGetAsyncError");
     g_nccl.GetErrorString = (decltype(g_nccl.GetErrorString))dlsym(h, "ncclGetErrorString");
-    if (!g_nccl.GetUniqueId || !g_nccl.CommInitRank || !g_nccl.AllReduce || !g_nccl.CommDestroy) { set_error("libnccl lacks a required symbol"); return HP_ECOMM; }
+    if (!g_nccl.GetUniqueId || !g_nccl.CommInitRank || !g_nccl.AllReduce || !g_nccl.AllGather || !g_nccl.ReduceScatter || !g_nccl.CommDestroy || !g_nccl.CommAbort || !g_nccl.CommGetAsyncError) {
+        set_error("libnccl lacks a required symbol"); return HP_ECOMM;
+    }
     g_nccl.lib = h; return HP_OK;
 }
 int nccl_check(int rc, const char* what) {
@@ -749,17 +874,62 @@ int nccl_check(int rc, const char* what) {
     set_error("NCCL error %d (%s) in %s", rc, g_nccl.GetErrorString ? g_nccl.GetErrorString(rc) : "?", what); return HP_ECOMM;
 }
 }  // namespace
+
+// The engine's wait for a stream that carries collectives: instead of blocking in the driver without a limit, poll the
+// stream and the communicator's asynchronous error state until the work is done, an error shows, or limit_ms passed.
+// stream_query: 0 = done, 1 = still running, anything else = failed; comm_error: 0 = healthy (or still in progress),
+// anything else = the communicator reports a failure. Returns HP_OK, HP_ECOMM (failure) or HP_ETIMEOUT.
+int ep_wait_poll(int (*stream_query)(void*), int (*comm_error)(void*), void* ctx, int limit_ms) {
+    HP_REQUIRE(stream_query && limit_ms >= 0, "ep_wait_poll: bad arguments");
+    const auto t0 = std::chrono::steady_clock::now();
+    for (unsigned it = 0;; ++it) {
+        const int q = stream_query(ctx);
+        if (q == 0) return HP_OK;
+        if (q != 1) { set_error("the stream failed while waiting for a collective (status %d)", q); return HP_ECOMM; }
+        if (comm_error) { const int ce = comm_error(ctx); if (ce != 0) { set_error("the communicator reported asynchronous error %d while waiting", ce); return HP_ECOMM; } }
+        const auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+        if (ms > limit_ms) { set_error("no progress on the collective stream after %d ms: a peer has stopped taking part", limit_ms); return HP_ETIMEOUT; }
+        if (it > 2000) std::this_thread::sleep_for(std::chrono::microseconds(50)); else std::this_thread::yield();
+    }
+}
+namespace {
+struct WaitCtx { cudaStream_t s; void* comm; };
+int wait_stream_query(void* p) { const cudaError_t e = cudaStreamQuery(((WaitCtx*)p)->s); return e == cudaSuccess ? 0 : e == cudaErrorNotReady ? 1 : 2 + (int)e; }
+int wait_comm_error(void* p) { int st = 0; if (g_nccl.CommGetAsyncError(((WaitCtx*)p)->comm, &st) != 0) return -1; return (st == 0 || st == 7 /* ncclInProgress */) ? 0 : st; }
+}
+// stream synchronisation of an engine: plain when no communicator is attached, bounded polling otherwise. After a
+// failure the communicator is aborted (its kernels are torn down) and the engine refuses further expert-parallel work.
+int Engine::sync_stream() {
+    if (!nccl_comm_) { HP_CUDA(cudaStreamSynchronize(s_)); return HP_OK; }
+    static const int limit = [] { const char* e = getenv("HIPSTER_B200_EP_TIMEOUT_MS"); return e ? atoi(e) : 30000; }();
+    WaitCtx c{s_, nccl_comm_};
+    const int rc = ep_wait_poll(wait_stream_query, wait_comm_error, &c, limit);
+    if (rc != HP_OK) { g_nccl.CommAbort(nccl_comm_); nccl_comm_ = nullptr; ep_failed_ = true; }
+    return rc;
+}
 int Engine::ep_unique_id(void* id128) { HP_TRY(nccl_load()); return nccl_check(g_nccl.GetUniqueId(id128), "ncclGetUniqueId"); }
 int Engine::ep_init(const void* id128) {
     HP_REQUIRE(c_.n_expert > 0 && c_.ep_world > 1, "ep_init: the model was not loaded with ep_world > 1");
+    HP_REQUIRE(!nccl_comm_, "ep_init: already initialised");
     HP_TRY(nccl_load());
     NcclId id; memcpy(id.b, id128, 128);
     HP_TRY(nccl_check(g_nccl.CommInitRank(&nccl_comm_, c_.ep_world, id, c_.ep_rank), "ncclCommInitRank"));
-    ep_world_ = c_.ep_world; ep_rank_ = c_.ep_rank; own_shared_ = c_.ep_rank == 0 ? 1 : 0;
+    ep_world_ = c_.ep_world; ep_rank_ = c_.ep_rank; ep_failed_ = false;
     return HP_OK;
 }
+// a model loaded as one shard of an expert-parallel group must not run a pass before (or after a failure of) its
+// communicator: the experts it does not hold would silently contribute zeros
+int Engine::ep_ready() {
+    if (c_.ep_world <= 1 || nccl_comm_) return HP_OK;
+    set_error(ep_failed_ ? "expert parallelism: the communicator failed earlier; reload the engine" : "expert parallelism is not initialised: call hp_ep_init on every rank before the first pass");
+    return HP_ESTATE;
+}
+void Engine::ep_destroy() {
+    if (nccl_comm_ && g_nccl.CommDestroy) { cudaStreamSynchronize(s_); g_nccl.CommDestroy(nccl_comm_); }
+    nccl_comm_ = nullptr;
+}
 int Engine::ep_allreduce(float* buf, size_t n) {
-    HP_REQUIRE(nccl_comm_, "expert parallelism is not initialised (hp_ep_init)");
+    HP_TRY(ep_ready());
     return nccl_check(g_nccl.AllReduce(buf, buf, n, /* ncclFloat32 */ 7, /* ncclSum */ 0, nccl_comm_, s_), "ncclAllReduce");
 }
 }

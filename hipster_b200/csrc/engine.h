@@ -41,13 +41,14 @@ public:
     int mtp_forward(const int* tokens, const float* h_dev, int T, int pos0, int slot, bool want_logits);   // qwen35.h:70
     int mtp_forward_reqs(const hp_slot_req* reqs, int S, const float* h_dev, bool want_logits);   // qwen4exp.h:66-70
     static int ep_unique_id(void* id128); int ep_init(const void* id128);
-    int topk(int which, int T, int* ids, float* vals);       // k = 1 (qwen35.h:87)
+    int topk(int which, int T, int k, int* ids, float* vals);   // Qwen35::topk (qwen35.h:87): ids / vals [T][k] on the host
+    int prefill(int slot, const int* tokens, int n, int pos0, int with_mtp);   // Qwen4Exp::prefill + mtp_catchup (qwen4exp.h:57-60,72-74)
     int reset(); int reset_slot(int slot);
     int flush_commits();                                     // apply every pending accept to the stored state
     int tensor(int layer, int kind, void** ptr, size_t* bytes) const;
     int gdn_state(int slot, int gdn_layer, float** ptr, size_t* bytes);
     int spec_begin(int slot, int id_last, int pos, const float* h_pending_dev);
-    int spec_round(int slot, int n_draft, const int* subst_host, int* out_tokens, int* out_count);
+    int spec_round(const int* slots, int S, int n_draft, const int* subst_host, int* out_tokens, int* out_counts);
     const hp_model_cfg& cfg() const { return c_; }
     float* logits() const { return logits_; } float* h_nextn() const { return h_; }
     float* mtp_logits() const { return mlogits_; } float* mtp_h() const { return mh_; }
@@ -72,7 +73,13 @@ private:
     int run_pass(int R, int nseq, int ngroups);              // trunk over the rows described by desc_ (already uploaded)
     int run_mtp(int R, int ngroups, const float* h_dev, int ldh, bool want_logits, bool kv_only = false);
     int upload_desc();
-    int enqueue_round(int slot, int n);
+    int enqueue_round(int S, int n);
+    int attn_rows_per_group() const;
+    int check_device_status();
+    int ep_ready();
+    void ep_destroy();
+    int sync_stream();                                       // wait for the engine's stream (bounded polling when collectives are in flight)
+    int fill_desc(const hp_slot_req* reqs, int S, int* rows, int* ngroups, bool with_seqs);
     int nattn() const; int ngdn() const;
     hp_model_cfg c_;
     std::vector<LayerW> layers_; LayerW mtp_;
@@ -89,11 +96,15 @@ private:
     float *pO_ = nullptr, *pm_ = nullptr, *pl_ = nullptr; int nsplit_max_ = 0;
     XQ8F xq_{nullptr, nullptr}, xq2_{nullptr, nullptr};
     float *rlogits_ = nullptr, *moe_w_ = nullptr, *moe_gu_ = nullptr, *moe_v_ = nullptr; int* moe_ids_ = nullptr; int* route_cnt_ = nullptr; Lin moe_out_;
-    int e_lo_ = 0, e_hi_ = 0, own_shared_ = 1, ep_world_ = 1, ep_rank_ = 0; void* nccl_comm_ = nullptr;
+    int e_lo_ = 0, e_hi_ = 0, own_shared_ = 1, ep_world_ = 1, ep_rank_ = 0; void* nccl_comm_ = nullptr; bool ep_failed_ = false;
     int *d_desc_ = nullptr, *h_desc_ = nullptr;                  // device / pinned host descriptor
     int *d_ids_ = nullptr, *d_mids_ = nullptr; float *d_vals_ = nullptr, *d_mvals_ = nullptr; void* am_scratch_ = nullptr;
     int *d_spec_ = nullptr, *h_spec_ = nullptr;                   // fused round state (device) / results (pinned host)
-    float* hpend_ = nullptr; int spec_pos_ = 0, spec_slot_ = -1;
+    int* d_specin_ = nullptr;                                     // the round's inputs: slot list, seeded substitutions
+    float *hpend_ = nullptr, *hstage_ = nullptr, *hprev_ = nullptr;   // per-slot pending h rows; gathered MTP inputs; per-slot last prompt h (prefill catch-up)
+    std::vector<int> spec_pos_, spec_on_;
+    void* topk_scratch_ = nullptr; int *d_topk_ids_ = nullptr; float* d_topk_vals_ = nullptr;
+    uint16_t* prof_kv_ = nullptr;                                 // K/V rows saved around profile_pass
     cudaGraphExec_t graphs_[64] = {}; bool warmed_[64] = {};
     int* err_ = nullptr;
     cudaStream_t s_ = nullptr; cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
@@ -101,5 +112,7 @@ private:
     size_t weight_bytes_ = 0; float last_ms_ = 0;
     int last_rows_ = 0, prof_skip_ = 0; bool gemv_only_ = false, tiled_ = true, keep_rowmajor_ = true; bool pdl_ = getenv("HIPSTER_B200_NO_PDL") == nullptr;
 };
+
+int ep_wait_poll(int (*stream_query)(void*), int (*comm_error)(void*), void* ctx, int limit_ms);
 
 }  // namespace hp

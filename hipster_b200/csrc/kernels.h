@@ -98,6 +98,11 @@ size_t attn_partial_floats(int ngroups, int n_kv, int nsplit_max);
 int attn_rope_kv(const AttnParams& p, int rows, cudaStream_t s);          // reference k_qk_norm_rope_kv (ops.hip:363-411)
 int attn_decode(const AttnParams& p, int rows, int ngroups, cudaStream_t s);   // reference attn_decode_mq (ops.h:72)
 
+// one sequence of R <= 8 rows at positions pos0.., descriptors and partials in caller-provided workspace
+size_t attn_seq_workspace_bytes(int R, int n_head, int n_kv, int max_ctx);
+int attn_decode_seq(float* qkv, int ld, int R, int pos0, int n_head, int n_kv, int n_rot, const void* q_norm, const void* k_norm, const void* rope, void* kc, void* vc, int max_ctx,
+                    float* out, XQ8F xq, float eps, void* workspace, cudaStream_t s);
+
 // ---- moe.cu ----
 // router (reference f32_gemv, fn.hip:252-277) and routing (k_moe_route, fn.hip:167-205) in one launch; counters: T zero-initialised ints (left zero)
 int router_route(const float* W, const float* x, float* logits, int* ids, float* w, int* counters, int E, int K, int k, int T, cudaStream_t s);
@@ -110,11 +115,17 @@ struct MoeParams {
 int moe_gemv_up(const MoeParams& p, cudaStream_t s);                  // reference gemv_moe, xrow_te = false (gemv.h:46)
 int moe_silu_quant(const float* gu, int F, const int* ids, int e_lo, int e_hi, int own_shared, XQ8F xq, int pairs, cudaStream_t s);   // fn.hip:206-211
 int moe_down_pairs(const MoeParams& p, cudaStream_t s);               // expert-parallel form: per-pair outputs, zeros for experts owned elsewhere
+// y[t] = sum over slots e in order of fmaf(slotw[t][e], v[(t, e)], acc) (reference combine, gemv.hip:1104-1112)
+int moe_combine(const float* v, const float* slotw, float* y, int T, int nslot, int E, cudaStream_t s);
 
 // ---- argmax.cu ----
 // per-row argmax (max value, lowest index) of logits [R][ld] -> ids/vals on device
 int argmax_rows(const float* logits, int R, int n, int ld, int* ids, float* vals, void* scratch, cudaStream_t s);
 size_t argmax_scratch_bytes(int R, int n);
+// per-row top-k (values descending, ties -> lower index; reference argmax_topk, ops.h:118) -> ids / vals [R][k] on device
+int topk_rows(const float* logits, int R, int n, int ld, int k, int* ids, float* vals, void* scratch, cudaStream_t s);
+size_t topk_scratch_bytes(int R, int n, int k);
+int topk_max_k();
 // allocation-free variant: partials in a static device array of fixed size (see argmax.cu)
 int argmax_rows_static(const float* logits, int R, int n, int ld, int* ids, float* vals, cudaStream_t s);
 int argmax_static_max_rows();

@@ -235,6 +235,15 @@ __global__ void __launch_bounds__(256) k_moe_silu_quant(const float* __restrict_
     warp_quant32_store(silu_det(gu[(size_t)pair * 2 * F + i]) * gu[(size_t)pair * 2 * F + F + i], pair, sb, F, q, sc, lane);
 }
 
+// in-order weighted combine of the per-(row, slot) expert outputs (gemv.hip:1104-1112); used by the kernel-level entry
+// point (inside the engine the combine runs in the norm kernel that follows)
+__global__ void __launch_bounds__(256) k_moe_combine(const float* __restrict__ v, const float* __restrict__ slotw, float* __restrict__ y, int nslot, int E) {
+    const int t = blockIdx.y, i = blockIdx.x * 256 + threadIdx.x; if (i >= E) return;
+    float acc = 0.f;
+    for (int e = 0; e < nslot; ++e) acc = fmaf(slotw[t * nslot + e], v[(size_t)(t * nslot + e) * E + i], acc);
+    y[(size_t)t * E + i] = acc;
+}
+
 }  // namespace
 
 int router_route(const float* W, const float* x, float* logits, int* ids, float* w, int* counters, int E, int K, int k, int T, cudaStream_t s) {
@@ -256,6 +265,11 @@ int moe_gemv_up(const MoeParams& p, cudaStream_t s) {
 int moe_silu_quant(const float* gu, int F, const int* ids, int e_lo, int e_hi, int own_shared, XQ8F xq, int pairs, cudaStream_t s) {
     HP_REQUIRE(F % 64 == 0 && pairs >= 1, "moe_silu_quant: bad shape");
     HP_CUDA(launch_pdl<8>(k_moe_silu_quant, dim3((F / 32 + 7) / 8, pairs), dim3(256), 0, s, gu, F, ids, e_lo, e_hi, own_shared, (int8_t*)xq.q, (float*)xq.sc));
+    HP_CUDA(cudaGetLastError()); return HP_OK;
+}
+int moe_combine(const float* v, const float* slotw, float* y, int T, int nslot, int E, cudaStream_t s) {
+    HP_REQUIRE(T >= 1 && nslot >= 1 && E >= 1, "moe_combine: bad shape");
+    k_moe_combine<<<dim3((E + 255) / 256, T), 256, 0, s>>>(v, slotw, y, nslot, E);
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 int moe_down_pairs(const MoeParams& p, cudaStream_t s) {

@@ -85,10 +85,17 @@ class Engine:
         buf = (ctypes.c_char * 128).from_buffer_copy(bytes(id128))
         check(lib().hp_ep_init(self._h, buf))
 
-    def topk(self, which, T):
-        ids = (ctypes.c_int * T)(); vals = (ctypes.c_float * T)()
-        check(lib().hp_topk(self._h, which, T, ids, vals))
-        return np.array(ids[:], dtype=np.int32), np.array(vals[:], dtype=np.float32)
+    def topk(self, which, T, k=1):
+        """Qwen35::topk: (ids, vals) of shape [T] for k = 1, [T][k] otherwise (values descending, ties -> lower id)."""
+        ids = (ctypes.c_int * (T * k))(); vals = (ctypes.c_float * (T * k))()
+        check(lib().hp_topk(self._h, which, T, k, ids, vals))
+        i = np.array(ids[:], dtype=np.int32); v = np.array(vals[:], dtype=np.float32)
+        return (i, v) if k == 1 else (i.reshape(T, k), v.reshape(T, k))
+
+    def prefill(self, slot, tokens, pos0=0, with_mtp=True):
+        """Qwen4Exp::prefill + mtp_catchup: commits the prompt; row 0 of logits / h_nextn / topk is the last prompt row."""
+        t = (ctypes.c_int * len(tokens))(*[int(x) for x in tokens])
+        check(lib().hp_prefill(self._h, slot, t, len(tokens), pos0, int(with_mtp)))
 
     def reset(self):
         check(lib().hp_reset(self._h))
@@ -165,12 +172,19 @@ class Engine:
         check(lib().hp_spec_begin(self._h, slot, int(id_last), int(pos), ctypes.c_void_p(h_pending_ptr)))
 
     def spec_round(self, slot, n_draft, subst=None):
-        out = (ctypes.c_int * (n_draft + 1))(); cnt = ctypes.c_int(0)
+        """One slot: the emitted tokens of the round."""
+        return self.spec_round_slots([slot], n_draft, None if subst is None else [subst])[0]
+
+    def spec_round_slots(self, slots, n_draft, subst=None):
+        """S slots in lock step; subst: per slot a list of n_draft substitutions (or None). -> per slot the emitted tokens."""
+        S = len(slots)
+        sl = (ctypes.c_int * S)(*[int(x) for x in slots])
+        out = (ctypes.c_int * (S * (n_draft + 1)))(); cnt = (ctypes.c_int * S)()
         sub = None
         if subst is not None:
-            sub = (ctypes.c_int * n_draft)(*[int(x) for x in subst])
-        check(lib().hp_spec_round(self._h, slot, n_draft, sub, out, ctypes.byref(cnt)))
-        return list(out[:cnt.value])
+            sub = (ctypes.c_int * (S * n_draft))(*[int(x) for row in subst for x in row])
+        check(lib().hp_spec_round(self._h, sl, S, n_draft, sub, out, cnt))
+        return [list(out[j * (n_draft + 1):j * (n_draft + 1) + cnt[j]]) for j in range(S)]
 
 
 def _memcpy_d2d(dst, src, nbytes):

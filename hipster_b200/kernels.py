@@ -92,3 +92,34 @@ def accept_greedy(ids, drafts):
 
 def device_status():
     check(lib().hp_device_status(_stream()))
+
+
+def attn_decode(qkv, pos0, n_head, n_kv, n_rot, q_norm, k_norm, rope, kc, vc, max_ctx, eps=1e-6, want_q8=True):
+    """GQA decode attention of one sequence: qkv f32 [R][ld] (normalised / rotated in place), rows at positions pos0 + r;
+    q_norm / k_norm bf16 [256] (int16 tensors), rope f32 [max_ctx][n_rot/2][2], kc / vc f16 [n_kv][max_ctx][256] (updated).
+    -> (out f32 [R][n_head*256], XQ8 of it or None). Reference: qk_norm_rope_kv + attn_decode_mq (ops.h:71-72,96)."""
+    L = lib()
+    L.hp_attn_workspace_bytes.restype = ctypes.c_size_t
+    R, ld = qkv.shape[0], qkv.stride(0)
+    ws = torch.empty(L.hp_attn_workspace_bytes(R, n_head, n_kv, max_ctx), dtype=torch.uint8, device=qkv.device)
+    out = torch.empty((R, n_head * 256), dtype=torch.float32, device=qkv.device)
+    xq = XQ8(R, n_head * 256, qkv.device) if want_q8 else None
+    check(L.hp_attn_decode(ptr(qkv), ld, R, int(pos0), n_head, n_kv, n_rot, ptr(q_norm), ptr(k_norm), ptr(rope), ptr(kc), ptr(vc), int(max_ctx), ptr(out),
+                           ptr(xq.q) if xq else None, ptr(xq.sc) if xq else None, ctypes.c_float(eps), ptr(ws), _stream()))
+    return out, xq
+
+
+def moe_layer(xn, router, exp_gate_up, exp_down, sh_gate_up, sh_down, F, n_expert, k):
+    """One mixture-of-experts FFN over the rows of xn f32 [T][E] -> (ids int32 [T][k+1], weights f32 [T][k+1], y f32 [T][E]).
+    Reference: Qwen4Exp::moe_layer (qwen4exp.cpp:345-354)."""
+    L = lib()
+    L.hp_moe_workspace_bytes.restype = ctypes.c_size_t
+    T, E = xn.shape
+    xq = quantize_x_q8(xn)
+    ws = torch.empty(L.hp_moe_workspace_bytes(T, E, F, n_expert, k), dtype=torch.uint8, device=xn.device)
+    ids = torch.empty((T, k + 1), dtype=torch.int32, device=xn.device)
+    w = torch.empty((T, k + 1), dtype=torch.float32, device=xn.device)
+    y = torch.empty((T, E), dtype=torch.float32, device=xn.device)
+    check(L.hp_moe_layer(ptr(xn), ptr(xq.q), ptr(xq.sc), ptr(router), ptr(exp_gate_up), ptr(exp_down), ptr(sh_gate_up), ptr(sh_down), T, E, F, n_expert, k,
+                         ptr(ids), ptr(w), ptr(y), ptr(ws), _stream()))
+    return ids, w, y

@@ -62,7 +62,9 @@ int hp_argmax(const float* logits_dev, int R, int n, int ld, int* ids_dev, float
  * hp_argmax_noalloc_max_rows() rows of hp_argmax_noalloc_max_n() entries and rejects larger shapes with HP_EINVAL.
  * It calls no allocating routine. The first call on each device resolves the array's address; make that call before
  * any stream capture begins. All calls share the one array: nothing in it has to be cleared between calls (every
- * element read is written first by the same call), but two calls that overlap on the GPU race on it. */
+ * element read is written first by the same call), but two calls that overlap on the GPU race on it. The stream must
+ * belong to the current device (a stream of another device is refused). Not thread-safe: the first call on a device
+ * records the address without a lock, so it must not run concurrently with another host thread's call. */
 int hp_argmax_noalloc(const float* logits_dev, int R, int n, int ld, int* ids_dev, float* vals_dev, void* stream);
 int hp_argmax_noalloc_max_rows(void);
 int hp_argmax_noalloc_max_n(void);
@@ -90,6 +92,29 @@ size_t hp_gdn_saved_floats(int n_v);
 int hp_gdn_layer(const float* rows_dev, int ld, int T, int n_replay, int n_qk, int n_v, const float* conv_w_dev, const void* dt_bias_bf16_dev, const void* a_neg_bf16_dev,
                  const void* norm_w_bf16_dev, float* state_dev, float* conv_state_dev, float* saved_dev, float* out_dev, void* xq_q_dev, void* xq_sc_dev,
                  float* snap_dev, float eps, int sigmoid_gate, void* stream);
+
+/* GQA decode attention for one sequence, as one call: per-head RMSNorm of q and k, NeoX RoPE on the first n_rot dims,
+ * f16 K/V cache write, causal attention over keys 0..pos (fixed 128-key splits merged in split order), sigmoid gate.
+ * qkv_dev [R][ld]: per row [n_head x (256 q | 256 gate) | n_kv x 256 k | n_kv x 256 v] (q and k are normalised and
+ * rotated in place); rows r = 0..R-1 (R <= 8) sit at positions pos0 + r. rope_dev: float (cos, sin) pairs
+ * [max_ctx][n_rot/2] of pos * base^(-2i/n_rot). k_cache_dev / v_cache_dev: f16 [n_kv][max_ctx][256]. out_dev f32
+ * [R][n_head*256] and/or its int8 quantisation (either may be NULL). workspace_dev: hp_attn_workspace_bytes(...) bytes.
+ * Replaces qk_norm_rope_kv + attn_decode_mq (ops.h:71-72,96; ops.hip:363-465,831-948). */
+size_t hp_attn_workspace_bytes(int R, int n_head, int n_kv, int max_ctx);
+int hp_attn_decode(float* qkv_dev, int ld, int R, int pos0, int n_head, int n_kv, int n_rot, const void* q_norm_bf16_dev, const void* k_norm_bf16_dev, const float* rope_dev,
+                   void* k_cache_dev, void* v_cache_dev, int max_ctx, float* out_dev, void* xq_q_dev, void* xq_sc_dev, float eps, void* workspace_dev, void* stream);
+/* One mixture-of-experts FFN for T <= 32 rows: exact f32 router over n_expert + 1 rows (row n_expert = the shared
+ * expert's gate), softmax top-k routing (ties -> lower id) renormalised over the k winners, slot k = the shared expert
+ * with weight sigmoid(logit[n_expert]); gate|up GEMV per (row, slot), silu * up + int8, down GEMV, and the weighted
+ * combine in slot order. xn_dev f32 [T][E] feeds the router, xq_* (hp_quantize_x_q8 of the same rows) the experts.
+ * Expert tensors are Q4_K, contiguous per tensor: gate|up [n_expert][2F][E/256 blocks], down [n_expert][E][F/256].
+ * Outputs: ids_dev / weights_dev [T][k+1] (id -1 = shared), y_dev f32 [T][E]. workspace_dev: hp_moe_workspace_bytes(...).
+ * Replaces f32_gemv + moe_route + gemv_moe + moe_silu_quant + gemv_moe_down (fn.h, gemv.h:43-50; fn.hip:167-277,
+ * gemv.hip:1075-1129; Qwen4Exp::moe_layer, qwen4exp.cpp:345-354). */
+size_t hp_moe_workspace_bytes(int T, int E, int F, int n_expert, int k);
+int hp_moe_layer(const float* xn_dev, const void* xq_q_dev, const void* xq_sc_dev, const float* router_dev, const void* exp_gate_up_dev, const void* exp_down_dev,
+                 const void* sh_gate_up_dev, const void* sh_down_dev, int T, int E, int F, int n_expert, int k, int* ids_dev, float* weights_dev, float* y_dev,
+                 void* workspace_dev, void* stream);
 
 /* ------------------------------------------------------------------ engine level (engine/src/qwen35.h, qwen4exp.h) */
 
@@ -133,9 +158,16 @@ int hp_accept(hp_engine* e, int slot, int m);
 /* MTP draft block over T (token, h) pairs at positions pos0.. of `slot`; h_dev [T][n_embd] device rows (may alias
  * hp_h_nextn_dev / hp_mtp_h_dev). Replaces Qwen35::mtp_forward (qwen35.h:68-70, qwen35.cpp:405-424). */
 int hp_mtp_forward(hp_engine* e, int slot, const int* tokens_host, const float* h_dev, int T, int pos0);
-/* Argmax of the first T rows of the target (which = 0) or MTP (which = 1) logits -> host arrays.
- * Replaces Qwen35::topk with k = 1 (qwen35.h:87, qwen35.cpp:426-430). */
-int hp_topk(hp_engine* e, int which, int T, int* ids_host, float* vals_host);
+/* Top-k (1 <= k <= 32) of the first T rows of the target (which = 0) or MTP (which = 1) logits -> host arrays
+ * ids_host / vals_host [T][k], values descending, ties -> lower id; vals_host may be NULL.
+ * Replaces Qwen35::topk (qwen35.h:87, qwen35.cpp:426-430; k_topk, ops.hip:702-716). */
+int hp_topk(hp_engine* e, int which, int T, int k, int* ids_host, float* vals_host);
+/* Prompt ingestion for one slot: n tokens at positions pos0.., committed (no accept needed). with_mtp != 0 also runs the
+ * MTP block over the same rows so that its KV cache covers the prompt; successive calls for one prompt must follow each
+ * other. Afterwards row 0 of hp_logits_dev / hp_h_nextn_dev (and hp_topk(0, 1, ...)) is the LAST prompt row.
+ * Replaces Qwen4Exp::prefill + mtp_catchup (qwen4exp.h:57-60,72-74) and Backend::prefill (front/serve.cpp:29); this
+ * build feeds the prompt through the verify path in chunks of 8 rows (the GEMM prefill path is not part of it). */
+int hp_prefill(hp_engine* e, int slot, const int* tokens_host, int n, int pos0, int with_mtp);
 const float* hp_logits_dev(const hp_engine* e);            /* qwen35.h:82 */
 const float* hp_h_nextn_dev(const hp_engine* e);           /* qwen35.h:83 */
 const float* hp_mtp_logits_dev(const hp_engine* e);        /* qwen35.h:84 */
@@ -150,6 +182,12 @@ int hp_mtp_forward_slots(hp_engine* e, const hp_slot_req* reqs, int S, const flo
  * the caller distributes them (e.g. through torch.distributed) and every rank calls hp_ep_init with the same bytes. */
 int hp_ep_unique_id(void* id128_out);
 int hp_ep_init(hp_engine* e, const void* id128);
+/* The wait the engine uses at the end of a pass that carries collectives, exposed so that an integrator can drive it with
+ * its own probes: polls stream_query(ctx) (0 = done, 1 = still running, else failed) and comm_error(ctx) (0 = healthy)
+ * for at most limit_ms, and returns HP_OK, HP_ECOMM (a failure was reported) or HP_ETIMEOUT (a peer stopped taking part).
+ * The engine applies it with cudaStreamQuery and ncclCommGetAsyncError (limit: HIPSTER_B200_EP_TIMEOUT_MS, default
+ * 30000), aborts its communicator on failure and then refuses further passes with HP_ESTATE. */
+int hp_ep_wait_poll(int (*stream_query)(void*), int (*comm_error)(void*), void* ctx, int limit_ms);
 /* Test/diagnostic access: device pointer and size of a generated tensor (layer = -1 for model-level tensors) and of a
  * slot's committed GDN state [gdn_v_heads][128][128] (pending accepts are applied first). */
 int hp_tensor_dev(const hp_engine* e, int layer, int kind, void** ptr_out, size_t* bytes_out);
@@ -157,19 +195,23 @@ int hp_gdn_state_dev(hp_engine* e, int slot, int gdn_layer, float** ptr_out, siz
 /* Measurement hooks (the reference's HIPSTER_TIMING categories, qwen35.h:95, qwen35.cpp:181-186): mean device time of
  * `reps` verify passes of R rows (what = 0), of only their GEMV launches (what = 1), or of passes that leave kernel
  * classes out to price them in place (what = 16 + mask: 1 GDN, 2 row norms, 4 attention, 8 SiLU, 16 gate|up, 32 down,
- * 64 LM head, 128 input projections, 256 other GEMVs; only the time means anything then); nothing is committed.
+ * 64 LM head, 128 input projections, 256 other GEMVs; only the time means anything then).
+ * The passes run on slot 0 at its current position; its context survives (pending accepts are applied first, the K/V rows
+ * written are put back), but the pass before the call can no longer be accepted.
  * hp_pass_weight_bytes: Q4_K bytes one trunk pass (mtp = 0) or one MTP-block pass (mtp = 1) reads, with or without the
  * LM head: the algorithmic bytes of the roofline. */
 int hp_profile_pass(hp_engine* e, int R, int what, int reps, float* ms_out);
 size_t hp_pass_weight_bytes(const hp_engine* e, int mtp, int with_head);
-/* The whole MTP round on the device: n_draft draft steps, one verify pass of n_draft+1 rows, argmax, greedy acceptance,
- * commit and MTP catch-up, with no logits or ids crossing to the host; only the emitted tokens come back.
- * hp_spec_begin seeds it with the last emitted token, its position and the pending hidden row (device pointer, n_embd).
- * subst_host (nullable, n_draft ints): >= 0 replaces that draft (seeded acceptance control), -1 keeps the MTP's argmax.
- * out_tokens_host receives the accepted drafts followed by the bonus token; *out_count = their number (mm + 1).
- * Replaces the host loop of engine/bench/spec27b.cpp:77-103. */
+/* The whole MTP round on the device, for S slots in lock step: n_draft draft steps (one row per slot each), one verify
+ * pass of S * (n_draft + 1) rows (<= 32), argmax, greedy acceptance per slot, commit and MTP catch-up, with no logits or
+ * ids crossing to the host; only the emitted tokens come back. hp_spec_begin seeds a slot with its last emitted token,
+ * that token's position and the pending hidden row (device pointer, n_embd floats).
+ * slot_ids_host: the S distinct slots taking part. subst_host (nullable, [S][n_draft] ints): >= 0 replaces that draft
+ * (seeded acceptance control), -1 keeps the MTP's argmax. out_tokens_host [S][n_draft + 1]: per slot the accepted drafts
+ * followed by the bonus token; out_counts_host [S] = their number (mm + 1).
+ * Replaces the host loops of engine/bench/spec27b.cpp:77-103 and engine/bench/batchfn.cpp:96-117. */
 int hp_spec_begin(hp_engine* e, int slot, int id_last, int pos, const float* h_pending_dev);
-int hp_spec_round(hp_engine* e, int slot, int n_draft, const int* subst_host, int* out_tokens_host, int* out_count);
+int hp_spec_round(hp_engine* e, const int* slot_ids_host, int S, int n_draft, const int* subst_host, int* out_tokens_host, int* out_counts_host);
 
 #ifdef __cplusplus
 }

@@ -291,6 +291,20 @@ extern "C" void orc_argmax(const float* logits, int R, int n, int ld, int* ids, 
     }
 }
 // spec27b.cpp:92-97
+// top-k per row: k rounds of a masked arg-max, strict > from the lowest index (ops.hip:702-716: values descending,
+// ties -> lower index; an entry equal to -inf is never selected: id -1)
+extern "C" void orc_topk(const float* logits, int R, int n, int ld, int k, int* ids, float* vals) {
+    std::vector<char> taken(n);
+    for (int r = 0; r < R; ++r) {
+        std::fill(taken.begin(), taken.end(), 0);
+        const float* x = logits + (size_t)r * ld;
+        for (int j = 0; j < k; ++j) {
+            float bv = -INFINITY; int bi = -1;
+            for (int i = 0; i < n; ++i) if (!taken[i] && x[i] > bv) { bv = x[i]; bi = i; }
+            ids[(size_t)r * k + j] = bi; vals[(size_t)r * k + j] = bv; if (bi >= 0) taken[bi] = 1;
+        }
+    }
+}
 extern "C" int orc_accept(const int* ids, const int* drafts, int n_draft, int* bonus) {
     int mm = 0; while (mm < n_draft && ids[mm] == drafts[mm]) ++mm;
     if (bonus) *bonus = ids[mm];

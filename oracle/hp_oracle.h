@@ -56,6 +56,8 @@ void orc_gemv_q4k_double(const uint8_t* W, const float* x, double* y, double* ma
 
 /* ---- argmax + greedy acceptance: ops.hip:702-716 (max value, lowest index), spec27b.cpp:92-97 ---- */
 void orc_argmax(const float* logits, int R, int n, int ld, int* ids, float* vals);
+/* top-k per row (ops.hip:702-716): ids / vals [R][k], values descending, ties -> lower index */
+void orc_topk(const float* logits, int R, int n, int ld, int k, int* ids, float* vals);
 /* ids [n_draft+1] = target argmax per verify row; returns mm = accepted drafts; *bonus = ids[mm] */
 int orc_accept(const int* ids, const int* drafts, int n_draft, int* bonus);
 

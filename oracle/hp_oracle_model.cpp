@@ -293,6 +293,10 @@ extern "C" void orc_gemv_q4k_q8_seq(const uint8_t* W, const int8_t* q, const flo
     }
 }
 
+// helpers for the Python restatement of one MoE layer: act = silu(g) * u (fn.hip:206-211), acc = fmaf(w, v, acc) (gemv.hip:1104-1112)
+extern "C" void orc_silu_mul(const float* gu, float* act, int F) { for (int i = 0; i < F; ++i) act[i] = orc_silu(gu[i]) * gu[F + i]; }
+extern "C" void orc_fma_rows(float* acc, const float* v, float w, int n) { for (int i = 0; i < n; ++i) acc[i] = fmaf(w, v[i], acc[i]); }
+
 // ---------------------------------------------------------------- engine (engine/src/qwen35.cpp restated on the CPU)
 struct OrcCfg {   // mirrors hp_model_cfg field for field
     int n_embd, n_layer, n_ff, n_vocab, n_head, n_head_kv, n_rot, gdn_qk_heads, gdn_v_heads, attn_every, max_ctx, n_slots;

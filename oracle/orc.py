@@ -181,3 +181,80 @@ def gdn_rows(rows, n_qk, n_v, conv_w, dt_bias, a_neg, norm_w, state, conv_hist, 
     lib().orc_gdn_rows(P(rows), ld, T, n_qk, n_v, P(conv_w), P(dt_bias), P(a_neg), P(norm_w), P(state), P(conv_hist), P(out),
                        P(snap) if want_snap else ctypes.c_void_p(0), ctypes.c_float(eps), int(sigmoid_gate))
     return out, snap
+
+
+def topk(logits, k):
+    logits = np.ascontiguousarray(logits, dtype=np.float32); R, n = logits.shape
+    ids = np.empty((R, k), dtype=np.int32); vals = np.empty((R, k), dtype=np.float32)
+    lib().orc_topk(P(logits), R, n, n, k, P(ids), P(vals))
+    return ids, vals
+
+
+def rope_table(max_ctx, n_rot, base):
+    """(cos, sin) of pos * base^(-2i/n_rot) computed in double precision and rounded to f32, [max_ctx][n_rot/2][2]."""
+    half = n_rot // 2
+    p = np.arange(max_ctx, dtype=np.float64)[:, None]
+    th = p * np.power(np.float64(np.float32(base)), -2.0 * np.arange(half, dtype=np.float64) / n_rot)[None, :]
+    return np.stack([np.cos(th), np.sin(th)], axis=-1).astype(np.float32)
+
+
+def attn_row(qkv_row, n_head, n_kv, n_rot, qw, kw, rope, pos, kc, vc, max_ctx, eps):
+    """Bit-exact restatement of the attention step for one row (updates qkv_row, kc, vc in place) -> out [n_head*256]."""
+    out = np.empty(n_head * 256, dtype=np.float32)
+    lib().orc_attn_row(P(qkv_row), n_head, n_kv, n_rot, P(qw), P(kw), P(rope), int(pos), P(kc), P(vc), int(max_ctx), P(out), ctypes.c_float(eps))
+    return out
+
+
+def moe_layer(xn, router, exp_gate_up, exp_down, sh_gate_up, sh_down, E, F, n_expert, k):
+    """Bit-exact restatement of one MoE FFN (router -> route -> per-(row, slot) expert GEMVs -> combine in slot order).
+    -> (ids [T][k+1], w [T][k+1], y [T][E])."""
+    L = lib()
+    xn = np.ascontiguousarray(xn, dtype=np.float32); T = xn.shape[0]; ns = k + 1
+    lg = np.empty((T, n_expert + 1), dtype=np.float32)
+    L.orc_router_gemv(P(router), P(xn), P(lg), n_expert + 1, E, T)
+    ids = np.empty((T, ns), dtype=np.int32); w = np.empty((T, ns), dtype=np.float32)
+    L.orc_moe_route(P(lg), P(ids), P(w), T, n_expert, k)
+    q, d, s = quantize_x_q8(xn)
+    eb_up = 2 * F * (E // 256) * 144; eb_dn = E * (F // 256) * 144
+    y = np.zeros((T, E), dtype=np.float32)
+    gu = np.empty(2 * F, dtype=np.float32); v = np.empty(E, dtype=np.float32)
+    sil = L.orc_silu
+    for t in range(T):
+        acc = np.zeros(E, dtype=np.float32)
+        for e in range(ns):
+            i = int(ids[t, e])
+            Wu = exp_gate_up[i * eb_up:(i + 1) * eb_up] if i >= 0 else sh_gate_up
+            Wd = exp_down[i * eb_dn:(i + 1) * eb_dn] if i >= 0 else sh_down
+            L.orc_gemv_q4k_q8_seq(P(Wu), P(q[t]), P(d[t]), P(s[t]), P(gu), 2 * F, E)
+            act = np.empty((1, F), dtype=np.float32)
+            L.orc_silu_mul(P(gu), P(act), F)
+            aq, ad, as_ = quantize_x_q8(act)
+            L.orc_gemv_q4k_q8_seq(P(Wd), P(aq), P(ad), P(as_), P(v), E, F)
+            L.orc_fma_rows(P(acc), P(v), ctypes.c_float(float(w[t, e])), E)
+        y[t] = acc
+    return ids, w, y, lg
+
+
+# ---- independent double-precision transcriptions of the reference's device source (hp_oracle_ref64.cpp): tolerance checks
+def ref64_gdn_rows(rows, n_qk, n_v, conv_w, dt_bias, a_neg, norm_w, state, conv_hist, eps, sigmoid_gate):
+    """rows f32 [T][ld]; conv_w / dt_bias / a_neg / norm_w f32; state f64 [n_v][128][128] and conv_hist f64 [3][C] are
+    updated in place -> out f64 [T][n_v*128]."""
+    rows = np.ascontiguousarray(rows, dtype=np.float32); T, ld = rows.shape
+    out = np.empty((T, n_v * 128), dtype=np.float64)
+    lib().ref64_gdn_rows(P(rows), ld, T, n_qk, n_v, P(conv_w), P(dt_bias), P(a_neg), P(norm_w), P(state), P(conv_hist), P(out), ctypes.c_double(eps), int(sigmoid_gate))
+    return out
+
+
+def ref64_attn_row(qkv_row, n_head, n_kv, n_rot, qw, kw, base, pos, kc, vc, max_ctx, eps):
+    """qkv_row f32 (not modified); qw / kw f32; kc / vc f32 [n_kv][max_ctx][256] holding f16-representable values,
+    updated in place -> out f64 [n_head*256]."""
+    out = np.empty(n_head * 256, dtype=np.float64)
+    lib().ref64_attn_row(P(qkv_row), n_head, n_kv, n_rot, P(qw), P(kw), ctypes.c_float(base), int(pos), P(kc), P(vc), int(max_ctx), P(out), ctypes.c_double(eps))
+    return out
+
+
+def ref64_moe_route(logits, E, k):
+    logits = np.ascontiguousarray(logits, dtype=np.float32); T = logits.shape[0]
+    ids = np.empty((T, k + 1), dtype=np.int32); w = np.empty((T, k + 1), dtype=np.float64)
+    lib().ref64_moe_route(P(logits), P(ids), P(w), T, E, k)
+    return ids, w

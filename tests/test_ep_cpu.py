@@ -106,3 +106,73 @@ def test_expert_ranges_partition_the_experts():
             seen += list(range(lo, hi))
         assert seen == list(range(512))
         assert ep.owner_of(511, world, 512) == world - 1
+
+
+# ---- the bounded wait of the engine (hp_ep_wait_poll) with host-made failures: no GPU, no NCCL
+QUERY = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p)
+
+
+def _poll(query, comm_error, limit_ms):
+    import hipster_b200 as hb
+    L = hb.lib()
+    q = QUERY(query); c = QUERY(comm_error) if comm_error else ctypes.cast(None, QUERY)
+    rc = L.hp_ep_wait_poll(q, c, None, limit_ms)
+    return rc, L.hp_last_error().decode()
+
+
+def test_wait_poll_returns_ok_when_the_stream_drains():
+    calls = {"n": 0}
+
+    def query(_):
+        calls["n"] += 1
+        return 0 if calls["n"] >= 4 else 1
+    rc, _ = _poll(query, lambda _: 0, 2000)
+    assert rc == 0 and calls["n"] == 4
+
+
+def test_wait_poll_reports_a_communicator_error_as_ecomm():
+    rc, msg = _poll(lambda _: 1, lambda _: 3, 2000)          # a fake of ncclCommGetAsyncError returning a failure code
+    assert rc == 6 and "asynchronous error 3" in msg
+    rc, msg = _poll(lambda _: 9, None, 2000)                 # a fake of cudaStreamQuery returning a failure
+    assert rc == 6 and "status 9" in msg
+
+
+def test_wait_poll_gives_up_after_the_time_limit():
+    import time
+    t0 = time.perf_counter()
+    rc, msg = _poll(lambda _: 1, lambda _: 0, 150)           # the stream never drains: a peer stopped taking part
+    dt = time.perf_counter() - t0
+    assert rc == 4 and "stopped taking part" in msg and 0.1 < dt < 5.0
+
+
+def _wait_worker(rank, port, out):
+    """Rank 1 leaves without ever posting its contribution; rank 0 waits for it with the engine's bounded wait, its probe
+    being "has the peer's message arrived in the store?". The wait must end with a time-out status, not hang."""
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=2)
+    store = dist.distributed_c10d._get_default_store()
+    if rank == 1:
+        store.set("rank1_alive", "1")        # joins, then exits between steps without posting "contribution"
+        dist.destroy_process_group()
+        return
+    store.wait(["rank1_alive"])
+
+    def query(_):
+        return 0 if store.check(["contribution"]) else 1
+    rc, msg = _poll(query, lambda _: 0, 400)
+    out[0] = (rc, msg)
+    dist.destroy_process_group()
+
+
+def test_wait_poll_times_out_when_a_gloo_peer_leaves():
+    ctx = mp.get_context("spawn")
+    mgr = ctx.Manager(); out = mgr.dict()
+    port = 31500 + (os.getpid() % 2000)
+    procs = [ctx.Process(target=_wait_worker, args=(r, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert out[0][0] == 4 and "stopped taking part" in out[0][1]

@@ -9,6 +9,7 @@ import torch
 
 import hipster_b200 as hb
 from hipster_b200 import kernels as K_
+from oracle import orc
 
 pytestmark = pytest.mark.gpu
 
@@ -26,6 +27,12 @@ def test_noalloc_argmax_matches_argmax_on_two_calls_in_a_row():
         torch.cuda.synchronize()
         assert torch.equal(got_ids, want_ids)
         assert np.array_equal(got_vals.cpu().numpy().view(np.uint32), want_vals.cpu().numpy().view(np.uint32))
+        # and directly against independent checkers: the CPU oracle and numpy (first maximum = lowest index on ties)
+        oi, ov = orc.argmax(a)
+        assert np.array_equal(got_ids.cpu().numpy(), oi) and np.array_equal(got_vals.cpu().numpy().view(np.uint32), ov.view(np.uint32))
+        assert np.array_equal(got_ids.cpu().numpy(), np.argmax(a, axis=1).astype(np.int32))
+        if a is first:
+            assert int(got_ids[2]) == 11            # the planted tie between columns 11 and 200000, in different partial blocks
     assert int(got_ids[0]) == 70000
 
 
