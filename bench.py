@@ -1,6 +1,6 @@
 """Benchmark of the MTP speculative-decode hot path on B200.
 
-python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload dense27b|gemv]
+python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload dense27b|moe|moe-ep|gemv]
 
 Prints ONE JSON line (rank 0). A "step" is one MTP round (n draft steps, one verify pass of n+1 rows, device argmax +
 greedy acceptance, commit, MTP catch-up) over seeded synthetic input. Workloads:
@@ -8,7 +8,10 @@ greedy acceptance, commit, MTP catch-up) over seeded synthetic input. Workloads:
             seeded acceptance 0.7 (default; the metric is quoted on this configuration and it fits one GPU)
   gemv      benchmark configuration 1: Q4_K 17408 x 5120 verify GEMV over 3 rows + argmax + greedy acceptance
 L2: every step streams 20 GB of weights, far beyond the 126 MB L2 (dense27b); the gemv workload rotates weight copies.
-N > 1 runs N independent replicas of the dense path (the dense trunk does not shard: "replicas only").
+  moe       benchmark configuration 4 (one slot of the MoE model, MTP n=2); moe-ep: configuration 5 alone
+N > 1 runs N independent replicas of the dense path (the dense trunk does not shard: "replicas only"); `value` is their
+aggregate. The one partition the path has, configuration 5 (8 slots in lock-step MTP n=2 rounds, routed experts sharded
+over the N GPUs, one exchange per MoE layer), is measured in the same run and reported in the line's `ep` block, at N = 1 too.
 """
 import argparse
 import json
@@ -35,9 +38,33 @@ WORKLOADS = {
 }
 
 
-GEMV_TRAFFIC_RATIO = 1.033   # DRAM bytes / algorithmic weight bytes of k_gemv_q4k_sk, from the ncu capture under profiles/
-# kernel launches of one round (counted from the ncu launch lists under profiles/)
-ROUND_LAUNCHES = {"dense27b": 653, "moe": 510}
+# measured constants that the line quotes (DRAM bytes / algorithmic bytes of the GEMV from an ncu capture): bench_data.json
+BENCH_DATA = json.load(open(os.path.join(ROOT, "bench_data.json")))
+GEMV_TRAFFIC_RATIO = BENCH_DATA["gemv_dram_bytes_over_algorithmic_bytes"]
+# The model shapes as plain data, for the CPU arm (which loads nothing of the CUDA library): the same numbers as
+# hp_model_preset("qwen35-27b") (struct Qwen35Dims, engine/src/qwen35.h:15-26).
+PRESET_27B = dict(n_embd=5120, n_layer=64, n_ff=17408, n_vocab=248320, n_head=24, n_head_kv=4, n_rot=64, gdn_qk_heads=16, gdn_v_heads=48,
+                  attn_every=4, max_ctx=8192, n_slots=1, n_expert=0, n_expert_used=0, expert_ff=0, gdn_sigmoid_gate=0, has_mtp=1,
+                  ep_rank=0, ep_world=1, rms_eps=1e-6, rope_base=1e7, seed=27)
+
+
+class Halton:
+    """Seeded low-discrepancy stream for the draft substitutions: successive calls walk the dimensions (one per draft
+    position of a round), so that over a few dozen rounds the share of rounds accepting k drafts is close to rate^k and
+    the emitted tokens per round close to their expectation (a pseudo-random draw of 20 rounds is off by several %)."""
+    PRIMES = (2, 3, 5, 7, 11, 13, 17)
+
+    def __init__(self, dims, start=20):
+        self.dims, self.i, self.d = dims, start, 0
+
+    def random(self):
+        b = self.PRIMES[self.d]; f, r, i = 1.0, 0.0, self.i
+        while i > 0:
+            f /= b; r += f * (i % b); i //= b
+        self.d += 1
+        if self.d == self.dims:
+            self.d = 0; self.i += 1
+        return r
 
 
 def peaks():
@@ -101,54 +128,54 @@ def expected_tokens_per_round(n, p):
 
 
 # ------------------------------------------------------------------------------------------ CPU arm (oracle port)
-def cpu_round_layers(rounds, warm, n_layer):
-    """The CPU restatement of the reference engine on the host cores, on a BOUNDED sample of the dense27b workload:
-    a 27B-shaped model cut to n_layer layers (3 GDN + 1 attention per four, full widths, full 248320 vocabulary, MTP
-    block), short context. One step = one MTP round (5 draft steps + 6-row verify + accept + catch-up)."""
-    import hipster_b200 as hb
+class _Cfg:
+    def __init__(self, d):
+        self.__dict__.update(d)
+
+
+def cpu_rounds(rounds, warm, budget_s=150.0, n_layer=0):
+    """The CPU restatement of the reference engine on the host cores: real MTP rounds (5 draft steps, 6-row verify, accept,
+    catch-up) of the FULL 64-layer 27B-shaped model, full widths and vocabulary, every host thread. The bounded part of
+    the sample is the context (a 4-token prefix instead of the 4096-token prompt: attention is ~2 % of a round's bytes)
+    and the number of rounds. Returns (seconds per round, rounds timed, threads)."""
     from oracle import orc
-    cfg = hb.ModelCfg.preset("qwen35-27b", n_layer=n_layer, max_ctx=256)
+    cfg = _Cfg(dict(PRESET_27B, max_ctx=256))
+    if n_layer:
+        cfg.n_layer = n_layer                        # reduced depth: only for quick self-checks of this script, and said so in the line
     m = orc.Model(cfg)
-    E = cfg.n_embd
     m.forward([(0, [11, 12, 13, 14], 0)]); m.accept(0, 4)
-    id_last, pos = 15, 4
-    h_pending = m.h_nextn(4)[3].copy()
+    st = dict(id_last=15, pos=4, h=m.h_nextn(4)[3].copy())
 
     def one_round():
-        nonlocal id_last, pos, h_pending
-        tok, h = id_last, h_pending[None, :]
-        drafts = []
+        tok, h, drafts = st["id_last"], st["h"][None, :], []
         for i in range(N_DRAFT):
-            m.mtp_forward(0, [tok], h, pos + i)
+            m.mtp_forward(0, [tok], h, st["pos"] + i)
             tok = int(orc.argmax(m.mtp_logits(1))[0][0]); drafts.append(tok); h = m.mtp_h(1)
-        m.forward([(0, [id_last] + drafts, pos)])
+        m.forward([(0, [st["id_last"]] + drafts, st["pos"])])
         ids = orc.argmax(m.logits(N_DRAFT + 1))[0]
-        mm = 2                                       # fixed acceptance for the timing sample
+        mm = 2                                       # fixed acceptance for the timing sample (a round costs the same whatever it accepts)
         m.accept(0, mm + 1)
-        m.mtp_forward(0, drafts[:mm], m.h_nextn(mm), pos + 1)
-        h_pending = m.h_nextn(mm + 1)[mm].copy()
-        id_last = int(ids[mm]); pos += mm + 1
+        m.mtp_forward(0, drafts[:mm], m.h_nextn(mm), st["pos"] + 1)
+        st.update(h=m.h_nextn(mm + 1)[mm].copy(), id_last=int(ids[mm]), pos=st["pos"] + mm + 1)
+    t_all = time.perf_counter(); warmed = 0
     for _ in range(warm):
-        one_round()
-    t0 = time.perf_counter()
-    for _ in range(rounds):
-        one_round()
-    dt = (time.perf_counter() - t0) / rounds
+        one_round(); warmed += 1
+        if time.perf_counter() - t_all > budget_s / 4:
+            break
+    done = 0; t0 = time.perf_counter()
+    while done < rounds:
+        one_round(); done += 1
+        if time.perf_counter() - t_all > budget_s:
+            break
+    dt = (time.perf_counter() - t0) / done
+    th = orc.lib().orc_num_threads()
     del m
-    return dt, orc.lib().orc_num_threads()
+    return dt, done, th, warmed
 
 
-def cpu_round_sample(rounds, warm):
-    """Round time of the full 64-layer model on the host cores, extrapolated from two bounded samples: the same round on
-    the model cut to 4 and to 8 layers gives the time of four more layers; 64 layers = t4 + 15 * (t8 - t4)."""
-    t4, th = cpu_round_layers(rounds, warm, 4)
-    t8, _ = cpu_round_layers(rounds, warm, 8)
-    return t4 + 15.0 * (t8 - t4), th
-
-
-CPU_SAMPLE = ("CPU restatement of the reference engine (its HIP kernels cannot be built without ROCm), one MTP round n=5 on a 27B-shaped "
-              "model (full widths, full vocabulary, MTP block, context < 64) cut to 4 and to 8 of its 64 layers; the 64-layer round time is "
-              "extrapolated as t4 + 15 * (t8 - t4); tokens/s = 2.941 expected tokens per round / that time")
+CPU_SAMPLE = ("CPU restatement of the reference engine (its HIP kernels cannot be built without ROCm): real MTP rounds n=5 of the full 64-layer "
+              "27B-shaped model (full widths, full vocabulary, MTP block) on all host threads, context < 128 instead of 4096; "
+              "tokens/s = 2.941 expected tokens per round / measured seconds per round")
 
 
 def run_reference(args, rank, world):
@@ -157,13 +184,15 @@ def run_reference(args, rank, world):
     # all the host threads this process may use (a launcher may have pinned OpenMP to one thread); set before the
     # oracle library, and with it the OpenMP runtime, is loaded
     os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
-    k = max(1, min(args.steps, 5)); w = 1
-    dt, th = cpu_round_sample(k, w)
+    dt, done, th, warmed = cpu_rounds(max(1, args.steps), args.warmup, n_layer=args.layers)
     v = expected_tokens_per_round(N_DRAFT, ACCEPT_RATE) / dt
-    return {"impl": "reference", "metric": METRIC, "value": v, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+    sample = CPU_SAMPLE + f"; {warmed} warm-up + {done} timed rounds (of --warmup {args.warmup} --steps {args.steps}: bounded to ~150 s)"
+    if args.layers:
+        sample = sample.replace("full 64-layer", f"{args.layers}-layer cut of the 64-layer")
+    return {"impl": "reference", "metric": METRIC, "value": v, "unit": "tokens/s", "n_gpus": world, "steps": done, "warmup": warmed,
             "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u4 x i8 -> i32, f32 epilogue/state", "data": "synthetic",
             "config": dense_config(world),
-            "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": th, "kind": "port", "sample": CPU_SAMPLE + f"; {k} timed rounds"},
+            "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": th, "kind": "port", "sample": sample},
             "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
 
 
@@ -223,7 +252,7 @@ def run_dense(args, rank, local_rank, world):
     assert id_last == plain[0]
     eng.spec_begin(0, id_last, pos, eng.h_nextn_ptr() + (T_last - 1) * E * 4)
     out = [id_last]
-    srng = np.random.default_rng(99 + rank)
+    srng = Halton(n)
     t_setup = time.perf_counter() - t_setup
 
     def one_round():
@@ -248,6 +277,8 @@ def run_dense(args, rank, local_rank, world):
     torch.cuda.profiler.stop()
     clocks = sampler.stop() if sampler else None
     exact = out[:len(plain)] == plain[:len(out)]
+    round_kernels = eng.last_round_kernels()
+    finite = bool(np.isfinite(eng.topk(0, n + 1)[1]).all())     # the verify rows' top logits (random-init weights must not blow up)
     # dominant kernel alone: the GEMV launches of one 6-row verify pass, CUDA events on the engine's stream
     gemv_ms = eng.profile_pass(n + 1, 1, 5)
     pass_ms = eng.profile_pass(n + 1, 0, 5)
@@ -277,51 +308,57 @@ def run_dense(args, rank, local_rank, world):
         "config": dense_config(world, args.workload),
         "e2e": {"value": toks / (wall_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 4 * n, "d2h_bytes_per_step": 256,
                 "note": "hp_spec_round with host token buffers; wall clock over the timed rounds, one stream synchronise per round"},
-        "gpu_launches": args.steps * world * ROUND_LAUNCHES.get(args.workload, 0) if not args.layers else None,
+        "gpu_launches": args.steps * world * round_kernels,
+        "value_at_expected_acceptance": world * expected_tokens_per_round(n, rate) / (dev_ms / args.steps / 1e3),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"], "traffic": verify_bytes * GEMV_TRAFFIC_RATIO,
-                     "traffic_note": "ncu dram read+write of the four GEMV launches of one layer / their weight bytes (profiles/gemv_q4k_sk_dense27b_layer.md), scaled to the pass",
+                     "traffic_note": "algorithmic bytes x the DRAM-bytes / algorithmic-bytes ratio of an ncu capture of this kernel (bench_data.json)",
                      "kernel": "k_gemv_q4k_sk: all GEMV launches of one 6-row verify pass (129 launches + LM head), timed alone with CUDA events",
                      "algorithmic_bytes": verify_bytes, "ms": gemv_ms, "full_pass_ms": pass_ms, "peak_source": pk["_src"],
                      "bytes_per_token_roofline": {"round_bytes": round_bytes, "tokens_per_round": tok_per_round, "bytes_per_token": bytes_per_token,
                                                   "roofline_tokens_per_s": world * pk["hbm_gbs"] * 1e9 / bytes_per_token, "frac_of_roofline": value / (world * pk["hbm_gbs"] * 1e9 / bytes_per_token)}},
         "clocks": clocks,
-        "checks": {"spec_stream_equals_plain_greedy": bool(exact), "tokens": int(toks), "accepted_drafts_per_round": tok_per_round - 1, "prompt_len": prompt_len, "setup_s": t_setup},
+        "checks": {"spec_stream_equals_plain_greedy": bool(exact), "logits_finite": finite, "tokens": int(toks), "accepted_drafts_per_round": tok_per_round - 1,
+                   "expected_tokens_per_round": expected_tokens_per_round(n, rate), "kernels_per_round": round_kernels, "prompt_len": prompt_len, "setup_s": t_setup},
     }
-    if world == 1 and not args.no_cpu:
-        dt, th = cpu_round_sample(3, 1)
-        line["cpu_baseline"] = {"value": expected_tokens_per_round(n, rate) / dt, "unit": "tokens/s", "cores": th, "kind": "port", "sample": CPU_SAMPLE + "; 3 timed rounds"}
     return line
 
 
 # ------------------------------------------------------------------------------------------ moe-ep (config 5)
-def run_moe_ep(args, rank, local_rank, world):
+EP_WORKLOAD = ("config5: Flash-Next-shaped MoE (48 layers, hidden 2048, 512 experts top-10 + shared, expert FFN 512, vocab 248320), 8 slots x distinct "
+               "2048-token seeded prompts, lock-step MTP n=2 (24 verify rows per pass), seeded acceptance 0.7, aggregate tokens/s")
+
+
+def run_moe_ep(args, rank, local_rank, world, steps=None, warmup=None):
     """Config 5: the Flash-Next-shaped MoE model, 8 slots with distinct seeded prompts in lock-step MTP n=2 rounds
-    (24 verify rows per pass; engine/bench/batchfn.cpp:96-117), routed experts sharded over the `world` GPUs, one NCCL
-    exchange per MoE layer. Every rank runs the same loop (the trunk is replicated); value = aggregate tokens/s."""
+    (engine/bench/batchfn.cpp:96-117) through the fused multi-slot round hp_spec_round, routed experts sharded over the
+    `world` GPUs with one exchange per MoE layer. Every rank runs the same rounds (the trunk is replicated);
+    value = aggregate tokens/s of the 8 slots. Returns the `ep` block (rank 0) or None."""
     import torch
     import torch.distributed as dist
     import hipster_b200 as hb
     from hipster_b200 import ep
     from hipster_b200.engine import _as_tensor
     torch.cuda.set_device(local_rank)
+    steps = steps or args.steps; warmup = warmup or args.warmup
     n, rate, S = 2, ACCEPT_RATE, 8
     prompt_len = args.prompt_len or 2048
-    cfg = hb.ModelCfg.preset(args.preset or "flash-next", n_slots=S, ep_rank=rank, ep_world=world)
+    cfg = hb.ModelCfg.preset("flash-next", n_slots=S, ep_rank=rank, ep_world=world)
+    if args.layers:
+        cfg.n_layer = args.layers
     eng = hb.Engine(cfg)
     if world > 1:
         eng.ep_init(ep.broadcast_unique_id(dist, rank))
     E = cfg.n_embd
     hview = _as_tensor(eng.h_nextn_ptr(), 32 * E * 4).view(torch.float32).view(32, E)
-    mhview = _as_tensor(eng.mtp_h_ptr(), 32 * E * 4).view(torch.float32).view(32, E)
     hbuf = torch.zeros((32, E), dtype=torch.float32, device="cuda")
-    hpend = torch.zeros((S, E), dtype=torch.float32, device="cuda")
     prompts = [[int(x) for x in np.random.default_rng(1000 + s).integers(0, cfg.n_vocab, size=prompt_len)] for s in range(S)]
-    rounds = args.warmup + args.steps
+    rounds = warmup + steps
     n_plain = rounds * (n + 1) + n + 2
 
     def prefill_all(with_mtp):
+        """all slots together, 4 rows per slot per pass (32 rows); the MTP block follows with the shifted hidden rows"""
         prev = [None] * S
-        for p0 in range(0, prompt_len, 4):          # 4 rows per slot per pass: 32 rows
+        for p0 in range(0, prompt_len, 4):
             T = min(4, prompt_len - p0)
             eng.forward([(s, prompts[s][p0:p0 + T], p0) for s in range(S)])
             for s in range(S):
@@ -335,8 +372,7 @@ def run_moe_ep(args, rank, local_rank, world):
                     prev[s] = hview[s * T + T - 1].clone()
                 torch.cuda.synchronize()
                 eng.mtp_forward_slots([(s, prompts[s][p0:p0 + T], p0) for s in range(S)], hbuf.data_ptr())
-        T_last = (prompt_len - 1) % 4 + 1
-        return T_last
+        return (prompt_len - 1) % 4 + 1
 
     t_setup = time.perf_counter()
     # plain greedy streams of all slots, computed in lock-step T=1 passes (each slot's rows are independent of the others)
@@ -353,80 +389,89 @@ def run_moe_ep(args, rank, local_rank, world):
     eng.reset()
     T_last = prefill_all(True)
     ids = eng.topk(0, S * T_last)[0]
-    torch.cuda.synchronize()
-    for s in range(S):
-        hpend[s] = hview[s * T_last + T_last - 1]
     out = [[int(ids[s * T_last + T_last - 1])] for s in range(S)]
-    pos = [prompt_len] * S
-    srng = np.random.default_rng(7)
+    for s in range(S):
+        eng.spec_begin(s, out[s][0], prompt_len, eng.h_nextn_ptr() + (s * T_last + T_last - 1) * E * 4)
+    srng = Halton(n)
+    slots = list(range(S))
     t_setup = time.perf_counter() - t_setup
 
     def one_round():
-        drafts = [[] for _ in range(S)]
-        toks = [out[s][-1] for s in range(S)]
-        hptr = hpend.data_ptr()
-        for i in range(n):                           # draft, chained on the MTP's own h (batchfn.cpp:98-104)
-            eng.mtp_forward_slots([(s, [toks[s]], pos[s] + i) for s in range(S)], hptr)
-            ids = eng.topk(1, S)[0]
-            for s in range(S):
-                k = len(out[s]) - 1
-                good = plain[s][k + 1 + i]
-                d = good if srng.random() < rate else (good + 1) % cfg.n_vocab   # seeded substitution
-                drafts[s].append(d); toks[s] = d
-            hptr = eng.mtp_h_ptr()
-        eng.forward([(s, [out[s][-1]] + drafts[s], pos[s]) for s in range(S)])   # verify: 24 rows
-        ids = eng.topk(0, S * (n + 1))[0]
-        emitted = 0; reqs = []; rows = []
+        # seeded substitution of every draft (the same stream on every rank)
+        sub = [[(plain[s][len(out[s]) + i] if srng.random() < rate else (plain[s][len(out[s]) + i] + 1) % cfg.n_vocab) for i in range(n)] for s in range(S)]
+        got = eng.spec_round_slots(slots, n, sub)
         for s in range(S):
-            r0 = s * (n + 1); mm = 0
-            while mm < n and ids[r0 + mm] == drafts[s][mm]:
-                mm += 1
-            eng.accept(s, mm + 1)
-            out[s] += drafts[s][:mm] + [int(ids[r0 + mm])]
-            if mm > 0:
-                reqs.append((s, drafts[s][:mm], pos[s] + 1)); rows += list(range(r0, r0 + mm))
-            hpend[s] = hview[r0 + mm]
-            pos[s] += mm + 1; emitted += mm + 1
-        if reqs:                                     # MTP catch-up with the target's h rows (batchfn.cpp:110-114)
-            idx = torch.tensor(rows, device="cuda")
-            hbuf[:len(rows)] = hview[idx]
-            torch.cuda.synchronize()
-            eng.mtp_forward_slots(reqs, hbuf.data_ptr())
-        return emitted
+            out[s] += got[s]
+        return sum(len(g) for g in got), eng.last_ms()
 
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         one_round()
+    eng.moe_touched()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
     sampler = ClockSampler(local_rank) if rank == 0 else None
-    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
     torch.cuda.profiler.start()
-    t0 = time.perf_counter(); e0.record()
-    toks = 0
-    for _ in range(args.steps):
-        toks += one_round()
-    e1.record(); torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    toks = 0; dev_ms = 0.0
+    for _ in range(steps):
+        c, ms = one_round(); toks += c; dev_ms += ms
+    torch.cuda.synchronize()
     wall_ms = (time.perf_counter() - t0) * 1e3
     torch.cuda.profiler.stop()
     clocks = sampler.stop() if sampler else None
+    touched = eng.moe_touched()                      # (layer, expert) matrices this GPU streamed in the timed rounds
+    exch_us = eng.ep_exchange_us(S * (n + 1), 20)
     exact = all(out[s][:len(plain[s])] == plain[s][:len(out[s])] for s in range(S))
+    kernels = eng.last_round_kernels()
+    # bytes one round must read on this GPU: the replicated dense part of every pass + the touched expert matrices
+    q4k = lambda N, K: N * (K // 256) * 144
+    F = cfg.expert_ff
+    expert_bytes = q4k(2 * F, E) + q4k(E, F)
+    # replicated part: every projection and the LM head, without the shared expert (it is one of the touched matrices)
+    dense_pass = eng.pass_weight_bytes(False, True) - cfg.n_layer * expert_bytes
+    head = eng.pass_weight_bytes(False, True) - eng.pass_weight_bytes(False, False)
+    dense_mtp = eng.pass_weight_bytes(True, False) - expert_bytes
+    catchup = q4k(E, 2 * E) + q4k(cfg.n_head * 512 + 2 * cfg.n_head_kv * 256, E)     # the catch-up stops at the MTP block's K/V rows
+    round_bytes = dense_pass + n * (dense_mtp + head) + catchup + touched / steps * expert_bytes
+    n_exchange = cfg.n_layer + n                                  # MoE layers executed per round: the verify pass and the n draft passes
     if world > 1:
-        t = torch.tensor([wall_ms], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX); wall_ms = float(t[0]); dist.barrier()
+        t = torch.tensor([dev_ms, wall_ms, round_bytes], device="cuda", dtype=torch.float64); dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dev_ms, wall_ms, round_bytes = float(t[0]), float(t[1]), float(t[2])
+        ok = torch.tensor([1.0 if exact else 0.0], device="cuda"); dist.all_reduce(ok, op=dist.ReduceOp.MIN); exact = bool(ok.item() > 0.5)
+        dist.barrier()
     eng.close()
     if rank != 0:
         return None
     pk = peaks()
-    v = toks / (wall_ms / 1e3)
-    return {"metric": METRIC, "value": v, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": wall_ms / args.steps,
+    v = toks / (dev_ms / 1e3)
+    ms_round = dev_ms / steps
+    roof_ms = round_bytes / (pk["hbm_gbs"] * 1e9) * 1e3
+    return {"workload": EP_WORKLOAD, "parallelism": f"ep{world} (routed experts sharded over {world} GPU(s), trunk replicated)", "n_gpus": world,
+            "value": v, "unit": "tokens/s", "ms_per_round": ms_round, "steps": steps, "warmup": warmup,
+            "e2e": {"value": toks / (wall_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 4 * (8 + 8 * 8), "d2h_bytes_per_step": 4 * 8 * 32,
+                    "note": "hp_spec_round over 8 slots with host token buffers, wall clock"},
+            "slot_streams_equal_solo": bool(exact), "tokens": int(toks), "tokens_per_round": toks / steps,
+            "exchange": {"collective": "ncclAllReduce(sum) of the per-(row, slot) expert outputs [24 rows][11 slots][2048] f32, one per MoE layer" if world > 1 else "none (one GPU)",
+                         "us_per_layer": exch_us, "layers_per_round": n_exchange if world > 1 else 0,
+                         "share_of_round": (exch_us * n_exchange / 1e3) / ms_round if world > 1 else 0.0},
+            "roofline": {"bound": "hbm", "unit": "GB/s", "peak": pk["hbm_gbs"], "peak_source": pk["_src"],
+                         "bytes_per_round_per_gpu": round_bytes, "unique_expert_matrices_per_round_rank0": touched / steps, "expert_bytes": expert_bytes,
+                         "achieved": round_bytes / (ms_round / 1e3) / 1e9, "frac": roof_ms / ms_round,
+                         "note": "bytes = replicated dense part of the round's passes + the (layer, expert) matrices the slowest GPU touched; max over ranks"},
+            "kernels_per_round": kernels, "clocks": clocks, "prompt_len": prompt_len, "setup_s": t_setup}
+
+
+def ep_line(args, block, world):
+    """`--workload moe-ep`: the configuration-5 block as a line of its own."""
+    pk = peaks()
+    return {"metric": METRIC, "value": block["value"], "unit": "tokens/s", "n_gpus": world, "steps": block["steps"], "warmup": block["warmup"], "ms_per_step": block["ms_per_round"],
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u4 x i8 -> i32, f32 epilogue/state", "data": "synthetic",
-            "config": {"workload": "config5: Flash-Next-shaped MoE, 8 slots x distinct 2048-token seeded prompts, lock-step MTP n=2 (24 verify rows per pass), "
-                                   "seeded acceptance 0.7, aggregate tokens/s", "parallelism": f"ep{world} (routed experts sharded, trunk replicated)",
-                       "l2": "inputs larger than L2", "prompt_len": prompt_len},
-            "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 4 * S * (2 * n + 1 + n), "d2h_bytes_per_step": 4 * S * (2 * n + 1),
-                    "note": "host-driven lock-step loop through hp_forward / hp_accept / hp_mtp_forward_slots / hp_topk; value and e2e are the same measurement"},
-            "gpu_launches": None, "roofline": {"bound": "hbm", "achieved": None, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": None, "traffic": None},
-            "clocks": clocks, "checks": {"slot_streams_equal_solo_plain_greedy": bool(exact), "tokens": int(toks), "setup_s": t_setup}}
+            "config": {"workload": block["workload"], "parallelism": block["parallelism"], "l2": "inputs larger than L2"},
+            "e2e": block["e2e"], "gpu_launches": block["kernels_per_round"] * block["steps"] * world,
+            "roofline": {"bound": "hbm", "achieved": block["roofline"]["achieved"], "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": block["roofline"]["frac"], "traffic": None,
+                         "kernel": "whole round (k_moe_gemv_grouped dominates): bytes the slowest GPU must read per round / round time"},
+            "clocks": block["clocks"], "ep": block}
 
 
 # ------------------------------------------------------------------------------------------ gemv (config 1)
@@ -510,6 +555,7 @@ def main():
     ap.add_argument("--workload", default="dense27b", choices=["dense27b", "moe", "moe-ep", "gemv"])
     ap.add_argument("--preset", default=None)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-ep", action="store_true", help="skip the configuration-5 (expert-parallel) block of the default run")
     ap.add_argument("--layers", type=int, default=0, help="override the trunk depth (profiling captures only: keeps the device footprint at a few GB)")
     ap.add_argument("--prompt-len", type=int, default=0, help="override the workload's prompt length (shorter prompts are for profiling captures only)")
     args = ap.parse_args()
@@ -535,8 +581,18 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     if args.workload in ("dense27b", "moe"):
         line = run_dense(args, rank, local_rank, world)
+        if args.workload == "dense27b" and not args.no_ep and not args.layers:
+            import gc
+            gc.collect(); torch.cuda.empty_cache()
+            block = run_moe_ep(args, rank, local_rank, world, steps=min(args.steps, 20), warmup=3)
+            if line:
+                line["ep"] = block
+        if line and world == 1 and not args.no_cpu and args.workload == "dense27b":
+            dt, done, th, _ = cpu_rounds(2, 1, budget_s=90.0)
+            line["cpu_baseline"] = {"value": expected_tokens_per_round(N_DRAFT, ACCEPT_RATE) / dt, "unit": "tokens/s", "cores": th, "kind": "port", "sample": CPU_SAMPLE + f"; {done} timed rounds"}
     elif args.workload == "moe-ep":
-        line = run_moe_ep(args, rank, local_rank, world)
+        block = run_moe_ep(args, rank, local_rank, world)
+        line = ep_line(args, block, world) if block else None
     else:
         line = run_gemv(args, rank, local_rank, world)
     if line:

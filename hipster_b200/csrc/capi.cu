@@ -168,43 +168,50 @@ int hp_attn_decode(float* qkv_dev, int ld, int R, int pos0, int n_head, int n_kv
                                hp::XQ8F{xq_q_dev, xq_sc_dev}, eps, workspace_dev, (cudaStream_t)stream);
     HP_GUARD_END
 }
-// workspace of hp_moe_layer: router logits | ticket counters | gate|up rows | per-pair outputs | quantised activations of the pairs
+size_t hp_q4k_tiled_bytes(size_t N, int K) { return (N < 1 || K < 256 || K % 256) ? 0 : hp::gemv_tiled_bytes(N, K); }
+int hp_q4k_repack_tiled(const void* w_dev, void* w_tiled_dev, size_t N, int K, int interleave_half, void* stream) {
+    HP_GUARD_BEGIN
+    HP_REQUIRE(w_dev && w_tiled_dev, "hp_q4k_repack_tiled: null pointer");
+    HP_REQUIRE(((uintptr_t)w_dev & 3) == 0 && ((uintptr_t)w_tiled_dev & 15) == 0, "hp_q4k_repack_tiled: misaligned tensor");
+    return hp::gemv_repack_tiled(w_dev, w_tiled_dev, N, K, (cudaStream_t)stream, interleave_half);
+    HP_GUARD_END
+}
+// workspace of hp_moe_layer: router logits | ticket counters | per-pair outputs | quantised activations of the pairs | segments | control words
 namespace {
-struct MoeWs { size_t logits, cnt, gu, v, q2, sc2, total; };
+struct MoeWs { size_t logits, cnt, v, q2, sc2, segs, ctl, total; };
 MoeWs moe_ws(int T, int E, int F, int n_expert, int k) {
     auto al = [](size_t x) { return (x + 255) & ~(size_t)255; };
     const size_t pairs = (size_t)T * (k + 1);
     MoeWs w; size_t o = 0;
     w.logits = o; o += al((size_t)T * (n_expert + 1) * 4);
     w.cnt = o; o += al((size_t)T * 4);
-    w.gu = o; o += al(pairs * 2 * F * 4);
     w.v = o; o += al(pairs * E * 4);
     w.q2 = o; o += al(hp::xq_q_bytes((int)pairs, F));
     w.sc2 = o; o += al(hp::xq_sc_floats((int)pairs, F) * 4);
+    w.segs = o; o += al(hp::moe_seg_bytes());
+    w.ctl = o; o += 256;
     w.total = o; return w;
 }
 }
 size_t hp_moe_workspace_bytes(int T, int E, int F, int n_expert, int k) { return (T < 1 || E < 1 || F < 1 || n_expert < 1 || k < 1) ? 0 : moe_ws(T, E, F, n_expert, k).total; }
-int hp_moe_layer(const float* xn_dev, const void* xq_q_dev, const void* xq_sc_dev, const float* router_dev, const void* exp_gate_up_dev, const void* exp_down_dev,
-                 const void* sh_gate_up_dev, const void* sh_down_dev, int T, int E, int F, int n_expert, int k, int* ids_dev, float* weights_dev, float* y_dev,
+int hp_moe_layer(const float* xn_dev, const void* xq_q_dev, const void* xq_sc_dev, const float* router_dev, const void* exp_gate_up_tiled_dev, const void* exp_down_tiled_dev,
+                 const void* sh_gate_up_tiled_dev, const void* sh_down_tiled_dev, int T, int E, int F, int n_expert, int k, int* ids_dev, float* weights_dev, float* y_dev,
                  void* workspace_dev, void* stream) {
     HP_GUARD_BEGIN
-    HP_REQUIRE(xn_dev && xq_q_dev && xq_sc_dev && router_dev && exp_gate_up_dev && exp_down_dev && sh_gate_up_dev && sh_down_dev && ids_dev && weights_dev && y_dev && workspace_dev, "hp_moe_layer: null pointer");
+    HP_REQUIRE(xn_dev && xq_q_dev && xq_sc_dev && router_dev && exp_gate_up_tiled_dev && exp_down_tiled_dev && sh_gate_up_tiled_dev && sh_down_tiled_dev && ids_dev && weights_dev && y_dev && workspace_dev, "hp_moe_layer: null pointer");
     HP_REQUIRE(T >= 1 && T <= 32 && E % 256 == 0 && F % 256 == 0 && n_expert >= k && k >= 1 && k <= 15, "hp_moe_layer: bad shape T=%d E=%d F=%d experts=%d k=%d", T, E, F, n_expert, k);
     cudaStream_t s = (cudaStream_t)stream;
     const MoeWs w = moe_ws(T, E, F, n_expert, k);
     char* ws = (char*)workspace_dev; const int ns = k + 1;
-    float* logits = (float*)(ws + w.logits); int* cnt = (int*)(ws + w.cnt); float* gu = (float*)(ws + w.gu); float* v = (float*)(ws + w.v);
-    hp::XQ8F xq2{ws + w.q2, ws + w.sc2};
+    float* logits = (float*)(ws + w.logits); int* cnt = (int*)(ws + w.cnt); float* v = (float*)(ws + w.v);
     HP_CUDA(cudaMemsetAsync(cnt, 0, (size_t)T * 4, s));
     HP_CUDA(cudaMemsetAsync(ws + w.q2, 0, w.total - w.q2, s));
     { const int rc = hp::router_route(router_dev, xn_dev, logits, ids_dev, weights_dev, cnt, n_expert, E, k, T, s); if (rc) return rc; }
-    hp::MoeParams p; p.w_exp = exp_gate_up_dev; p.w_sh = sh_gate_up_dev; p.ebytes = (size_t)2 * F * (E / 256) * 144; p.N = 2 * F; p.K = E;
-    p.ids = ids_dev; p.slotw = nullptr; p.nslot = ns; p.xq = hp::XQ8F{(void*)xq_q_dev, (void*)xq_sc_dev}; p.y = gu; p.T = T; p.e_lo = 0; p.e_hi = n_expert; p.own_shared = 1;
-    { const int rc = hp::moe_gemv_up(p, s); if (rc) return rc; }
-    { const int rc = hp::moe_silu_quant(gu, F, ids_dev, 0, n_expert, 1, xq2, T * ns, s); if (rc) return rc; }
-    hp::MoeParams d = p; d.w_exp = exp_down_dev; d.w_sh = sh_down_dev; d.ebytes = (size_t)E * (F / 256) * 144; d.N = E; d.K = F; d.xq = xq2; d.slotw = weights_dev; d.y = v;
-    { const int rc = hp::moe_down_pairs(d, s); if (rc) return rc; }
+    hp::MoeGroupParams g; g.w_gate_up = exp_gate_up_tiled_dev; g.w_down = exp_down_tiled_dev; g.sh_gate_up = sh_gate_up_tiled_dev; g.sh_down = sh_down_tiled_dev;
+    g.E = E; g.F = F; g.n_expert = n_expert; g.nslot = ns; g.T = T; g.e_lo = 0; g.e_hi = n_expert; g.own_shared = 1;
+    g.ids = ids_dev; g.xq = hp::XQ8F{(void*)xq_q_dev, (void*)xq_sc_dev}; g.xq2 = hp::XQ8F{ws + w.q2, ws + w.sc2}; g.v = v;
+    g.segs = ws + w.segs; g.ctl = (int*)(ws + w.ctl); g.touched = nullptr; g.err = hp::device_err_flag();
+    { const int rc = hp::moe_experts_grouped(g, s); if (rc) return rc; }
     return hp::moe_combine(v, weights_dev, y_dev, T, ns, E, s);
     HP_GUARD_END
 }
@@ -271,6 +278,9 @@ int hp_mtp_forward_slots(hp_engine* e, const hp_slot_req* reqs, int S, const flo
 int hp_ep_unique_id(void* id128_out) { HP_GUARD_BEGIN HP_REQUIRE(id128_out, "hp_ep_unique_id: null pointer"); return hp::Engine::ep_unique_id(id128_out); HP_GUARD_END }
 int hp_ep_init(hp_engine* e, const void* id128) { HP_GUARD_BEGIN HP_REQUIRE(e && id128, "hp_ep_init: null pointer"); return e->impl.ep_init(id128); HP_GUARD_END }
 int hp_profile_pass(hp_engine* e, int R, int what, int reps, float* ms_out) { HP_ENGINE_CALL(e->impl.profile_pass(R, what, reps, ms_out)) }
+int hp_moe_touched(hp_engine* e, unsigned long long* n_out) { HP_ENGINE_CALL(e->impl.moe_touched(n_out)) }
+int hp_ep_exchange_us(hp_engine* e, int R, int reps, float* us_out) { HP_ENGINE_CALL(e->impl.ep_exchange_us(R, reps, us_out)) }
+int hp_last_round_kernels(const hp_engine* e) { return e ? e->impl.last_round_kernels() : 0; }
 size_t hp_pass_weight_bytes(const hp_engine* e, int mtp, int with_head) { return e ? e->impl.pass_weight_bytes(mtp != 0, with_head != 0) : 0; }
 int hp_spec_begin(hp_engine* e, int slot, int id_last, int pos, const float* h_pending_dev) { HP_ENGINE_CALL(e->impl.spec_begin(slot, id_last, pos, h_pending_dev)) }
 int hp_spec_round(hp_engine* e, const int* slot_ids_host, int S, int n_draft, const int* subst_host, int* out_tokens_host, int* out_counts_host) {

@@ -42,9 +42,10 @@ __global__ void k_gen_q4k(uint64_t* __restrict__ w, size_t nwords, uint64_t seed
     }
     w[li] = v;
 }
-__global__ void k_gen_bf16(uint16_t* __restrict__ p, size_t n, uint64_t seed, uint64_t tid, float mean, float std) {
+__global__ void k_gen_bf16(uint16_t* __restrict__ p, size_t n, uint64_t seed, uint64_t tid, float mean, float std, int neg_abs) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; if (i >= n) return;
-    p[i] = f32_to_bf16_bits(mean + std * irwin(rnd64(seed, tid, i)));
+    float v = mean + std * irwin(rnd64(seed, tid, i)); if (neg_abs) v = -fabsf(v);
+    p[i] = f32_to_bf16_bits(v);
 }
 __global__ void k_gen_f32(float* __restrict__ p, size_t n, uint64_t seed, uint64_t tid, float mean, float std, int neg_abs) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; if (i >= n) return;
@@ -174,24 +175,33 @@ int Engine::gen_lin(Lin& l, int N, int K, uint64_t tid) {
     }
     return HP_OK;
 }
-int Engine::gen_raw_q4k(Lin& l, size_t rows, int K, uint64_t tid, size_t row0, size_t nrows_local) {   // expert stacks: no GEMV partition attached
+int Engine::gen_raw_q4k(Lin& l, size_t rows, int K, uint64_t tid, size_t row0, size_t nrows_local, int interleave_half) {   // expert stacks: no GEMV partition attached
     // rows [row0, row0 + nrows_local) of a tensor of `rows` rows are generated; l.w is offset so that it can be indexed
-    // with global row numbers (a GPU that holds a shard of the experts never dereferences the rows of other shards)
+    // with global row numbers (a GPU that holds a shard of the experts never dereferences the rows of other shards).
+    // The grouped expert GEMV streams the tile-major copy l.wt, which holds the local rows only.
     if (nrows_local == (size_t)-1) nrows_local = rows;
     const size_t rb = (size_t)(K / 256) * 144;
     l.N = (int)std::min<size_t>(rows, 0x7fffffff); l.K = K; l.P = 1; l.bytes = nrows_local * rb;
-    HP_REQUIRE(K % 256 == 0, "expert tensor K=%d is not a multiple of 256", K);
+    HP_REQUIRE(K % 256 == 0 && nrows_local % 16 == 0, "expert tensor K=%d must be a multiple of 256 (rows a multiple of 16)", K);
     uint8_t* base = nullptr;
     if (int rc = alloc((void**)&base, l.bytes)) return rc;
     const size_t nwords = l.bytes / 8;
     k_gen_q4k<<<(unsigned)((nwords + 255) / 256), 256, 0, s_>>>((uint64_t*)base, nwords, c_.seed, tid, row0 * rb / 8);
     HP_CUDA(cudaGetLastError());
     l.w = base - row0 * rb;
-    weight_bytes_ += l.bytes; return HP_OK;
+    weight_bytes_ += l.bytes;
+    HP_TRY(alloc((void**)&l.wt, gemv_tiled_bytes(nrows_local, K)));
+    HP_TRY(gemv_repack_tiled(base, l.wt, nrows_local, K, s_, interleave_half));
+    if (!keep_rowmajor_) {
+        HP_CUDA(cudaStreamSynchronize(s_));
+        for (size_t i = 0; i < allocs_.size(); ++i) if (allocs_[i] == base) { allocs_.erase(allocs_.begin() + i); break; }
+        HP_CUDA(cudaFree(base)); l.w = nullptr;
+    }
+    return HP_OK;
 }
-int Engine::gen_bf16(uint16_t** p, size_t n, uint64_t tid, float mean, float std) {
+int Engine::gen_bf16(uint16_t** p, size_t n, uint64_t tid, float mean, float std, bool neg_abs) {
     if (int rc = alloc((void**)p, n * 2)) return rc;
-    k_gen_bf16<<<(unsigned)((n + 255) / 256), 256, 0, s_>>>(*p, n, c_.seed, tid, mean, std);
+    k_gen_bf16<<<(unsigned)((n + 255) / 256), 256, 0, s_>>>(*p, n, c_.seed, tid, mean, std, neg_abs ? 1 : 0);
     HP_CUDA(cudaGetLastError()); weight_bytes_ += n * 2; return HP_OK;
 }
 int Engine::gen_f32(float** p, size_t n, uint64_t tid, float mean, float std, bool neg_abs) {
@@ -212,7 +222,9 @@ int Engine::init() {
     HP_REQUIRE(c.n_expert == 0 ? (c.n_ff > 0 && c.n_ff % 256 == 0) : (c.expert_ff % 256 == 0 && c.n_expert_used >= 1 && c.n_expert_used <= 15), "bad FFN shape");
     HP_CUDA(cudaStreamCreateWithFlags(&s_, cudaStreamNonBlocking));
     tiled_ = getenv("HIPSTER_B200_ROWMAJOR") == nullptr;
-    keep_rowmajor_ = (size_t)c.n_layer * c.n_embd * (size_t)std::max(c.n_ff, 1) < ((size_t)1 << 28);   // small models keep both layouts (tensor access in tests)
+    // small models keep both layouts (tensor access in tests): dense FFN elements, or routed-expert elements, below 2^28 / 2^30
+    keep_rowmajor_ = (size_t)c.n_layer * c.n_embd * (size_t)std::max(c.n_ff, 1) < ((size_t)1 << 28) &&
+                     (size_t)c.n_layer * std::max(c.n_expert, 0) * 3 * c.n_embd * (size_t)std::max(c.expert_ff, 0) < ((size_t)1 << 30);
     HP_CUDA(cudaEventCreate(&ev0_)); HP_CUDA(cudaEventCreate(&ev1_));
     const int E = c.n_embd, nv = c.gdn_v_heads, nq = c.gdn_qk_heads;
     const int gdn_in = (2 * nq + nv) * 128 + nv * 128 + 2 * nv, attn_in = c.n_head * 512 + 2 * c.n_head_kv * 256;
@@ -231,7 +243,9 @@ int Engine::init() {
             HP_TRY(gen_lin(L.out_proj, E, nv * 128, tensor_id(il, TK_OUT_PROJ)));
             HP_TRY(gen_f32(&L.conv_w, (size_t)(2 * nq + nv) * 128 * 4, tensor_id(il, TK_CONV_W), 0.f, 0.5f, false));
             HP_TRY(gen_bf16(&L.dt_bias, nv, tensor_id(il, TK_DT_BIAS), 0.f, 0.5f));
-            HP_TRY(gen_bf16(&L.a_neg, nv, tensor_id(il, TK_A_NEG), -0.8f, 0.4f));
+            // the decay exponent must not be positive (a_neg = -exp(A_log) in the model; the reference's kernel test draws
+            // -|N(0, 1)|, engine/bench/test_fnkernels.cpp:33): a positive one makes the recurrent state grow without bound
+            HP_TRY(gen_bf16(&L.a_neg, nv, tensor_id(il, TK_A_NEG), 0.8f, 0.4f, true));
             HP_TRY(gen_bf16(&L.ssm_norm, 128, tensor_id(il, TK_SSM_NORM), 1.f, 0.3f));
         }
         if (c.n_expert == 0) {
@@ -241,10 +255,10 @@ int Engine::init() {
             const int F = c.expert_ff;
             HP_TRY(gen_f32(&L.router, (size_t)(c.n_expert + 1) * E, tensor_id(il, TK_ROUTER), 0.f, 1.0f / sqrtf((float)E), false));
             const int w = std::max(1, c.ep_world), elo = (int)((long long)c.ep_rank * c.n_expert / w), ehi = (int)((long long)(c.ep_rank + 1) * c.n_expert / w);
-            HP_TRY(gen_raw_q4k(L.exp_gate_up, (size_t)c.n_expert * 2 * F, E, tensor_id(il, TK_EXP_GATE_UP), (size_t)elo * 2 * F, (size_t)(ehi - elo) * 2 * F));
-            HP_TRY(gen_raw_q4k(L.exp_down, (size_t)c.n_expert * E, F, tensor_id(il, TK_EXP_DOWN), (size_t)elo * E, (size_t)(ehi - elo) * E));
-            HP_TRY(gen_raw_q4k(L.sh_gate_up, (size_t)2 * F, E, tensor_id(il, TK_SH_GATE_UP)));
-            HP_TRY(gen_raw_q4k(L.sh_down, (size_t)E, F, tensor_id(il, TK_SH_DOWN)));
+            HP_TRY(gen_raw_q4k(L.exp_gate_up, (size_t)c.n_expert * 2 * F, E, tensor_id(il, TK_EXP_GATE_UP), (size_t)elo * 2 * F, (size_t)(ehi - elo) * 2 * F, F));
+            HP_TRY(gen_raw_q4k(L.exp_down, (size_t)c.n_expert * E, F, tensor_id(il, TK_EXP_DOWN), (size_t)elo * E, (size_t)(ehi - elo) * E, 0));
+            HP_TRY(gen_raw_q4k(L.sh_gate_up, (size_t)2 * F, E, tensor_id(il, TK_SH_GATE_UP), 0, (size_t)-1, F));
+            HP_TRY(gen_raw_q4k(L.sh_down, (size_t)E, F, tensor_id(il, TK_SH_DOWN), 0, (size_t)-1, 0));
         }
         return HP_OK;
     };
@@ -305,7 +319,9 @@ int Engine::init() {
         HP_TRY(alloc((void**)&rlogits_, (size_t)MAXR * (c.n_expert + 1) * 4));
         HP_TRY(alloc((void**)&moe_ids_, (size_t)pairs * 4)); HP_TRY(alloc((void**)&moe_w_, (size_t)pairs * 4));
         HP_TRY(alloc((void**)&route_cnt_, (size_t)MAXR * 4)); HP_CUDA(cudaMemsetAsync(route_cnt_, 0, (size_t)MAXR * 4, s_));
-        HP_TRY(alloc((void**)&moe_gu_, (size_t)pairs * 2 * F * 4)); HP_TRY(alloc((void**)&moe_v_, (size_t)pairs * E * 4));
+        HP_TRY(alloc((void**)&moe_v_, (size_t)pairs * E * 4));
+        HP_TRY(alloc(&moe_segs_, moe_seg_bytes())); HP_TRY(alloc((void**)&moe_ctl_, 16)); HP_TRY(alloc((void**)&moe_touched_, 8));
+        HP_CUDA(cudaMemsetAsync(moe_ctl_, 0, 16, s_)); HP_CUDA(cudaMemsetAsync(moe_touched_, 0, 8, s_));
         HP_TRY(alloc(&xq2_.q, xq_q_bytes(pairs, F))); HP_TRY(alloc(&xq2_.sc, xq_sc_floats(pairs, F) * 4));
         HP_CUDA(cudaMemsetAsync(xq2_.q, 0, xq_q_bytes(pairs, F), s_)); HP_CUDA(cudaMemsetAsync(xq2_.sc, 0, xq_sc_floats(pairs, F) * 4, s_));
         moe_out_.N = E; moe_out_.K = F; moe_out_.P = 1;
@@ -399,16 +415,15 @@ int Engine::moe_block(const LayerW& L, int R) {
     const hp_model_cfg& c = c_; const int E = c.n_embd, F = c.expert_ff, ns = c.n_expert_used + 1;
     if (gemv_only_) return HP_OK;
     HP_TRY(router_route(L.router, xn_, rlogits_, moe_ids_, moe_w_, route_cnt_, c.n_expert, E, c.n_expert_used, R, s_));
-    MoeParams p; p.w_exp = L.exp_gate_up.w; p.w_sh = L.sh_gate_up.w; p.ebytes = (size_t)2 * F * (E / 256) * 144; p.N = 2 * F; p.K = E;
-    p.ids = moe_ids_; p.slotw = nullptr; p.nslot = ns; p.xq = xq_; p.y = moe_gu_; p.T = R; p.e_lo = e_lo_; p.e_hi = e_hi_; p.own_shared = own_shared_;
-    HP_TRY(moe_gemv_up(p, s_));
-    HP_TRY(moe_silu_quant(moe_gu_, F, moe_ids_, e_lo_, e_hi_, own_shared_, xq2_, R * ns, s_));
-    MoeParams d = p; d.w_exp = L.exp_down.w; d.w_sh = L.sh_down.w; d.ebytes = (size_t)E * (F / 256) * 144; d.N = E; d.K = F; d.xq = xq2_; d.slotw = moe_w_;
-    // per-(row, slot) outputs of the experts this GPU owns (exact zeros for experts owned elsewhere), exchanged when
-    // the experts are sharded, then combined in slot order (the arithmetic of gemv.hip:1104-1112 on every GPU)
-    d.y = moe_v_;
-    HP_TRY(moe_down_pairs(d, s_));
-    if (c.ep_world > 1) { HP_TRY(ep_ready()); HP_TRY(ep_exchange(moe_v_, (size_t)R * ns * E)); }
+    // per-(row, slot) outputs of the experts this GPU owns, grouped by expert so that each touched expert matrix is read
+    // once; pairs of experts owned elsewhere stay exact zeros, the exchange fills them in, and the combine runs in slot
+    // order (the arithmetic of gemv.hip:1104-1112) on every GPU
+    if (c.ep_world > 1) { HP_TRY(ep_ready()); HP_CUDA(cudaMemsetAsync(moe_v_, 0, (size_t)R * ns * E * 4, s_)); }
+    MoeGroupParams g; g.w_gate_up = L.exp_gate_up.wt; g.w_down = L.exp_down.wt; g.sh_gate_up = L.sh_gate_up.wt; g.sh_down = L.sh_down.wt;
+    g.E = E; g.F = F; g.n_expert = c.n_expert; g.nslot = ns; g.T = R; g.e_lo = e_lo_; g.e_hi = e_hi_; g.own_shared = own_shared_;
+    g.ids = moe_ids_; g.xq = xq_; g.xq2 = xq2_; g.v = moe_v_; g.segs = moe_segs_; g.ctl = moe_ctl_; g.touched = moe_touched_; g.err = err_;
+    HP_TRY(moe_experts_grouped(g, s_));
+    if (c.ep_world > 1) HP_TRY(ep_exchange(moe_v_, (size_t)R * ns * E));
     return HP_OK;   // combined in slot order by the norm that follows (norm_in)
 }
 
@@ -665,8 +680,10 @@ int Engine::tensor(int layer, int kind, void** ptr, size_t* bytes) const {
         case TK_Q_NORM: return set(L.q_norm, 512);
         case TK_K_NORM: return set(L.k_norm, 512);
         case TK_ROUTER: return set(L.router, (size_t)(c.n_expert + 1) * E * 4);
-        case TK_EXP_GATE_UP: return set(L.exp_gate_up.w + (size_t)e_lo_ * 2 * c.expert_ff * (E / 256) * 144, L.exp_gate_up.bytes);   // this GPU's shard
-        case TK_EXP_DOWN: return set(L.exp_down.w + (size_t)e_lo_ * E * (c.expert_ff / 256) * 144, L.exp_down.bytes);
+        case TK_EXP_GATE_UP: HP_REQUIRE(L.exp_gate_up.w, "the row-major copy of this tensor was released after repacking");
+                             return set(L.exp_gate_up.w + (size_t)e_lo_ * 2 * c.expert_ff * (E / 256) * 144, L.exp_gate_up.bytes);   // this GPU's shard
+        case TK_EXP_DOWN: HP_REQUIRE(L.exp_down.w, "the row-major copy of this tensor was released after repacking");
+                          return set(L.exp_down.w + (size_t)e_lo_ * E * (c.expert_ff / 256) * 144, L.exp_down.bytes);
         case TK_SH_GATE_UP: return set(L.sh_gate_up.w, L.sh_gate_up.bytes);
         case TK_SH_DOWN: return set(L.sh_down.w, L.sh_down.bytes);
     }
@@ -804,10 +821,17 @@ int Engine::spec_round(const int* slots, int S, int n, const int* subst, int* ou
             const cudaError_t ce = cudaStreamEndCapture(s_, &g);
             if (rc != HP_OK) { if (g) cudaGraphDestroy(g); return rc; }
             HP_CUDA(ce);
+            {   // kernels of one round: counted from the captured graph
+                size_t nn = 0; HP_CUDA(cudaGraphGetNodes(g, nullptr, &nn));
+                std::vector<cudaGraphNode_t> nodes(nn); if (nn) HP_CUDA(cudaGraphGetNodes(g, nodes.data(), &nn));
+                int nk = 0; for (size_t i = 0; i < nn; ++i) { cudaGraphNodeType ty; if (cudaGraphNodeGetType(nodes[i], &ty) == cudaSuccess && ty == cudaGraphNodeTypeKernel) ++nk; }
+                graph_kernels_[key] = nk;
+            }
             HP_CUDA(cudaGraphInstantiate(&graphs_[key], g, 0));
             HP_CUDA(cudaGraphDestroy(g));
         }
         HP_CUDA(cudaGraphLaunch(graphs_[key], s_));
+        last_round_kernels_ = graph_kernels_[key];
     }
 done:
     HP_CUDA(cudaEventRecord(ev1_, s_));
@@ -906,6 +930,27 @@ int Engine::sync_stream() {
     const int rc = ep_wait_poll(wait_stream_query, wait_comm_error, &c, limit);
     if (rc != HP_OK) { g_nccl.CommAbort(nccl_comm_); nccl_comm_ = nullptr; ep_failed_ = true; }
     return rc;
+}
+int Engine::moe_touched(unsigned long long* n) {
+    HP_REQUIRE(n && moe_touched_, "moe_touched: not a mixture-of-experts engine");
+    HP_TRY(sync_stream());
+    HP_CUDA(cudaMemcpy(n, moe_touched_, 8, cudaMemcpyDeviceToHost)); HP_CUDA(cudaMemset(moe_touched_, 0, 8));
+    return HP_OK;
+}
+int Engine::ep_exchange_us(int R, int reps, float* us) {
+    HP_REQUIRE(c_.n_expert > 0 && R >= 1 && R <= MAXR && reps >= 1 && us, "ep_exchange_us: bad arguments");
+    *us = 0.f;
+    if (c_.ep_world <= 1) return HP_OK;
+    HP_TRY(ep_ready());
+    const size_t n = (size_t)R * (c_.n_expert_used + 1) * c_.n_embd;
+    HP_CUDA(cudaMemsetAsync(moe_v_, 0, n * 4, s_));
+    HP_TRY(ep_exchange(moe_v_, n));   // warm-up
+    HP_CUDA(cudaEventRecord(ev0_, s_));
+    for (int i = 0; i < reps; ++i) HP_TRY(ep_exchange(moe_v_, n));
+    HP_CUDA(cudaEventRecord(ev1_, s_));
+    HP_TRY(sync_stream());
+    float ms = 0; HP_CUDA(cudaEventElapsedTime(&ms, ev0_, ev1_)); *us = ms * 1000.f / reps;
+    return HP_OK;
 }
 int Engine::ep_unique_id(void* id128) { HP_TRY(nccl_load()); return nccl_check(g_nccl.GetUniqueId(id128), "ncclGetUniqueId"); }
 int Engine::ep_init(const void* id128) {

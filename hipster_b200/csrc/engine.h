@@ -54,13 +54,16 @@ public:
     float* mtp_logits() const { return mlogits_; } float* mtp_h() const { return mh_; }
     size_t weight_bytes() const { return weight_bytes_; } float last_ms() const { return last_ms_; }
     size_t pass_weight_bytes(bool mtp, bool with_head) const;
+    int moe_touched(unsigned long long* n);                 // touched (layer, expert) matrices since the last call (measurement)
+    int ep_exchange_us(int R, int reps, float* us);          // mean device time of one exchange for R rows (measurement)
+    int last_round_kernels() const { return last_round_kernels_; }
     int profile_pass(int R, int what, int reps, float* ms);
 private:
     struct Desc;   // device-visible pass descriptor (see engine.cu)
     int alloc(void** p, size_t bytes);
     int gen_lin(Lin& l, int N, int K, uint64_t tid);
-    int gen_raw_q4k(Lin& l, size_t rows, int K, uint64_t tid, size_t row0 = 0, size_t nrows_local = (size_t)-1);
-    int gen_bf16(uint16_t** p, size_t n, uint64_t tid, float mean, float std);
+    int gen_raw_q4k(Lin& l, size_t rows, int K, uint64_t tid, size_t row0 = 0, size_t nrows_local = (size_t)-1, int interleave_half = 0);
+    int gen_bf16(uint16_t** p, size_t n, uint64_t tid, float mean, float std, bool neg_abs = false);
     int gen_f32(float** p, size_t n, uint64_t tid, float mean, float std, bool neg_abs);
     int lin(const Lin& l, float* out, int ld, int R);        // GEMV; P > 1 planes are reduced into out
     int lin_parts(const Lin& l, int R);                      // GEMV into the plane buffer yparts_ (consumer adds the planes)
@@ -95,7 +98,7 @@ private:
     float *x_ = nullptr, *xn_ = nullptr, *big_ = nullptr, *act_ = nullptr, *yparts_ = nullptr, *logits_ = nullptr, *mlogits_ = nullptr, *h_ = nullptr, *mh_ = nullptr, *cat_ = nullptr, *emb_ = nullptr;
     float *pO_ = nullptr, *pm_ = nullptr, *pl_ = nullptr; int nsplit_max_ = 0;
     XQ8F xq_{nullptr, nullptr}, xq2_{nullptr, nullptr};
-    float *rlogits_ = nullptr, *moe_w_ = nullptr, *moe_gu_ = nullptr, *moe_v_ = nullptr; int* moe_ids_ = nullptr; int* route_cnt_ = nullptr; Lin moe_out_;
+    float *rlogits_ = nullptr, *moe_w_ = nullptr, *moe_v_ = nullptr; void* moe_segs_ = nullptr; int* moe_ctl_ = nullptr; unsigned long long* moe_touched_ = nullptr; int* moe_ids_ = nullptr; int* route_cnt_ = nullptr; Lin moe_out_;
     int e_lo_ = 0, e_hi_ = 0, own_shared_ = 1, ep_world_ = 1, ep_rank_ = 0; void* nccl_comm_ = nullptr; bool ep_failed_ = false;
     int *d_desc_ = nullptr, *h_desc_ = nullptr;                  // device / pinned host descriptor
     int *d_ids_ = nullptr, *d_mids_ = nullptr; float *d_vals_ = nullptr, *d_mvals_ = nullptr; void* am_scratch_ = nullptr;
@@ -105,7 +108,7 @@ private:
     std::vector<int> spec_pos_, spec_on_;
     void* topk_scratch_ = nullptr; int *d_topk_ids_ = nullptr; float* d_topk_vals_ = nullptr;
     uint16_t* prof_kv_ = nullptr;                                 // K/V rows saved around profile_pass
-    cudaGraphExec_t graphs_[64] = {}; bool warmed_[64] = {};
+    cudaGraphExec_t graphs_[64] = {}; bool warmed_[64] = {}; int graph_kernels_[64] = {}; int last_round_kernels_ = 0;
     int* err_ = nullptr;
     cudaStream_t s_ = nullptr; cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
     std::vector<void*> allocs_;

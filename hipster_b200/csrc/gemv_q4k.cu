@@ -40,52 +40,6 @@ template <int CB, bool TILED> struct SkGeom {
     static constexpr int FIXED = GEMV_WARPS * SK_STAGES * STAGE_BYTES + 1024;
 };
 
-__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
-    float2 r;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(reinterpret_cast<unsigned long long&>(r))
-        : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)));
-    return r;
-}
-__device__ __forceinline__ float2 add2(float2 a, float2 b) {
-    float2 r;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(reinterpret_cast<unsigned long long&>(r))
-        : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)));
-    return r;
-}
-// D = A * B + 0x4B400000 per element
-__device__ __forceinline__ void mma_u8s8_magic(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0x4B400000));
-}
-__device__ __forceinline__ void fma2(float2& acc, float2 a, float2 b) {   // acc = a * b + acc, per lane, one rounding each
-    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(reinterpret_cast<unsigned long long&>(acc))
-        : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)));
-}
-
-// Scales of one row of one block: {d*sc, d*sc, -(dmin*mn), -(dmin*mn)} per sub-block, computed on demand.
-struct RowScales {
-    float d, cd, dq, cdq, nd, cnd;          // d, -(d*2^23), d/16, -(d/16*2^23), -dmin, dmin*2^23
-    uint32_t sc[2], mn[2];                  // 6-bit scales / mins of sub-blocks 0-3 and 4-7, one per byte
-    __device__ __forceinline__ float4 get(int k) const {
-        const float fs = __uint_as_float(__byte_perm(sc[k >> 2], 0x4B000000u, 0x7540u | (k & 3)));
-        const float fm = __uint_as_float(__byte_perm(mn[k >> 2], 0x4B000000u, 0x7540u | (k & 3)));
-        const float s0 = (k & 1) ? fmaf(dq, fs, cdq) : fmaf(d, fs, cd);
-        const float nm = fmaf(nd, fm, cnd);
-        return make_float4(s0, s0, nm, nm);
-    }
-};
-__device__ __forceinline__ RowScales decode_scales(const uint4 hdr) {
-    RowScales r;
-    r.d = h2f((uint16_t)(hdr.x & 0xFFFF)); r.nd = -h2f((uint16_t)(hdr.x >> 16));
-    r.dq = r.d * 0.0625f;
-    r.cd = -(r.d * 8388608.f); r.cdq = -(r.dq * 8388608.f); r.cnd = -(r.nd * 8388608.f);
-    r.sc[0] = hdr.y & 0x3F3F3F3Fu; r.mn[0] = hdr.z & 0x3F3F3F3Fu;
-    r.sc[1] = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
-    r.mn[1] = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
-    return r;
-}
-
 template <int NT, int CB, bool TILED>
 __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __restrict__ W, const uint4* __restrict__ xq, const float4* __restrict__ xsc,
                                                                 float* __restrict__ y, int N, int nb, int P, int R, int ldy, size_t part_stride,
@@ -420,8 +374,11 @@ int launch_sk(const uint8_t* W, bool tiled, const void* xq, const void* xsc, flo
                : launch_sk2<NT, 1, false>(W, xq, xsc, y, N, nb, P, R, ldy, part_stride, err, s, pdl);
 }
 
-// row-major ggml blocks -> tile-major chunks (see SkGeom); rows beyond N are zero (they contribute nothing)
-__global__ void __launch_bounds__(256) k_repack_tiled(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int N, int nb) {
+// row-major ggml blocks -> tile-major chunks (see SkGeom); rows beyond N are zero (they contribute nothing).
+// half > 0: the tensor is a stack of matrices of 2 * half rows (gate rows then up rows of an expert); tile q of a matrix
+// then holds gate rows 8q..8q+7 followed by up rows 8q..8q+7, so that one lane of the tensor-core tile owns gate and up
+// of the same feature.
+__global__ void __launch_bounds__(256) k_repack_tiled(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int N, int nb, int half) {
     const size_t chunk = blockIdx.x;                       // (tile, block)
     const int tile = (int)(chunk / nb), b = (int)(chunk % nb);
     uint8_t* out = dst + chunk * 2304;
@@ -430,7 +387,8 @@ __global__ void __launch_bounds__(256) k_repack_tiled(const uint8_t* __restrict_
         int row, off;                                      // source row in the tile and byte offset in its 144-byte block
         if (o < 256) { row = o / 16; off = o % 16; }
         else { const int q = o - 256, j = q / 512, lane = (q % 512) / 16, w = q % 16, g = lane >> 2, t = lane & 3; row = g + (w >= 8 ? 8 : 0); off = 16 + 32 * j + 8 * t + (w & 7); }
-        const int r = tile * 16 + row;
+        int r = tile * 16 + row;
+        if (half > 0) { const int tpe = half / 8, eb = tile / tpe, q = tile % tpe; r = eb * 2 * half + (row < 8 ? 8 * q + row : half + 8 * q + row - 8); }
         if (r < N) v = *reinterpret_cast<const uint32_t*>(src + ((size_t)r * nb + b) * 144 + off);
         *reinterpret_cast<uint32_t*>(out + o) = v;
     }
@@ -449,10 +407,11 @@ __global__ void k_reduce_parts(const float* __restrict__ parts, size_t part_stri
 
 int gemv_parts(int N, int K) { return gemv_num_parts(N, K / 256); }
 
-size_t gemv_tiled_bytes(int N, int K) { return (size_t)((N + 15) / 16) * (K / 256) * 2304; }
-int gemv_repack_tiled(const void* src, void* dst, int N, int K, cudaStream_t s) {
-    HP_REQUIRE(N > 0 && K > 0 && K % 256 == 0, "gemv_repack_tiled: bad shape");
-    k_repack_tiled<<<(unsigned)(((size_t)(N + 15) / 16) * (K / 256)), 256, 0, s>>>((const uint8_t*)src, (uint8_t*)dst, N, K / 256);
+size_t gemv_tiled_bytes(size_t N, int K) { return ((N + 15) / 16) * (size_t)(K / 256) * 2304; }
+int gemv_repack_tiled(const void* src, void* dst, size_t N, int K, cudaStream_t s, int interleave_half) {
+    HP_REQUIRE(N > 0 && N < ((size_t)1 << 31) && K > 0 && K % 256 == 0, "gemv_repack_tiled: bad shape");
+    HP_REQUIRE(interleave_half == 0 || (interleave_half % 8 == 0 && N % (2 * (size_t)interleave_half) == 0), "gemv_repack_tiled: the gate|up interleave needs stacks of 2 * half rows, half a multiple of 8");
+    k_repack_tiled<<<(unsigned)(((N + 15) / 16) * (K / 256)), 256, 0, s>>>((const uint8_t*)src, (uint8_t*)dst, (int)N, K / 256, interleave_half);
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 

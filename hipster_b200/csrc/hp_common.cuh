@@ -176,6 +176,53 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// ---- shared pieces of the Q4_K tensor-core GEMV inner loop (dense GEMV and routed-expert GEMV) ----
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+    float2 r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(reinterpret_cast<unsigned long long&>(r))
+        : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)));
+    return r;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    float2 r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(reinterpret_cast<unsigned long long&>(r))
+        : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)));
+    return r;
+}
+// D = A * B + 0x4B400000 per element
+__device__ __forceinline__ void mma_u8s8_magic(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0x4B400000));
+}
+__device__ __forceinline__ void fma2(float2& acc, float2 a, float2 b) {   // acc = a * b + acc, per lane, one rounding each
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(reinterpret_cast<unsigned long long&>(acc))
+        : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)));
+}
+
+// Scales of one row of one block: {d*sc, d*sc, -(dmin*mn), -(dmin*mn)} per sub-block, computed on demand.
+struct RowScales {
+    float d, cd, dq, cdq, nd, cnd;          // d, -(d*2^23), d/16, -(d/16*2^23), -dmin, dmin*2^23
+    uint32_t sc[2], mn[2];                  // 6-bit scales / mins of sub-blocks 0-3 and 4-7, one per byte
+    __device__ __forceinline__ float4 get(int k) const {
+        const float fs = __uint_as_float(__byte_perm(sc[k >> 2], 0x4B000000u, 0x7540u | (k & 3)));
+        const float fm = __uint_as_float(__byte_perm(mn[k >> 2], 0x4B000000u, 0x7540u | (k & 3)));
+        const float s0 = (k & 1) ? fmaf(dq, fs, cdq) : fmaf(d, fs, cd);
+        const float nm = fmaf(nd, fm, cnd);
+        return make_float4(s0, s0, nm, nm);
+    }
+};
+__device__ __forceinline__ RowScales decode_scales(const uint4 hdr) {
+    RowScales r;
+    r.d = h2f((uint16_t)(hdr.x & 0xFFFF)); r.nd = -h2f((uint16_t)(hdr.x >> 16));
+    r.dq = r.d * 0.0625f;
+    r.cd = -(r.d * 8388608.f); r.cdq = -(r.dq * 8388608.f); r.cnd = -(r.nd * 8388608.f);
+    r.sc[0] = hdr.y & 0x3F3F3F3Fu; r.mn[0] = hdr.z & 0x3F3F3F3Fu;
+    r.sc[1] = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
+    r.mn[1] = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
+    return r;
+}
+
 // int8 tensor-core tile: D(16x8,s32) = A(16x32,u8 row) * B(32x8,s8 col) + 0
 __device__ __forceinline__ void mma_u8s8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"

@@ -51,8 +51,9 @@ int gemv_parts(int N, int K);
 // raw form: part p of the K split writes plane yparts + p * part_stride ([R][ldy] each); the caller adds the planes in order
 // tiled = true: W is in the tile-major layout produced by gemv_repack_tiled (gemv_tiled_bytes(N, K) bytes)
 int gemv_q4k_q8_parts(const void* W, const XQ8F& x, float* yparts, int N, int K, int R, int ldy, size_t part_stride, int* err, cudaStream_t s, bool pdl, bool tiled);
-size_t gemv_tiled_bytes(int N, int K);
-int gemv_repack_tiled(const void* src, void* dst, int N, int K, cudaStream_t s);
+size_t gemv_tiled_bytes(size_t N, int K);
+// interleave_half = F > 0: src is a stack of [gate F rows | up F rows] matrices; gate and up rows of a feature share a tile
+int gemv_repack_tiled(const void* src, void* dst, size_t N, int K, cudaStream_t s, int interleave_half = 0);
 int gemv_q4k_q8(const void* W, const XQ8F& x, float* y, int N, int K, int R, int ldy, const GemvWorkspace& ws, cudaStream_t s, bool pdl);
 int gemv_q4k_f32(const void* W, const float* x, float* y, int N, int K, int R, int* err, cudaStream_t s);
 
@@ -106,15 +107,20 @@ int attn_decode_seq(float* qkv, int ld, int R, int pos0, int n_head, int n_kv, i
 // ---- moe.cu ----
 // router (reference f32_gemv, fn.hip:252-277) and routing (k_moe_route, fn.hip:167-205) in one launch; counters: T zero-initialised ints (left zero)
 int router_route(const float* W, const float* x, float* logits, int* ids, float* w, int* counters, int E, int K, int k, int T, cudaStream_t s);
-struct MoeParams {
-    const void* w_exp; const void* w_sh; size_t ebytes; int N, K;   // expert matrices [E][N][K/256 blocks] and the shared expert's [N][K/256]
-    const int* ids; const float* slotw; int nslot;                    // [T][nslot] expert ids (-1 = shared) and combine weights
-    XQ8F xq; float* y; int T;
-    int e_lo, e_hi, own_shared;                                        // routed experts owned by this GPU, and whether it computes the shared slot
+// Routed experts grouped by expert (see moe.cu). Expert tensors tile-major: gate|up repacked with interleave_half = F.
+constexpr int MOE_MAX_PAIRS = 32 * 16;
+struct MoeGroupParams {
+    const void* w_gate_up; const void* w_down; const void* sh_gate_up; const void* sh_down;   // this GPU's experts [e_lo, e_hi) and the shared expert
+    int E, F, n_expert, nslot, T;                       // hidden, expert FFN, routed experts, slots per row (k + 1), rows
+    int e_lo, e_hi, own_shared;
+    const int* ids;                                     // [T][nslot], -1 = shared
+    XQ8F xq, xq2;                                       // quantised rows [T] (K = E) in; quantised silu(gate)*up per pair [T * nslot] (K = F) scratch
+    float* v;                                           // per-pair outputs [T * nslot][E] (pairs of experts owned elsewhere are not written)
+    void* segs; int* ctl; unsigned long long* touched;  // device scratch: MOE_MAX_PAIRS segments of 64 bytes, 4 ints, optional counter of touched experts
+    int* err;
 };
-int moe_gemv_up(const MoeParams& p, cudaStream_t s);                  // reference gemv_moe, xrow_te = false (gemv.h:46)
-int moe_silu_quant(const float* gu, int F, const int* ids, int e_lo, int e_hi, int own_shared, XQ8F xq, int pairs, cudaStream_t s);   // fn.hip:206-211
-int moe_down_pairs(const MoeParams& p, cudaStream_t s);               // expert-parallel form: per-pair outputs, zeros for experts owned elsewhere
+size_t moe_seg_bytes();
+int moe_experts_grouped(const MoeGroupParams& p, cudaStream_t s);   // reference gemv_moe + moe_silu_quant + gemv_moe_down (gemv.h:43-50, fn.hip:206-211)
 // y[t] = sum over slots e in order of fmaf(slotw[t][e], v[(t, e)], acc) (reference combine, gemv.hip:1104-1112)
 int moe_combine(const float* v, const float* slotw, float* y, int T, int nslot, int E, cudaStream_t s);
 

@@ -98,141 +98,182 @@ __global__ void __launch_bounds__(256) k_router_route(const float* __restrict__ 
     }
 }
 
-// ---- one 16-row tile of an expert matrix against one activation row: blocks in order, weights read straight from
-// global memory (each expert tile is touched once), CH blocks per batch so that their loads share one round trip.
-// Returns the column of interest in r0 / r1 (rows g, g+8). Scales are decoded in registers per lane (rows g, g+8):
-// a 6-bit value v becomes the float 2^23 + v by a byte permute, and fmaf(d, 2^23 + v, -(d * 2^23)) is exactly d * v;
-// odd sub-blocks take the high nibbles unshifted (16 * q), their d carries the exact 1/16. ----
-struct MoeRowScales {
-    float d, cd, dq, cdq, nd, cnd; uint32_t sc[2], mn[2];
-    __device__ __forceinline__ void get(int k, float& s0, float& nm) const {
-        const float fs = __uint_as_float(__byte_perm(sc[k >> 2], 0x4B000000u, 0x7540u | (k & 3)));
-        const float fm = __uint_as_float(__byte_perm(mn[k >> 2], 0x4B000000u, 0x7540u | (k & 3)));
-        s0 = (k & 1) ? fmaf(dq, fs, cdq) : fmaf(d, fs, cd);
-        nm = fmaf(nd, fm, cnd);
+// ---- routed-expert GEMVs, grouped by expert -------------------------------------------------------------------------
+// After routing, the (row, slot) pairs of a pass are grouped by expert: one SEGMENT per touched expert this GPU owns
+// (and one for the shared expert), holding up to 8 pairs as the columns of the tensor-core tile; an expert with more
+// than 8 pairs gets several segments. Every touched expert matrix is therefore streamed from HBM once per pass for all
+// the rows that routed to it (once per 8 of them). Work unit = (segment, 4 consecutive 16-row tiles); warps take units
+// from a global ticket counter (which warp computes a unit has no influence on the result: a unit is computed by one
+// warp alone, blocks in order along K, no split), and stream their tiles through a private ring of bulk async copies.
+// Expert tensors are kept tile-major (the layout of gemv_q4k.cu: per (16-row tile, block) 2304 contiguous bytes); the
+// gate|up tensor is repacked with gate rows 8q..8q+7 and up rows 8q..8q+7 sharing tile q, so that a lane holds gate
+// and up of the same feature and the SiLU-gated product and its int8 quantisation (fn.hip:206-211) finish in registers:
+// a unit's 4 tiles are exactly one 32-feature quantisation group.
+struct MoeSeg { int expert, ncols, cols[8]; int pad[6]; };   // 64 bytes; cols = pair indices t * nslot + e
+constexpr int MOE_WARPS = 8, MOE_DEPTH = 3, MOE_UNIT_TILES = 4;
+
+// one CTA: segments in increasing expert id, the shared expert last; pairs of a segment in increasing pair index
+__global__ void __launch_bounds__(512) k_moe_group(const int* __restrict__ ids, int npairs, int n_expert, int e_lo, int e_hi, int own_shared,
+                                                   MoeSeg* __restrict__ segs, int* __restrict__ ctl, unsigned long long* __restrict__ touched) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ int sid[MOE_MAX_PAIRS]; __shared__ int soff[1026];
+    for (int i = threadIdx.x; i < npairs; i += 512) sid[i] = ids[i];
+    __syncthreads();
+    // bucket b: expert e_lo + b (b < e_hi - e_lo), then the shared expert
+    const int nown = e_hi - e_lo, nb = nown + (own_shared ? 1 : 0);
+    for (int b = threadIdx.x; b < nb; b += 512) {
+        const int want = b < nown ? e_lo + b : -1; int c = 0;
+        for (int i = 0; i < npairs; ++i) c += sid[i] == want;
+        soff[b] = (c + 7) >> 3;
     }
-};
-__device__ __forceinline__ MoeRowScales moe_decode_scales(const uint4 hdr) {
-    MoeRowScales r;
-    r.d = h2f((uint16_t)(hdr.x & 0xFFFF)); r.nd = -h2f((uint16_t)(hdr.x >> 16));
-    r.dq = r.d * 0.0625f;
-    r.cd = -(r.d * 8388608.f); r.cdq = -(r.dq * 8388608.f); r.cnd = -(r.nd * 8388608.f);
-    r.sc[0] = hdr.y & 0x3F3F3F3Fu; r.mn[0] = hdr.z & 0x3F3F3F3Fu;
-    r.sc[1] = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
-    r.mn[1] = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
-    return r;
+    __syncthreads();
+    if (threadIdx.x == 0) {   // exclusive prefix sum (at most 1025 buckets)
+        int acc = 0, nt = 0;
+        for (int b = 0; b < nb; ++b) { const int v = soff[b]; soff[b] = acc; acc += v; nt += v > 0; }
+        ctl[0] = acc; ctl[1] = 0; ctl[2] = 0;   // segments, ticket counters of the two GEMVs
+        if (touched) atomicAdd(touched, (unsigned long long)nt);
+    }
+    __syncthreads();
+    for (int b = threadIdx.x; b < nb; b += 512) {
+        const int want = b < nown ? e_lo + b : -1; int c = 0; MoeSeg* sg = segs + soff[b];
+        for (int i = 0; i < npairs; ++i)
+            if (sid[i] == want) { MoeSeg* q = sg + (c >> 3); if ((c & 7) == 0) { q->expert = want; q->ncols = 0; } q->cols[c & 7] = i; q->ncols = (c & 7) + 1; ++c; }
+    }
 }
-template <int CH>
-__device__ __forceinline__ void expert_tile(const uint8_t* __restrict__ W, int row_bytes, int nb, const uint4* __restrict__ xq, const float4* __restrict__ xsc,
-                                            int xtile, int xcol, int lane, float& r0, float& r1) {
-    const int g = lane >> 2, t = lane & 3;
-    float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
-    const uint8_t* rowa = W + (size_t)g * row_bytes;
-    const uint8_t* rowb = W + (size_t)(g + 8) * row_bytes;
-    for (int b0 = 0; b0 < nb; b0 += CH) {
-        uint4 ha[CH], hb[CH]; uint2 wa[CH][4], wb[CH][4];
+
+struct MoeGArgs {
+    const uint8_t* w_exp; const uint8_t* w_sh;     // tile-major expert tensors: this GPU's experts [e_hi - e_lo][tiles][nb] chunks, and the shared expert's
+    int e_lo, tiles, nb;                            // tiles of 16 rows per expert, blocks per row
+    const MoeSeg* segs; int* ctl; int ticket;      // ticket counter index in ctl (1 = gate|up, 2 = down)
+    const uint8_t* xq; const float* xsc; int xK, xdiv;   // activations: fragment-major rows of xK elements; row of pair p = p / xdiv
+    float* y; int N;                                // MODE 1: y[pair][N]
+    int8_t* oq; float* osc; int F;                  // MODE 0: quantised silu(gate) * up per pair, F features
+    int* err;
+};
+// MODE 0: gate|up with the fused SiLU-gated product + quantisation; MODE 1: down projection (per-pair f32 outputs)
+template <int MODE, int SB>
+__global__ void __launch_bounds__(MOE_WARPS * 32, 1) k_moe_gemv_grouped(MoeGArgs a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int STAGE = SB * 2304;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    uint8_t* ring = smem + warp * MOE_DEPTH * STAGE;
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + MOE_WARPS * MOE_DEPTH * STAGE);
+    const uint32_t bar0 = smem_u32(&bars[warp * MOE_DEPTH]);
+    pdl_launch_dependents();
+    if (lane == 0) { for (int s = 0; s < MOE_DEPTH; ++s) mbar_init(bar0 + 8 * s, 1); fence_barrier_init(); }
+    __syncwarp();
+    pdl_wait();
+    const int spt = a.nb / SB;                                 // stages per tile
+    const int ups = a.tiles / MOE_UNIT_TILES, total = a.ctl[0] * ups, spu = MOE_UNIT_TILES * spt;   // units per segment, units, stages per unit
+    auto grab = [&]() { int u = 0; if (lane == 0) u = atomicAdd(a.ctl + a.ticket, 1); return __shfl_sync(0xffffffffu, u, 0); };
+    auto unit_base = [&](int u) -> const uint8_t* {           // first chunk of the unit's first tile
+        const MoeSeg& sg = a.segs[u / ups];
+        const uint8_t* w = sg.expert >= 0 ? a.w_exp + (size_t)(sg.expert - a.e_lo) * a.tiles * a.nb * 2304 : a.w_sh;
+        return w + (size_t)(u % ups) * MOE_UNIT_TILES * a.nb * 2304;
+    };
+    // issue cursor: unit iu, stage is (0..spu) of it; the copies of a unit are consecutive in memory (4 tiles x nb chunks)
+    int iu = grab(), is = 0, icount = 0; const uint8_t* isrc = iu < total ? unit_base(iu) : nullptr;
+    int nu = -1;                                               // unit grabbed by the issue cursor while `cu` is still being computed
+    auto issue = [&]() {
+        if (iu >= total) return;
+        const uint32_t bar = bar0 + 8 * (icount % MOE_DEPTH);
+        if (lane == 0) { mbar_expect_tx(bar, STAGE); bulk_g2s(smem_u32(ring + (icount % MOE_DEPTH) * STAGE), isrc, STAGE, bar); }
+        ++icount; isrc += STAGE;
+        if (++is == spu) { is = 0; iu = grab(); nu = iu; isrc = iu < total ? unit_base(iu) : nullptr; }
+    };
+    int cu = iu;
+    for (int i = 0; i < MOE_DEPTH; ++i) issue();
+    int ccount = 0; bool ok = true;
+    while (cu < total && ok) {
+        const MoeSeg sg = a.segs[cu / ups];
+        // this lane's columns: B fragments of column g, scales of columns 2t and 2t + 1
+        const int rg = g < sg.ncols ? sg.cols[g] / a.xdiv : -1;
+        const int c0 = 2 * t < sg.ncols ? sg.cols[2 * t] : -1, c1 = 2 * t + 1 < sg.ncols ? sg.cols[2 * t + 1] : -1;
+        const int r0 = c0 >= 0 ? c0 / a.xdiv : -1, r1 = c1 >= 0 ? c1 / a.xdiv : -1;
+        const uint4* xq_g = rg >= 0 ? reinterpret_cast<const uint4*>(a.xq) + ((size_t)(rg >> 3) * (a.xK >> 6)) * 32 + ((rg & 7) * 4 + t) : nullptr;
+        const float* xs0 = r0 >= 0 ? a.xsc + xq_d_index(r0, 0, a.xK) : nullptr;
+        const float* xs1 = r1 >= 0 ? a.xsc + xq_d_index(r1, 0, a.xK) : nullptr;
+        float act[MOE_UNIT_TILES][2];
+        for (int ti = 0; ti < MOE_UNIT_TILES && ok; ++ti) {
+            float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+            for (int st = 0; st < spt && ok; ++st) {
+                const int s = ccount % MOE_DEPTH;
+                ok = mbar_wait(bar0 + 8 * s, (ccount / MOE_DEPTH) & 1, a.err);
+                if (!ok) break;
+                const uint8_t* sp = ring + s * STAGE;
 #pragma unroll
-        for (int c = 0; c < CH; ++c) {
-            const int b = b0 + c < nb ? b0 + c : nb - 1;
-            ha[c] = __ldg(reinterpret_cast<const uint4*>(rowa + (size_t)b * 144)); hb[c] = __ldg(reinterpret_cast<const uint4*>(rowb + (size_t)b * 144));
+                for (int blk = 0; blk < SB; ++blk) {
+                    const int b = st * SB + blk;
+                    const RowScales ra = decode_scales(*reinterpret_cast<const uint4*>(sp + g * 16 + blk * 2304));
+                    const RowScales rb = decode_scales(*reinterpret_cast<const uint4*>(sp + g * 16 + 128 + blk * 2304));
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                wa[c][j] = __ldg(reinterpret_cast<const uint2*>(rowa + (size_t)b * 144 + 16 + 8 * t + 32 * j));
-                wb[c][j] = __ldg(reinterpret_cast<const uint2*>(rowb + (size_t)b * 144 + 16 + 8 * t + 32 * j));
+                    for (int j = 0; j < 4; ++j) {
+                        const uint4 ww = *reinterpret_cast<const uint4*>(sp + 256 + lane * 16 + blk * 2304 + 512 * j);
+                        const uint32_t alo[4] = {ww.x & 0x0F0F0F0Fu, ww.z & 0x0F0F0F0Fu, ww.y & 0x0F0F0F0Fu, ww.w & 0x0F0F0F0Fu};
+                        const uint32_t ahi[4] = {ww.x & 0xF0F0F0F0u, ww.z & 0xF0F0F0F0u, ww.y & 0xF0F0F0F0u, ww.w & 0xF0F0F0F0u};
+                        const float4 sa0 = ra.get(2 * j), sb0 = rb.get(2 * j), sa1 = ra.get(2 * j + 1), sb1 = rb.get(2 * j + 1);
+                        const uint4 xf = xq_g ? __ldg(xq_g + (size_t)(b * 4 + j) * 32) : make_uint4(0, 0, 0, 0);
+                        // scales {d, s} of sub-blocks 2j (low nibbles) and 2j + 1 (high nibbles) for this lane's two columns
+                        const int sb = b * 8 + 2 * j;
+                        float2 xd0 = make_float2(0.f, 0.f), xs0v = xd0, xd1 = xd0, xs1v = xd0;
+                        if (xs0) { xd0.x = __ldg(xs0 + sb * 16); xs0v.x = __ldg(xs0 + sb * 16 + 2); xd1.x = __ldg(xs0 + (sb + 1) * 16); xs1v.x = __ldg(xs0 + (sb + 1) * 16 + 2); }
+                        if (xs1) { xd0.y = __ldg(xs1 + sb * 16); xs0v.y = __ldg(xs1 + sb * 16 + 2); xd1.y = __ldg(xs1 + (sb + 1) * 16); xs1v.y = __ldg(xs1 + (sb + 1) * 16 + 2); }
+                        int m0[4], m1[4];
+                        mma_u8s8_magic(m0, alo, xf.x, xf.y);
+                        mma_u8s8_magic(m1, ahi, xf.z, xf.w);
+                        const float2 mg = make_float2(-12582912.f, -12582912.f);
+                        fma2(acc0, mul2(make_float2(sa0.x, sa0.y), xd0), add2(make_float2(__int_as_float(m0[0]), __int_as_float(m0[1])), mg));
+                        fma2(acc0, make_float2(sa0.z, sa0.w), xs0v);
+                        fma2(acc1, mul2(make_float2(sb0.x, sb0.y), xd0), add2(make_float2(__int_as_float(m0[2]), __int_as_float(m0[3])), mg));
+                        fma2(acc1, make_float2(sb0.z, sb0.w), xs0v);
+                        fma2(acc0, mul2(make_float2(sa1.x, sa1.y), xd1), add2(make_float2(__int_as_float(m1[0]), __int_as_float(m1[1])), mg));
+                        fma2(acc0, make_float2(sa1.z, sa1.w), xs1v);
+                        fma2(acc1, mul2(make_float2(sb1.x, sb1.y), xd1), add2(make_float2(__int_as_float(m1[2]), __int_as_float(m1[3])), mg));
+                        fma2(acc1, make_float2(sb1.z, sb1.w), xs1v);
+                    }
+                }
+                __syncwarp();   // every lane has read the stage before it is refilled
+                ++ccount;
+                issue();
+            }
+            if (!ok) break;
+            const int tile = (cu % ups) * MOE_UNIT_TILES + ti;
+            if constexpr (MODE == 1) {
+                if (c0 >= 0) { a.y[(size_t)c0 * a.N + tile * 16 + g] = acc0.x; a.y[(size_t)c0 * a.N + tile * 16 + g + 8] = acc1.x; }
+                if (c1 >= 0) { a.y[(size_t)c1 * a.N + tile * 16 + g] = acc0.y; a.y[(size_t)c1 * a.N + tile * 16 + g + 8] = acc1.y; }
+            } else {   // rows g = gate of feature 8 * tile + g, rows g + 8 = up of the same feature
+                act[ti][0] = silu_det(acc0.x) * acc1.x; act[ti][1] = silu_det(acc0.y) * acc1.y;
             }
         }
+        if (!ok) break;
+        if constexpr (MODE == 0) {
+            // quantise the unit's 32 features (8 * ti + g over the 4 tiles and the 8 lanes that share t) per column:
+            // amax / 127, q = rint(v * (127 / amax)), s = d * sum(q) (gemv.hip:36-51)
+            const int sbk = cu % ups;                           // 32-feature sub-block of the F features
 #pragma unroll
-        for (int c = 0; c < CH; ++c) {
-            const int b = b0 + c;
-            if (b < nb) {
-                const MoeRowScales ra = moe_decode_scales(ha[c]), rb = moe_decode_scales(hb[c]);
+            for (int c = 0; c < 2; ++c) {
+                float amax = 0.f;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint2 w0 = wa[c][j], w1 = wb[c][j];
-                    const uint32_t alo[4] = {w0.x & 0x0F0F0F0Fu, w1.x & 0x0F0F0F0Fu, w0.y & 0x0F0F0F0Fu, w1.y & 0x0F0F0F0Fu};
-                    const uint32_t ahi[4] = {w0.x & 0xF0F0F0F0u, w1.x & 0xF0F0F0F0u, w0.y & 0xF0F0F0F0u, w1.y & 0xF0F0F0F0u};
-                    float sa0, na0, sb0, nb0, sa1, na1, sb1, nb1;
-                    ra.get(2 * j, sa0, na0); rb.get(2 * j, sb0, nb0); ra.get(2 * j + 1, sa1, na1); rb.get(2 * j + 1, sb1, nb1);
-                    const uint4 xf = __ldg(xq + ((size_t)xtile * nb * 4 + b * 4 + j) * 32 + lane);
-                    const float4 x0 = __ldg(xsc + ((size_t)xtile * nb * 8 + b * 8 + 2 * j) * 4 + t), x1 = __ldg(xsc + ((size_t)xtile * nb * 8 + b * 8 + 2 * j + 1) * 4 + t);
-                    int c0[4], c1[4];
-                    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-                                 : "=r"(c0[0]), "=r"(c0[1]), "=r"(c0[2]), "=r"(c0[3]) : "r"(alo[0]), "r"(alo[1]), "r"(alo[2]), "r"(alo[3]), "r"(xf.x), "r"(xf.y), "r"(0));
-                    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-                                 : "=r"(c1[0]), "=r"(c1[1]), "=r"(c1[2]), "=r"(c1[3]) : "r"(ahi[0]), "r"(ahi[1]), "r"(ahi[2]), "r"(ahi[3]), "r"(xf.z), "r"(xf.w), "r"(0));
-                    // columns 2t, 2t+1 of the activation tile; only column xcol is kept at the end
-                    acc0.x = fmaf(sa0 * x0.x, (float)c0[0], acc0.x); acc0.x = fmaf(na0, x0.z, acc0.x);
-                    acc0.y = fmaf(sa0 * x0.y, (float)c0[1], acc0.y); acc0.y = fmaf(na0, x0.w, acc0.y);
-                    acc1.x = fmaf(sb0 * x0.x, (float)c0[2], acc1.x); acc1.x = fmaf(nb0, x0.z, acc1.x);
-                    acc1.y = fmaf(sb0 * x0.y, (float)c0[3], acc1.y); acc1.y = fmaf(nb0, x0.w, acc1.y);
-                    acc0.x = fmaf(sa1 * x1.x, (float)c1[0], acc0.x); acc0.x = fmaf(na1, x1.z, acc0.x);
-                    acc0.y = fmaf(sa1 * x1.y, (float)c1[1], acc0.y); acc0.y = fmaf(na1, x1.w, acc0.y);
-                    acc1.x = fmaf(sb1 * x1.x, (float)c1[2], acc1.x); acc1.x = fmaf(nb1, x1.z, acc1.x);
-                    acc1.y = fmaf(sb1 * x1.y, (float)c1[3], acc1.y); acc1.y = fmaf(nb1, x1.w, acc1.y);
+                for (int ti = 0; ti < MOE_UNIT_TILES; ++ti) amax = fmaxf(amax, fabsf(act[ti][c]));
+#pragma unroll
+                for (int off = 4; off < 32; off <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+                const float dd = amax / 127.f, id = amax > 0.f ? 127.f / amax : 0.f;
+                int q[MOE_UNIT_TILES], sum = 0;
+#pragma unroll
+                for (int ti = 0; ti < MOE_UNIT_TILES; ++ti) { q[ti] = __float2int_rn(act[ti][c] * id); sum += q[ti]; }
+#pragma unroll
+                for (int off = 4; off < 32; off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+                const int pair = c ? c1 : c0;
+                if (pair >= 0) {
+#pragma unroll
+                    for (int ti = 0; ti < MOE_UNIT_TILES; ++ti) a.oq[xq_q_index(pair, sbk * 32 + 8 * ti + g, a.F)] = (int8_t)q[ti];
+                    if (g == 0) { const size_t di = xq_d_index(pair, sbk, a.F); a.osc[di] = dd; a.osc[di + 2] = dd * (float)sum; }
                 }
             }
         }
+        cu = (cu == iu) ? iu : nu;   // the next unit is the one the issue cursor moved on to
     }
-    // hand column xcol to every lane of its row group: it lives in lane (g, xcol/2), component xcol & 1
-    const float m0 = (xcol & 1) ? acc0.y : acc0.x, m1 = (xcol & 1) ? acc1.y : acc1.x;
-    r0 = __shfl_sync(0xffffffffu, m0, (lane & ~3) | (xcol >> 1));
-    r1 = __shfl_sync(0xffffffffu, m1, (lane & ~3) | (xcol >> 1));
-}
-
-struct MoeArgs {
-    const uint8_t* w_exp; const uint8_t* w_sh; size_t ebytes; int N, K;     // expert matrices [E][N][K/256 blocks], shared [N][K/256]
-    const int* ids; const float* slotw; int nslot;                           // [T][nslot]
-    const uint4* xq; const float4* xsc;                                      // quantised activations (rows = T, or T*nslot for the down projection)
-    float* y; int T;
-    int e_lo, e_hi, own_shared;                                              // routed experts owned by this GPU [e_lo, e_hi) and whether it computes the shared slot
-};
-__device__ __forceinline__ bool moe_owned(const MoeArgs& a, int id) { return id >= 0 ? (id >= a.e_lo && id < a.e_hi) : a.own_shared != 0; }
-// gate|up: y[(t,e)][N] = W[ids[t,e]] . x[t]; one warp per (pair, 16-row tile)
-__global__ void __launch_bounds__(256) k_moe_gemv(MoeArgs a) {
-    pdl_launch_dependents();
-    pdl_wait();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tiles = a.N / 16, unit = blockIdx.x * 8 + warp;
-    if (unit >= a.T * a.nslot * tiles) return;
-    const int pair = unit / tiles, tile = unit % tiles, t = pair / a.nslot;
-    const int id = a.ids[pair];
-    if (!moe_owned(a, id)) return;                                           // expert lives on another GPU
-    const int nb = a.K / 256, row_bytes = nb * 144;
-    const uint8_t* W = (id >= 0 ? a.w_exp + (size_t)id * a.ebytes : a.w_sh) + (size_t)tile * 16 * row_bytes;
-    float r0, r1;
-    expert_tile<4>(W, row_bytes, nb, a.xq, a.xsc, t >> 3, t & 7, lane, r0, r1);
-    const int g = lane >> 2;
-    if ((lane & 3) == 0) { a.y[(size_t)pair * a.N + tile * 16 + g] = r0; a.y[(size_t)pair * a.N + tile * 16 + g + 8] = r1; }
-}
-// per-pair expert output of the down projection: v[(t,e)][N] = W_down[ids[t,e]] . act[(t,e)] (expert-parallel form)
-__global__ void __launch_bounds__(256) k_moe_down_pairs(MoeArgs a) {
-    pdl_launch_dependents();
-    pdl_wait();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tiles = a.N / 16, unit = blockIdx.x * 8 + warp;
-    if (unit >= a.T * a.nslot * tiles) return;
-    const int pair = unit / tiles, tile = unit % tiles;
-    const int id = a.ids[pair];
-    const int g = lane >> 2;
-    if (!moe_owned(a, id)) {   // not ours: contribute exact zeros to the exchange buffer
-        if ((lane & 3) == 0) { a.y[(size_t)pair * a.N + tile * 16 + g] = 0.f; a.y[(size_t)pair * a.N + tile * 16 + g + 8] = 0.f; }
-        return;
-    }
-    const int nb = a.K / 256, row_bytes = nb * 144;
-    const uint8_t* W = (id >= 0 ? a.w_exp + (size_t)id * a.ebytes : a.w_sh) + (size_t)tile * 16 * row_bytes;
-    float r0, r1;
-    expert_tile<2>(W, row_bytes, nb, a.xq, a.xsc, pair >> 3, pair & 7, lane, r0, r1);
-    if ((lane & 3) == 0) { a.y[(size_t)pair * a.N + tile * 16 + g] = r0; a.y[(size_t)pair * a.N + tile * 16 + g + 8] = r1; }
-}
-// q8(silu(g) * u) per (t,e) row: gu [pairs][2F] (fn.hip:206-211); pairs of experts that live elsewhere are skipped
-__global__ void __launch_bounds__(256) k_moe_silu_quant(const float* __restrict__ gu, int F, const int* __restrict__ ids, int e_lo, int e_hi, int own_shared, int8_t* __restrict__ q, float* __restrict__ sc) {
-    pdl_launch_dependents();
-    pdl_wait();
-    const int pair = blockIdx.y, sb = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (sb * 32 >= F) return;
-    const int id = ids[pair]; if (id >= 0 ? (id < e_lo || id >= e_hi) : !own_shared) return;
-    const int i = sb * 32 + lane;
-    warp_quant32_store(silu_det(gu[(size_t)pair * 2 * F + i]) * gu[(size_t)pair * 2 * F + F + i], pair, sb, F, q, sc, lane);
 }
 
 // in-order weighted combine of the per-(row, slot) expert outputs (gemv.hip:1104-1112); used by the kernel-level entry
@@ -252,19 +293,36 @@ int router_route(const float* W, const float* x, float* logits, int* ids, float*
     HP_CUDA(launch_pdl<8>(k_router_route, dim3((N * 32 + 255) / 256, T), dim3(256), 0, s, W, x, logits, N, K, ids, w, E, k, counters));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
-static MoeArgs moe_args(const MoeParams& p) {
-    MoeArgs a; a.w_exp = (const uint8_t*)p.w_exp; a.w_sh = (const uint8_t*)p.w_sh; a.ebytes = p.ebytes; a.N = p.N; a.K = p.K; a.ids = p.ids; a.slotw = p.slotw; a.nslot = p.nslot;
-    a.xq = (const uint4*)p.xq.q; a.xsc = (const float4*)p.xq.sc; a.y = p.y; a.T = p.T; a.e_lo = p.e_lo; a.e_hi = p.e_hi; a.own_shared = p.own_shared; return a;
+size_t moe_seg_bytes() { return (size_t)MOE_MAX_PAIRS * sizeof(MoeSeg); }
+template <int MODE, int SB>
+static int launch_grouped(const MoeGArgs& a, cudaStream_t s) {
+    const size_t smem = (size_t)MOE_WARPS * MOE_DEPTH * SB * 2304 + MOE_WARPS * MOE_DEPTH * 8;
+    static bool attr[MAX_DEVICES] = {};
+    const int dev = current_device(); if (dev < 0) return HP_ECUDA;
+    if (!attr[dev]) { HP_CUDA(cudaFuncSetAttribute(k_moe_gemv_grouped<MODE, SB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr[dev] = true; }
+    HP_CUDA(launch_pdl<8>(k_moe_gemv_grouped<MODE, SB>, dim3(GEMV_NCTA), dim3(MOE_WARPS * 32), smem, s, a));
+    return HP_OK;
 }
-int moe_gemv_up(const MoeParams& p, cudaStream_t s) {
-    HP_REQUIRE(p.N % 16 == 0 && p.K % 256 == 0 && p.T >= 1 && p.nslot >= 1, "moe_gemv_up: bad shape");
-    const int units = p.T * p.nslot * (p.N / 16);
-    HP_CUDA(launch_pdl<8>(k_moe_gemv, dim3((units + 7) / 8), dim3(256), 0, s, moe_args(p)));
-    HP_CUDA(cudaGetLastError()); return HP_OK;
+template <int MODE>
+static int launch_grouped_sb(const MoeGArgs& a, cudaStream_t s) {
+    return a.nb % 4 == 0 ? launch_grouped<MODE, 4>(a, s) : a.nb % 2 == 0 ? launch_grouped<MODE, 2>(a, s) : launch_grouped<MODE, 1>(a, s);
 }
-int moe_silu_quant(const float* gu, int F, const int* ids, int e_lo, int e_hi, int own_shared, XQ8F xq, int pairs, cudaStream_t s) {
-    HP_REQUIRE(F % 64 == 0 && pairs >= 1, "moe_silu_quant: bad shape");
-    HP_CUDA(launch_pdl<8>(k_moe_silu_quant, dim3((F / 32 + 7) / 8, pairs), dim3(256), 0, s, gu, F, ids, e_lo, e_hi, own_shared, (int8_t*)xq.q, (float*)xq.sc));
+int moe_experts_grouped(const MoeGroupParams& p, cudaStream_t s) {
+    HP_REQUIRE(p.E % 256 == 0 && p.F % 256 == 0 && p.T >= 1 && p.nslot >= 1 && p.T * p.nslot <= MOE_MAX_PAIRS && p.n_expert <= 1024, "moe_experts_grouped: bad shape");
+    HP_REQUIRE(p.segs && p.ctl && p.ids && p.v, "moe_experts_grouped: null pointer");
+    const int npairs = p.T * p.nslot;
+    HP_CUDA(launch_pdl<8>(k_moe_group, dim3(1), dim3(512), 0, s, p.ids, npairs, p.n_expert, p.e_lo, p.e_hi, p.own_shared, (MoeSeg*)p.segs, p.ctl, p.touched));
+    MoeGArgs a; a.e_lo = p.e_lo; a.segs = (const MoeSeg*)p.segs; a.ctl = p.ctl; a.err = p.err;
+    // gate|up: [2F rows][E]; tile q = gate rows 8q.. | up rows 8q..; 4 tiles = one 32-feature quantisation group
+    a.w_exp = (const uint8_t*)p.w_gate_up; a.w_sh = (const uint8_t*)p.sh_gate_up; a.tiles = 2 * p.F / 16; a.nb = p.E / 256; a.ticket = 1;
+    a.xq = (const uint8_t*)p.xq.q; a.xsc = (const float*)p.xq.sc; a.xK = p.E; a.xdiv = p.nslot;
+    a.y = nullptr; a.N = 0; a.oq = (int8_t*)p.xq2.q; a.osc = (float*)p.xq2.sc; a.F = p.F;
+    { const int rc = launch_grouped_sb<0>(a, s); if (rc != HP_OK) return rc; }
+    // down: [E rows][F]; per-pair outputs
+    a.w_exp = (const uint8_t*)p.w_down; a.w_sh = (const uint8_t*)p.sh_down; a.tiles = p.E / 16; a.nb = p.F / 256; a.ticket = 2;
+    a.xq = (const uint8_t*)p.xq2.q; a.xsc = (const float*)p.xq2.sc; a.xK = p.F; a.xdiv = 1;
+    a.y = p.v; a.N = p.E; a.oq = nullptr; a.osc = nullptr;
+    { const int rc = launch_grouped_sb<1>(a, s); if (rc != HP_OK) return rc; }
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 int moe_combine(const float* v, const float* slotw, float* y, int T, int nslot, int E, cudaStream_t s) {
@@ -272,11 +330,4 @@ int moe_combine(const float* v, const float* slotw, float* y, int T, int nslot, 
     k_moe_combine<<<dim3((E + 255) / 256, T), 256, 0, s>>>(v, slotw, y, nslot, E);
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
-int moe_down_pairs(const MoeParams& p, cudaStream_t s) {
-    HP_REQUIRE(p.N % 16 == 0 && p.K % 256 == 0 && p.T >= 1 && p.nslot >= 1, "moe_down_pairs: bad shape");
-    const int units = p.T * p.nslot * (p.N / 16);
-    HP_CUDA(launch_pdl<8>(k_moe_down_pairs, dim3((units + 7) / 8), dim3(256), 0, s, moe_args(p)));
-    HP_CUDA(cudaGetLastError()); return HP_OK;
-}
-
 }  // namespace hp

@@ -167,6 +167,20 @@ class Engine:
         lib().hp_pass_weight_bytes.restype = ctypes.c_size_t
         return lib().hp_pass_weight_bytes(self._h, int(mtp), int(with_head))
 
+    def moe_touched(self):
+        """(layer, expert) matrices touched by the passes since the last call."""
+        n = ctypes.c_ulonglong(0)
+        check(lib().hp_moe_touched(self._h, ctypes.byref(n)))
+        return n.value
+
+    def ep_exchange_us(self, R, reps=20):
+        us = ctypes.c_float(0)
+        check(lib().hp_ep_exchange_us(self._h, R, reps, ctypes.byref(us)))
+        return us.value
+
+    def last_round_kernels(self):
+        return lib().hp_last_round_kernels(self._h)
+
     # ---- fused device-side round
     def spec_begin(self, slot, id_last, pos, h_pending_ptr):
         check(lib().hp_spec_begin(self._h, slot, int(id_last), int(pos), ctypes.c_void_p(h_pending_ptr)))

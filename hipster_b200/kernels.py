@@ -109,17 +109,30 @@ def attn_decode(qkv, pos0, n_head, n_kv, n_rot, q_norm, k_norm, rope, kc, vc, ma
     return out, xq
 
 
+def repack_tiled(w, N, K, interleave_half=0):
+    """ggml Q4_K [N][K/256 blocks] (uint8 tensor) -> the library's tile-major streaming layout (same bytes, permuted)."""
+    L = lib()
+    L.hp_q4k_tiled_bytes.restype = ctypes.c_size_t
+    L.hp_q4k_tiled_bytes.argtypes = [ctypes.c_size_t, ctypes.c_int]
+    out = torch.empty(L.hp_q4k_tiled_bytes(N, K), dtype=torch.uint8, device=w.device)
+    check(L.hp_q4k_repack_tiled(ptr(w), ptr(out), ctypes.c_size_t(N), K, interleave_half, _stream()))
+    return out
+
+
 def moe_layer(xn, router, exp_gate_up, exp_down, sh_gate_up, sh_down, F, n_expert, k):
     """One mixture-of-experts FFN over the rows of xn f32 [T][E] -> (ids int32 [T][k+1], weights f32 [T][k+1], y f32 [T][E]).
+    The expert tensors are given in ggml order and repacked here (an engine does that once at load).
     Reference: Qwen4Exp::moe_layer (qwen4exp.cpp:345-354)."""
     L = lib()
     L.hp_moe_workspace_bytes.restype = ctypes.c_size_t
     T, E = xn.shape
     xq = quantize_x_q8(xn)
+    egu = repack_tiled(exp_gate_up, n_expert * 2 * F, E, F); edn = repack_tiled(exp_down, n_expert * E, F, 0)
+    sgu = repack_tiled(sh_gate_up, 2 * F, E, F); sdn = repack_tiled(sh_down, E, F, 0)
     ws = torch.empty(L.hp_moe_workspace_bytes(T, E, F, n_expert, k), dtype=torch.uint8, device=xn.device)
     ids = torch.empty((T, k + 1), dtype=torch.int32, device=xn.device)
     w = torch.empty((T, k + 1), dtype=torch.float32, device=xn.device)
     y = torch.empty((T, E), dtype=torch.float32, device=xn.device)
-    check(L.hp_moe_layer(ptr(xn), ptr(xq.q), ptr(xq.sc), ptr(router), ptr(exp_gate_up), ptr(exp_down), ptr(sh_gate_up), ptr(sh_down), T, E, F, n_expert, k,
+    check(L.hp_moe_layer(ptr(xn), ptr(xq.q), ptr(xq.sc), ptr(router), ptr(egu), ptr(edn), ptr(sgu), ptr(sdn), T, E, F, n_expert, k,
                          ptr(ids), ptr(w), ptr(y), ptr(ws), _stream()))
     return ids, w, y

@@ -93,6 +93,13 @@ int hp_gdn_layer(const float* rows_dev, int ld, int T, int n_replay, int n_qk, i
                  const void* norm_w_bf16_dev, float* state_dev, float* conv_state_dev, float* saved_dev, float* out_dev, void* xq_q_dev, void* xq_sc_dev,
                  float* snap_dev, float eps, int sigmoid_gate, void* stream);
 
+/* The streaming layout of the engine's GEMVs: the same Q4_K bytes, permuted so that each (16-row tile, 256-element block)
+ * is one contiguous 2304-byte chunk in tensor-core fragment order. w_dev: ggml Q4_K [N][K/256 blocks]; w_tiled_dev:
+ * hp_q4k_tiled_bytes(N, K) bytes. interleave_half = F > 0 treats the tensor as a stack of [gate F rows | up F rows]
+ * matrices and lets gate and up rows of a feature share a tile (the routed experts' gate|up tensors). The reference keeps
+ * ggml row order and repacks nothing; its nearest analogue is the SoA repack of other formats at load (qwen35.cpp:128-134). */
+size_t hp_q4k_tiled_bytes(size_t N, int K);
+int hp_q4k_repack_tiled(const void* w_dev, void* w_tiled_dev, size_t N, int K, int interleave_half, void* stream);
 /* GQA decode attention for one sequence, as one call: per-head RMSNorm of q and k, NeoX RoPE on the first n_rot dims,
  * f16 K/V cache write, causal attention over keys 0..pos (fixed 128-key splits merged in split order), sigmoid gate.
  * qkv_dev [R][ld]: per row [n_head x (256 q | 256 gate) | n_kv x 256 k | n_kv x 256 v] (q and k are normalised and
@@ -107,13 +114,15 @@ int hp_attn_decode(float* qkv_dev, int ld, int R, int pos0, int n_head, int n_kv
  * expert's gate), softmax top-k routing (ties -> lower id) renormalised over the k winners, slot k = the shared expert
  * with weight sigmoid(logit[n_expert]); gate|up GEMV per (row, slot), silu * up + int8, down GEMV, and the weighted
  * combine in slot order. xn_dev f32 [T][E] feeds the router, xq_* (hp_quantize_x_q8 of the same rows) the experts.
- * Expert tensors are Q4_K, contiguous per tensor: gate|up [n_expert][2F][E/256 blocks], down [n_expert][E][F/256].
+ * Expert tensors are Q4_K in the library's tile-major layout (hp_q4k_repack_tiled of the ggml tensors, contiguous per
+ * tensor: gate|up [n_expert][2F][E/256 blocks] repacked with interleave_half = F, down [n_expert][E][F/256] with 0).
+ * The (row, slot) pairs are grouped by expert, so every touched expert matrix is read once per call.
  * Outputs: ids_dev / weights_dev [T][k+1] (id -1 = shared), y_dev f32 [T][E]. workspace_dev: hp_moe_workspace_bytes(...).
  * Replaces f32_gemv + moe_route + gemv_moe + moe_silu_quant + gemv_moe_down (fn.h, gemv.h:43-50; fn.hip:167-277,
  * gemv.hip:1075-1129; Qwen4Exp::moe_layer, qwen4exp.cpp:345-354). */
 size_t hp_moe_workspace_bytes(int T, int E, int F, int n_expert, int k);
-int hp_moe_layer(const float* xn_dev, const void* xq_q_dev, const void* xq_sc_dev, const float* router_dev, const void* exp_gate_up_dev, const void* exp_down_dev,
-                 const void* sh_gate_up_dev, const void* sh_down_dev, int T, int E, int F, int n_expert, int k, int* ids_dev, float* weights_dev, float* y_dev,
+int hp_moe_layer(const float* xn_dev, const void* xq_q_dev, const void* xq_sc_dev, const float* router_dev, const void* exp_gate_up_tiled_dev, const void* exp_down_tiled_dev,
+                 const void* sh_gate_up_tiled_dev, const void* sh_down_tiled_dev, int T, int E, int F, int n_expert, int k, int* ids_dev, float* weights_dev, float* y_dev,
                  void* workspace_dev, void* stream);
 
 /* ------------------------------------------------------------------ engine level (engine/src/qwen35.h, qwen4exp.h) */
@@ -201,6 +210,12 @@ int hp_gdn_state_dev(hp_engine* e, int slot, int gdn_layer, float** ptr_out, siz
  * hp_pass_weight_bytes: Q4_K bytes one trunk pass (mtp = 0) or one MTP-block pass (mtp = 1) reads, with or without the
  * LM head: the algorithmic bytes of the roofline. */
 int hp_profile_pass(hp_engine* e, int R, int what, int reps, float* ms_out);
+/* More measurement hooks: the number of (layer, expert) matrices touched by the passes since the last call (mixture of
+ * experts: the unique expert bytes of the roofline = that count x bytes per expert); the mean device time in microseconds
+ * of one expert-parallel exchange for R rows (0 on a single GPU); the kernels in the last fused round's graph. */
+int hp_moe_touched(hp_engine* e, unsigned long long* n_out);
+int hp_ep_exchange_us(hp_engine* e, int R, int reps, float* us_out);
+int hp_last_round_kernels(const hp_engine* e);
 size_t hp_pass_weight_bytes(const hp_engine* e, int mtp, int with_head);
 /* The whole MTP round on the device, for S slots in lock step: n_draft draft steps (one row per slot each), one verify
  * pass of S * (n_draft + 1) rows (<= 32), argmax, greedy acceptance per slot, commit and MTP catch-up, with no logits or

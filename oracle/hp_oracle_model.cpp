@@ -62,10 +62,10 @@ void gen_q4k(std::vector<uint8_t>& w, int N, int K, uint64_t seed, uint64_t tid)
         memcpy(&w[i * 8], &v, 8);
     }
 }
-void gen_bf16(std::vector<uint16_t>& p, size_t n, uint64_t seed, uint64_t tid, float mean, float sd) {
+void gen_bf16(std::vector<uint16_t>& p, size_t n, uint64_t seed, uint64_t tid, float mean, float sd, bool neg_abs = false) {
     p.resize(n);
 #pragma omp parallel for schedule(static)
-    for (size_t i = 0; i < n; ++i) p[i] = f32_to_bf16(mean + sd * irwin(rnd64(seed, tid, i)));
+    for (size_t i = 0; i < n; ++i) { float v = mean + sd * irwin(rnd64(seed, tid, i)); if (neg_abs) v = -fabsf(v); p[i] = f32_to_bf16(v); }
 }
 void gen_f32(std::vector<float>& p, size_t n, uint64_t seed, uint64_t tid, float mean, float sd, bool neg_abs) {
     p.resize(n); for (size_t i = 0; i < n; ++i) { float v = mean + sd * irwin(rnd64(seed, tid, i)); if (neg_abs) v = -fabsf(v); p[i] = v; }
@@ -336,7 +336,7 @@ struct OrcModel {
             L.in_proj.N = ld_in; L.in_proj.K = E; gen_q4k(L.in_proj.w, ld_in, E, c.seed, tensor_id(il, TK_IN_PROJ));
             L.out_proj.N = E; L.out_proj.K = nv * 128; gen_q4k(L.out_proj.w, E, nv * 128, c.seed, tensor_id(il, TK_OUT_PROJ));
             gen_f32(L.conv_w, (size_t)(2 * nq + nv) * 128 * 4, c.seed, tensor_id(il, TK_CONV_W), 0.f, 0.5f, false);
-            gen_bf16(L.dt_bias, nv, c.seed, tensor_id(il, TK_DT_BIAS), 0.f, 0.5f); gen_bf16(L.a_neg, nv, c.seed, tensor_id(il, TK_A_NEG), -0.8f, 0.4f);
+            gen_bf16(L.dt_bias, nv, c.seed, tensor_id(il, TK_DT_BIAS), 0.f, 0.5f); gen_bf16(L.a_neg, nv, c.seed, tensor_id(il, TK_A_NEG), 0.8f, 0.4f, true);   // never positive (test_fnkernels.cpp:33 draws -|N(0,1)|)
             gen_bf16(L.ssm_norm, 128, c.seed, tensor_id(il, TK_SSM_NORM), 1.f, 0.3f);
         }
         if (c.n_expert == 0) {

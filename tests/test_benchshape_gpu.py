@@ -55,6 +55,7 @@ def test_dense27b_widths_context_beyond_one_split(dense4):
     rows = [int(x) for x in np.random.default_rng(3).integers(0, cfg.n_vocab, size=6)]
     for e in (eng, ref):
         e.forward([(0, rows, pos)])
+    assert np.isfinite(ref.logits(6)).all()                                   # random-init weights must not blow the model up
     assert np.array_equal(bits(eng.logits(6)), bits(ref.logits(6)))           # P = 4 K parts of `down`, 248320-row LM head
     assert np.array_equal(bits(eng.h_nextn(6)), bits(ref.h_nextn(6)))
     ids, vals = eng.topk(0, 6, k=5)
@@ -132,6 +133,7 @@ def test_config5_pass_24_rows_equals_solo_and_oracle(moe4):
         eng.prefill(s, prompts[s], with_mtp=False)
     eng.forward([(s, rows[s], len(prompts[s])) for s in range(S)])            # 8 slots x 3 rows = 24 rows, NT = 3 column tiles
     batched = eng.logits(S * (n + 1)).copy(); hb_ = eng.h_nextn(S * (n + 1)).copy()
+    assert np.isfinite(batched).all()
     for s in (0, 3, 7):                                                        # solo runs of three slots
         eng.reset_slot(s)
         eng.prefill(s, prompts[s], with_mtp=False)
