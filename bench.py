@@ -45,7 +45,7 @@ GEMV_TRAFFIC_RATIO = BENCH_DATA["gemv_dram_bytes_over_algorithmic_bytes"]
 # hp_model_preset("qwen35-27b") (struct Qwen35Dims, engine/src/qwen35.h:15-26).
 PRESET_27B = dict(n_embd=5120, n_layer=64, n_ff=17408, n_vocab=248320, n_head=24, n_head_kv=4, n_rot=64, gdn_qk_heads=16, gdn_v_heads=48,
                   attn_every=4, max_ctx=8192, n_slots=1, n_expert=0, n_expert_used=0, expert_ff=0, gdn_sigmoid_gate=0, has_mtp=1,
-                  ep_rank=0, ep_world=1, rms_eps=1e-6, rope_base=1e7, seed=27)
+                  ep_rank=0, ep_world=1, synth_router_logits=0, rms_eps=1e-6, rope_base=1e7, seed=27)
 
 
 class Halton:

@@ -231,7 +231,7 @@ int hp_model_preset(const char* preset, hp_model_cfg* o) {
     } else if (!strcmp(preset, "flash-next")) {   // benchmark configuration 4 shape (head geometry from struct FnDims, qwen4exp.h:18-28)
         o->n_embd = 2048; o->n_layer = 48; o->n_ff = 0; o->n_vocab = 248320; o->n_head = 24; o->n_head_kv = 2;
         o->gdn_qk_heads = 16; o->gdn_v_heads = 48; o->max_ctx = 4096; o->n_slots = 8; o->seed = 48;
-        o->n_expert = 512; o->n_expert_used = 10; o->expert_ff = 512; o->gdn_sigmoid_gate = 1;
+        o->n_expert = 512; o->n_expert_used = 10; o->expert_ff = 512; o->gdn_sigmoid_gate = 1; o->synth_router_logits = 1;
     } else if (!strcmp(preset, "tiny")) {
         o->n_embd = 512; o->n_layer = 4; o->n_ff = 1024; o->n_vocab = 2048; o->n_head = 4; o->n_head_kv = 2;
         o->gdn_qk_heads = 2; o->gdn_v_heads = 4; o->max_ctx = 512; o->n_slots = 2; o->seed = 7;

@@ -12,14 +12,6 @@ namespace hp {
 // Counter-based: value = f(seed, tensor id, index); integer arithmetic plus exactly-rounded float operations only,
 // so a CPU regenerates identical tensors. Normal deviates are approximated by the sum of four uniform 16-bit
 // integers (Irwin-Hall, sigma = 65536 * sqrt(4/12)), which is bounded by +-3.46 sigma.
-__host__ __device__ inline uint64_t splitmix64(uint64_t x) {
-    x += 0x9E3779B97F4A7C15ull; x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull; x = (x ^ (x >> 27)) * 0x94D049BB133111EBull; return x ^ (x >> 31);
-}
-__host__ __device__ inline uint64_t rnd64(uint64_t seed, uint64_t tid, uint64_t idx) { return splitmix64(splitmix64(seed ^ (tid * 0x9E3779B97F4A7C15ull)) + idx); }
-__host__ __device__ inline float irwin(uint64_t u) {
-    const int sum = (int)(u & 0xFFFF) + (int)((u >> 16) & 0xFFFF) + (int)((u >> 32) & 0xFFFF) + (int)(u >> 48) - 131070;
-    return (float)sum * 2.6429e-5f;
-}
 __host__ __device__ inline uint16_t f32_to_f16_bits(float f) {   // same rounding as the reference's f32_to_f16 (engine/src/quant.h:150-155)
     const uint32_t x = f_bits(f); const uint32_t sign = (x >> 16) & 0x8000; const int e = (int)((x >> 23) & 0xff) - 127 + 15; uint32_t m = x & 0x7fffff;
     if (e <= 0) { if (e < -10) return (uint16_t)sign; m |= 0x800000; const uint32_t t = 14 - e; uint32_t r = m >> t; if ((m >> (t - 1)) & 1) r++; return (uint16_t)(sign | r); }
@@ -414,7 +406,9 @@ int Engine::ffn_block(const LayerW& L, int R) {
 int Engine::moe_block(const LayerW& L, int R) {
     const hp_model_cfg& c = c_; const int E = c.n_embd, F = c.expert_ff, ns = c.n_expert_used + 1;
     if (gemv_only_) return HP_OK;
-    HP_TRY(router_route(L.router, xn_, rlogits_, moe_ids_, moe_w_, route_cnt_, c.n_expert, E, c.n_expert_used, R, s_));
+    // synthetic routing (see hp_model_cfg.synth_router_logits): the key of a layer's draws; 0 = the router's own logits
+    const uint64_t rkey = c.synth_router_logits ? (splitmix64(c.seed ^ 0x726F75746572ull ^ ((uint64_t)(&L == &mtp_ ? c.n_layer : (int)(&L - layers_.data())) << 40)) | 1ull) : 0ull;
+    HP_TRY(router_route(L.router, xn_, rlogits_, moe_ids_, moe_w_, route_cnt_, c.n_expert, E, c.n_expert_used, R, s_, d_desc_ + D_TOK, d_desc_ + D_POS, rkey));
     // per-(row, slot) outputs of the experts this GPU owns, grouped by expert so that each touched expert matrix is read
     // once; pairs of experts owned elsewhere stay exact zeros, the exchange fills them in, and the combine runs in slot
     // order (the arithmetic of gemv.hip:1104-1112) on every GPU

@@ -79,6 +79,16 @@ __host__ __device__ __forceinline__ float log1pf_pos_det(float e) {
     const float c = (e - (u - 1.0f)) / u;
     return logf_ge1_det(u) + c;
 }
+// ---- counter-based seeded generation: value = f(seed, stream id, index); integer arithmetic plus exactly rounded float
+// operations only, so a CPU regenerates identical values ----
+__host__ __device__ inline uint64_t splitmix64(uint64_t x) {
+    x += 0x9E3779B97F4A7C15ull; x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull; x = (x ^ (x >> 27)) * 0x94D049BB133111EBull; return x ^ (x >> 31);
+}
+__host__ __device__ inline uint64_t rnd64(uint64_t seed, uint64_t tid, uint64_t idx) { return splitmix64(splitmix64(seed ^ (tid * 0x9E3779B97F4A7C15ull)) + idx); }
+__host__ __device__ inline float irwin(uint64_t u) {
+    const int sum = (int)(u & 0xFFFF) + (int)((u >> 16) & 0xFFFF) + (int)((u >> 32) & 0xFFFF) + (int)(u >> 48) - 131070;
+    return (float)sum * 2.6429e-5f;
+}
 __host__ __device__ __forceinline__ float sigmoid_det(float x) { return 1.0f / (1.0f + expf_det(-x)); }
 __host__ __device__ __forceinline__ float silu_det(float x) { return x / (1.0f + expf_det(-x)); }
 __host__ __device__ __forceinline__ float softplus_det(float x) { return x > 20.f ? x : log1pf_pos_det(expf_det(x)); }

@@ -300,7 +300,7 @@ extern "C" void orc_fma_rows(float* acc, const float* v, float w, int n) { for (
 // ---------------------------------------------------------------- engine (engine/src/qwen35.cpp restated on the CPU)
 struct OrcCfg {   // mirrors hp_model_cfg field for field
     int n_embd, n_layer, n_ff, n_vocab, n_head, n_head_kv, n_rot, gdn_qk_heads, gdn_v_heads, attn_every, max_ctx, n_slots;
-    int n_expert, n_expert_used, expert_ff, gdn_sigmoid_gate, has_mtp, ep_rank, ep_world; float rms_eps, rope_base; unsigned long long seed;
+    int n_expert, n_expert_used, expert_ff, gdn_sigmoid_gate, has_mtp, ep_rank, ep_world, synth_router_logits; float rms_eps, rope_base; unsigned long long seed;
 };
 namespace {
 struct OLin { std::vector<uint8_t> w; int N = 0, K = 0; };
@@ -399,10 +399,15 @@ struct OrcModel {
     }
     // qwen35.cpp:278-287
     // Qwen4Exp::moe_layer (qwen4exp.cpp:345-354); xn = the normalised f32 rows the router reads
-    void moe_block(const OLayer& L, XQ& xq, const std::vector<float>& xn, int R, std::vector<float>& y) {
+    void moe_block(const OLayer& L, XQ& xq, const std::vector<float>& xn, int R, std::vector<float>& y, const int* tok, const int* pos, int layer_index) {
         const int E = c.n_embd, F = c.expert_ff, ns = c.n_expert_used + 1, nb = E / 256, nsb = E / 32;
         std::vector<float> lg((size_t)R * (c.n_expert + 1)), w((size_t)R * ns); std::vector<int> ids((size_t)R * ns);
         orc_router_gemv(L.router.data(), xn.data(), lg.data(), c.n_expert + 1, E, R);
+        if (c.synth_router_logits) {   // benchmark input control: seeded N(0, 1) expert logits keyed by (layer, token, position, expert)
+            const uint64_t key = splitmix64(c.seed ^ 0x726F75746572ull ^ ((uint64_t)layer_index << 40)) | 1ull;
+            for (int t = 0; t < R; ++t) for (int e = 0; e < c.n_expert; ++e)
+                lg[(size_t)t * (c.n_expert + 1) + e] = irwin(rnd64(key, ((uint64_t)(uint32_t)tok[t] << 32) | (uint32_t)pos[t], (uint64_t)e));
+        }
         orc_moe_route(lg.data(), ids.data(), w.data(), R, c.n_expert, c.n_expert_used);
         const size_t eb_up = (size_t)2 * F * nb * 144, eb_dn = (size_t)E * (F / 256) * 144;
         y.assign((size_t)R * E, 0.f);
@@ -464,7 +469,7 @@ struct OrcModel {
             } else {
                 attn_block(L, xq, kc, vc, (size_t)ai * kvl, pos.data(), slot.data(), R, y); ++ai;
             }
-            if (c.n_expert) { std::vector<float> xn((size_t)R * E); norm_in(x, y.data(), L.post_norm, xn.data(), xq, R); moe_block(L, xq, xn, R, y); }
+            if (c.n_expert) { std::vector<float> xn((size_t)R * E); norm_in(x, y.data(), L.post_norm, xn.data(), xq, R); moe_block(L, xq, xn, R, y, tok.data(), pos.data(), il); }
             else { norm_in(x, y.data(), L.post_norm, nullptr, xq, R); ffn_block(L, xq, R, y); }
             have_y = true;
         }
@@ -499,7 +504,7 @@ struct OrcModel {
         std::vector<int> pos(T), sl(T, slot); for (int t = 0; t < T; ++t) pos[t] = pos0 + t;
         norm_in(x, nullptr, mtp.attn_norm, nullptr, xq, T);
         attn_block(mtp, xq, mkc, mvc, 0, pos.data(), sl.data(), T, y);
-        if (c.n_expert) { std::vector<float> xn((size_t)T * E); norm_in(x, y.data(), mtp.post_norm, xn.data(), xq, T); moe_block(mtp, xq, xn, T, y); }
+        if (c.n_expert) { std::vector<float> xn((size_t)T * E); norm_in(x, y.data(), mtp.post_norm, xn.data(), xq, T); moe_block(mtp, xq, xn, T, y, tok, pos.data(), c.n_layer); }
         else { norm_in(x, y.data(), mtp.post_norm, nullptr, xq, T); ffn_block(mtp, xq, T, y); }
         norm_in(x, y.data(), head_norm, mh.data(), xq, T);
         gemv(lm_head, xq, mlogits.data(), T, c.n_vocab);

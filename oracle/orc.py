@@ -102,7 +102,7 @@ def accept(ids, drafts):
 # ---------------------------------------------------------------- engine oracle (hp_oracle_model.cpp)
 class OrcCfg(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int) for n in ("n_embd", "n_layer", "n_ff", "n_vocab", "n_head", "n_head_kv", "n_rot", "gdn_qk_heads", "gdn_v_heads",
-                                             "attn_every", "max_ctx", "n_slots", "n_expert", "n_expert_used", "expert_ff", "gdn_sigmoid_gate", "has_mtp", "ep_rank", "ep_world")] + \
+                                             "attn_every", "max_ctx", "n_slots", "n_expert", "n_expert_used", "expert_ff", "gdn_sigmoid_gate", "has_mtp", "ep_rank", "ep_world", "synth_router_logits")] + \
                [("rms_eps", ctypes.c_float), ("rope_base", ctypes.c_float), ("seed", ctypes.c_ulonglong)]
 
 
