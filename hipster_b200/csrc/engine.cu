@@ -802,7 +802,10 @@ int Engine::spec_round(const int* slots, int S, int n, const int* subst, int* ou
         h_spec_[SI_SLOTS + j] = j < S ? slots[j] : 0;
         for (int i = 0; i < 8; ++i) h_spec_[SI_SUBST + 8 * j + i] = (subst && j < S && i < n) ? subst[j * n + i] : -1;
     }
-    static const bool no_graph = getenv("HIPSTER_B200_NO_GRAPH") != nullptr;
+    // A round that carries collectives is enqueued kernel by kernel: the host stays able to watch the communicator
+    // (sync_stream) and no collective is baked into a graph that outlives a failed peer.
+    static const bool env_no_graph = getenv("HIPSTER_B200_NO_GRAPH") != nullptr;
+    const bool no_graph = env_no_graph || c_.ep_world > 1;
     const int key = (S - 1) * 8 + n;
     HP_CUDA(cudaEventRecord(ev0_, s_));
     if (no_graph) HP_TRY(enqueue_round(S, n));

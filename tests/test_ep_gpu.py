@@ -29,6 +29,17 @@ def _run(eng, cfg):
 
 
 def _worker(rank, world, port, out):
+    import faulthandler
+    faulthandler.dump_traceback_later(240, exit=True)      # a rank that waits for a lost peer must not outlive the test
+    try:
+        _worker_body(rank, world, port, out)
+    except Exception as e:                                  # report instead of leaving the peer to wait
+        out[rank] = ("error", repr(e))
+        os._exit(1)
+    os._exit(0)                                             # skip interpreter teardown (a process group without its peer can block there)
+
+
+def _worker_body(rank, world, port, out):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
@@ -46,7 +57,7 @@ def _worker(rank, world, port, out):
     want_outs, want_logits = _run(solo, solo_cfg)
     solo.close()
     out[rank] = (outs == want_outs, bool(np.array_equal(logits.view(np.uint32), want_logits.view(np.uint32))))
-    dist.barrier(); dist.destroy_process_group()
+    dist.barrier()
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
@@ -54,10 +65,15 @@ def test_expert_parallel_two_gpus_bit_exact_vs_single_gpu():
     ctx = mp.get_context("spawn")
     mgr = ctx.Manager(); out = mgr.dict()
     port = 32500 + (os.getpid() % 2000)
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, out)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, out), daemon=True) for r in range(2)]
     for p in procs:
         p.start()
     for p in procs:
-        p.join(timeout=600)
-        assert p.exitcode == 0
-    assert out[0] == (True, True) and out[1] == (True, True)
+        p.join(timeout=300)
+    alive = [p.is_alive() for p in procs]
+    for p in procs:
+        if p.is_alive():
+            p.kill()
+    assert not any(alive), f"a rank did not finish: {dict(out)}"
+    assert all(p.exitcode == 0 for p in procs), dict(out)
+    assert out[0] == (True, True) and out[1] == (True, True), dict(out)
