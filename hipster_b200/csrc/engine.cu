@@ -408,7 +408,7 @@ int Engine::moe_block(const LayerW& L, int R) {
     if (gemv_only_) return HP_OK;
     // synthetic routing (see hp_model_cfg.synth_router_logits): the key of a layer's draws; 0 = the router's own logits
     const uint64_t rkey = c.synth_router_logits ? (splitmix64(c.seed ^ 0x726F75746572ull ^ ((uint64_t)(&L == &mtp_ ? c.n_layer : (int)(&L - layers_.data())) << 40)) | 1ull) : 0ull;
-    HP_TRY(router_route(L.router, xn_, rlogits_, moe_ids_, moe_w_, route_cnt_, c.n_expert, E, c.n_expert_used, R, s_, d_desc_ + D_TOK, d_desc_ + D_POS, rkey));
+    HP_TRY(router_route(L.router, xn_, rlogits_, moe_ids_, moe_w_, route_cnt_, c.n_expert, E, c.n_expert_used, R, s_, d_desc_ + D_TOK, d_desc_ + D_POS, d_desc_ + D_SLOT, rkey));
     // per-(row, slot) outputs of the experts this GPU owns, grouped by expert so that each touched expert matrix is read
     // once; pairs of experts owned elsewhere stay exact zeros, the exchange fills them in, and the combine runs in slot
     // order (the arithmetic of gemv.hip:1104-1112) on every GPU

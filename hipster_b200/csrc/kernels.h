@@ -107,7 +107,7 @@ int attn_decode_seq(float* qkv, int ld, int R, int pos0, int n_head, int n_kv, i
 // ---- moe.cu ----
 // router (reference f32_gemv, fn.hip:252-277) and routing (k_moe_route, fn.hip:167-205) in one launch; counters: T zero-initialised ints (left zero)
 int router_route(const float* W, const float* x, float* logits, int* ids, float* w, int* counters, int E, int K, int k, int T, cudaStream_t s,
-                 const int* row_tok = nullptr, const int* row_pos = nullptr, unsigned long long synth_key = 0);   // synth_key != 0: seeded N(0,1) expert logits per (token, position)
+                 const int* row_tok = nullptr, const int* row_pos = nullptr, const int* row_slot = nullptr, unsigned long long synth_key = 0);   // synth_key != 0: seeded N(0,1) expert logits per (slot, token, position)
 // Routed experts grouped by expert (see moe.cu). Expert tensors tile-major: gate|up repacked with interleave_half = F.
 constexpr int MOE_MAX_PAIRS = 32 * 16;
 struct MoeGroupParams {

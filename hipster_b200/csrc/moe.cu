@@ -21,12 +21,12 @@ __device__ __forceinline__ void better(float& bv, int& bi, float v, int i) { if 
 // Both in one launch: the CTA that finishes a row's logits last (ticket counter per row) routes that row. The softmax
 // sums follow a fixed order: xor tree inside each 32-element group, the 32 group results combined in group order (warp w
 // of the 256-thread CTA does groups w, w+8, w+16, w+24).
-// synth_key != 0: the E expert logits fed to the softmax are seeded N(0, 1) draws keyed by (layer key, token, position,
-// expert) instead of the GEMV's (benchmark input control: with random-init weights every row's hidden state is nearly the
+// synth_key != 0: the E expert logits fed to the softmax are seeded N(0, 1) draws keyed by (layer key, slot, token,
+// position, expert) instead of the GEMV's (benchmark input control: with random-init weights every row's hidden state is nearly the
 // same vector, so a linear router would send all rows to the same experts); the shared expert's gate keeps its logit.
 __global__ void __launch_bounds__(256) k_router_route(const float* __restrict__ W, const float* __restrict__ x, float* __restrict__ y, int N, int K,
                                                      int* __restrict__ ids, float* __restrict__ w, int E, int k, int* __restrict__ cnt,
-                                                     const int* __restrict__ row_tok, const int* __restrict__ row_pos, unsigned long long synth_key) {
+                                                     const int* __restrict__ row_tok, const int* __restrict__ row_pos, const int* __restrict__ row_slot, unsigned long long synth_key) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float sh[32]; __shared__ float selp[16]; __shared__ int seli[16]; __shared__ float sp[1024]; __shared__ int s_last;
@@ -55,7 +55,7 @@ __global__ void __launch_bounds__(256) k_router_route(const float* __restrict__ 
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         const int i = 32 * (warp + 8 * j) + lane;
-        v[j] = i < E ? (synth_key ? irwin(rnd64(synth_key, ((uint64_t)(uint32_t)row_tok[t] << 32) | (uint32_t)row_pos[t], (uint64_t)i)) : __ldcg(lg + i)) : -INFINITY;
+        v[j] = i < E ? (synth_key ? irwin(rnd64(synth_key + (uint64_t)row_slot[t], ((uint64_t)(uint32_t)row_tok[t] << 32) | (uint32_t)row_pos[t], (uint64_t)i)) : __ldcg(lg + i)) : -INFINITY;
         float m = v[j];
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
@@ -292,11 +292,11 @@ __global__ void __launch_bounds__(256) k_moe_combine(const float* __restrict__ v
 }  // namespace
 
 int router_route(const float* W, const float* x, float* logits, int* ids, float* w, int* counters, int E, int K, int k, int T, cudaStream_t s,
-                 const int* row_tok, const int* row_pos, unsigned long long synth_key) {
-    HP_REQUIRE(synth_key == 0 || (row_tok && row_pos), "router_route: synthetic logits need the rows' tokens and positions");
+                 const int* row_tok, const int* row_pos, const int* row_slot, unsigned long long synth_key) {
+    HP_REQUIRE(synth_key == 0 || (row_tok && row_pos && row_slot), "router_route: synthetic logits need the rows' tokens, positions and slots");
     HP_REQUIRE(E >= 1 && E <= 1024 && k >= 1 && k <= 15 && k <= E && K > 0 && K % 128 == 0 && T >= 1 && T <= 32 && counters, "router_route: bad shape E=%d K=%d k=%d T=%d", E, K, k, T);
     const int N = E + 1;
-    HP_CUDA(launch_pdl<8>(k_router_route, dim3((N * 32 + 255) / 256, T), dim3(256), 0, s, W, x, logits, N, K, ids, w, E, k, counters, row_tok, row_pos, synth_key));
+    HP_CUDA(launch_pdl<8>(k_router_route, dim3((N * 32 + 255) / 256, T), dim3(256), 0, s, W, x, logits, N, K, ids, w, E, k, counters, row_tok, row_pos, row_slot, synth_key));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 size_t moe_seg_bytes() { return (size_t)MOE_MAX_PAIRS * sizeof(MoeSeg); }

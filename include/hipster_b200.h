@@ -141,7 +141,7 @@ typedef struct hp_model_cfg {
     int has_mtp;
     int ep_rank, ep_world;       /* expert parallelism: this GPU holds routed experts [ep_rank*n_expert/ep_world, ...); 0, 1 = all */
     int synth_router_logits;     /* benchmark input control ("router logits N(0,1)"): 1 = the expert logits that enter the routing
-                                    softmax are seeded N(0,1) draws keyed by (layer, token, position, expert), so that rows route to
+                                    softmax are seeded N(0,1) draws keyed by (layer, slot, token, position, expert), so that rows route to
                                     different experts as they do in a trained model; the router GEMV still runs and its last row still
                                     gates the shared expert. 0 = the router's own logits (the reference arithmetic, fn.hip:252-266) */
     float rms_eps, rope_base;

@@ -399,14 +399,14 @@ struct OrcModel {
     }
     // qwen35.cpp:278-287
     // Qwen4Exp::moe_layer (qwen4exp.cpp:345-354); xn = the normalised f32 rows the router reads
-    void moe_block(const OLayer& L, XQ& xq, const std::vector<float>& xn, int R, std::vector<float>& y, const int* tok, const int* pos, int layer_index) {
+    void moe_block(const OLayer& L, XQ& xq, const std::vector<float>& xn, int R, std::vector<float>& y, const int* tok, const int* pos, const int* slot, int layer_index) {
         const int E = c.n_embd, F = c.expert_ff, ns = c.n_expert_used + 1, nb = E / 256, nsb = E / 32;
         std::vector<float> lg((size_t)R * (c.n_expert + 1)), w((size_t)R * ns); std::vector<int> ids((size_t)R * ns);
         orc_router_gemv(L.router.data(), xn.data(), lg.data(), c.n_expert + 1, E, R);
-        if (c.synth_router_logits) {   // benchmark input control: seeded N(0, 1) expert logits keyed by (layer, token, position, expert)
+        if (c.synth_router_logits) {   // benchmark input control: seeded N(0, 1) expert logits keyed by (layer, slot, token, position, expert)
             const uint64_t key = splitmix64(c.seed ^ 0x726F75746572ull ^ ((uint64_t)layer_index << 40)) | 1ull;
             for (int t = 0; t < R; ++t) for (int e = 0; e < c.n_expert; ++e)
-                lg[(size_t)t * (c.n_expert + 1) + e] = irwin(rnd64(key, ((uint64_t)(uint32_t)tok[t] << 32) | (uint32_t)pos[t], (uint64_t)e));
+                lg[(size_t)t * (c.n_expert + 1) + e] = irwin(rnd64(key + (uint64_t)slot[t], ((uint64_t)(uint32_t)tok[t] << 32) | (uint32_t)pos[t], (uint64_t)e));
         }
         orc_moe_route(lg.data(), ids.data(), w.data(), R, c.n_expert, c.n_expert_used);
         const size_t eb_up = (size_t)2 * F * nb * 144, eb_dn = (size_t)E * (F / 256) * 144;
@@ -469,7 +469,7 @@ struct OrcModel {
             } else {
                 attn_block(L, xq, kc, vc, (size_t)ai * kvl, pos.data(), slot.data(), R, y); ++ai;
             }
-            if (c.n_expert) { std::vector<float> xn((size_t)R * E); norm_in(x, y.data(), L.post_norm, xn.data(), xq, R); moe_block(L, xq, xn, R, y, tok.data(), pos.data(), il); }
+            if (c.n_expert) { std::vector<float> xn((size_t)R * E); norm_in(x, y.data(), L.post_norm, xn.data(), xq, R); moe_block(L, xq, xn, R, y, tok.data(), pos.data(), slot.data(), il); }
             else { norm_in(x, y.data(), L.post_norm, nullptr, xq, R); ffn_block(L, xq, R, y); }
             have_y = true;
         }
@@ -504,7 +504,7 @@ struct OrcModel {
         std::vector<int> pos(T), sl(T, slot); for (int t = 0; t < T; ++t) pos[t] = pos0 + t;
         norm_in(x, nullptr, mtp.attn_norm, nullptr, xq, T);
         attn_block(mtp, xq, mkc, mvc, 0, pos.data(), sl.data(), T, y);
-        if (c.n_expert) { std::vector<float> xn((size_t)T * E); norm_in(x, y.data(), mtp.post_norm, xn.data(), xq, T); moe_block(mtp, xq, xn, T, y, tok, pos.data(), c.n_layer); }
+        if (c.n_expert) { std::vector<float> xn((size_t)T * E); norm_in(x, y.data(), mtp.post_norm, xn.data(), xq, T); moe_block(mtp, xq, xn, T, y, tok, pos.data(), sl.data(), c.n_layer); }
         else { norm_in(x, y.data(), mtp.post_norm, nullptr, xq, T); ffn_block(mtp, xq, T, y); }
         norm_in(x, y.data(), head_norm, mh.data(), xq, T);
         gemv(lm_head, xq, mlogits.data(), T, c.n_vocab);
