@@ -206,11 +206,13 @@ int hp_moe_layer(const float* xn_dev, const void* xq_q_dev, const void* xq_sc_de
     float* logits = (float*)(ws + w.logits); int* cnt = (int*)(ws + w.cnt); float* v = (float*)(ws + w.v);
     HP_CUDA(cudaMemsetAsync(cnt, 0, (size_t)T * 4, s));
     HP_CUDA(cudaMemsetAsync(ws + w.q2, 0, w.total - w.q2, s));
-    { const int rc = hp::router_route(router_dev, xn_dev, logits, ids_dev, weights_dev, cnt, n_expert, E, k, T, s); if (rc) return rc; }
+    hp::MoeRouteParams rp; rp.W = router_dev; rp.x = xn_dev; rp.logits = logits; rp.E = n_expert; rp.K = E; rp.k = k; rp.T = T; rp.ids = ids_dev; rp.w = weights_dev; rp.ticket = cnt;
+    rp.e_lo = 0; rp.e_hi = n_expert; rp.own_shared = 1; rp.segs = ws + w.segs; rp.ctl = (int*)(ws + w.ctl);
+    { const int rc = hp::moe_route_group(rp, s); if (rc) return rc; }
     hp::MoeGroupParams g; g.w_gate_up = exp_gate_up_tiled_dev; g.w_down = exp_down_tiled_dev; g.sh_gate_up = sh_gate_up_tiled_dev; g.sh_down = sh_down_tiled_dev;
     g.E = E; g.F = F; g.n_expert = n_expert; g.nslot = ns; g.T = T; g.e_lo = 0; g.e_hi = n_expert; g.own_shared = 1;
-    g.ids = ids_dev; g.xq = hp::XQ8F{(void*)xq_q_dev, (void*)xq_sc_dev}; g.xq2 = hp::XQ8F{ws + w.q2, ws + w.sc2}; g.v = v;
-    g.segs = ws + w.segs; g.ctl = (int*)(ws + w.ctl); g.touched = nullptr; g.err = hp::device_err_flag();
+    g.xq = hp::XQ8F{(void*)xq_q_dev, (void*)xq_sc_dev}; g.xq2 = hp::XQ8F{ws + w.q2, ws + w.sc2}; g.v = v;
+    g.segs = ws + w.segs; g.ctl = (int*)(ws + w.ctl); g.err = hp::device_err_flag();
     { const int rc = hp::moe_experts_grouped(g, s); if (rc) return rc; }
     return hp::moe_combine(v, weights_dev, y_dev, T, ns, E, s);
     HP_GUARD_END

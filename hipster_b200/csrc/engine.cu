@@ -148,7 +148,7 @@ int Engine::alloc(void** p, size_t bytes) {
     if (e != cudaSuccess) { set_error("out of device memory allocating %zu bytes (%s)", bytes, cudaGetErrorString(e)); return HP_ENOMEM; }
     allocs_.push_back(*p); return HP_OK;
 }
-int Engine::gen_lin(Lin& l, int N, int K, uint64_t tid) {
+int Engine::gen_lin(Lin& l, int N, int K, uint64_t tid, bool gate_up) {
     l.N = N; l.K = K; l.bytes = (size_t)N * (K / 256) * 144; l.P = gemv_parts(N, K);
     HP_REQUIRE(K % 256 == 0 && l.P > 0, "tensor %d x %d is not a valid Q4_K GEMV shape", N, K);
     if (int rc = alloc((void**)&l.w, l.bytes)) return rc;
@@ -157,8 +157,11 @@ int Engine::gen_lin(Lin& l, int N, int K, uint64_t tid) {
     HP_CUDA(cudaGetLastError());
     weight_bytes_ += l.bytes;
     if (tiled_) {   // the GEMV streams the tile-major copy; the row-major original is kept only for small (test) models
+        // gate|up of a dense FFN: gate and up rows of a feature share a tile, so that the GEMV's epilogue can form
+        // silu(gate) * up in registers (needs an unsplit K and whole tiles)
+        l.ileave = gate_up && l.P == 1 && N % 32 == 0;
         HP_TRY(alloc((void**)&l.wt, gemv_tiled_bytes(N, K)));
-        HP_TRY(gemv_repack_tiled(l.w, l.wt, N, K, s_));
+        HP_TRY(gemv_repack_tiled(l.w, l.wt, N, K, s_, l.ileave ? N / 2 : 0));
         if (!keep_rowmajor_) {
             HP_CUDA(cudaStreamSynchronize(s_));
             for (size_t i = 0; i < allocs_.size(); ++i) if (allocs_[i] == l.w) { allocs_.erase(allocs_.begin() + i); break; }
@@ -241,7 +244,7 @@ int Engine::init() {
             HP_TRY(gen_bf16(&L.ssm_norm, 128, tensor_id(il, TK_SSM_NORM), 1.f, 0.3f));
         }
         if (c.n_expert == 0) {
-            HP_TRY(gen_lin(L.gate_up, 2 * c.n_ff, E, tensor_id(il, TK_GATE_UP)));
+            HP_TRY(gen_lin(L.gate_up, 2 * c.n_ff, E, tensor_id(il, TK_GATE_UP), true));
             HP_TRY(gen_lin(L.down, E, c.n_ff, tensor_id(il, TK_DOWN)));
         } else {   // routed experts (contiguous per tensor, qwen4exp weights layout [512*N][K]) + one shared expert + f32 router
             const int F = c.expert_ff;
@@ -302,6 +305,7 @@ int Engine::init() {
     HP_TRY(alloc((void**)&yparts_, (size_t)4 * MAXR * std::max<size_t>(bigw, E) * 4));
     HP_TRY(alloc((void**)&logits_, (size_t)MAXR * c.n_vocab * 4)); HP_TRY(alloc((void**)&mlogits_, (size_t)MAXR * c.n_vocab * 4));
     HP_TRY(alloc((void**)&h_, (size_t)MAXR * E * 4)); HP_TRY(alloc((void**)&mh_, (size_t)MAXR * E * 4));
+    HP_TRY(alloc((void**)&act_, (size_t)MAXR * std::max(F, 64) * 4)); HP_CUDA(cudaMemsetAsync(act_, 0, (size_t)MAXR * std::max(F, 64) * 4, s_));
     HP_CUDA(cudaMemsetAsync(h_, 0, (size_t)MAXR * E * 4, s_)); HP_CUDA(cudaMemsetAsync(mh_, 0, (size_t)MAXR * E * 4, s_));
     HP_TRY(alloc(&xq_.q, xq_q_bytes(MAXR, (int)kmax))); HP_TRY(alloc(&xq_.sc, xq_sc_floats(MAXR, (int)kmax) * 4));
     HP_CUDA(cudaMemsetAsync(xq_.q, 0, xq_q_bytes(MAXR, (int)kmax), s_)); HP_CUDA(cudaMemsetAsync(xq_.sc, 0, xq_sc_floats(MAXR, (int)kmax) * 4, s_));
@@ -397,6 +401,13 @@ int Engine::attn_block(const LayerW& L, uint16_t* kc, uint16_t* vc, size_t kv_st
 int Engine::ffn_block(const LayerW& L, int R) {
     if (c_.n_expert) return moe_block(L, R);
     const int F = c_.n_ff;
+    if (L.gate_up.ileave && L.down.wt) {
+        // SwiGLU without a launch of its own: gate|up's epilogue leaves silu(gate) * up as f32 rows, and the down projection
+        // quantises the part of them each CTA needs while it stages its activations
+        if (!(prof_skip_ & 16)) HP_TRY(gemv_q4k_q8_parts(L.gate_up.wt, xq_, act_, 2 * F, c_.n_embd, R, F, 0, err_, s_, pdl_, true, 1));
+        if (prof_skip_ & 32) return HP_OK;
+        return gemv_q4k_q8_parts(L.down.wt, xq_, yparts_, L.down.N, F, R, L.down.N, (size_t)R * L.down.N, err_, s_, pdl_, true, 2, act_, F);
+    }
     HP_TRY(lin(L.gate_up, big_, 2 * F, R));
     if (!gemv_only_ && !(prof_skip_ & 8)) HP_TRY(silu_mul_quant(big_, 2 * F, F, xq_, R, s_));
     return lin_parts(L.down, R);
@@ -408,14 +419,17 @@ int Engine::moe_block(const LayerW& L, int R) {
     if (gemv_only_) return HP_OK;
     // synthetic routing (see hp_model_cfg.synth_router_logits): the key of a layer's draws; 0 = the router's own logits
     const uint64_t rkey = c.synth_router_logits ? (splitmix64(c.seed ^ 0x726F75746572ull ^ ((uint64_t)(&L == &mtp_ ? c.n_layer : (int)(&L - layers_.data())) << 40)) | 1ull) : 0ull;
-    HP_TRY(router_route(L.router, xn_, rlogits_, moe_ids_, moe_w_, route_cnt_, c.n_expert, E, c.n_expert_used, R, s_, d_desc_ + D_TOK, d_desc_ + D_POS, d_desc_ + D_SLOT, rkey));
+    MoeRouteParams rp; rp.W = L.router; rp.x = xn_; rp.logits = rlogits_; rp.E = c.n_expert; rp.K = E; rp.k = c.n_expert_used; rp.T = R;
+    rp.ids = moe_ids_; rp.w = moe_w_; rp.ticket = route_cnt_; rp.row_tok = d_desc_ + D_TOK; rp.row_pos = d_desc_ + D_POS; rp.row_slot = d_desc_ + D_SLOT; rp.synth_key = rkey;
+    rp.e_lo = e_lo_; rp.e_hi = e_hi_; rp.own_shared = own_shared_; rp.segs = moe_segs_; rp.ctl = moe_ctl_; rp.touched = moe_touched_;
+    HP_TRY(moe_route_group(rp, s_));
     // per-(row, slot) outputs of the experts this GPU owns, grouped by expert so that each touched expert matrix is read
     // once; pairs of experts owned elsewhere stay exact zeros, the exchange fills them in, and the combine runs in slot
     // order (the arithmetic of gemv.hip:1104-1112) on every GPU
     if (c.ep_world > 1) { HP_TRY(ep_ready()); HP_CUDA(cudaMemsetAsync(moe_v_, 0, (size_t)R * ns * E * 4, s_)); }
     MoeGroupParams g; g.w_gate_up = L.exp_gate_up.wt; g.w_down = L.exp_down.wt; g.sh_gate_up = L.sh_gate_up.wt; g.sh_down = L.sh_down.wt;
     g.E = E; g.F = F; g.n_expert = c.n_expert; g.nslot = ns; g.T = R; g.e_lo = e_lo_; g.e_hi = e_hi_; g.own_shared = own_shared_;
-    g.ids = moe_ids_; g.xq = xq_; g.xq2 = xq2_; g.v = moe_v_; g.segs = moe_segs_; g.ctl = moe_ctl_; g.touched = moe_touched_; g.err = err_;
+    g.xq = xq_; g.xq2 = xq2_; g.v = moe_v_; g.segs = moe_segs_; g.ctl = moe_ctl_; g.err = err_;
     HP_TRY(moe_experts_grouped(g, s_));
     if (c.ep_world > 1) HP_TRY(ep_exchange(moe_v_, (size_t)R * ns * E));
     return HP_OK;   // combined in slot order by the norm that follows (norm_in)

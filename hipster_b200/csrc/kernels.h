@@ -50,7 +50,10 @@ struct GemvWorkspace { float* part; size_t part_bytes; int* err; };
 int gemv_parts(int N, int K);
 // raw form: part p of the K split writes plane yparts + p * part_stride ([R][ldy] each); the caller adds the planes in order
 // tiled = true: W is in the tile-major layout produced by gemv_repack_tiled (gemv_tiled_bytes(N, K) bytes)
-int gemv_q4k_q8_parts(const void* W, const XQ8F& x, float* yparts, int N, int K, int R, int ldy, size_t part_stride, int* err, cudaStream_t s, bool pdl, bool tiled);
+// mode 0: plain. mode 1 (tile-major gate|up repacked with interleave_half = N / 2, P = 1): the output is silu(gate) * up,
+// f32 [R][ldy >= N / 2]. mode 2: the activations are f32 rows xf32 [R][ldx] (x is ignored) and are quantised by the kernel.
+int gemv_q4k_q8_parts(const void* W, const XQ8F& x, float* yparts, int N, int K, int R, int ldy, size_t part_stride, int* err, cudaStream_t s, bool pdl, bool tiled,
+                      int mode = 0, const float* xf32 = nullptr, int ldx = 0);
 size_t gemv_tiled_bytes(size_t N, int K);
 // interleave_half = F > 0: src is a stack of [gate F rows | up F rows] matrices; gate and up rows of a feature share a tile
 int gemv_repack_tiled(const void* src, void* dst, size_t N, int K, cudaStream_t s, int interleave_half = 0);
@@ -105,19 +108,26 @@ int attn_decode_seq(float* qkv, int ld, int R, int pos0, int n_head, int n_kv, i
                     float* out, XQ8F xq, float eps, void* workspace, cudaStream_t s);
 
 // ---- moe.cu ----
-// router (reference f32_gemv, fn.hip:252-277) and routing (k_moe_route, fn.hip:167-205) in one launch; counters: T zero-initialised ints (left zero)
-int router_route(const float* W, const float* x, float* logits, int* ids, float* w, int* counters, int E, int K, int k, int T, cudaStream_t s,
-                 const int* row_tok = nullptr, const int* row_pos = nullptr, const int* row_slot = nullptr, unsigned long long synth_key = 0);   // synth_key != 0: seeded N(0,1) expert logits per (slot, token, position)
-// Routed experts grouped by expert (see moe.cu). Expert tensors tile-major: gate|up repacked with interleave_half = F.
+// router (reference f32_gemv, fn.hip:252-277), routing (k_moe_route, fn.hip:167-205) and the grouping of the (row, slot)
+// pairs by expert, in one launch
 constexpr int MOE_MAX_PAIRS = 32 * 16;
+struct MoeRouteParams {
+    const float* W; const float* x; float* logits; int E, K, k, T;   // router [E + 1][K] f32, rows x [T][K], logits [T][E + 1]
+    int* ids; float* w;                                               // [T][k + 1]: expert ids (-1 = shared) and combine weights
+    int* ticket;                                                      // one zero-initialised int (left zero)
+    const int* row_tok = nullptr; const int* row_pos = nullptr; const int* row_slot = nullptr; unsigned long long synth_key = 0;   // synth_key != 0: seeded N(0,1) expert logits per (slot, token, position)
+    int e_lo = 0, e_hi = 0, own_shared = 1;                           // experts this GPU owns
+    void* segs = nullptr; int* ctl = nullptr; unsigned long long* touched = nullptr;   // grouping outputs (segs == nullptr: no grouping)
+};
+int moe_route_group(const MoeRouteParams& p, cudaStream_t s);
+// Routed experts grouped by expert (see moe.cu). Expert tensors tile-major: gate|up repacked with interleave_half = F.
 struct MoeGroupParams {
     const void* w_gate_up; const void* w_down; const void* sh_gate_up; const void* sh_down;   // this GPU's experts [e_lo, e_hi) and the shared expert
     int E, F, n_expert, nslot, T;                       // hidden, expert FFN, routed experts, slots per row (k + 1), rows
     int e_lo, e_hi, own_shared;
-    const int* ids;                                     // [T][nslot], -1 = shared
     XQ8F xq, xq2;                                       // quantised rows [T] (K = E) in; quantised silu(gate)*up per pair [T * nslot] (K = F) scratch
     float* v;                                           // per-pair outputs [T * nslot][E] (pairs of experts owned elsewhere are not written)
-    void* segs; int* ctl; unsigned long long* touched;  // device scratch: MOE_MAX_PAIRS segments of 64 bytes, 4 ints, optional counter of touched experts
+    void* segs; int* ctl;                               // filled by moe_route_group: MOE_MAX_PAIRS segments of 64 bytes, 4 control ints
     int* err;
 };
 size_t moe_seg_bytes();

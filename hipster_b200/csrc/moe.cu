@@ -13,92 +13,147 @@
 namespace hp {
 namespace {
 
-// ---- router (exact f32: one warp per weight row; lane l takes k = 4l + 128 i as float4, four fmaf per step in element
-// order, then the xor-shuffle tree 16..1) and routing (softmax over the first E logits, top-k by (value desc, index asc),
-// weights renormalised by the sum of the selected probabilities taken in rank order; slot k = shared expert, id -1, with
-// weight sigmoid(logit[E])). Reference: k_f32_gemv (fn.hip:252-266), k_moe_route (fn.hip:167-205). ----
-__device__ __forceinline__ void better(float& bv, int& bi, float v, int i) { if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; } }
-// Both in one launch: the CTA that finishes a row's logits last (ticket counter per row) routes that row. The softmax
-// sums follow a fixed order: xor tree inside each 32-element group, the 32 group results combined in group order (warp w
-// of the 256-thread CTA does groups w, w+8, w+16, w+24).
+// ---- router + routing + grouping in ONE launch ------------------------------------------------------------------------
+// Phase 1, router (exact f32; reference k_f32_gemv, fn.hip:252-266): one warp per weight row n, for all T rows of the
+// pass (the weight row is read once); lane l takes k = 4l + 128 i as float4, four fmaf per step in element order, then
+// the xor-shuffle tree 16..1. Phase 2, in the CTA that finishes last (ticket counter), routing (k_moe_route,
+// fn.hip:167-205), one warp per row: softmax over the first E logits (sum: xor tree inside each group of 32 experts, the
+// group sums added in group order), top-k by (value desc, index asc), weights renormalised by the sum of the selected
+// probabilities taken in rank order; slot k = shared expert, id -1, weight sigmoid(logit[E]). Phase 3, same CTA: the
+// (row, slot) pairs are grouped by expert into segments of up to 8 pairs (see below).
 // synth_key != 0: the E expert logits fed to the softmax are seeded N(0, 1) draws keyed by (layer key, slot, token,
-// position, expert) instead of the GEMV's (benchmark input control: with random-init weights every row's hidden state is nearly the
-// same vector, so a linear router would send all rows to the same experts); the shared expert's gate keeps its logit.
-__global__ void __launch_bounds__(256) k_router_route(const float* __restrict__ W, const float* __restrict__ x, float* __restrict__ y, int N, int K,
-                                                     int* __restrict__ ids, float* __restrict__ w, int E, int k, int* __restrict__ cnt,
-                                                     const int* __restrict__ row_tok, const int* __restrict__ row_pos, const int* __restrict__ row_slot, unsigned long long synth_key) {
+// position, expert) instead of the GEMV's (benchmark input control: with random-init weights every row's hidden state is
+// nearly the same vector, so a linear router would send all rows to the same experts); the shared expert's gate keeps its logit.
+struct MoeSeg { int expert, ncols, cols[8]; int pad[6]; };   // 64 bytes; cols = pair indices t * nslot + e
+__device__ __forceinline__ void better(float& bv, int& bi, float v, int i) { if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; } }
+struct RouteArgs {
+    const float* W; const float* x; float* y; int N, K, T;       // router [N = E + 1][K], rows x [T][K], logits y [T][N]
+    int* ids; float* w; int E, k;                                 // outputs [T][k + 1]
+    int* ticket;                                                  // one zero-initialised int (left zero)
+    const int* row_tok; const int* row_pos; const int* row_slot; unsigned long long synth_key;
+    int e_lo, e_hi, own_shared; MoeSeg* segs; int* ctl; unsigned long long* touched;   // grouping (segs == nullptr: skipped)
+};
+__global__ void __launch_bounds__(1024) k_route_group(RouteArgs a) {
     pdl_launch_dependents();
     pdl_wait();
-    __shared__ float sh[32]; __shared__ float selp[16]; __shared__ int seli[16]; __shared__ float sp[1024]; __shared__ int s_last;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, t = blockIdx.y;
-    const int n = (blockIdx.x * 256 + tid) >> 5;
-    if (n < N) {
-        const float* wr = W + (size_t)n * K; const float* xr = x + (size_t)t * K;
-        float acc = 0.f;
-#pragma unroll 8
-        for (int i = lane * 4; i < K; i += 128) {
-            const float4 a = __ldg(reinterpret_cast<const float4*>(wr + i)), b = *reinterpret_cast<const float4*>(xr + i);
-            acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc); acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
-        }
+    __shared__ int sid[MOE_MAX_PAIRS]; __shared__ int scnt[1025]; __shared__ int soff[1025]; __shared__ int swt[32]; __shared__ int s_last;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n = blockIdx.x * 32 + warp;
+    if (n < a.N) {
+        const float* wr = a.W + (size_t)n * a.K;
+        for (int t0 = 0; t0 < a.T; t0 += 8) {
+            float acc[8];
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) acc = acc + __shfl_xor_sync(0xffffffffu, acc, off);
-        if (lane == 0) { y[(size_t)t * N + n] = acc; __threadfence(); }
+            for (int q = 0; q < 8; ++q) acc[q] = 0.f;
+            for (int i = lane * 4; i < a.K; i += 128) {
+                const float4 wv = __ldg(reinterpret_cast<const float4*>(wr + i));
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                    if (t0 + q < a.T) {
+                        const float4 xv = *reinterpret_cast<const float4*>(a.x + (size_t)(t0 + q) * a.K + i);
+                        acc[q] = fmaf(wv.x, xv.x, acc[q]); acc[q] = fmaf(wv.y, xv.y, acc[q]); acc[q] = fmaf(wv.z, xv.z, acc[q]); acc[q] = fmaf(wv.w, xv.w, acc[q]);
+                    }
+            }
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) acc[q] = acc[q] + __shfl_xor_sync(0xffffffffu, acc[q], off);
+                if (lane == 0 && t0 + q < a.T) a.y[(size_t)(t0 + q) * a.N + n] = acc[q];
+            }
+        }
     }
+    __threadfence();
     __syncthreads();
-    if (tid == 0) s_last = atomicAdd(&cnt[t], 1) == (int)gridDim.x - 1;
+    if (tid == 0) s_last = atomicAdd(a.ticket, 1) == (int)gridDim.x - 1;
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    const float* lg = y + (size_t)t * N;   // N = E + 1 logits of this row, written by all the CTAs of the row
-    float v[4], e[4];
-    float mx = -INFINITY;
+    const int ns = a.k + 1;
+    // ---- routing: warp t routes row t
+    if (warp < a.T) {
+        const int t = warp;
+        const float* lg = a.y + (size_t)t * a.N;
+        const unsigned long long key = a.synth_key ? a.synth_key + (unsigned long long)a.row_slot[t] : 0ull;
+        const unsigned long long rowkey = a.synth_key ? (((unsigned long long)(unsigned)a.row_tok[t] << 32) | (unsigned)a.row_pos[t]) : 0ull;
+        float v[32]; float mx = -INFINITY;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const int i = 32 * (warp + 8 * j) + lane;
-        v[j] = i < E ? (synth_key ? irwin(rnd64(synth_key + (uint64_t)row_slot[t], ((uint64_t)(uint32_t)row_tok[t] << 32) | (uint32_t)row_pos[t], (uint64_t)i)) : __ldcg(lg + i)) : -INFINITY;
-        float m = v[j];
+        for (int q = 0; q < 32; ++q) {
+            const int i = 32 * q + lane;
+            v[q] = i < a.E ? (a.synth_key ? irwin(rnd64(key, rowkey, (uint64_t)i)) : __ldcg(lg + i)) : -INFINITY;
+            mx = fmaxf(mx, v[q]);
+        }
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
-        if (lane == 0) sh[warp + 8 * j] = m;
-    }
-    __syncthreads();
-    mx = sh[0]; for (int q = 1; q < 32; ++q) mx = fmaxf(mx, sh[q]);
-    __syncthreads();
+        for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+        float sum = 0.f;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const int i = 32 * (warp + 8 * j) + lane;
-        e[j] = i < E ? expf_det(v[j] - mx) : 0.f;
-        float sacc = e[j];
+        for (int q = 0; q < 32; ++q) {
+            const int i = 32 * q + lane;
+            v[q] = i < a.E ? expf_det(v[q] - mx) : 0.f;
+            float sg = v[q];
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) sacc = sacc + __shfl_xor_sync(0xffffffffu, sacc, off);
-        if (lane == 0) sh[warp + 8 * j] = sacc;
-    }
-    __syncthreads();
-    float sum = sh[0]; for (int q = 1; q < 32; ++q) sum = sum + sh[q];
+            for (int off = 16; off > 0; off >>= 1) sg = sg + __shfl_xor_sync(0xffffffffu, sg, off);
+            sum = q == 0 ? sg : sum + sg;
+        }
 #pragma unroll
-    for (int j = 0; j < 4; ++j) { const int i = 32 * (warp + 8 * j) + lane; sp[i] = i < E ? e[j] / sum : -2.f; }
-    __syncthreads();
-    if (warp == 0) {   // top-k by (value desc, index asc); lane l owns indices l, l+32, ...
-        float pv[32];
+        for (int q = 0; q < 32; ++q) v[q] = 32 * q + lane < a.E ? v[q] / sum : -2.f;
+        float wsum = 0.f; float selp = 0.f; int seli = 0;   // lane r keeps the r-th winner
+        for (int r = 0; r < a.k; ++r) {
+            float bv = v[0]; int bi = lane;
 #pragma unroll
-        for (int q = 0; q < 32; ++q) pv[q] = sp[lane + 32 * q];
-        for (int r = 0; r < k; ++r) {
-            float bv = pv[0]; int bi = lane;
-#pragma unroll
-            for (int q = 1; q < 32; ++q) better(bv, bi, pv[q], lane + 32 * q);
+            for (int q = 1; q < 32; ++q) better(bv, bi, v[q], lane + 32 * q);
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) { const float ov = __shfl_xor_sync(0xffffffffu, bv, off); const int oi = __shfl_xor_sync(0xffffffffu, bi, off); better(bv, bi, ov, oi); }
-            if (lane == 0) { selp[r] = bv; seli[r] = bi; }
+            if (lane == r) { selp = bv; seli = bi; }
+            wsum = wsum + bv;
 #pragma unroll
-            for (int q = 0; q < 32; ++q) if (bi == lane + 32 * q) pv[q] = -1.f;
+            for (int q = 0; q < 32; ++q) if (bi == lane + 32 * q) v[q] = -1.f;
+        }
+        if (lane < a.k) { a.ids[t * ns + lane] = seli; a.w[t * ns + lane] = selp / wsum; sid[t * ns + lane] = seli; }
+        if (lane == 0) { a.ids[t * ns + a.k] = -1; a.w[t * ns + a.k] = sigmoid_det(__ldcg(lg + a.E)); sid[t * ns + a.k] = -1; }
+    }
+    if (tid == 0) *a.ticket = 0;   // ready for the next launch
+    if (!a.segs) return;
+    // ---- grouping: bucket b = expert e_lo + b (b < nown), then the shared expert; segments in bucket order, the pairs of
+    // a bucket in increasing pair index
+    const int nown = a.e_hi - a.e_lo, nb = nown + (a.own_shared ? 1 : 0), np = a.T * ns;
+    for (int b = tid; b < 1025; b += 1024) scnt[b] = 0;
+    __syncthreads();
+    int my_b = -1, my_rank = 0, my_id = 0;
+    if (tid < np) {
+        my_id = sid[tid];
+        my_b = my_id >= 0 ? ((my_id >= a.e_lo && my_id < a.e_hi) ? my_id - a.e_lo : -1) : (a.own_shared ? nown : -1);
+        if (my_b >= 0) { for (int j = 0; j < tid; ++j) my_rank += sid[j] == my_id; atomicMax(&scnt[my_b], my_rank + 1); }
+    }
+    __syncthreads();
+    {   // exclusive scan of the segments per bucket over buckets 0..1023 (thread = bucket), bucket 1024 appended
+        const int c = tid < nb ? (scnt[tid] + 7) >> 3 : 0;
+        int inc = c;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) { const int o = __shfl_up_sync(0xffffffffu, inc, off); if (lane >= off) inc += o; }
+        if (lane == 31) swt[warp] = inc;
+        const int ntouch = __syncthreads_count(tid < nb && scnt[tid] > 0);
+        if (warp == 0) {
+            int wv = swt[lane], winc = wv;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) { const int o = __shfl_up_sync(0xffffffffu, winc, off); if (lane >= off) winc += o; }
+            swt[lane] = winc - wv;   // exclusive offset of each warp
+        }
+        __syncthreads();
+        soff[tid] = swt[warp] + inc - c;
+        if (tid == 1023) {
+            const int tot1024 = swt[warp] + inc;
+            soff[1024] = tot1024;
+            const int c2 = nb > 1024 ? (scnt[1024] + 7) >> 3 : 0;
+            a.ctl[0] = tot1024 + c2; a.ctl[1] = 0; a.ctl[2] = 0;   // segments, ticket counters of the two GEMVs
+            if (a.touched) atomicAdd(a.touched, (unsigned long long)(ntouch + (nb > 1024 && scnt[1024] > 0 ? 1 : 0)));
         }
     }
     __syncthreads();
-    if (tid == 0) {
-        float wsum = 0.f; for (int r = 0; r < k; ++r) wsum = wsum + selp[r];
-        for (int r = 0; r < k; ++r) { ids[t * (k + 1) + r] = seli[r]; w[t * (k + 1) + r] = selp[r] / wsum; }
-        ids[t * (k + 1) + k] = -1; w[t * (k + 1) + k] = sigmoid_det(__ldcg(lg + E));
-        cnt[t] = 0;   // ready for the next launch
+    if (my_b >= 0) {
+        MoeSeg* sg = a.segs + soff[my_b] + (my_rank >> 3); const int c = my_rank & 7;
+        sg->cols[c] = tid;
+        if (c == 0) sg->expert = my_id;
+        if (c == 7 || my_rank == scnt[my_b] - 1) sg->ncols = c + 1;
     }
 }
 
@@ -113,38 +168,7 @@ __global__ void __launch_bounds__(256) k_router_route(const float* __restrict__ 
 // gate|up tensor is repacked with gate rows 8q..8q+7 and up rows 8q..8q+7 sharing tile q, so that a lane holds gate
 // and up of the same feature and the SiLU-gated product and its int8 quantisation (fn.hip:206-211) finish in registers:
 // a unit's 4 tiles are exactly one 32-feature quantisation group.
-struct MoeSeg { int expert, ncols, cols[8]; int pad[6]; };   // 64 bytes; cols = pair indices t * nslot + e
-constexpr int MOE_WARPS = 8, MOE_DEPTH = 3, MOE_UNIT_TILES = 4;
-
-// one CTA: segments in increasing expert id, the shared expert last; pairs of a segment in increasing pair index
-__global__ void __launch_bounds__(512) k_moe_group(const int* __restrict__ ids, int npairs, int n_expert, int e_lo, int e_hi, int own_shared,
-                                                   MoeSeg* __restrict__ segs, int* __restrict__ ctl, unsigned long long* __restrict__ touched) {
-    pdl_launch_dependents();
-    pdl_wait();
-    __shared__ int sid[MOE_MAX_PAIRS]; __shared__ int soff[1026];
-    for (int i = threadIdx.x; i < npairs; i += 512) sid[i] = ids[i];
-    __syncthreads();
-    // bucket b: expert e_lo + b (b < e_hi - e_lo), then the shared expert
-    const int nown = e_hi - e_lo, nb = nown + (own_shared ? 1 : 0);
-    for (int b = threadIdx.x; b < nb; b += 512) {
-        const int want = b < nown ? e_lo + b : -1; int c = 0;
-        for (int i = 0; i < npairs; ++i) c += sid[i] == want;
-        soff[b] = (c + 7) >> 3;
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {   // exclusive prefix sum (at most 1025 buckets)
-        int acc = 0, nt = 0;
-        for (int b = 0; b < nb; ++b) { const int v = soff[b]; soff[b] = acc; acc += v; nt += v > 0; }
-        ctl[0] = acc; ctl[1] = 0; ctl[2] = 0;   // segments, ticket counters of the two GEMVs
-        if (touched) atomicAdd(touched, (unsigned long long)nt);
-    }
-    __syncthreads();
-    for (int b = threadIdx.x; b < nb; b += 512) {
-        const int want = b < nown ? e_lo + b : -1; int c = 0; MoeSeg* sg = segs + soff[b];
-        for (int i = 0; i < npairs; ++i)
-            if (sid[i] == want) { MoeSeg* q = sg + (c >> 3); if ((c & 7) == 0) { q->expert = want; q->ncols = 0; } q->cols[c & 7] = i; q->ncols = (c & 7) + 1; ++c; }
-    }
-}
+constexpr int MOE_WARPS = 12, MOE_DEPTH = 2, MOE_UNIT_TILES = 4;
 
 struct MoeGArgs {
     const uint8_t* w_exp; const uint8_t* w_sh;     // tile-major expert tensors: this GPU's experts [e_hi - e_lo][tiles][nb] chunks, and the shared expert's
@@ -291,12 +315,14 @@ __global__ void __launch_bounds__(256) k_moe_combine(const float* __restrict__ v
 
 }  // namespace
 
-int router_route(const float* W, const float* x, float* logits, int* ids, float* w, int* counters, int E, int K, int k, int T, cudaStream_t s,
-                 const int* row_tok, const int* row_pos, const int* row_slot, unsigned long long synth_key) {
-    HP_REQUIRE(synth_key == 0 || (row_tok && row_pos && row_slot), "router_route: synthetic logits need the rows' tokens, positions and slots");
-    HP_REQUIRE(E >= 1 && E <= 1024 && k >= 1 && k <= 15 && k <= E && K > 0 && K % 128 == 0 && T >= 1 && T <= 32 && counters, "router_route: bad shape E=%d K=%d k=%d T=%d", E, K, k, T);
-    const int N = E + 1;
-    HP_CUDA(launch_pdl<8>(k_router_route, dim3((N * 32 + 255) / 256, T), dim3(256), 0, s, W, x, logits, N, K, ids, w, E, k, counters, row_tok, row_pos, row_slot, synth_key));
+int moe_route_group(const MoeRouteParams& p, cudaStream_t s) {
+    HP_REQUIRE(p.E >= 1 && p.E <= 1024 && p.k >= 1 && p.k <= 15 && p.k <= p.E && p.K > 0 && p.K % 128 == 0 && p.T >= 1 && p.T <= 32 && p.ticket, "moe_route_group: bad shape E=%d K=%d k=%d T=%d", p.E, p.K, p.k, p.T);
+    HP_REQUIRE(p.synth_key == 0 || (p.row_tok && p.row_pos && p.row_slot), "moe_route_group: synthetic logits need the rows' tokens, positions and slots");
+    HP_REQUIRE(!p.segs || (p.ctl && p.T * (p.k + 1) <= MOE_MAX_PAIRS && p.e_lo >= 0 && p.e_hi <= p.E && p.e_lo <= p.e_hi), "moe_route_group: bad grouping arguments");
+    RouteArgs a; a.W = p.W; a.x = p.x; a.y = p.logits; a.N = p.E + 1; a.K = p.K; a.T = p.T; a.ids = p.ids; a.w = p.w; a.E = p.E; a.k = p.k; a.ticket = p.ticket;
+    a.row_tok = p.row_tok; a.row_pos = p.row_pos; a.row_slot = p.row_slot; a.synth_key = p.synth_key;
+    a.e_lo = p.e_lo; a.e_hi = p.e_hi; a.own_shared = p.own_shared; a.segs = (MoeSeg*)p.segs; a.ctl = p.ctl; a.touched = p.touched;
+    HP_CUDA(launch_pdl<8>(k_route_group, dim3((a.N + 31) / 32), dim3(1024), 0, s, a));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 size_t moe_seg_bytes() { return (size_t)MOE_MAX_PAIRS * sizeof(MoeSeg); }
@@ -315,9 +341,7 @@ static int launch_grouped_sb(const MoeGArgs& a, cudaStream_t s) {
 }
 int moe_experts_grouped(const MoeGroupParams& p, cudaStream_t s) {
     HP_REQUIRE(p.E % 256 == 0 && p.F % 256 == 0 && p.T >= 1 && p.nslot >= 1 && p.T * p.nslot <= MOE_MAX_PAIRS && p.n_expert <= 1024, "moe_experts_grouped: bad shape");
-    HP_REQUIRE(p.segs && p.ctl && p.ids && p.v, "moe_experts_grouped: null pointer");
-    const int npairs = p.T * p.nslot;
-    HP_CUDA(launch_pdl<8>(k_moe_group, dim3(1), dim3(512), 0, s, p.ids, npairs, p.n_expert, p.e_lo, p.e_hi, p.own_shared, (MoeSeg*)p.segs, p.ctl, p.touched));
+    HP_REQUIRE(p.segs && p.ctl && p.v, "moe_experts_grouped: null pointer");
     MoeGArgs a; a.e_lo = p.e_lo; a.segs = (const MoeSeg*)p.segs; a.ctl = p.ctl; a.err = p.err;
     // gate|up: [2F rows][E]; tile q = gate rows 8q.. | up rows 8q..; 4 tiles = one 32-feature quantisation group
     a.w_exp = (const uint8_t*)p.w_gate_up; a.w_sh = (const uint8_t*)p.sh_gate_up; a.tiles = 2 * p.F / 16; a.nb = p.E / 256; a.ticket = 1;
