@@ -418,17 +418,20 @@ int Engine::moe_block(const LayerW& L, int R) {
     const hp_model_cfg& c = c_; const int E = c.n_embd, F = c.expert_ff, ns = c.n_expert_used + 1;
     if (gemv_only_) return HP_OK;
     // synthetic routing (see hp_model_cfg.synth_router_logits): the key of a layer's draws; 0 = the router's own logits
-    const uint64_t rkey = c.synth_router_logits ? (splitmix64(c.seed ^ 0x726F75746572ull ^ ((uint64_t)(&L == &mtp_ ? c.n_layer : (int)(&L - layers_.data())) << 40)) | 1ull) : 0ull;
+    const int lidx = &L == &mtp_ ? c.n_layer : (int)(&L - layers_.data());
+    const uint64_t rkey = c.synth_router_logits ? (splitmix64(c.seed ^ 0x726F75746572ull ^ ((uint64_t)lidx << 40)) | 1ull) : 0ull;
+    // the (replicated) shared expert is computed by one GPU per layer, in turn, so that no GPU carries all of them
+    const int own_sh = c.ep_world > 1 ? (lidx % c.ep_world == c.ep_rank ? 1 : 0) : 1;
     MoeRouteParams rp; rp.W = L.router; rp.x = xn_; rp.logits = rlogits_; rp.E = c.n_expert; rp.K = E; rp.k = c.n_expert_used; rp.T = R;
     rp.ids = moe_ids_; rp.w = moe_w_; rp.ticket = route_cnt_; rp.row_tok = d_desc_ + D_TOK; rp.row_pos = d_desc_ + D_POS; rp.row_slot = d_desc_ + D_SLOT; rp.synth_key = rkey;
-    rp.e_lo = e_lo_; rp.e_hi = e_hi_; rp.own_shared = own_shared_; rp.segs = moe_segs_; rp.ctl = moe_ctl_; rp.touched = moe_touched_;
+    rp.e_lo = e_lo_; rp.e_hi = e_hi_; rp.own_shared = own_sh; rp.segs = moe_segs_; rp.ctl = moe_ctl_; rp.touched = moe_touched_;
     HP_TRY(moe_route_group(rp, s_));
     // per-(row, slot) outputs of the experts this GPU owns, grouped by expert so that each touched expert matrix is read
     // once; pairs of experts owned elsewhere stay exact zeros, the exchange fills them in, and the combine runs in slot
     // order (the arithmetic of gemv.hip:1104-1112) on every GPU
     if (c.ep_world > 1) { HP_TRY(ep_ready()); HP_CUDA(cudaMemsetAsync(moe_v_, 0, (size_t)R * ns * E * 4, s_)); }
     MoeGroupParams g; g.w_gate_up = L.exp_gate_up.wt; g.w_down = L.exp_down.wt; g.sh_gate_up = L.sh_gate_up.wt; g.sh_down = L.sh_down.wt;
-    g.E = E; g.F = F; g.n_expert = c.n_expert; g.nslot = ns; g.T = R; g.e_lo = e_lo_; g.e_hi = e_hi_; g.own_shared = own_shared_;
+    g.E = E; g.F = F; g.n_expert = c.n_expert; g.nslot = ns; g.T = R; g.e_lo = e_lo_; g.e_hi = e_hi_; g.own_shared = own_sh;
     g.xq = xq_; g.xq2 = xq2_; g.v = moe_v_; g.segs = moe_segs_; g.ctl = moe_ctl_; g.err = err_;
     HP_TRY(moe_experts_grouped(g, s_));
     if (c.ep_world > 1) HP_TRY(ep_exchange(moe_v_, (size_t)R * ns * E));
