@@ -148,7 +148,7 @@ int Engine::alloc(void** p, size_t bytes) {
     if (e != cudaSuccess) { set_error("out of device memory allocating %zu bytes (%s)", bytes, cudaGetErrorString(e)); return HP_ENOMEM; }
     allocs_.push_back(*p); return HP_OK;
 }
-int Engine::gen_lin(Lin& l, int N, int K, uint64_t tid, bool gate_up) {
+int Engine::gen_lin(Lin& l, int N, int K, uint64_t tid) {
     l.N = N; l.K = K; l.bytes = (size_t)N * (K / 256) * 144; l.P = gemv_parts(N, K);
     HP_REQUIRE(K % 256 == 0 && l.P > 0, "tensor %d x %d is not a valid Q4_K GEMV shape", N, K);
     if (int rc = alloc((void**)&l.w, l.bytes)) return rc;
@@ -157,11 +157,8 @@ int Engine::gen_lin(Lin& l, int N, int K, uint64_t tid, bool gate_up) {
     HP_CUDA(cudaGetLastError());
     weight_bytes_ += l.bytes;
     if (tiled_) {   // the GEMV streams the tile-major copy; the row-major original is kept only for small (test) models
-        // gate|up of a dense FFN: gate and up rows of a feature share a tile, so that the GEMV's epilogue can form
-        // silu(gate) * up in registers (needs an unsplit K and whole tiles)
-        l.ileave = gate_up && l.P == 1 && N % 32 == 0;
         HP_TRY(alloc((void**)&l.wt, gemv_tiled_bytes(N, K)));
-        HP_TRY(gemv_repack_tiled(l.w, l.wt, N, K, s_, l.ileave ? N / 2 : 0));
+        HP_TRY(gemv_repack_tiled(l.w, l.wt, N, K, s_));
         if (!keep_rowmajor_) {
             HP_CUDA(cudaStreamSynchronize(s_));
             for (size_t i = 0; i < allocs_.size(); ++i) if (allocs_[i] == l.w) { allocs_.erase(allocs_.begin() + i); break; }
@@ -244,7 +241,7 @@ int Engine::init() {
             HP_TRY(gen_bf16(&L.ssm_norm, 128, tensor_id(il, TK_SSM_NORM), 1.f, 0.3f));
         }
         if (c.n_expert == 0) {
-            HP_TRY(gen_lin(L.gate_up, 2 * c.n_ff, E, tensor_id(il, TK_GATE_UP), true));
+            HP_TRY(gen_lin(L.gate_up, 2 * c.n_ff, E, tensor_id(il, TK_GATE_UP)));
             HP_TRY(gen_lin(L.down, E, c.n_ff, tensor_id(il, TK_DOWN)));
         } else {   // routed experts (contiguous per tensor, qwen4exp weights layout [512*N][K]) + one shared expert + f32 router
             const int F = c.expert_ff;
@@ -305,7 +302,6 @@ int Engine::init() {
     HP_TRY(alloc((void**)&yparts_, (size_t)4 * MAXR * std::max<size_t>(bigw, E) * 4));
     HP_TRY(alloc((void**)&logits_, (size_t)MAXR * c.n_vocab * 4)); HP_TRY(alloc((void**)&mlogits_, (size_t)MAXR * c.n_vocab * 4));
     HP_TRY(alloc((void**)&h_, (size_t)MAXR * E * 4)); HP_TRY(alloc((void**)&mh_, (size_t)MAXR * E * 4));
-    HP_TRY(alloc((void**)&act_, (size_t)MAXR * std::max(F, 64) * 4)); HP_CUDA(cudaMemsetAsync(act_, 0, (size_t)MAXR * std::max(F, 64) * 4, s_));
     HP_CUDA(cudaMemsetAsync(h_, 0, (size_t)MAXR * E * 4, s_)); HP_CUDA(cudaMemsetAsync(mh_, 0, (size_t)MAXR * E * 4, s_));
     HP_TRY(alloc(&xq_.q, xq_q_bytes(MAXR, (int)kmax))); HP_TRY(alloc(&xq_.sc, xq_sc_floats(MAXR, (int)kmax) * 4));
     HP_CUDA(cudaMemsetAsync(xq_.q, 0, xq_q_bytes(MAXR, (int)kmax), s_)); HP_CUDA(cudaMemsetAsync(xq_.sc, 0, xq_sc_floats(MAXR, (int)kmax) * 4, s_));
@@ -401,13 +397,10 @@ int Engine::attn_block(const LayerW& L, uint16_t* kc, uint16_t* vc, size_t kv_st
 int Engine::ffn_block(const LayerW& L, int R) {
     if (c_.n_expert) return moe_block(L, R);
     const int F = c_.n_ff;
-    if (L.gate_up.ileave && L.down.wt) {
-        // SwiGLU without a launch of its own: gate|up's epilogue leaves silu(gate) * up as f32 rows, and the down projection
-        // quantises the part of them each CTA needs while it stages its activations
-        if (!(prof_skip_ & 16)) HP_TRY(gemv_q4k_q8_parts(L.gate_up.wt, xq_, act_, 2 * F, c_.n_embd, R, F, 0, err_, s_, pdl_, true, 1));
-        if (prof_skip_ & 32) return HP_OK;
-        return gemv_q4k_q8_parts(L.down.wt, xq_, yparts_, L.down.N, F, R, L.down.N, (size_t)R * L.down.N, err_, s_, pdl_, true, 2, act_, F);
-    }
+    // The SiLU-gated product keeps a launch of its own between the two GEMVs on purpose. Folding it into the gate|up
+    // epilogue and the down projection's staging was measured slower (GEMV launches of a 6-row pass 3.85 -> 4.75 ms): two
+    // one-CTA-per-SM GEMVs back to back cannot overlap, while the small kernel between them is the window in which the
+    // down projection's CTAs become resident and prime their weight rings.
     HP_TRY(lin(L.gate_up, big_, 2 * F, R));
     if (!gemv_only_ && !(prof_skip_ & 8)) HP_TRY(silu_mul_quant(big_, 2 * F, F, xq_, R, s_));
     return lin_parts(L.down, R);

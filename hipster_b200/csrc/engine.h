@@ -12,7 +12,7 @@
 
 namespace hp {
 
-struct Lin { uint8_t* w = nullptr; uint8_t* wt = nullptr; int N = 0, K = 0, P = 1; size_t bytes = 0; bool ileave = false; };   // ileave: gate and up rows of a feature share a tile of wt   // merged Q4_K matrix [N][K/256 blocks]; wt = tile-major copy
+struct Lin { uint8_t* w = nullptr; uint8_t* wt = nullptr; int N = 0, K = 0, P = 1; size_t bytes = 0; };   // merged Q4_K matrix [N][K/256 blocks]; wt = tile-major copy
 
 struct LayerW {
     bool is_attn = false;
@@ -61,7 +61,7 @@ public:
 private:
     struct Desc;   // device-visible pass descriptor (see engine.cu)
     int alloc(void** p, size_t bytes);
-    int gen_lin(Lin& l, int N, int K, uint64_t tid, bool gate_up = false);
+    int gen_lin(Lin& l, int N, int K, uint64_t tid);
     int gen_raw_q4k(Lin& l, size_t rows, int K, uint64_t tid, size_t row0 = 0, size_t nrows_local = (size_t)-1, int interleave_half = 0);
     int gen_bf16(uint16_t** p, size_t n, uint64_t tid, float mean, float std, bool neg_abs = false);
     int gen_f32(float** p, size_t n, uint64_t tid, float mean, float std, bool neg_abs);

@@ -40,17 +40,10 @@ template <int CB, bool TILED> struct SkGeom {
     static constexpr int FIXED = GEMV_WARPS * SK_STAGES * STAGE_BYTES + 1024;
 };
 
-// MODE 0: quantised activations staged by bulk copies, plain f32 output.
-// MODE 1 (gate|up of a dense FFN; needs the tile-major layout repacked with gate rows 8q..8q+7 and up rows 8q..8q+7 in
-//   tile q, and P = 1): a lane holds gate and up of one feature, so the epilogue stores silu(gate) * up [R][N/2] directly
-//   (reference k_silu_mul_quant, ops.hip:146-151, minus its quantiser).
-// MODE 2 (the down projection that follows): the activations arrive as those f32 rows and every CTA quantises the K
-//   part it needs into shared memory itself (per 32 elements: amax/127, rint(x * 127/amax), d * sum(q); gemv.hip:36-51),
-//   which replaces a separate SiLU + quantiser launch between the two GEMVs. xf32 [R][ldx].
-template <int NT, int CB, bool TILED, int MODE>
+template <int NT, int CB, bool TILED>
 __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __restrict__ W, const uint4* __restrict__ xq, const float4* __restrict__ xsc,
                                                                 float* __restrict__ y, int N, int nb, int P, int R, int ldy, size_t part_stride,
-                                                                int* __restrict__ err, const float* __restrict__ xf32, int ldx) {
+                                                                int* __restrict__ err) {
     using Geo = SkGeom<CB, TILED>;
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* ring_all = smem;
@@ -107,40 +100,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
 
     pdl_wait();
 
-    if constexpr (MODE == 2) {
-        // f32 rows -> int8 + scales of blocks [kb0, kb0 + nbp) in the staged layout, by all warps: 8 consecutive lanes own
-        // one (column, 32-element sub-block), 4 elements each; columns beyond R are zero
-        uint8_t* xq_w = smem + Geo::FIXED; float* xsc_w = reinterpret_cast<float*>(smem + Geo::FIXED + NT * nbp * 2048);
-        const int l8 = threadIdx.x & 7, nitem = NT * 8 * nbp * 8;
-        for (int base = 0; base < nitem; base += 4 * (SK_THREADS / 8)) {   // the same trip count for every lane (shuffles inside)
-            const int it0 = base + (threadIdx.x >> 3);
-            float4 v[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int it = it0 + u * (SK_THREADS / 8), c = it / (nbp * 8), sbl = it - c * (nbp * 8);
-                v[u] = (it < nitem && c < R) ? *reinterpret_cast<const float4*>(xf32 + (size_t)c * ldx + (size_t)kb0 * 256 + sbl * 32 + l8 * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int it = it0 + u * (SK_THREADS / 8);   // uniform over the 8 lanes of an item; items of a warp differ only in it
-                float amax = fmaxf(fmaxf(fabsf(v[u].x), fabsf(v[u].y)), fmaxf(fabsf(v[u].z), fabsf(v[u].w)));
-#pragma unroll
-                for (int off = 1; off < 8; off <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-                const float dd = amax / 127.f, id = amax > 0.f ? 127.f / amax : 0.f;
-                const int q0 = __float2int_rn(v[u].x * id), q1 = __float2int_rn(v[u].y * id), q2 = __float2int_rn(v[u].z * id), q3 = __float2int_rn(v[u].w * id);
-                int sum = (q0 + q1) + (q2 + q3);
-#pragma unroll
-                for (int off = 1; off < 8; off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
-                if (it < nitem) {
-                    const int c = it / (nbp * 8), sbl = it - c * (nbp * 8), b = sbl >> 3, k = sbl & 7, n = c >> 3, gc = c & 7;
-                    *reinterpret_cast<uint32_t*>(xq_w + (size_t)(n * nbp + b) * 2048 + (((k >> 1) * 32 + gc * 4 + (l8 >> 1)) << 4) + (k & 1) * 8 + (l8 & 1) * 4) =
-                        (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) | ((uint32_t)(q3 & 0xFF) << 24);
-                    if (l8 == 0) { float* sc = xsc_w + ((size_t)(n * nbp + b) * 8 + k) * 16 + (gc >> 1) * 4 + (gc & 1); sc[0] = dd; sc[2] = dd * (float)sum; }
-                }
-            }
-        }
-        __syncthreads();
-    } else if (warp == 0) {   // quantised activations of blocks [kb0, kb0 + nbp), all NT column tiles, by bulk copies: one block
+    if (warp == 0) {   // quantised activations of blocks [kb0, kb0 + nbp), all NT column tiles, by bulk copies: one block
         // (2048 + 512 B) per copy pair, lanes in parallel, each CTA starting at a different block so that the 148 CTAs do
         // not walk the same L2 lines in lockstep
         if (lane == 0) mbar_expect_tx(xbar, (uint32_t)NT * nbp * 2560u);
@@ -159,23 +119,13 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
     };
     zero_acc();
     auto store_tile = [&](int tile, const float (&v)[NT][4]) {
-        if constexpr (MODE == 1) {   // rows g = gate of feature 8 * tile + g, rows g + 8 = up of the same feature
 #pragma unroll
-            for (int n = 0; n < NT; ++n)
+        for (int n = 0; n < NT; ++n)
 #pragma unroll
-                for (int k = 0; k < 2; ++k) {
-                    const int f = tile * 8 + g, col = n * 8 + 2 * t + k;
-                    if (2 * f < N && col < R) y[(size_t)col * ldy + f] = silu_det(v[n][k]) * v[n][2 + k];
-                }
-        } else {
-#pragma unroll
-            for (int n = 0; n < NT; ++n)
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const int row = tile * 16 + g + ((k & 2) ? 8 : 0), col = n * 8 + 2 * t + (k & 1);
-                    if (row < N && col < R) y[(size_t)col * ldy + row] = v[n][k];
-                }
-        }
+            for (int k = 0; k < 4; ++k) {
+                const int row = tile * 16 + g + ((k & 2) ? 8 : 0), col = n * 8 + 2 * t + (k & 1);
+                if (row < N && col < R) y[(size_t)col * ldy + row] = v[n][k];
+            }
     };
     // a tile covered by this warp alone is stored at once; otherwise the partial sum goes to shared memory
     // (slot 0 = the warp's first tile, slot 1 = its last tile) and is combined after the CTA barrier
@@ -202,7 +152,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
 
     int cur_tile = first_tile, chunk = nunits ? u0 % C : 0;
     bool cur_from_start = chunk == 0;
-    bool ok = MODE == 2 ? true : mbar_wait(xbar, 0, err);
+    bool ok = mbar_wait(xbar, 0, err);
     for (int i = 0; i < nunits && ok; ++i) {
         const int s = i % SK_STAGES;
         ok = mbar_wait(bar0 + 8 * s, (i / SK_STAGES) & 1, err);
@@ -400,31 +350,28 @@ __global__ void __launch_bounds__(F32_THREADS) k_gemv_q4k_f32(const uint8_t* __r
     }
 }
 
-struct SkExtra { int mode = 0; const float* xf32 = nullptr; int ldx = 0; };
-template <int NT, int CB, bool TILED, int MODE>
+template <int NT, int CB, bool TILED>
 int launch_sk2(const uint8_t* W, const void* xq, const void* xsc, float* y, int N, int nb, int P, int R, int ldy, size_t part_stride,
-               int* err, cudaStream_t s, bool pdl, const float* xf32, int ldx) {
+               int* err, cudaStream_t s, bool pdl) {
     const size_t smem = SkGeom<CB, TILED>::FIXED + (size_t)NT * (nb / P) * 2560;
     static size_t attr_smem[MAX_DEVICES] = {};   // per device: the opt-in belongs to the device's copy of the kernel
     const int dev = current_device(); if (dev < 0) return HP_ECUDA;
-    if (smem > attr_smem[dev]) { HP_CUDA(cudaFuncSetAttribute(k_gemv_q4k_sk<NT, CB, TILED, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr_smem[dev] = smem; }
+    if (smem > attr_smem[dev]) { HP_CUDA(cudaFuncSetAttribute(k_gemv_q4k_sk<NT, CB, TILED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr_smem[dev] = smem; }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(GEMV_NCTA); cfg.blockDim = dim3(SK_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = s;
     cudaLaunchAttribute at[1]; at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at; cfg.numAttrs = pdl && !(pdl_off_mask(s) & 64) ? 1 : 0;
-    HP_CUDA(cudaLaunchKernelEx(&cfg, k_gemv_q4k_sk<NT, CB, TILED, MODE>, W, (const uint4*)xq, (const float4*)xsc, y, N, nb, P, R, ldy, part_stride, err, xf32, ldx));
+    HP_CUDA(cudaLaunchKernelEx(&cfg, k_gemv_q4k_sk<NT, CB, TILED>, W, (const uint4*)xq, (const float4*)xsc, y, N, nb, P, R, ldy, part_stride, err));
     return HP_OK;
 }
 template <int NT>
 int launch_sk(const uint8_t* W, bool tiled, const void* xq, const void* xsc, float* y, int N, int nb, int P, int R, int ldy, size_t part_stride,
-              int* err, cudaStream_t s, bool pdl, const SkExtra& ex) {
+              int* err, cudaStream_t s, bool pdl) {
     const bool cb2 = (nb / P) % 2 == 0;
-#define HP_SK(CBV, TL, MD) launch_sk2<NT, CBV, TL, MD>(W, xq, xsc, y, N, nb, P, R, ldy, part_stride, err, s, pdl, ex.xf32, ex.ldx)
-    if (ex.mode == 1) return cb2 ? HP_SK(2, true, 1) : HP_SK(1, true, 1);
-    if (ex.mode == 2) return cb2 ? HP_SK(2, true, 2) : HP_SK(1, true, 2);
-    if (tiled) return cb2 ? HP_SK(2, true, 0) : HP_SK(1, true, 0);
-    return cb2 ? HP_SK(2, false, 0) : HP_SK(1, false, 0);
-#undef HP_SK
+    if (tiled) return cb2 ? launch_sk2<NT, 2, true>(W, xq, xsc, y, N, nb, P, R, ldy, part_stride, err, s, pdl)
+                          : launch_sk2<NT, 1, true>(W, xq, xsc, y, N, nb, P, R, ldy, part_stride, err, s, pdl);
+    return cb2 ? launch_sk2<NT, 2, false>(W, xq, xsc, y, N, nb, P, R, ldy, part_stride, err, s, pdl)
+               : launch_sk2<NT, 1, false>(W, xq, xsc, y, N, nb, P, R, ldy, part_stride, err, s, pdl);
 }
 
 // row-major ggml blocks -> tile-major chunks (see SkGeom); rows beyond N are zero (they contribute nothing).
@@ -468,15 +415,11 @@ int gemv_repack_tiled(const void* src, void* dst, size_t N, int K, cudaStream_t 
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 
-int gemv_q4k_q8_parts(const void* W, const XQ8F& x, float* yparts, int N, int K, int R, int ldy, size_t part_stride, int* err, cudaStream_t s, bool pdl, bool tiled,
-                      int mode, const float* xf32, int ldx) {
+int gemv_q4k_q8_parts(const void* W, const XQ8F& x, float* yparts, int N, int K, int R, int ldy, size_t part_stride, int* err, cudaStream_t s, bool pdl, bool tiled) {
     HP_REQUIRE(K > 0 && K % 256 == 0, "gemv_q4k_q8: K=%d must be a positive multiple of 256", K);
-    HP_REQUIRE(N > 0 && R >= 1 && R <= 32 && ldy >= (mode == 1 ? N / 2 : N), "gemv_q4k_q8: bad shape N=%d R=%d ldy=%d", N, R, ldy);
+    HP_REQUIRE(N > 0 && R >= 1 && R <= 32 && ldy >= N, "gemv_q4k_q8: bad shape N=%d R=%d ldy=%d", N, R, ldy);
     const int nb = K / 256, P = gemv_num_parts(N, nb);
     HP_REQUIRE(P > 0, "gemv_q4k_q8: K=%d is too large for the activation staging buffer", K);
-    HP_REQUIRE(mode == 0 || tiled, "gemv_q4k_q8: the fused SwiGLU forms need the tile-major layout");
-    HP_REQUIRE(mode != 1 || (P == 1 && N % 16 == 0), "gemv_q4k_q8: the SiLU epilogue needs an unsplit K (P = 1) and whole tiles");
-    HP_REQUIRE(mode != 2 || (xf32 && ldx >= K && ldx % 4 == 0 && ((uintptr_t)xf32 & 15) == 0), "gemv_q4k_q8: f32 activations [R][ldx >= K], 16-byte aligned rows");
     const int ntile = (R + 7) / 8, nbp = nb / P;
     // all column tiles in one launch when their activations fit in shared memory beside the rings; otherwise one
     // launch per tile of 8 columns (same per-column arithmetic either way)
@@ -487,13 +430,12 @@ int gemv_q4k_q8_parts(const void* W, const XQ8F& x, float* yparts, int N, int K,
         const uint8_t* xqp = (const uint8_t*)x.q + (size_t)c0 * K * 8;
         const uint8_t* xsp = (const uint8_t*)x.sc + (size_t)c0 * (K / 32) * 64;
         float* yp = yparts + (size_t)c0 * 8 * ldy;
-        SkExtra ex; ex.mode = mode; ex.xf32 = xf32 ? xf32 + (size_t)c0 * 8 * ldx : nullptr; ex.ldx = ldx;
         int rc;
         switch (nt) {
-            case 1: rc = launch_sk<1>((const uint8_t*)W, tiled, xqp, xsp, yp, N, nb, P, Rl, ldy, part_stride, err, s, pdl, ex); break;
-            case 2: rc = launch_sk<2>((const uint8_t*)W, tiled, xqp, xsp, yp, N, nb, P, Rl, ldy, part_stride, err, s, pdl, ex); break;
-            case 3: rc = launch_sk<3>((const uint8_t*)W, tiled, xqp, xsp, yp, N, nb, P, Rl, ldy, part_stride, err, s, pdl, ex); break;
-            default: rc = launch_sk<4>((const uint8_t*)W, tiled, xqp, xsp, yp, N, nb, P, Rl, ldy, part_stride, err, s, pdl, ex); break;
+            case 1: rc = launch_sk<1>((const uint8_t*)W, tiled, xqp, xsp, yp, N, nb, P, Rl, ldy, part_stride, err, s, pdl); break;
+            case 2: rc = launch_sk<2>((const uint8_t*)W, tiled, xqp, xsp, yp, N, nb, P, Rl, ldy, part_stride, err, s, pdl); break;
+            case 3: rc = launch_sk<3>((const uint8_t*)W, tiled, xqp, xsp, yp, N, nb, P, Rl, ldy, part_stride, err, s, pdl); break;
+            default: rc = launch_sk<4>((const uint8_t*)W, tiled, xqp, xsp, yp, N, nb, P, Rl, ldy, part_stride, err, s, pdl); break;
         }
         if (rc != HP_OK) return rc;
     }

@@ -50,10 +50,7 @@ struct GemvWorkspace { float* part; size_t part_bytes; int* err; };
 int gemv_parts(int N, int K);
 // raw form: part p of the K split writes plane yparts + p * part_stride ([R][ldy] each); the caller adds the planes in order
 // tiled = true: W is in the tile-major layout produced by gemv_repack_tiled (gemv_tiled_bytes(N, K) bytes)
-// mode 0: plain. mode 1 (tile-major gate|up repacked with interleave_half = N / 2, P = 1): the output is silu(gate) * up,
-// f32 [R][ldy >= N / 2]. mode 2: the activations are f32 rows xf32 [R][ldx] (x is ignored) and are quantised by the kernel.
-int gemv_q4k_q8_parts(const void* W, const XQ8F& x, float* yparts, int N, int K, int R, int ldy, size_t part_stride, int* err, cudaStream_t s, bool pdl, bool tiled,
-                      int mode = 0, const float* xf32 = nullptr, int ldx = 0);
+int gemv_q4k_q8_parts(const void* W, const XQ8F& x, float* yparts, int N, int K, int R, int ldy, size_t part_stride, int* err, cudaStream_t s, bool pdl, bool tiled);
 size_t gemv_tiled_bytes(size_t N, int K);
 // interleave_half = F > 0: src is a stack of [gate F rows | up F rows] matrices; gate and up rows of a feature share a tile
 int gemv_repack_tiled(const void* src, void* dst, size_t N, int K, cudaStream_t s, int interleave_half = 0);

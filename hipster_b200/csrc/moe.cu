@@ -14,9 +14,9 @@ namespace hp {
 namespace {
 
 // ---- router + routing + grouping in ONE launch ------------------------------------------------------------------------
-// Phase 1, router (exact f32; reference k_f32_gemv, fn.hip:252-266): one warp per weight row n, for all T rows of the
-// pass (the weight row is read once); lane l takes k = 4l + 128 i as float4, four fmaf per step in element order, then
-// the xor-shuffle tree 16..1. Phase 2, in the CTA that finishes last (ticket counter), routing (k_moe_route,
+// Phase 1, router (exact f32; reference k_f32_gemv, fn.hip:252-266): per (weight row n, pass row t) lane l takes
+// k = 4l + 128 i as float4, four fmaf per step in element order, then the xor-shuffle tree 16..1; a warp computes two
+// weight rows against eight pass rows at once. Phase 2, in the CTA that finishes last (ticket counter), routing (k_moe_route,
 // fn.hip:167-205), one warp per row: softmax over the first E logits (sum: xor tree inside each group of 32 experts, the
 // group sums added in group order), top-k by (value desc, index asc), weights renormalised by the sum of the selected
 // probabilities taken in rank order; slot k = shared expert, id -1, weight sigmoid(logit[E]). Phase 3, same CTA: the
@@ -38,33 +38,39 @@ __global__ void __launch_bounds__(1024) k_route_group(RouteArgs a) {
     pdl_wait();
     __shared__ int sid[MOE_MAX_PAIRS]; __shared__ int scnt[1025]; __shared__ int soff[1025]; __shared__ int swt[32]; __shared__ int s_last;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n = blockIdx.x * 32 + warp;
-    if (n < a.N) {
-        const float* wr = a.W + (size_t)n * a.K;
-        for (int t0 = 0; t0 < a.T; t0 += 8) {
-            float acc[8];
+    // Router GEMV: CTA (bx, by) covers weight rows 16 bx .. 16 bx + 15 for pass rows 8 by .. 8 by + 7; its first 8 warps
+    // take two weight rows each (the other warps of the 1024 only serve the routing and grouping phases of the last
+    // CTA). Spreading the 2 N T K fmaf over ~100 CTAs keeps the load pipes of any one SM out of the critical path.
+    if (warp < 8) {
+        const int n0 = blockIdx.x * 16 + 2 * warp, t0 = blockIdx.y * 8;
+        const bool live0 = n0 < a.N, live1 = n0 + 1 < a.N;
+        const float* wr0 = a.W + (size_t)(live0 ? n0 : 0) * a.K; const float* wr1 = a.W + (size_t)(live1 ? n0 + 1 : 0) * a.K;
+        float acc0[8], acc1[8];
 #pragma unroll
-            for (int q = 0; q < 8; ++q) acc[q] = 0.f;
-            for (int i = lane * 4; i < a.K; i += 128) {
-                const float4 wv = __ldg(reinterpret_cast<const float4*>(wr + i));
+        for (int q = 0; q < 8; ++q) { acc0[q] = 0.f; acc1[q] = 0.f; }
+        for (int i = lane * 4; i < a.K; i += 128) {
+            const float4 w0 = __ldg(reinterpret_cast<const float4*>(wr0 + i)), w1 = __ldg(reinterpret_cast<const float4*>(wr1 + i));
 #pragma unroll
-                for (int q = 0; q < 8; ++q)
-                    if (t0 + q < a.T) {
-                        const float4 xv = *reinterpret_cast<const float4*>(a.x + (size_t)(t0 + q) * a.K + i);
-                        acc[q] = fmaf(wv.x, xv.x, acc[q]); acc[q] = fmaf(wv.y, xv.y, acc[q]); acc[q] = fmaf(wv.z, xv.z, acc[q]); acc[q] = fmaf(wv.w, xv.w, acc[q]);
-                    }
-            }
+            for (int q = 0; q < 8; ++q)
+                if (t0 + q < a.T) {
+                    const float4 xv = *reinterpret_cast<const float4*>(a.x + (size_t)(t0 + q) * a.K + i);
+                    acc0[q] = fmaf(w0.x, xv.x, acc0[q]); acc0[q] = fmaf(w0.y, xv.y, acc0[q]); acc0[q] = fmaf(w0.z, xv.z, acc0[q]); acc0[q] = fmaf(w0.w, xv.w, acc0[q]);
+                    acc1[q] = fmaf(w1.x, xv.x, acc1[q]); acc1[q] = fmaf(w1.y, xv.y, acc1[q]); acc1[q] = fmaf(w1.z, xv.z, acc1[q]); acc1[q] = fmaf(w1.w, xv.w, acc1[q]);
+                }
+        }
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
+        for (int q = 0; q < 8; ++q) {
 #pragma unroll
-                for (int off = 16; off > 0; off >>= 1) acc[q] = acc[q] + __shfl_xor_sync(0xffffffffu, acc[q], off);
-                if (lane == 0 && t0 + q < a.T) a.y[(size_t)(t0 + q) * a.N + n] = acc[q];
+            for (int off = 16; off > 0; off >>= 1) { acc0[q] = acc0[q] + __shfl_xor_sync(0xffffffffu, acc0[q], off); acc1[q] = acc1[q] + __shfl_xor_sync(0xffffffffu, acc1[q], off); }
+            if (lane == 0 && t0 + q < a.T) {
+                if (live0) a.y[(size_t)(t0 + q) * a.N + n0] = acc0[q];
+                if (live1) a.y[(size_t)(t0 + q) * a.N + n0 + 1] = acc1[q];
             }
         }
     }
     __threadfence();
     __syncthreads();
-    if (tid == 0) s_last = atomicAdd(a.ticket, 1) == (int)gridDim.x - 1;
+    if (tid == 0) s_last = atomicAdd(a.ticket, 1) == (int)(gridDim.x * gridDim.y) - 1;
     __syncthreads();
     if (!s_last) return;
     __threadfence();
@@ -322,7 +328,7 @@ int moe_route_group(const MoeRouteParams& p, cudaStream_t s) {
     RouteArgs a; a.W = p.W; a.x = p.x; a.y = p.logits; a.N = p.E + 1; a.K = p.K; a.T = p.T; a.ids = p.ids; a.w = p.w; a.E = p.E; a.k = p.k; a.ticket = p.ticket;
     a.row_tok = p.row_tok; a.row_pos = p.row_pos; a.row_slot = p.row_slot; a.synth_key = p.synth_key;
     a.e_lo = p.e_lo; a.e_hi = p.e_hi; a.own_shared = p.own_shared; a.segs = (MoeSeg*)p.segs; a.ctl = p.ctl; a.touched = p.touched;
-    HP_CUDA(launch_pdl<8>(k_route_group, dim3((a.N + 31) / 32), dim3(1024), 0, s, a));
+    HP_CUDA(launch_pdl<8>(k_route_group, dim3((a.N + 15) / 16, (a.T + 7) / 8), dim3(1024), 0, s, a));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 size_t moe_seg_bytes() { return (size_t)MOE_MAX_PAIRS * sizeof(MoeSeg); }
