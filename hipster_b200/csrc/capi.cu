@@ -184,7 +184,7 @@ MoeWs moe_ws(int T, int E, int F, int n_expert, int k) {
     const size_t pairs = (size_t)T * (k + 1);
     MoeWs w; size_t o = 0;
     w.logits = o; o += al((size_t)T * (n_expert + 1) * 4);
-    w.cnt = o; o += al((size_t)T * 4);
+    w.cnt = o; o += al(32 * 4);
     w.v = o; o += al(pairs * E * 4);
     w.q2 = o; o += al(hp::xq_q_bytes((int)pairs, F));
     w.sc2 = o; o += al(hp::xq_sc_floats((int)pairs, F) * 4);
@@ -204,7 +204,7 @@ int hp_moe_layer(const float* xn_dev, const void* xq_q_dev, const void* xq_sc_de
     const MoeWs w = moe_ws(T, E, F, n_expert, k);
     char* ws = (char*)workspace_dev; const int ns = k + 1;
     float* logits = (float*)(ws + w.logits); int* cnt = (int*)(ws + w.cnt); float* v = (float*)(ws + w.v);
-    HP_CUDA(cudaMemsetAsync(cnt, 0, (size_t)T * 4, s));
+    HP_CUDA(cudaMemsetAsync(cnt, 0, 32 * 4, s));
     HP_CUDA(cudaMemsetAsync(ws + w.q2, 0, w.total - w.q2, s));
     hp::MoeRouteParams rp; rp.W = router_dev; rp.x = xn_dev; rp.logits = logits; rp.E = n_expert; rp.K = E; rp.k = k; rp.T = T; rp.ids = ids_dev; rp.w = weights_dev; rp.ticket = cnt;
     rp.e_lo = 0; rp.e_hi = n_expert; rp.own_shared = 1; rp.segs = ws + w.segs; rp.ctl = (int*)(ws + w.ctl);

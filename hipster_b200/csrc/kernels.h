@@ -111,7 +111,7 @@ constexpr int MOE_MAX_PAIRS = 32 * 16;
 struct MoeRouteParams {
     const float* W; const float* x; float* logits; int E, K, k, T;   // router [E + 1][K] f32, rows x [T][K], logits [T][E + 1]
     int* ids; float* w;                                               // [T][k + 1]: expert ids (-1 = shared) and combine weights
-    int* ticket;                                                      // one zero-initialised int (left zero)
+    int* ticket;                                                      // five zero-initialised ints (left zero)
     const int* row_tok = nullptr; const int* row_pos = nullptr; const int* row_slot = nullptr; unsigned long long synth_key = 0;   // synth_key != 0: seeded N(0,1) expert logits per (slot, token, position)
     int e_lo = 0, e_hi = 0, own_shared = 1;                           // experts this GPU owns
     void* segs = nullptr; int* ctl = nullptr; unsigned long long* touched = nullptr;   // grouping outputs (segs == nullptr: no grouping)

@@ -29,18 +29,19 @@ __device__ __forceinline__ void better(float& bv, int& bi, float v, int i) { if 
 struct RouteArgs {
     const float* W; const float* x; float* y; int N, K, T;       // router [N = E + 1][K], rows x [T][K], logits y [T][N]
     int* ids; float* w; int E, k;                                 // outputs [T][k + 1]
-    int* ticket;                                                  // one zero-initialised int (left zero)
+    int* ticket;                                                  // five zero-initialised ints (left zero)
     const int* row_tok; const int* row_pos; const int* row_slot; unsigned long long synth_key;
     int e_lo, e_hi, own_shared; MoeSeg* segs; int* ctl; unsigned long long* touched;   // grouping (segs == nullptr: skipped)
 };
-__global__ void __launch_bounds__(1024) k_route_group(RouteArgs a) {
+constexpr int RG_THREADS = 512;
+__global__ void __launch_bounds__(RG_THREADS) k_route_group(RouteArgs a) {
     pdl_launch_dependents();
     pdl_wait();
-    __shared__ int sid[MOE_MAX_PAIRS]; __shared__ int scnt[1025]; __shared__ int soff[1025]; __shared__ int swt[32]; __shared__ int s_last;
+    __shared__ int sid[MOE_MAX_PAIRS]; __shared__ int scnt[1026]; __shared__ int soff[1026]; __shared__ int swt[RG_THREADS / 32]; __shared__ int s_last;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // Router GEMV: CTA (bx, by) covers weight rows 16 bx .. 16 bx + 15 for pass rows 8 by .. 8 by + 7; its first 8 warps
-    // take two weight rows each (the other warps of the 1024 only serve the routing and grouping phases of the last
-    // CTA). Spreading the 2 N T K fmaf over ~100 CTAs keeps the load pipes of any one SM out of the critical path.
+    // take two weight rows each. Spreading the 2 N T K fmaf over ~100 CTAs keeps the load pipes of any one SM out of
+    // the critical path.
     if (warp < 8) {
         const int n0 = blockIdx.x * 16 + 2 * warp, t0 = blockIdx.y * 8;
         const bool live0 = n0 < a.N, live1 = n0 + 1 < a.N;
@@ -68,24 +69,25 @@ __global__ void __launch_bounds__(1024) k_route_group(RouteArgs a) {
             }
         }
     }
+    // ---- routing of the 8 rows of group `by`, by the CTA that completes their logits last (ticket per group), so that
+    // the groups are routed on different SMs at the same time: warp w routes row 8 by + w
     __threadfence();
     __syncthreads();
-    if (tid == 0) s_last = atomicAdd(a.ticket, 1) == (int)(gridDim.x * gridDim.y) - 1;
+    if (tid == 0) s_last = atomicAdd(a.ticket + blockIdx.y, 1) == (int)gridDim.x - 1;
     __syncthreads();
     if (!s_last) return;
     __threadfence();
     const int ns = a.k + 1;
-    // ---- routing: warp t routes row t
-    if (warp < a.T) {
-        const int t = warp;
+    if (warp < 8 && (int)blockIdx.y * 8 + warp < a.T) {
+        const int t = blockIdx.y * 8 + warp;
         const float* lg = a.y + (size_t)t * a.N;
-        const unsigned long long key = a.synth_key ? a.synth_key + (unsigned long long)a.row_slot[t] : 0ull;
-        const unsigned long long rowkey = a.synth_key ? (((unsigned long long)(unsigned)a.row_tok[t] << 32) | (unsigned)a.row_pos[t]) : 0ull;
+        // synthetic logits: rnd64(key + slot, (token, position), expert) = splitmix64(base + expert)
+        const unsigned long long base = a.synth_key ? splitmix64((a.synth_key + (unsigned long long)a.row_slot[t]) ^ ((((unsigned long long)(unsigned)a.row_tok[t] << 32) | (unsigned)a.row_pos[t]) * 0x9E3779B97F4A7C15ull)) : 0ull;
         float v[32]; float mx = -INFINITY;
 #pragma unroll
         for (int q = 0; q < 32; ++q) {
             const int i = 32 * q + lane;
-            v[q] = i < a.E ? (a.synth_key ? irwin(rnd64(key, rowkey, (uint64_t)i)) : __ldcg(lg + i)) : -INFINITY;
+            v[q] = i < a.E ? (a.synth_key ? irwin(splitmix64(base + (uint64_t)i)) : __ldcg(lg + i)) : -INFINITY;
             mx = fmaxf(mx, v[q]);
         }
 #pragma unroll
@@ -114,15 +116,22 @@ __global__ void __launch_bounds__(1024) k_route_group(RouteArgs a) {
 #pragma unroll
             for (int q = 0; q < 32; ++q) if (bi == lane + 32 * q) v[q] = -1.f;
         }
-        if (lane < a.k) { a.ids[t * ns + lane] = seli; a.w[t * ns + lane] = selp / wsum; sid[t * ns + lane] = seli; }
-        if (lane == 0) { a.ids[t * ns + a.k] = -1; a.w[t * ns + a.k] = sigmoid_det(__ldcg(lg + a.E)); sid[t * ns + a.k] = -1; }
+        if (lane < a.k) { a.ids[t * ns + lane] = seli; a.w[t * ns + lane] = selp / wsum; }
+        if (lane == 0) { a.ids[t * ns + a.k] = -1; a.w[t * ns + a.k] = sigmoid_det(__ldcg(lg + a.E)); }
     }
-    if (tid == 0) *a.ticket = 0;   // ready for the next launch
+    if (tid == 0) a.ticket[blockIdx.y] = 0;   // ready for the next launch
     if (!a.segs) return;
-    // ---- grouping: bucket b = expert e_lo + b (b < nown), then the shared expert; segments in bucket order, the pairs of
-    // a bucket in increasing pair index
+    // ---- grouping, by the CTA that routes last (second-level ticket): bucket b = expert e_lo + b (b < nown), then the
+    // shared expert; segments in bucket order, the pairs of a bucket in increasing pair index
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = atomicAdd(a.ticket + 4, 1) == (int)gridDim.y - 1;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
     const int nown = a.e_hi - a.e_lo, nb = nown + (a.own_shared ? 1 : 0), np = a.T * ns;
-    for (int b = tid; b < 1025; b += 1024) scnt[b] = 0;
+    for (int i = tid; i < np; i += RG_THREADS) sid[i] = __ldcg(a.ids + i);
+    for (int b = tid; b < 1026; b += RG_THREADS) scnt[b] = 0;
     __syncthreads();
     int my_b = -1, my_rank = 0, my_id = 0;
     if (tid < np) {
@@ -131,27 +140,29 @@ __global__ void __launch_bounds__(1024) k_route_group(RouteArgs a) {
         if (my_b >= 0) { for (int j = 0; j < tid; ++j) my_rank += sid[j] == my_id; atomicMax(&scnt[my_b], my_rank + 1); }
     }
     __syncthreads();
-    {   // exclusive scan of the segments per bucket over buckets 0..1023 (thread = bucket), bucket 1024 appended
-        const int c = tid < nb ? (scnt[tid] + 7) >> 3 : 0;
-        int inc = c;
+    {   // exclusive scan of the segments per bucket: thread = buckets 2 tid and 2 tid + 1 (0..1023), bucket 1024 appended
+        const int b0 = 2 * tid, c0 = b0 < nb ? (scnt[b0] + 7) >> 3 : 0, c1 = b0 + 1 < nb ? (scnt[b0 + 1] + 7) >> 3 : 0;
+        int inc = c0 + c1;
 #pragma unroll
         for (int off = 1; off < 32; off <<= 1) { const int o = __shfl_up_sync(0xffffffffu, inc, off); if (lane >= off) inc += o; }
         if (lane == 31) swt[warp] = inc;
-        const int ntouch = __syncthreads_count(tid < nb && scnt[tid] > 0);
+        const int ntouch = __syncthreads_count(b0 < nb && scnt[b0] > 0) + __syncthreads_count(b0 + 1 < nb && scnt[b0 + 1] > 0);
         if (warp == 0) {
-            int wv = swt[lane], winc = wv;
+            int wv = lane < RG_THREADS / 32 ? swt[lane] : 0, winc = wv;
 #pragma unroll
             for (int off = 1; off < 32; off <<= 1) { const int o = __shfl_up_sync(0xffffffffu, winc, off); if (lane >= off) winc += o; }
-            swt[lane] = winc - wv;   // exclusive offset of each warp
+            if (lane < RG_THREADS / 32) swt[lane] = winc - wv;   // exclusive offset of each warp
         }
         __syncthreads();
-        soff[tid] = swt[warp] + inc - c;
-        if (tid == 1023) {
-            const int tot1024 = swt[warp] + inc;
+        const int ex = swt[warp] + inc - (c0 + c1);
+        soff[b0] = ex; soff[b0 + 1] = ex + c0;
+        if (tid == RG_THREADS - 1) {
+            const int tot1024 = ex + c0 + c1;
             soff[1024] = tot1024;
             const int c2 = nb > 1024 ? (scnt[1024] + 7) >> 3 : 0;
             a.ctl[0] = tot1024 + c2; a.ctl[1] = 0; a.ctl[2] = 0;   // segments, ticket counters of the two GEMVs
             if (a.touched) atomicAdd(a.touched, (unsigned long long)(ntouch + (nb > 1024 && scnt[1024] > 0 ? 1 : 0)));
+            a.ticket[4] = 0;
         }
     }
     __syncthreads();
@@ -328,7 +339,7 @@ int moe_route_group(const MoeRouteParams& p, cudaStream_t s) {
     RouteArgs a; a.W = p.W; a.x = p.x; a.y = p.logits; a.N = p.E + 1; a.K = p.K; a.T = p.T; a.ids = p.ids; a.w = p.w; a.E = p.E; a.k = p.k; a.ticket = p.ticket;
     a.row_tok = p.row_tok; a.row_pos = p.row_pos; a.row_slot = p.row_slot; a.synth_key = p.synth_key;
     a.e_lo = p.e_lo; a.e_hi = p.e_hi; a.own_shared = p.own_shared; a.segs = (MoeSeg*)p.segs; a.ctl = p.ctl; a.touched = p.touched;
-    HP_CUDA(launch_pdl<8>(k_route_group, dim3((a.N + 15) / 16, (a.T + 7) / 8), dim3(1024), 0, s, a));
+    HP_CUDA(launch_pdl<8>(k_route_group, dim3((a.N + 15) / 16, (a.T + 7) / 8), dim3(RG_THREADS), 0, s, a));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 size_t moe_seg_bytes() { return (size_t)MOE_MAX_PAIRS * sizeof(MoeSeg); }
