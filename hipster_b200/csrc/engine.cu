@@ -134,6 +134,7 @@ Engine::Engine(const hp_model_cfg& cfg) : c_(cfg) {}
 Engine::~Engine() {
     ep_destroy();
     for (cudaGraphExec_t g : graphs_) if (g) cudaGraphExecDestroy(g);
+    for (auto& v : ep_segs_) for (EpSeg& sg : v) if (sg.g) cudaGraphExecDestroy(sg.g);
     for (void* p : allocs_) cudaFree(p);
     if (h_desc_) cudaFreeHost(h_desc_);
     if (h_spec_) cudaFreeHost(h_spec_);
@@ -754,12 +755,30 @@ int Engine::profile_pass(int R, int what, int reps, float* ms) {
     return check_device_status();
 }
 
+static int count_kernel_nodes(cudaGraph_t g, int* out) {
+    size_t nn = 0; HP_CUDA(cudaGraphGetNodes(g, nullptr, &nn));
+    std::vector<cudaGraphNode_t> nodes(nn); if (nn) HP_CUDA(cudaGraphGetNodes(g, nodes.data(), &nn));
+    int nk = 0; for (size_t i = 0; i < nn; ++i) { cudaGraphNodeType ty; if (cudaGraphNodeGetType(nodes[i], &ty) == cudaSuccess && ty == cudaGraphNodeTypeKernel) ++nk; }
+    *out += nk; return HP_OK;
+}
 // Expert-parallel exchange of the per-(row, slot) expert outputs. Every element of the buffer is produced by exactly one
 // GPU (the owner of that slot's expert) and is an exact zero on the others, so the result is the owner's value bit for
 // bit whatever order the library adds in: an all-gather of a permuted buffer expressed as one NCCL call.
 int Engine::ep_exchange(float* buf, size_t n) {
     if (ep_world_ <= 1) return HP_OK;
-    return ep_allreduce(buf, n);
+    if (!seg_out_) return ep_allreduce(buf, n);
+    // a round is being captured in segments: close the stretch that ends here, remember the exchange, open the next one
+    cudaGraph_t g = nullptr; cudaGraphExec_t ex = nullptr;
+    HP_CUDA(cudaStreamEndCapture(s_, &g));
+    int nk = 0; const int rc = count_kernel_nodes(g, &nk);
+    const cudaError_t ce = rc == HP_OK ? cudaGraphInstantiate(&ex, g, 0) : cudaErrorUnknown;
+    cudaGraphDestroy(g);
+    if (rc != HP_OK) return rc;
+    HP_CUDA(ce);
+    seg_out_->push_back(EpSeg{ex, buf, n});
+    for (int k = 0; k < 64; ++k) if (seg_out_ == &ep_segs_[k]) graph_kernels_[k] += nk;
+    HP_CUDA(cudaStreamBeginCapture(s_, cudaStreamCaptureModeThreadLocal));
+    return HP_OK;
 }
 
 // ------------------------------------------------------------------ fused device-side round
@@ -812,14 +831,22 @@ int Engine::spec_round(const int* slots, int S, int n, const int* subst, int* ou
         h_spec_[SI_SLOTS + j] = j < S ? slots[j] : 0;
         for (int i = 0; i < 8; ++i) h_spec_[SI_SUBST + 8 * j + i] = (subst && j < S && i < n) ? subst[j * n + i] : -1;
     }
-    // A round that carries collectives is enqueued kernel by kernel: the host stays able to watch the communicator
-    // (sync_stream) and no collective is baked into a graph that outlives a failed peer.
-    static const bool env_no_graph = getenv("HIPSTER_B200_NO_GRAPH") != nullptr;
-    const bool no_graph = env_no_graph || c_.ep_world > 1;
+    // A round that carries collectives is replayed as the graphs of the stretches between two exchanges, with the
+    // exchanges themselves enqueued by the host in between: capturing the collectives into the graph hung on 2 GPUs
+    // (NCCL 2.28.9), and this way the host also stays able to watch the communicator (sync_stream).
+    static const bool no_graph = getenv("HIPSTER_B200_NO_GRAPH") != nullptr;
     const int key = (S - 1) * 8 + n;
     HP_CUDA(cudaEventRecord(ev0_, s_));
     if (no_graph) HP_TRY(enqueue_round(S, n));
-    else {
+    else if (c_.ep_world > 1) {
+        if (!warmed_[key]) { HP_TRY(enqueue_round(S, n)); HP_TRY(sync_stream()); warmed_[key] = true; goto done; }   // first call: eager
+        if (ep_segs_[key].empty()) HP_TRY(capture_segments(key, S, n));
+        for (const EpSeg& sg : ep_segs_[key]) {
+            HP_CUDA(cudaGraphLaunch(sg.g, s_));
+            if (sg.n) HP_TRY(ep_allreduce(sg.buf, sg.n));
+        }
+        last_round_kernels_ = graph_kernels_[key];
+    } else {
         if (!graphs_[key]) {
             if (!warmed_[key]) { HP_TRY(enqueue_round(S, n)); HP_TRY(sync_stream()); warmed_[key] = true; goto done; }   // first call: eager (sets kernel attributes)
             cudaGraph_t g = nullptr;
@@ -852,6 +879,28 @@ done:
         spec_pos_[slots[j]] = r[SP_POS]; last_T_[slots[j]] = 0; pend_[slots[j]] = r[SP_COUNT];
     }
     return HP_OK;
+}
+// capture one round as segments: ep_exchange() closes the running capture at every exchange and opens the next one
+int Engine::capture_segments(int key, int S, int n) {
+    std::vector<EpSeg>& segs = ep_segs_[key];
+    graph_kernels_[key] = 0;
+    HP_CUDA(cudaStreamBeginCapture(s_, cudaStreamCaptureModeThreadLocal));
+    seg_out_ = &segs;
+    const int rc = enqueue_round(S, n);
+    seg_out_ = nullptr;
+    cudaGraph_t g = nullptr;
+    const cudaError_t ce = cudaStreamEndCapture(s_, &g);
+    int rc2 = rc;
+    if (rc2 == HP_OK && ce != cudaSuccess) rc2 = cuda_fail(ce, "cudaStreamEndCapture", __FILE__, __LINE__);
+    if (rc2 == HP_OK) {
+        cudaGraphExec_t ex = nullptr;
+        rc2 = count_kernel_nodes(g, &graph_kernels_[key]);
+        if (rc2 == HP_OK && cudaGraphInstantiate(&ex, g, 0) != cudaSuccess) { set_error("cannot instantiate a round segment"); rc2 = HP_ECUDA; }
+        if (rc2 == HP_OK) segs.push_back(EpSeg{ex, nullptr, 0});
+    }
+    if (g) cudaGraphDestroy(g);
+    if (rc2 != HP_OK) { for (EpSeg& sg : segs) cudaGraphExecDestroy(sg.g); segs.clear(); }
+    return rc2;
 }
 int Engine::check_device_status() {
     int herr = 0; HP_CUDA(cudaMemcpy(&herr, err_, 4, cudaMemcpyDeviceToHost));

@@ -108,6 +108,10 @@ private:
     std::vector<int> spec_pos_, spec_on_;
     void* topk_scratch_ = nullptr; int *d_topk_ids_ = nullptr; float* d_topk_vals_ = nullptr;
     uint16_t* prof_kv_ = nullptr;                                 // K/V rows saved around profile_pass
+    // a round that carries collectives: the stretches between two exchanges as graphs, the exchanges enqueued by the host
+    struct EpSeg { cudaGraphExec_t g; float* buf; size_t n; };
+    std::vector<EpSeg> ep_segs_[64]; std::vector<EpSeg>* seg_out_ = nullptr;
+    int capture_segments(int key, int S, int n);
     cudaGraphExec_t graphs_[64] = {}; bool warmed_[64] = {}; int graph_kernels_[64] = {}; int last_round_kernels_ = 0;
     int* err_ = nullptr;
     cudaStream_t s_ = nullptr; cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
