@@ -207,7 +207,7 @@ int hp_moe_layer(const float* xn_dev, const void* xq_q_dev, const void* xq_sc_de
     HP_CUDA(cudaMemsetAsync(cnt, 0, 32 * 4, s));
     HP_CUDA(cudaMemsetAsync(ws + w.q2, 0, w.total - w.q2, s));
     hp::MoeRouteParams rp; rp.W = router_dev; rp.x = xn_dev; rp.logits = logits; rp.E = n_expert; rp.K = E; rp.k = k; rp.T = T; rp.ids = ids_dev; rp.w = weights_dev; rp.ticket = cnt;
-    rp.e_lo = 0; rp.e_hi = n_expert; rp.own_shared = 1; rp.segs = ws + w.segs; rp.ctl = (int*)(ws + w.ctl);
+    rp.e_lo = 0; rp.e_hi = n_expert; rp.own_shared = 1; rp.segs = ws + w.segs; rp.ctl = (int*)(ws + w.ctl); rp.err = hp::device_err_flag();
     { const int rc = hp::moe_route_group(rp, s); if (rc) return rc; }
     hp::MoeGroupParams g; g.w_gate_up = exp_gate_up_tiled_dev; g.w_down = exp_down_tiled_dev; g.sh_gate_up = sh_gate_up_tiled_dev; g.sh_down = sh_down_tiled_dev;
     g.E = E; g.F = F; g.n_expert = n_expert; g.nslot = ns; g.T = T; g.e_lo = 0; g.e_hi = n_expert; g.own_shared = 1;

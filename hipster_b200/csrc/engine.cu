@@ -418,7 +418,7 @@ int Engine::moe_block(const LayerW& L, int R) {
     const int own_sh = c.ep_world > 1 ? (lidx % c.ep_world == c.ep_rank ? 1 : 0) : 1;
     MoeRouteParams rp; rp.W = L.router; rp.x = xn_; rp.logits = rlogits_; rp.E = c.n_expert; rp.K = E; rp.k = c.n_expert_used; rp.T = R;
     rp.ids = moe_ids_; rp.w = moe_w_; rp.ticket = route_cnt_; rp.row_tok = d_desc_ + D_TOK; rp.row_pos = d_desc_ + D_POS; rp.row_slot = d_desc_ + D_SLOT; rp.synth_key = rkey;
-    rp.e_lo = e_lo_; rp.e_hi = e_hi_; rp.own_shared = own_sh; rp.segs = moe_segs_; rp.ctl = moe_ctl_; rp.touched = moe_touched_;
+    rp.e_lo = e_lo_; rp.e_hi = e_hi_; rp.own_shared = own_sh; rp.segs = moe_segs_; rp.ctl = moe_ctl_; rp.touched = moe_touched_; rp.err = err_;
     HP_TRY(moe_route_group(rp, s_));
     // per-(row, slot) outputs of the experts this GPU owns, grouped by expert so that each touched expert matrix is read
     // once; pairs of experts owned elsewhere stay exact zeros, the exchange fills them in, and the combine runs in slot

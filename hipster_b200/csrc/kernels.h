@@ -115,6 +115,7 @@ struct MoeRouteParams {
     const int* row_tok = nullptr; const int* row_pos = nullptr; const int* row_slot = nullptr; unsigned long long synth_key = 0;   // synth_key != 0: seeded N(0,1) expert logits per (slot, token, position)
     int e_lo = 0, e_hi = 0, own_shared = 1;                           // experts this GPU owns
     void* segs = nullptr; int* ctl = nullptr; unsigned long long* touched = nullptr;   // grouping outputs (segs == nullptr: no grouping)
+    int* err = nullptr;                                               // device status word (bounded waits)
 };
 int moe_route_group(const MoeRouteParams& p, cudaStream_t s);
 // Routed experts grouped by expert (see moe.cu). Expert tensors tile-major: gate|up repacked with interleave_half = F.

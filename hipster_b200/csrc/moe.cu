@@ -32,32 +32,54 @@ struct RouteArgs {
     int* ticket;                                                  // five zero-initialised ints (left zero)
     const int* row_tok; const int* row_pos; const int* row_slot; unsigned long long synth_key;
     int e_lo, e_hi, own_shared; MoeSeg* segs; int* ctl; unsigned long long* touched;   // grouping (segs == nullptr: skipped)
+    int stage_w; int* err;                                        // router rows staged in shared memory; status word for the bounded wait
 };
 constexpr int RG_THREADS = 512;
 __global__ void __launch_bounds__(RG_THREADS) k_route_group(RouteArgs a) {
     pdl_launch_dependents();
-    pdl_wait();
     __shared__ int sid[MOE_MAX_PAIRS]; __shared__ int scnt[1026]; __shared__ int soff[1026]; __shared__ int swt[RG_THREADS / 32]; __shared__ int s_last;
+    __shared__ __align__(8) unsigned long long wbar;
+    extern __shared__ __align__(128) uint8_t rg_smem[];   // the CTA's 16 router rows [16][K] f32 (when they fit: a.stage_w)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // Router GEMV: CTA (bx, by) covers weight rows 16 bx .. 16 bx + 15 for pass rows 8 by .. 8 by + 7; its first 8 warps
     // take two weight rows each. Spreading the 2 N T K fmaf over ~100 CTAs keeps the load pipes of any one SM out of
-    // the critical path.
+    // the critical path. The 16 weight rows do not depend on the previous kernel: they are fetched by bulk async copies
+    // before the dependency wait, all at once, instead of one dependent DRAM round trip per 128 columns.
+    const float* wsm = reinterpret_cast<const float*>(rg_smem);
+    const uint32_t wb = smem_u32(&wbar);
+    if (a.stage_w) {
+        if (tid == 0) { mbar_init(wb, 1); fence_barrier_init(); }
+        __syncthreads();
+        if (warp == 0) {
+            const int nrow = min(16, a.N - (int)blockIdx.x * 16);
+            if (lane == 0) mbar_expect_tx(wb, (uint32_t)nrow * (uint32_t)a.K * 4u);
+            __syncwarp();
+            if (lane < nrow) bulk_g2s(smem_u32(rg_smem + (size_t)lane * a.K * 4), a.W + (size_t)(blockIdx.x * 16 + lane) * a.K, (uint32_t)a.K * 4u, wb);
+        }
+    }
+    pdl_wait();
+    bool ok = true;
     if (warp < 8) {
         const int n0 = blockIdx.x * 16 + 2 * warp, t0 = blockIdx.y * 8;
         const bool live0 = n0 < a.N, live1 = n0 + 1 < a.N;
-        const float* wr0 = a.W + (size_t)(live0 ? n0 : 0) * a.K; const float* wr1 = a.W + (size_t)(live1 ? n0 + 1 : 0) * a.K;
+        const float* wr0; const float* wr1;
+        if (a.stage_w) { ok = mbar_wait(wb, 0, a.err); wr0 = wsm + (size_t)(2 * warp) * a.K; wr1 = wsm + (size_t)(live1 ? 2 * warp + 1 : 2 * warp) * a.K; }
+        else { wr0 = a.W + (size_t)(live0 ? n0 : 0) * a.K; wr1 = a.W + (size_t)(live1 ? n0 + 1 : 0) * a.K; }
         float acc0[8], acc1[8];
 #pragma unroll
         for (int q = 0; q < 8; ++q) { acc0[q] = 0.f; acc1[q] = 0.f; }
-        for (int i = lane * 4; i < a.K; i += 128) {
-            const float4 w0 = __ldg(reinterpret_cast<const float4*>(wr0 + i)), w1 = __ldg(reinterpret_cast<const float4*>(wr1 + i));
+        if (ok && live0) {
+#pragma unroll 2
+            for (int i = lane * 4; i < a.K; i += 128) {
+                const float4 w0 = *reinterpret_cast<const float4*>(wr0 + i), w1 = *reinterpret_cast<const float4*>(wr1 + i);
 #pragma unroll
-            for (int q = 0; q < 8; ++q)
-                if (t0 + q < a.T) {
-                    const float4 xv = *reinterpret_cast<const float4*>(a.x + (size_t)(t0 + q) * a.K + i);
-                    acc0[q] = fmaf(w0.x, xv.x, acc0[q]); acc0[q] = fmaf(w0.y, xv.y, acc0[q]); acc0[q] = fmaf(w0.z, xv.z, acc0[q]); acc0[q] = fmaf(w0.w, xv.w, acc0[q]);
-                    acc1[q] = fmaf(w1.x, xv.x, acc1[q]); acc1[q] = fmaf(w1.y, xv.y, acc1[q]); acc1[q] = fmaf(w1.z, xv.z, acc1[q]); acc1[q] = fmaf(w1.w, xv.w, acc1[q]);
-                }
+                for (int q = 0; q < 8; ++q)
+                    if (t0 + q < a.T) {
+                        const float4 xv = *reinterpret_cast<const float4*>(a.x + (size_t)(t0 + q) * a.K + i);
+                        acc0[q] = fmaf(w0.x, xv.x, acc0[q]); acc0[q] = fmaf(w0.y, xv.y, acc0[q]); acc0[q] = fmaf(w0.z, xv.z, acc0[q]); acc0[q] = fmaf(w0.w, xv.w, acc0[q]);
+                        acc1[q] = fmaf(w1.x, xv.x, acc1[q]); acc1[q] = fmaf(w1.y, xv.y, acc1[q]); acc1[q] = fmaf(w1.z, xv.z, acc1[q]); acc1[q] = fmaf(w1.w, xv.w, acc1[q]);
+                    }
+            }
         }
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
@@ -339,7 +361,16 @@ int moe_route_group(const MoeRouteParams& p, cudaStream_t s) {
     RouteArgs a; a.W = p.W; a.x = p.x; a.y = p.logits; a.N = p.E + 1; a.K = p.K; a.T = p.T; a.ids = p.ids; a.w = p.w; a.E = p.E; a.k = p.k; a.ticket = p.ticket;
     a.row_tok = p.row_tok; a.row_pos = p.row_pos; a.row_slot = p.row_slot; a.synth_key = p.synth_key;
     a.e_lo = p.e_lo; a.e_hi = p.e_hi; a.own_shared = p.own_shared; a.segs = (MoeSeg*)p.segs; a.ctl = p.ctl; a.touched = p.touched;
-    HP_CUDA(launch_pdl<8>(k_route_group, dim3((a.N + 15) / 16, (a.T + 7) / 8), dim3(RG_THREADS), 0, s, a));
+    // the CTA's 16 router rows are staged in shared memory when they fit (K <= 3072 floats per row)
+    const size_t wbytes = (size_t)16 * a.K * 4;
+    a.stage_w = wbytes <= 192 * 1024 && a.K % 4 == 0 && ((uintptr_t)a.W & 15) == 0 ? 1 : 0; a.err = p.err;
+    const size_t smem = a.stage_w ? wbytes : 0;
+    if (smem > 48 * 1024) {
+        static size_t attr[MAX_DEVICES] = {};
+        const int dev = current_device(); if (dev < 0) return HP_ECUDA;
+        if (smem > attr[dev]) { HP_CUDA(cudaFuncSetAttribute(k_route_group, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr[dev] = smem; }
+    }
+    HP_CUDA(launch_pdl<8>(k_route_group, dim3((a.N + 15) / 16, (a.T + 7) / 8), dim3(RG_THREADS), smem, s, a));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 size_t moe_seg_bytes() { return (size_t)MOE_MAX_PAIRS * sizeof(MoeSeg); }
