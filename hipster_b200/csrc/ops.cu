@@ -260,7 +260,11 @@ __device__ __forceinline__ float2 gdn_fma2(float2 a, float2 b, float2 c) {   // 
         : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)), "l"(reinterpret_cast<unsigned long long&>(c)));
     return r;
 }
-__global__ void __cluster_dims__(GDN_CL, 1, 1) __launch_bounds__(256) k_gdn(GdnArgs a) {
+// MINB = resident CTAs per SM the register budget is cut for: 3 (80 registers) for one or two sequences (one wave either
+// way), 4 (64 registers, a few bytes of spills) for passes over several sequences, where the grid runs in several waves
+// of this latency-bound kernel and a fourth CTA per SM shortens them. Same instructions, same results.
+template <int MINB>
+__global__ void __cluster_dims__(GDN_CL, 1, 1) __launch_bounds__(256, MINB) k_gdn(GdnArgs a) {
     constexpr int D = 128, NLD = 8, NCV = 6;   // items per thread: (16 + 3) * 96 <= 8 * 256 raw values, 16 * 96 = 6 * 256 conv outputs
     // conv'ed, then normalised q | k of every row (filled by all four CTAs); 16-float chunks padded to 20 so that the
     // eight chunk owners of a state row read 128 bits each from distinct banks
@@ -479,7 +483,8 @@ int gdn_forward(const GdnParams& p, int nseq, cudaStream_t s) {
     a.state = p.state; a.conv_state = p.conv_state; a.state_stride = p.state_stride; a.conv_stride = p.conv_stride;
     a.seq = p.seq; a.replay_n = p.replay_n; a.imm_T = p.imm_T; a.imm_replay = p.imm_replay; a.out = p.out; a.oq = (int8_t*)p.xq.q; a.osc = (float*)p.xq.sc;
     a.snap = p.snap; a.snap_row_stride = p.snap_row_stride; a.eps = p.eps; a.sigmoid_gate = p.sigmoid_gate;
-    HP_CUDA(launch_pdl<128>(k_gdn, dim3(p.n_v * GDN_CL, nseq), dim3(256), 0, s, a));
+    if (nseq >= 3) HP_CUDA(launch_pdl<128>(k_gdn<4>, dim3(p.n_v * GDN_CL, nseq), dim3(256), 0, s, a));
+    else HP_CUDA(launch_pdl<128>(k_gdn<3>, dim3(p.n_v * GDN_CL, nseq), dim3(256), 0, s, a));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 
