@@ -210,7 +210,7 @@ int hp_moe_layer(const float* xn_dev, const void* xq_q_dev, const void* xq_sc_de
     rp.e_lo = 0; rp.e_hi = n_expert; rp.own_shared = 1; rp.segs = ws + w.segs; rp.ctl = (int*)(ws + w.ctl); rp.err = hp::device_err_flag();
     { const int rc = hp::moe_route_group(rp, s); if (rc) return rc; }
     hp::MoeGroupParams g; g.w_gate_up = exp_gate_up_tiled_dev; g.w_down = exp_down_tiled_dev; g.sh_gate_up = sh_gate_up_tiled_dev; g.sh_down = sh_down_tiled_dev;
-    g.E = E; g.F = F; g.n_expert = n_expert; g.nslot = ns; g.T = T; g.e_lo = 0; g.e_hi = n_expert; g.own_shared = 1;
+    g.E = E; g.F = F; g.nslot = ns; g.T = T; g.e_lo = 0;
     g.xq = hp::XQ8F{(void*)xq_q_dev, (void*)xq_sc_dev}; g.xq2 = hp::XQ8F{ws + w.q2, ws + w.sc2}; g.v = v;
     g.segs = ws + w.segs; g.ctl = (int*)(ws + w.ctl); g.err = hp::device_err_flag();
     { const int rc = hp::moe_experts_grouped(g, s); if (rc) return rc; }

@@ -299,7 +299,7 @@ int Engine::init() {
     const size_t bigw = std::max<size_t>({(size_t)gdn_in, (size_t)attn_in, (size_t)2 * F, (size_t)2 * E});
     const size_t kmax = std::max<size_t>({(size_t)2 * E, (size_t)F, (size_t)c.n_head * 256, (size_t)nv * 128});
     HP_TRY(alloc((void**)&x_, (size_t)MAXR * E * 4)); HP_TRY(alloc((void**)&emb_, (size_t)MAXR * E * 4));
-    HP_TRY(alloc((void**)&big_, (size_t)MAXR * bigw * 4)); HP_TRY(alloc((void**)&cat_, (size_t)MAXR * 2 * E * 4));
+    HP_TRY(alloc((void**)&big_, (size_t)MAXR * bigw * 4));
     HP_TRY(alloc((void**)&yparts_, (size_t)4 * MAXR * std::max<size_t>(bigw, E) * 4));
     HP_TRY(alloc((void**)&logits_, (size_t)MAXR * c.n_vocab * 4)); HP_TRY(alloc((void**)&mlogits_, (size_t)MAXR * c.n_vocab * 4));
     HP_TRY(alloc((void**)&h_, (size_t)MAXR * E * 4)); HP_TRY(alloc((void**)&mh_, (size_t)MAXR * E * 4));
@@ -318,7 +318,7 @@ int Engine::init() {
         HP_TRY(alloc(&xq2_.q, xq_q_bytes(pairs, F))); HP_TRY(alloc(&xq2_.sc, xq_sc_floats(pairs, F) * 4));
         HP_CUDA(cudaMemsetAsync(xq2_.q, 0, xq_q_bytes(pairs, F), s_)); HP_CUDA(cudaMemsetAsync(xq2_.sc, 0, xq_sc_floats(pairs, F) * 4, s_));
         moe_out_.N = E; moe_out_.K = F; moe_out_.P = 1;
-        { const int w = std::max(1, c.ep_world); e_lo_ = (int)((long long)c.ep_rank * c.n_expert / w); e_hi_ = (int)((long long)(c.ep_rank + 1) * c.n_expert / w); own_shared_ = (w == 1 || c.ep_rank == 0) ? 1 : 0; }
+        { const int w = std::max(1, c.ep_world); e_lo_ = (int)((long long)c.ep_rank * c.n_expert / w); e_hi_ = (int)((long long)(c.ep_rank + 1) * c.n_expert / w); }
     }
     nsplit_max_ = (c.max_ctx + ATTN_SPLIT - 1) / ATTN_SPLIT;
     const size_t np = attn_partial_floats(MAXR, c.n_head_kv, nsplit_max_);
@@ -425,7 +425,7 @@ int Engine::moe_block(const LayerW& L, int R) {
     // order (the arithmetic of gemv.hip:1104-1112) on every GPU
     if (c.ep_world > 1) { HP_TRY(ep_ready()); HP_CUDA(cudaMemsetAsync(moe_v_, 0, (size_t)R * ns * E * 4, s_)); }
     MoeGroupParams g; g.w_gate_up = L.exp_gate_up.wt; g.w_down = L.exp_down.wt; g.sh_gate_up = L.sh_gate_up.wt; g.sh_down = L.sh_down.wt;
-    g.E = E; g.F = F; g.n_expert = c.n_expert; g.nslot = ns; g.T = R; g.e_lo = e_lo_; g.e_hi = e_hi_; g.own_shared = own_sh;
+    g.E = E; g.F = F; g.nslot = ns; g.T = R; g.e_lo = e_lo_;
     g.xq = xq_; g.xq2 = xq2_; g.v = moe_v_; g.segs = moe_segs_; g.ctl = moe_ctl_; g.err = err_;
     HP_TRY(moe_experts_grouped(g, s_));
     if (c.ep_world > 1) HP_TRY(ep_exchange(moe_v_, (size_t)R * ns * E));
@@ -533,7 +533,6 @@ int Engine::forward(const hp_slot_req* reqs, int S, float* ms) {
         HP_CUDA(cudaMemsetAsync(replay_n_ + r.slot, 0, 4, s_)); pend_[r.slot] = 0;
         last_r0_[r.slot] = r0; last_T_[r.slot] = r.T; r0 += r.T;
     }
-    last_rows_ = T;
     HP_CUDA(cudaEventRecord(ev1_, s_)); HP_TRY(sync_stream());
     HP_CUDA(cudaEventElapsedTime(&last_ms_, ev0_, ev1_));
     HP_TRY(check_device_status());
@@ -1015,7 +1014,7 @@ int Engine::ep_init(const void* id128) {
     HP_TRY(nccl_load());
     NcclId id; memcpy(id.b, id128, 128);
     HP_TRY(nccl_check(g_nccl.CommInitRank(&nccl_comm_, c_.ep_world, id, c_.ep_rank), "ncclCommInitRank"));
-    ep_world_ = c_.ep_world; ep_rank_ = c_.ep_rank; ep_failed_ = false;
+    ep_world_ = c_.ep_world; ep_failed_ = false;
     return HP_OK;
 }
 // a model loaded as one shard of an expert-parallel group must not run a pass before (or after a failure of) its

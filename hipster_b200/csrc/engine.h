@@ -95,11 +95,11 @@ private:
     float* saved_ = nullptr; size_t sv_layer_ = 0, sv_stride_ = 0; int ld_in_ = 0;   // raw GDN inputs of the last pass (for the deferred commit)
     int* replay_n_ = nullptr; std::vector<int> pend_, last_r0_, last_T_;
     // work
-    float *x_ = nullptr, *xn_ = nullptr, *big_ = nullptr, *act_ = nullptr, *yparts_ = nullptr, *logits_ = nullptr, *mlogits_ = nullptr, *h_ = nullptr, *mh_ = nullptr, *cat_ = nullptr, *emb_ = nullptr;
+    float *x_ = nullptr, *xn_ = nullptr, *big_ = nullptr, *yparts_ = nullptr, *logits_ = nullptr, *mlogits_ = nullptr, *h_ = nullptr, *mh_ = nullptr, *emb_ = nullptr;
     float *pO_ = nullptr, *pm_ = nullptr, *pl_ = nullptr; int nsplit_max_ = 0;
     XQ8F xq_{nullptr, nullptr}, xq2_{nullptr, nullptr};
     float *rlogits_ = nullptr, *moe_w_ = nullptr, *moe_v_ = nullptr; void* moe_segs_ = nullptr; int* moe_ctl_ = nullptr; unsigned long long* moe_touched_ = nullptr; int* moe_ids_ = nullptr; int* route_cnt_ = nullptr; Lin moe_out_;
-    int e_lo_ = 0, e_hi_ = 0, own_shared_ = 1, ep_world_ = 1, ep_rank_ = 0; void* nccl_comm_ = nullptr; bool ep_failed_ = false;
+    int e_lo_ = 0, e_hi_ = 0, ep_world_ = 1; void* nccl_comm_ = nullptr; bool ep_failed_ = false;
     int *d_desc_ = nullptr, *h_desc_ = nullptr;                  // device / pinned host descriptor
     int *d_ids_ = nullptr, *d_mids_ = nullptr; float *d_vals_ = nullptr, *d_mvals_ = nullptr; void* am_scratch_ = nullptr;
     int *d_spec_ = nullptr, *h_spec_ = nullptr;                   // fused round state (device) / results (pinned host)
@@ -117,7 +117,7 @@ private:
     cudaStream_t s_ = nullptr; cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
     std::vector<void*> allocs_;
     size_t weight_bytes_ = 0; float last_ms_ = 0;
-    int last_rows_ = 0, prof_skip_ = 0; bool gemv_only_ = false, tiled_ = true, keep_rowmajor_ = true; bool pdl_ = getenv("HIPSTER_B200_NO_PDL") == nullptr;
+    int prof_skip_ = 0; bool gemv_only_ = false, tiled_ = true, keep_rowmajor_ = true; bool pdl_ = getenv("HIPSTER_B200_NO_PDL") == nullptr;
 };
 
 int ep_wait_poll(int (*stream_query)(void*), int (*comm_error)(void*), void* ctx, int limit_ms);

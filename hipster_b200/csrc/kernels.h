@@ -121,8 +121,8 @@ int moe_route_group(const MoeRouteParams& p, cudaStream_t s);
 // Routed experts grouped by expert (see moe.cu). Expert tensors tile-major: gate|up repacked with interleave_half = F.
 struct MoeGroupParams {
     const void* w_gate_up; const void* w_down; const void* sh_gate_up; const void* sh_down;   // this GPU's experts [e_lo, e_hi) and the shared expert
-    int E, F, n_expert, nslot, T;                       // hidden, expert FFN, routed experts, slots per row (k + 1), rows
-    int e_lo, e_hi, own_shared;
+    int E, F, nslot, T;                                 // hidden, expert FFN, slots per row (k + 1), rows
+    int e_lo;                                           // first routed expert this GPU holds (its tensors start there)
     XQ8F xq, xq2;                                       // quantised rows [T] (K = E) in; quantised silu(gate)*up per pair [T * nslot] (K = F) scratch
     float* v;                                           // per-pair outputs [T * nslot][E] (pairs of experts owned elsewhere are not written)
     void* segs; int* ctl;                               // filled by moe_route_group: MOE_MAX_PAIRS segments of 64 bytes, 4 control ints

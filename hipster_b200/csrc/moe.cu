@@ -388,7 +388,7 @@ static int launch_grouped_sb(const MoeGArgs& a, cudaStream_t s) {
     return a.nb % 4 == 0 ? launch_grouped<MODE, 4>(a, s) : a.nb % 2 == 0 ? launch_grouped<MODE, 2>(a, s) : launch_grouped<MODE, 1>(a, s);
 }
 int moe_experts_grouped(const MoeGroupParams& p, cudaStream_t s) {
-    HP_REQUIRE(p.E % 256 == 0 && p.F % 256 == 0 && p.T >= 1 && p.nslot >= 1 && p.T * p.nslot <= MOE_MAX_PAIRS && p.n_expert <= 1024, "moe_experts_grouped: bad shape");
+    HP_REQUIRE(p.E % 256 == 0 && p.F % 256 == 0 && p.T >= 1 && p.nslot >= 1 && p.T * p.nslot <= MOE_MAX_PAIRS, "moe_experts_grouped: bad shape");
     HP_REQUIRE(p.segs && p.ctl && p.v, "moe_experts_grouped: null pointer");
     MoeGArgs a; a.e_lo = p.e_lo; a.segs = (const MoeSeg*)p.segs; a.ctl = p.ctl; a.err = p.err;
     // gate|up: [2F rows][E]; tile q = gate rows 8q.. | up rows 8q..; 4 tiles = one 32-feature quantisation group

@@ -127,3 +127,55 @@ def test_cpp_driver_through_the_c_abi_reports_exact():
         assert r.stdout.count("EXACT") == 2 and "MISMATCH" not in r.stdout, r.stdout
     deps = subprocess.run(["ldd", exe], capture_output=True, text=True).stdout
     assert "libhipster_b200.so" in deps and "libcudart" not in deps and "libtorch" not in deps
+
+
+def test_measurement_hooks_and_full_width_lockstep_round():
+    """8 slots x (3 drafts + 1) = 32 verify rows, the most a pass can hold, through the fused multi-slot round on the reduced
+    MoE model; the kernel count of the round's graph, the touched-expert counter and the exchange timer answer."""
+    cfg = hb.ModelCfg.preset("tiny-moe", n_slots=8)
+    eng = hb.Engine(cfg)
+    S, n = 8, 3
+    prompts = [[int(x) for x in np.random.default_rng(500 + s).integers(0, cfg.n_vocab, size=3 + s)] for s in range(S)]
+    for s in range(S):
+        eng.prefill(s, prompts[s], with_mtp=True)
+        eng.spec_begin(s, int(eng.topk(0, 1)[0][0]), len(prompts[s]), eng.h_nextn_ptr())
+    eng.moe_touched()
+    lock = [[] for _ in range(S)]
+    for r in range(3):
+        out = eng.spec_round_slots(list(range(S)), n)
+        assert all(1 <= len(o) <= n + 1 for o in out)
+        for s in range(S):
+            lock[s] += out[s]
+    assert eng.last_round_kernels() > 100
+    assert eng.moe_touched() > 0 and eng.ep_exchange_us(8) == 0.0          # one GPU: nothing to exchange
+    with pytest.raises(hb.HipsterError):
+        eng.spec_round_slots(list(range(S)), 4)                             # 8 x 5 rows > 32
+    with pytest.raises(hb.HipsterError):
+        eng.spec_round_slots([0, 0], 2)                                     # a slot listed twice
+    # every slot equals its solo run in another order of slots (the row order of a pass has no influence)
+    eng.reset()
+    for s in (5, 2):
+        eng.prefill(s, prompts[s], with_mtp=True)
+        eng.spec_begin(s, int(eng.topk(0, 1)[0][0]), len(prompts[s]), eng.h_nextn_ptr())
+    two = [[], []]
+    for r in range(3):
+        out = eng.spec_round_slots([5, 2], n)
+        two[0] += out[0]; two[1] += out[1]
+    assert two[0] == lock[5] and two[1] == lock[2]
+    eng.close()
+
+
+def test_single_token_prefill_zero_rows_and_reset_slot():
+    cfg = hb.ModelCfg.preset("tiny")
+    eng = hb.Engine(cfg); ref = orc.Model(cfg)
+    eng.prefill(1, [77], with_mtp=True)                                      # one token: no "last row" move is needed
+    ref.forward([(1, [77], 0)]); ref.accept(1, 1)
+    assert np.array_equal(bits(eng.logits(1)), bits(ref.logits(1)))
+    eng.reset_slot(1); ref.reset_slot(1)
+    for e in (eng, ref):
+        e.forward([(1, [5, 6], 0), (0, [9], 0)])                             # slots in descending order, ragged row counts
+    assert np.array_equal(bits(eng.logits(3)), bits(ref.logits(3)))
+    for bad in ([], [(0, [], 0)], [(0, [1] * 9, 0)], [(7, [1], 0)], [(0, [1], cfg.max_ctx)]):
+        with pytest.raises(hb.HipsterError):
+            eng.forward(bad)
+    eng.close()

@@ -113,3 +113,17 @@ def test_bad_arguments_are_rejected_not_launched():
         K_.gemv_q4k_q8(W, xq, 16, 100)         # K not a multiple of 256
     with pytest.raises(hb.HipsterError):
         K_.gemv_q4k_q8(W[1:], xq, 16, 256)     # misaligned weights
+
+
+def test_all_zero_and_tiny_activations():
+    """A 32-element sub-block of zeros quantises to d = 0, q = 0 (no 0/0), and a whole zero row gives exact zeros."""
+    N, K = 48, 512
+    W = synth.q4k_matrix(N, K, seed=3)
+    x = synth.activations(3, K, seed=4); x[1] = 0.0; x[2, 64:96] = 0.0; x[0, :32] = 1e-30
+    xq = K_.quantize_x_q8(dev(x))
+    q, d, s = [t.cpu().numpy() for t in xq.unpack()]
+    oq, od, os_ = orc.quantize_x_q8(x)
+    assert np.array_equal(q, oq) and np.array_equal(bits(d), bits(od)) and np.array_equal(bits(s), bits(os_))
+    y = K_.gemv_q4k_q8(dev(W), xq, N, K).cpu().numpy()
+    assert np.array_equal(bits(y), bits(orc.gemv_q4k_q8(W, oq, od, os_, N, K)))
+    assert not y[1].any() and np.isfinite(y).all()
