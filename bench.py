@@ -263,6 +263,8 @@ def run_dense(args, rank, local_rank, world):
 
     for _ in range(args.warmup):
         one_round()
+    if cfg.n_expert:
+        eng.moe_touched()            # count the (layer, expert) matrices of the timed rounds only
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
@@ -277,6 +279,7 @@ def run_dense(args, rank, local_rank, world):
     torch.cuda.profiler.stop()
     clocks = sampler.stop() if sampler else None
     exact = out[:len(plain)] == plain[:len(out)]
+    touched = eng.moe_touched() if cfg.n_expert else 0
     round_kernels = eng.last_round_kernels()
     finite = bool(np.isfinite(eng.topk(0, n + 1)[1]).all())     # the verify rows' top logits (random-init weights must not blow up)
     # dominant kernel alone: the GEMV launches of one 6-row verify pass, CUDA events on the engine's stream
@@ -289,6 +292,9 @@ def run_dense(args, rank, local_rank, world):
     q4k = lambda N, K: N * (K // 256) * 144
     catchup_bytes = q4k(cfg.n_embd, 2 * cfg.n_embd) + q4k(cfg.n_head * 512 + 2 * cfg.n_head_kv * 256, cfg.n_embd)
     round_bytes = verify_bytes + n * (mtp_bytes + head_bytes) + catchup_bytes
+    if cfg.n_expert:   # mixture of experts: the shared expert is inside pass_weight_bytes and among the touched matrices; count it once
+        eb = q4k(2 * cfg.expert_ff, cfg.n_embd) + q4k(cfg.n_embd, cfg.expert_ff)
+        round_bytes += (touched / args.steps - (cfg.n_layer + n)) * eb
     if world > 1:
         t = torch.tensor([dev_ms, wall_ms], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX); dev_ms, wall_ms = float(t[0]), float(t[1])
         tt = torch.tensor([toks], device="cuda", dtype=torch.float64); dist.all_reduce(tt); toks = float(tt.item())

@@ -207,7 +207,10 @@ __global__ void __launch_bounds__(RG_THREADS) k_route_group(RouteArgs a) {
 // gate|up tensor is repacked with gate rows 8q..8q+7 and up rows 8q..8q+7 sharing tile q, so that a lane holds gate
 // and up of the same feature and the SiLU-gated product and its int8 quantisation (fn.hip:206-211) finish in registers:
 // a unit's 4 tiles are exactly one 32-feature quantisation group.
-constexpr int MOE_WARPS = 12, MOE_DEPTH = 2, MOE_UNIT_TILES = 4;
+constexpr int MOE_UNIT_TILES = 4;
+// Ring geometry (warps per CTA x stages per warp), chosen by the number of rows of the pass: the shared memory of an SM
+// buys either many warps with a short ring (many units: throughput) or few warps with a long one (few units, e.g. the
+// 3 rows of a single-slot verify pass: each busy warp must keep enough bytes in flight by itself to hide the DRAM latency).
 
 struct MoeGArgs {
     const uint8_t* w_exp; const uint8_t* w_sh;     // tile-major expert tensors: this GPU's experts [e_hi - e_lo][tiles][nb] chunks, and the shared expert's
@@ -219,7 +222,7 @@ struct MoeGArgs {
     int* err;
 };
 // MODE 0: gate|up with the fused SiLU-gated product + quantisation; MODE 1: down projection (per-pair f32 outputs)
-template <int MODE, int SB>
+template <int MODE, int SB, int MOE_WARPS, int MOE_DEPTH>
 __global__ void __launch_bounds__(MOE_WARPS * 32, 1) k_moe_gemv_grouped(MoeGArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int STAGE = SB * 2304;
@@ -239,15 +242,21 @@ __global__ void __launch_bounds__(MOE_WARPS * 32, 1) k_moe_gemv_grouped(MoeGArgs
         const uint8_t* w = sg.expert >= 0 ? a.w_exp + (size_t)(sg.expert - a.e_lo) * a.tiles * a.nb * 2304 : a.w_sh;
         return w + (size_t)(u % ups) * MOE_UNIT_TILES * a.nb * 2304;
     };
-    // issue cursor: unit iu, stage is (0..spu) of it; the copies of a unit are consecutive in memory (4 tiles x nb chunks)
+    // issue cursor: unit iu, stage is (0..spu) of it; the copies of a unit are consecutive in memory (4 tiles x nb chunks).
+    // It runs MOE_DEPTH stages ahead of the compute cursor, i.e. up to MOE_DEPTH / spu + 1 units ahead: the units it has
+    // moved on to wait in a short queue (q0 = next to compute) until the compute cursor reaches them.
     int iu = grab(), is = 0, icount = 0; const uint8_t* isrc = iu < total ? unit_base(iu) : nullptr;
-    int nu = -1;                                               // unit grabbed by the issue cursor while `cu` is still being computed
+    int q0 = -1, q1 = -1, q2 = -1, q3 = -1, qn = 0;
     auto issue = [&]() {
         if (iu >= total) return;
         const uint32_t bar = bar0 + 8 * (icount % MOE_DEPTH);
         if (lane == 0) { mbar_expect_tx(bar, STAGE); bulk_g2s(smem_u32(ring + (icount % MOE_DEPTH) * STAGE), isrc, STAGE, bar); }
         ++icount; isrc += STAGE;
-        if (++is == spu) { is = 0; iu = grab(); nu = iu; isrc = iu < total ? unit_base(iu) : nullptr; }
+        if (++is == spu) {
+            is = 0; iu = grab(); isrc = iu < total ? unit_base(iu) : nullptr;
+            if (qn == 0) q0 = iu; else if (qn == 1) q1 = iu; else if (qn == 2) q2 = iu; else q3 = iu;
+            ++qn;
+        }
     };
     int cu = iu;
     for (int i = 0; i < MOE_DEPTH; ++i) issue();
@@ -339,7 +348,7 @@ __global__ void __launch_bounds__(MOE_WARPS * 32, 1) k_moe_gemv_grouped(MoeGArgs
                 }
             }
         }
-        cu = (cu == iu) ? iu : nu;   // the next unit is the one the issue cursor moved on to
+        cu = q0; q0 = q1; q1 = q2; q2 = q3; q3 = -1; --qn;   // the next unit is the oldest one the issue cursor moved on to
     }
 }
 
@@ -374,18 +383,23 @@ int moe_route_group(const MoeRouteParams& p, cudaStream_t s) {
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 size_t moe_seg_bytes() { return (size_t)MOE_MAX_PAIRS * sizeof(MoeSeg); }
-template <int MODE, int SB>
+template <int MODE, int SB, int WARPS, int DEPTH>
 static int launch_grouped(const MoeGArgs& a, cudaStream_t s) {
-    const size_t smem = (size_t)MOE_WARPS * MOE_DEPTH * SB * 2304 + MOE_WARPS * MOE_DEPTH * 8;
+    const size_t smem = (size_t)WARPS * DEPTH * SB * 2304 + WARPS * DEPTH * 8;
     static bool attr[MAX_DEVICES] = {};
     const int dev = current_device(); if (dev < 0) return HP_ECUDA;
-    if (!attr[dev]) { HP_CUDA(cudaFuncSetAttribute(k_moe_gemv_grouped<MODE, SB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr[dev] = true; }
-    HP_CUDA(launch_pdl<8>(k_moe_gemv_grouped<MODE, SB>, dim3(GEMV_NCTA), dim3(MOE_WARPS * 32), smem, s, a));
+    if (!attr[dev]) { HP_CUDA(cudaFuncSetAttribute(k_moe_gemv_grouped<MODE, SB, WARPS, DEPTH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr[dev] = true; }
+    HP_CUDA(launch_pdl<8>(k_moe_gemv_grouped<MODE, SB, WARPS, DEPTH>, dim3(GEMV_NCTA), dim3(WARPS * 32), smem, s, a));
     return HP_OK;
 }
+// few rows (units <= T * nslot * tiles / 4 stay below ~4 per SM): 4 warps x 6 stages; otherwise 12 warps x 2 stages
+template <int MODE, int SB>
+static int launch_grouped_geo(const MoeGArgs& a, bool few, cudaStream_t s) {
+    return few ? launch_grouped<MODE, SB, 4, 6>(a, s) : launch_grouped<MODE, SB, 12, 2>(a, s);
+}
 template <int MODE>
-static int launch_grouped_sb(const MoeGArgs& a, cudaStream_t s) {
-    return a.nb % 4 == 0 ? launch_grouped<MODE, 4>(a, s) : a.nb % 2 == 0 ? launch_grouped<MODE, 2>(a, s) : launch_grouped<MODE, 1>(a, s);
+static int launch_grouped_sb(const MoeGArgs& a, bool few, cudaStream_t s) {
+    return a.nb % 4 == 0 ? launch_grouped_geo<MODE, 4>(a, few, s) : a.nb % 2 == 0 ? launch_grouped_geo<MODE, 2>(a, few, s) : launch_grouped_geo<MODE, 1>(a, few, s);
 }
 int moe_experts_grouped(const MoeGroupParams& p, cudaStream_t s) {
     HP_REQUIRE(p.E % 256 == 0 && p.F % 256 == 0 && p.T >= 1 && p.nslot >= 1 && p.T * p.nslot <= MOE_MAX_PAIRS, "moe_experts_grouped: bad shape");
@@ -395,12 +409,13 @@ int moe_experts_grouped(const MoeGroupParams& p, cudaStream_t s) {
     a.w_exp = (const uint8_t*)p.w_gate_up; a.w_sh = (const uint8_t*)p.sh_gate_up; a.tiles = 2 * p.F / 16; a.nb = p.E / 256; a.ticket = 1;
     a.xq = (const uint8_t*)p.xq.q; a.xsc = (const float*)p.xq.sc; a.xK = p.E; a.xdiv = p.nslot;
     a.y = nullptr; a.N = 0; a.oq = (int8_t*)p.xq2.q; a.osc = (float*)p.xq2.sc; a.F = p.F;
-    { const int rc = launch_grouped_sb<0>(a, s); if (rc != HP_OK) return rc; }
+    const bool few = p.T <= 4;
+    { const int rc = launch_grouped_sb<0>(a, few, s); if (rc != HP_OK) return rc; }
     // down: [E rows][F]; per-pair outputs
     a.w_exp = (const uint8_t*)p.w_down; a.w_sh = (const uint8_t*)p.sh_down; a.tiles = p.E / 16; a.nb = p.F / 256; a.ticket = 2;
     a.xq = (const uint8_t*)p.xq2.q; a.xsc = (const float*)p.xq2.sc; a.xK = p.F; a.xdiv = 1;
     a.y = p.v; a.N = p.E; a.oq = nullptr; a.osc = nullptr;
-    { const int rc = launch_grouped_sb<1>(a, s); if (rc != HP_OK) return rc; }
+    { const int rc = launch_grouped_sb<1>(a, few, s); if (rc != HP_OK) return rc; }
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 int moe_combine(const float* v, const float* slotw, float* y, int T, int nslot, int E, cudaStream_t s) {
