@@ -1,4 +1,4 @@
-// spec_driver [preset] [n_gen] [n_draft] [prompt_len] [accept_rate_percent] : greedy generation with MTP speculative
+// spec_driver [preset] [n_gen] [n_draft] [prompt_len] [accept_rate_percent] [slots] : greedy generation with MTP speculative
 // decoding through the C ABI alone (this file includes include/hipster_b200.h and links libhipster_b200.so, nothing else).
 //
 // It plays the part of the reference's MTP driver (engine/bench/spec27b.cpp:34-110) for this library: the plain T = 1
@@ -8,6 +8,8 @@
 // exits 0 or 1. Weights are the library's seeded random-init tensors and the prompt is a seeded token sequence (no
 // checkpoint, no dataset). accept_rate_percent >= 0 replaces each draft of the fused rounds by the plain stream's own
 // next token with that probability and by a different token otherwise (seeded acceptance control); -1 keeps the drafts.
+// slots > 1 adds the multi-slot contract of engine/bench/batchfn.cpp:96-131: that many sequences with distinct prompts
+// advance in lock step through hp_spec_round over all slots, and each slot's stream must equal its solo run.
 #include "hipster_b200.h"
 #include <chrono>
 #include <cstdio>
@@ -22,10 +24,11 @@ struct Lcg { unsigned long long s; unsigned next() { s = s * 6364136223846793005
 int main(int argc, char** argv) {
     const char* preset = argc > 1 ? argv[1] : "tiny";
     const int n_gen = argc > 2 ? atoi(argv[2]) : 48, n_draft = argc > 3 ? atoi(argv[3]) : 3, n_prompt = argc > 4 ? atoi(argv[4]) : 21;
-    const int rate = argc > 5 ? atoi(argv[5]) : 70;
+    const int rate = argc > 5 ? atoi(argv[5]) : 70, n_slots = argc > 6 ? atoi(argv[6]) : 1;
     if (n_gen < 1 || n_draft < 1 || n_draft > 7 || n_prompt < 1) { fprintf(stderr, "usage: %s [preset] [n_gen] [n_draft 1..7] [prompt_len] [accept_rate_percent]\n", argv[0]); return 2; }
     hp_model_cfg cfg; CK(hp_model_preset(preset, &cfg));
-    cfg.n_slots = 1;
+    if (n_slots < 1 || n_slots > 8 || n_slots * (n_draft + 1) > 32) { fprintf(stderr, "slots must be 1..8 with slots * (n_draft + 1) <= 32\n"); return 2; }
+    cfg.n_slots = n_slots;
     if (n_prompt + n_gen + 3 * n_draft + 8 > cfg.max_ctx) { fprintf(stderr, "prompt + generation exceed max_ctx %d\n", cfg.max_ctx); return 2; }
     hp_engine* m = nullptr; CK(hp_load(&cfg, &m));
     const int E = cfg.n_embd;
@@ -105,6 +108,38 @@ int main(int argc, char** argv) {
         }
         printf("%s %s: %d/%d tokens identical to plain greedy\n", match == n_gen ? "EXACT" : "MISMATCH", pass ? "(fused round)" : "(host loop)", match, n_gen);
         bad |= match != n_gen;
+    }
+    // ---- S slots in lock step vs each slot alone (the drafts are the MTP block's own: no substitution)
+    if (n_slots > 1) {
+        const int S = n_slots, rounds = (n_gen + n_draft) / (n_draft + 1);
+        std::vector<std::vector<int>> prompts(S), lock(S), solo(S);
+        for (int s = 0; s < S; ++s) { Lcg pr{5000ull + (unsigned)s}; prompts[s].resize(n_prompt - (s % 3)); for (int& t : prompts[s]) t = (int)(pr.next() % (unsigned)cfg.n_vocab); }
+        auto begin = [&](int s) -> int {
+            if (hp_prefill(m, s, prompts[s].data(), (int)prompts[s].size(), 0, 1)) return 1;
+            if (hp_topk(m, 0, 1, 1, ids, vals)) return 1;
+            return hp_spec_begin(m, s, ids[0], (int)prompts[s].size(), hp_h_nextn_dev(m));
+        };
+        CK(hp_reset(m));
+        std::vector<int> slots(S), out(S * (n_draft + 1)), cnt(S);
+        for (int s = 0; s < S; ++s) { slots[s] = s; CK(begin(s)); }
+        const double t0 = now_ms(); size_t total = 0;
+        for (int r = 0; r < rounds; ++r) {
+            CK(hp_spec_round(m, slots.data(), S, n_draft, nullptr, out.data(), cnt.data()));
+            for (int s = 0; s < S; ++s) { lock[s].insert(lock[s].end(), out.begin() + s * (n_draft + 1), out.begin() + s * (n_draft + 1) + cnt[s]); total += cnt[s]; }
+        }
+        const double dt = now_ms() - t0;
+        printf("mtp n=%d, %d slots in lock step: %zu tokens in %.1f ms = %.1f t/s aggregate\n", n_draft, S, total, dt, total * 1000.0 / dt);
+        int same = 0;
+        for (int s = 0; s < S; ++s) {
+            CK(hp_reset(m)); CK(begin(s));
+            for (int r = 0; r < rounds; ++r) {
+                int c1 = 0; CK(hp_spec_round(m, &s, 1, n_draft, nullptr, out.data(), &c1));
+                solo[s].insert(solo[s].end(), out.begin(), out.begin() + c1);
+            }
+            same += solo[s] == lock[s];
+        }
+        printf("%s (slots): %d/%d slot streams identical to their solo runs\n", same == S ? "EXACT" : "MISMATCH", same, S);
+        bad |= same != S;
     }
     hp_free(m);
     return bad ? 1 : 0;

@@ -121,10 +121,10 @@ def test_expert_parallel_shard_refuses_to_run_without_its_communicator():
 def test_cpp_driver_through_the_c_abi_reports_exact():
     """spec_driver.cpp (the reference's spec27b.cpp:59-110 loop for this library) links only libhipster_b200.so."""
     exe = hb_build.build_driver()
-    for args in (["tiny", "40", "3", "21", "70"], ["tiny", "24", "5", "9", "-1"]):
+    for args, n_exact in ((["tiny", "40", "3", "21", "70"], 2), (["tiny", "24", "5", "9", "-1"], 2), (["tiny-moe", "18", "2", "11", "70", "4"], 3)):
         r = subprocess.run([exe] + args, capture_output=True, text=True, timeout=600)
         assert r.returncode == 0, r.stdout + r.stderr
-        assert r.stdout.count("EXACT") == 2 and "MISMATCH" not in r.stdout, r.stdout
+        assert r.stdout.count("EXACT") == n_exact and "MISMATCH" not in r.stdout, r.stdout
     deps = subprocess.run(["ldd", exe], capture_output=True, text=True).stdout
     assert "libhipster_b200.so" in deps and "libcudart" not in deps and "libtorch" not in deps
 

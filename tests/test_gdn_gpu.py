@@ -130,3 +130,28 @@ def test_commit_only_call_and_sigmoid_gate():
     oo, _ = orc.gdn_rows(Ly.rows[:3], NQK, NV, Ly.conv_w, Ly.dt, Ly.an, Ly.nw, st, hist, Ly.eps, 1)
     assert np.array_equal(bits(d["state"].cpu().numpy()), bits(st))
     assert np.array_equal(bits(out.cpu().numpy()[:3]), bits(oo))
+
+
+@pytest.mark.parametrize("gate", [0, 1])
+def test_kernel_within_1e5_of_the_double_precision_transcription(gate):
+    """The stated tolerance of configuration 2 against a checker that owes nothing to this build's kernels: the reference's
+    conv + step source (engine/kernels/ops.hip:188-256) evaluated in double precision. Outputs of the 6 rows, every
+    per-row state snapshot and the committed state agree within 1e-5 of the largest magnitude."""
+    lay = Layer(seed=5, sigmoid_gate=gate)
+    d = lay.dev()
+    out = torch.zeros((6, NV * D), dtype=torch.float32, device="cuda")
+    snap = torch.zeros((6, NV, D, D), dtype=torch.float32, device="cuda")
+    lay.call(d, d["rows"], 6, 0, out=out, snap=snap)
+    lay.call(d, None, 0, 6)                                   # commit all six rows
+    st64 = lay.state0.astype(np.float64); hist64 = lay.hist0.astype(np.float64)
+    snaps64 = []
+    outs64 = []
+    for r in range(6):
+        outs64.append(orc.ref64_gdn_rows(lay.rows[r:r + 1], NQK, NV, lay.conv_w.reshape(-1), bf16_to_f32(lay.dt), bf16_to_f32(lay.an), bf16_to_f32(lay.nw),
+                                         st64, hist64, lay.eps, gate)[0])
+        snaps64.append(st64.copy())
+    out64 = np.stack(outs64); snap64 = np.stack(snaps64)
+    o = out.cpu().numpy().astype(np.float64); sn = snap.cpu().numpy().astype(np.float64); st = d["state"].cpu().numpy().astype(np.float64)
+    assert np.abs(o - out64).max() <= 1e-5 * np.abs(out64).max()
+    assert np.abs(sn - snap64).max() <= 1e-5 * np.abs(snap64).max()
+    assert np.abs(st - st64).max() <= 1e-5 * np.abs(st64).max()
