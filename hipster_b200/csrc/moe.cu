@@ -16,8 +16,8 @@ namespace {
 // ---- router + routing + grouping in ONE launch ------------------------------------------------------------------------
 // Phase 1, router (exact f32; reference k_f32_gemv, fn.hip:252-266): per (weight row n, pass row t) lane l takes
 // k = 4l + 128 i as float4, four fmaf per step in element order, then the xor-shuffle tree 16..1; a warp computes two
-// weight rows against eight pass rows at once. Phase 2, in the CTA that finishes last (ticket counter), routing (k_moe_route,
-// fn.hip:167-205), one warp per row: softmax over the first E logits (sum: xor tree inside each group of 32 experts, the
+// weight rows against four pass rows at once. Phase 2, in the CTA that finishes last (ticket counter), routing (k_moe_route,
+// fn.hip:167-205), two warps per row: softmax over the first E logits (sum: xor tree inside each group of 32 experts, the
 // group sums added in group order), top-k by (value desc, index asc), weights renormalised by the sum of the selected
 // probabilities taken in rank order; slot k = shared expert, id -1, weight sigmoid(logit[E]). Phase 3, same CTA: the
 // (row, slot) pairs are grouped by expert into segments of up to 8 pairs (see below).
@@ -26,29 +26,36 @@ namespace {
 // nearly the same vector, so a linear router would send all rows to the same experts); the shared expert's gate keeps its logit.
 struct MoeSeg { int expert, ncols, cols[8]; int pad[6]; };   // 64 bytes; cols = pair indices t * nslot + e
 __device__ __forceinline__ void better(float& bv, int& bi, float v, int i) { if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; } }
+__device__ __forceinline__ void row_barrier(int row) { asm volatile("bar.sync %0, 64;" ::"r"(row + 1) : "memory"); }   // the two warps of a row
 struct RouteArgs {
     const float* W; const float* x; float* y; int N, K, T;       // router [N = E + 1][K], rows x [T][K], logits y [T][N]
     int* ids; float* w; int E, k;                                 // outputs [T][k + 1]
     int* ticket;                                                  // five zero-initialised ints (left zero)
     const int* row_tok; const int* row_pos; const int* row_slot; unsigned long long synth_key;
     int e_lo, e_hi, own_shared; MoeSeg* segs; int* ctl; unsigned long long* touched;   // grouping (segs == nullptr: skipped)
-    int stage_w; int* err;                                        // router rows staged in shared memory; status word for the bounded wait
+    int stage_w, stage_x; int* err;                               // router rows / pass rows staged in shared memory; status word for the bounded waits
 };
 constexpr int RG_THREADS = 512;
+constexpr int RG_ROUTE_SMEM = 8 * 1024 * 4;   // routing scratch: the probabilities of 8 rows x up to 1024 experts
 __global__ void __launch_bounds__(RG_THREADS) k_route_group(RouteArgs a) {
     pdl_launch_dependents();
-    __shared__ int sid[MOE_MAX_PAIRS]; __shared__ int scnt[1026]; __shared__ int soff[1026]; __shared__ int swt[RG_THREADS / 32]; __shared__ int s_last;
-    __shared__ __align__(8) unsigned long long wbar;
-    extern __shared__ __align__(128) uint8_t rg_smem[];   // the CTA's 16 router rows [16][K] f32 (when they fit: a.stage_w)
+    __shared__ int scnt[1026]; __shared__ int soff[1026]; __shared__ int swt[RG_THREADS / 32]; __shared__ int s_last;
+    __shared__ __align__(8) unsigned long long wbar, xbar;
+    __shared__ float s_max[8][2], s_gsum[8][32], s_sel[8][16]; __shared__ uint32_t s_ck[8][32]; __shared__ int s_ci[8][32];
+    // dynamic shared memory: the CTA's 16 router rows [16][K] f32 (a.stage_w), then its 8 pass rows [8][K] f32 (a.stage_x);
+    // the routing phase reuses the front of it
+    extern __shared__ __align__(128) uint8_t rg_smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // Router GEMV: CTA (bx, by) covers weight rows 16 bx .. 16 bx + 15 for pass rows 8 by .. 8 by + 7; its first 8 warps
-    // take two weight rows each. Spreading the 2 N T K fmaf over ~100 CTAs keeps the load pipes of any one SM out of
-    // the critical path. The 16 weight rows do not depend on the previous kernel: they are fetched by bulk async copies
-    // before the dependency wait, all at once, instead of one dependent DRAM round trip per 128 columns.
+    // Router GEMV: CTA (bx, by) covers weight rows 16 bx .. 16 bx + 15 for pass rows 8 by .. 8 by + 7; warp w takes the
+    // weight rows 2 (w & 7), +1 against the pass rows 4 (w >> 3) .. +3. Spreading the 2 N T K fmaf over ~100 CTAs keeps
+    // the load pipes of any one SM out of the critical path. The 16 weight rows do not depend on the previous kernel:
+    // they are fetched by bulk async copies before the dependency wait; the pass rows by bulk copies right after it,
+    // all at once, instead of one dependent L2 round trip per 128 columns.
     const float* wsm = reinterpret_cast<const float*>(rg_smem);
-    const uint32_t wb = smem_u32(&wbar);
+    const float* xsm = reinterpret_cast<const float*>(rg_smem + (size_t)16 * a.K * 4);
+    const uint32_t wb = smem_u32(&wbar), xb = smem_u32(&xbar);
     if (a.stage_w) {
-        if (tid == 0) { mbar_init(wb, 1); fence_barrier_init(); }
+        if (tid == 0) { mbar_init(wb, 1); mbar_init(xb, 1); fence_barrier_init(); }
         __syncthreads();
         if (warp == 0) {
             const int nrow = min(16, a.N - (int)blockIdx.x * 16);
@@ -58,31 +65,43 @@ __global__ void __launch_bounds__(RG_THREADS) k_route_group(RouteArgs a) {
         }
     }
     pdl_wait();
-    bool ok = true;
-    if (warp < 8) {
-        const int n0 = blockIdx.x * 16 + 2 * warp, t0 = blockIdx.y * 8;
+    if (a.stage_x && warp == 0) {
+        const int nrow = min(8, a.T - (int)blockIdx.y * 8);
+        if (lane == 0) mbar_expect_tx(xb, (uint32_t)nrow * (uint32_t)a.K * 4u);
+        __syncwarp();
+        if (lane < nrow) bulk_g2s(smem_u32(xsm + (size_t)lane * a.K), a.x + (size_t)(blockIdx.y * 8 + lane) * a.K, (uint32_t)a.K * 4u, xb);
+    }
+    // the routing phase's row key does not depend on the logits: fetched here, under the copies of the pass rows
+    const int row = warp >> 1, sub = warp & 1, t = blockIdx.y * 8 + row;   // routing: two warps per row, half of the expert groups each
+    unsigned long long base = 0ull;   // synthetic logits: rnd64(key + slot, (token, position), expert) = splitmix64(base + expert)
+    if (a.synth_key && t < a.T) base = splitmix64((a.synth_key + (unsigned long long)a.row_slot[t]) ^ ((((unsigned long long)(unsigned)a.row_tok[t] << 32) | (unsigned)a.row_pos[t]) * 0x9E3779B97F4A7C15ull));
+    {
+        const int n0 = blockIdx.x * 16 + 2 * (warp & 7), q0 = 4 * (warp >> 3), t0 = blockIdx.y * 8 + q0;
         const bool live0 = n0 < a.N, live1 = n0 + 1 < a.N;
+        bool ok = true;
         const float* wr0; const float* wr1;
-        if (a.stage_w) { ok = mbar_wait(wb, 0, a.err); wr0 = wsm + (size_t)(2 * warp) * a.K; wr1 = wsm + (size_t)(live1 ? 2 * warp + 1 : 2 * warp) * a.K; }
+        if (a.stage_w) { ok = mbar_wait(wb, 0, a.err); wr0 = wsm + (size_t)(2 * (warp & 7)) * a.K; wr1 = wsm + (size_t)(live1 ? 2 * (warp & 7) + 1 : 2 * (warp & 7)) * a.K; }
         else { wr0 = a.W + (size_t)(live0 ? n0 : 0) * a.K; wr1 = a.W + (size_t)(live1 ? n0 + 1 : 0) * a.K; }
-        float acc0[8], acc1[8];
+        if (a.stage_x) ok = mbar_wait(xb, 0, a.err) && ok;
+        const float* xr = a.stage_x ? xsm + (size_t)q0 * a.K : a.x + (size_t)t0 * a.K;
+        float acc0[4], acc1[4];
 #pragma unroll
-        for (int q = 0; q < 8; ++q) { acc0[q] = 0.f; acc1[q] = 0.f; }
-        if (ok && live0) {
+        for (int q = 0; q < 4; ++q) { acc0[q] = 0.f; acc1[q] = 0.f; }
+        if (ok && live0 && t0 < a.T) {
 #pragma unroll 2
             for (int i = lane * 4; i < a.K; i += 128) {
                 const float4 w0 = *reinterpret_cast<const float4*>(wr0 + i), w1 = *reinterpret_cast<const float4*>(wr1 + i);
 #pragma unroll
-                for (int q = 0; q < 8; ++q)
+                for (int q = 0; q < 4; ++q)
                     if (t0 + q < a.T) {
-                        const float4 xv = *reinterpret_cast<const float4*>(a.x + (size_t)(t0 + q) * a.K + i);
+                        const float4 xv = *reinterpret_cast<const float4*>(xr + (size_t)q * a.K + i);
                         acc0[q] = fmaf(w0.x, xv.x, acc0[q]); acc0[q] = fmaf(w0.y, xv.y, acc0[q]); acc0[q] = fmaf(w0.z, xv.z, acc0[q]); acc0[q] = fmaf(w0.w, xv.w, acc0[q]);
                         acc1[q] = fmaf(w1.x, xv.x, acc1[q]); acc1[q] = fmaf(w1.y, xv.y, acc1[q]); acc1[q] = fmaf(w1.z, xv.z, acc1[q]); acc1[q] = fmaf(w1.w, xv.w, acc1[q]);
                     }
             }
         }
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
+        for (int q = 0; q < 4; ++q) {
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) { acc0[q] = acc0[q] + __shfl_xor_sync(0xffffffffu, acc0[q], off); acc1[q] = acc1[q] + __shfl_xor_sync(0xffffffffu, acc1[q], off); }
             if (lane == 0 && t0 + q < a.T) {
@@ -92,7 +111,9 @@ __global__ void __launch_bounds__(RG_THREADS) k_route_group(RouteArgs a) {
         }
     }
     // ---- routing of the 8 rows of group `by`, by the CTA that completes their logits last (ticket per group), so that
-    // the groups are routed on different SMs at the same time: warp w routes row 8 by + w
+    // the groups are routed on different SMs at the same time: warps 2 r and 2 r + 1 route row 8 by + r. This code runs once per
+    // launch on an SM that has not executed it before, so it is written for a small instruction footprint (rolled loops
+    // over values kept in shared memory): unrolled over 32 register values it was bound by instruction fetch.
     __threadfence();
     __syncthreads();
     if (tid == 0) s_last = atomicAdd(a.ticket + blockIdx.y, 1) == (int)gridDim.x - 1;
@@ -100,46 +121,80 @@ __global__ void __launch_bounds__(RG_THREADS) k_route_group(RouteArgs a) {
     if (!s_last) return;
     __threadfence();
     const int ns = a.k + 1;
-    if (warp < 8 && (int)blockIdx.y * 8 + warp < a.T) {
-        const int t = blockIdx.y * 8 + warp;
+    if (t < a.T) {
         const float* lg = a.y + (size_t)t * a.N;
-        // synthetic logits: rnd64(key + slot, (token, position), expert) = splitmix64(base + expert)
-        const unsigned long long base = a.synth_key ? splitmix64((a.synth_key + (unsigned long long)a.row_slot[t]) ^ ((((unsigned long long)(unsigned)a.row_tok[t] << 32) | (unsigned)a.row_pos[t]) * 0x9E3779B97F4A7C15ull)) : 0ull;
-        float v[32]; float mx = -INFINITY;
-#pragma unroll
-        for (int q = 0; q < 32; ++q) {
+        const float shared_logit = __ldcg(lg + a.E);
+        float* sv = reinterpret_cast<float*>(rg_smem) + row * 1024;   // lane l owns the entries l + 32 q of its warp's groups
+        uint32_t* sk = reinterpret_cast<uint32_t*>(sv);
+        const int nq = (a.E + 31) >> 5, hq = (nq + 1) >> 1, qa = sub * hq, qb = min(nq, qa + hq);
+        float mx = -INFINITY;
+#pragma unroll 4
+        for (int q = qa; q < qb; ++q) {
             const int i = 32 * q + lane;
-            v[q] = i < a.E ? (a.synth_key ? irwin(splitmix64(base + (uint64_t)i)) : __ldcg(lg + i)) : -INFINITY;
-            mx = fmaxf(mx, v[q]);
+            const float val = i < a.E ? (a.synth_key ? irwin(splitmix64(base + (uint64_t)i)) : __ldcg(lg + i)) : -INFINITY;
+            sv[i] = val; mx = fmaxf(mx, val);
         }
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-        float sum = 0.f;
-#pragma unroll
-        for (int q = 0; q < 32; ++q) {
+        if (lane == 0) s_max[row][sub] = mx;
+        row_barrier(row);
+        mx = fmaxf(s_max[row][0], s_max[row][1]);
+        // softmax denominator: xor tree inside each group of 32 experts, the group sums added in group order
+#pragma unroll 4
+        for (int q = qa; q < qb; ++q) {
             const int i = 32 * q + lane;
-            v[q] = i < a.E ? expf_det(v[q] - mx) : 0.f;
-            float sg = v[q];
+            const float pr = i < a.E ? expf_det(sv[i] - mx) : 0.f;
+            sv[i] = pr;
+            float sg = pr;
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) sg = sg + __shfl_xor_sync(0xffffffffu, sg, off);
-            sum = q == 0 ? sg : sum + sg;
+            if (lane == 0) s_gsum[row][q] = sg;
         }
-#pragma unroll
-        for (int q = 0; q < 32; ++q) v[q] = 32 * q + lane < a.E ? v[q] / sum : -2.f;
-        float wsum = 0.f; float selp = 0.f; int seli = 0;   // lane r keeps the r-th winner
+        row_barrier(row);
+        float sum = s_gsum[row][0];
+        for (int q = 1; q < nq; ++q) sum = sum + s_gsum[row][q];
+        // Selection keys: a probability is a non-negative float, so its bit pattern orders like an unsigned integer;
+        // key = bits + 1, 0 = no entry (padding, or already taken). The warp's own k best by (key desc, index asc): one
+        // integer max and one integer min across the warp per winner; every global winner is among the 2 k candidates.
+        uint32_t lk = 0u; int li = 0x7fffffff;
+#pragma unroll 4
+        for (int q = qa; q < qb; ++q) {
+            const int i = 32 * q + lane;
+            const uint32_t key = i < a.E ? __float_as_uint(sv[i] / sum) + 1u : 0u;
+            sk[i] = key;
+            if (key > lk) { lk = key; li = i; }
+        }
+        uint32_t myk = 0u; int myi = 0x7fffffff;
         for (int r = 0; r < a.k; ++r) {
-            float bv = v[0]; int bi = lane;
-#pragma unroll
-            for (int q = 1; q < 32; ++q) better(bv, bi, v[q], lane + 32 * q);
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) { const float ov = __shfl_xor_sync(0xffffffffu, bv, off); const int oi = __shfl_xor_sync(0xffffffffu, bi, off); better(bv, bi, ov, oi); }
-            if (lane == r) { selp = bv; seli = bi; }
-            wsum = wsum + bv;
-#pragma unroll
-            for (int q = 0; q < 32; ++q) if (bi == lane + 32 * q) v[q] = -1.f;
+            const uint32_t m = __reduce_max_sync(0xffffffffu, lk);
+            const int wi = (int)__reduce_min_sync(0xffffffffu, lk == m ? (uint32_t)li : 0x7fffffffu);
+            if (lane == r) { myk = m; myi = wi; }
+            if (m != 0u && (wi & 31) == lane) {   // the owner retires the entry and looks for its next best
+                sk[wi] = 0u; lk = 0u; li = 0x7fffffff;
+#pragma unroll 4
+                for (int q = qa; q < qb; ++q) { const uint32_t key = sk[32 * q + lane]; if (key > lk) { lk = key; li = 32 * q + lane; } }
+            }
         }
-        if (lane < a.k) { a.ids[t * ns + lane] = seli; a.w[t * ns + lane] = selp / wsum; }
-        if (lane == 0) { a.ids[t * ns + a.k] = -1; a.w[t * ns + a.k] = sigmoid_det(__ldcg(lg + a.E)); }
+        if (lane < a.k) { s_ck[row][16 * sub + lane] = myk; s_ci[row][16 * sub + lane] = myi; }
+        row_barrier(row);
+        if (sub == 0) {
+            // merge by rank: candidate c is the winner number (count of candidates that beat it)
+            const bool valid = lane < 2 * a.k;
+            const int slot = lane < a.k ? lane : 16 + lane - a.k;
+            const uint32_t ck = valid ? s_ck[row][slot] : 0u; const int ci = valid ? s_ci[row][slot] : 0x7fffffff;
+            int rank = 0;
+            for (int j = 0; j < 2 * a.k; ++j) {
+                const int sj = j < a.k ? j : 16 + j - a.k;
+                const uint32_t kj = s_ck[row][sj]; const int ij = s_ci[row][sj];
+                rank += (kj > ck || (kj == ck && ij < ci)) ? 1 : 0;
+            }
+            if (ck != 0u && rank < a.k) { a.ids[t * ns + rank] = ci; s_sel[row][rank] = __uint_as_float(ck - 1u); }
+            __syncwarp();
+            float wsum = s_sel[row][0];   // the selected probabilities added in rank order
+            for (int r = 1; r < a.k; ++r) wsum = wsum + s_sel[row][r];
+            if (lane < a.k) a.w[t * ns + lane] = s_sel[row][lane] / wsum;
+            if (lane == 0) { a.ids[t * ns + a.k] = -1; a.w[t * ns + a.k] = sigmoid_det(shared_logit); }
+        }
     }
     if (tid == 0) a.ticket[blockIdx.y] = 0;   // ready for the next launch
     if (!a.segs) return;
@@ -152,23 +207,25 @@ __global__ void __launch_bounds__(RG_THREADS) k_route_group(RouteArgs a) {
     if (!s_last) return;
     __threadfence();
     const int nown = a.e_hi - a.e_lo, nb = nown + (a.own_shared ? 1 : 0), np = a.T * ns;
-    for (int i = tid; i < np; i += RG_THREADS) sid[i] = __ldcg(a.ids + i);
+    // scnt[b] = bit mask of the rows that picked bucket b (a row picks an expert at most once, T <= 32): a pair's place in
+    // its bucket is the number of lower rows in the mask
     for (int b = tid; b < 1026; b += RG_THREADS) scnt[b] = 0;
     __syncthreads();
     int my_b = -1, my_rank = 0, my_id = 0;
     if (tid < np) {
-        my_id = sid[tid];
+        my_id = __ldcg(a.ids + tid);
         my_b = my_id >= 0 ? ((my_id >= a.e_lo && my_id < a.e_hi) ? my_id - a.e_lo : -1) : (a.own_shared ? nown : -1);
-        if (my_b >= 0) { for (int j = 0; j < tid; ++j) my_rank += sid[j] == my_id; atomicMax(&scnt[my_b], my_rank + 1); }
+        if (my_b >= 0) atomicOr(reinterpret_cast<unsigned*>(&scnt[my_b]), 1u << (tid / ns));
     }
     __syncthreads();
+    if (my_b >= 0) my_rank = __popc((unsigned)scnt[my_b] & ((1u << (tid / ns)) - 1u));
     {   // exclusive scan of the segments per bucket: thread = buckets 2 tid and 2 tid + 1 (0..1023), bucket 1024 appended
-        const int b0 = 2 * tid, c0 = b0 < nb ? (scnt[b0] + 7) >> 3 : 0, c1 = b0 + 1 < nb ? (scnt[b0 + 1] + 7) >> 3 : 0;
+        const int b0 = 2 * tid, c0 = b0 < nb ? (__popc((unsigned)scnt[b0]) + 7) >> 3 : 0, c1 = b0 + 1 < nb ? (__popc((unsigned)scnt[b0 + 1]) + 7) >> 3 : 0;
         int inc = c0 + c1;
 #pragma unroll
         for (int off = 1; off < 32; off <<= 1) { const int o = __shfl_up_sync(0xffffffffu, inc, off); if (lane >= off) inc += o; }
         if (lane == 31) swt[warp] = inc;
-        const int ntouch = __syncthreads_count(b0 < nb && scnt[b0] > 0) + __syncthreads_count(b0 + 1 < nb && scnt[b0 + 1] > 0);
+        const int ntouch = __syncthreads_count(b0 < nb && scnt[b0] != 0) + __syncthreads_count(b0 + 1 < nb && scnt[b0 + 1] != 0);
         if (warp == 0) {
             int wv = lane < RG_THREADS / 32 ? swt[lane] : 0, winc = wv;
 #pragma unroll
@@ -181,9 +238,9 @@ __global__ void __launch_bounds__(RG_THREADS) k_route_group(RouteArgs a) {
         if (tid == RG_THREADS - 1) {
             const int tot1024 = ex + c0 + c1;
             soff[1024] = tot1024;
-            const int c2 = nb > 1024 ? (scnt[1024] + 7) >> 3 : 0;
+            const int c2 = nb > 1024 ? (__popc((unsigned)scnt[1024]) + 7) >> 3 : 0;
             a.ctl[0] = tot1024 + c2; a.ctl[1] = 0; a.ctl[2] = 0;   // segments, ticket counters of the two GEMVs
-            if (a.touched) atomicAdd(a.touched, (unsigned long long)(ntouch + (nb > 1024 && scnt[1024] > 0 ? 1 : 0)));
+            if (a.touched) atomicAdd(a.touched, (unsigned long long)(ntouch + (nb > 1024 && scnt[1024] != 0 ? 1 : 0)));
             a.ticket[4] = 0;
         }
     }
@@ -192,7 +249,7 @@ __global__ void __launch_bounds__(RG_THREADS) k_route_group(RouteArgs a) {
         MoeSeg* sg = a.segs + soff[my_b] + (my_rank >> 3); const int c = my_rank & 7;
         sg->cols[c] = tid;
         if (c == 0) sg->expert = my_id;
-        if (c == 7 || my_rank == scnt[my_b] - 1) sg->ncols = c + 1;
+        if (c == 7 || my_rank == __popc((unsigned)scnt[my_b]) - 1) sg->ncols = c + 1;
     }
 }
 
@@ -370,10 +427,13 @@ int moe_route_group(const MoeRouteParams& p, cudaStream_t s) {
     RouteArgs a; a.W = p.W; a.x = p.x; a.y = p.logits; a.N = p.E + 1; a.K = p.K; a.T = p.T; a.ids = p.ids; a.w = p.w; a.E = p.E; a.k = p.k; a.ticket = p.ticket;
     a.row_tok = p.row_tok; a.row_pos = p.row_pos; a.row_slot = p.row_slot; a.synth_key = p.synth_key;
     a.e_lo = p.e_lo; a.e_hi = p.e_hi; a.own_shared = p.own_shared; a.segs = (MoeSeg*)p.segs; a.ctl = p.ctl; a.touched = p.touched;
-    // the CTA's 16 router rows are staged in shared memory when they fit (K <= 3072 floats per row)
-    const size_t wbytes = (size_t)16 * a.K * 4;
-    a.stage_w = wbytes <= 192 * 1024 && a.K % 4 == 0 && ((uintptr_t)a.W & 15) == 0 ? 1 : 0; a.err = p.err;
-    const size_t smem = a.stage_w ? wbytes : 0;
+    // the CTA's 16 router rows are staged in shared memory when they fit (K <= 3072 floats per row), its 8 pass rows too
+    // when both fit (K <= 2176); the routing phase needs RG_ROUTE_SMEM bytes of the same buffer
+    const size_t wbytes = (size_t)16 * a.K * 4, xbytes = (size_t)8 * a.K * 4;
+    a.stage_w = wbytes <= 192 * 1024 && ((uintptr_t)a.W & 15) == 0 ? 1 : 0;
+    a.stage_x = a.stage_w && wbytes + xbytes <= 204 * 1024 && ((uintptr_t)a.x & 15) == 0 ? 1 : 0; a.err = p.err;
+    size_t smem = a.stage_w ? wbytes + (a.stage_x ? xbytes : 0) : 0;
+    if (smem < (size_t)RG_ROUTE_SMEM) smem = RG_ROUTE_SMEM;
     if (smem > 48 * 1024) {
         static size_t attr[MAX_DEVICES] = {};
         const int dev = current_device(); if (dev < 0) return HP_ECUDA;
