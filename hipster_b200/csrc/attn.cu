@@ -88,13 +88,16 @@ struct AttnArgs {
     const int* groups;        // device: per group {r0, T, slot, pos0}
     float* pO; float* pm; float* pl; int nsplit_max;   // partials [group][kv head][split][MAXP] (x 256 for pO)
 };
-// grid (nsplit_max, n_kv, ngroups), 256 threads, dynamic smem. PPT = (row, head) pairs per thread in the score phase
-// (warp w takes pairs w*PPT .. w*PPT+PPT-1): 6 covers the 48 pairs of a full verify group, 1 the <= 8 pairs of a
-// single-row pass, where the wider tile would spend seven warps on absent pairs. Every score and every output element
-// is the same fmaf chain whatever PPT is.
-template <int PPT>
-__global__ void __launch_bounds__(256) k_attn_split(AttnArgs a) {
-    constexpr int NP = 8 * PPT;   // pairs this instantiation can hold
+// grid (nsplit_max, n_kv, ngroups), NT threads, dynamic smem. PPT = (row, head) pairs per thread in the score phase
+// (warp w takes pairs w*PPT .. w*PPT+PPT-1): 16 warps x 3 cover the 48 pairs of a full verify group, 8 warps x 1 the
+// <= 8 pairs of a single-row pass, where the wider tile would spend most warps on absent pairs. The kernel is bound by
+// the latency of its fp32 chains at one CTA per SM, so the verify form spreads them over 16 warps. Every score and
+// every output element is the same fmaf chain whatever the geometry is.
+template <int PPT, int NT>
+__global__ void __launch_bounds__(NT) k_attn_split(AttnArgs a) {
+    constexpr int NW = NT / 32, NP = NW * PPT;   // pairs this instantiation can hold
+    constexpr int PARTS = NT / HD, PP = NP / PARTS;   // P.V phase: thread = (dim, part of the pairs)
+    static_assert(NT % HD == 0 && PP % 4 == 0 && NP <= MAXP, "attention tile geometry");
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(16) uint8_t sm_raw[];
@@ -110,13 +113,13 @@ __global__ void __launch_bounds__(256) k_attn_split(AttnArgs a) {
     if (nkeys <= 0 || T <= 0) return;
     const size_t pbase = (((size_t)gi * a.n_kv + kh) * a.nsplit_max + split) * MAXP;
     // stage Q (pair = t*G + hh -> row r0+t, head kh*G + hh), K and V tiles
-    for (int i = tid; i < npairs * (HD / 4); i += 256) {
+    for (int i = tid; i < npairs * (HD / 4); i += NT) {
         const int p = i / (HD / 4), d4 = i % (HD / 4), tr = p / G, hh = p % G;
         reinterpret_cast<float4*>(sQ)[p * (HD / 4) + d4] = reinterpret_cast<const float4*>(a.qkv + (size_t)(r0 + tr) * a.ld + (kh * G + hh) * 512)[d4];
     }
     const uint16_t* Kg = a.kc + (size_t)slot * a.kv_stride + ((size_t)kh * a.max_ctx + k_lo) * HD;
     const uint16_t* Vg = a.vc + (size_t)slot * a.kv_stride + ((size_t)kh * a.max_ctx + k_lo) * HD;
-    for (int i = tid; i < nkeys * (HD / 8); i += 256) {
+    for (int i = tid; i < nkeys * (HD / 8); i += NT) {
         const int k = i / (HD / 8), c = i % (HD / 8);
         const uint4 kv = reinterpret_cast<const uint4*>(Kg + (size_t)k * HD)[c], vv = reinterpret_cast<const uint4*>(Vg + (size_t)k * HD)[c];
         uint2* dk = reinterpret_cast<uint2*>(sK + k * KSTRIDE + c * 8); dk[0] = make_uint2(kv.x, kv.y); dk[1] = make_uint2(kv.z, kv.w);
@@ -160,7 +163,7 @@ __global__ void __launch_bounds__(256) k_attn_split(AttnArgs a) {
     // sees keys <= pos0 + t. Maximum: exact in any order. Sum: the lane's keys in ascending order, then the xor tree (16..1).
     {
         const int warp = tid >> 5, lane = tid & 31;
-        for (int p = warp; p < npairs; p += 8) {
+        for (int p = warp; p < npairs; p += NW) {
             const int tr = p / G;
             const int nk = min(nkeys, pos0 + tr + 1 - k_lo);
             float sc[4]; float mx = -INFINITY;
@@ -182,25 +185,26 @@ __global__ void __launch_bounds__(256) k_attn_split(AttnArgs a) {
         }
     }
     __syncthreads();
-    // o[pair][d] = sum_k e[k][pair] * v[k][d], keys in position order; thread = dim d
+    // o[pair][d] = sum_k e[k][pair] * v[k][d], keys in position order; thread = (dim d, part of the pairs)
     {
-        float2 o[NP / 2];   // packed pairs of (row, head) accumulators: two fp32 fmaf per instruction, each rounded once
+        const int d = tid % HD, p_lo = (tid / HD) * PP;
+        float2 o[PP / 2];   // packed pairs of (row, head) accumulators: two fp32 fmaf per instruction, each rounded once
 #pragma unroll
-        for (int p = 0; p < NP / 2; ++p) o[p] = make_float2(0.f, 0.f);
+        for (int p = 0; p < PP / 2; ++p) o[p] = make_float2(0.f, 0.f);
         for (int k = 0; k < nkeys; ++k) {
-            const float v = h2f(sV[k * KSTRIDE + tid]);
+            const float v = h2f(sV[k * KSTRIDE + d]);
             const float2 vv = make_float2(v, v);
 #pragma unroll
-            for (int p4 = 0; p4 < NP / 4; ++p4) {
-                const float4 e = *reinterpret_cast<const float4*>(sE + k * MAXP + p4 * 4);
+            for (int p4 = 0; p4 < PP / 4; ++p4) {
+                const float4 e = *reinterpret_cast<const float4*>(sE + k * MAXP + p_lo + p4 * 4);
                 o[p4 * 2] = attn_fma2(make_float2(e.x, e.y), vv, o[p4 * 2]);
                 o[p4 * 2 + 1] = attn_fma2(make_float2(e.z, e.w), vv, o[p4 * 2 + 1]);
             }
         }
 #pragma unroll
-        for (int p = 0; p < NP / 2; ++p) {
-            if (2 * p < npairs) a.pO[(pbase + 2 * p) * HD + tid] = o[p].x;
-            if (2 * p + 1 < npairs) a.pO[(pbase + 2 * p + 1) * HD + tid] = o[p].y;
+        for (int p = 0; p < PP / 2; ++p) {
+            if (p_lo + 2 * p < npairs) a.pO[(pbase + p_lo + 2 * p) * HD + d] = o[p].x;
+            if (p_lo + 2 * p + 1 < npairs) a.pO[(pbase + p_lo + 2 * p + 1) * HD + d] = o[p].y;
         }
     }
 }
@@ -257,15 +261,15 @@ int attn_decode(const AttnParams& p, int rows, int ngroups, cudaStream_t s) {
     const int dev = current_device(); if (dev < 0) return HP_ECUDA;
     bool& attr = attr_dev[dev];
     if (!attr) {
-        HP_CUDA(cudaFuncSetAttribute(k_attn_split<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem_bytes()));
-        HP_CUDA(cudaFuncSetAttribute(k_attn_split<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem_bytes()));
+        HP_CUDA(cudaFuncSetAttribute(k_attn_split<3, 512>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem_bytes()));
+        HP_CUDA(cudaFuncSetAttribute(k_attn_split<1, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem_bytes()));
         attr = true;
     }
     AttnArgs a; a.qkv = p.qkv; a.ld = p.ld; a.n_head = p.n_head; a.n_kv = p.n_kv; a.kc = (const uint16_t*)p.kc; a.vc = (const uint16_t*)p.vc;
     a.kv_stride = p.kv_stride; a.max_ctx = p.max_ctx; a.groups = p.groups; a.pO = p.pO; a.pm = p.pm; a.pl = p.pl; a.nsplit_max = p.nsplit_max;
     // group sizes live on the device; `rows` bounds the rows of any group, so rows * G <= 8 selects the narrow score tile
-    if (rows * (p.n_head / p.n_kv) <= 8) HP_CUDA(launch_pdl<4>(k_attn_split<1>, dim3(p.nsplit_max, p.n_kv, ngroups), dim3(256), attn_smem_bytes(), s, a));
-    else HP_CUDA(launch_pdl<4>(k_attn_split<6>, dim3(p.nsplit_max, p.n_kv, ngroups), dim3(256), attn_smem_bytes(), s, a));
+    if (rows * (p.n_head / p.n_kv) <= 8) HP_CUDA(launch_pdl<4>(k_attn_split<1, 256>, dim3(p.nsplit_max, p.n_kv, ngroups), dim3(256), attn_smem_bytes(), s, a));
+    else HP_CUDA(launch_pdl<4>(k_attn_split<3, 512>, dim3(p.nsplit_max, p.n_kv, ngroups), dim3(512), attn_smem_bytes(), s, a));
     HP_CUDA(launch_pdl<4>(k_attn_merge, dim3(rows * p.n_head), dim3(256), 0, s, p.qkv, p.ld, p.n_head, p.n_kv, p.groups, p.row_group, p.pO, p.pm, p.pl, p.nsplit_max, p.out, (int8_t*)p.xq.q, (float*)p.xq.sc));
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }

@@ -30,6 +30,7 @@ namespace {
 
 constexpr int SK_STAGES = GEMV_STAGES;
 constexpr int SK_THREADS = GEMV_WARPS * 32;
+constexpr int SK_XG = 4;   // copy pairs per column tile of the activations; NT * SK_XG <= 32
 // Two weight layouts. Row-major ggml (TILED = false): a stage holds 16 row pieces of CB blocks, one bulk copy per row.
 // Tile-major (TILED = true, the engine repacks to it at load; same bytes, permuted): for every 16-row tile and block a
 // contiguous 2304-byte chunk = 16 headers (16 B each) + nibbles stored [j][lane][row g 8 B | row g+8 8 B], so a stage
@@ -100,15 +101,20 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
 
     pdl_wait();
 
-    if (warp == 0) {   // quantised activations of blocks [kb0, kb0 + nbp), all NT column tiles, by bulk copies: one block
-        // (2048 + 512 B) per copy pair, lanes in parallel, each CTA starting at a different block so that the 148 CTAs do
-        // not walk the same L2 lines in lockstep
+    if (warp == 0) {   // quantised activations of blocks [kb0, kb0 + nbp), all NT column tiles, by bulk copies. Per column
+        // tile the int8 fragments (2048 B per block) and the scales (512 B per block) of consecutive blocks are
+        // contiguous. Issuing a bulk copy costs ~45 ns (one copy pair per block took 1.8 us), so each column tile is
+        // fetched as SK_XG copy pairs over ranges of blocks, each CTA starting at a different range so that the 148 CTAs
+        // do not walk the same L2 lines in lockstep.
         if (lane == 0) mbar_expect_tx(xbar, (uint32_t)NT * nbp * 2560u);
         __syncwarp();
-        for (int i = lane; i < NT * nbp; i += 32) {
-            const int n = i / nbp, b = (i % nbp + blockIdx.x) % nbp;
-            bulk_g2s(smem_u32(smem + Geo::FIXED + (n * nbp + b) * 2048), xq + ((size_t)n * nb + kb0 + b) * 128, 2048u, xbar);
-            bulk_g2s(smem_u32(smem + Geo::FIXED + NT * nbp * 2048 + (n * nbp + b) * 512), xsc + ((size_t)n * nb + kb0 + b) * 32, 512u, xbar);
+        if (lane < NT * SK_XG) {
+            const int n = lane / SK_XG, gx = (lane % SK_XG + blockIdx.x) % SK_XG;
+            const int b0 = (gx * nbp) / SK_XG, b1 = ((gx + 1) * nbp) / SK_XG;
+            if (b1 > b0) {
+                bulk_g2s(smem_u32(smem + Geo::FIXED + (n * nbp + b0) * 2048), xq + ((size_t)n * nb + kb0 + b0) * 128, (uint32_t)(b1 - b0) * 2048u, xbar);
+                bulk_g2s(smem_u32(smem + Geo::FIXED + NT * nbp * 2048 + (n * nbp + b0) * 512), xsc + ((size_t)n * nb + kb0 + b0) * 32, (uint32_t)(b1 - b0) * 512u, xbar);
+            }
         }
     }
 
