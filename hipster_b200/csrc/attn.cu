@@ -19,6 +19,7 @@ namespace {
 
 constexpr int HD = 256, SPL = ATTN_SPLIT, MAXP = ATTN_MAX_PAIRS;   // pairs = rows of the group x q-heads per kv head
 constexpr int KSTRIDE = HD + 4;                                     // f16 elements per K/V tile row (520 B: conflict-free)
+constexpr int ESTR = MAXP + 4;                                      // floats per key row of the score tile: lanes = keys hit 8 banks (16-way conflicts at 48)
 
 template <int NW>
 __device__ __forceinline__ float block_sum_det(float v, float* sh) {
@@ -96,14 +97,14 @@ struct AttnArgs {
 template <int PPT, int NT>
 __global__ void __launch_bounds__(NT) k_attn_split(AttnArgs a) {
     constexpr int NW = NT / 32, NP = NW * PPT;   // pairs this instantiation can hold
-    constexpr int PARTS = NT / HD, PP = NP / PARTS;   // P.V phase: thread = (dim, part of the pairs)
-    static_assert(NT % HD == 0 && PP % 4 == 0 && NP <= MAXP, "attention tile geometry");
+    constexpr int PARTS = NT / (HD / 2), PP = NP / PARTS;   // P.V phase: thread = (two dims, part of the pairs)
+    static_assert(NT % (HD / 2) == 0 && PP % 4 == 0 && NP <= MAXP, "attention tile geometry");
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(16) uint8_t sm_raw[];
     float* sQ = reinterpret_cast<float*>(sm_raw);                                   // [MAXP][256]
-    float* sE = sQ + MAXP * HD;                                                     // [SPL][MAXP] scores, then weights
-    uint16_t* sK = reinterpret_cast<uint16_t*>(sE + SPL * MAXP);                    // [SPL][KSTRIDE]
+    float* sE = sQ + MAXP * HD;                                                     // [SPL][ESTR] scores, then weights
+    uint16_t* sK = reinterpret_cast<uint16_t*>(sE + SPL * ESTR);                    // [SPL][KSTRIDE]
     uint16_t* sV = sK + SPL * KSTRIDE;                                              // [SPL][KSTRIDE]
     const int split = blockIdx.x, kh = blockIdx.y, gi = blockIdx.z, tid = threadIdx.x;
     const int r0 = a.groups[gi * 4], T = a.groups[gi * 4 + 1], slot = a.groups[gi * 4 + 2], pos0 = a.groups[gi * 4 + 3];
@@ -156,7 +157,7 @@ __global__ void __launch_bounds__(NT) k_attn_split(AttnArgs a) {
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
-            for (int jx = 0; jx < PPT; ++jx) { const int p = pq * PPT + jx; if (p < MAXP) sE[(kq + 32 * i) * MAXP + p] = s[i][jx] * 0.0625f; }
+            for (int jx = 0; jx < PPT; ++jx) { const int p = pq * PPT + jx; if (p < MAXP) sE[(kq + 32 * i) * ESTR + p] = s[i][jx] * 0.0625f; }
     }
     __syncthreads();
     // softmax pieces per pair: warp w takes pairs w, w+8, ...; lane l takes keys l, l+32, l+64, l+96. Row t of the group
@@ -168,7 +169,7 @@ __global__ void __launch_bounds__(NT) k_attn_split(AttnArgs a) {
             const int nk = min(nkeys, pos0 + tr + 1 - k_lo);
             float sc[4]; float mx = -INFINITY;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) { const int k = lane + 32 * i; sc[i] = k < nk ? sE[k * MAXP + p] : -INFINITY; mx = fmaxf(mx, sc[i]); }
+            for (int i = 0; i < 4; ++i) { const int k = lane + 32 * i; sc[i] = k < nk ? sE[k * ESTR + p] : -INFINITY; mx = fmaxf(mx, sc[i]); }
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
             float l = 0.f;
@@ -176,7 +177,7 @@ __global__ void __launch_bounds__(NT) k_attn_split(AttnArgs a) {
             for (int i = 0; i < 4; ++i) {
                 const int k = lane + 32 * i;
                 const float e = k < nk ? expf_det(sc[i] - mx) : 0.f;
-                if (k < nkeys) sE[k * MAXP + p] = e;
+                if (k < nkeys) sE[k * ESTR + p] = e;
                 l = i == 0 ? e : l + e;
             }
 #pragma unroll
@@ -185,26 +186,30 @@ __global__ void __launch_bounds__(NT) k_attn_split(AttnArgs a) {
         }
     }
     __syncthreads();
-    // o[pair][d] = sum_k e[k][pair] * v[k][d], keys in position order; thread = (dim d, part of the pairs)
+    // o[pair][d] = sum_k e[k][pair] * v[k][d], keys in position order; thread = (dims 2 dq and 2 dq + 1, part of the pairs):
+    // a warp's read of four weights serves 64 dims, which halves the shared-memory traffic that bounds this phase
     {
-        const int d = tid % HD, p_lo = (tid / HD) * PP;
-        float2 o[PP / 2];   // packed pairs of (row, head) accumulators: two fp32 fmaf per instruction, each rounded once
+        const int dq = tid % (HD / 2), p_lo = (tid / (HD / 2)) * PP;
+        float2 o[PP / 2][2];   // [pairs 2 p, 2 p + 1][dim]: two fp32 fmaf per instruction, each rounded once
 #pragma unroll
-        for (int p = 0; p < PP / 2; ++p) o[p] = make_float2(0.f, 0.f);
+        for (int p = 0; p < PP / 2; ++p) { o[p][0] = make_float2(0.f, 0.f); o[p][1] = make_float2(0.f, 0.f); }
         for (int k = 0; k < nkeys; ++k) {
-            const float v = h2f(sV[k * KSTRIDE + d]);
-            const float2 vv = make_float2(v, v);
+            const uint32_t vh = *reinterpret_cast<const uint32_t*>(sV + k * KSTRIDE + 2 * dq);
+            const float v0 = h2f((uint16_t)(vh & 0xFFFF)), v1 = h2f((uint16_t)(vh >> 16));
+            const float2 vv0 = make_float2(v0, v0), vv1 = make_float2(v1, v1);
 #pragma unroll
             for (int p4 = 0; p4 < PP / 4; ++p4) {
-                const float4 e = *reinterpret_cast<const float4*>(sE + k * MAXP + p_lo + p4 * 4);
-                o[p4 * 2] = attn_fma2(make_float2(e.x, e.y), vv, o[p4 * 2]);
-                o[p4 * 2 + 1] = attn_fma2(make_float2(e.z, e.w), vv, o[p4 * 2 + 1]);
+                const float4 e = *reinterpret_cast<const float4*>(sE + k * ESTR + p_lo + p4 * 4);
+                o[p4 * 2][0] = attn_fma2(make_float2(e.x, e.y), vv0, o[p4 * 2][0]);
+                o[p4 * 2][1] = attn_fma2(make_float2(e.x, e.y), vv1, o[p4 * 2][1]);
+                o[p4 * 2 + 1][0] = attn_fma2(make_float2(e.z, e.w), vv0, o[p4 * 2 + 1][0]);
+                o[p4 * 2 + 1][1] = attn_fma2(make_float2(e.z, e.w), vv1, o[p4 * 2 + 1][1]);
             }
         }
 #pragma unroll
         for (int p = 0; p < PP / 2; ++p) {
-            if (p_lo + 2 * p < npairs) a.pO[(pbase + p_lo + 2 * p) * HD + d] = o[p].x;
-            if (p_lo + 2 * p + 1 < npairs) a.pO[(pbase + p_lo + 2 * p + 1) * HD + d] = o[p].y;
+            if (p_lo + 2 * p < npairs) *reinterpret_cast<float2*>(a.pO + (pbase + p_lo + 2 * p) * HD + 2 * dq) = make_float2(o[p][0].x, o[p][1].x);
+            if (p_lo + 2 * p + 1 < npairs) *reinterpret_cast<float2*>(a.pO + (pbase + p_lo + 2 * p + 1) * HD + 2 * dq) = make_float2(o[p][0].y, o[p][1].y);
         }
     }
 }
@@ -246,7 +251,7 @@ __global__ void k_attn_desc(int* __restrict__ d, int R, int pos0, int gr) {
 
 }  // namespace
 
-size_t attn_smem_bytes() { return (size_t)MAXP * HD * 4 + (size_t)SPL * MAXP * 4 + 2 * (size_t)SPL * KSTRIDE * 2; }
+size_t attn_smem_bytes() { return (size_t)MAXP * HD * 4 + (size_t)SPL * ESTR * 4 + 2 * (size_t)SPL * KSTRIDE * 2; }
 size_t attn_partial_floats(int ngroups, int n_kv, int nsplit_max) { return (size_t)ngroups * n_kv * nsplit_max * MAXP; }
 
 int attn_rope_kv(const AttnParams& p, int rows, cudaStream_t s) {

@@ -409,6 +409,178 @@ __global__ void __launch_bounds__(MOE_WARPS * 32, 1) k_moe_gemv_grouped(MoeGArgs
     }
 }
 
+// ---- the same GEMVs with the work cut by quads of warps ------------------------------------------------------------
+// A CTA is three quads of four warps. A quad owns a contiguous range of work units (segment, 4 tiles), i.e. mostly one
+// or two segments: it gathers the segment's <= 8 activation columns ONCE into shared memory in the layout of the dense
+// kernel (so a lane fetches its int8 fragment and its columns' scales with three 128-bit shared loads per 64 weights
+// instead of nine global loads), and its warps take one tile of every unit each (warp w: tile w), streamed through a
+// private ring. A warp's pipeline thus runs over ~7 tiles per launch instead of ~1.75 four-tile units, which removes
+// the quantisation of the launch time to whole units. MODE 0: the 32-feature quantisation group spans the quad's four
+// tiles: amax (a maximum) and the integer sum of the quantised values go through shared memory between two quad
+// barriers. Per output element the arithmetic is unchanged: one warp, blocks in order along K, no split.
+constexpr int MQ_WARPS = 12, MQ_QUADS = 3, MQ_AUX = 2048;   // bytes after the rings: barriers + the quads' exchange words
+__device__ __forceinline__ void quad_barrier(int quad) { asm volatile("bar.sync %0, 128;" ::"r"(quad + 1) : "memory"); }
+template <int MODE, int SB, int DEPTH>
+__global__ void __launch_bounds__(MQ_WARPS * 32, 1) k_moe_gemv_quad(MoeGArgs a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int STAGE = SB * 2304;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3, quad = warp >> 2, w4 = warp & 3, qtid = threadIdx.x & 127;
+    uint8_t* ring = smem + warp * DEPTH * STAGE;
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + MQ_WARPS * DEPTH * STAGE);
+    float* ex_amax = reinterpret_cast<float*>(smem + MQ_WARPS * DEPTH * STAGE + 1024) + quad * 32;   // [warp of the quad][t * 2 + c]
+    int* ex_sum = reinterpret_cast<int*>(smem + MQ_WARPS * DEPTH * STAGE + 1536) + quad * 32;
+    uint8_t* xbuf = smem + MQ_WARPS * DEPTH * STAGE + MQ_AUX + (size_t)quad * a.nb * 2560;          // int8 fragments [nb][2048], then scales [nb][512]
+    uint4* xq_s = reinterpret_cast<uint4*>(xbuf);
+    float* xsc_s = reinterpret_cast<float*>(xbuf + (size_t)a.nb * 2048);
+    const uint32_t bar0 = smem_u32(&bars[warp * DEPTH]);
+    pdl_launch_dependents();
+    if (lane == 0) { for (int s = 0; s < DEPTH; ++s) mbar_init(bar0 + 8 * s, 1); fence_barrier_init(); }
+    __syncwarp();
+    pdl_wait();
+    const int spt = a.nb / SB, ups = a.tiles / MOE_UNIT_TILES;   // stages per tile, units per segment
+    const int total = a.ctl[0] * ups, nquads = (int)gridDim.x * MQ_QUADS, gq = (int)blockIdx.x * MQ_QUADS + quad;
+    const int u_lo = (int)((long long)gq * total / nquads), u_hi = (int)((long long)(gq + 1) * total / nquads);
+    const size_t tile_bytes = (size_t)a.nb * 2304;
+    auto seg_weights = [&](int seg) -> const uint8_t* {
+        const int e = __ldcg(&a.segs[seg].expert);
+        return e >= 0 ? a.w_exp + (size_t)(e - a.e_lo) * a.tiles * tile_bytes : a.w_sh;
+    };
+    // issue cursor: unit iu (segment iseg, unit i_us of it), stage ist of this warp's tile of the unit
+    int iu = u_lo, iseg = u_lo < u_hi ? u_lo / ups : 0, i_us = u_lo < u_hi ? u_lo % ups : 0, ist = 0, icount = 0;
+    const uint8_t* ibase = u_lo < u_hi ? seg_weights(iseg) : nullptr;
+    const uint8_t* isrc = ibase ? ibase + (size_t)(i_us * MOE_UNIT_TILES + w4) * tile_bytes : nullptr;
+    bool ok = true;
+    auto issue = [&]() {
+        if (iu >= u_hi || !ok) return;
+        const uint32_t bar = bar0 + 8 * (icount % DEPTH);
+        if (lane == 0) { mbar_expect_tx(bar, STAGE); bulk_g2s(smem_u32(ring + (icount % DEPTH) * STAGE), isrc, STAGE, bar); }
+        ++icount; isrc += STAGE;
+        if (++ist == spt) {
+            ist = 0; ++iu;
+            if (iu < u_hi) {
+                if (++i_us == ups) { i_us = 0; ++iseg; ibase = seg_weights(iseg); }
+                isrc = ibase + (size_t)(i_us * MOE_UNIT_TILES + w4) * tile_bytes;
+            }
+        }
+    };
+    for (int i = 0; i < DEPTH; ++i) issue();
+    int cseg = u_lo < u_hi ? u_lo / ups : 0, c_us = u_lo < u_hi ? u_lo % ups : 0, staged = -1, ccount = 0;
+    int c0 = -1, c1 = -1;   // pair indices of this lane's columns 2t, 2t + 1
+    const uint4* xq4 = reinterpret_cast<const uint4*>(a.xq);
+    const int nsb = a.xK >> 5, nk64 = a.xK >> 6;
+    for (int cu = u_lo; cu < u_hi; ++cu) {
+        if (cseg != staged) {
+            // gather the segment's columns: fragment (k block of 64, column gg, quarter tt) and scales (sub-block, column)
+            quad_barrier(quad);   // everybody has finished with the previous segment's activations
+            const MoeSeg* sg = a.segs + cseg;
+            const int ncols = __ldcg(&sg->ncols);
+            {   // a thread's column and quarter are the same for all its items (the items are 128 apart): the column's row
+                // is looked up once, and the item loads are independent of each other (one L2 round trip, not one per item)
+                const int gg = (qtid & 31) >> 2, tt = qtid & 3;
+                const int r = gg < ncols ? __ldcg(&sg->cols[gg]) / a.xdiv : -1;
+                const uint4* src = r >= 0 ? xq4 + (size_t)(r >> 3) * nk64 * 32 + (r & 7) * 4 + tt : nullptr;
+#pragma unroll 8
+                for (int kb = qtid >> 5; kb < nk64; kb += 4) xq_s[kb * 32 + (qtid & 31)] = src ? __ldcg(src + (size_t)kb * 32) : make_uint4(0u, 0u, 0u, 0u);
+                const int w = qtid & 15, gs = (w >> 2) * 2 + (w & 1), is_s = (w >> 1) & 1;
+                const int rs = gs < ncols ? __ldcg(&sg->cols[gs]) / a.xdiv : -1;
+                const float* ssrc = rs >= 0 ? a.xsc + (size_t)(rs >> 3) * nsb * 16 + ((rs & 7) >> 1) * 4 + (rs & 1) + 2 * is_s : nullptr;
+#pragma unroll 8
+                for (int sb = qtid >> 4; sb < nsb; sb += 8) xsc_s[sb * 16 + w] = ssrc ? __ldcg(ssrc + (size_t)sb * 16) : 0.f;
+            }
+            c0 = 2 * t < ncols ? __ldcg(&sg->cols[2 * t]) : -1; c1 = 2 * t + 1 < ncols ? __ldcg(&sg->cols[2 * t + 1]) : -1;
+            staged = cseg;
+            quad_barrier(quad);
+        }
+        float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+        for (int st = 0; st < spt; ++st) {
+            const int s = ccount % DEPTH;
+            if (ok) ok = mbar_wait(bar0 + 8 * s, (ccount / DEPTH) & 1, a.err);
+            if (ok) {
+                const uint8_t* sp = ring + s * STAGE;
+#pragma unroll
+                for (int blk = 0; blk < SB; ++blk) {
+                    const int b = st * SB + blk;
+                    const RowScales ra = decode_scales(*reinterpret_cast<const uint4*>(sp + g * 16 + blk * 2304));
+                    const RowScales rb = decode_scales(*reinterpret_cast<const uint4*>(sp + g * 16 + 128 + blk * 2304));
+                    const uint4* xqp = xq_s + (size_t)b * 128 + lane;
+                    const float4* xsp = reinterpret_cast<const float4*>(xsc_s) + (size_t)b * 32 + t;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint4 ww = *reinterpret_cast<const uint4*>(sp + 256 + lane * 16 + blk * 2304 + 512 * j);
+                        const uint32_t alo[4] = {ww.x & 0x0F0F0F0Fu, ww.z & 0x0F0F0F0Fu, ww.y & 0x0F0F0F0Fu, ww.w & 0x0F0F0F0Fu};
+                        const uint32_t ahi[4] = {ww.x & 0xF0F0F0F0u, ww.z & 0xF0F0F0F0u, ww.y & 0xF0F0F0F0u, ww.w & 0xF0F0F0F0u};
+                        const float4 sa0 = ra.get(2 * j), sb0 = rb.get(2 * j), sa1 = ra.get(2 * j + 1), sb1 = rb.get(2 * j + 1);
+                        const uint4 xf = xqp[j * 32];
+                        const float4 x0 = xsp[(2 * j) * 4], x1 = xsp[(2 * j + 1) * 4];
+                        const float2 xd0 = make_float2(x0.x, x0.y), xs0v = make_float2(x0.z, x0.w), xd1 = make_float2(x1.x, x1.y), xs1v = make_float2(x1.z, x1.w);
+                        int m0[4], m1[4];
+                        mma_u8s8_magic(m0, alo, xf.x, xf.y);
+                        mma_u8s8_magic(m1, ahi, xf.z, xf.w);
+                        const float2 mg = make_float2(-12582912.f, -12582912.f);
+                        fma2(acc0, mul2(make_float2(sa0.x, sa0.y), xd0), add2(make_float2(__int_as_float(m0[0]), __int_as_float(m0[1])), mg));
+                        fma2(acc0, make_float2(sa0.z, sa0.w), xs0v);
+                        fma2(acc1, mul2(make_float2(sb0.x, sb0.y), xd0), add2(make_float2(__int_as_float(m0[2]), __int_as_float(m0[3])), mg));
+                        fma2(acc1, make_float2(sb0.z, sb0.w), xs0v);
+                        fma2(acc0, mul2(make_float2(sa1.x, sa1.y), xd1), add2(make_float2(__int_as_float(m1[0]), __int_as_float(m1[1])), mg));
+                        fma2(acc0, make_float2(sa1.z, sa1.w), xs1v);
+                        fma2(acc1, mul2(make_float2(sb1.x, sb1.y), xd1), add2(make_float2(__int_as_float(m1[2]), __int_as_float(m1[3])), mg));
+                        fma2(acc1, make_float2(sb1.z, sb1.w), xs1v);
+                    }
+                }
+            }
+            __syncwarp();   // every lane has read the stage before it is refilled
+            ++ccount;
+            issue();
+        }
+        const int tile = c_us * MOE_UNIT_TILES + w4;
+        if constexpr (MODE == 1) {
+            if (ok) {
+                if (c0 >= 0) { a.y[(size_t)c0 * a.N + tile * 16 + g] = acc0.x; a.y[(size_t)c0 * a.N + tile * 16 + g + 8] = acc1.x; }
+                if (c1 >= 0) { a.y[(size_t)c1 * a.N + tile * 16 + g] = acc0.y; a.y[(size_t)c1 * a.N + tile * 16 + g + 8] = acc1.y; }
+            }
+        } else {
+            // rows g = gate of feature 8 * tile + g, rows g + 8 = up of the same feature; the unit's 4 tiles (this quad's 4
+            // warps) are one 32-feature quantisation group per column: amax / 127, q = rint(v * (127 / amax)),
+            // s = d * sum(q) (gemv.hip:36-51)
+            const float act[2] = {silu_det(acc0.x) * acc1.x, silu_det(acc0.y) * acc1.y};
+            float am[2] = {fabsf(act[0]), fabsf(act[1])};
+#pragma unroll
+            for (int off = 4; off < 32; off <<= 1) { am[0] = fmaxf(am[0], __shfl_xor_sync(0xffffffffu, am[0], off)); am[1] = fmaxf(am[1], __shfl_xor_sync(0xffffffffu, am[1], off)); }
+            if (g == 0) { ex_amax[w4 * 8 + t * 2] = am[0]; ex_amax[w4 * 8 + t * 2 + 1] = am[1]; }
+            quad_barrier(quad);
+            int qs[2]; float dd[2];
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                float amax = 0.f;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) amax = fmaxf(amax, ex_amax[w * 8 + t * 2 + c]);
+                dd[c] = amax / 127.f;
+                const float id = amax > 0.f ? 127.f / amax : 0.f;
+                const int q = __float2int_rn(act[c] * id);
+                int sum = q;
+#pragma unroll
+                for (int off = 4; off < 32; off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+                qs[c] = sum;
+                const int pair = c ? c1 : c0;
+                if (pair >= 0 && ok) a.oq[xq_q_index(pair, c_us * 32 + 8 * w4 + g, a.F)] = (int8_t)q;
+            }
+            if (g == 0) { ex_sum[w4 * 8 + t * 2] = qs[0]; ex_sum[w4 * 8 + t * 2 + 1] = qs[1]; }
+            quad_barrier(quad);
+            if (w4 == 0 && g == 0 && ok) {
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const int pair = c ? c1 : c0;
+                    if (pair >= 0) {
+                        const int sum = ex_sum[t * 2 + c] + ex_sum[8 + t * 2 + c] + ex_sum[16 + t * 2 + c] + ex_sum[24 + t * 2 + c];
+                        const size_t di = xq_d_index(pair, c_us, a.F); a.osc[di] = dd[c]; a.osc[di + 2] = dd[c] * (float)sum;
+                    }
+                }
+            }
+        }
+        if (++c_us == ups) { c_us = 0; ++cseg; }
+    }
+}
+
 // in-order weighted combine of the per-(row, slot) expert outputs (gemv.hip:1104-1112); used by the kernel-level entry
 // point (inside the engine the combine runs in the norm kernel that follows)
 __global__ void __launch_bounds__(256) k_moe_combine(const float* __restrict__ v, const float* __restrict__ slotw, float* __restrict__ y, int nslot, int E) {
@@ -461,6 +633,24 @@ template <int MODE>
 static int launch_grouped_sb(const MoeGArgs& a, bool few, cudaStream_t s) {
     return a.nb % 4 == 0 ? launch_grouped_geo<MODE, 4>(a, few, s) : a.nb % 2 == 0 ? launch_grouped_geo<MODE, 2>(a, few, s) : launch_grouped_geo<MODE, 1>(a, few, s);
 }
+template <int MODE, int SB, int DEPTH>
+static int launch_quad(const MoeGArgs& a, size_t smem, cudaStream_t s) {
+    static size_t attr[MAX_DEVICES] = {};
+    const int dev = current_device(); if (dev < 0) return HP_ECUDA;
+    if (smem > attr[dev]) { HP_CUDA(cudaFuncSetAttribute(k_moe_gemv_quad<MODE, SB, DEPTH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr[dev] = smem; }
+    HP_CUDA(launch_pdl<8>(k_moe_gemv_quad<MODE, SB, DEPTH>, dim3(GEMV_NCTA), dim3(MQ_WARPS * 32), smem, s, a));
+    return HP_OK;
+}
+// the quad form when the three quads' activation buffers fit beside the rings (K <= 2048 for the gate|up projection),
+// the one-warp-per-unit form otherwise
+template <int MODE>
+static int launch_experts(const MoeGArgs& a, bool few, cudaStream_t s) {
+    static const bool v1 = getenv("HIPSTER_B200_MOE_UNITS") != nullptr;
+    const int sb = a.nb % 2 == 0 ? 2 : 1, depth = sb == 2 ? 3 : 6;
+    const size_t smem = (size_t)MQ_WARPS * depth * sb * 2304 + MQ_AUX + (size_t)MQ_QUADS * a.nb * 2560;
+    if (v1 || smem > 227 * 1024 || a.tiles % MOE_UNIT_TILES != 0) return launch_grouped_sb<MODE>(a, few, s);
+    return sb == 2 ? launch_quad<MODE, 2, 3>(a, smem, s) : launch_quad<MODE, 1, 6>(a, smem, s);
+}
 int moe_experts_grouped(const MoeGroupParams& p, cudaStream_t s) {
     HP_REQUIRE(p.E % 256 == 0 && p.F % 256 == 0 && p.T >= 1 && p.nslot >= 1 && p.T * p.nslot <= MOE_MAX_PAIRS, "moe_experts_grouped: bad shape");
     HP_REQUIRE(p.segs && p.ctl && p.v, "moe_experts_grouped: null pointer");
@@ -470,12 +660,12 @@ int moe_experts_grouped(const MoeGroupParams& p, cudaStream_t s) {
     a.xq = (const uint8_t*)p.xq.q; a.xsc = (const float*)p.xq.sc; a.xK = p.E; a.xdiv = p.nslot;
     a.y = nullptr; a.N = 0; a.oq = (int8_t*)p.xq2.q; a.osc = (float*)p.xq2.sc; a.F = p.F;
     const bool few = p.T <= 4;
-    { const int rc = launch_grouped_sb<0>(a, few, s); if (rc != HP_OK) return rc; }
+    { const int rc = launch_experts<0>(a, few, s); if (rc != HP_OK) return rc; }
     // down: [E rows][F]; per-pair outputs
     a.w_exp = (const uint8_t*)p.w_down; a.w_sh = (const uint8_t*)p.sh_down; a.tiles = p.E / 16; a.nb = p.F / 256; a.ticket = 2;
     a.xq = (const uint8_t*)p.xq2.q; a.xsc = (const float*)p.xq2.sc; a.xK = p.F; a.xdiv = 1;
     a.y = p.v; a.N = p.E; a.oq = nullptr; a.osc = nullptr;
-    { const int rc = launch_grouped_sb<1>(a, few, s); if (rc != HP_OK) return rc; }
+    { const int rc = launch_experts<1>(a, few, s); if (rc != HP_OK) return rc; }
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }
 int moe_combine(const float* v, const float* slotw, float* y, int T, int nslot, int E, cudaStream_t s) {
