@@ -606,7 +606,7 @@ int moe_route_group(const MoeRouteParams& p, cudaStream_t s) {
     a.stage_x = a.stage_w && wbytes + xbytes <= 204 * 1024 && ((uintptr_t)a.x & 15) == 0 ? 1 : 0; a.err = p.err;
     size_t smem = a.stage_w ? wbytes + (a.stage_x ? xbytes : 0) : 0;
     if (smem < (size_t)RG_ROUTE_SMEM) smem = RG_ROUTE_SMEM;
-    if (smem > 48 * 1024) {
+    if (smem > 32 * 1024) {   // the kernel also has ~12 KB of static shared memory: opt in above 48 KB in total
         static size_t attr[MAX_DEVICES] = {};
         const int dev = current_device(); if (dev < 0) return HP_ECUDA;
         if (smem > attr[dev]) { HP_CUDA(cudaFuncSetAttribute(k_route_group, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr[dev] = smem; }

@@ -50,3 +50,18 @@ def test_router_ties_go_to_the_lower_expert_id():
     ids_o, w_o, y_o, _ = orc.moe_layer(xn, router, egu, edn, sgu, sdn, E, F, n_expert, k)
     assert list(ids_o[0][:2]) == [7, 40]
     assert np.array_equal(ids.cpu().numpy(), ids_o) and np.array_equal(bits(y.cpu().numpy()), bits(y_o))
+
+
+def test_unit_form_of_the_expert_gemv_matches_too():
+    """The one-warp-per-unit form of the expert GEMVs (taken when the quads' activation buffers do not fit in shared
+    memory, or with HIPSTER_B200_MOE_UNITS set) must give the same bits: the switch is read once per process, so the
+    parity test of the small shape runs again in a child process with it set."""
+    import os, subprocess, sys
+    if os.environ.get("HIPSTER_B200_MOE_UNITS"):
+        pytest.skip("already inside the child process")
+    env = dict(os.environ, HIPSTER_B200_MOE_UNITS="1")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(root, "tests", "test_moe_kernels_gpu.py"), "-q", "-m", "gpu", "-k", "bit_exact and 64-4"],
+                       env=env, cwd=root, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "1 passed" in r.stdout
