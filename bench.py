@@ -485,6 +485,58 @@ GEMV_N, GEMV_K, GEMV_R = 17408, 5120, 3
 GEMV_BYTES = GEMV_N * (GEMV_K // 256) * 144 + GEMV_R * GEMV_K * 4 + GEMV_R * GEMV_N * 4   # 50,405,376 algorithmic bytes
 
 
+def run_moe_layer(args, rank, local_rank, world):
+    """One mixture-of-experts FFN at the configuration-5 shape (24 rows, 512 experts top-10 + shared, hidden 2048, expert
+    FFN 512) through the kernel-level entry hp_moe_layer, timed alone with CUDA events: the workload of the ncu captures
+    of k_route_group and of the expert GEMVs. Weights: seeded Q4_K expert tensors (~0.9 GB on the device); rows and
+    router: seeded N(0, 1), so the router spreads the rows over the experts. L2 is flushed between the timed calls."""
+    import ctypes
+    import numpy as np
+    import torch
+    from hipster_b200 import kernels as K_, synth
+    from hipster_b200._lib import lib
+    torch.cuda.set_device(local_rank)
+    n_expert, k, E, F, T = 512, 10, 2048, 512, 24
+    rng = np.random.default_rng(1)
+    d = lambda a: torch.from_numpy(a).cuda()
+    xn = d(rng.normal(0, 1, size=(T, E)).astype(np.float32)); xq = K_.quantize_x_q8(xn)
+    router = d((rng.normal(0, 1, size=(n_expert + 1, E)) / np.sqrt(E)).astype(np.float32))
+    egu = K_.repack_tiled(d(synth.q4k_matrix(n_expert * 2 * F, E, seed=1).reshape(-1)), n_expert * 2 * F, E, F)
+    edn = K_.repack_tiled(d(synth.q4k_matrix(n_expert * E, F, seed=2).reshape(-1)), n_expert * E, F, 0)
+    sgu = K_.repack_tiled(d(synth.q4k_matrix(2 * F, E, seed=3).reshape(-1)), 2 * F, E, F)
+    sdn = K_.repack_tiled(d(synth.q4k_matrix(E, F, seed=4).reshape(-1)), E, F, 0)
+    L = lib(); L.hp_moe_workspace_bytes.restype = ctypes.c_size_t
+    ws = torch.empty(L.hp_moe_workspace_bytes(T, E, F, n_expert, k), dtype=torch.uint8, device="cuda")
+    ids = torch.empty((T, k + 1), dtype=torch.int32, device="cuda"); w = torch.empty((T, k + 1), dtype=torch.float32, device="cuda")
+    y = torch.empty((T, E), dtype=torch.float32, device="cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def run():
+        K_.check(L.hp_moe_layer(K_.ptr(xn), K_.ptr(xq.q), K_.ptr(xq.sc), K_.ptr(router), K_.ptr(egu), K_.ptr(edn), K_.ptr(sgu), K_.ptr(sdn), T, E, F, n_expert, k,
+                                K_.ptr(ids), K_.ptr(w), K_.ptr(y), K_.ptr(ws), K_._stream()))
+    for _ in range(max(args.warmup, 3)):
+        run()
+    sampler = ClockSampler(local_rank)
+    ts = []
+    for _ in range(args.steps):
+        flush.zero_(); torch.cuda.synchronize()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record(); run(); e1.record(); torch.cuda.synchronize(); ts.append(e0.elapsed_time(e1))
+    clocks = sampler.stop()
+    K_.device_status()
+    touched = len(set(ids.cpu().numpy()[:, :k].reshape(-1).tolist()))
+    nbytes = (touched + 1) * (2 * F * E + E * F) * 144 // 256 + (n_expert + 1) * E * 4
+    ms = sum(ts) / len(ts)
+    pk = peaks()
+    return {"metric": METRIC, "value": T / (ms / 1e3), "unit": "rows/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "u4 x i8 -> i32, f32 epilogue", "data": "synthetic",
+            "config": {"workload": "one MoE FFN at the config-5 shape through hp_moe_layer (router + routing + grouping, expert gate|up, expert down, combine)",
+                       "rows": T, "touched_experts": touched, "l2": "256 MiB written between timed calls"},
+            "roofline": {"bound": "hbm", "achieved": nbytes / (ms / 1e3) / 1e9, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], "traffic": None,
+                         "algorithmic_bytes": nbytes, "kernel": "whole hp_moe_layer call (five launches)", "peak_source": pk["_src"]},
+            "gpu_launches": 5 * args.steps, "clocks": clocks}
+
+
 def run_gemv(args, rank, local_rank, world):
     import torch
     from hipster_b200 import kernels as K_, synth
@@ -558,7 +610,7 @@ def main():
     ap.add_argument("--steps", type=int, default=87)     # ~256 emitted tokens at 2.94 tokens per round
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="dense27b", choices=["dense27b", "moe", "moe-ep", "gemv"])
+    ap.add_argument("--workload", default="dense27b", choices=["dense27b", "moe", "moe-ep", "moe-layer", "gemv"])
     ap.add_argument("--preset", default=None)
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-ep", action="store_true", help="skip the configuration-5 (expert-parallel) block of the default run")
@@ -599,6 +651,8 @@ def main():
     elif args.workload == "moe-ep":
         block = run_moe_ep(args, rank, local_rank, world)
         line = ep_line(args, block, world) if block else None
+    elif args.workload == "moe-layer":
+        line = run_moe_layer(args, rank, local_rank, world) if rank == 0 else None
     else:
         line = run_gemv(args, rank, local_rank, world)
     if line:
