@@ -41,7 +41,9 @@ template <int CB, bool TILED> struct SkGeom {
     static constexpr int FIXED = GEMV_WARPS * SK_STAGES * STAGE_BYTES + 1024;
 };
 
-template <int NT, int CB, bool TILED>
+// XG: the activations are read from global memory (L2) inside the loop instead of being staged in shared memory: the
+// form for several column tiles whose activations do not fit beside the rings (small matrices with a long K).
+template <int NT, int CB, bool TILED, bool XG = false>
 __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __restrict__ W, const uint4* __restrict__ xq, const float4* __restrict__ xsc,
                                                                 float* __restrict__ y, int N, int nb, int P, int R, int ldy, size_t part_stride,
                                                                 int* __restrict__ err) {
@@ -50,8 +52,9 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
     uint8_t* ring_all = smem;
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + GEMV_WARPS * SK_STAGES * Geo::STAGE_BYTES);
     const int nbp = nb / P;                                // blocks of this CTA's K part
-    const uint4* xq_s = reinterpret_cast<const uint4*>(smem + Geo::FIXED);
-    const float4* xsc_s = reinterpret_cast<const float4*>(smem + Geo::FIXED + NT * nbp * 2048);
+    const int xstride = XG ? nb : nbp;                     // blocks between two column tiles of the activations
+    const uint4* xq_s = XG ? xq : reinterpret_cast<const uint4*>(smem + Geo::FIXED);
+    const float4* xsc_s = XG ? xsc : reinterpret_cast<const float4*>(smem + Geo::FIXED + NT * nbp * 2048);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const GemvCta ct = gemv_cta(N, nb, P, blockIdx.x);
@@ -101,7 +104,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
 
     pdl_wait();
 
-    if (warp == 0) {   // quantised activations of blocks [kb0, kb0 + nbp), all NT column tiles, by bulk copies. Per column
+    if (!XG && warp == 0) {   // quantised activations of blocks [kb0, kb0 + nbp), all NT column tiles, by bulk copies. Per column
         // tile the int8 fragments (2048 B per block) and the scales (512 B per block) of consecutive blocks are
         // contiguous. Issuing a bulk copy costs ~45 ns (one copy pair per block took 1.8 us), so each column tile is
         // fetched as SK_XG copy pairs over ranges of blocks, each CTA starting at a different range so that the 148 CTAs
@@ -158,14 +161,14 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
 
     int cur_tile = first_tile, chunk = nunits ? u0 % C : 0;
     bool cur_from_start = chunk == 0;
-    bool ok = mbar_wait(xbar, 0, err);
+    bool ok = XG ? true : mbar_wait(xbar, 0, err);
     for (int i = 0; i < nunits && ok; ++i) {
         const int s = i % SK_STAGES;
         ok = mbar_wait(bar0 + 8 * s, (i / SK_STAGES) & 1, err);
         if (!ok) break;
         const uint8_t* st = ring + s * Geo::STAGE_BYTES;
-        const uint4* xqp = xq_s + (chunk * CB) * 128 + lane;
-        const float4* xsp = xsc_s + (chunk * CB) * 32 + t;
+        const uint4* xqp = xq_s + ((XG ? kb0 : 0) + chunk * CB) * 128 + lane;
+        const float4* xsp = xsc_s + ((XG ? kb0 : 0) + chunk * CB) * 32 + t;
 #pragma unroll
         for (int blk = 0; blk < CB; ++blk) {
             // Scales of this lane's two rows (g, g+8), decoded in registers from the 16-byte headers. A 6-bit value v
@@ -190,9 +193,11 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_gemv_q4k_sk(const uint8_t* __
                 const float4 sa1 = ra.get(2 * j + 1), sb1 = rb.get(2 * j + 1);   // high-nibble sub-block
 #pragma unroll
                 for (int n = 0; n < NT; ++n) {
-                    const uint4 xf = xqp[n * nbp * 128 + (blk * 4 + j) * 32];
-                    const float4 x0 = xsp[n * nbp * 32 + (blk * 8 + 2 * j) * 4];
-                    const float4 x1 = xsp[n * nbp * 32 + (blk * 8 + 2 * j + 1) * 4];
+                    const uint4* xfp = xqp + n * xstride * 128 + (blk * 4 + j) * 32;
+                    const float4* x0p = xsp + n * xstride * 32 + (blk * 8 + 2 * j) * 4;
+                    const uint4 xf = XG ? __ldcg(xfp) : *xfp;
+                    const float4 x0 = XG ? __ldcg(x0p) : *x0p;
+                    const float4 x1 = XG ? __ldcg(x0p + 4) : x0p[4];
                     // The accumulator input carries 0x4B400000: the int32 result, read as fp32, is 12582912 + idot
                     // exactly (|idot| < 2^22), so the int -> float conversion is one exact packed subtraction.
                     int c0[4], c1[4];
@@ -356,28 +361,28 @@ __global__ void __launch_bounds__(F32_THREADS) k_gemv_q4k_f32(const uint8_t* __r
     }
 }
 
-template <int NT, int CB, bool TILED>
+template <int NT, int CB, bool TILED, bool XG = false>
 int launch_sk2(const uint8_t* W, const void* xq, const void* xsc, float* y, int N, int nb, int P, int R, int ldy, size_t part_stride,
                int* err, cudaStream_t s, bool pdl) {
-    const size_t smem = SkGeom<CB, TILED>::FIXED + (size_t)NT * (nb / P) * 2560;
+    const size_t smem = SkGeom<CB, TILED>::FIXED + (XG ? 0 : (size_t)NT * (nb / P) * 2560);
     static size_t attr_smem[MAX_DEVICES] = {};   // per device: the opt-in belongs to the device's copy of the kernel
     const int dev = current_device(); if (dev < 0) return HP_ECUDA;
-    if (smem > attr_smem[dev]) { HP_CUDA(cudaFuncSetAttribute(k_gemv_q4k_sk<NT, CB, TILED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr_smem[dev] = smem; }
+    if (smem > attr_smem[dev]) { HP_CUDA(cudaFuncSetAttribute(k_gemv_q4k_sk<NT, CB, TILED, XG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr_smem[dev] = smem; }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(GEMV_NCTA); cfg.blockDim = dim3(SK_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = s;
     cudaLaunchAttribute at[1]; at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at; cfg.numAttrs = pdl && !(pdl_off_mask(s) & 64) ? 1 : 0;
-    HP_CUDA(cudaLaunchKernelEx(&cfg, k_gemv_q4k_sk<NT, CB, TILED>, W, (const uint4*)xq, (const float4*)xsc, y, N, nb, P, R, ldy, part_stride, err));
+    HP_CUDA(cudaLaunchKernelEx(&cfg, k_gemv_q4k_sk<NT, CB, TILED, XG>, W, (const uint4*)xq, (const float4*)xsc, y, N, nb, P, R, ldy, part_stride, err));
     return HP_OK;
 }
-template <int NT>
+template <int NT, bool XG = false>
 int launch_sk(const uint8_t* W, bool tiled, const void* xq, const void* xsc, float* y, int N, int nb, int P, int R, int ldy, size_t part_stride,
               int* err, cudaStream_t s, bool pdl) {
     const bool cb2 = (nb / P) % 2 == 0;
-    if (tiled) return cb2 ? launch_sk2<NT, 2, true>(W, xq, xsc, y, N, nb, P, R, ldy, part_stride, err, s, pdl)
-                          : launch_sk2<NT, 1, true>(W, xq, xsc, y, N, nb, P, R, ldy, part_stride, err, s, pdl);
-    return cb2 ? launch_sk2<NT, 2, false>(W, xq, xsc, y, N, nb, P, R, ldy, part_stride, err, s, pdl)
-               : launch_sk2<NT, 1, false>(W, xq, xsc, y, N, nb, P, R, ldy, part_stride, err, s, pdl);
+    if (tiled) return cb2 ? launch_sk2<NT, 2, true, XG>(W, xq, xsc, y, N, nb, P, R, ldy, part_stride, err, s, pdl)
+                          : launch_sk2<NT, 1, true, XG>(W, xq, xsc, y, N, nb, P, R, ldy, part_stride, err, s, pdl);
+    return cb2 ? launch_sk2<NT, 2, false, XG>(W, xq, xsc, y, N, nb, P, R, ldy, part_stride, err, s, pdl)
+               : launch_sk2<NT, 1, false, XG>(W, xq, xsc, y, N, nb, P, R, ldy, part_stride, err, s, pdl);
 }
 
 // row-major ggml blocks -> tile-major chunks (see SkGeom); rows beyond N are zero (they contribute nothing).
@@ -427,24 +432,27 @@ int gemv_q4k_q8_parts(const void* W, const XQ8F& x, float* yparts, int N, int K,
     const int nb = K / 256, P = gemv_num_parts(N, nb);
     HP_REQUIRE(P > 0, "gemv_q4k_q8: K=%d is too large for the activation staging buffer", K);
     const int ntile = (R + 7) / 8, nbp = nb / P;
-    // all column tiles in one launch when their activations fit in shared memory beside the rings; otherwise one
-    // launch per tile of 8 columns (same per-column arithmetic either way)
-    const bool fused = ntile == 1 || (size_t)SkGeom<2, false>::FIXED + (size_t)ntile * nbp * 2560 <= (size_t)GEMV_SMEM_LIMIT;
-    for (int c0 = 0; c0 < ntile; c0 += fused ? ntile : 1) {
-        const int nt = fused ? ntile : 1;
-        const int Rl = min(R - c0 * 8, nt * 8);
-        const uint8_t* xqp = (const uint8_t*)x.q + (size_t)c0 * K * 8;
-        const uint8_t* xsp = (const uint8_t*)x.sc + (size_t)c0 * (K / 32) * 64;
-        float* yp = yparts + (size_t)c0 * 8 * ldy;
-        int rc;
-        switch (nt) {
-            case 1: rc = launch_sk<1>((const uint8_t*)W, tiled, xqp, xsp, yp, N, nb, P, Rl, ldy, part_stride, err, s, pdl); break;
-            case 2: rc = launch_sk<2>((const uint8_t*)W, tiled, xqp, xsp, yp, N, nb, P, Rl, ldy, part_stride, err, s, pdl); break;
-            case 3: rc = launch_sk<3>((const uint8_t*)W, tiled, xqp, xsp, yp, N, nb, P, Rl, ldy, part_stride, err, s, pdl); break;
-            default: rc = launch_sk<4>((const uint8_t*)W, tiled, xqp, xsp, yp, N, nb, P, Rl, ldy, part_stride, err, s, pdl); break;
+    // all column tiles in one launch: their activations staged in shared memory beside the rings when they fit, read
+    // from L2 inside the loop otherwise (small matrices with a long K: one launch instead of one per tile of 8 columns;
+    // same per-column arithmetic either way)
+    const bool staged = ntile == 1 || (size_t)SkGeom<2, false>::FIXED + (size_t)ntile * nbp * 2560 <= (size_t)GEMV_SMEM_LIMIT;
+    const uint8_t* w = (const uint8_t*)W;
+    int rc;
+    if (staged) {
+        switch (ntile) {
+            case 1: rc = launch_sk<1>(w, tiled, x.q, x.sc, yparts, N, nb, P, R, ldy, part_stride, err, s, pdl); break;
+            case 2: rc = launch_sk<2>(w, tiled, x.q, x.sc, yparts, N, nb, P, R, ldy, part_stride, err, s, pdl); break;
+            case 3: rc = launch_sk<3>(w, tiled, x.q, x.sc, yparts, N, nb, P, R, ldy, part_stride, err, s, pdl); break;
+            default: rc = launch_sk<4>(w, tiled, x.q, x.sc, yparts, N, nb, P, R, ldy, part_stride, err, s, pdl); break;
         }
-        if (rc != HP_OK) return rc;
+    } else {
+        switch (ntile) {
+            case 2: rc = launch_sk<2, true>(w, tiled, x.q, x.sc, yparts, N, nb, P, R, ldy, part_stride, err, s, pdl); break;
+            case 3: rc = launch_sk<3, true>(w, tiled, x.q, x.sc, yparts, N, nb, P, R, ldy, part_stride, err, s, pdl); break;
+            default: rc = launch_sk<4, true>(w, tiled, x.q, x.sc, yparts, N, nb, P, R, ldy, part_stride, err, s, pdl); break;
+        }
     }
+    if (rc != HP_OK) return rc;
     return HP_OK;
 }
 

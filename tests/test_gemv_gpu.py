@@ -36,7 +36,8 @@ def test_quantize_x_q8_bit_exact(R, K):
 
 
 @pytest.mark.parametrize("N,K,R", [(16, 256, 1), (48, 1024, 3), (512, 5120, 6), (100, 768, 2), (40, 2048, 8),
-                                     (64, 1024, 9), (128, 2048, 24), (32, 17408, 6), (7, 512, 5)])
+                                     (64, 1024, 9), (128, 2048, 24), (32, 17408, 6), (7, 512, 5),
+                                     (256, 6144, 24), (80, 6144, 12), (48, 9216, 32)])   # the last three: activations read from L2 (too large to stage)
 def test_gemv_q8_bit_exact_vs_oracle(N, K, R):
     W = synth.q4k_matrix(N, K, seed=N + K); x = synth.activations(R, K, seed=R)
     xq = K_.quantize_x_q8(dev(x))
