@@ -428,6 +428,7 @@ def run_moe_ep(args, rank, local_rank, world, steps=None, warmup=None):
     clocks = sampler.stop() if sampler else None
     touched = eng.moe_touched()                      # (layer, expert) matrices this GPU streamed in the timed rounds
     exch_us = eng.ep_exchange_us(S * (n + 1), 20)
+    peer = eng.ep_peer() if world > 1 else False
     exact = all(out[s][:len(plain[s])] == plain[s][:len(out[s])] for s in range(S))
     kernels = eng.last_round_kernels()
     # bytes one round must read on this GPU: the replicated dense part of every pass + the touched expert matrices
@@ -458,7 +459,10 @@ def run_moe_ep(args, rank, local_rank, world, steps=None, warmup=None):
             "e2e": {"value": toks / (wall_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 4 * (8 + 8 * 8), "d2h_bytes_per_step": 4 * 8 * 32,
                     "note": "hp_spec_round over 8 slots with host token buffers, wall clock"},
             "slot_streams_equal_solo": bool(exact), "tokens": int(toks), "tokens_per_round": toks / steps,
-            "exchange": {"collective": "ncclAllReduce(sum) of the per-(row, slot) expert outputs [24 rows][11 slots][2048] f32, one per MoE layer" if world > 1 else "none (one GPU)",
+            "exchange": {"collective": ("none (one GPU)" if world == 1 else
+                                        "peer memory: the down projection stores the output rows of the experts a GPU owns into the other GPUs' exchange buffers (CUDA IPC mappings) and raises a flag; a gather kernel waits for the peers' flags; one per MoE layer, inside the round's graph" if peer else
+                                        "ncclAllReduce(sum) of the per-(row, slot) expert outputs [24 rows][11 slots][2048] f32, one per MoE layer, enqueued by the host between graph segments"),
+                         "us_per_layer_note": "a stand-alone exchange (separate push and gather launches, or the NCCL call) timed in a loop, not the fused in-round form",
                          "us_per_layer": exch_us, "layers_per_round": n_exchange if world > 1 else 0,
                          "share_of_round": (exch_us * n_exchange / 1e3) / ms_round if world > 1 else 0.0},
             "roofline": {"bound": "hbm", "unit": "GB/s", "peak": pk["hbm_gbs"], "peak_source": pk["_src"],

@@ -423,12 +423,14 @@ int Engine::moe_block(const LayerW& L, int R) {
     // per-(row, slot) outputs of the experts this GPU owns, grouped by expert so that each touched expert matrix is read
     // once; pairs of experts owned elsewhere stay exact zeros, the exchange fills them in, and the combine runs in slot
     // order (the arithmetic of gemv.hip:1104-1112) on every GPU
-    if (c.ep_world > 1) { HP_TRY(ep_ready()); HP_CUDA(cudaMemsetAsync(moe_v_, 0, (size_t)R * ns * E * 4, s_)); }
+    if (c.ep_world > 1) { HP_TRY(ep_ready()); if (!ep_peer_) HP_CUDA(cudaMemsetAsync(moe_v_, 0, (size_t)R * ns * E * 4, s_)); }
     MoeGroupParams g; g.w_gate_up = L.exp_gate_up.wt; g.w_down = L.exp_down.wt; g.sh_gate_up = L.sh_gate_up.wt; g.sh_down = L.sh_down.wt;
     g.E = E; g.F = F; g.nslot = ns; g.T = R; g.e_lo = e_lo_;
     g.xq = xq_; g.xq2 = xq2_; g.v = moe_v_; g.segs = moe_segs_; g.ctl = moe_ctl_; g.err = err_;
-    HP_TRY(moe_experts_grouped(g, s_));
-    if (c.ep_world > 1) HP_TRY(ep_exchange(moe_v_, (size_t)R * ns * E));
+    int pushed = 0;
+    if (ep_peer_) { g.ep_world = c.ep_world; g.ep_rank = c.ep_rank; g.ep_half = ep_half_; for (int q = 0; q < 8; ++q) { g.ep_x[q] = ep_peer_x_[q]; g.ep_ctl[q] = ep_peer_ctl_[q]; } }
+    HP_TRY(moe_experts_grouped(g, s_, &pushed));
+    if (c.ep_world > 1) HP_TRY(ep_peer_ ? ep_exchange_peer(R, lidx % c.ep_world, pushed != 0) : ep_exchange(moe_v_, (size_t)R * ns * E));
     return HP_OK;   // combined in slot order by the norm that follows (norm_in)
 }
 
@@ -613,6 +615,67 @@ int Engine::topk(int which, int T, int k, int* ids, float* vals) {
 // of 8 rows; with_mtp also runs the MTP block over the same rows, row p paired with the trunk's hidden row of position
 // p - 1 (zeros at position 0; the last row of the previous chunk / call otherwise), so that the draft block's KV cache
 // covers the prompt (spec27b.cpp:62-71). Afterwards row 0 of logits / h_nextn / the arg-max ids holds the LAST prompt row.
+// ---- expert-parallel exchange over peer memory -------------------------------------------------------------------------
+// After the down projection a rank holds the output rows of the (row, slot) pairs whose expert it owns. k_ep_push copies
+// them into the other ranks' exchange buffers (plain stores through the NVLink mapping), makes them visible system-wide
+// and then, from the CTA that finishes last, stores the number of this exchange into its flag word on every rank.
+// k_ep_gather waits (bounded) until every other rank's flag has reached that number and copies the rows it does not own
+// from its own exchange buffer into the pair buffer. Exchange n uses half n & 1 of the buffers: a rank can be at most one
+// exchange ahead of another (it cannot pass gather n before every rank has pushed n), so two halves never collide.
+struct EpXArgs {
+    float* v; const int* ids; int npairs, E, n_expert, world, rank, sh_owner;   // pair buffer [npairs][E], expert id per pair (-1 = shared)
+    float* x[8]; unsigned* ctl[8]; size_t half; int* err;
+};
+__device__ __forceinline__ int ep_owner(int id, const EpXArgs& a) {
+    if (id < 0) return a.sh_owner;
+    if (id >= a.n_expert) return -1;
+    return (int)(((long long)(id + 1) * a.world - 1) / a.n_expert);
+}
+__global__ void __launch_bounds__(256) k_ep_push(EpXArgs a) {
+    unsigned* ctl = a.ctl[a.rank];
+    const unsigned e = __ldcg(ctl + 8) + 1u;   // number of this exchange (the counter moves when every CTA is done)
+    const size_t off = (size_t)(e & 1u) * a.half;
+    const int e4 = a.E >> 2, items = a.npairs * e4;
+    for (int i = blockIdx.x * 256 + threadIdx.x; i < items; i += gridDim.x * 256) {
+        const int pair = i / e4, c = i - pair * e4;
+        if (ep_owner(__ldcg(a.ids + pair), a) != a.rank) continue;
+        const float4 val = __ldcg(reinterpret_cast<const float4*>(a.v + (size_t)pair * a.E) + c);
+        for (int q = 0; q < a.world; ++q)
+            if (q != a.rank) reinterpret_cast<float4*>(a.x[q] + off + (size_t)pair * a.E)[c] = val;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0 && atomicAdd(ctl + 9, 1u) == gridDim.x - 1) {
+        __threadfence_system();
+        for (int q = 0; q < a.world; ++q)
+            if (q != a.rank) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.ctl[q] + a.rank), "r"(e) : "memory");
+        ctl[9] = 0u; __threadfence();
+        atomicExch(ctl + 8, e);
+    }
+}
+__global__ void __launch_bounds__(256) k_ep_gather(EpXArgs a) {
+    unsigned* ctl = a.ctl[a.rank];
+    const unsigned e = __ldcg(ctl + 8);        // the exchange k_ep_push has just sent
+    if (threadIdx.x < a.world && (int)threadIdx.x != a.rank && __ldcg(a.err) == 0) {   // after a wait has been given up the later ones do not wait again
+        unsigned f = 0u; int it = 0;
+        for (;;) {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(f) : "l"(ctl + threadIdx.x) : "memory");
+            if ((int)(f - e) >= 0 || ++it >= (1 << 22)) break;
+            __nanosleep(64);
+        }
+        if ((int)(f - e) < 0) atomicExch(a.err, HP_ETIMEOUT);   // a peer did not deliver: reported through the device status word
+    }
+    __syncthreads();
+    const float* x = a.x[a.rank] + (size_t)(e & 1u) * a.half;
+    const int e4 = a.E >> 2, items = a.npairs * e4;
+    for (int i = blockIdx.x * 256 + threadIdx.x; i < items; i += gridDim.x * 256) {
+        const int pair = i / e4, c = i - pair * e4;
+        const int o = ep_owner(__ldcg(a.ids + pair), a);
+        if (o == a.rank || o < 0 || o >= a.world) continue;
+        reinterpret_cast<float4*>(a.v + (size_t)pair * a.E)[c] = __ldcg(reinterpret_cast<const float4*>(x + (size_t)pair * a.E) + c);
+    }
+}
+
 __global__ void k_prefill_shift(const float* __restrict__ h, const float* __restrict__ hprev, float* __restrict__ dst, int E, int zero_first) {
     const int t = blockIdx.x;   // dst row t = h row t - 1, row 0 = the remembered row (or zeros at position 0)
     const float* src = t == 0 ? hprev : h + (size_t)(t - 1) * E;
@@ -837,7 +900,7 @@ int Engine::spec_round(const int* slots, int S, int n, const int* subst, int* ou
     const int key = (S - 1) * 8 + n;
     HP_CUDA(cudaEventRecord(ev0_, s_));
     if (no_graph) HP_TRY(enqueue_round(S, n));
-    else if (c_.ep_world > 1) {
+    else if (c_.ep_world > 1 && !ep_peer_) {
         if (!warmed_[key]) { HP_TRY(enqueue_round(S, n)); HP_TRY(sync_stream()); warmed_[key] = true; goto done; }   // first call: eager
         if (ep_segs_[key].empty()) HP_TRY(capture_segments(key, S, n));
         for (const EpSeg& sg : ep_segs_[key]) {
@@ -998,10 +1061,10 @@ int Engine::ep_exchange_us(int R, int reps, float* us) {
     if (c_.ep_world <= 1) return HP_OK;
     HP_TRY(ep_ready());
     const size_t n = (size_t)R * (c_.n_expert_used + 1) * c_.n_embd;
-    HP_CUDA(cudaMemsetAsync(moe_v_, 0, n * 4, s_));
-    HP_TRY(ep_exchange(moe_v_, n));   // warm-up
+    if (!ep_peer_) HP_CUDA(cudaMemsetAsync(moe_v_, 0, n * 4, s_));
+    HP_TRY(ep_peer_ ? ep_exchange_peer(R, 0, false) : ep_exchange(moe_v_, n));   // warm-up
     HP_CUDA(cudaEventRecord(ev0_, s_));
-    for (int i = 0; i < reps; ++i) HP_TRY(ep_exchange(moe_v_, n));
+    for (int i = 0; i < reps; ++i) HP_TRY(ep_peer_ ? ep_exchange_peer(R, 0, false) : ep_exchange(moe_v_, n));
     HP_CUDA(cudaEventRecord(ev1_, s_));
     HP_TRY(sync_stream());
     float ms = 0; HP_CUDA(cudaEventElapsedTime(&ms, ev0_, ev1_)); *us = ms * 1000.f / reps;
@@ -1015,6 +1078,72 @@ int Engine::ep_init(const void* id128) {
     NcclId id; memcpy(id.b, id128, 128);
     HP_TRY(nccl_check(g_nccl.CommInitRank(&nccl_comm_, c_.ep_world, id, c_.ep_rank), "ncclCommInitRank"));
     ep_world_ = c_.ep_world; ep_failed_ = false;
+    // the peer-memory exchange when every rank can map every other rank's buffers; the NCCL collective otherwise
+    static const bool want_peer = getenv("HIPSTER_B200_EP_NCCL") == nullptr;
+    if (want_peer) HP_TRY(ep_peer_setup());
+    return HP_OK;
+}
+// Exchange buffers and flag words of this rank, exported through CUDA IPC handles that travel in one all-gather; the mode
+// is taken only if EVERY rank mapped every peer (agreed by an all-reduce of the outcome), so that no rank waits for flags
+// that another one will never write.
+int Engine::ep_peer_setup() {
+    struct Handles { cudaIpcMemHandle_t x, c; };
+    static_assert(sizeof(Handles) == 128, "two IPC handles");
+    const int W = c_.ep_world, me = c_.ep_rank;
+    HP_REQUIRE(W <= 8, "ep_peer_setup: at most 8 ranks");
+    ep_half_ = (size_t)MAXR * (c_.n_expert_used + 1) * c_.n_embd;
+    int okv = 1;
+    if (cudaMalloc((void**)&ep_xbuf_, 2 * ep_half_ * 4) != cudaSuccess || cudaMalloc((void**)&ep_ctl_, 64) != cudaSuccess) { cudaGetLastError(); okv = 0; }
+    Handles mine; memset(&mine, 0, sizeof(mine));
+    if (okv) {
+        HP_CUDA(cudaMemset(ep_ctl_, 0, 64));
+        if (cudaIpcGetMemHandle(&mine.x, ep_xbuf_) != cudaSuccess || cudaIpcGetMemHandle(&mine.c, ep_ctl_) != cudaSuccess) { cudaGetLastError(); okv = 0; }
+    }
+    char* d_h = nullptr; HP_CUDA(cudaMalloc((void**)&d_h, (size_t)128 * (W + 1) + 16));
+    HP_CUDA(cudaMemcpy(d_h, &mine, 128, cudaMemcpyHostToDevice));
+    int rc = nccl_check(g_nccl.AllGather(d_h, d_h + 128, 128, /* ncclChar */ 0, nccl_comm_, s_), "ncclAllGather");
+    if (rc == HP_OK) rc = sync_stream();
+    std::vector<Handles> all(W);
+    if (rc == HP_OK && cudaMemcpy(all.data(), d_h + 128, (size_t)128 * W, cudaMemcpyDeviceToHost) != cudaSuccess) rc = HP_ECUDA;
+    if (rc != HP_OK) { cudaFree(d_h); return rc; }
+    for (int q = 0; q < W && okv; ++q) {
+        if (q == me) { ep_peer_x_[q] = ep_xbuf_; ep_peer_ctl_[q] = ep_ctl_; continue; }
+        void *px = nullptr, *pc = nullptr;
+        if (cudaIpcOpenMemHandle(&px, all[q].x, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { cudaGetLastError(); okv = 0; break; }
+        ep_peer_x_[q] = (float*)px;
+        if (cudaIpcOpenMemHandle(&pc, all[q].c, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { cudaGetLastError(); okv = 0; break; }
+        ep_peer_ctl_[q] = (unsigned*)pc;
+    }
+    // agreement: the minimum of the ranks' outcomes
+    float* d_ok = (float*)(d_h + 128 * (W + 1)); const float fok = (float)okv; float agreed = 0.f;
+    HP_CUDA(cudaMemcpy(d_ok, &fok, 4, cudaMemcpyHostToDevice));
+    rc = nccl_check(g_nccl.AllReduce(d_ok, d_ok, 1, /* ncclFloat32 */ 7, /* ncclMin */ 3, nccl_comm_, s_), "ncclAllReduce");
+    if (rc == HP_OK) rc = sync_stream();
+    if (rc == HP_OK && cudaMemcpy(&agreed, d_ok, 4, cudaMemcpyDeviceToHost) != cudaSuccess) rc = HP_ECUDA;
+    cudaFree(d_h);
+    if (rc != HP_OK) return rc;
+    ep_peer_ = agreed > 0.5f;
+    if (!ep_peer_) ep_peer_teardown();
+    return HP_OK;
+}
+void Engine::ep_peer_teardown() {
+    for (int q = 0; q < 8; ++q) {
+        if (q != c_.ep_rank) { if (ep_peer_x_[q]) cudaIpcCloseMemHandle(ep_peer_x_[q]); if (ep_peer_ctl_[q]) cudaIpcCloseMemHandle(ep_peer_ctl_[q]); }
+        ep_peer_x_[q] = nullptr; ep_peer_ctl_[q] = nullptr;
+    }
+    if (ep_xbuf_) cudaFree(ep_xbuf_);
+    if (ep_ctl_) cudaFree(ep_ctl_);
+    ep_xbuf_ = nullptr; ep_ctl_ = nullptr; ep_peer_ = false;
+}
+int Engine::ep_exchange_peer(int R, int sh_owner, bool pushed) {
+    HP_TRY(ep_ready());
+    EpXArgs a; a.v = moe_v_; a.ids = moe_ids_; a.npairs = R * (c_.n_expert_used + 1); a.E = c_.n_embd; a.n_expert = c_.n_expert; a.world = c_.ep_world; a.rank = c_.ep_rank;
+    a.sh_owner = sh_owner; a.half = ep_half_; a.err = err_;
+    for (int q = 0; q < 8; ++q) { a.x[q] = ep_peer_x_[q]; a.ctl[q] = ep_peer_ctl_[q]; }
+    const int items = a.npairs * (a.E >> 2), grid = std::max(1, std::min(64, (items + 2047) / 2048));
+    if (!pushed) k_ep_push<<<grid, 256, 0, s_>>>(a);   // the quad form of the down projection has delivered its outputs itself
+    k_ep_gather<<<grid, 256, 0, s_>>>(a);
+    HP_CUDA(cudaGetLastError());
     return HP_OK;
 }
 // a model loaded as one shard of an expert-parallel group must not run a pass before (or after a failure of) its
@@ -1025,6 +1154,12 @@ int Engine::ep_ready() {
     return HP_ESTATE;
 }
 void Engine::ep_destroy() {
+    if (ep_peer_ && nccl_comm_) {
+        // nobody may still be pushing into this rank's exchange buffer when it is freed: one collective as a barrier
+        // (bounded like every other wait on this stream)
+        if (ep_ctl_ && g_nccl.AllReduce(ep_ctl_ + 12, ep_ctl_ + 12, 1, 7, 0, nccl_comm_, s_) == 0) sync_stream();
+    }
+    if (ep_xbuf_ || ep_ctl_) { cudaStreamSynchronize(s_); ep_peer_teardown(); }
     if (nccl_comm_ && g_nccl.CommDestroy) { cudaStreamSynchronize(s_); g_nccl.CommDestroy(nccl_comm_); }
     nccl_comm_ = nullptr;
 }

@@ -56,6 +56,7 @@ public:
     size_t pass_weight_bytes(bool mtp, bool with_head) const;
     int moe_touched(unsigned long long* n);                 // touched (layer, expert) matrices since the last call (measurement)
     int ep_exchange_us(int R, int reps, float* us);          // mean device time of one exchange for R rows (measurement)
+    bool ep_peer() const { return ep_peer_; }
     int last_round_kernels() const { return last_round_kernels_; }
     int profile_pass(int R, int what, int reps, float* ms);
 private:
@@ -100,6 +101,14 @@ private:
     XQ8F xq_{nullptr, nullptr}, xq2_{nullptr, nullptr};
     float *rlogits_ = nullptr, *moe_w_ = nullptr, *moe_v_ = nullptr; void* moe_segs_ = nullptr; int* moe_ctl_ = nullptr; unsigned long long* moe_touched_ = nullptr; int* moe_ids_ = nullptr; int* route_cnt_ = nullptr; Lin moe_out_;
     int e_lo_ = 0, e_hi_ = 0, ep_world_ = 1; void* nccl_comm_ = nullptr; bool ep_failed_ = false;
+    // Peer-memory form of the expert-parallel exchange (one process per GPU, buffers mapped through CUDA IPC): every rank
+    // pushes the output rows of the experts it owns into the other ranks' exchange buffers and raises a flag there.
+    bool ep_peer_ = false;
+    float* ep_xbuf_ = nullptr; size_t ep_half_ = 0;             // own exchange buffer: two halves of MAXR * slots * E floats, used in turn
+    unsigned* ep_ctl_ = nullptr;                                // own words: [q] = last exchange rank q has delivered, [8] = exchanges done, [9] = ticket
+    float* ep_peer_x_[8] = {}; unsigned* ep_peer_ctl_[8] = {};  // the ranks' buffers as mapped here (own rank: the own pointers)
+    int ep_peer_setup(); void ep_peer_teardown();
+    int ep_exchange_peer(int R, int sh_owner, bool pushed);
     int *d_desc_ = nullptr, *h_desc_ = nullptr;                  // device / pinned host descriptor
     int *d_ids_ = nullptr, *d_mids_ = nullptr; float *d_vals_ = nullptr, *d_mvals_ = nullptr; void* am_scratch_ = nullptr;
     int *d_spec_ = nullptr, *h_spec_ = nullptr;                   // fused round state (device) / results (pinned host)

@@ -127,9 +127,16 @@ struct MoeGroupParams {
     float* v;                                           // per-pair outputs [T * nslot][E] (pairs of experts owned elsewhere are not written)
     void* segs; int* ctl;                               // filled by moe_route_group: MOE_MAX_PAIRS segments of 64 bytes, 4 control ints
     int* err;
+    // Expert parallelism over peer memory (ep_world > 1, optional): the down projection also stores every output it
+    // computes into the other ranks' exchange buffers (half (n & 1) of it for exchange number n) and, when the whole grid
+    // is done, raises this rank's flag word there. ep_ctl[q] = rank q's words: [r] = last exchange delivered by rank r,
+    // [8] = exchanges this rank has completed, [9] = ticket.
+    int ep_world = 1, ep_rank = 0; float* ep_x[8] = {}; unsigned* ep_ctl[8] = {}; size_t ep_half = 0;
 };
 size_t moe_seg_bytes();
-int moe_experts_grouped(const MoeGroupParams& p, cudaStream_t s);   // reference gemv_moe + moe_silu_quant + gemv_moe_down (gemv.h:43-50, fn.hip:206-211)
+// *pushed (nullable): set to 1 when the down projection delivered its outputs to the peers itself (the quad form), 0 when the
+// caller has to send them
+int moe_experts_grouped(const MoeGroupParams& p, cudaStream_t s, int* pushed = nullptr);   // reference gemv_moe + moe_silu_quant + gemv_moe_down (gemv.h:43-50, fn.hip:206-211)
 // y[t] = sum over slots e in order of fmaf(slotw[t][e], v[(t, e)], acc) (reference combine, gemv.hip:1104-1112)
 int moe_combine(const float* v, const float* slotw, float* y, int T, int nslot, int E, cudaStream_t s);
 

@@ -277,6 +277,7 @@ struct MoeGArgs {
     float* y; int N;                                // MODE 1: y[pair][N]
     int8_t* oq; float* osc; int F;                  // MODE 0: quantised silu(gate) * up per pair, F features
     int* err;
+    int ep_world, ep_rank; float* ep_x[8]; unsigned* ep_ctl[8]; size_t ep_half;   // MODE 1 of the quad form: peers to deliver y to (ep_world <= 1: none)
 };
 // MODE 0: gate|up with the fused SiLU-gated product + quantisation; MODE 1: down projection (per-pair f32 outputs)
 template <int MODE, int SB, int MOE_WARPS, int MOE_DEPTH>
@@ -438,6 +439,9 @@ __global__ void __launch_bounds__(MQ_WARPS * 32, 1) k_moe_gemv_quad(MoeGArgs a) 
     __syncwarp();
     pdl_wait();
     const int spt = a.nb / SB, ups = a.tiles / MOE_UNIT_TILES;   // stages per tile, units per segment
+    // expert parallelism: number of the exchange this launch feeds, and the half of the peers' buffers it goes to
+    unsigned ep_e = 0u; size_t ep_off = 0;
+    if constexpr (MODE == 1) { if (a.ep_world > 1) { ep_e = __ldcg(a.ep_ctl[a.ep_rank] + 8) + 1u; ep_off = (size_t)(ep_e & 1u) * a.ep_half; } }
     const int total = a.ctl[0] * ups, nquads = (int)gridDim.x * MQ_QUADS, gq = (int)blockIdx.x * MQ_QUADS + quad;
     const int u_lo = (int)((long long)gq * total / nquads), u_hi = (int)((long long)(gq + 1) * total / nquads);
     const size_t tile_bytes = (size_t)a.nb * 2304;
@@ -537,6 +541,14 @@ __global__ void __launch_bounds__(MQ_WARPS * 32, 1) k_moe_gemv_quad(MoeGArgs a) 
             if (ok) {
                 if (c0 >= 0) { a.y[(size_t)c0 * a.N + tile * 16 + g] = acc0.x; a.y[(size_t)c0 * a.N + tile * 16 + g + 8] = acc1.x; }
                 if (c1 >= 0) { a.y[(size_t)c1 * a.N + tile * 16 + g] = acc0.y; a.y[(size_t)c1 * a.N + tile * 16 + g + 8] = acc1.y; }
+                // the same values into every other rank's exchange buffer: the transfer rides on the stores, tile by tile
+                // (the 8 lanes that share t write 32 consecutive bytes of a pair's row)
+                for (int q = 0; q < a.ep_world; ++q) {
+                    if (a.ep_world <= 1 || q == a.ep_rank) continue;
+                    float* py = a.ep_x[q] + ep_off;
+                    if (c0 >= 0) { py[(size_t)c0 * a.N + tile * 16 + g] = acc0.x; py[(size_t)c0 * a.N + tile * 16 + g + 8] = acc1.x; }
+                    if (c1 >= 0) { py[(size_t)c1 * a.N + tile * 16 + g] = acc0.y; py[(size_t)c1 * a.N + tile * 16 + g + 8] = acc1.y; }
+                }
             }
         } else {
             // rows g = gate of feature 8 * tile + g, rows g + 8 = up of the same feature; the unit's 4 tiles (this quad's 4
@@ -578,6 +590,20 @@ __global__ void __launch_bounds__(MQ_WARPS * 32, 1) k_moe_gemv_quad(MoeGArgs a) 
             }
         }
         if (++c_us == ups) { c_us = 0; ++cseg; }
+    }
+    if constexpr (MODE == 1) {
+        if (a.ep_world > 1) {   // every CTA's deliveries are visible system-wide before the last one raises this rank's flag on the peers
+            unsigned* ctl = a.ep_ctl[a.ep_rank];
+            __threadfence_system();
+            __syncthreads();
+            if (threadIdx.x == 0 && atomicAdd(ctl + 9, 1u) == gridDim.x - 1) {
+                __threadfence_system();
+                for (int q = 0; q < a.ep_world; ++q)
+                    if (q != a.ep_rank) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.ep_ctl[q] + a.ep_rank), "r"(ep_e) : "memory");
+                ctl[9] = 0u; __threadfence();
+                atomicExch(ctl + 8, ep_e);
+            }
+        }
     }
 }
 
@@ -643,15 +669,19 @@ static int launch_quad(const MoeGArgs& a, size_t smem, cudaStream_t s) {
 }
 // the quad form when the three quads' activation buffers fit beside the rings (K <= 2048 for the gate|up projection),
 // the one-warp-per-unit form otherwise
+static size_t quad_smem(const MoeGArgs& a) { const int sb = a.nb % 2 == 0 ? 2 : 1, depth = sb == 2 ? 3 : 6; return (size_t)MQ_WARPS * depth * sb * 2304 + MQ_AUX + (size_t)MQ_QUADS * a.nb * 2560; }
+static bool quad_form(const MoeGArgs& a) {
+    static const bool v1 = getenv("HIPSTER_B200_MOE_UNITS") != nullptr;
+    return !v1 && quad_smem(a) <= 227 * 1024 && a.tiles % MOE_UNIT_TILES == 0;
+}
 template <int MODE>
 static int launch_experts(const MoeGArgs& a, bool few, cudaStream_t s) {
-    static const bool v1 = getenv("HIPSTER_B200_MOE_UNITS") != nullptr;
-    const int sb = a.nb % 2 == 0 ? 2 : 1, depth = sb == 2 ? 3 : 6;
-    const size_t smem = (size_t)MQ_WARPS * depth * sb * 2304 + MQ_AUX + (size_t)MQ_QUADS * a.nb * 2560;
-    if (v1 || smem > 227 * 1024 || a.tiles % MOE_UNIT_TILES != 0) return launch_grouped_sb<MODE>(a, few, s);
+    const int sb = a.nb % 2 == 0 ? 2 : 1;
+    const size_t smem = quad_smem(a);
+    if (!quad_form(a)) return launch_grouped_sb<MODE>(a, few, s);
     return sb == 2 ? launch_quad<MODE, 2, 3>(a, smem, s) : launch_quad<MODE, 1, 6>(a, smem, s);
 }
-int moe_experts_grouped(const MoeGroupParams& p, cudaStream_t s) {
+int moe_experts_grouped(const MoeGroupParams& p, cudaStream_t s, int* pushed) {
     HP_REQUIRE(p.E % 256 == 0 && p.F % 256 == 0 && p.T >= 1 && p.nslot >= 1 && p.T * p.nslot <= MOE_MAX_PAIRS, "moe_experts_grouped: bad shape");
     HP_REQUIRE(p.segs && p.ctl && p.v, "moe_experts_grouped: null pointer");
     MoeGArgs a; a.e_lo = p.e_lo; a.segs = (const MoeSeg*)p.segs; a.ctl = p.ctl; a.err = p.err;
@@ -659,12 +689,20 @@ int moe_experts_grouped(const MoeGroupParams& p, cudaStream_t s) {
     a.w_exp = (const uint8_t*)p.w_gate_up; a.w_sh = (const uint8_t*)p.sh_gate_up; a.tiles = 2 * p.F / 16; a.nb = p.E / 256; a.ticket = 1;
     a.xq = (const uint8_t*)p.xq.q; a.xsc = (const float*)p.xq.sc; a.xK = p.E; a.xdiv = p.nslot;
     a.y = nullptr; a.N = 0; a.oq = (int8_t*)p.xq2.q; a.osc = (float*)p.xq2.sc; a.F = p.F;
+    a.ep_world = 1; a.ep_rank = 0; a.ep_half = 0; for (int q = 0; q < 8; ++q) { a.ep_x[q] = nullptr; a.ep_ctl[q] = nullptr; }
+    if (pushed) *pushed = 0;
     const bool few = p.T <= 4;
     { const int rc = launch_experts<0>(a, few, s); if (rc != HP_OK) return rc; }
     // down: [E rows][F]; per-pair outputs
     a.w_exp = (const uint8_t*)p.w_down; a.w_sh = (const uint8_t*)p.sh_down; a.tiles = p.E / 16; a.nb = p.F / 256; a.ticket = 2;
     a.xq = (const uint8_t*)p.xq2.q; a.xsc = (const float*)p.xq2.sc; a.xK = p.F; a.xdiv = 1;
     a.y = p.v; a.N = p.E; a.oq = nullptr; a.osc = nullptr;
+    if (p.ep_world > 1 && p.ep_x[p.ep_rank] && quad_form(a)) {
+        HP_REQUIRE(p.ep_world <= 8 && p.ep_rank >= 0 && p.ep_rank < p.ep_world && p.ep_half >= (size_t)p.T * p.nslot * p.E, "moe_experts_grouped: bad peer arguments");
+        a.ep_world = p.ep_world; a.ep_rank = p.ep_rank; a.ep_half = p.ep_half;
+        for (int q = 0; q < p.ep_world; ++q) { a.ep_x[q] = p.ep_x[q]; a.ep_ctl[q] = p.ep_ctl[q]; }
+        if (pushed) *pushed = 1;
+    }
     { const int rc = launch_experts<1>(a, few, s); if (rc != HP_OK) return rc; }
     HP_CUDA(cudaGetLastError()); return HP_OK;
 }

@@ -178,6 +178,10 @@ class Engine:
         check(lib().hp_ep_exchange_us(self._h, R, reps, ctypes.byref(us)))
         return us.value
 
+    def ep_peer(self):
+        """True when the expert-parallel exchange runs over peer memory, False when it is the NCCL collective."""
+        return bool(lib().hp_ep_peer(self._h))
+
     def last_round_kernels(self):
         return lib().hp_last_round_kernels(self._h)
 

@@ -219,6 +219,10 @@ int hp_profile_pass(hp_engine* e, int R, int what, int reps, float* ms_out);
  * of one expert-parallel exchange for R rows (0 on a single GPU); the kernels in the last fused round's graph. */
 int hp_moe_touched(hp_engine* e, unsigned long long* n_out);
 int hp_ep_exchange_us(hp_engine* e, int R, int reps, float* us_out);
+/* 1 when the expert-parallel exchange runs over peer memory (every rank mapped every other rank's exchange buffer through
+ * CUDA IPC at hp_ep_init: one process per GPU on one node), 0 when it is the NCCL collective (HIPSTER_B200_EP_NCCL set, or a
+ * rank could not map a peer). In the peer form a fused round is one CUDA graph again. No counterpart in the reference. */
+int hp_ep_peer(hp_engine* e);
 int hp_last_round_kernels(const hp_engine* e);
 size_t hp_pass_weight_bytes(const hp_engine* e, int mtp, int with_head);
 /* The whole MTP round on the device, for S slots in lock step: n_draft draft steps (one row per slot each), one verify
