@@ -167,16 +167,17 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 // Launch with the programmatic-dependent-launch attribute: the kernel may start while its predecessor in the stream is
 // still running; it must execute pdl_wait() before touching anything the predecessor writes.
 // Which kernel classes are launched WITHOUT the attribute (bit mask; class 0 counts as 32; the GEMV is 64). Measured on
-// B200: in plain stream launches every class gains from the early launch; inside a captured CUDA graph only the GEMV and
-// the MoE kernels (work before the dependency wait: ring set-up, router rows) do (programmatic edges on the small
-// kernels cost ~0.5 us per launch there), so while a stream is being captured the default mask switches every other
-// class off. HIPSTER_B200_PDL_OFF=<mask> overrides both.
+// B200, class by class: in plain stream launches every class gains from the early launch; inside a captured CUDA graph the
+// GEMV, the MoE kernels (work before the dependency wait: ring set-up, router rows), the SiLU kernel (-0.13 ms per dense
+// round: its CTAs sit beside the gate|up GEMV's and start the moment it ends) and attention gain, while programmatic
+// edges on the row norms and the GDN kernel cost ~0.1 ms per round each, so while a stream is being captured the default
+// mask switches those and the bookkeeping classes off. HIPSTER_B200_PDL_OFF=<mask> overrides both.
 inline int pdl_off_mask(cudaStream_t s) {
     static const int env = [] { const char* e = getenv("HIPSTER_B200_PDL_OFF"); return e ? atoi(e) : -1; }();
     if (env >= 0) return env;
     cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
     if (cudaStreamIsCapturing(s, &st) != cudaSuccess) return 0;
-    return st == cudaStreamCaptureStatusActive ? 0x1B7 : 0;
+    return st == cudaStreamCaptureStatusActive ? 0x0B3 : 0;
 }
 template <int CLS = 0, typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
