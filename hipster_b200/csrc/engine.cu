@@ -628,8 +628,7 @@ struct EpXArgs {
 };
 __device__ __forceinline__ int ep_owner(int id, const EpXArgs& a) {
     if (id < 0) return a.sh_owner;
-    if (id >= a.n_expert) return -1;
-    return (int)(((long long)(id + 1) * a.world - 1) / a.n_expert);
+    return ep_owner_of(id, a.n_expert, a.world);
 }
 __global__ void __launch_bounds__(256) k_ep_push(EpXArgs a) {
     unsigned* ctl = a.ctl[a.rank];

@@ -130,5 +130,11 @@ private:
 };
 
 int ep_wait_poll(int (*stream_query)(void*), int (*comm_error)(void*), void* ctx, int limit_ms);
+// rank that holds routed expert `id` when n_expert experts are cut into `world` contiguous shards [r * n / world,
+// (r + 1) * n / world); -1 for an id outside [0, n_expert)
+__host__ __device__ inline int ep_owner_of(int id, int n_expert, int world) {
+    if (id < 0 || id >= n_expert || world < 1) return -1;
+    return (int)(((long long)(id + 1) * world - 1) / n_expert);
+}
 
 }  // namespace hp

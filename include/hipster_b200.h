@@ -223,6 +223,9 @@ int hp_ep_exchange_us(hp_engine* e, int R, int reps, float* us_out);
  * CUDA IPC at hp_ep_init: one process per GPU on one node), 0 when it is the NCCL collective (HIPSTER_B200_EP_NCCL set, or a
  * rank could not map a peer). In the peer form a fused round is one CUDA graph again. No counterpart in the reference. */
 int hp_ep_peer(hp_engine* e);
+/* Rank that holds routed expert `expert` (contiguous shards [r * n_expert / world, (r + 1) * n_expert / world)); -1 for an id
+ * outside [0, n_expert). The rule the peer-memory exchange uses to tell which rows a rank delivers. */
+int hp_ep_owner(int expert, int n_expert, int world);
 int hp_last_round_kernels(const hp_engine* e);
 size_t hp_pass_weight_bytes(const hp_engine* e, int mtp, int with_head);
 /* The whole MTP round on the device, for S slots in lock step: n_draft draft steps (one row per slot each), one verify

@@ -108,6 +108,18 @@ def test_expert_ranges_partition_the_experts():
         assert ep.owner_of(511, world, 512) == world - 1
 
 
+def test_owner_rule_of_the_peer_exchange_matches_the_shard_ranges():
+    """The device-side rule that decides which rows a rank delivers must agree with the ranges the weights are sharded by."""
+    import hipster_b200 as hb
+    from hipster_b200 import ep
+    L = hb.lib()
+    for n_expert in (16, 100, 512):
+        for world in range(1, 9):
+            for e in range(n_expert):
+                assert L.hp_ep_owner(e, n_expert, world) == ep.owner_of(e, world, n_expert), (e, n_expert, world)
+            assert L.hp_ep_owner(-1, n_expert, world) == -1 and L.hp_ep_owner(n_expert, n_expert, world) == -1
+
+
 # ---- the bounded wait of the engine (hp_ep_wait_poll) with host-made failures: no GPU, no NCCL
 QUERY = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p)
 
