@@ -1099,12 +1099,13 @@ int Engine::ep_peer_setup() {
         if (cudaIpcGetMemHandle(&mine.x, ep_xbuf_) != cudaSuccess || cudaIpcGetMemHandle(&mine.c, ep_ctl_) != cudaSuccess) { cudaGetLastError(); okv = 0; }
     }
     char* d_h = nullptr; HP_CUDA(cudaMalloc((void**)&d_h, (size_t)128 * (W + 1) + 16));
+    struct Free { char* p; ~Free() { cudaFree(p); } } free_d_h{d_h};   // scratch of this function, released on every path
     HP_CUDA(cudaMemcpy(d_h, &mine, 128, cudaMemcpyHostToDevice));
     int rc = nccl_check(g_nccl.AllGather(d_h, d_h + 128, 128, /* ncclChar */ 0, nccl_comm_, s_), "ncclAllGather");
     if (rc == HP_OK) rc = sync_stream();
     std::vector<Handles> all(W);
     if (rc == HP_OK && cudaMemcpy(all.data(), d_h + 128, (size_t)128 * W, cudaMemcpyDeviceToHost) != cudaSuccess) rc = HP_ECUDA;
-    if (rc != HP_OK) { cudaFree(d_h); return rc; }
+    if (rc != HP_OK) return rc;
     for (int q = 0; q < W && okv; ++q) {
         if (q == me) { ep_peer_x_[q] = ep_xbuf_; ep_peer_ctl_[q] = ep_ctl_; continue; }
         void *px = nullptr, *pc = nullptr;
@@ -1119,7 +1120,6 @@ int Engine::ep_peer_setup() {
     rc = nccl_check(g_nccl.AllReduce(d_ok, d_ok, 1, /* ncclFloat32 */ 7, /* ncclMin */ 3, nccl_comm_, s_), "ncclAllReduce");
     if (rc == HP_OK) rc = sync_stream();
     if (rc == HP_OK && cudaMemcpy(&agreed, d_ok, 4, cudaMemcpyDeviceToHost) != cudaSuccess) rc = HP_ECUDA;
-    cudaFree(d_h);
     if (rc != HP_OK) return rc;
     ep_peer_ = agreed > 0.5f;
     if (!ep_peer_) ep_peer_teardown();
