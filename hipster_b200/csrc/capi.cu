@@ -284,6 +284,13 @@ int hp_moe_touched(hp_engine* e, unsigned long long* n_out) { HP_ENGINE_CALL(e->
 int hp_ep_exchange_us(hp_engine* e, int R, int reps, float* us_out) { HP_ENGINE_CALL(e->impl.ep_exchange_us(R, reps, us_out)) }
 int hp_ep_peer(hp_engine* e) { return e && e->impl.ep_peer() ? 1 : 0; }
 int hp_ep_owner(int expert, int n_expert, int world) { return hp::ep_owner_of(expert, n_expert, world); }
+int hp_ep_wait_probe(const void* flags_dev, int world, int rank, unsigned expect, void* stream) {
+    HP_GUARD_BEGIN
+    int* f = hp::device_err_flag();
+    if (!f) { hp::set_error("cannot allocate the device status word"); return HP_ENOMEM; }
+    return hp::ep_wait_probe((const unsigned*)flags_dev, world, rank, expect, f, (cudaStream_t)stream);
+    HP_GUARD_END
+}
 int hp_last_round_kernels(const hp_engine* e) { return e ? e->impl.last_round_kernels() : 0; }
 size_t hp_pass_weight_bytes(const hp_engine* e, int mtp, int with_head) { return e ? e->impl.pass_weight_bytes(mtp != 0, with_head != 0) : 0; }
 int hp_spec_begin(hp_engine* e, int slot, int id_last, int pos, const float* h_pending_dev) { HP_ENGINE_CALL(e->impl.spec_begin(slot, id_last, pos, h_pending_dev)) }

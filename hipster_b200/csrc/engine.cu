@@ -652,19 +652,25 @@ __global__ void __launch_bounds__(256) k_ep_push(EpXArgs a) {
         atomicExch(ctl + 8, e);
     }
 }
-__global__ void __launch_bounds__(256) k_ep_gather(EpXArgs a) {
-    unsigned* ctl = a.ctl[a.rank];
-    const unsigned e = __ldcg(ctl + 8);        // the exchange k_ep_push has just sent
-    if (threadIdx.x < a.world && (int)threadIdx.x != a.rank && __ldcg(a.err) == 0) {   // after a wait has been given up the later ones do not wait again
+// Bounded wait of thread q < world (q != rank) for flags[q] to reach exchange number e: 2^22 polls, then the device status
+// word is set (and once it is set, later waits give up at once: a lost peer costs one limit, not one per exchange).
+__device__ __forceinline__ void ep_wait_flags(const unsigned* flags, int world, int rank, unsigned e, int* err) {
+    if (threadIdx.x < world && (int)threadIdx.x != rank && __ldcg(err) == 0) {
         unsigned f = 0u; int it = 0;
         for (;;) {
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(f) : "l"(ctl + threadIdx.x) : "memory");
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(f) : "l"(flags + threadIdx.x) : "memory");
             if ((int)(f - e) >= 0 || ++it >= (1 << 22)) break;
             __nanosleep(64);
         }
-        if ((int)(f - e) < 0) atomicExch(a.err, HP_ETIMEOUT);   // a peer did not deliver: reported through the device status word
+        if ((int)(f - e) < 0) atomicExch(err, HP_ETIMEOUT);   // a peer did not deliver: reported through the device status word
     }
     __syncthreads();
+}
+__global__ void k_ep_wait_probe(const unsigned* flags, int world, int rank, unsigned e, int* err) { ep_wait_flags(flags, world, rank, e, err); }
+__global__ void __launch_bounds__(256) k_ep_gather(EpXArgs a) {
+    unsigned* ctl = a.ctl[a.rank];
+    const unsigned e = __ldcg(ctl + 8);        // the exchange k_ep_push has just sent
+    ep_wait_flags(ctl, a.world, a.rank, e, a.err);
     const float* x = a.x[a.rank] + (size_t)(e & 1u) * a.half;
     const int e4 = a.E >> 2, items = a.npairs * e4;
     for (int i = blockIdx.x * 256 + threadIdx.x; i < items; i += gridDim.x * 256) {
@@ -1133,6 +1139,13 @@ void Engine::ep_peer_teardown() {
     if (ep_xbuf_) cudaFree(ep_xbuf_);
     if (ep_ctl_) cudaFree(ep_ctl_);
     ep_xbuf_ = nullptr; ep_ctl_ = nullptr; ep_peer_ = false;
+}
+// the gather kernel's wait alone, on caller-provided flag words (one per rank): what a rank does while a peer is silent
+int ep_wait_probe(const unsigned* flags_dev, int world, int rank, unsigned expect, int* err, cudaStream_t s) {
+    HP_REQUIRE(flags_dev && err && world >= 1 && world <= 8 && rank >= 0 && rank < world, "ep_wait_probe: bad arguments");
+    k_ep_wait_probe<<<1, 32, 0, s>>>(flags_dev, world, rank, expect, err);
+    HP_CUDA(cudaGetLastError());
+    return HP_OK;
 }
 int Engine::ep_exchange_peer(int R, int sh_owner, bool pushed) {
     HP_TRY(ep_ready());

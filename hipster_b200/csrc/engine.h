@@ -130,6 +130,7 @@ private:
 };
 
 int ep_wait_poll(int (*stream_query)(void*), int (*comm_error)(void*), void* ctx, int limit_ms);
+int ep_wait_probe(const unsigned* flags_dev, int world, int rank, unsigned expect, int* err, cudaStream_t s);
 // rank that holds routed expert `id` when n_expert experts are cut into `world` contiguous shards [r * n / world,
 // (r + 1) * n / world); -1 for an id outside [0, n_expert)
 __host__ __device__ inline int ep_owner_of(int id, int n_expert, int world) {

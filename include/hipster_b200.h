@@ -226,6 +226,11 @@ int hp_ep_peer(hp_engine* e);
 /* Rank that holds routed expert `expert` (contiguous shards [r * n_expert / world, (r + 1) * n_expert / world)); -1 for an id
  * outside [0, n_expert). The rule the peer-memory exchange uses to tell which rows a rank delivers. */
 int hp_ep_owner(int expert, int n_expert, int world);
+/* The wait of the peer-memory exchange on its own: one launch in which rank `rank` waits until each of the other ranks'
+ * flag words flags_dev[q] (unsigned, q < world) has reached `expect`. The wait is bounded (2^22 polls, about a second):
+ * when a flag stays behind the launch ends, the device status word is set and hp_device_status returns HP_ETIMEOUT; the
+ * context stays usable. For failure-detection tests (a flag that nothing sets). */
+int hp_ep_wait_probe(const void* flags_dev, int world, int rank, unsigned expect, void* stream);
 int hp_last_round_kernels(const hp_engine* e);
 size_t hp_pass_weight_bytes(const hp_engine* e, int mtp, int with_head);
 /* The whole MTP round on the device, for S slots in lock step: n_draft draft steps (one row per slot each), one verify

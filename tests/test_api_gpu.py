@@ -179,3 +179,30 @@ def test_single_token_prefill_zero_rows_and_reset_slot():
         with pytest.raises(hb.HipsterError):
             eng.forward(bad)
     eng.close()
+
+
+def test_peer_exchange_wait_is_bounded_and_reports_through_the_status_word():
+    """The wait of the peer-memory exchange for a flag that nothing sets must run out by itself (about a second), set the
+    device status word (HP_ETIMEOUT through hp_device_status) and leave the context usable; flags that are there pass."""
+    import ctypes
+    import time
+    import torch
+    from hipster_b200 import kernels as K_
+    from hipster_b200._lib import lib, ptr, HipsterError
+    L = lib()
+    K_.device_status()
+    flags = torch.zeros(8, dtype=torch.int32, device="cuda")
+    flags[1] = 5
+    st = torch.cuda.current_stream().cuda_stream
+    assert L.hp_ep_wait_probe(ptr(flags), 2, 0, ctypes.c_uint(5), ctypes.c_void_p(st)) == 0
+    K_.device_status()                                        # rank 1 has delivered exchange 5: no complaint
+    assert L.hp_ep_wait_probe(ptr(flags), 2, 0, ctypes.c_uint(4), ctypes.c_void_p(st)) == 0
+    K_.device_status()                                        # a peer that is ahead is fine too
+    t0 = time.perf_counter()
+    assert L.hp_ep_wait_probe(ptr(flags), 3, 0, ctypes.c_uint(5), ctypes.c_void_p(st)) == 0   # rank 2 never delivers
+    with pytest.raises(HipsterError) as ei:
+        K_.device_status()
+    assert ei.value.code == 4 and "bounded wait" in str(ei.value)        # HP_ETIMEOUT
+    assert time.perf_counter() - t0 < 30.0
+    K_.device_status()                                        # the word was cleared, the context works
+    assert int((flags + 1).sum().item()) == 13
